@@ -1,0 +1,90 @@
+"""Dense building blocks used by the models, with one implementation per device class.
+
+On CUDA tensors every function runs the package's own sm_100a kernels (:mod:`gt_b200.ops.native`: tcgen05 GEMM with
+fused bias / activation / dropout epilogues, fused dropout + residual + LayerNorm, ...) and raises if the extension is
+not built.  On CPU tensors the same mathematics is expressed with PyTorch ops; that path is the oracle of the kernel
+tests and carries the gloo multi-process tests.
+
+    linear(x, w, b, activation, dropout)    y = drop(act(x w^T + b))
+    dropout_add_norm(norm, y, x, bias, p)   norm(x + drop(y + bias))
+    LayerNorm                               nn.LayerNorm whose CUDA forward / backward are the native kernels
+    matmul_tn(a, b) = a^T b,  matmul_nn(a, b) = a b,  linear_nograd   (explicit-backward layers)
+"""
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+def _native():
+    from . import native
+    return native
+
+
+def _use_native(*tensors):
+    return all(t is None or t.is_cuda for t in tensors) and any(t is not None for t in tensors) \
+        and tensors[0].dtype in (torch.bfloat16, torch.float32)
+
+
+def linear(x, weight, bias=None, activation=None, dropout=0.0, training=False):
+    """``drop(act(x @ weight^T + bias))`` with ``activation`` in ``None | 'relu' | 'gelu'``.  ``weight`` is the fp32
+    master parameter; the kernels read a bf16 copy when ``x`` is bf16."""
+    if _use_native(x):
+        return _native().linear(x, weight, bias, activation, dropout if training else 0.0)
+    w = weight.to(x.dtype)
+    y = F.linear(x, w, bias.to(x.dtype) if bias is not None else None)
+    if activation == "relu":
+        y = F.relu(y)
+    elif activation == "gelu":
+        y = F.gelu(y)
+    elif activation is not None:
+        raise ValueError(activation)
+    return F.dropout(y, dropout, training) if dropout > 0 else y
+
+
+@torch.no_grad()
+def linear_nograd(x, weight):
+    if _use_native(x):
+        return _native().gemm_nt(x, weight.to(x.dtype))
+    return x @ weight.to(x.dtype).t()
+
+
+@torch.no_grad()
+def matmul_tn(a, b):
+    """``a^T @ b`` (weight gradients: ``a [M, N]``, ``b [M, K]`` -> ``[N, K]``), fp32 result for bf16 inputs."""
+    if _use_native(a):
+        return _native().gemm_tn(a, b)
+    return a.t() @ b
+
+
+@torch.no_grad()
+def matmul_nn(a, w):
+    """``a @ w`` (input gradients: ``a [M, N]``, ``w [N, K]``) in ``a``'s dtype."""
+    if _use_native(a):
+        return _native().gemm_nn(a, w.to(a.dtype))
+    return a @ w.to(a.dtype)
+
+
+class LayerNorm(nn.LayerNorm):
+    """``nn.LayerNorm`` (same parameters / state-dict keys); CUDA inputs use the native row kernel."""
+
+    def forward(self, x):
+        if _use_native(x):
+            return _native().layer_norm(x, None, None, self.weight, self.bias, self.eps, 0.0)
+        return F.layer_norm(x, self.normalized_shape, self.weight.to(x.dtype), self.bias.to(x.dtype), self.eps)
+
+
+def dropout_add_norm(norm, y, x, bias=None, p=0.0, training=False):
+    """``norm(x + dropout(y + bias))``: the residual step of every branch.  Fused into one kernel for LayerNorm on CUDA."""
+    p = p if training else 0.0
+    if isinstance(norm, LayerNorm) and _use_native(x):
+        return _native().layer_norm(y.to(x.dtype), x, bias, norm.weight, norm.bias, norm.eps, p)
+    y = y.to(x.dtype)
+    if bias is not None:
+        y = y + bias.to(x.dtype)
+    if p > 0:
+        y = F.dropout(y, p, True)
+    return norm(x + y)
+
+
+def gelu(x):
+    return F.gelu(x)

@@ -1,0 +1,100 @@
+"""Distributed Exphormer (every layer kind) vs the single-process reference on gloo CPU ranks, fp64: owned-chunk logits,
+loss, every parameter gradient after the all-reduce, BatchNorm running statistics (dropout 0 makes parity exact)."""
+import pytest
+import torch
+
+from dist_utils import run_dist
+
+CASES = {
+    "plain_2x2": dict(grid=(2, 2)),
+    "plain_4x1_ln": dict(grid=(4, 1), norm="ln"),
+    "plain_gcn_only": dict(grid=(2, 2), with_attn=False),
+    "fused_2x2": dict(grid=(2, 2), fused=True),
+    "fused_1x4_rms": dict(grid=(1, 4), fused=True, norm="rms"),
+    "fused_colmajor": dict(grid=(2, 2), fused=True, layout="col_major"),
+    "fused_nogcn": dict(grid=(2, 2), fused=True, with_gcn=False),
+    "fused_gather_proj": dict(grid=(2, 2), fused=True, gather_proj=True),
+    "fused_sparse": dict(grid=(2, 2), fused=True, sparse_comm=True, sparse_threshold=1.0),
+    "fused_ckpt": dict(grid=(2, 2), fused=True, checkpoint=True),
+    "pipelined": dict(grid=(2, 2), fused=True, pipeline_sub=2),
+    "streamed": dict(grid=(2, 2), fused=True, stream_sub=2),
+    "streamed_sync_ckpt": dict(grid=(2, 2), fused=True, stream_sub=4, stream_overlap=False, checkpoint=True),
+    "streamed_sparse": dict(grid=(2, 2), fused=True, stream_sub=2, sparse_comm=True, sparse_threshold=1.0),
+    "ring": dict(grid=(4, 1), ring=True),
+    "ring_nogcn": dict(grid=(3, 1), ring=True, with_gcn=False),
+    "head_2x1x2": dict(grid=(2, 1, 2), with_gcn=False),
+    "head_1x2x2_gcn": dict(grid=(1, 2, 2)),
+    "head_1x1x4": dict(grid=(1, 1, 4), with_gcn=False),
+    "head_sparse": dict(grid=(2, 1, 2), sparse_comm=True, sparse_threshold=1.0),
+}
+
+
+def _worker(rank, world, case):
+    import sys, os
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from helpers import random_graph
+    from gt_b200.data.expander import random_regular_expander_edges
+    from gt_b200.models.exphormer_dist import DistExphormer
+    from gt_b200.models.exphormer_ref import ExphormerRef, gcn_edges_with_self_loops
+    from gt_b200.parallel.grid import make_grid
+    from gt_b200.parallel.layers import allreduce_grads, dist_cross_entropy, set_step
+    cfg = dict(CASES[case])
+    grid_shape = cfg.pop("grid")
+    layout = cfg.pop("layout", "row_major")
+    n, f, hid, classes, heads = 94, 12, 16, 5, 4
+    torch.manual_seed(0)
+    ei, _ = random_graph(n, 3, seed=3, hub=True, empty=())
+    ei = ei[:, ei[0] != ei[1]]
+    exp = random_regular_expander_edges(n, 2, seed=1)
+    x = torch.randn(n, f, dtype=torch.float64)
+    y = torch.randint(0, classes, (n,))
+    mask = torch.rand(n) < 0.6
+    norm = cfg.get("norm", "bn")
+    with_gcn, with_attn = cfg.get("with_gcn", True), cfg.get("with_attn", True)
+    ref = ExphormerRef(f, hid, classes, 2, heads, dropout=0.0, gnn_dropout=0.0, with_gcn=with_gcn, with_attn=with_attn, norm=norm).double()
+    n_pad = 96
+    grid = make_grid(grid_shape, n, n_pad=n_pad, layout=layout)
+    gcn_blk, _ = grid.local_block(gcn_edges_with_self_loops(ei, n))
+    attn_ei, attn_et = ExphormerRef.build_attention_edges(ei, exp)
+    a_blk, a_et = grid.local_block(attn_ei, attn_et)
+    model = DistExphormer(grid, gcn_blk, a_blk, a_et, f, hid, classes, 2, heads, dropout=0.0, gnn_dropout=0.0, backend="torch", **cfg).double()
+    model.load_ref_state_dict(ref.state_dict())
+    set_step(0)
+    ref.train(); model.train()
+    out_ref = ref(x, ei, exp)
+    loss_ref = torch.nn.functional.cross_entropy(out_ref[mask], y[mask], reduction="sum") / int(mask.sum())
+    loss_ref.backward()
+    out = model(grid.take_owned(x))
+    lo, hi = grid.owned_range()
+    nv = max(min(hi, n) - lo, 0)
+    assert (out[:nv] - out_ref[lo:lo + nv]).abs().max() < 1e-9, (out[:nv] - out_ref[lo:lo + nv]).abs().max()
+    m_loc = grid.take_owned(mask.to(torch.uint8)).bool() & grid.valid_mask
+    loss = dist_cross_entropy(out, grid.take_owned(y), m_loc, int(mask.sum()))
+    loss.backward()
+    params = list(model.parameters())
+    allreduce_grads(params)
+    ref_grads = dict(ref.named_parameters())
+    for name, p in model.named_parameters():
+        gr = ref_grads[name].grad
+        if gr is None:
+            assert p.grad is None or p.grad.abs().max() == 0, name
+            continue
+        err = (p.grad - gr).abs().max().item()
+        assert err < 1e-8 * max(1.0, gr.abs().max().item()), (name, err)
+    if norm == "bn":
+        sd, rsd = model.state_dict(), ref.state_dict()
+        for k in sd:
+            if "running" in k:
+                assert (sd[k] - rsd[k]).abs().max() < 1e-10, k
+    ref.eval(); model.eval()
+    with torch.no_grad():
+        assert (model(grid.take_owned(x))[:nv] - ref(x, ei, exp)[lo:lo + nv]).abs().max() < 1e-9
+
+
+@pytest.mark.parametrize("case", list(CASES))
+def test_dist_exphormer_matches_reference(case):
+    shape = CASES[case]["grid"]
+    world = 1
+    for s in shape:
+        world *= s
+    run_dist(_worker, world, case)
