@@ -1,0 +1,208 @@
+"""Attention back-end on the hand-written sm_100a kernels (``csrc/attn.cu``).
+
+Same contract as :mod:`gt_b200.attention.backend_torch`.  ``q / k / v`` are bf16 or fp32 ``[n, H, d]`` (fp32
+accumulation inside), the partials ``(acc, l, m)`` are fp32.  Shapes the kernels do not tile (a head dim that is not a
+power of two >= 8, ``H * d`` not in {32, 64, 128, 256, 512}, more than 4 edge types) run on the torch-op backend on
+the same device; that is a shape restriction, not a missing-extension fallback: if the extension is not built, every
+call raises.
+
+Extra entry points:
+``attn_fwd_partial_accum``   compact-accumulate forward of the streamed layer: partials of the rows that own an edge
+                             are added in place into the strided reduce-scatter payload (DCSR row list)
+``attn_fwd_partial_pull``    forward that fetches K / V rows from the owners' symmetric buffers over NVLink
+"""
+import math
+
+import torch
+
+from ..ops import native
+from . import backend_torch as _bt
+from .csr import BlockCSR
+
+SEG_EDGES = 256
+_SCORE = {"dot": 0, "gated": 1, "biased": 2}
+_NORM = {"softmax": 0, "clampexp": 1}
+
+
+def _supported(q, gate, bias):
+    h, d = q.shape[1], q.shape[2]
+    t = gate.shape[0] if gate is not None else (bias.shape[0] if bias is not None else 1)
+    return q.dtype in (torch.bfloat16, torch.float32) and native.ext().attn_shape_supported(h, d, t)
+
+
+def _cfg(q, score, norm, clamp, scale):
+    scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else float(scale)
+    return _SCORE[score], _NORM[norm], scale, float(clamp[0]), float(clamp[1])
+
+
+def _plan_list(plan):
+    return [plan.seg_row, plan.seg_beg, plan.seg_end, plan.seg_slot, plan.split_rows, plan.split_ptr]
+
+
+def _tables(gate, bias, score):
+    g = gate.float().contiguous().view(gate.shape[0], -1) if (score == "gated" and gate is not None) else None
+    b = bias.float().contiguous() if (score == "biased" and bias is not None) else None
+    return g, b
+
+
+def _dcsr_plan(blk: BlockCSR, seg_edges):
+    """Plan over the rows that own an edge, plus the map from plan row to block row."""
+    key = ("dcsr_plan", seg_edges)
+    if key not in blk._cache:
+        rows = blk.dcsr_rows()
+        crow = blk.crow.long()
+        ptr = torch.stack([crow[rows.long()], crow[rows.long() + 1]], 1)
+        # pointer array of the compressed rows: edges stay contiguous because the skipped rows are empty
+        cptr = torch.cat([ptr[:, 0], crow[-1:]]) if rows.numel() else crow[:1]
+        from .csr import SegmentPlan, _segments
+        blk._cache[key] = (SegmentPlan(*_segments(cptr, seg_edges), seg_edges), rows)
+        blk._cache[key][0].num_slots
+    return blk._cache[key]
+
+
+def attn_fwd_partial(q, k, v, blk: BlockCSR, gate=None, bias=None, *, score="dot", norm="softmax", clamp=(-5.0, 5.0),
+                     scale=None, seg_edges=SEG_EDGES, k_peers=None, v_peers=None, rows_per_peer=0):
+    if not _supported(q, gate, bias):
+        acc, l, m = _bt.attn_fwd_partial(q.float(), k.float(), v.float(), blk, gate.float() if gate is not None else None,
+                                         bias.float() if bias is not None else None, score=score, norm=norm, clamp=clamp, scale=scale)
+        return acc, l, m
+    n, h, d = q.shape
+    sc, nm, scale, lo, hi = _cfg(q, score, norm, clamp, scale)
+    plan = blk.row_plan(seg_edges)
+    acc = torch.empty(n, h, d, dtype=torch.float32, device=q.device)
+    l = torch.empty(n, h, dtype=torch.float32, device=q.device)
+    m = torch.empty(n, h, dtype=torch.float32, device=q.device)
+    scratch = torch.empty(plan.num_slots, h * d + 2 * h, dtype=torch.float32, device=q.device) if plan.num_slots else None
+    g, b = _tables(gate, bias, score)
+    native.ext().attn_fwd(q.contiguous(), k.contiguous() if k is not None else None, v.contiguous() if v is not None else None,
+                          blk.col, blk.etype, g, b, _plan_list(plan), None, acc, l, m, scratch, h, d, sc, nm, scale, lo, hi,
+                          h * d, h, False, k_peers, v_peers, int(rows_per_peer))
+    return acc, l, m
+
+
+def attn_fwd_partial_pull(q, k_peers, v_peers, rows_per_peer, blk, gate=None, bias=None, **kw):
+    """Forward with K / V read from peer memory: ``k_peers`` / ``v_peers`` are int64 device tensors of buffer addresses."""
+    return attn_fwd_partial(q, None, None, blk, gate, bias, k_peers=k_peers, v_peers=v_peers, rows_per_peer=rows_per_peer, **kw)
+
+
+def attn_fwd_partial_accum(q, k, v, blk: BlockCSR, gate, bias, packed, hd, *, score="gated", norm="clampexp",
+                           clamp=(-5.0, 5.0), scale=None, seg_edges=SEG_EDGES):
+    """Add the block's clamp-exp partials into ``packed[:, :hd]`` (acc) and ``packed[:, hd:hd + H]`` (l) in place."""
+    if norm != "clampexp":
+        raise ValueError("in-place accumulation of partials is only valid for clamp-exp")
+    if blk.num_edges == 0:
+        return
+    n, h, d = q.shape
+    if not _supported(q, gate, bias) or packed.dtype != torch.float32:
+        acc, l, _ = attn_fwd_partial(q, k, v, blk, gate, bias, score=score, norm=norm, clamp=clamp, scale=scale)
+        packed[:, :hd] += acc.reshape(n, hd).to(packed.dtype)
+        packed[:, hd:hd + h] += l.to(packed.dtype)
+        return
+    sc, nm, scale, lo, hi = _cfg(q, score, norm, clamp, scale)
+    plan, rows = _dcsr_plan(blk, seg_edges)
+    scratch = torch.empty(plan.num_slots, h * d + 2 * h, dtype=torch.float32, device=q.device) if plan.num_slots else None
+    g, b = _tables(gate, bias, score)
+    # q rows are addressed through the plan row; the kernel reads q[row] so hand it the compressed q
+    qc = q.reshape(n, hd)[rows.long()].contiguous()
+    stride = packed.stride(0)
+    native.ext().attn_fwd(qc, k.contiguous(), v.contiguous(), blk.col, blk.etype, g, b, _plan_list(plan), rows,
+                          packed, packed[:, hd:], None, scratch, h, d, sc, nm, scale, lo, hi, stride, stride, True, None, None, 0)
+
+
+def normalize(acc, l, norm, eps=1e-6, dtype=None):
+    return _bt.normalize(acc, l, norm, eps, dtype)
+
+
+def _pack_stat(m, row_bias, p_scale):
+    z = torch.zeros_like(m)
+    ps = p_scale if p_scale is not None else torch.ones_like(m)
+    return torch.stack([m.float(), row_bias.float(), ps.float(), z.float()], dim=-1).contiguous()
+
+
+def _bwd(q, k, v, blk, gate, bias, row_vec, stat, score, norm, clamp, scale, seg_edges):
+    n, h, d = q.shape
+    nc = k.shape[0]
+    e = native.ext()
+    sc, nm, scale, lo, hi = _cfg(q, score, norm, clamp, scale)
+    g, b = _tables(gate, bias, score)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    rv = row_vec.to(q.dtype).contiguous()
+    # row pass
+    plan = blk.row_plan(seg_edges)
+    nb = e.attn_bwd_row_blocks(plan.num_segments)
+    dq = torch.empty_like(q)
+    t = g.shape[0] if g is not None else (b.shape[0] if b is not None else 0)
+    dgp = torch.empty(nb, t * h * d, dtype=torch.float32, device=q.device) if g is not None else None
+    dbp = torch.empty(nb, t * h, dtype=torch.float32, device=q.device) if b is not None else None
+    scratch = torch.empty(plan.num_slots, h * d, dtype=torch.float32, device=q.device) if plan.num_slots else None
+    e.attn_bwd_row(q, k, v, rv, stat, blk.col, blk.etype, g, b, _plan_list(plan), None, dq, False, dgp, dbp, nb, scratch,
+                   h, d, sc, nm, scale, lo, hi)
+    dgate = dbias = None
+    if g is not None:
+        dgate = torch.empty(t * h * d, dtype=torch.float32, device=q.device)
+        e.reduce_partials(dgp, dgate)
+        dgate = dgate.view(t, h, d)
+    if b is not None:
+        dbias = torch.empty(t * h, dtype=torch.float32, device=q.device)
+        e.reduce_partials(dbp, dbias)
+        dbias = dbias.view(t, h)
+    # column pass over the transposed structure
+    _, rowidx, et_t, _, _ = blk.csc()
+    cplan = blk.col_plan(seg_edges)
+    dk, dv = torch.empty(nc, h, d, dtype=q.dtype, device=q.device), torch.empty(nc, h, d, dtype=q.dtype, device=q.device)
+    cscratch = torch.empty(cplan.num_slots, 2 * h * d, dtype=torch.float32, device=q.device) if cplan.num_slots else None
+    e.attn_bwd_col(q, k, v, rv, stat, rowidx, et_t, g, b, _plan_list(cplan), dk, dv, cscratch, h, d, sc, nm, scale, lo, hi)
+    return dq, dk, dv, dgate, dbias
+
+
+def attn_bwd_partial(q, k, v, blk: BlockCSR, gate, bias, m, dacc, dl, *, score="dot", norm="softmax", clamp=(-5.0, 5.0),
+                     scale=None, seg_edges=SEG_EDGES):
+    if not _supported(q, gate, bias):
+        f = lambda t: t.float() if t is not None else None          # noqa: E731
+        return _bt.attn_bwd_partial(f(q), f(k), f(v), blk, f(gate), f(bias), f(m), f(dacc), f(dl), score=score, norm=norm,
+                                    clamp=clamp, scale=scale)
+    stat = _pack_stat(m, dl, None)
+    return _bwd(q, k, v, blk, gate, bias, dacc.reshape(q.shape), stat, score, norm, clamp, scale, seg_edges)
+
+
+def attn_bwd(q, k, v, blk: BlockCSR, gate, bias, o, l, m, do, *, score="dot", norm="softmax", clamp=(-5.0, 5.0), eps=1e-6,
+             scale=None, seg_edges=SEG_EDGES):
+    if not _supported(q, gate, bias):
+        f = lambda t: t.float() if t is not None else None          # noqa: E731
+        return _bt.attn_bwd(f(q), f(k), f(v), blk, f(gate), f(bias), f(o), f(l), f(m), f(do), score=score, norm=norm, clamp=clamp,
+                            eps=eps, scale=scale)
+    dd = (do.float() * o.float()).sum(-1)
+    l = l.float()
+    inv = 1.0 / torch.where(l > 0, l, torch.ones_like(l)) if norm == "softmax" else 1.0 / (l + eps)
+    stat = _pack_stat(m, -dd, inv)
+    return _bwd(q, k, v, blk, gate, bias, do.reshape(q.shape), stat, score, norm, clamp, scale, seg_edges)
+
+
+class _MaskedSparseAttentionCuda(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, gate, bias, blk, cfg):
+        score, norm, clamp, eps, scale = cfg
+        acc, l, m = attn_fwd_partial(q, k, v, blk, gate, bias, score=score, norm=norm, clamp=clamp, scale=scale)
+        o = normalize(acc, l, norm, eps).to(q.dtype)
+        ctx.blk, ctx.cfg = blk, cfg
+        ctx.save_for_backward(q, k, v, gate, bias, o, l, m)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, gate, bias, o, l, m = ctx.saved_tensors
+        score, norm, clamp, eps, scale = ctx.cfg
+        dq, dk, dv, dgate, dbias = attn_bwd(q, k, v, ctx.blk, gate, bias, o, l, m, do.contiguous(), score=score, norm=norm,
+                                            clamp=clamp, eps=eps, scale=scale)
+        return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dgate.to(gate.dtype) if dgate is not None else None,
+                dbias.to(bias.dtype) if dbias is not None else None, None, None)
+
+
+def masked_sparse_attention_cuda(q, k, v, blk: BlockCSR, *, gate=None, bias=None, score="dot", norm="softmax",
+                                 clamp=(-5.0, 5.0), eps=1e-6, scale=None):
+    """Differentiable normalised attention over ``blk`` on the native kernels."""
+    if score in ("gated", "biased") and blk.etype is None:
+        raise ValueError(f"score={score!r} needs edge types in the block")
+    scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else float(scale)
+    cfg = (score, norm, (float(clamp[0]), float(clamp[1])), float(eps), scale)
+    return _MaskedSparseAttentionCuda.apply(q, k, v, gate, bias, blk.to(q.device), cfg)

@@ -94,7 +94,10 @@ class SegmentPlan:
 
     @property
     def num_slots(self) -> int:
-        return int(self.split_ptr[-1].item()) if self.split_ptr.numel() else 0
+        # cached as a Python int at first use: the launch wrappers must not synchronise (CUDA-graph capture)
+        if not hasattr(self, "_n_slots"):
+            self._n_slots = int(self.split_ptr[-1].item()) if self.split_ptr.numel() else 0
+        return self._n_slots
 
     def tensors(self):
         return [self.seg_row, self.seg_beg, self.seg_end, self.seg_slot, self.split_rows, self.split_ptr]
@@ -170,12 +173,14 @@ class BlockCSR:
         key = ("row_plan", seg_edges)
         if key not in self._cache:
             self._cache[key] = SegmentPlan(*_segments(self.crow, seg_edges), seg_edges)
+            self._cache[key].num_slots
         return self._cache[key]
 
     def col_plan(self, seg_edges: int = 256) -> SegmentPlan:
         key = ("col_plan", seg_edges)
         if key not in self._cache:
             self._cache[key] = SegmentPlan(*_segments(self.csc()[0], seg_edges), seg_edges)
+            self._cache[key].num_slots
         return self._cache[key]
 
     def dcsr_rows(self) -> torch.Tensor:

@@ -1,0 +1,700 @@
+// Fused structure-masked sparse attention for sm_100a: SDDMM -> (clamp-)softmax -> SpMM in one pass over the CSR,
+// forward and backward, nothing of size [E, H] or [E, H, d] is materialised.
+//
+// Work decomposition.  One warp owns one *segment* of a row (at most seg_edges consecutive CSR entries; rows longer
+// than that -- hubs, the global token -- are cut and merged by a combine kernel: split-KV).  A feature row of H*D
+// elements is cut into chunks of 8 elements (16 bytes of bf16); LPR = min(32, H*D/8) lanes cover one row, so a warp
+// processes 32/LPR edges at once and every K / V row of an edge is fetched by one fully coalesced 16-byte-per-lane
+// transaction.  A head occupies D/8 consecutive lanes; its dot product is finished with log2(D/8) shuffles.  Two edge
+// groups are in flight per iteration (their K / V loads are issued before any arithmetic) to keep enough bytes
+// outstanding per SM for HBM3e.  Why SIMT and not tcgen05 here: with ~20 edges per row the operation moves ~1 KB per
+// edge and does ~1 KFLOP on it (1 FLOP/B against a machine balance of ~215 FLOP/B), so the kernel is bound by the
+// gather traffic; a dense tile formulation would gather the same bytes and add >100x redundant MACs.
+//
+// The same kernels serve every layer kind: `row_map` + `accumulate` implement the compact-accumulate mode of the
+// streamed layer (doubly-compressed row list, partials added in place into the reduce-scatter payload), and the
+// `*_peers` tables let the forward fetch K / V rows straight from the owners' memory over NVLink (receiver-driven pull
+// fused into the kernel: only the rows a tile references cross the switch).
+//
+// Semantics follow the operator specification in gt_b200/attention/ref.py (reference kernels:
+// gt3d/gt3d/attention/triton_kernel.py:38-284, triton_tiled.py:157-479).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace gt {
+
+namespace {
+
+constexpr int kWarpsPerBlock = 4;
+constexpr int kMaxTypesReg = 4;     // edge types whose gate / bias gradients are kept in registers
+
+struct Lanes {
+    int lpr;     // lanes per feature row
+    int lph;     // lanes per head
+    int epw;     // edges per warp iteration
+    int sub;     // my edge slot
+    int ll;      // my lane inside the row
+};
+
+__device__ __forceinline__ Lanes make_lanes(int HD, int D) {
+    Lanes L;
+    int nch = HD >> 3;
+    L.lpr = nch < 32 ? nch : 32;
+    L.lph = D >> 3;
+    L.epw = 32 / L.lpr;
+    int lane = threadIdx.x & 31;
+    L.sub = lane / L.lpr;
+    L.ll = lane - L.sub * L.lpr;
+    return L;
+}
+
+__device__ __forceinline__ float head_sum(float v, int lph) {
+    for (int o = lph >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(GT_FULL_MASK, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float safe_exp_diff(float a, float b) {   // exp(a - b) with exp(-inf - -inf) := 0
+    return (a == -INFINITY) ? 0.f : __expf(a - b);
+}
+
+// shared-memory tables: gate [T, HD] and bias [T, H]
+__device__ __forceinline__ void load_tables(const AttnCommon& c, float* s_gate, float* s_bias) {
+    int HD = c.H * c.D;
+    if (c.score == SCORE_GATED)
+        for (int i = threadIdx.x; i < c.T * HD; i += blockDim.x) s_gate[i] = c.gate[i];
+    if (c.score == SCORE_BIASED)
+        for (int i = threadIdx.x; i < c.T * c.H; i += blockDim.x) s_bias[i] = c.bias[i];
+    __syncthreads();
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// forward
+// ------------------------------------------------------------------------------------------------------------------
+template <typename T, int CPL, bool PEER>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) attn_fwd_kernel(AttnFwdArgs a) {
+    extern __shared__ float smem[];
+    const AttnCommon& c = a.c;
+    const int H = c.H, D = c.D, HD = H * D;
+    float* s_gate = smem;
+    float* s_bias = smem + (c.score == SCORE_GATED ? c.T * HD : 0);
+    load_tables(c, s_gate, s_bias);
+    const Lanes L = make_lanes(HD, D);
+    const int warp = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (warp >= c.plan.n_seg) return;
+    const int row = c.plan.seg_row[warp], beg = c.plan.seg_beg[warp], end = c.plan.seg_end[warp];
+    const int slot = c.plan.seg_slot[warp];
+    const T* q = static_cast<const T*>(a.q);
+    const T* kb = static_cast<const T*>(a.k);
+    const T* vb = static_cast<const T*>(a.v);
+    const bool softmax = c.norm == NORM_SOFTMAX;
+
+    int foff[CPL], head[CPL];
+    float qf[CPL][8], acc[CPL][8], l[CPL], m[CPL];
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) {
+        foff[i] = (L.ll + L.lpr * i) << 3;
+        head[i] = foff[i] / D;
+        Vec8<T>::load(q + (size_t)row * HD + foff[i], qf[i]);
+#pragma unroll
+        for (int x = 0; x < 8; ++x) { qf[i][x] *= c.scale; acc[i][x] = 0.f; }
+        l[i] = 0.f;
+        m[i] = softmax ? -INFINITY : 0.f;
+    }
+
+    for (int base = beg; base < end; base += 2 * L.epw) {
+        int e[2]; bool ok[2]; int j[2], t[2];
+        float kf[2][CPL][8], vf[2][CPL][8];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            e[u] = base + u * L.epw + L.sub;
+            ok[u] = e[u] < end;
+            j[u] = ok[u] ? c.idx[e[u]] : -1;
+            t[u] = (ok[u] && c.etype) ? c.etype[e[u]] : 0;
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            if (j[u] >= 0) {
+                const T* kr; const T* vr;
+                if (PEER) {
+                    int p = j[u] / a.rows_per_peer, r = j[u] - p * a.rows_per_peer;
+                    kr = static_cast<const T*>(a.k_peers[p]) + (size_t)r * HD;
+                    vr = static_cast<const T*>(a.v_peers[p]) + (size_t)r * HD;
+                } else {
+                    kr = kb + (size_t)j[u] * HD;
+                    vr = vb + (size_t)j[u] * HD;
+                }
+#pragma unroll
+                for (int i = 0; i < CPL; ++i) {
+                    Vec8<T>::load_nc(kr + foff[i], kf[u][i]);
+                    Vec8<T>::load_nc(vr + foff[i], vf[u][i]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < CPL; ++i)
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) { kf[u][i][x] = 0.f; vf[u][i][x] = 0.f; }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+#pragma unroll
+            for (int i = 0; i < CPL; ++i) {
+                float s = 0.f;
+                if (c.score == SCORE_GATED) {
+                    const float* g = s_gate + t[u] * HD + foff[i];
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) s = fmaf(qf[i][x] * kf[u][i][x], g[x], s);
+                } else {
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) s = fmaf(qf[i][x], kf[u][i][x], s);
+                }
+                s = head_sum(s, L.lph);
+                if (c.score == SCORE_BIASED) s += s_bias[t[u] * H + head[i]];
+                float p;
+                if (softmax) {
+                    float mn = ok[u] ? fmaxf(m[i], s) : m[i];
+                    float corr = safe_exp_diff(m[i], mn);
+                    p = ok[u] ? __expf(s - mn) : 0.f;
+                    l[i] = l[i] * corr + p;
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) acc[i][x] = fmaf(acc[i][x], corr, p * vf[u][i][x]);
+                    m[i] = mn;
+                } else {
+                    p = ok[u] ? __expf(fminf(fmaxf(s, c.lo), c.hi)) : 0.f;
+                    l[i] += p;
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) acc[i][x] = fmaf(p, vf[u][i][x], acc[i][x]);
+                }
+            }
+        }
+    }
+    // merge the edge slots of the warp
+    for (int off = L.lpr; off < 32; off <<= 1) {
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) {
+            float mo = __shfl_xor_sync(GT_FULL_MASK, m[i], off);
+            float lo_ = __shfl_xor_sync(GT_FULL_MASK, l[i], off);
+            float wa = 1.f, wb = 1.f;
+            if (softmax) {
+                float mn = fmaxf(m[i], mo);
+                wa = safe_exp_diff(m[i], mn);
+                wb = safe_exp_diff(mo, mn);
+                m[i] = mn;
+            }
+            l[i] = l[i] * wa + lo_ * wb;
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+                float ao = __shfl_xor_sync(GT_FULL_MASK, acc[i][x], off);
+                acc[i][x] = acc[i][x] * wa + ao * wb;
+            }
+        }
+    }
+    if (L.sub != 0) return;
+    const bool head_writer = (L.ll & (L.lph - 1)) == 0;
+    if (slot < 0) {
+        const long long orow = a.row_map ? a.row_map[row] : row;
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) {
+            float* dst = a.acc + orow * a.acc_stride + foff[i];
+            if (a.accumulate) {
+                float old[8];
+                Vec8<float>::load(dst, old);
+#pragma unroll
+                for (int x = 0; x < 8; ++x) acc[i][x] += old[x];
+            }
+            Vec8<float>::store(dst, acc[i]);
+            if (head_writer) {
+                float* lp = a.l + orow * a.l_stride + head[i];
+                *lp = a.accumulate ? *lp + l[i] : l[i];
+                if (a.m) a.m[orow * H + head[i]] = (m[i] == -INFINITY) ? 0.f : m[i];
+            }
+        }
+    } else {
+        float* sc = c.scratch + (size_t)slot * (HD + 2 * H);
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) {
+            Vec8<float>::store(sc + foff[i], acc[i]);
+            if (head_writer) { sc[HD + head[i]] = l[i]; sc[HD + H + head[i]] = m[i]; }
+        }
+    }
+}
+
+// merge the slots of the split rows: one block per split row, one thread per feature
+__global__ void attn_fwd_combine_kernel(AttnFwdArgs a) {
+    const AttnCommon& c = a.c;
+    const int H = c.H, D = c.D, HD = H * D, W = HD + 2 * H;
+    const int r = blockIdx.x;
+    const int row = c.plan.split_rows[r];
+    const long long orow = a.row_map ? a.row_map[row] : row;
+    const int s0 = c.plan.split_ptr[r], s1 = c.plan.split_ptr[r + 1];
+    const bool softmax = c.norm == NORM_SOFTMAX;
+    for (int f = threadIdx.x; f < HD; f += blockDim.x) {
+        const int h = f / D;
+        float mx = -INFINITY;
+        if (softmax)
+            for (int s = s0; s < s1; ++s) mx = fmaxf(mx, c.scratch[(size_t)s * W + HD + H + h]);
+        float accv = 0.f, lv = 0.f;
+        for (int s = s0; s < s1; ++s) {
+            const float* sc = c.scratch + (size_t)s * W;
+            float w = softmax ? safe_exp_diff(sc[HD + H + h], mx) : 1.f;
+            accv = fmaf(sc[f], w, accv);
+            lv = fmaf(sc[HD + h], w, lv);
+        }
+        float* dst = a.acc + orow * a.acc_stride + f;
+        *dst = a.accumulate ? *dst + accv : accv;
+        if (f == h * D) {
+            float* lp = a.l + orow * a.l_stride + h;
+            *lp = a.accumulate ? *lp + lv : lv;
+            if (a.m) a.m[orow * H + h] = (!softmax || mx == -INFINITY) ? 0.f : mx;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// backward, row pass: dQ and the per-type gate / bias gradients
+// ------------------------------------------------------------------------------------------------------------------
+template <typename T, int CPL>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) attn_bwd_row_kernel(AttnBwdRowArgs a) {
+    extern __shared__ float smem[];
+    const AttnCommon& c = a.c;
+    const int H = c.H, D = c.D, HD = H * D;
+    float* s_gate = smem;
+    float* s_bias = smem + (c.score == SCORE_GATED ? c.T * HD : 0);
+    float* s_dg = s_bias + (c.score == SCORE_BIASED ? c.T * H : 0);      // [T, HD] or [T, H] block accumulators
+    load_tables(c, s_gate, s_bias);
+    const bool want_dg = c.score == SCORE_GATED && a.dgate_part;
+    const bool want_db = c.score == SCORE_BIASED && a.dbias_part;
+    const int acc_n = want_dg ? c.T * HD : (want_db ? c.T * H : 0);
+    for (int i = threadIdx.x; i < acc_n; i += blockDim.x) s_dg[i] = 0.f;
+    __syncthreads();
+    const Lanes L = make_lanes(HD, D);
+    const bool softmax = c.norm == NORM_SOFTMAX;
+    const T* q = static_cast<const T*>(a.q);
+    const T* kb = static_cast<const T*>(a.k);
+    const T* vb = static_cast<const T*>(a.v);
+    const T* rvb = static_cast<const T*>(a.row_vec);
+    const bool head_writer = (L.ll & (L.lph - 1)) == 0;
+
+    int foff[CPL], head[CPL];
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) { foff[i] = (L.ll + L.lpr * i) << 3; head[i] = foff[i] / D; }
+    float dg[kMaxTypesReg][CPL][8];
+    float db[kMaxTypesReg][CPL];
+#pragma unroll
+    for (int tt = 0; tt < kMaxTypesReg; ++tt)
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) {
+            db[tt][i] = 0.f;
+#pragma unroll
+            for (int x = 0; x < 8; ++x) dg[tt][i][x] = 0.f;
+        }
+
+    const int n_warps = gridDim.x * kWarpsPerBlock;
+    for (int seg = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); seg < c.plan.n_seg; seg += n_warps) {
+        const int row = c.plan.seg_row[seg], beg = c.plan.seg_beg[seg], end = c.plan.seg_end[seg];
+        const int slot = c.plan.seg_slot[seg];
+        const long long srow = a.row_map ? a.row_map[row] : row;     // row of q / row_vec / stat / dq
+        float qf[CPL][8], rv[CPL][8], dq[CPL][8], mrow[CPL], rb[CPL], ps[CPL];
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) {
+            Vec8<T>::load(q + srow * HD + foff[i], qf[i]);
+            Vec8<T>::load(rvb + srow * HD + foff[i], rv[i]);
+            float4 st = a.stat[srow * H + head[i]];
+            mrow[i] = st.x; rb[i] = st.y; ps[i] = st.z;
+#pragma unroll
+            for (int x = 0; x < 8; ++x) { qf[i][x] *= c.scale; dq[i][x] = 0.f; }
+        }
+        for (int base = beg; base < end; base += 2 * L.epw) {
+            int j[2], t[2]; bool ok[2];
+            float kf[2][CPL][8], vf[2][CPL][8];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                int e = base + u * L.epw + L.sub;
+                ok[u] = e < end;
+                j[u] = ok[u] ? c.idx[e] : -1;
+                t[u] = (ok[u] && c.etype) ? c.etype[e] : 0;
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                if (j[u] >= 0) {
+#pragma unroll
+                    for (int i = 0; i < CPL; ++i) {
+                        Vec8<T>::load_nc(kb + (size_t)j[u] * HD + foff[i], kf[u][i]);
+                        Vec8<T>::load_nc(vb + (size_t)j[u] * HD + foff[i], vf[u][i]);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < CPL; ++i)
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) { kf[u][i][x] = 0.f; vf[u][i][x] = 0.f; }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+#pragma unroll
+                for (int i = 0; i < CPL; ++i) {
+                    const float* g = s_gate + t[u] * HD + foff[i];
+                    float s = 0.f, dp = 0.f;
+                    if (c.score == SCORE_GATED) {
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) s = fmaf(qf[i][x] * kf[u][i][x], g[x], s);
+                    } else {
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) s = fmaf(qf[i][x], kf[u][i][x], s);
+                    }
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) dp = fmaf(rv[i][x], vf[u][i][x], dp);
+                    for (int o = L.lph >> 1; o > 0; o >>= 1) {
+                        s += __shfl_xor_sync(GT_FULL_MASK, s, o);
+                        dp += __shfl_xor_sync(GT_FULL_MASK, dp, o);
+                    }
+                    if (c.score == SCORE_BIASED) s += s_bias[t[u] * H + head[i]];
+                    float p, mask = 1.f;
+                    if (softmax) {
+                        p = __expf(s - mrow[i]);
+                    } else {
+                        p = __expf(fminf(fmaxf(s, c.lo), c.hi));
+                        mask = (s >= c.lo && s <= c.hi) ? 1.f : 0.f;
+                    }
+                    float ds = ok[u] ? p * ps[i] * (dp + rb[i]) * mask : 0.f;
+                    if (c.score == SCORE_GATED) {
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) dq[i][x] = fmaf(ds * kf[u][i][x], g[x], dq[i][x]);
+                        if (want_dg) {
+#pragma unroll
+                            for (int tt = 0; tt < kMaxTypesReg; ++tt)
+                                if (t[u] == tt) {
+#pragma unroll
+                                    for (int x = 0; x < 8; ++x) dg[tt][i][x] = fmaf(ds * qf[i][x], kf[u][i][x], dg[tt][i][x]);
+                                }
+                        }
+                    } else {
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) dq[i][x] = fmaf(ds, kf[u][i][x], dq[i][x]);
+                        if (want_db) {
+#pragma unroll
+                            for (int tt = 0; tt < kMaxTypesReg; ++tt)
+                                if (t[u] == tt) db[tt][i] += ds;
+                        }
+                    }
+                }
+            }
+        }
+        for (int off = L.lpr; off < 32; off <<= 1)
+#pragma unroll
+            for (int i = 0; i < CPL; ++i)
+#pragma unroll
+                for (int x = 0; x < 8; ++x) dq[i][x] += __shfl_xor_sync(GT_FULL_MASK, dq[i][x], off);
+        if (L.sub == 0) {
+#pragma unroll
+            for (int i = 0; i < CPL; ++i) {
+#pragma unroll
+                for (int x = 0; x < 8; ++x) dq[i][x] *= c.scale;
+                if (slot >= 0) {
+                    Vec8<float>::store(c.scratch + (size_t)slot * HD + foff[i], dq[i]);
+                } else if (a.accumulate_dq) {
+                    float* dst = static_cast<float*>(a.dq) + srow * HD + foff[i];
+                    float old[8];
+                    Vec8<float>::load(dst, old);
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) old[x] += dq[i][x];
+                    Vec8<float>::store(dst, old);
+                } else {
+                    Vec8<T>::store(static_cast<T*>(a.dq) + srow * HD + foff[i], dq[i]);
+                }
+            }
+        }
+    }
+    // flush the per-type gradients: registers -> shared (atomics) -> this block's row of the partial buffer
+    if (want_dg) {
+#pragma unroll
+        for (int tt = 0; tt < kMaxTypesReg; ++tt)
+            if (tt < c.T)
+#pragma unroll
+                for (int i = 0; i < CPL; ++i)
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) atomicAdd(&s_dg[tt * HD + foff[i] + x], dg[tt][i][x]);
+    }
+    if (want_db && head_writer) {
+#pragma unroll
+        for (int tt = 0; tt < kMaxTypesReg; ++tt)
+            if (tt < c.T)
+#pragma unroll
+                for (int i = 0; i < CPL; ++i) atomicAdd(&s_dg[tt * H + head[i]], db[tt][i]);
+    }
+    __syncthreads();
+    float* part = want_dg ? a.dgate_part + (size_t)blockIdx.x * acc_n : (want_db ? a.dbias_part + (size_t)blockIdx.x * acc_n : nullptr);
+    for (int i = threadIdx.x; i < acc_n; i += blockDim.x) part[i] = s_dg[i];
+}
+
+// out[row] (+)= sum of the row's slots
+template <typename T>
+__global__ void sum_slots_kernel(const SegPlan plan, const float* scratch, int width, const int* row_map, T* out, float* out_f32,
+                                 int accumulate) {
+    const int r = blockIdx.x;
+    const int row = plan.split_rows[r];
+    const long long orow = row_map ? row_map[row] : row;
+    const int s0 = plan.split_ptr[r], s1 = plan.split_ptr[r + 1];
+    for (int f = threadIdx.x; f < width; f += blockDim.x) {
+        float v = 0.f;
+        for (int s = s0; s < s1; ++s) v += scratch[(size_t)s * width + f];
+        if (out_f32) {
+            float* d = out_f32 + orow * width + f;
+            *d = accumulate ? *d + v : v;
+        } else {
+            out[orow * width + f] = from_float<T>(v);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// backward, column pass: dK, dV over the CSC (no atomics)
+// ------------------------------------------------------------------------------------------------------------------
+template <typename T, int CPL>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) attn_bwd_col_kernel(AttnBwdColArgs a) {
+    extern __shared__ float smem[];
+    const AttnCommon& c = a.c;
+    const int H = c.H, D = c.D, HD = H * D;
+    float* s_gate = smem;
+    float* s_bias = smem + (c.score == SCORE_GATED ? c.T * HD : 0);
+    load_tables(c, s_gate, s_bias);
+    const Lanes L = make_lanes(HD, D);
+    const int warp = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (warp >= c.plan.n_seg) return;
+    const int colj = c.plan.seg_row[warp], beg = c.plan.seg_beg[warp], end = c.plan.seg_end[warp];
+    const int slot = c.plan.seg_slot[warp];
+    const bool softmax = c.norm == NORM_SOFTMAX;
+    const T* qb = static_cast<const T*>(a.q);
+    const T* rvb = static_cast<const T*>(a.row_vec);
+
+    int foff[CPL], head[CPL];
+    float kf[CPL][8], vf[CPL][8], dk[CPL][8], dv[CPL][8];
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) {
+        foff[i] = (L.ll + L.lpr * i) << 3;
+        head[i] = foff[i] / D;
+        Vec8<T>::load(static_cast<const T*>(a.k) + (size_t)colj * HD + foff[i], kf[i]);
+        Vec8<T>::load(static_cast<const T*>(a.v) + (size_t)colj * HD + foff[i], vf[i]);
+#pragma unroll
+        for (int x = 0; x < 8; ++x) { dk[i][x] = 0.f; dv[i][x] = 0.f; }
+    }
+    for (int base = beg; base < end; base += 2 * L.epw) {
+        int r[2], t[2]; bool ok[2];
+        float qf[2][CPL][8], rv[2][CPL][8];
+        float4 st[2][CPL];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            int e = base + u * L.epw + L.sub;
+            ok[u] = e < end;
+            r[u] = ok[u] ? c.idx[e] : -1;
+            t[u] = (ok[u] && c.etype) ? c.etype[e] : 0;
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            if (r[u] >= 0) {
+#pragma unroll
+                for (int i = 0; i < CPL; ++i) {
+                    Vec8<T>::load_nc(qb + (size_t)r[u] * HD + foff[i], qf[u][i]);
+                    Vec8<T>::load_nc(rvb + (size_t)r[u] * HD + foff[i], rv[u][i]);
+                    st[u][i] = __ldg(a.stat + (size_t)r[u] * H + head[i]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < CPL; ++i) {
+                    st[u][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) { qf[u][i][x] = 0.f; rv[u][i][x] = 0.f; }
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+#pragma unroll
+            for (int i = 0; i < CPL; ++i) {
+                const float* g = s_gate + t[u] * HD + foff[i];
+                float s = 0.f, dp = 0.f;
+                if (c.score == SCORE_GATED) {
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) s = fmaf(qf[u][i][x] * kf[i][x], g[x], s);
+                } else {
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) s = fmaf(qf[u][i][x], kf[i][x], s);
+                }
+#pragma unroll
+                for (int x = 0; x < 8; ++x) dp = fmaf(rv[u][i][x], vf[i][x], dp);
+                for (int o = L.lph >> 1; o > 0; o >>= 1) {
+                    s += __shfl_xor_sync(GT_FULL_MASK, s, o);
+                    dp += __shfl_xor_sync(GT_FULL_MASK, dp, o);
+                }
+                s *= c.scale;
+                if (c.score == SCORE_BIASED) s += s_bias[t[u] * H + head[i]];
+                float p, mask = 1.f;
+                if (softmax) {
+                    p = __expf(s - st[u][i].x);
+                } else {
+                    p = __expf(fminf(fmaxf(s, c.lo), c.hi));
+                    mask = (s >= c.lo && s <= c.hi) ? 1.f : 0.f;
+                }
+                float P = ok[u] ? p * st[u][i].z : 0.f;
+                float ds = P * (dp + st[u][i].y) * mask * c.scale;
+#pragma unroll
+                for (int x = 0; x < 8; ++x) dv[i][x] = fmaf(P, rv[u][i][x], dv[i][x]);
+                if (c.score == SCORE_GATED) {
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) dk[i][x] = fmaf(ds * qf[u][i][x], g[x], dk[i][x]);
+                } else {
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) dk[i][x] = fmaf(ds, qf[u][i][x], dk[i][x]);
+                }
+            }
+        }
+    }
+    for (int off = L.lpr; off < 32; off <<= 1)
+#pragma unroll
+        for (int i = 0; i < CPL; ++i)
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+                dk[i][x] += __shfl_xor_sync(GT_FULL_MASK, dk[i][x], off);
+                dv[i][x] += __shfl_xor_sync(GT_FULL_MASK, dv[i][x], off);
+            }
+    if (L.sub != 0) return;
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) {
+        if (slot >= 0) {
+            Vec8<float>::store(c.scratch + (size_t)slot * 2 * HD + foff[i], dk[i]);
+            Vec8<float>::store(c.scratch + (size_t)slot * 2 * HD + HD + foff[i], dv[i]);
+        } else {
+            Vec8<T>::store(static_cast<T*>(a.dk) + (size_t)colj * HD + foff[i], dk[i]);
+            Vec8<T>::store(static_cast<T*>(a.dv) + (size_t)colj * HD + foff[i], dv[i]);
+        }
+    }
+}
+
+template <typename T>
+__global__ void sum_slots_kv_kernel(const SegPlan plan, const float* scratch, int HD, T* dk, T* dv) {
+    const int r = blockIdx.x;
+    const int colj = plan.split_rows[r];
+    const int s0 = plan.split_ptr[r], s1 = plan.split_ptr[r + 1];
+    for (int f = threadIdx.x; f < 2 * HD; f += blockDim.x) {
+        float v = 0.f;
+        for (int s = s0; s < s1; ++s) v += scratch[(size_t)s * 2 * HD + f];
+        if (f < HD) dk[(size_t)colj * HD + f] = from_float<T>(v);
+        else dv[(size_t)colj * HD + f - HD] = from_float<T>(v);
+    }
+}
+
+__global__ void reduce_partials_kernel(const float* part, int n_blocks, int width, float* out) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= width) return;
+    float v = 0.f;
+    for (int b = 0; b < n_blocks; ++b) v += part[(size_t)b * width + i];
+    out[i] = v;
+}
+
+size_t table_bytes(const AttnCommon& c) {
+    size_t n = 0;
+    if (c.score == SCORE_GATED) n += (size_t)c.T * c.H * c.D;
+    if (c.score == SCORE_BIASED) n += (size_t)c.T * c.H;
+    return n * sizeof(float);
+}
+
+int cpl_of(int H, int D) { return (H * D / 8) > 32 ? (H * D / 8) / 32 : 1; }
+
+template <typename K>
+void set_smem(K kernel, size_t bytes) {
+    if (bytes > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
+}  // namespace
+
+bool attn_shape_supported(int H, int D, int T) {
+    int HD = H * D;
+    if (D < 8 || (D & (D - 1)) || D > 256) return false;          // a head spans a power-of-two number of 8-chunks
+    int nch = HD / 8;
+    if (nch < 32) { if (nch & (nch - 1)) return false; }
+    else if (nch != 32 && nch != 64) return false;                // H*D in {.., 256, 512}
+    if (D / 8 > 32) return false;
+    if (T > kMaxTypesReg) return false;                           // per-type gradients live in registers
+    return true;
+}
+
+int attn_scratch_width_fwd(int H, int D) { return H * D + 2 * H; }
+
+int attn_bwd_row_blocks(int n_seg) {
+    int want = (n_seg + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    int cap = 148 * 8;
+    return want < cap ? (want > 0 ? want : 1) : cap;
+}
+
+void attn_fwd(const AttnFwdArgs& a, cudaStream_t s) {
+    const AttnCommon& c = a.c;
+    if (c.plan.n_seg == 0) return;
+    const int blocks = (c.plan.n_seg + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    const size_t sm = table_bytes(c);
+    const bool peer = a.k_peers != nullptr;
+    const int cpl = cpl_of(c.H, c.D);
+#define GT_LAUNCH_FWD(TT, CPL, PEER)                                                     \
+    do {                                                                                 \
+        set_smem(attn_fwd_kernel<TT, CPL, PEER>, sm);                                    \
+        attn_fwd_kernel<TT, CPL, PEER><<<blocks, kWarpsPerBlock * 32, sm, s>>>(a);       \
+    } while (0)
+    if (c.dtype == DT_BF16) {
+        if (cpl == 1) { if (peer) GT_LAUNCH_FWD(__nv_bfloat16, 1, true); else GT_LAUNCH_FWD(__nv_bfloat16, 1, false); }
+        else          { if (peer) GT_LAUNCH_FWD(__nv_bfloat16, 2, true); else GT_LAUNCH_FWD(__nv_bfloat16, 2, false); }
+    } else {
+        if (cpl == 1) { if (peer) GT_LAUNCH_FWD(float, 1, true); else GT_LAUNCH_FWD(float, 1, false); }
+        else          { if (peer) GT_LAUNCH_FWD(float, 2, true); else GT_LAUNCH_FWD(float, 2, false); }
+    }
+#undef GT_LAUNCH_FWD
+    if (c.plan.n_split > 0) attn_fwd_combine_kernel<<<c.plan.n_split, 256, 0, s>>>(a);
+}
+
+void attn_bwd_row(const AttnBwdRowArgs& a, cudaStream_t s) {
+    const AttnCommon& c = a.c;
+    if (c.plan.n_seg == 0) return;
+    const int blocks = a.n_blocks > 0 ? a.n_blocks : attn_bwd_row_blocks(c.plan.n_seg);
+    size_t sm = table_bytes(c);
+    if (c.score == SCORE_GATED && a.dgate_part) sm += (size_t)c.T * c.H * c.D * sizeof(float);
+    if (c.score == SCORE_BIASED && a.dbias_part) sm += (size_t)c.T * c.H * sizeof(float);
+    const int cpl = cpl_of(c.H, c.D);
+    const int HD = c.H * c.D;
+#define GT_LAUNCH_ROW(TT, CPL)                                                           \
+    do {                                                                                 \
+        set_smem(attn_bwd_row_kernel<TT, CPL>, sm);                                      \
+        attn_bwd_row_kernel<TT, CPL><<<blocks, kWarpsPerBlock * 32, sm, s>>>(a);         \
+        if (c.plan.n_split > 0)                                                          \
+            sum_slots_kernel<TT><<<c.plan.n_split, 256, 0, s>>>(c.plan, c.scratch, HD, a.row_map,                       \
+                a.accumulate_dq ? nullptr : static_cast<TT*>(a.dq), a.accumulate_dq ? static_cast<float*>(a.dq) : nullptr, \
+                a.accumulate_dq);                                                        \
+    } while (0)
+    if (c.dtype == DT_BF16) { if (cpl == 1) GT_LAUNCH_ROW(__nv_bfloat16, 1); else GT_LAUNCH_ROW(__nv_bfloat16, 2); }
+    else                    { if (cpl == 1) GT_LAUNCH_ROW(float, 1); else GT_LAUNCH_ROW(float, 2); }
+#undef GT_LAUNCH_ROW
+}
+
+void attn_bwd_col(const AttnBwdColArgs& a, cudaStream_t s) {
+    const AttnCommon& c = a.c;
+    if (c.plan.n_seg == 0) return;
+    const int blocks = (c.plan.n_seg + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    const size_t sm = table_bytes(c);
+    const int cpl = cpl_of(c.H, c.D);
+    const int HD = c.H * c.D;
+#define GT_LAUNCH_COL(TT, CPL)                                                           \
+    do {                                                                                 \
+        set_smem(attn_bwd_col_kernel<TT, CPL>, sm);                                      \
+        attn_bwd_col_kernel<TT, CPL><<<blocks, kWarpsPerBlock * 32, sm, s>>>(a);         \
+        if (c.plan.n_split > 0)                                                          \
+            sum_slots_kv_kernel<TT><<<c.plan.n_split, 256, 0, s>>>(c.plan, c.scratch, HD, static_cast<TT*>(a.dk),       \
+                                                                   static_cast<TT*>(a.dv));                              \
+    } while (0)
+    if (c.dtype == DT_BF16) { if (cpl == 1) GT_LAUNCH_COL(__nv_bfloat16, 1); else GT_LAUNCH_COL(__nv_bfloat16, 2); }
+    else                    { if (cpl == 1) GT_LAUNCH_COL(float, 1); else GT_LAUNCH_COL(float, 2); }
+#undef GT_LAUNCH_COL
+}
+
+void reduce_partials(const float* part, int n_blocks, int width, float* out, cudaStream_t s) {
+    if (width <= 0) return;
+    reduce_partials_kernel<<<(width + 255) / 256, 256, 0, s>>>(part, n_blocks, width, out);
+}
+
+}  // namespace gt

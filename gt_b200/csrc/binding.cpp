@@ -1,0 +1,358 @@
+// Python binding of the gt_b200 kernels: translates torch tensors into the POD launch arguments of kernels.h and enqueues
+// on the current CUDA stream.  No kernel allocates; output and scratch tensors are created by the Python wrappers.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <vector>
+
+#include "kernels.h"
+
+namespace {
+
+using torch::Tensor;
+using OptT = c10::optional<Tensor>;
+
+cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+int dt(const Tensor& t) {
+    if (t.scalar_type() == torch::kBFloat16) return gt::DT_BF16;
+    TORCH_CHECK(t.scalar_type() == torch::kFloat32, "expected a float32 or bfloat16 tensor");
+    return gt::DT_F32;
+}
+
+template <typename T>
+const T* cptr(const OptT& t) { return t.has_value() && t->defined() ? static_cast<const T*>(t->data_ptr()) : nullptr; }
+
+void check_cuda_contig(const Tensor& t, const char* name) {
+    TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+    TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+}
+
+gt::SegPlan make_plan(const std::vector<Tensor>& p) {
+    TORCH_CHECK(p.size() == 6, "plan = [seg_row, seg_beg, seg_end, seg_slot, split_rows, split_ptr]");
+    gt::SegPlan s;
+    s.seg_row = p[0].data_ptr<int>(); s.seg_beg = p[1].data_ptr<int>(); s.seg_end = p[2].data_ptr<int>();
+    s.seg_slot = p[3].data_ptr<int>(); s.n_seg = (int)p[0].numel();
+    s.split_rows = p[4].data_ptr<int>(); s.split_ptr = p[5].data_ptr<int>(); s.n_split = (int)p[4].numel();
+    return s;
+}
+
+gt::AttnCommon make_common(const Tensor& q, int64_t H, int64_t D, const Tensor& idx, const OptT& etype, const OptT& gate,
+                           const OptT& bias, const std::vector<Tensor>& plan, const OptT& scratch, int64_t score, int64_t norm,
+                           double scale, double lo, double hi) {
+    gt::AttnCommon c{};
+    c.dtype = dt(q);
+    c.H = (int)H; c.D = (int)D;
+    c.T = gate.has_value() && gate->defined() ? (int)gate->size(0) : (bias.has_value() && bias->defined() ? (int)bias->size(0) : 1);
+    c.score = (int)score; c.norm = (int)norm;
+    c.scale = (float)scale; c.lo = (float)lo; c.hi = (float)hi;
+    c.idx = idx.data_ptr<int>();
+    c.etype = cptr<int>(etype);
+    c.gate = cptr<float>(gate);
+    c.bias = cptr<float>(bias);
+    c.plan = make_plan(plan);
+    c.scratch = scratch.has_value() && scratch->defined() ? scratch->data_ptr<float>() : nullptr;
+    TORCH_CHECK(gt::attn_shape_supported(c.H, c.D, c.T), "attention shape (H=", H, ", D=", D, ", T=", c.T, ") not supported by the kernels");
+    if (c.score != gt::SCORE_DOT) TORCH_CHECK(c.etype != nullptr, "gated / biased scores need edge types");
+    return c;
+}
+
+void attn_fwd(Tensor q, OptT k, OptT v, Tensor idx, OptT etype, OptT gate, OptT bias, std::vector<Tensor> plan, OptT row_map,
+              Tensor acc, Tensor l, OptT m, OptT scratch, int64_t H, int64_t D, int64_t score, int64_t norm, double scale, double lo,
+              double hi, int64_t acc_stride, int64_t l_stride, bool accumulate, OptT k_peers, OptT v_peers, int64_t rows_per_peer) {
+    c10::cuda::CUDAGuard guard(q.device());
+    check_cuda_contig(q, "q");
+    gt::AttnFwdArgs a{};
+    a.c = make_common(q, H, D, idx, etype, gate, bias, plan, scratch, score, norm, scale, lo, hi);
+    a.q = q.data_ptr();
+    a.k = k.has_value() ? k->data_ptr() : nullptr;
+    a.v = v.has_value() ? v->data_ptr() : nullptr;
+    a.k_peers = k_peers.has_value() ? reinterpret_cast<const void* const*>(k_peers->data_ptr()) : nullptr;
+    a.v_peers = v_peers.has_value() ? reinterpret_cast<const void* const*>(v_peers->data_ptr()) : nullptr;
+    a.rows_per_peer = (int)rows_per_peer;
+    TORCH_CHECK(a.k_peers != nullptr || (a.k != nullptr && a.v != nullptr), "k / v or their peer tables are required");
+    a.row_map = cptr<int>(row_map);
+    a.acc = acc.data_ptr<float>(); a.l = l.data_ptr<float>();
+    a.m = m.has_value() && m->defined() ? m->data_ptr<float>() : nullptr;
+    a.acc_stride = acc_stride; a.l_stride = l_stride; a.accumulate = accumulate ? 1 : 0;
+    gt::attn_fwd(a, stream());
+}
+
+int64_t attn_bwd_row_blocks(int64_t n_seg) { return gt::attn_bwd_row_blocks((int)n_seg); }
+
+void attn_bwd_row(Tensor q, Tensor k, Tensor v, Tensor row_vec, Tensor stat, Tensor idx, OptT etype, OptT gate, OptT bias,
+                  std::vector<Tensor> plan, OptT row_map, Tensor dq, bool accumulate_dq, OptT dgate_part, OptT dbias_part,
+                  int64_t n_blocks, OptT scratch, int64_t H, int64_t D, int64_t score, int64_t norm, double scale, double lo, double hi) {
+    c10::cuda::CUDAGuard guard(q.device());
+    gt::AttnBwdRowArgs a{};
+    a.c = make_common(q, H, D, idx, etype, gate, bias, plan, scratch, score, norm, scale, lo, hi);
+    TORCH_CHECK(row_vec.scalar_type() == q.scalar_type(), "row_vec must have the dtype of q");
+    a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr(); a.row_vec = row_vec.data_ptr();
+    a.stat = reinterpret_cast<const float4*>(stat.data_ptr<float>());
+    a.row_map = cptr<int>(row_map);
+    a.dq = dq.data_ptr(); a.accumulate_dq = accumulate_dq ? 1 : 0;
+    a.dgate_part = dgate_part.has_value() && dgate_part->defined() ? dgate_part->data_ptr<float>() : nullptr;
+    a.dbias_part = dbias_part.has_value() && dbias_part->defined() ? dbias_part->data_ptr<float>() : nullptr;
+    a.n_blocks = (int)n_blocks;
+    gt::attn_bwd_row(a, stream());
+}
+
+void attn_bwd_col(Tensor q, Tensor k, Tensor v, Tensor row_vec, Tensor stat, Tensor rowidx, OptT etype_t, OptT gate, OptT bias,
+                  std::vector<Tensor> plan, Tensor dk, Tensor dv, OptT scratch, int64_t H, int64_t D, int64_t score, int64_t norm,
+                  double scale, double lo, double hi) {
+    c10::cuda::CUDAGuard guard(q.device());
+    gt::AttnBwdColArgs a{};
+    a.c = make_common(q, H, D, rowidx, etype_t, gate, bias, plan, scratch, score, norm, scale, lo, hi);
+    a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr(); a.row_vec = row_vec.data_ptr();
+    a.stat = reinterpret_cast<const float4*>(stat.data_ptr<float>());
+    a.dk = dk.data_ptr(); a.dv = dv.data_ptr();
+    gt::attn_bwd_col(a, stream());
+}
+
+void reduce_partials(Tensor part, Tensor out) {
+    c10::cuda::CUDAGuard guard(part.device());
+    gt::reduce_partials(part.data_ptr<float>(), (int)part.size(0), (int)out.numel(), out.data_ptr<float>(), stream());
+}
+
+bool attn_shape_supported(int64_t H, int64_t D, int64_t T) { return gt::attn_shape_supported((int)H, (int)D, (int)T); }
+
+void spmm(Tensor ptr, Tensor idx, OptT w, Tensor x, Tensor out, bool accumulate) {
+    c10::cuda::CUDAGuard guard(x.device());
+    check_cuda_contig(x, "x");
+    TORCH_CHECK(x.size(1) % 8 == 0 && x.size(1) <= 1024, "feature width must be a multiple of 8 and <= 1024");
+    gt::SpmmArgs a{};
+    a.dtype = dt(x); a.ptr = ptr.data_ptr<int>(); a.idx = idx.data_ptr<int>(); a.w = cptr<float>(w);
+    a.x = x.data_ptr(); a.out = out.data_ptr(); a.n_out = (int)out.size(0); a.d = (int)x.size(1); a.accumulate = accumulate ? 1 : 0;
+    gt::spmm(a, stream());
+}
+
+void layer_norm_fwd(Tensor y, OptT x, OptT ybias, Tensor gamma, Tensor beta, Tensor out, OptT mean_rstd, double eps, double p,
+                    OptT seed, int64_t stream_id) {
+    c10::cuda::CUDAGuard guard(y.device());
+    check_cuda_contig(y, "y");
+    TORCH_CHECK(y.size(1) % 8 == 0 && y.size(1) <= 1024, "LayerNorm width must be a multiple of 8 and <= 1024");
+    gt::LayerNormArgs a{};
+    a.dtype = dt(y); a.y = y.data_ptr(); a.x = x.has_value() && x->defined() ? x->data_ptr() : nullptr;
+    a.ybias = cptr<float>(ybias); a.gamma = gamma.data_ptr<float>(); a.beta = beta.data_ptr<float>();
+    a.out = out.data_ptr(); a.mean_rstd = mean_rstd.has_value() && mean_rstd->defined() ? mean_rstd->data_ptr<float>() : nullptr;
+    a.n = (int)y.size(0); a.d = (int)y.size(1); a.eps = (float)eps; a.p = (float)p;
+    a.seed = cptr<long long>(seed); a.stream_id = stream_id;
+    gt::layer_norm_fwd(a, stream());
+}
+
+int64_t layer_norm_bwd_blocks(int64_t n) { return gt::layer_norm_bwd_blocks((int)n); }
+
+void layer_norm_bwd(Tensor dout, Tensor y, OptT x, OptT ybias, Tensor gamma, Tensor mean_rstd, Tensor dy, OptT dx, bool accumulate_dx,
+                    Tensor dgamma_part, Tensor dbeta_part, OptT dybias_part, double p, OptT seed, int64_t stream_id) {
+    c10::cuda::CUDAGuard guard(y.device());
+    gt::LayerNormBwdArgs a{};
+    a.dtype = dt(y); a.dout = dout.data_ptr(); a.y = y.data_ptr(); a.x = x.has_value() && x->defined() ? x->data_ptr() : nullptr;
+    a.ybias = cptr<float>(ybias); a.gamma = gamma.data_ptr<float>(); a.mean_rstd = mean_rstd.data_ptr<float>();
+    a.dy = dy.data_ptr(); a.dx = dx.has_value() && dx->defined() ? dx->data_ptr() : nullptr; a.accumulate_dx = accumulate_dx ? 1 : 0;
+    a.dgamma_part = dgamma_part.data_ptr<float>(); a.dbeta_part = dbeta_part.data_ptr<float>();
+    a.dybias_part = dybias_part.has_value() && dybias_part->defined() ? dybias_part->data_ptr<float>() : nullptr;
+    a.n_blocks = (int)dgamma_part.size(0);
+    a.n = (int)y.size(0); a.d = (int)y.size(1); a.p = (float)p; a.seed = cptr<long long>(seed); a.stream_id = stream_id;
+    gt::layer_norm_bwd(a, stream());
+}
+
+void bias_act_dropout(Tensor in, OptT bias, Tensor out, int64_t act, double p, OptT seed, int64_t stream_id) {
+    c10::cuda::CUDAGuard guard(in.device());
+    TORCH_CHECK(in.size(-1) % 8 == 0, "width must be a multiple of 8");
+    gt::bias_act_dropout(dt(in), in.data_ptr(), cptr<float>(bias), out.data_ptr(), in.numel() / in.size(-1), (int)in.size(-1), (int)act,
+                         (float)p, cptr<long long>(seed), stream_id, stream());
+}
+
+int64_t colsum_blocks(int64_t n) { return gt::colsum_blocks(n); }
+
+void bias_act_dropout_bwd(Tensor dout, OptT in, OptT bias, Tensor dz, int64_t act, double p, OptT seed, int64_t stream_id, OptT dbias_part) {
+    c10::cuda::CUDAGuard guard(dout.device());
+    const int d = (int)dout.size(-1);
+    TORCH_CHECK(d % 8 == 0 && d <= 8192, "width must be a multiple of 8");
+    const long long n = dout.numel() / d;
+    const int n_blocks = dbias_part.has_value() && dbias_part->defined() ? (int)dbias_part->size(0) : gt::colsum_blocks(n);
+    gt::bias_act_dropout_bwd(dt(dout), dout.data_ptr(), in.has_value() && in->defined() ? in->data_ptr() : nullptr, cptr<float>(bias),
+                             dz.data_ptr(), n, d, (int)act, (float)p, cptr<long long>(seed), stream_id,
+                             dbias_part.has_value() && dbias_part->defined() ? dbias_part->data_ptr<float>() : nullptr, n_blocks, stream());
+}
+
+void cross_entropy(Tensor logits, Tensor labels, Tensor mask, double inv_denom, Tensor loss, OptT dlogits) {
+    c10::cuda::CUDAGuard guard(logits.device());
+    check_cuda_contig(logits, "logits");
+    TORCH_CHECK(labels.scalar_type() == torch::kInt64 && mask.scalar_type() == torch::kBool, "labels int64, mask bool");
+    gt::cross_entropy_fwd_bwd(dt(logits), logits.data_ptr(), reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()),
+                              mask.data_ptr<bool>(), (int)logits.size(0), (int)logits.size(1), (float)inv_denom, loss.data_ptr<float>(),
+                              dlogits.has_value() && dlogits->defined() ? dlogits->data_ptr() : nullptr, stream());
+}
+
+void adamw_step(Tensor p, Tensor g, Tensor m, Tensor v, OptT p_bf16, Tensor hyper, OptT decay_mask) {
+    c10::cuda::CUDAGuard guard(p.device());
+    gt::AdamWArgs a{};
+    a.p = p.data_ptr<float>(); a.g = g.data_ptr<float>(); a.m = m.data_ptr<float>(); a.v = v.data_ptr<float>();
+    a.p_bf16 = p_bf16.has_value() && p_bf16->defined() ? p_bf16->data_ptr() : nullptr;
+    a.n = p.numel(); a.hyper = hyper.data_ptr<float>(); a.decay_mask = cptr<float>(decay_mask);
+    gt::adamw_step(a, stream());
+}
+
+void sq_norm(Tensor g, Tensor out) {
+    c10::cuda::CUDAGuard guard(g.device());
+    gt::sq_norm(g.data_ptr<float>(), g.numel(), out.data_ptr<float>(), stream());
+}
+
+void cast_bf16(Tensor in, Tensor out) {
+    c10::cuda::CUDAGuard guard(in.device());
+    gt::cast_f32_to_bf16(in.data_ptr<float>(), out.data_ptr(), in.numel(), stream());
+}
+
+// C[M, N] = epilogue(A[M, K] @ B[N, K]^T)
+void gemm_nt(Tensor a, Tensor b, Tensor c, OptT bias, int64_t act, double p, OptT seed, int64_t stream_id, bool accumulate, Tensor status) {
+    c10::cuda::CUDAGuard guard(a.device());
+    TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16, "bf16 operands expected");
+    TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && c.stride(1) == 1, "row-major operands expected");
+    gt::GemmArgs g{};
+    g.a = a.data_ptr(); g.b = b.data_ptr(); g.c = c.data_ptr();
+    g.M = (int)a.size(0); g.K = (int)a.size(1); g.N = (int)b.size(0);
+    TORCH_CHECK(b.size(1) == a.size(1) && c.size(0) == a.size(0) && c.size(1) == b.size(0), "shape mismatch");
+    g.lda = (int)a.stride(0); g.ldb = (int)b.stride(0); g.ldc = (int)c.stride(0);
+    g.c_dtype = dt(c); g.bias = cptr<float>(bias); g.act = (int)act; g.p = (float)p; g.seed = cptr<long long>(seed);
+    g.stream_id = stream_id; g.accumulate = accumulate ? 1 : 0; g.status = status.data_ptr<int>();
+    TORCH_CHECK(gt::gemm_tcgen05_supported(g.M, g.N, g.K, g.lda, g.ldb, g.ldc), "GEMM shape / strides not supported (K, lda, ldb % 8)");
+    int rc = gt::gemm_tcgen05(g, stream());
+    TORCH_CHECK(rc == 0, "tcgen05 GEMM launch failed with code ", rc);
+}
+
+// C[N, K] (+)= A[M, N]^T @ B[M, K]
+void gemm_tn(Tensor a, Tensor b, Tensor c, bool accumulate, Tensor status) {
+    c10::cuda::CUDAGuard guard(a.device());
+    TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16 && c.scalar_type() == torch::kFloat32,
+                "bf16 operands and an fp32 result expected");
+    TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && c.is_contiguous(), "row-major operands expected");
+    gt::GemmTNArgs g{};
+    g.a = a.data_ptr(); g.b = b.data_ptr(); g.c = c.data_ptr<float>();
+    g.M = (int)a.size(0); g.N = (int)a.size(1); g.K = (int)b.size(1);
+    TORCH_CHECK(b.size(0) == a.size(0) && c.size(0) == a.size(1) && c.size(1) == b.size(1), "shape mismatch");
+    g.lda = (int)a.stride(0); g.ldb = (int)b.stride(0); g.ldc = (int)c.stride(0);
+    g.accumulate = accumulate ? 1 : 0; g.status = status.data_ptr<int>();
+    int rc = gt::gemm_tn_tcgen05(g, stream());
+    TORCH_CHECK(rc == 0, "tcgen05 TN GEMM launch failed with code ", rc);
+}
+
+// ---- symmetric heap: cudaMalloc + CUDA IPC ----------------------------------------------------------------------------
+int64_t heap_alloc(int64_t bytes) {
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, (size_t)bytes);
+    TORCH_CHECK(e == cudaSuccess, "cudaMalloc of the symmetric heap failed: ", cudaGetErrorString(e));
+    cudaMemset(p, 0, (size_t)bytes);
+    return reinterpret_cast<int64_t>(p);
+}
+
+void heap_free(int64_t ptr) { cudaFree(reinterpret_cast<void*>(ptr)); }
+
+py::bytes heap_ipc_handle(int64_t ptr) {
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(ptr));
+    TORCH_CHECK(e == cudaSuccess, "cudaIpcGetMemHandle failed: ", cudaGetErrorString(e));
+    return py::bytes(reinterpret_cast<const char*>(&h), sizeof(h));
+}
+
+int64_t heap_open(py::bytes handle) {
+    std::string s = handle;
+    TORCH_CHECK(s.size() == sizeof(cudaIpcMemHandle_t), "bad IPC handle size");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, s.data(), sizeof(h));
+    void* p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    TORCH_CHECK(e == cudaSuccess, "cudaIpcOpenMemHandle failed: ", cudaGetErrorString(e));
+    return reinterpret_cast<int64_t>(p);
+}
+
+void heap_close(int64_t ptr) { cudaIpcCloseMemHandle(reinterpret_cast<void*>(ptr)); }
+
+Tensor tensor_from_ptr(int64_t ptr, std::vector<int64_t> shape, int64_t dtype_code, int64_t device_index) {
+    auto dtype = dtype_code == 0 ? torch::kFloat32 : dtype_code == 1 ? torch::kBFloat16 : dtype_code == 2 ? torch::kInt32 : dtype_code == 3 ? torch::kInt64 : torch::kUInt8;
+    auto opts = torch::TensorOptions().dtype(dtype).device(torch::kCUDA, (int)device_index);
+    return torch::from_blob(reinterpret_cast<void*>(ptr), shape, [](void*) {}, opts);
+}
+
+void signal_peers(Tensor peer_flag_ptrs, int64_t my_index, int64_t value) {
+    c10::cuda::CUDAGuard guard(peer_flag_ptrs.device());
+    gt::signal_peers(reinterpret_cast<int* const*>(peer_flag_ptrs.data_ptr()), (int)peer_flag_ptrs.numel(), (int)my_index, (int)value, stream());
+}
+
+void wait_flags(Tensor my_flags, int64_t n_peers, int64_t value, int64_t max_spins, Tensor status) {
+    c10::cuda::CUDAGuard guard(my_flags.device());
+    gt::wait_flags(my_flags.data_ptr<int>(), (int)n_peers, (int)value, max_spins, status.data_ptr<int>(), stream());
+}
+
+void pull_gather_rows(Tensor peer_ptrs, Tensor owner, Tensor row, Tensor out) {
+    c10::cuda::CUDAGuard guard(out.device());
+    const int row_bytes = (int)(out.numel() / std::max<int64_t>(out.size(0), 1) * out.element_size());
+    TORCH_CHECK(row_bytes % 16 == 0, "rows must be a multiple of 16 bytes");
+    gt::pull_gather_rows(reinterpret_cast<const void* const*>(peer_ptrs.data_ptr()), owner.data_ptr<int>(), row.data_ptr<int>(), out.data_ptr(),
+                         (int)out.size(0), row_bytes, stream());
+}
+
+void pull_reduce_rows(Tensor peer_ptrs, Tensor src, Tensor out) {
+    c10::cuda::CUDAGuard guard(out.device());
+    TORCH_CHECK(out.size(1) % 8 == 0, "row width must be a multiple of 8 elements");
+    gt::pull_reduce_rows(dt(out), reinterpret_cast<const void* const*>(peer_ptrs.data_ptr()), (int)peer_ptrs.numel(), src.data_ptr<int>(),
+                         out.data_ptr(), (int)out.size(0), (int)out.size(1), stream());
+}
+
+void pull_all_gather(Tensor peer_ptrs, Tensor out) {
+    c10::cuda::CUDAGuard guard(out.device());
+    const long long chunk_bytes = (long long)out.numel() * out.element_size() / peer_ptrs.numel();
+    TORCH_CHECK(chunk_bytes % 16 == 0, "chunks must be a multiple of 16 bytes");
+    gt::pull_all_gather(reinterpret_cast<const void* const*>(peer_ptrs.data_ptr()), (int)peer_ptrs.numel(), out.data_ptr(), chunk_bytes, stream());
+}
+
+void pull_reduce_scatter(Tensor peer_ptrs, int64_t my_index, Tensor out) {
+    c10::cuda::CUDAGuard guard(out.device());
+    TORCH_CHECK(out.numel() % 8 == 0, "chunk must be a multiple of 8 elements");
+    gt::pull_reduce_scatter(dt(out), reinterpret_cast<const void* const*>(peer_ptrs.data_ptr()), (int)peer_ptrs.numel(), (int)my_index,
+                            out.data_ptr(), out.numel(), stream());
+}
+
+void pull_all_reduce(Tensor peer_ptrs, Tensor out) {
+    c10::cuda::CUDAGuard guard(out.device());
+    TORCH_CHECK(out.numel() % 8 == 0, "payload must be a multiple of 8 elements");
+    gt::pull_all_reduce(dt(out), reinterpret_cast<const void* const*>(peer_ptrs.data_ptr()), (int)peer_ptrs.numel(), out.data_ptr(), out.numel(), stream());
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("attn_fwd", &attn_fwd);
+    m.def("attn_bwd_row", &attn_bwd_row);
+    m.def("attn_bwd_row_blocks", &attn_bwd_row_blocks);
+    m.def("attn_bwd_col", &attn_bwd_col);
+    m.def("attn_shape_supported", &attn_shape_supported);
+    m.def("reduce_partials", &reduce_partials);
+    m.def("spmm", &spmm);
+    m.def("layer_norm_fwd", &layer_norm_fwd);
+    m.def("layer_norm_bwd", &layer_norm_bwd);
+    m.def("layer_norm_bwd_blocks", &layer_norm_bwd_blocks);
+    m.def("bias_act_dropout", &bias_act_dropout);
+    m.def("bias_act_dropout_bwd", &bias_act_dropout_bwd);
+    m.def("colsum_blocks", &colsum_blocks);
+    m.def("cross_entropy", &cross_entropy);
+    m.def("adamw_step", &adamw_step);
+    m.def("sq_norm", &sq_norm);
+    m.def("cast_bf16", &cast_bf16);
+    m.def("gemm_nt", &gemm_nt);
+    m.def("gemm_tn", &gemm_tn);
+    m.def("heap_alloc", &heap_alloc);
+    m.def("heap_free", &heap_free);
+    m.def("heap_ipc_handle", &heap_ipc_handle);
+    m.def("heap_open", &heap_open);
+    m.def("heap_close", &heap_close);
+    m.def("tensor_from_ptr", &tensor_from_ptr);
+    m.def("signal_peers", &signal_peers);
+    m.def("wait_flags", &wait_flags);
+    m.def("pull_gather_rows", &pull_gather_rows);
+    m.def("pull_reduce_rows", &pull_reduce_rows);
+    m.def("pull_all_gather", &pull_all_gather);
+    m.def("pull_reduce_scatter", &pull_reduce_scatter);
+    m.def("pull_all_reduce", &pull_all_reduce);
+}

@@ -1,0 +1,454 @@
+// Dense GEMMs on the 5th-generation tensor cores (tcgen05) of sm_100a, written with inline PTX.
+//
+//   gemm_tcgen05      C[M, N]  = epilogue(A[M, K] * B[N, K]^T)     both operands K-major (activations x weights:
+//                     forward projections, FFN, input gradients with a pre-transposed weight)
+//   gemm_tn_tcgen05   C[N, K] += A[M, N]^T * B[M, K]               both operands MN-major (weight gradients: the
+//                     reduction runs over the long row dimension and is split across CTAs)
+//
+// Structure of a CTA (192 threads): warp 0 / one elected thread issues the TMA loads (cp.async.bulk.tensor, 128-byte
+// swizzle, completion on an mbarrier); warp 1 allocates tensor memory and one elected thread issues tcgen05.mma
+// (M = 128, N = 128, K = 16 per instruction, fp32 accumulator of 128 lanes x 128 columns in TMEM) and releases each
+// shared-memory stage with tcgen05.commit; warps 2-5 are the epilogue: tcgen05.ld of the accumulator (32 lanes per warp),
+// bias / ReLU / dropout / cast in registers, vector stores.  Three 32 KB stages per CTA, two CTAs per SM so that one
+// CTA's epilogue overlaps the other's main loop (the GEMMs of these models have K = 128..1024, i.e. 2..16 stages, and are
+// as much bound by streaming A and C as by the MMAs).
+//
+// Every wait (mbarrier phases) is bounded: on expiry the waiting thread raises a CTA-wide abort flag and the global status
+// word, the producer drains the copies it has in flight, tensor memory is released and the CTA returns.  The host checks
+// the status word after synchronising.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace gt {
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 64, STAGES = 3;
+constexpr int kThreads = 192;
+constexpr uint32_t kTmemCols = 128;
+constexpr long long kWaitCycles = 2000000000LL;          // ~1 s at 2 GHz: a healthy pipeline waits microseconds
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait on an mbarrier phase.  Returns false when the CTA is aborting (or the limit expired, which raises the abort).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitCycles) {
+            *abort_flag = 1;
+            if (status) atomicExch(status, code);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrive on an mbarrier once all previously issued MMAs of this thread have completed
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// shared-memory matrix descriptor of a 128-byte-swizzled operand tile
+//   K-major : rows of 128 bytes (64 bf16 along K), 8-row groups 1024 bytes apart (SBO), LBO unused (=1)
+//   MN-major: rows of 128 bytes (64 bf16 along M/N), 8 K-rows per 1024-byte group (SBO), 64-element MN blocks LBO bytes apart
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= 1ull << 46;                                       // descriptor version of sm_100
+    d |= 2ull << 61;                                       // SWIZZLE_128B
+    return d;
+}
+
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, int a_mn_major, int b_mn_major) {
+    return (1u << 4)                                       // D format fp32
+           | (1u << 7) | (1u << 10)                        // A, B format bf16
+           | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+struct __align__(1024) SharedStorage {
+    __nv_bfloat16 a[STAGES][BM * BK];                      // 16 KB per stage
+    __nv_bfloat16 b[STAGES][BN * BK];                      // 16 KB per stage
+    uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t tmem_full;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+
+__device__ __forceinline__ uint64_t site_seed(const long long* seed, long long stream_id) {
+    uint64_t s0 = seed ? (uint64_t)seed[0] : 0x1234567ull, s1 = seed ? (uint64_t)seed[1] : 0ull;
+    return s0 + 0x9E3779B97F4A7C15ull * (s1 * 4096ull + (uint64_t)stream_id + 1ull);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// C = A * B^T (K-major operands)
+// ------------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads) gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                           const __grid_constant__ CUtensorMap map_b, GemmArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    SharedStorage& sh = *reinterpret_cast<SharedStorage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+    const int nkb = (g.K + BK - 1) / BK;
+    volatile int* abort_flag = &sh.abort_flag;
+
+    if (threadIdx.x == 0) {
+        sh.abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&sh.full[s], 1); mbar_init(&sh.empty[s], 1); }
+        mbar_init(&sh.tmem_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(&sh.tmem_base, kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh.tmem_base;
+
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer ----
+        int issued = 0;
+        for (int kb = 0; kb < nkb; ++kb) {
+            const int s = kb % STAGES;
+            if (!mbar_wait(&sh.empty[s], ((kb / STAGES) & 1) ^ 1, abort_flag, g.status, 1)) break;
+            mbar_expect_tx(&sh.full[s], (BM + BN) * BK * 2);
+            tma_load_2d(sh.a[s], &map_a, kb * BK, m0, &sh.full[s]);
+            tma_load_2d(sh.b[s], &map_b, kb * BK, n0, &sh.full[s]);
+            issued = kb + 1;
+        }
+        if (*abort_flag) {
+            // drain: every stage whose copy was issued must land before the CTA may exit
+            for (int kb = (issued > STAGES ? issued - STAGES : 0); kb < issued; ++kb) {
+                const long long t0 = clock64();
+                while (!mbar_try_wait(&sh.full[kb % STAGES], (kb / STAGES) & 1) && clock64() - t0 < kWaitCycles) {}
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer ----
+        const uint32_t idesc = make_idesc(BM, BN, 0, 0);
+        bool okay = true;
+        for (int kb = 0; kb < nkb && okay; ++kb) {
+            const int s = kb % STAGES;
+            okay = mbar_wait(&sh.full[s], (kb / STAGES) & 1, abort_flag, g.status, 2);
+            if (!okay) break;
+            tc_fence_after();
+            const uint32_t a_addr = smem_u32(sh.a[s]), b_addr = smem_u32(sh.b[s]);
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k) {
+                const uint64_t ad = make_desc(a_addr + k * 32, 16, 1024);
+                const uint64_t bd = make_desc(b_addr + k * 32, 16, 1024);
+                umma_bf16(tmem, ad, bd, idesc, (kb | k) != 0);
+            }
+            umma_commit(&sh.empty[s]);                    // frees the stage once these MMAs have read it
+        }
+        if (okay) umma_commit(&sh.tmem_full);
+    } else if (warp >= 2) {
+        // ---- epilogue: TMEM -> registers -> global ----
+        const bool okay = mbar_wait(&sh.tmem_full, 0, abort_flag, g.status, 3);
+        tc_fence_after();
+        if (okay) {
+            const int quad = warp & 3;                     // TMEM lanes [32 * quad, 32 * quad + 32)
+            const int row = m0 + quad * 32 + lane;
+            const uint64_t sd = site_seed(g.seed, g.stream_id);
+            const float inv_keep = g.p > 0.f ? 1.f / (1.f - g.p) : 1.f;
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + c0, r);     // whole warp: sync.aligned
+                if (row >= g.M) continue;
+                const int col0 = n0 + c0;
+                if (col0 >= g.N) continue;
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int col = col0 + j;
+                    if (col < g.N) {
+                        float t = v[j] + (g.bias ? g.bias[col] : 0.f);
+                        if (g.act == 1) t = fmaxf(t, 0.f);
+                        else if (g.act == 2) t = gelu_f(t);
+                        if (g.p > 0.f) t = uniform01(sd, (uint64_t)row * g.N + col) >= g.p ? t * inv_keep : 0.f;
+                        v[j] = t;
+                    }
+                }
+                const bool full = col0 + 32 <= g.N;
+                if (g.c_dtype == DT_BF16) {
+                    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(g.c) + (size_t)row * g.ldc + col0;
+                    if (full && (g.ldc & 7) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) Vec8<__nv_bfloat16>::store(dst + j, *reinterpret_cast<float(*)[8]>(&v[j]));
+                    } else {
+                        for (int j = 0; j < 32 && col0 + j < g.N; ++j) dst[j] = __float2bfloat16(v[j]);
+                    }
+                } else {
+                    float* dst = static_cast<float*>(g.c) + (size_t)row * g.ldc + col0;
+                    if (full && (g.ldc & 3) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                            if (g.accumulate) {
+                                float4 old = *reinterpret_cast<float4*>(dst + j);
+                                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                            }
+                            *reinterpret_cast<float4*>(dst + j) = o;
+                        }
+                    } else {
+                        for (int j = 0; j < 32 && col0 + j < g.N; ++j) dst[j] = g.accumulate ? dst[j] + v[j] : v[j];
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// C[N, K] += A[M, N]^T * B[M, K]  (MN-major operands, reduction over rows split across gridDim.z)
+// ------------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads) gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                           const __grid_constant__ CUtensorMap map_b, GemmTNArgs g, int rows_per_split) {
+    extern __shared__ uint8_t smem_raw[];
+    SharedStorage& sh = *reinterpret_cast<SharedStorage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k0 = blockIdx.x * BN;                        // output column tile (features of B)
+    const int n0 = blockIdx.y * BM;                        // output row tile (features of A)
+    const int r_beg = blockIdx.z * rows_per_split;
+    const int r_end = min(g.M, r_beg + rows_per_split);
+    const int nkb = r_end > r_beg ? (r_end - r_beg + BK - 1) / BK : 0;
+    volatile int* abort_flag = &sh.abort_flag;
+
+    if (threadIdx.x == 0) {
+        sh.abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&sh.full[s], 1); mbar_init(&sh.empty[s], 1); }
+        mbar_init(&sh.tmem_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(&sh.tmem_base, kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh.tmem_base;
+    if (nkb > 0) {
+        if (warp == 0 && lane == 0) {
+            int issued = 0;
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % STAGES;
+                if (!mbar_wait(&sh.empty[s], ((kb / STAGES) & 1) ^ 1, abort_flag, g.status, 4)) break;
+                mbar_expect_tx(&sh.full[s], (BM + BN) * BK * 2);
+                const int r = r_beg + kb * BK;
+                // two 64-column boxes per operand: [BK rows][64 cols] each, 128-byte rows
+                tma_load_2d(sh.a[s], &map_a, n0, r, &sh.full[s]);
+                tma_load_2d(sh.a[s] + BK * 64, &map_a, n0 + 64, r, &sh.full[s]);
+                tma_load_2d(sh.b[s], &map_b, k0, r, &sh.full[s]);
+                tma_load_2d(sh.b[s] + BK * 64, &map_b, k0 + 64, r, &sh.full[s]);
+                issued = kb + 1;
+            }
+            if (*abort_flag) {
+                for (int kb = (issued > STAGES ? issued - STAGES : 0); kb < issued; ++kb) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(&sh.full[kb % STAGES], (kb / STAGES) & 1) && clock64() - t0 < kWaitCycles) {}
+                }
+            }
+        } else if (warp == 1 && lane == 0) {
+            const uint32_t idesc = make_idesc(BM, BN, 1, 1);
+            bool okay = true;
+            for (int kb = 0; kb < nkb && okay; ++kb) {
+                const int s = kb % STAGES;
+                okay = mbar_wait(&sh.full[s], (kb / STAGES) & 1, abort_flag, g.status, 5);
+                if (!okay) break;
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(sh.a[s]), b_addr = smem_u32(sh.b[s]);
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k) {
+                    // 16 reduction rows = two 8-row groups of 1024 bytes; the two 64-wide MN blocks are BK * 128 bytes apart
+                    const uint64_t ad = make_desc(a_addr + k * 2048, BK * 128, 1024);
+                    const uint64_t bd = make_desc(b_addr + k * 2048, BK * 128, 1024);
+                    umma_bf16(tmem, ad, bd, idesc, (kb | k) != 0);
+                }
+                umma_commit(&sh.empty[s]);
+            }
+            if (okay) umma_commit(&sh.tmem_full);
+        } else if (warp >= 2) {
+            const bool okay = mbar_wait(&sh.tmem_full, 0, abort_flag, g.status, 6);
+            tc_fence_after();
+            if (okay) {
+                const int quad = warp & 3;
+                const int row = n0 + quad * 32 + lane;
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + c0, r);
+                    if (row >= g.N) continue;
+                    float* dst = g.c + (size_t)row * g.ldc + k0 + c0;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (k0 + c0 + j < g.K) atomicAdd(dst + j, __uint_as_float(r[j]));
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
+
+// ---- host side: tensor maps ------------------------------------------------------------------------------------------
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+    });
+    return fn;
+}
+
+// 2D bf16 tensor [rows, cols] with row stride ld (elements); box = [box_rows][box_cols]
+bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows, int box_cols) {
+    using Key = std::tuple<const void*, int, int, int, int, int>;
+    static std::map<Key, CUtensorMap> cache;
+    static std::mutex mu;
+    Key key{base, rows, cols, ld, box_rows, box_cols};
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) { *map = it->second; return true; }
+    }
+    auto fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return false;
+    std::lock_guard<std::mutex> lk(mu);
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = *map;
+    return true;
+}
+
+constexpr size_t kSmemBytes = sizeof(SharedStorage) + 1024;
+
+}  // namespace
+
+bool gemm_tcgen05_supported(int M, int N, int K, int lda, int ldb, int ldc) {
+    (void)ldc;
+    return M > 0 && N > 0 && K > 0 && (lda % 8) == 0 && (ldb % 8) == 0 && (K % 8) == 0;
+}
+
+int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
+    if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.b) & 15)) return -2;
+    CUtensorMap ma, mb;
+    if (!make_map(&ma, g.a, g.M, g.K, g.lda, BM, BK)) return -1;
+    if (!make_map(&mb, g.b, g.N, g.K, g.ldb, BN, BK)) return -1;
+    static bool attr = false;
+    if (!attr) {
+        cudaFuncSetAttribute(gemm_nt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+        attr = true;
+    }
+    dim3 grid((g.N + BN - 1) / BN, (g.M + BM - 1) / BM);
+    gemm_nt_kernel<<<grid, kThreads, kSmemBytes, s>>>(ma, mb, g);
+    return (int)cudaGetLastError();
+}
+
+int gemm_tn_tcgen05(const GemmTNArgs& g, cudaStream_t s) {
+    if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.b) & 15)) return -2;
+    if ((g.lda % 8) || (g.ldb % 8) || (g.N % 8) || (g.K % 8)) return -3;
+    CUtensorMap ma, mb;
+    if (!make_map(&ma, g.a, g.M, g.N, g.lda, BK, 64)) return -1;
+    if (!make_map(&mb, g.b, g.M, g.K, g.ldb, BK, 64)) return -1;
+    static bool attr = false;
+    if (!attr) {
+        cudaFuncSetAttribute(gemm_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+        attr = true;
+    }
+    const int tiles = ((g.K + BN - 1) / BN) * ((g.N + BM - 1) / BM);
+    int splits = (2 * 148 + tiles - 1) / tiles;
+    const int kblocks = (g.M + BK - 1) / BK;
+    if (splits > kblocks) splits = kblocks;
+    if (splits < 1) splits = 1;
+    const int rows_per_split = ((kblocks + splits - 1) / splits) * BK;
+    splits = (g.M + rows_per_split - 1) / rows_per_split;
+    if (!g.accumulate) cudaMemsetAsync(g.c, 0, (size_t)g.N * g.ldc * sizeof(float), s);
+    dim3 grid((g.K + BN - 1) / BN, (g.N + BM - 1) / BM, splits);
+    gemm_tn_kernel<<<grid, kThreads, kSmemBytes, s>>>(ma, mb, g, rows_per_split);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace gt

@@ -1,0 +1,193 @@
+// Host-side launch interface of the gt_b200 kernels.  Everything here is plain C++ (no torch headers): the binding
+// translates tensors to these PODs, and the launchers enqueue on the given stream and never allocate.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace gt {
+
+enum Dtype : int { DT_F32 = 0, DT_BF16 = 1 };
+enum Score : int { SCORE_DOT = 0, SCORE_GATED = 1, SCORE_BIASED = 2 };
+enum Norm : int { NORM_SOFTMAX = 0, NORM_CLAMPEXP = 1 };
+
+// Work list of a pass: one warp per segment (see gt_b200/attention/csr.py).
+struct SegPlan {
+    const int* seg_row;
+    const int* seg_beg;
+    const int* seg_end;
+    const int* seg_slot;    // -1: the row has one segment; else index of the segment's scratch slot
+    int n_seg;
+    const int* split_rows;  // rows cut in several segments
+    const int* split_ptr;   // their slot ranges
+    int n_split;
+};
+
+struct AttnCommon {
+    int dtype;              // Dtype of q / k / v / row_vec
+    int H, D, T;            // heads, head dim, number of edge types (rows of gate / bias)
+    int score, norm;
+    float scale, lo, hi;
+    const int* idx;         // CSR: source column of every entry;  CSC: destination row of every entry
+    const int* etype;       // per entry, nullable
+    const float* gate;      // [T, H*D] fp32, nullable
+    const float* bias;      // [T, H]   fp32, nullable
+    SegPlan plan;
+    float* scratch;         // [n_slots, scratch_width] fp32
+};
+
+struct AttnFwdArgs {
+    AttnCommon c;
+    const void* q;          // [n_rows, H*D]
+    const void* k;          // [n_cols, H*D]  (ignored when peers are given)
+    const void* v;
+    // receiver-driven pull over NVLink: column j lives in k_peers[j / rows_per_peer] at row j % rows_per_peer
+    const void* const* k_peers;
+    const void* const* v_peers;
+    int rows_per_peer;
+    const int* row_map;     // nullable: output row of every plan row (doubly-compressed row lists)
+    float* acc; float* l; float* m;   // outputs (m nullable)
+    long long acc_stride, l_stride;   // elements between consecutive output rows
+    int accumulate;         // add into acc / l instead of overwriting
+};
+
+struct AttnBwdRowArgs {
+    AttnCommon c;
+    const void* q; const void* k; const void* v;
+    const void* row_vec;    // [n_rows, H*D] dtype: dacc (partial form) or dO (normalised form)
+    const float4* stat;     // [n_rows, H]: {m, row_bias, p_scale, unused}
+    const int* row_map;     // nullable
+    void* dq;               // [n_rows, H*D] dtype
+    int accumulate_dq;      // dq is fp32 and is added to (streamed layer)
+    float* dgate_part;      // [n_blocks, T, H*D] per-block partial sums (nullable)
+    float* dbias_part;      // [n_blocks, T, H]   (nullable)
+    int n_blocks;           // grid size the partial buffers were sized for
+};
+
+struct AttnBwdColArgs {
+    AttnCommon c;           // idx = destination row of every CSC entry; plan over the columns
+    const void* q; const void* k; const void* v;
+    const void* row_vec;
+    const float4* stat;
+    void* dk; void* dv;     // [n_cols, H*D] dtype
+};
+
+int attn_scratch_width_fwd(int H, int D);              // floats per forward slot
+void attn_fwd(const AttnFwdArgs& a, cudaStream_t s);
+void attn_bwd_row(const AttnBwdRowArgs& a, cudaStream_t s);
+void attn_bwd_col(const AttnBwdColArgs& a, cudaStream_t s);
+bool attn_shape_supported(int H, int D, int T);
+int attn_bwd_row_blocks(int n_seg);                    // grid size attn_bwd_row will use for n_seg segments
+// sum of per-block partials: out[i] = sum_b part[b, i]
+void reduce_partials(const float* part, int n_blocks, int width, float* out, cudaStream_t s);
+
+// ---- sparse aggregation ---------------------------------------------------------------------------------------------
+struct SpmmArgs {
+    int dtype;              // dtype of x / out
+    const int* ptr;         // [n_out + 1]
+    const int* idx;         // [E]
+    const float* w;         // [E]
+    const void* x;          // [n_in, d]
+    void* out;              // [n_out, d]
+    int n_out, d;
+    int accumulate;
+};
+void spmm(const SpmmArgs& a, cudaStream_t s);
+// out[r] = sum_{k in [ptr[r], ptr[r+1])} rows[perm[k]]   (deterministic segmented row sum)
+void segment_sum_rows(int dtype, const void* rows, const int* perm, const int* ptr, void* out, int n_out, int width, cudaStream_t s);
+
+// ---- row-wise dense kernels -----------------------------------------------------------------------------------------
+struct LayerNormArgs {
+    int dtype;              // dtype of y / x / out
+    const void* y;          // [n, d] branch output (dropout applied to y + ybias)
+    const void* x;          // [n, d] residual, nullable
+    const float* ybias;     // [d], nullable
+    const float* gamma; const float* beta;
+    void* out;              // [n, d]
+    float* mean_rstd;       // [n, 2] saved statistics (nullable in inference)
+    int n, d; float eps;
+    float p;                // dropout probability (0 = none)
+    const long long* seed;  // device pointer: {seed, offset}
+    long long stream_id;    // distinguishes the dropout sites of a step
+};
+void layer_norm_fwd(const LayerNormArgs& a, cudaStream_t s);
+struct LayerNormBwdArgs {
+    int dtype;
+    const void* dout;       // [n, d]
+    const void* y; const void* x; const float* ybias;   // forward inputs (recompute z = x + drop(y + ybias))
+    const float* gamma;
+    const float* mean_rstd;
+    void* dy;               // [n, d] dtype (gradient w.r.t. y, dropout mask applied)
+    void* dx;               // [n, d] dtype, nullable; accumulate_dx adds dz to it instead of overwriting
+    int accumulate_dx;
+    float* dgamma_part; float* dbeta_part; float* dybias_part;   // [n_blocks, d] partials (dybias nullable)
+    int n_blocks;
+    int n, d; float p; const long long* seed; long long stream_id;
+};
+void layer_norm_bwd(const LayerNormBwdArgs& a, cudaStream_t s);
+int layer_norm_bwd_blocks(int n);
+
+// elementwise epilogue used when a GEMM is not fused: out = drop(act(in + bias))
+void bias_act_dropout(int dtype, const void* in, const float* bias, void* out, long long n, int d, int act, float p,
+                      const long long* seed, long long stream_id, cudaStream_t s);
+// dz = dout * act'(in + bias) * dropmask ; optional per-block bias gradient partials
+void bias_act_dropout_bwd(int dtype, const void* dout, const void* in, const float* bias, void* dz, long long n, int d, int act,
+                          float p, const long long* seed, long long stream_id, float* dbias_part, int n_blocks, cudaStream_t s);
+int colsum_blocks(long long n);
+
+// masked softmax cross-entropy: loss_sum += sum_i mask_i * nll_i / denom ; dlogits = mask_i (softmax - onehot) / denom
+void cross_entropy_fwd_bwd(int dtype, const void* logits, const long long* labels, const bool* mask, int n, int c, float inv_denom,
+                           float* loss, void* dlogits, cudaStream_t s);
+
+// multi-tensor AdamW over a flat fp32 parameter / gradient / moment space with a device-side LR and clip coefficient
+struct AdamWArgs {
+    float* p; const float* g; float* m; float* v;
+    void* p_bf16;           // optional bf16 shadow of the parameters (nullable)
+    long long n;
+    const float* hyper;     // device: {lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2, max_grad_norm, grad_sq_norm}
+    const float* decay_mask;// nullable per-element weight-decay multiplier
+};
+void adamw_step(const AdamWArgs& a, cudaStream_t s);
+// sum of squares of g into out[0] (fp32 atomics over block partials)
+void sq_norm(const float* g, long long n, float* out, cudaStream_t s);
+void cast_f32_to_bf16(const float* in, void* out, long long n, cudaStream_t s);
+
+// ---- tcgen05 GEMM -----------------------------------------------------------------------------------------------------
+// C[M, N] = A[M, K] * B[N, K]^T  (both operands K-major bf16, fp32 accumulation in tensor memory)
+struct GemmArgs {
+    const void* a; const void* b; void* c;
+    int M, N, K;
+    int lda, ldb, ldc;      // elements
+    int c_dtype;            // DT_BF16 or DT_F32
+    const float* bias;      // [N], nullable
+    int act;                // 0 none, 1 relu, 2 gelu
+    float p; const long long* seed; long long stream_id;   // dropout epilogue
+    int accumulate;         // C += result (fp32 C only)
+    int* status;            // device status word: nonzero when a bounded wait expired
+};
+bool gemm_tcgen05_supported(int M, int N, int K, int lda, int ldb, int ldc);
+// returns a CUDA error code or 0; fails (-1) when the tensor maps cannot be encoded
+int gemm_tcgen05(const GemmArgs& g, cudaStream_t s);
+// C[N, K] = A[M, N]^T * B[M, K]  (weight gradients: reduction over the long row dimension, split across CTAs)
+struct GemmTNArgs {
+    const void* a; const void* b; float* c;   // bf16 inputs, fp32 output
+    int M, N, K; int lda, ldb, ldc;
+    int accumulate;
+    int* status;
+};
+int gemm_tn_tcgen05(const GemmTNArgs& g, cudaStream_t s);
+
+// ---- peer-memory kernels (NVLink) ------------------------------------------------------------------------------------
+// out[k] = peers[owner[k]][row[k]]  : receiver-driven gather of rows from the peers' buffers
+void pull_gather_rows(const void* const* peers, const int* owner, const int* row, void* out, int n, int row_bytes, cudaStream_t s);
+// out[r] = sum over peers p (fixed order) of peers[p][src[p * n_rows + r]] for src >= 0 ; fp32 accumulation
+void pull_reduce_rows(int dtype, const void* const* peers, int n_peers, const int* src, void* out, int n_rows, int width, cudaStream_t s);
+// dense variants: all-gather / reduce-scatter of equal chunks by direct peer reads
+void pull_all_gather(const void* const* peers, int n_peers, void* out, long long chunk_bytes, cudaStream_t s);
+void pull_reduce_scatter(int dtype, const void* const* peers, int n_peers, int my_index, void* out, long long chunk_elems, cudaStream_t s);
+// out = sum over peers of their buffers (one-shot all-reduce by peer reads), fp32 or bf16 payload with fp32 accumulation
+void pull_all_reduce(int dtype, const void* const* peers, int n_peers, void* out, long long n, cudaStream_t s);
+// signal / wait on epoch flags in peer memory with a bounded spin; status != 0 on expiry
+void signal_peers(int* const* peer_flags, int n_peers, int my_index, int value, cudaStream_t s);
+void wait_flags(const int* my_flags, int n_peers, int value, long long max_spins, int* status, cudaStream_t s);
+
+}  // namespace gt

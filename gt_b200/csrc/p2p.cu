@@ -1,0 +1,174 @@
+// Collectives written as kernels over peer memory (NVLink 5 / NVSwitch): every rank exposes buffers of a symmetric heap,
+// and a kernel on the *receiving* GPU reads exactly the bytes it needs from the owners' memory (receiver-driven pull).
+// There is no packing step, no send/recv matching and no intermediate copy; reductions accumulate in fp32 in a fixed peer
+// order (deterministic).  This is the sm_100a replacement of the reference's NVSHMEM pull collectives
+// (gt3d/gt3d/dist/pullcomm/pullcomm.cu:50-108) and of its all-to-all-v sparse collectives.
+//
+// Ordering between ranks uses epoch flags that live in the symmetric heap: after a rank's producer kernels,
+// `signal_peers` publishes the epoch with a system-scope release store into every peer's flag array; `wait_flags` spins
+// (bounded) with system-scope acquire loads until every peer has published it.  On expiry the kernel records the peer in
+// the status word and returns, so the context stays usable and the host can raise.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace gt {
+namespace {
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void signal_kernel(int* const* peer_flags, int n_peers, int my_index, int value) {
+    __threadfence_system();
+    int p = threadIdx.x;
+    if (p < n_peers) st_release_sys(peer_flags[p] + my_index, value);
+}
+
+__global__ void wait_kernel(const int* my_flags, int n_peers, int value, long long max_spins, int* status) {
+    int p = threadIdx.x;
+    if (p >= n_peers) return;
+    long long spins = 0;
+    while (ld_acquire_sys(my_flags + p) < value) {
+        if (++spins > max_spins) {
+            atomicExch(status, 100 + p);
+            return;
+        }
+        __nanosleep(64);
+    }
+}
+
+// warp per row: out[k] = peers[owner[k]][row[k]]
+__global__ void pull_gather_kernel(const void* const* peers, const int* owner, const int* row, uint8_t* out, int n, int row_bytes) {
+    const int warps = (blockDim.x >> 5) * gridDim.x;
+    const int lane = threadIdx.x & 31;
+    const int vec = row_bytes >> 4;
+    for (int k = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); k < n; k += warps) {
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(peers[owner[k]]) + (size_t)row[k] * row_bytes);
+        uint4* dst = reinterpret_cast<uint4*>(out + (size_t)k * row_bytes);
+        for (int i = lane; i < vec; i += 32) dst[i] = src[i];
+    }
+}
+
+// warp per owned row: fp32 sum over the peers (fixed order) of the partial rows they hold for it
+template <typename T>
+__global__ void pull_reduce_kernel(const void* const* peers, int n_peers, const int* src, T* out, int n_rows, int width) {
+    const int warps = (blockDim.x >> 5) * gridDim.x;
+    const int lane = threadIdx.x & 31;
+    const int nch = width >> 3;
+    for (int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < n_rows; r += warps) {
+        for (int c0 = 0; c0 < nch; c0 += 32) {
+            const int ch = c0 + lane;
+            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int p = 0; p < n_peers; ++p) {
+                const int s = src[(size_t)p * n_rows + r];
+                if (s >= 0 && ch < nch) {
+                    float v[8];
+                    Vec8<T>::load(static_cast<const T*>(peers[p]) + (size_t)s * width + (ch << 3), v);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) acc[k] += v[k];
+                }
+            }
+            if (ch < nch) Vec8<T>::store(out + (size_t)r * width + (ch << 3), acc);
+        }
+    }
+}
+
+// dense all-gather by peer reads: out[p * chunk + i] = peers[p][i]
+__global__ void pull_all_gather_kernel(const void* const* peers, int n_peers, uint4* out, long long chunk_vec) {
+    const long long total = chunk_vec * n_peers;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int p = (int)(i / chunk_vec);
+        const long long o = i - p * chunk_vec;
+        out[i] = static_cast<const uint4*>(peers[p])[o];
+    }
+}
+
+// dense reduce-scatter by peer reads: out[i] = sum_p peers[p][my_index * chunk + i]
+template <typename T>
+__global__ void pull_reduce_scatter_kernel(const void* const* peers, int n_peers, int my_index, T* out, long long chunk_elems) {
+    const long long nch = chunk_elems >> 3;
+    for (long long c = blockIdx.x * (long long)blockDim.x + threadIdx.x; c < nch; c += (long long)gridDim.x * blockDim.x) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int p = 0; p < n_peers; ++p) {
+            float v[8];
+            Vec8<T>::load(static_cast<const T*>(peers[p]) + my_index * chunk_elems + (c << 3), v);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] += v[k];
+        }
+        Vec8<T>::store(out + (c << 3), acc);
+    }
+}
+
+// one-shot all-reduce by peer reads (every rank reads every buffer): small / latency-bound payloads such as gradients
+template <typename T>
+__global__ void pull_all_reduce_kernel(const void* const* peers, int n_peers, T* out, long long n) {
+    const long long nch = n >> 3;
+    for (long long c = blockIdx.x * (long long)blockDim.x + threadIdx.x; c < nch; c += (long long)gridDim.x * blockDim.x) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int p = 0; p < n_peers; ++p) {
+            float v[8];
+            Vec8<T>::load(static_cast<const T*>(peers[p]) + (c << 3), v);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] += v[k];
+        }
+        Vec8<T>::store(out + (c << 3), acc);
+    }
+}
+
+int grid_for(long long items, int per_block) {
+    long long b = (items + per_block - 1) / per_block;
+    long long cap = 148LL * 8;
+    return (int)(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace
+
+void signal_peers(int* const* peer_flags, int n_peers, int my_index, int value, cudaStream_t s) {
+    signal_kernel<<<1, 32, 0, s>>>(peer_flags, n_peers, my_index, value);
+}
+
+void wait_flags(const int* my_flags, int n_peers, int value, long long max_spins, int* status, cudaStream_t s) {
+    wait_kernel<<<1, 32, 0, s>>>(my_flags, n_peers, value, max_spins, status);
+}
+
+void pull_gather_rows(const void* const* peers, const int* owner, const int* row, void* out, int n, int row_bytes, cudaStream_t s) {
+    if (n <= 0) return;
+    pull_gather_kernel<<<grid_for(n, 8), 256, 0, s>>>(peers, owner, row, static_cast<uint8_t*>(out), n, row_bytes);
+}
+
+void pull_reduce_rows(int dtype, const void* const* peers, int n_peers, const int* src, void* out, int n_rows, int width, cudaStream_t s) {
+    if (n_rows <= 0) return;
+    if (dtype == DT_BF16)
+        pull_reduce_kernel<__nv_bfloat16><<<grid_for(n_rows, 8), 256, 0, s>>>(peers, n_peers, src, static_cast<__nv_bfloat16*>(out), n_rows, width);
+    else
+        pull_reduce_kernel<float><<<grid_for(n_rows, 8), 256, 0, s>>>(peers, n_peers, src, static_cast<float*>(out), n_rows, width);
+}
+
+void pull_all_gather(const void* const* peers, int n_peers, void* out, long long chunk_bytes, cudaStream_t s) {
+    if (chunk_bytes <= 0) return;
+    pull_all_gather_kernel<<<grid_for(chunk_bytes / 16 * n_peers, 1024), 256, 0, s>>>(peers, n_peers, static_cast<uint4*>(out), chunk_bytes / 16);
+}
+
+void pull_reduce_scatter(int dtype, const void* const* peers, int n_peers, int my_index, void* out, long long chunk_elems, cudaStream_t s) {
+    if (chunk_elems <= 0) return;
+    if (dtype == DT_BF16)
+        pull_reduce_scatter_kernel<__nv_bfloat16><<<grid_for(chunk_elems / 8, 512), 256, 0, s>>>(peers, n_peers, my_index,
+                                                                                                  static_cast<__nv_bfloat16*>(out), chunk_elems);
+    else
+        pull_reduce_scatter_kernel<float><<<grid_for(chunk_elems / 8, 512), 256, 0, s>>>(peers, n_peers, my_index, static_cast<float*>(out), chunk_elems);
+}
+
+void pull_all_reduce(int dtype, const void* const* peers, int n_peers, void* out, long long n, cudaStream_t s) {
+    if (n <= 0) return;
+    if (dtype == DT_BF16)
+        pull_all_reduce_kernel<__nv_bfloat16><<<grid_for(n / 8, 512), 256, 0, s>>>(peers, n_peers, static_cast<__nv_bfloat16*>(out), n);
+    else
+        pull_all_reduce_kernel<float><<<grid_for(n / 8, 512), 256, 0, s>>>(peers, n_peers, static_cast<float*>(out), n);
+}
+
+}  // namespace gt

@@ -1,0 +1,385 @@
+// Row-wise dense kernels (bandwidth-bound): fused dropout + residual + LayerNorm forward / backward, bias + activation +
+// dropout epilogues, masked cross-entropy forward + backward, multi-tensor AdamW with global-norm clipping, casts.
+// One warp per row, 16-byte vector accesses, fp32 arithmetic; per-block partial sums for the parameter gradients are
+// written to a [n_blocks, d] buffer and folded by reduce_partials (deterministic, no global atomics).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace gt {
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kMaxCpl = 4;      // up to 4 * 32 * 8 = 1024 features per row
+
+__device__ __forceinline__ uint64_t site_seed(const long long* seed, long long stream_id) {
+    uint64_t s0 = seed ? (uint64_t)seed[0] : 0x1234567ull, s1 = seed ? (uint64_t)seed[1] : 0ull;
+    return s0 + 0x9E3779B97F4A7C15ull * (s1 * 4096ull + (uint64_t)stream_id + 1ull);
+}
+
+__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ float gelu_grad(float x) {
+    return 0.5f * (1.f + erff(x * 0.70710678118654752f)) + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+}
+
+// z = x + dropout(y + ybias) for one 8-chunk
+template <typename T>
+__device__ __forceinline__ void load_z(const T* y, const T* x, const float* ybias, size_t row, int d, int f, float p, uint64_t sd,
+                                       float (&z)[8], float (&keep)[8]) {
+    float yv[8];
+    Vec8<T>::load(y + row * d + f, yv);
+    const float inv = p > 0.f ? 1.f / (1.f - p) : 1.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        if (ybias) yv[k] += ybias[f + k];
+        keep[k] = (p > 0.f) ? (uniform01(sd, row * d + f + k) >= p ? inv : 0.f) : 1.f;
+        z[k] = yv[k] * keep[k];
+    }
+    if (x) {
+        float xv[8];
+        Vec8<T>::load(x + row * d + f, xv);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) z[k] += xv[k];
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32) ln_fwd_kernel(LayerNormArgs a) {
+    const int row = blockIdx.x * kWarps + (threadIdx.x >> 5);
+    if (row >= a.n) return;
+    const int lane = threadIdx.x & 31, nch = a.d >> 3;
+    const uint64_t sd = site_seed(a.seed, a.stream_id);
+    float z[kMaxCpl][8], keep[8];
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxCpl; ++i) {
+        int ch = lane + 32 * i;
+        if (ch < nch) {
+            load_z<T>(static_cast<const T*>(a.y), static_cast<const T*>(a.x), a.ybias, row, a.d, ch << 3, a.p, sd, z[i], keep);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) sum += z[i][k];
+        }
+    }
+    const float mean = warp_sum(sum) / a.d;
+    float var = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxCpl; ++i)
+        if (lane + 32 * i < nch)
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { float t = z[i][k] - mean; var = fmaf(t, t, var); }
+    const float rstd = rsqrtf(warp_sum(var) / a.d + a.eps);
+#pragma unroll
+    for (int i = 0; i < kMaxCpl; ++i) {
+        int ch = lane + 32 * i;
+        if (ch < nch) {
+            int f = ch << 3;
+            float o[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) o[k] = (z[i][k] - mean) * rstd * a.gamma[f + k] + a.beta[f + k];
+            Vec8<T>::store(static_cast<T*>(a.out) + (size_t)row * a.d + f, o);
+        }
+    }
+    if (lane == 0 && a.mean_rstd) { a.mean_rstd[2 * row] = mean; a.mean_rstd[2 * row + 1] = rstd; }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32) ln_bwd_kernel(LayerNormBwdArgs a) {
+    extern __shared__ float smem[];                    // [3][d] block accumulators: dgamma, dbeta, dybias
+    const int lane = threadIdx.x & 31, nch = a.d >> 3;
+    for (int i = threadIdx.x; i < 3 * a.d; i += blockDim.x) smem[i] = 0.f;
+    __syncthreads();
+    const uint64_t sd = site_seed(a.seed, a.stream_id);
+    float dgam[kMaxCpl][8], dbet[kMaxCpl][8], dyb[kMaxCpl][8];
+#pragma unroll
+    for (int i = 0; i < kMaxCpl; ++i)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { dgam[i][k] = 0.f; dbet[i][k] = 0.f; dyb[i][k] = 0.f; }
+    for (int row = blockIdx.x * kWarps + (threadIdx.x >> 5); row < a.n; row += gridDim.x * kWarps) {
+        const float mean = a.mean_rstd[2 * row], rstd = a.mean_rstd[2 * row + 1];
+        float zh[kMaxCpl][8], dzh[kMaxCpl][8], keep[kMaxCpl][8];
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < kMaxCpl; ++i) {
+            int ch = lane + 32 * i;
+            if (ch < nch) {
+                int f = ch << 3;
+                float z[8], go[8];
+                load_z<T>(static_cast<const T*>(a.y), static_cast<const T*>(a.x), a.ybias, row, a.d, f, a.p, sd, z, keep[i]);
+                Vec8<T>::load(static_cast<const T*>(a.dout) + (size_t)row * a.d + f, go);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    zh[i][k] = (z[k] - mean) * rstd;
+                    dzh[i][k] = go[k] * a.gamma[f + k];
+                    s1 += dzh[i][k];
+                    s2 = fmaf(dzh[i][k], zh[i][k], s2);
+                    dgam[i][k] = fmaf(go[k], zh[i][k], dgam[i][k]);
+                    dbet[i][k] += go[k];
+                }
+            }
+        }
+        s1 = warp_sum(s1) / a.d;
+        s2 = warp_sum(s2) / a.d;
+#pragma unroll
+        for (int i = 0; i < kMaxCpl; ++i) {
+            int ch = lane + 32 * i;
+            if (ch < nch) {
+                int f = ch << 3;
+                float dz[8], dy[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    dz[k] = rstd * (dzh[i][k] - s1 - zh[i][k] * s2);
+                    dy[k] = dz[k] * keep[i][k];
+                    dyb[i][k] += dy[k];
+                }
+                Vec8<T>::store(static_cast<T*>(a.dy) + (size_t)row * a.d + f, dy);
+                if (a.dx) {
+                    T* dxp = static_cast<T*>(a.dx) + (size_t)row * a.d + f;
+                    if (a.accumulate_dx) {
+                        float old[8];
+                        Vec8<T>::load(dxp, old);
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) dz[k] += old[k];
+                    }
+                    Vec8<T>::store(dxp, dz);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < kMaxCpl; ++i) {
+        int ch = lane + 32 * i;
+        if (ch < nch) {
+            int f = ch << 3;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                atomicAdd(&smem[f + k], dgam[i][k]);
+                atomicAdd(&smem[a.d + f + k], dbet[i][k]);
+                atomicAdd(&smem[2 * a.d + f + k], dyb[i][k]);
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < a.d; i += blockDim.x) {
+        a.dgamma_part[(size_t)blockIdx.x * a.d + i] = smem[i];
+        a.dbeta_part[(size_t)blockIdx.x * a.d + i] = smem[a.d + i];
+        if (a.dybias_part) a.dybias_part[(size_t)blockIdx.x * a.d + i] = smem[2 * a.d + i];
+    }
+}
+
+// out = dropout(act(in + bias)) on [n, d] (d % 8 == 0), grid-stride over 8-chunks
+template <typename T>
+__global__ void bias_act_dropout_kernel(const T* in, const float* bias, T* out, long long n_chunks, int d, int act, float p,
+                                        const long long* seed, long long stream_id) {
+    const uint64_t sd = site_seed(seed, stream_id);
+    const float inv = p > 0.f ? 1.f / (1.f - p) : 1.f;
+    for (long long c = blockIdx.x * (long long)blockDim.x + threadIdx.x; c < n_chunks; c += (long long)gridDim.x * blockDim.x) {
+        long long e = c << 3;
+        int f = (int)(e % d);
+        float v[8];
+        Vec8<T>::load(in + e, v);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            float t = v[k] + (bias ? bias[f + k] : 0.f);
+            if (act == 1) t = fmaxf(t, 0.f);
+            else if (act == 2) t = gelu_f(t);
+            if (p > 0.f) t = uniform01(sd, e + k) >= p ? t * inv : 0.f;
+            v[k] = t;
+        }
+        Vec8<T>::store(out + e, v);
+    }
+}
+
+// relu (act 1): `in` is the forward OUTPUT; dz = dout * (out > 0) / (1 - p)  (dropped and inactive units are both zero there)
+// gelu (act 2): `in` is the pre-activation without bias; dz = dout * gelu'(in + bias)
+// none (act 0): dz = dout * dropmask
+template <typename T>
+__global__ void bias_act_dropout_bwd_kernel(const T* dout, const T* in, const float* bias, T* dz, long long n_rows, int d, int act,
+                                            float p, const long long* seed, long long stream_id, float* dbias_part) {
+    extern __shared__ float s_db[];                    // [d]
+    for (int i = threadIdx.x; i < d; i += blockDim.x) s_db[i] = 0.f;
+    __syncthreads();
+    const uint64_t sd = site_seed(seed, stream_id);
+    const float inv = p > 0.f ? 1.f / (1.f - p) : 1.f;
+    const int nch = d >> 3;
+    // thread t handles chunk column (t % nch) of rows (t / nch) + k * rows_per_pass: a thread keeps one column group
+    const int tpb = blockDim.x;
+    const int colc = threadIdx.x % nch;
+    const int rsub = threadIdx.x / nch;
+    const int rows_per_block_pass = tpb / nch;
+    float db[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (rsub < rows_per_block_pass) {
+        for (long long row = (long long)blockIdx.x * rows_per_block_pass + rsub; row < n_rows; row += (long long)gridDim.x * rows_per_block_pass) {
+            long long e = row * d + (colc << 3);
+            float g[8], v[8], o[8];
+            Vec8<T>::load(dout + e, g);
+            if (act != 0) Vec8<T>::load(in + e, v);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                float t;
+                if (act == 1) t = v[k] > 0.f ? g[k] * inv : 0.f;
+                else if (act == 2) t = g[k] * gelu_grad(v[k] + (bias ? bias[(colc << 3) + k] : 0.f));
+                else t = (p > 0.f) ? (uniform01(sd, e + k) >= p ? g[k] * inv : 0.f) : g[k];
+                o[k] = t;
+                db[k] += t;
+            }
+            Vec8<T>::store(dz + e, o);
+        }
+        if (dbias_part)
+#pragma unroll
+            for (int k = 0; k < 8; ++k) atomicAdd(&s_db[(colc << 3) + k], db[k]);
+    }
+    __syncthreads();
+    if (dbias_part)
+        for (int i = threadIdx.x; i < d; i += blockDim.x) dbias_part[(size_t)blockIdx.x * d + i] = s_db[i];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32) ce_kernel(const T* logits, const long long* labels, const bool* mask, int n, int c,
+                                                         float inv_denom, float* loss, T* dlogits) {
+    const int row = blockIdx.x * kWarps + (threadIdx.x >> 5);
+    if (row >= n) return;
+    const int lane = threadIdx.x & 31;
+    const T* lg = logits + (size_t)row * c;
+    T* dl = dlogits ? dlogits + (size_t)row * c : nullptr;
+    if (!mask[row]) {
+        if (dl) for (int j = lane; j < c; j += 32) dl[j] = from_float<T>(0.f);
+        return;
+    }
+    float mx = -INFINITY;
+    for (int j = lane; j < c; j += 32) mx = fmaxf(mx, to_float(lg[j]));
+    mx = warp_max(mx);
+    float se = 0.f;
+    for (int j = lane; j < c; j += 32) se += __expf(to_float(lg[j]) - mx);
+    se = warp_sum(se);
+    const int y = (int)labels[row];
+    const float lse = mx + __logf(se);
+    if (lane == 0) atomicAdd(loss, (lse - to_float(lg[y])) * inv_denom);
+    if (dl)
+        for (int j = lane; j < c; j += 32) {
+            float pj = __expf(to_float(lg[j]) - lse);
+            dl[j] = from_float<T>((pj - (j == y ? 1.f : 0.f)) * inv_denom);
+        }
+}
+
+__global__ void adamw_kernel(AdamWArgs a) {
+    const float lr = a.hyper[0], b1 = a.hyper[1], b2 = a.hyper[2], eps = a.hyper[3], wd = a.hyper[4];
+    const float bc1 = a.hyper[5], bc2 = a.hyper[6];
+    // hyper[7] = max gradient norm (<= 0: no clipping), hyper[8] = sum of squared gradients (written by sq_norm)
+    float gs = 1.f;
+    if (a.hyper[7] > 0.f) gs = fminf(1.f, a.hyper[7] / (sqrtf(a.hyper[8]) + 1e-6f));
+    __nv_bfloat16* shadow = static_cast<__nv_bfloat16*>(a.p_bf16);
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < a.n; i += (long long)gridDim.x * blockDim.x) {
+        float g = a.g[i] * gs, p = a.p[i];
+        float m = b1 * a.m[i] + (1.f - b1) * g;
+        float v = b2 * a.v[i] + (1.f - b2) * g * g;
+        a.m[i] = m;
+        a.v[i] = v;
+        float decay = a.decay_mask ? a.decay_mask[i] : 1.f;
+        p = p * (1.f - lr * wd * decay) - lr * (m / bc1) / (sqrtf(v / bc2) + eps);
+        a.p[i] = p;
+        if (shadow) shadow[i] = __float2bfloat16(p);
+    }
+}
+
+__global__ void sq_norm_kernel(const float* g, long long n, float* out) {
+    float s = 0.f;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) s = fmaf(g[i], g[i], s);
+    s = warp_sum(s);
+    __shared__ float ws[32];
+    if ((threadIdx.x & 31) == 0) ws[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float t = threadIdx.x < (blockDim.x >> 5) ? ws[threadIdx.x] : 0.f;
+        t = warp_sum(t);
+        if (threadIdx.x == 0) atomicAdd(out, t);
+    }
+}
+
+__global__ void cast_kernel(const float* in, __nv_bfloat16* out, long long n) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        out[i] = __float2bfloat16(in[i]);
+}
+
+int grid_for(long long work_items, int per_block) {
+    long long b = (work_items + per_block - 1) / per_block;
+    long long cap = 148LL * 16;
+    return (int)(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace
+
+void layer_norm_fwd(const LayerNormArgs& a, cudaStream_t s) {
+    if (a.n <= 0) return;
+    const int blocks = (a.n + kWarps - 1) / kWarps;
+    if (a.dtype == DT_BF16) ln_fwd_kernel<__nv_bfloat16><<<blocks, kWarps * 32, 0, s>>>(a);
+    else ln_fwd_kernel<float><<<blocks, kWarps * 32, 0, s>>>(a);
+}
+
+int layer_norm_bwd_blocks(int n) { return grid_for(n, kWarps * 8); }
+
+void layer_norm_bwd(const LayerNormBwdArgs& a, cudaStream_t s) {
+    if (a.n <= 0) return;
+    const size_t sm = 3 * (size_t)a.d * sizeof(float);
+    if (a.dtype == DT_BF16) ln_bwd_kernel<__nv_bfloat16><<<a.n_blocks, kWarps * 32, sm, s>>>(a);
+    else ln_bwd_kernel<float><<<a.n_blocks, kWarps * 32, sm, s>>>(a);
+}
+
+void bias_act_dropout(int dtype, const void* in, const float* bias, void* out, long long n, int d, int act, float p,
+                      const long long* seed, long long stream_id, cudaStream_t s) {
+    const long long chunks = n * d / 8;
+    if (chunks <= 0) return;
+    const int blocks = grid_for(chunks, 256);
+    if (dtype == DT_BF16)
+        bias_act_dropout_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(in), bias,
+                                                                      static_cast<__nv_bfloat16*>(out), chunks, d, act, p, seed, stream_id);
+    else
+        bias_act_dropout_kernel<float><<<blocks, 256, 0, s>>>(static_cast<const float*>(in), bias, static_cast<float*>(out), chunks, d,
+                                                              act, p, seed, stream_id);
+}
+
+int colsum_blocks(long long n) { return grid_for(n, 64); }
+
+void bias_act_dropout_bwd(int dtype, const void* dout, const void* in, const float* bias, void* dz, long long n, int d, int act,
+                          float p, const long long* seed, long long stream_id, float* dbias_part, int n_blocks, cudaStream_t s) {
+    if (n <= 0) return;
+    const int nch = d / 8;
+    int threads = 256;
+    if (nch > threads) threads = ((nch + 31) / 32) * 32;
+    const size_t sm = (size_t)d * sizeof(float);
+    if (dtype == DT_BF16)
+        bias_act_dropout_bwd_kernel<__nv_bfloat16><<<n_blocks, threads, sm, s>>>(
+            static_cast<const __nv_bfloat16*>(dout), static_cast<const __nv_bfloat16*>(in), bias, static_cast<__nv_bfloat16*>(dz), n, d,
+            act, p, seed, stream_id, dbias_part);
+    else
+        bias_act_dropout_bwd_kernel<float><<<n_blocks, threads, sm, s>>>(static_cast<const float*>(dout), static_cast<const float*>(in),
+                                                                        bias, static_cast<float*>(dz), n, d, act, p, seed, stream_id,
+                                                                        dbias_part);
+}
+
+void cross_entropy_fwd_bwd(int dtype, const void* logits, const long long* labels, const bool* mask, int n, int c, float inv_denom,
+                           float* loss, void* dlogits, cudaStream_t s) {
+    if (n <= 0) return;
+    const int blocks = (n + kWarps - 1) / kWarps;
+    if (dtype == DT_BF16)
+        ce_kernel<__nv_bfloat16><<<blocks, kWarps * 32, 0, s>>>(static_cast<const __nv_bfloat16*>(logits), labels, mask, n, c, inv_denom,
+                                                                loss, static_cast<__nv_bfloat16*>(dlogits));
+    else
+        ce_kernel<float><<<blocks, kWarps * 32, 0, s>>>(static_cast<const float*>(logits), labels, mask, n, c, inv_denom, loss,
+                                                        static_cast<float*>(dlogits));
+}
+
+void adamw_step(const AdamWArgs& a, cudaStream_t s) {
+    if (a.n <= 0) return;
+    adamw_kernel<<<grid_for(a.n, 256), 256, 0, s>>>(a);
+}
+
+void sq_norm(const float* g, long long n, float* out, cudaStream_t s) {
+    if (n <= 0) return;
+    sq_norm_kernel<<<grid_for(n, 1024), 256, 0, s>>>(g, n, out);
+}
+
+void cast_f32_to_bf16(const float* in, void* out, long long n, cudaStream_t s) {
+    if (n <= 0) return;
+    cast_kernel<<<grid_for(n, 1024), 256, 0, s>>>(in, static_cast<__nv_bfloat16*>(out), n);
+}
+
+}  // namespace gt

@@ -88,3 +88,16 @@ def dropout_add_norm(norm, y, x, bias=None, p=0.0, training=False):
 
 def gelu(x):
     return F.gelu(x)
+
+
+def gated_residual(r, o, gate_weight, gate_bias, ln, p=0.0, training=False):
+    """UniMP combine: ``beta = sigmoid(W_g [r | o | r - o] + b)``; ``drop(relu(LN(beta r + (1 - beta) o)))``.
+    ``W_g [1, 3 dim]`` is split in three ``dim``-wide pieces so the concatenation is never materialised."""
+    if _use_native(r) and isinstance(ln, LayerNorm):
+        return _native().gated_residual(r, o, gate_weight, gate_bias, ln.weight, ln.bias, ln.eps, p if training else 0.0)
+    d = r.shape[1]
+    w = gate_weight.to(r.dtype).view(3, d)
+    logit = r @ (w[0] + w[2]) + o @ (w[1] - w[2]) + gate_bias.to(r.dtype)
+    beta = torch.sigmoid(logit).unsqueeze(-1)
+    out = F.relu(ln(beta * r + (1.0 - beta) * o))
+    return F.dropout(out, p, training) if p > 0 else out

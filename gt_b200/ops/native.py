@@ -1,0 +1,312 @@
+"""Python face of the sm_100a extension (``gt_b200/_ext/gt_b200_native*.so``, built by :mod:`gt_b200.build_ext`).
+
+``ext()`` imports the prebuilt module and raises when it is missing on a machine that has a GPU: no operation of
+this file falls back to a library kernel silently.  The wrappers allocate outputs / scratch with torch's caching
+allocator, hand raw tensors to the launchers and wire the kernels into autograd:
+
+    linear          tcgen05 GEMM with fused bias / ReLU / dropout epilogue; backward = tcgen05 GEMMs (input gradient on a
+                    transposed weight copy, weight gradient with the split-K MN-major kernel)
+    layer_norm      fused dropout + bias + residual + LayerNorm, forward and backward
+    spmm            CSR aggregation and its transpose
+    gemm_nt / gemm_nn / gemm_tn   raw GEMMs for the explicit-backward layers
+
+Dropout masks are never stored: kernels regenerate them from ``(seed, step offset, site id)`` held in a device tensor
+(``rng_state``), which keeps a whole training step capturable in one CUDA graph (the step offset is advanced on the
+device by ``advance_rng``).
+"""
+import itertools
+import os
+
+import torch
+
+_EXT = [None]
+_GEMM_IMPL = os.environ.get("GT_GEMM", "tcgen05")      # "tcgen05" (default) | "cublas" (debug / comparison only)
+
+
+def ext():
+    """The native module; raises if it has not been built."""
+    if _EXT[0] is None:
+        from .. import build_ext
+        mod = build_ext.load_prebuilt()
+        if mod is None:
+            raise RuntimeError("gt_b200 native extension is not built: run `python -m gt_b200.build_ext` "
+                               "(or __graft_entry__.build()) before using CUDA tensors")
+        _EXT[0] = mod
+    return _EXT[0]
+
+
+# ---- per-device state: status word of the bounded waits, dropout RNG state -------------------------------------------
+_STATE = {}
+
+
+def _state(device):
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    st = _STATE.get(key)
+    if st is None:
+        dev = torch.device("cuda", key)
+        st = dict(status=torch.zeros(1, dtype=torch.int32, device=dev),
+                  rng=torch.tensor([0x5EED, 0], dtype=torch.int64, device=dev))
+        _STATE[key] = st
+    return st
+
+
+def status(device=None):
+    return _state(device if device is not None else torch.cuda.current_device())["status"]
+
+
+def check_status(device=None):
+    """Raise if a kernel recorded an expired bounded wait (synchronises the device)."""
+    code = int(status(device).item())
+    if code != 0:
+        status(device).zero_()
+        raise RuntimeError(f"gt_b200 kernel reported an expired wait (code {code}): "
+                           "1-3 GEMM producer/MMA/epilogue, 4-6 TN GEMM, >=100 peer flag of rank code-100")
+
+
+def rng_state(device=None):
+    return _state(device if device is not None else torch.cuda.current_device())["rng"]
+
+
+def seed_rng(seed: int, device=None):
+    st = rng_state(device)
+    st.copy_(torch.tensor([int(seed), 0], dtype=torch.int64))
+
+
+def advance_rng(device=None):
+    """Next step's dropout masks (device-side increment: legal inside a CUDA graph)."""
+    rng_state(device)[1:2].add_(1)
+
+
+_SITE = itertools.count(1)
+
+
+def new_site() -> int:
+    """A process-wide unique id for one dropout site (one per module instance and use)."""
+    return next(_SITE)
+
+
+def _dt_ok(t):
+    return t.dtype in (torch.bfloat16, torch.float32)
+
+
+# ---- GEMMs ---------------------------------------------------------------------------------------------------------------
+def _rowmajor(t):
+    if t.stride(-1) != 1 or (t.stride(0) % 8) or (t.data_ptr() % 16):
+        t = t.contiguous()
+    return t
+
+
+def _pad_k(a, b):
+    k = a.shape[1]
+    if k % 8 == 0:
+        return a, b
+    pad = 8 - k % 8
+    return torch.nn.functional.pad(a, (0, pad)), torch.nn.functional.pad(b, (0, pad))
+
+
+_ACT = {None: 0, "relu": 1, "gelu": 2}
+
+
+def gemm_nt(a, b, bias=None, act=None, p=0.0, site=0, out_dtype=None, out=None, accumulate=False):
+    """``epilogue(a @ b^T)``: ``a [M, K]``, ``b [N, K]`` (bf16 -> tcgen05; fp32 -> cuBLAS, a plain library GEMM kept for
+    fp32 parity runs).  ``bias`` fp32 ``[N]``; ``act`` in None/'relu'/'gelu'; dropout ``p`` at site id ``site``."""
+    if a.dtype != torch.bfloat16 or _GEMM_IMPL == "cublas":
+        y = a @ b.to(a.dtype).t()
+        if bias is not None:
+            y = y + bias.to(y.dtype)
+        if act is not None or p > 0:
+            y2 = torch.empty_like(y)
+            pad = (-y.shape[1]) % 8
+            if pad:
+                raise ValueError("epilogue width must be a multiple of 8")
+            ext().bias_act_dropout(y.contiguous(), None, y2, _ACT[act], float(p), rng_state(a.device), int(site))
+            y = y2
+        if out is not None:
+            out.copy_(out + y if accumulate else y)
+            return out
+        return y.to(out_dtype) if out_dtype is not None else y
+    a, b = _pad_k(a, b.to(torch.bfloat16))
+    a, b = _rowmajor(a), _rowmajor(b)
+    m, n = a.shape[0], b.shape[0]
+    if out is None:
+        out = torch.empty(m, n, dtype=out_dtype or torch.bfloat16, device=a.device)
+    if m == 0:
+        return out
+    ext().gemm_nt(a, b, out, bias.float() if bias is not None and bias.dtype != torch.float32 else bias, _ACT[act], float(p),
+                  rng_state(a.device) if p > 0 else None, int(site), bool(accumulate), status(a.device))
+    return out
+
+
+def gemm_nn(a, w):
+    """``a @ w``: ``a [M, N]``, ``w [N, K]`` (input gradients).  The small weight is transposed so that both operands of
+    the tensor-core kernel are K-major."""
+    return gemm_nt(a, w.t().contiguous())
+
+
+def gemm_tn(a, b, out=None, accumulate=False):
+    """``a^T @ b`` in fp32: ``a [M, N]``, ``b [M, K]`` -> ``[N, K]`` (weight gradients; reduction over the rows)."""
+    if a.dtype != torch.bfloat16 or _GEMM_IMPL == "cublas" or (a.shape[1] % 8) or (b.shape[1] % 8):
+        y = (a.t() @ b.to(a.dtype)).float()
+        if out is not None:
+            out.copy_(out + y if accumulate else y)
+            return out
+        return y
+    a, b = _rowmajor(a), _rowmajor(b.to(torch.bfloat16))
+    if out is None:
+        out = torch.empty(a.shape[1], b.shape[1], dtype=torch.float32, device=a.device)
+        accumulate = False
+    if a.shape[0] == 0:
+        return out if accumulate else out.zero_()
+    ext().gemm_tn(a, b, out, bool(accumulate), status(a.device))
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    """y = drop(act(x W^T + b)).  Saved: x, W (bf16 copy), and y (ReLU: mask and dropout are read off y) or the
+    pre-activation (GELU)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, act, p, site):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        wb = weight.to(x2.dtype)
+        if act == "gelu":
+            pre = gemm_nt(x2, wb, bias)
+            y = torch.empty_like(pre)
+            ext().bias_act_dropout(pre, None, y, 2, float(p), rng_state(x.device) if p > 0 else None, int(site))
+            ctx.save_for_backward(x2, wb, pre)
+        else:
+            y = gemm_nt(x2, wb, bias, act, p, site)
+            ctx.save_for_backward(x2, wb, y if (act == "relu" or p > 0) else None)
+        ctx.cfg = (act, float(p), int(site), bias is not None, weight.dtype, shp)
+        return y.view(*shp[:-1], y.shape[-1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, wb, aux = ctx.saved_tensors
+        act, p, site, has_bias, wdt, shp = ctx.cfg
+        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        e = ext()
+        dbias = None
+        n = dy2.shape[0]
+        if act is not None or p > 0 or has_bias:
+            # dz = dy * act' * dropmask, with the bias gradient (column sums) as per-block partials
+            part = torch.empty(e.colsum_blocks(n), dy2.shape[1], dtype=torch.float32, device=dy2.device) if has_bias else None
+            if dy2.shape[1] % 8 == 0 and dy2.dtype in (torch.bfloat16, torch.float32) and n > 0:
+                dz = torch.empty_like(dy2)
+                code = 1 if act == "relu" else (2 if act == "gelu" else 0)
+                src = aux if code != 0 else None
+                if code == 0 and p > 0:
+                    # identity activation with dropout: the mask is regenerated from the site id
+                    pass
+                e.bias_act_dropout_bwd(dy2, src, None, dz, code, p if code != 2 else 0.0, rng_state(dy2.device) if p > 0 else None,
+                                       site, part)
+                if has_bias:
+                    dbias = torch.empty(dy2.shape[1], dtype=torch.float32, device=dy2.device)
+                    e.reduce_partials(part, dbias)
+            else:
+                dz = dy2
+                if has_bias:
+                    dbias = dy2.float().sum(0)
+        else:
+            dz = dy2
+        dx = gemm_nn(dz, wb) if ctx.needs_input_grad[0] else None
+        dw = gemm_tn(dz, x2).to(wdt) if ctx.needs_input_grad[1] else None
+        return (dx.view(shp) if dx is not None else None), dw, dbias, None, None, None
+
+
+def linear(x, weight, bias=None, activation=None, dropout=0.0):
+    site = weight.data_ptr() & 0xFFFFFFFFFF
+    return _Linear.apply(x, weight, bias, activation, float(dropout), site)
+
+
+# ---- fused dropout + bias + residual + LayerNorm -----------------------------------------------------------------------------
+class _LayerNorm(torch.autograd.Function):
+    """out = LN(x + dropout(y + ybias)).  ``x`` / ``ybias`` may be None.  Saved: y, x, the row statistics."""
+
+    @staticmethod
+    def forward(ctx, y, x, ybias, gamma, beta, eps, p, site):
+        y = y.contiguous()
+        x = x.contiguous() if x is not None else None
+        out = torch.empty_like(y)
+        stats = torch.empty(y.shape[0], 2, dtype=torch.float32, device=y.device)
+        yb = ybias.float() if ybias is not None else None
+        ext().layer_norm_fwd(y, x, yb, gamma.float(), beta.float(), out, stats, float(eps), float(p),
+                             rng_state(y.device) if p > 0 else None, int(site))
+        ctx.save_for_backward(y, x, yb, gamma, stats)
+        ctx.cfg = (float(p), int(site), ybias is not None, beta.dtype)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        y, x, yb, gamma, stats = ctx.saved_tensors
+        p, site, has_yb, pdt = ctx.cfg
+        e = ext()
+        dout = dout.contiguous()
+        n, d = y.shape
+        nb = e.layer_norm_bwd_blocks(n)
+        parts = torch.empty(3, nb, d, dtype=torch.float32, device=y.device)
+        dy = torch.empty_like(y)
+        dx = torch.empty_like(y) if x is not None else None
+        e.layer_norm_bwd(dout, y, x, yb, gamma.float(), stats, dy, dx, False, parts[0], parts[1], parts[2] if has_yb else None,
+                         p, rng_state(y.device) if p > 0 else None, site)
+        red = torch.empty(3, d, dtype=torch.float32, device=y.device)
+        e.reduce_partials(parts[0], red[0])
+        e.reduce_partials(parts[1], red[1])
+        if has_yb:
+            e.reduce_partials(parts[2], red[2])
+        return dy, dx, (red[2].to(pdt) if has_yb else None), red[0].to(gamma.dtype), red[1].to(pdt), None, None, None
+
+
+def layer_norm(y, x, ybias, gamma, beta, eps, p):
+    """``LayerNorm(x + dropout(y + ybias))`` over the last dimension of ``[n, d]`` tensors (d % 8 == 0, d <= 1024)."""
+    if y.shape[-1] % 8 or y.shape[-1] > 1024:
+        z = y + ybias.to(y.dtype) if ybias is not None else y
+        z = torch.nn.functional.dropout(z, p, True) if p > 0 else z
+        z = z + x if x is not None else z
+        return torch.nn.functional.layer_norm(z, z.shape[-1:], gamma.to(z.dtype), beta.to(z.dtype), eps)
+    site = gamma.data_ptr() & 0xFFFFFFFFFF
+    return _LayerNorm.apply(y, x, ybias, gamma, beta, float(eps), float(p), site)
+
+
+def gated_residual(r, o, gate_weight, gate_bias, ln_weight, ln_bias, eps, p):
+    """UniMP combine; the gate logit is two mat-vec products, the blend feeds the fused LayerNorm kernel."""
+    d = r.shape[1]
+    w = gate_weight.to(r.dtype).view(3, d)
+    logit = r @ (w[0] + w[2]) + o @ (w[1] - w[2]) + gate_bias.to(r.dtype)
+    beta = torch.sigmoid(logit).unsqueeze(-1)
+    out = torch.relu(layer_norm(beta * r + (1.0 - beta) * o, None, None, ln_weight, ln_bias, eps, 0.0))
+    return torch.nn.functional.dropout(out, p, True) if p > 0 else out
+
+
+# ---- sparse ------------------------------------------------------------------------------------------------------------------
+def spmm(blk, x, transpose=False, out=None):
+    """``A @ x`` or ``A^T @ x`` for a BlockCSR with fp32 weights; ``out`` is accumulated into when given."""
+    if x.shape[1] % 8 or x.shape[1] > 1024 or not _dt_ok(x):
+        from .sparse import _spmm_torch
+        if not transpose:
+            return _spmm_torch(blk.rows().long(), blk.col.long(), blk.weight, x, blk.n_rows, out)
+        ccol, rowidx, _, _, w_t = blk.csc()
+        cols_of = torch.repeat_interleave(torch.arange(blk.n_cols, device=x.device), (ccol[1:] - ccol[:-1]).long())
+        return _spmm_torch(cols_of, rowidx.long(), w_t, x, blk.n_cols, out)
+    x = x.contiguous()
+    if not transpose:
+        ptr, idx, w, n_out = blk.crow, blk.col, blk.weight, blk.n_rows
+    else:
+        ptr, idx, _, _, w = blk.csc()
+        n_out = blk.n_cols
+    w = w if w.dtype == torch.float32 else w.float()
+    acc = out is not None
+    if out is None:
+        out = torch.empty(n_out, x.shape[1], dtype=x.dtype, device=x.device)
+    ext().spmm(ptr, idx, w, x, out, acc)
+    return out
+
+
+def segment_sum_rows(rows, perm, ptr, out):
+    """``out[r] = sum_{k in [ptr[r], ptr[r+1])} rows[perm[k]]`` (deterministic)."""
+    if rows.shape[1] % 8 or rows.shape[1] > 1024 or not _dt_ok(rows):
+        seg = torch.repeat_interleave(torch.arange(out.shape[0], device=rows.device), (ptr[1:] - ptr[:-1]).long())
+        return out.zero_().index_add_(0, seg, rows[perm.long()])
+    ext().spmm(ptr, perm, None, rows.contiguous(), out, False)
+    return out

@@ -1,0 +1,156 @@
+"""UniMP / Graphormer-node (2D fused and 3D head-parallel) and the TorchGT-style Graphormer vs their single-process
+references on gloo CPU ranks (fp64), plus the plain distributed operator and the K/V ring vs the edge-list oracle."""
+import pytest
+import torch
+
+from dist_utils import run_dist
+
+VARIANTS = {
+    "unimp_2x2": dict(model="unimp", grid=(2, 2)),
+    "unimp_label_1x2": dict(model="unimp", grid=(1, 2), label=True),
+    "unimp_head_2x1x2": dict(model="unimp", grid=(2, 1, 2)),
+    "graphormer_2x2": dict(model="graphormer", grid=(2, 2)),
+    "graphormer_ckpt_4x1": dict(model="graphormer", grid=(4, 1), checkpoint=True),
+    "graphormer_khop_head_1x2x2": dict(model="graphormer", grid=(1, 2, 2), khop=True),
+}
+
+
+def _variant_worker(rank, world, case):
+    import os, sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from helpers import random_graph
+    from gt_b200.data.synthetic import symmetrize, degrees
+    from gt_b200.models import gt_variants as gv
+    from gt_b200.parallel.grid import make_grid
+    from gt_b200.parallel.layers import allreduce_grads, dist_cross_entropy
+    cfg = dict(VARIANTS[case])
+    n, f, hid, classes, heads = 61, 10, 16, 4, 4
+    torch.manual_seed(0)
+    ei, _ = random_graph(n, 3, seed=4, hub=True, empty=())
+    ei = symmetrize(ei[:, ei[0] != ei[1]], n)
+    x = torch.randn(n + 1, f, dtype=torch.float64)
+    y = torch.randint(0, classes, (n + 1,))
+    mask = torch.rand(n + 1) < 0.6
+    mask[n] = False
+    grid = make_grid(cfg["grid"], n, n_pad=64)
+    if cfg["model"] == "unimp":
+        a_ei, a_et = gv.typed_graph_edges(ei, n)
+        ref = gv.UniMPRef(f, hid, classes, 2, heads, dropout=0.0, num_classes_label=classes if cfg.get("label") else None).double()
+        label_feat = torch.where(torch.rand(n + 1) < 0.5, y, torch.full_like(y, classes)) if cfg.get("label") else None
+        out_ref = ref(x[:n], a_ei, label_feat[:n] if label_feat is not None else None)
+        kw = dict(num_classes_label=classes if cfg.get("label") else None)
+        fw = dict(label_feat=grid.take_owned(label_feat) if label_feat is not None else None)
+    else:
+        if cfg.get("khop"):
+            a_ei, a_et = gv.khop_typed_edges(ei, n)
+            nt, tok, outdeg = 3, None, True
+            nb = a_ei[:, a_et == 1]
+        else:
+            a_ei, a_et = gv.graphormer_edges(ei, n)
+            nt, tok, outdeg = 4, n, False
+            nb = a_ei[:, a_et == 0]
+        n_ref = n if cfg.get("khop") else n + 1
+        ind, outd = degrees(nb, n_ref)
+        ref = gv.GraphormerNodeRef(f, hid, classes, 2, heads, dropout=0.0, max_degree=5, num_edge_types=nt, out_degree=outdeg).double()
+        with torch.no_grad():
+            ref.attn_bias.normal_()
+        out_ref = ref(x[:n_ref], a_ei, a_et, ind, tok, outd if outdeg else None)
+        kw = dict(max_degree=5, num_edge_types=nt, out_degree=outdeg, token_row=gv.token_owned_row(grid, n) if tok is not None else None)
+        blk_ei, blk_et = grid.local_block(a_ei, a_et)
+        d_in, d_out = gv.owned_degrees(grid, blk_ei, blk_et, "cpu", neighbour_type=1 if cfg.get("khop") else 0)
+        lo, hi = grid.owned_range()
+        nvd = max(min(hi, n_ref) - lo, 0)
+        assert (d_in[:nvd] == ind[lo:hi]).all() and (d_out[:nvd] == outd[lo:hi]).all()
+        fw = dict(degree_loc=d_in, out_degree_loc=d_out if outdeg else None)
+    blk_ei, blk_et = grid.local_block(a_ei, a_et)
+    model = gv.DistGTVariant(grid, blk_ei, blk_et, f, hid, classes, 2, heads, model=cfg["model"], dropout=0.0, backend="torch",
+                             checkpoint=cfg.get("checkpoint", False), **kw).double()
+    model.load_ref_state_dict(ref.state_dict())
+    nm = int(mask.sum())
+    loss_ref = torch.nn.functional.cross_entropy(out_ref[mask[:out_ref.shape[0]]], y[:out_ref.shape[0]][mask[:out_ref.shape[0]]], reduction="sum") / nm
+    loss_ref.backward()
+    model.train()
+    out = model(grid.take_owned(x), **fw)
+    lo, hi = grid.owned_range()
+    nv = max(min(hi, out_ref.shape[0]) - lo, 0)
+    assert (out[:nv] - out_ref[lo:lo + nv]).abs().max() < 1e-9
+    m_loc = grid.take_owned(mask.to(torch.uint8)).bool()
+    dist_cross_entropy(out, grid.take_owned(y), m_loc, nm).backward()
+    allreduce_grads(list(model.parameters()))
+    rg = dict(ref.named_parameters())
+    for name, p in model.named_parameters():
+        gr = rg[name].grad
+        if gr is None:
+            continue
+        assert (p.grad - gr).abs().max() < 1e-8 * max(1.0, gr.abs().max().item()), name
+
+
+@pytest.mark.parametrize("case", list(VARIANTS))
+def test_variants_match_reference(case):
+    world = 1
+    for s in VARIANTS[case]["grid"]:
+        world *= s
+    run_dist(_variant_worker, world, case)
+
+
+OPS = {
+    "plain_softmax_2x2": dict(grid=(2, 2), op="plain", score="biased", norm="softmax"),
+    "plain_clampexp_bf16wire_1x3": dict(grid=(1, 3), op="plain", score="gated", norm="clampexp"),
+    "head_softmax_2x1x2": dict(grid=(2, 1, 2), op="head", score="dot", norm="softmax"),
+    "ring_kv_3": dict(grid=(3, 1), op="ring_kv"),
+    "ring_kv2_4": dict(grid=(4, 1), op="ring_kv", bidir=True),
+}
+
+
+def _op_worker(rank, world, case):
+    import os, sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from helpers import random_graph
+    from gt_b200.attention import masked_sparse_attention_ref
+    from gt_b200.parallel.attention import DistHeadSparseAttention, DistMaskedSparseAttention
+    from gt_b200.parallel.grid import make_grid
+    from gt_b200.parallel.ring_kv import DistRingAttentionKV
+    import torch.distributed as dist
+    cfg = OPS[case]
+    n, h, d, t = 45, 4, 6, 3
+    torch.manual_seed(0)
+    ei, et = random_graph(n, 4, seed=8)
+    q, k, v = (torch.randn(48, h, d, dtype=torch.float64) for _ in range(3))
+    gate, bias = torch.randn(t, h, d, dtype=torch.float64), torch.randn(t, h, dtype=torch.float64)
+    w = torch.randn(48, h, d, dtype=torch.float64)
+    score, norm = cfg.get("score", "gated"), cfg.get("norm", "clampexp")
+    leaves = [x_.clone().requires_grad_() for x_ in (q, k, v, gate, bias)]
+    o_ref = masked_sparse_attention_ref(leaves[0], leaves[1], leaves[2], ei, edge_type=et, gate=leaves[3] if score == "gated" else None,
+                                        bias=leaves[4] if score == "biased" else None, score=score, norm=norm)
+    (o_ref * w).sum().backward()
+    grid = make_grid(cfg["grid"], n, n_pad=48)
+    b_ei, b_et = grid.local_block(ei, et)
+    mine = [grid.take_owned(x_).clone().requires_grad_() for x_ in (q, k, v)]
+    g_loc, b_loc = gate.clone().requires_grad_(), bias.clone().requires_grad_()
+    if cfg["op"] == "plain":
+        op = DistMaskedSparseAttention(grid, (b_ei, b_et), h, d, backend="torch", score=score, norm=norm)
+        o = op(*mine, g_loc if score == "gated" else None, b_loc if score == "biased" else None)
+    elif cfg["op"] == "head":
+        op = DistHeadSparseAttention(grid, (b_ei, b_et), h, d, backend="torch", score=score, norm=norm)
+        o = op(*mine, g_loc if score == "gated" else None, b_loc if score == "biased" else None)
+    else:
+        op = DistRingAttentionKV.from_block(grid, b_ei, b_et, h, d, backend="torch", bidir=cfg.get("bidir", False))
+        o = op(*mine, g_loc)
+    lo, hi = grid.owned_range()
+    assert (o - o_ref[lo:hi]).abs().max() < 1e-10
+    (o * w[lo:hi]).sum().backward()
+    for a, b in zip(mine, leaves[:3]):
+        assert (a.grad - b.grad[lo:hi]).abs().max() < 1e-10
+    for a, b, used in ((g_loc, leaves[3], score == "gated"), (b_loc, leaves[4], score == "biased")):
+        if used:
+            gsum = a.grad.clone()
+            dist.all_reduce(gsum)
+            assert (gsum - b.grad).abs().max() < 1e-10
+
+
+@pytest.mark.parametrize("case", list(OPS))
+def test_dist_operator_matches_reference(case):
+    world = 1
+    for s in OPS[case]["grid"]:
+        world *= s
+    run_dist(_op_worker, world, case)
