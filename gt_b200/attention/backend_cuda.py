@@ -72,7 +72,7 @@ def attn_fwd_partial(q, k, v, blk: BlockCSR, gate=None, bias=None, *, score="dot
     acc = torch.empty(n, h, d, dtype=torch.float32, device=q.device)
     l = torch.empty(n, h, dtype=torch.float32, device=q.device)
     m = torch.empty(n, h, dtype=torch.float32, device=q.device)
-    scratch = torch.empty(plan.num_slots, h * d + 2 * h, dtype=torch.float32, device=q.device) if plan.num_slots else None
+    scratch = torch.empty(plan.num_slots, (h * d + 2 * h + 3) // 4 * 4, dtype=torch.float32, device=q.device) if plan.num_slots else None
     g, b = _tables(gate, bias, score)
     native.ext().attn_fwd(q.contiguous(), k.contiguous() if k is not None else None, v.contiguous() if v is not None else None,
                           blk.col, blk.etype, g, b, _plan_list(plan), None, acc, l, m, scratch, h, d, sc, nm, scale, lo, hi,
@@ -100,7 +100,7 @@ def attn_fwd_partial_accum(q, k, v, blk: BlockCSR, gate, bias, packed, hd, *, sc
         return
     sc, nm, scale, lo, hi = _cfg(q, score, norm, clamp, scale)
     plan, rows = _dcsr_plan(blk, seg_edges)
-    scratch = torch.empty(plan.num_slots, h * d + 2 * h, dtype=torch.float32, device=q.device) if plan.num_slots else None
+    scratch = torch.empty(plan.num_slots, (h * d + 2 * h + 3) // 4 * 4, dtype=torch.float32, device=q.device) if plan.num_slots else None
     g, b = _tables(gate, bias, score)
     # q rows are addressed through the plan row; the kernel reads q[row] so hand it the compressed q
     qc = q.reshape(n, hd)[rows.long()].contiguous()

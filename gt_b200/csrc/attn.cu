@@ -27,6 +27,8 @@ namespace {
 
 constexpr int kWarpsPerBlock = 4;
 constexpr int kMaxTypesReg = 4;     // edge types whose gate / bias gradients are kept in registers
+// edge groups in flight per warp (memory-level parallelism)
+constexpr int kUnrollFwd = 2, kUnrollRow = 2, kUnrollCol = 2;
 
 struct Lanes {
     int lpr;     // lanes per feature row
@@ -71,7 +73,7 @@ __device__ __forceinline__ void load_tables(const AttnCommon& c, float* s_gate, 
 // forward
 // ------------------------------------------------------------------------------------------------------------------
 template <typename T, int CPL, bool PEER>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32) attn_fwd_kernel(AttnFwdArgs a) {
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 6 : 3)) attn_fwd_kernel(AttnFwdArgs a) {
     extern __shared__ float smem[];
     const AttnCommon& c = a.c;
     const int H = c.H, D = c.D, HD = H * D;
@@ -79,142 +81,152 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) attn_fwd_kernel(AttnFwdAr
     float* s_bias = smem + (c.score == SCORE_GATED ? c.T * HD : 0);
     load_tables(c, s_gate, s_bias);
     const Lanes L = make_lanes(HD, D);
-    const int warp = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
-    if (warp >= c.plan.n_seg) return;
-    const int row = c.plan.seg_row[warp], beg = c.plan.seg_beg[warp], end = c.plan.seg_end[warp];
-    const int slot = c.plan.seg_slot[warp];
     const T* q = static_cast<const T*>(a.q);
     const T* kb = static_cast<const T*>(a.k);
     const T* vb = static_cast<const T*>(a.v);
     const bool softmax = c.norm == NORM_SOFTMAX;
-
+    const bool head_writer = (L.ll & (L.lph - 1)) == 0;
+    using Raw = typename Vec8<T>::Raw;
+    constexpr int U = kUnrollFwd;
     int foff[CPL], head[CPL];
-    float qf[CPL][8], acc[CPL][8], l[CPL], m[CPL];
 #pragma unroll
-    for (int i = 0; i < CPL; ++i) {
-        foff[i] = (L.ll + L.lpr * i) << 3;
-        head[i] = foff[i] / D;
-        Vec8<T>::load(q + (size_t)row * HD + foff[i], qf[i]);
-#pragma unroll
-        for (int x = 0; x < 8; ++x) { qf[i][x] *= c.scale; acc[i][x] = 0.f; }
-        l[i] = 0.f;
-        m[i] = softmax ? -INFINITY : 0.f;
-    }
+    for (int i = 0; i < CPL; ++i) { foff[i] = (L.ll + L.lpr * i) << 3; head[i] = foff[i] / D; }
 
-    for (int base = beg; base < end; base += 2 * L.epw) {
-        int e[2]; bool ok[2]; int j[2], t[2];
-        float kf[2][CPL][8], vf[2][CPL][8];
+    // persistent blocks: the tables are loaded once, warps stride over the segments
+    const int n_warps = gridDim.x * kWarpsPerBlock;
+    for (int seg = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); seg < c.plan.n_seg; seg += n_warps) {
+        const int row = c.plan.seg_row[seg], beg = c.plan.seg_beg[seg], end = c.plan.seg_end[seg];
+        const int slot = c.plan.seg_slot[seg];
+        float qf[CPL][8], acc[CPL][8], l[CPL], m[CPL];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            e[u] = base + u * L.epw + L.sub;
-            ok[u] = e[u] < end;
-            j[u] = ok[u] ? c.idx[e[u]] : -1;
-            t[u] = (ok[u] && c.etype) ? c.etype[e[u]] : 0;
+        for (int i = 0; i < CPL; ++i) {
+            Vec8<T>::load(q + (size_t)row * HD + foff[i], qf[i]);
+#pragma unroll
+            for (int x = 0; x < 8; ++x) { qf[i][x] *= c.scale; acc[i][x] = 0.f; }
+            l[i] = 0.f;
+            m[i] = softmax ? -INFINITY : 0.f;
         }
+        // indices of the first group; every iteration prefetches the next group's indices before it touches K / V
+        int jn[U], tn[U];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            if (j[u] >= 0) {
-                const T* kr; const T* vr;
-                if (PEER) {
-                    int p = j[u] / a.rows_per_peer, r = j[u] - p * a.rows_per_peer;
-                    kr = static_cast<const T*>(a.k_peers[p]) + (size_t)r * HD;
-                    vr = static_cast<const T*>(a.v_peers[p]) + (size_t)r * HD;
+        for (int u = 0; u < U; ++u) {
+            const int e = beg + u * L.epw + L.sub;
+            jn[u] = e < end ? c.idx[e] : -1;
+            tn[u] = (e < end && c.etype) ? c.etype[e] : 0;
+        }
+        for (int base = beg; base < end; base += U * L.epw) {
+            int j[U], t[U];
+            Raw kr[U][CPL], vr[U][CPL];
+#pragma unroll
+            for (int u = 0; u < U; ++u) { j[u] = jn[u]; t[u] = tn[u]; }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (j[u] >= 0) {
+                    const T* kp; const T* vp;
+                    if (PEER) {
+                        const int p = j[u] / a.rows_per_peer, r = j[u] - p * a.rows_per_peer;
+                        kp = static_cast<const T*>(a.k_peers[p]) + (size_t)r * HD;
+                        vp = static_cast<const T*>(a.v_peers[p]) + (size_t)r * HD;
+                    } else {
+                        kp = kb + (size_t)j[u] * HD;
+                        vp = vb + (size_t)j[u] * HD;
+                    }
+#pragma unroll
+                    for (int i = 0; i < CPL; ++i) { kr[u][i] = Vec8<T>::load_raw(kp + foff[i]); vr[u][i] = Vec8<T>::load_raw(vp + foff[i]); }
                 } else {
-                    kr = kb + (size_t)j[u] * HD;
-                    vr = vb + (size_t)j[u] * HD;
+#pragma unroll
+                    for (int i = 0; i < CPL; ++i) { kr[u][i] = Vec8<T>::zero_raw(); vr[u][i] = Vec8<T>::zero_raw(); }
                 }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int e = base + (U + u) * L.epw + L.sub;
+                jn[u] = e < end ? c.idx[e] : -1;
+                tn[u] = (e < end && c.etype) ? c.etype[e] : 0;
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const bool ok = j[u] >= 0;
 #pragma unroll
                 for (int i = 0; i < CPL; ++i) {
-                    Vec8<T>::load_nc(kr + foff[i], kf[u][i]);
-                    Vec8<T>::load_nc(vr + foff[i], vf[u][i]);
+                    float kf[8], vf[8];
+                    Vec8<T>::unpack(kr[u][i], kf);
+                    float s = 0.f;
+                    if (c.score == SCORE_GATED) {
+                        const float* g = s_gate + t[u] * HD + foff[i];
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) s = fmaf(qf[i][x] * kf[x], g[x], s);
+                    } else {
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) s = fmaf(qf[i][x], kf[x], s);
+                    }
+                    s = head_sum(s, L.lph);
+                    if (c.score == SCORE_BIASED) s += s_bias[t[u] * H + head[i]];
+                    Vec8<T>::unpack(vr[u][i], vf);
+                    if (softmax) {
+                        const float mn = ok ? fmaxf(m[i], s) : m[i];
+                        const float corr = safe_exp_diff(m[i], mn);
+                        const float p = ok ? __expf(s - mn) : 0.f;
+                        l[i] = l[i] * corr + p;
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) acc[i][x] = fmaf(acc[i][x], corr, p * vf[x]);
+                        m[i] = mn;
+                    } else {
+                        const float p = ok ? __expf(fminf(fmaxf(s, c.lo), c.hi)) : 0.f;
+                        l[i] += p;
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) acc[i][x] = fmaf(p, vf[x], acc[i][x]);
+                    }
                 }
-            } else {
-#pragma unroll
-                for (int i = 0; i < CPL; ++i)
-#pragma unroll
-                    for (int x = 0; x < 8; ++x) { kf[u][i][x] = 0.f; vf[u][i][x] = 0.f; }
             }
         }
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        // merge the edge slots of the warp
+        for (int off = L.lpr; off < 32; off <<= 1) {
 #pragma unroll
             for (int i = 0; i < CPL; ++i) {
-                float s = 0.f;
-                if (c.score == SCORE_GATED) {
-                    const float* g = s_gate + t[u] * HD + foff[i];
-#pragma unroll
-                    for (int x = 0; x < 8; ++x) s = fmaf(qf[i][x] * kf[u][i][x], g[x], s);
-                } else {
-#pragma unroll
-                    for (int x = 0; x < 8; ++x) s = fmaf(qf[i][x], kf[u][i][x], s);
-                }
-                s = head_sum(s, L.lph);
-                if (c.score == SCORE_BIASED) s += s_bias[t[u] * H + head[i]];
-                float p;
+                const float mo = __shfl_xor_sync(GT_FULL_MASK, m[i], off);
+                const float lo_ = __shfl_xor_sync(GT_FULL_MASK, l[i], off);
+                float wa = 1.f, wb = 1.f;
                 if (softmax) {
-                    float mn = ok[u] ? fmaxf(m[i], s) : m[i];
-                    float corr = safe_exp_diff(m[i], mn);
-                    p = ok[u] ? __expf(s - mn) : 0.f;
-                    l[i] = l[i] * corr + p;
-#pragma unroll
-                    for (int x = 0; x < 8; ++x) acc[i][x] = fmaf(acc[i][x], corr, p * vf[u][i][x]);
+                    const float mn = fmaxf(m[i], mo);
+                    wa = safe_exp_diff(m[i], mn);
+                    wb = safe_exp_diff(mo, mn);
                     m[i] = mn;
-                } else {
-                    p = ok[u] ? __expf(fminf(fmaxf(s, c.lo), c.hi)) : 0.f;
-                    l[i] += p;
+                }
+                l[i] = l[i] * wa + lo_ * wb;
 #pragma unroll
-                    for (int x = 0; x < 8; ++x) acc[i][x] = fmaf(p, vf[u][i][x], acc[i][x]);
+                for (int x = 0; x < 8; ++x) {
+                    const float ao = __shfl_xor_sync(GT_FULL_MASK, acc[i][x], off);
+                    acc[i][x] = acc[i][x] * wa + ao * wb;
                 }
             }
         }
-    }
-    // merge the edge slots of the warp
-    for (int off = L.lpr; off < 32; off <<= 1) {
+        if (L.sub != 0) continue;
+        if (slot < 0) {
+            const long long orow = a.row_map ? a.row_map[row] : row;
 #pragma unroll
-        for (int i = 0; i < CPL; ++i) {
-            float mo = __shfl_xor_sync(GT_FULL_MASK, m[i], off);
-            float lo_ = __shfl_xor_sync(GT_FULL_MASK, l[i], off);
-            float wa = 1.f, wb = 1.f;
-            if (softmax) {
-                float mn = fmaxf(m[i], mo);
-                wa = safe_exp_diff(m[i], mn);
-                wb = safe_exp_diff(mo, mn);
-                m[i] = mn;
+            for (int i = 0; i < CPL; ++i) {
+                float* dst = a.acc + orow * a.acc_stride + foff[i];
+                if (a.accumulate) {
+                    float old[8];
+                    Vec8<float>::load(dst, old);
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) acc[i][x] += old[x];
+                }
+                Vec8<float>::store(dst, acc[i]);
+                if (head_writer) {
+                    float* lp = a.l + orow * a.l_stride + head[i];
+                    *lp = a.accumulate ? *lp + l[i] : l[i];
+                    if (a.m) a.m[orow * H + head[i]] = (m[i] == -INFINITY) ? 0.f : m[i];
+                }
             }
-            l[i] = l[i] * wa + lo_ * wb;
+        } else {
+            float* sc = c.scratch + (size_t)slot * ((HD + 2 * H + 3) & ~3);
 #pragma unroll
-            for (int x = 0; x < 8; ++x) {
-                float ao = __shfl_xor_sync(GT_FULL_MASK, acc[i][x], off);
-                acc[i][x] = acc[i][x] * wa + ao * wb;
+            for (int i = 0; i < CPL; ++i) {
+                Vec8<float>::store(sc + foff[i], acc[i]);
+                if (head_writer) { sc[HD + head[i]] = l[i]; sc[HD + H + head[i]] = m[i]; }
             }
-        }
-    }
-    if (L.sub != 0) return;
-    const bool head_writer = (L.ll & (L.lph - 1)) == 0;
-    if (slot < 0) {
-        const long long orow = a.row_map ? a.row_map[row] : row;
-#pragma unroll
-        for (int i = 0; i < CPL; ++i) {
-            float* dst = a.acc + orow * a.acc_stride + foff[i];
-            if (a.accumulate) {
-                float old[8];
-                Vec8<float>::load(dst, old);
-#pragma unroll
-                for (int x = 0; x < 8; ++x) acc[i][x] += old[x];
-            }
-            Vec8<float>::store(dst, acc[i]);
-            if (head_writer) {
-                float* lp = a.l + orow * a.l_stride + head[i];
-                *lp = a.accumulate ? *lp + l[i] : l[i];
-                if (a.m) a.m[orow * H + head[i]] = (m[i] == -INFINITY) ? 0.f : m[i];
-            }
-        }
-    } else {
-        float* sc = c.scratch + (size_t)slot * (HD + 2 * H);
-#pragma unroll
-        for (int i = 0; i < CPL; ++i) {
-            Vec8<float>::store(sc + foff[i], acc[i]);
-            if (head_writer) { sc[HD + head[i]] = l[i]; sc[HD + H + head[i]] = m[i]; }
         }
     }
 }
@@ -222,7 +234,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) attn_fwd_kernel(AttnFwdAr
 // merge the slots of the split rows: one block per split row, one thread per feature
 __global__ void attn_fwd_combine_kernel(AttnFwdArgs a) {
     const AttnCommon& c = a.c;
-    const int H = c.H, D = c.D, HD = H * D, W = HD + 2 * H;
+    const int H = c.H, D = c.D, HD = H * D, W = (HD + 2 * H + 3) & ~3;     // slots are 16-byte aligned
     const int r = blockIdx.x;
     const int row = c.plan.split_rows[r];
     const long long orow = a.row_map ? a.row_map[row] : row;
@@ -253,8 +265,11 @@ __global__ void attn_fwd_combine_kernel(AttnFwdArgs a) {
 // ------------------------------------------------------------------------------------------------------------------
 // backward, row pass: dQ and the per-type gate / bias gradients
 // ------------------------------------------------------------------------------------------------------------------
-template <typename T, int CPL>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32) attn_bwd_row_kernel(AttnBwdRowArgs a) {
+// Per row and edge type t the kernel accumulates A_t = sum_{edges of type t} ds_ij k_j.  Then dq_i = scale * sum_t g_t * A_t
+// and the row's contribution to the gate gradient is q_i * scale * A_t: the per-edge work is one FMA set, and the per-type
+// gradients are flushed to shared memory once per row instead of being carried in registers.
+template <typename T, int CPL, bool GATED>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 4 : 2)) attn_bwd_row_kernel(AttnBwdRowArgs a) {
     extern __shared__ float smem[];
     const AttnCommon& c = a.c;
     const int H = c.H, D = c.D, HD = H * D;
@@ -262,7 +277,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) attn_bwd_row_kernel(AttnB
     float* s_bias = smem + (c.score == SCORE_GATED ? c.T * HD : 0);
     float* s_dg = s_bias + (c.score == SCORE_BIASED ? c.T * H : 0);      // [T, HD] or [T, H] block accumulators
     load_tables(c, s_gate, s_bias);
-    const bool want_dg = c.score == SCORE_GATED && a.dgate_part;
+    const bool want_dg = GATED && a.dgate_part;
     const bool want_db = c.score == SCORE_BIASED && a.dbias_part;
     const int acc_n = want_dg ? c.T * HD : (want_db ? c.T * H : 0);
     for (int i = threadIdx.x; i < acc_n; i += blockDim.x) s_dg[i] = 0.f;
@@ -274,76 +289,85 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) attn_bwd_row_kernel(AttnB
     const T* vb = static_cast<const T*>(a.v);
     const T* rvb = static_cast<const T*>(a.row_vec);
     const bool head_writer = (L.ll & (L.lph - 1)) == 0;
+    using Raw = typename Vec8<T>::Raw;
+    constexpr int U = kUnrollRow;
+    constexpr int NT = GATED ? kMaxTypesReg : 1;
 
     int foff[CPL], head[CPL];
 #pragma unroll
     for (int i = 0; i < CPL; ++i) { foff[i] = (L.ll + L.lpr * i) << 3; head[i] = foff[i] / D; }
-    float dg[kMaxTypesReg][CPL][8];
-    float db[kMaxTypesReg][CPL];
-#pragma unroll
-    for (int tt = 0; tt < kMaxTypesReg; ++tt)
-#pragma unroll
-        for (int i = 0; i < CPL; ++i) {
-            db[tt][i] = 0.f;
-#pragma unroll
-            for (int x = 0; x < 8; ++x) dg[tt][i][x] = 0.f;
-        }
 
     const int n_warps = gridDim.x * kWarpsPerBlock;
     for (int seg = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); seg < c.plan.n_seg; seg += n_warps) {
         const int row = c.plan.seg_row[seg], beg = c.plan.seg_beg[seg], end = c.plan.seg_end[seg];
         const int slot = c.plan.seg_slot[seg];
         const long long srow = a.row_map ? a.row_map[row] : row;     // row of q / row_vec / stat / dq
-        float qf[CPL][8], rv[CPL][8], dq[CPL][8], mrow[CPL], rb[CPL], ps[CPL];
+        float qf[CPL][8], rv[CPL][8], A[NT][CPL][8], db[kMaxTypesReg][CPL], mrow[CPL], rb[CPL], ps[CPL];
 #pragma unroll
         for (int i = 0; i < CPL; ++i) {
             Vec8<T>::load(q + srow * HD + foff[i], qf[i]);
             Vec8<T>::load(rvb + srow * HD + foff[i], rv[i]);
-            float4 st = a.stat[srow * H + head[i]];
+            const float4 st = a.stat[srow * H + head[i]];
             mrow[i] = st.x; rb[i] = st.y; ps[i] = st.z;
 #pragma unroll
-            for (int x = 0; x < 8; ++x) { qf[i][x] *= c.scale; dq[i][x] = 0.f; }
+            for (int x = 0; x < 8; ++x) qf[i][x] *= c.scale;
+#pragma unroll
+            for (int tt = 0; tt < NT; ++tt)
+#pragma unroll
+                for (int x = 0; x < 8; ++x) A[tt][i][x] = 0.f;
+#pragma unroll
+            for (int tt = 0; tt < kMaxTypesReg; ++tt) db[tt][i] = 0.f;
         }
-        for (int base = beg; base < end; base += 2 * L.epw) {
-            int j[2], t[2]; bool ok[2];
-            float kf[2][CPL][8], vf[2][CPL][8];
+        int jn[U], tn[U];
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                int e = base + u * L.epw + L.sub;
-                ok[u] = e < end;
-                j[u] = ok[u] ? c.idx[e] : -1;
-                t[u] = (ok[u] && c.etype) ? c.etype[e] : 0;
-            }
+        for (int u = 0; u < U; ++u) {
+            const int e = beg + u * L.epw + L.sub;
+            jn[u] = e < end ? c.idx[e] : -1;
+            tn[u] = (e < end && c.etype) ? c.etype[e] : 0;
+        }
+        for (int base = beg; base < end; base += U * L.epw) {
+            int j[U], t[U];
+            Raw kr[U][CPL], vr[U][CPL];
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
+            for (int u = 0; u < U; ++u) { j[u] = jn[u]; t[u] = tn[u]; }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
                 if (j[u] >= 0) {
 #pragma unroll
                     for (int i = 0; i < CPL; ++i) {
-                        Vec8<T>::load_nc(kb + (size_t)j[u] * HD + foff[i], kf[u][i]);
-                        Vec8<T>::load_nc(vb + (size_t)j[u] * HD + foff[i], vf[u][i]);
+                        kr[u][i] = Vec8<T>::load_raw(kb + (size_t)j[u] * HD + foff[i]);
+                        vr[u][i] = Vec8<T>::load_raw(vb + (size_t)j[u] * HD + foff[i]);
                     }
                 } else {
 #pragma unroll
-                    for (int i = 0; i < CPL; ++i)
-#pragma unroll
-                        for (int x = 0; x < 8; ++x) { kf[u][i][x] = 0.f; vf[u][i][x] = 0.f; }
+                    for (int i = 0; i < CPL; ++i) { kr[u][i] = Vec8<T>::zero_raw(); vr[u][i] = Vec8<T>::zero_raw(); }
                 }
             }
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
+            for (int u = 0; u < U; ++u) {
+                const int e = base + (U + u) * L.epw + L.sub;
+                jn[u] = e < end ? c.idx[e] : -1;
+                tn[u] = (e < end && c.etype) ? c.etype[e] : 0;
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const bool ok = j[u] >= 0;
 #pragma unroll
                 for (int i = 0; i < CPL; ++i) {
-                    const float* g = s_gate + t[u] * HD + foff[i];
+                    float kf[8], vf[8];
+                    Vec8<T>::unpack(kr[u][i], kf);
+                    Vec8<T>::unpack(vr[u][i], vf);
                     float s = 0.f, dp = 0.f;
-                    if (c.score == SCORE_GATED) {
+                    if (GATED) {
+                        const float* g = s_gate + t[u] * HD + foff[i];
 #pragma unroll
-                        for (int x = 0; x < 8; ++x) s = fmaf(qf[i][x] * kf[u][i][x], g[x], s);
+                        for (int x = 0; x < 8; ++x) s = fmaf(qf[i][x] * kf[x], g[x], s);
                     } else {
 #pragma unroll
-                        for (int x = 0; x < 8; ++x) s = fmaf(qf[i][x], kf[u][i][x], s);
+                        for (int x = 0; x < 8; ++x) s = fmaf(qf[i][x], kf[x], s);
                     }
 #pragma unroll
-                    for (int x = 0; x < 8; ++x) dp = fmaf(rv[i][x], vf[u][i][x], dp);
+                    for (int x = 0; x < 8; ++x) dp = fmaf(rv[i][x], vf[x], dp);
                     for (int o = L.lph >> 1; o > 0; o >>= 1) {
                         s += __shfl_xor_sync(GT_FULL_MASK, s, o);
                         dp += __shfl_xor_sync(GT_FULL_MASK, dp, o);
@@ -356,21 +380,17 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) attn_bwd_row_kernel(AttnB
                         p = __expf(fminf(fmaxf(s, c.lo), c.hi));
                         mask = (s >= c.lo && s <= c.hi) ? 1.f : 0.f;
                     }
-                    float ds = ok[u] ? p * ps[i] * (dp + rb[i]) * mask : 0.f;
-                    if (c.score == SCORE_GATED) {
+                    const float ds = ok ? p * ps[i] * (dp + rb[i]) * mask : 0.f;
+                    if (GATED) {
 #pragma unroll
-                        for (int x = 0; x < 8; ++x) dq[i][x] = fmaf(ds * kf[u][i][x], g[x], dq[i][x]);
-                        if (want_dg) {
+                        for (int tt = 0; tt < NT; ++tt)
+                            if (t[u] == tt) {
 #pragma unroll
-                            for (int tt = 0; tt < kMaxTypesReg; ++tt)
-                                if (t[u] == tt) {
-#pragma unroll
-                                    for (int x = 0; x < 8; ++x) dg[tt][i][x] = fmaf(ds * qf[i][x], kf[u][i][x], dg[tt][i][x]);
-                                }
-                        }
+                                for (int x = 0; x < 8; ++x) A[tt][i][x] = fmaf(ds, kf[x], A[tt][i][x]);
+                            }
                     } else {
 #pragma unroll
-                        for (int x = 0; x < 8; ++x) dq[i][x] = fmaf(ds, kf[u][i][x], dq[i][x]);
+                        for (int x = 0; x < 8; ++x) A[0][i][x] = fmaf(ds, kf[x], A[0][i][x]);
                         if (want_db) {
 #pragma unroll
                             for (int tt = 0; tt < kMaxTypesReg; ++tt)
@@ -380,47 +400,63 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) attn_bwd_row_kernel(AttnB
                 }
             }
         }
-        for (int off = L.lpr; off < 32; off <<= 1)
+        // merge the edge slots of the warp
+        for (int off = L.lpr; off < 32; off <<= 1) {
 #pragma unroll
-            for (int i = 0; i < CPL; ++i)
-#pragma unroll
-                for (int x = 0; x < 8; ++x) dq[i][x] += __shfl_xor_sync(GT_FULL_MASK, dq[i][x], off);
-        if (L.sub == 0) {
-#pragma unroll
-            for (int i = 0; i < CPL; ++i) {
-#pragma unroll
-                for (int x = 0; x < 8; ++x) dq[i][x] *= c.scale;
-                if (slot >= 0) {
-                    Vec8<float>::store(c.scratch + (size_t)slot * HD + foff[i], dq[i]);
-                } else if (a.accumulate_dq) {
-                    float* dst = static_cast<float*>(a.dq) + srow * HD + foff[i];
-                    float old[8];
-                    Vec8<float>::load(dst, old);
-#pragma unroll
-                    for (int x = 0; x < 8; ++x) old[x] += dq[i][x];
-                    Vec8<float>::store(dst, old);
-                } else {
-                    Vec8<T>::store(static_cast<T*>(a.dq) + srow * HD + foff[i], dq[i]);
-                }
-            }
-        }
-    }
-    // flush the per-type gradients: registers -> shared (atomics) -> this block's row of the partial buffer
-    if (want_dg) {
-#pragma unroll
-        for (int tt = 0; tt < kMaxTypesReg; ++tt)
-            if (tt < c.T)
+            for (int tt = 0; tt < NT; ++tt)
 #pragma unroll
                 for (int i = 0; i < CPL; ++i)
 #pragma unroll
-                    for (int x = 0; x < 8; ++x) atomicAdd(&s_dg[tt * HD + foff[i] + x], dg[tt][i][x]);
-    }
-    if (want_db && head_writer) {
+                    for (int x = 0; x < 8; ++x) A[tt][i][x] += __shfl_xor_sync(GT_FULL_MASK, A[tt][i][x], off);
+            if (want_db) {
 #pragma unroll
-        for (int tt = 0; tt < kMaxTypesReg; ++tt)
-            if (tt < c.T)
+                for (int tt = 0; tt < kMaxTypesReg; ++tt)
 #pragma unroll
-                for (int i = 0; i < CPL; ++i) atomicAdd(&s_dg[tt * H + head[i]], db[tt][i]);
+                    for (int i = 0; i < CPL; ++i) db[tt][i] += __shfl_xor_sync(GT_FULL_MASK, db[tt][i], off);
+            }
+        }
+        if (L.sub != 0) continue;
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) {
+            float dq[8];
+#pragma unroll
+            for (int x = 0; x < 8; ++x) dq[x] = 0.f;
+            if (GATED) {
+#pragma unroll
+                for (int tt = 0; tt < NT; ++tt)
+                    if (tt < c.T) {
+                        const float* g = s_gate + tt * HD + foff[i];
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) dq[x] = fmaf(g[x], A[tt][i][x], dq[x]);
+                        if (want_dg) {
+#pragma unroll
+                            for (int x = 0; x < 8; ++x) atomicAdd(&s_dg[tt * HD + foff[i] + x], qf[i][x] * A[tt][i][x]);
+                        }
+                    }
+            } else {
+#pragma unroll
+                for (int x = 0; x < 8; ++x) dq[x] = A[0][i][x];
+                if (want_db && head_writer) {
+#pragma unroll
+                    for (int tt = 0; tt < kMaxTypesReg; ++tt)
+                        if (tt < c.T) atomicAdd(&s_dg[tt * H + head[i]], db[tt][i]);
+                }
+            }
+#pragma unroll
+            for (int x = 0; x < 8; ++x) dq[x] *= c.scale;
+            if (slot >= 0) {
+                Vec8<float>::store(c.scratch + (size_t)slot * HD + foff[i], dq);
+            } else if (a.accumulate_dq) {
+                float* dst = static_cast<float*>(a.dq) + srow * HD + foff[i];
+                float old[8];
+                Vec8<float>::load(dst, old);
+#pragma unroll
+                for (int x = 0; x < 8; ++x) old[x] += dq[x];
+                Vec8<float>::store(dst, old);
+            } else {
+                Vec8<T>::store(static_cast<T*>(a.dq) + srow * HD + foff[i], dq);
+            }
+        }
     }
     __syncthreads();
     float* part = want_dg ? a.dgate_part + (size_t)blockIdx.x * acc_n : (want_db ? a.dbias_part + (size_t)blockIdx.x * acc_n : nullptr);
@@ -451,7 +487,7 @@ __global__ void sum_slots_kernel(const SegPlan plan, const float* scratch, int w
 // backward, column pass: dK, dV over the CSC (no atomics)
 // ------------------------------------------------------------------------------------------------------------------
 template <typename T, int CPL>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32) attn_bwd_col_kernel(AttnBwdColArgs a) {
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 5 : 2)) attn_bwd_col_kernel(AttnBwdColArgs a) {
     extern __shared__ float smem[];
     const AttnCommon& c = a.c;
     const int H = c.H, D = c.D, HD = H * D;
@@ -459,113 +495,127 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) attn_bwd_col_kernel(AttnB
     float* s_bias = smem + (c.score == SCORE_GATED ? c.T * HD : 0);
     load_tables(c, s_gate, s_bias);
     const Lanes L = make_lanes(HD, D);
-    const int warp = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
-    if (warp >= c.plan.n_seg) return;
-    const int colj = c.plan.seg_row[warp], beg = c.plan.seg_beg[warp], end = c.plan.seg_end[warp];
-    const int slot = c.plan.seg_slot[warp];
     const bool softmax = c.norm == NORM_SOFTMAX;
     const T* qb = static_cast<const T*>(a.q);
     const T* rvb = static_cast<const T*>(a.row_vec);
-
+    using Raw = typename Vec8<T>::Raw;
+    constexpr int U = kUnrollCol;
     int foff[CPL], head[CPL];
-    float kf[CPL][8], vf[CPL][8], dk[CPL][8], dv[CPL][8];
 #pragma unroll
-    for (int i = 0; i < CPL; ++i) {
-        foff[i] = (L.ll + L.lpr * i) << 3;
-        head[i] = foff[i] / D;
-        Vec8<T>::load(static_cast<const T*>(a.k) + (size_t)colj * HD + foff[i], kf[i]);
-        Vec8<T>::load(static_cast<const T*>(a.v) + (size_t)colj * HD + foff[i], vf[i]);
+    for (int i = 0; i < CPL; ++i) { foff[i] = (L.ll + L.lpr * i) << 3; head[i] = foff[i] / D; }
+
+    const int n_warps = gridDim.x * kWarpsPerBlock;
+    for (int seg = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); seg < c.plan.n_seg; seg += n_warps) {
+        const int colj = c.plan.seg_row[seg], beg = c.plan.seg_beg[seg], end = c.plan.seg_end[seg];
+        const int slot = c.plan.seg_slot[seg];
+        float kf[CPL][8], vf[CPL][8], dk[CPL][8], dv[CPL][8];
 #pragma unroll
-        for (int x = 0; x < 8; ++x) { dk[i][x] = 0.f; dv[i][x] = 0.f; }
-    }
-    for (int base = beg; base < end; base += 2 * L.epw) {
-        int r[2], t[2]; bool ok[2];
-        float qf[2][CPL][8], rv[2][CPL][8];
-        float4 st[2][CPL];
+        for (int i = 0; i < CPL; ++i) {
+            Vec8<T>::load(static_cast<const T*>(a.k) + (size_t)colj * HD + foff[i], kf[i]);
+            Vec8<T>::load(static_cast<const T*>(a.v) + (size_t)colj * HD + foff[i], vf[i]);
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            int e = base + u * L.epw + L.sub;
-            ok[u] = e < end;
-            r[u] = ok[u] ? c.idx[e] : -1;
-            t[u] = (ok[u] && c.etype) ? c.etype[e] : 0;
+            for (int x = 0; x < 8; ++x) { dk[i][x] = 0.f; dv[i][x] = 0.f; }
         }
+        int rn[U], tn[U];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            if (r[u] >= 0) {
+        for (int u = 0; u < U; ++u) {
+            const int e = beg + u * L.epw + L.sub;
+            rn[u] = e < end ? c.idx[e] : -1;
+            tn[u] = (e < end && c.etype) ? c.etype[e] : 0;
+        }
+        for (int base = beg; base < end; base += U * L.epw) {
+            int r[U], t[U];
+            Raw qr[U][CPL], rr[U][CPL];
+            float4 st[U][CPL];
+#pragma unroll
+            for (int u = 0; u < U; ++u) { r[u] = rn[u]; t[u] = tn[u]; }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (r[u] >= 0) {
+#pragma unroll
+                    for (int i = 0; i < CPL; ++i) {
+                        qr[u][i] = Vec8<T>::load_raw(qb + (size_t)r[u] * HD + foff[i]);
+                        rr[u][i] = Vec8<T>::load_raw(rvb + (size_t)r[u] * HD + foff[i]);
+                        st[u][i] = __ldg(a.stat + (size_t)r[u] * H + head[i]);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < CPL; ++i) {
+                        qr[u][i] = Vec8<T>::zero_raw(); rr[u][i] = Vec8<T>::zero_raw();
+                        st[u][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int e = base + (U + u) * L.epw + L.sub;
+                rn[u] = e < end ? c.idx[e] : -1;
+                tn[u] = (e < end && c.etype) ? c.etype[e] : 0;
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const bool ok = r[u] >= 0;
 #pragma unroll
                 for (int i = 0; i < CPL; ++i) {
-                    Vec8<T>::load_nc(qb + (size_t)r[u] * HD + foff[i], qf[u][i]);
-                    Vec8<T>::load_nc(rvb + (size_t)r[u] * HD + foff[i], rv[u][i]);
-                    st[u][i] = __ldg(a.stat + (size_t)r[u] * H + head[i]);
+                    float qf[8], rv[8];
+                    Vec8<T>::unpack(qr[u][i], qf);
+                    Vec8<T>::unpack(rr[u][i], rv);
+                    const float* g = s_gate + t[u] * HD + foff[i];
+                    float s = 0.f, dp = 0.f;
+                    if (c.score == SCORE_GATED) {
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) s = fmaf(qf[x] * kf[i][x], g[x], s);
+                    } else {
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) s = fmaf(qf[x], kf[i][x], s);
+                    }
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) dp = fmaf(rv[x], vf[i][x], dp);
+                    for (int o = L.lph >> 1; o > 0; o >>= 1) {
+                        s += __shfl_xor_sync(GT_FULL_MASK, s, o);
+                        dp += __shfl_xor_sync(GT_FULL_MASK, dp, o);
+                    }
+                    s *= c.scale;
+                    if (c.score == SCORE_BIASED) s += s_bias[t[u] * H + head[i]];
+                    float p, mask = 1.f;
+                    if (softmax) {
+                        p = __expf(s - st[u][i].x);
+                    } else {
+                        p = __expf(fminf(fmaxf(s, c.lo), c.hi));
+                        mask = (s >= c.lo && s <= c.hi) ? 1.f : 0.f;
+                    }
+                    const float P = ok ? p * st[u][i].z : 0.f;
+                    const float ds = P * (dp + st[u][i].y) * mask * c.scale;
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) dv[i][x] = fmaf(P, rv[x], dv[i][x]);
+                    if (c.score == SCORE_GATED) {
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) dk[i][x] = fmaf(ds * qf[x], g[x], dk[i][x]);
+                    } else {
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) dk[i][x] = fmaf(ds, qf[x], dk[i][x]);
+                    }
                 }
+            }
+        }
+        for (int off = L.lpr; off < 32; off <<= 1)
+#pragma unroll
+            for (int i = 0; i < CPL; ++i)
+#pragma unroll
+                for (int x = 0; x < 8; ++x) {
+                    dk[i][x] += __shfl_xor_sync(GT_FULL_MASK, dk[i][x], off);
+                    dv[i][x] += __shfl_xor_sync(GT_FULL_MASK, dv[i][x], off);
+                }
+        if (L.sub != 0) continue;
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) {
+            if (slot >= 0) {
+                Vec8<float>::store(c.scratch + (size_t)slot * 2 * HD + foff[i], dk[i]);
+                Vec8<float>::store(c.scratch + (size_t)slot * 2 * HD + HD + foff[i], dv[i]);
             } else {
-#pragma unroll
-                for (int i = 0; i < CPL; ++i) {
-                    st[u][i] = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                    for (int x = 0; x < 8; ++x) { qf[u][i][x] = 0.f; rv[u][i][x] = 0.f; }
-                }
+                Vec8<T>::store(static_cast<T*>(a.dk) + (size_t)colj * HD + foff[i], dk[i]);
+                Vec8<T>::store(static_cast<T*>(a.dv) + (size_t)colj * HD + foff[i], dv[i]);
             }
-        }
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-#pragma unroll
-            for (int i = 0; i < CPL; ++i) {
-                const float* g = s_gate + t[u] * HD + foff[i];
-                float s = 0.f, dp = 0.f;
-                if (c.score == SCORE_GATED) {
-#pragma unroll
-                    for (int x = 0; x < 8; ++x) s = fmaf(qf[u][i][x] * kf[i][x], g[x], s);
-                } else {
-#pragma unroll
-                    for (int x = 0; x < 8; ++x) s = fmaf(qf[u][i][x], kf[i][x], s);
-                }
-#pragma unroll
-                for (int x = 0; x < 8; ++x) dp = fmaf(rv[u][i][x], vf[i][x], dp);
-                for (int o = L.lph >> 1; o > 0; o >>= 1) {
-                    s += __shfl_xor_sync(GT_FULL_MASK, s, o);
-                    dp += __shfl_xor_sync(GT_FULL_MASK, dp, o);
-                }
-                s *= c.scale;
-                if (c.score == SCORE_BIASED) s += s_bias[t[u] * H + head[i]];
-                float p, mask = 1.f;
-                if (softmax) {
-                    p = __expf(s - st[u][i].x);
-                } else {
-                    p = __expf(fminf(fmaxf(s, c.lo), c.hi));
-                    mask = (s >= c.lo && s <= c.hi) ? 1.f : 0.f;
-                }
-                float P = ok[u] ? p * st[u][i].z : 0.f;
-                float ds = P * (dp + st[u][i].y) * mask * c.scale;
-#pragma unroll
-                for (int x = 0; x < 8; ++x) dv[i][x] = fmaf(P, rv[u][i][x], dv[i][x]);
-                if (c.score == SCORE_GATED) {
-#pragma unroll
-                    for (int x = 0; x < 8; ++x) dk[i][x] = fmaf(ds * qf[u][i][x], g[x], dk[i][x]);
-                } else {
-#pragma unroll
-                    for (int x = 0; x < 8; ++x) dk[i][x] = fmaf(ds, qf[u][i][x], dk[i][x]);
-                }
-            }
-        }
-    }
-    for (int off = L.lpr; off < 32; off <<= 1)
-#pragma unroll
-        for (int i = 0; i < CPL; ++i)
-#pragma unroll
-            for (int x = 0; x < 8; ++x) {
-                dk[i][x] += __shfl_xor_sync(GT_FULL_MASK, dk[i][x], off);
-                dv[i][x] += __shfl_xor_sync(GT_FULL_MASK, dv[i][x], off);
-            }
-    if (L.sub != 0) return;
-#pragma unroll
-    for (int i = 0; i < CPL; ++i) {
-        if (slot >= 0) {
-            Vec8<float>::store(c.scratch + (size_t)slot * 2 * HD + foff[i], dk[i]);
-            Vec8<float>::store(c.scratch + (size_t)slot * 2 * HD + HD + foff[i], dv[i]);
-        } else {
-            Vec8<T>::store(static_cast<T*>(a.dk) + (size_t)colj * HD + foff[i], dk[i]);
-            Vec8<T>::store(static_cast<T*>(a.dv) + (size_t)colj * HD + foff[i], dv[i]);
         }
     }
 }
@@ -583,12 +633,22 @@ __global__ void sum_slots_kv_kernel(const SegPlan plan, const float* scratch, in
     }
 }
 
+// out[i] = sum_b part[b, i]: a block owns 32 columns, its 8 thread rows stride over the partial blocks (coalesced
+// 128-byte reads), the 8 sums are folded through shared memory in a fixed order (deterministic)
 __global__ void reduce_partials_kernel(const float* part, int n_blocks, int width, float* out) {
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= width) return;
+    __shared__ float sm[8][33];
+    const int i = blockIdx.x * 32 + threadIdx.x;
     float v = 0.f;
-    for (int b = 0; b < n_blocks; ++b) v += part[(size_t)b * width + i];
-    out[i] = v;
+    if (i < width)
+        for (int b = threadIdx.y; b < n_blocks; b += 8) v += part[(size_t)b * width + i];
+    sm[threadIdx.y][threadIdx.x] = v;
+    __syncthreads();
+    if (threadIdx.y == 0 && i < width) {
+        float t = 0.f;
+#pragma unroll
+        for (int y = 0; y < 8; ++y) t += sm[y][threadIdx.x];
+        out[i] = t;
+    }
 }
 
 size_t table_bytes(const AttnCommon& c) {
@@ -618,18 +678,19 @@ bool attn_shape_supported(int H, int D, int T) {
     return true;
 }
 
-int attn_scratch_width_fwd(int H, int D) { return H * D + 2 * H; }
+int attn_scratch_width_fwd(int H, int D) { return (H * D + 2 * H + 3) & ~3; }
 
 int attn_bwd_row_blocks(int n_seg) {
     int want = (n_seg + kWarpsPerBlock - 1) / kWarpsPerBlock;
-    int cap = 148 * 8;
+    int cap = 148 * 12;
     return want < cap ? (want > 0 ? want : 1) : cap;
 }
 
 void attn_fwd(const AttnFwdArgs& a, cudaStream_t s) {
     const AttnCommon& c = a.c;
     if (c.plan.n_seg == 0) return;
-    const int blocks = (c.plan.n_seg + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    int blocks = (c.plan.n_seg + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    if (blocks > 148 * 24) blocks = 148 * 24;          // persistent: a few waves of resident blocks stride over the segments
     const size_t sm = table_bytes(c);
     const bool peer = a.k_peers != nullptr;
     const int cpl = cpl_of(c.H, c.D);
@@ -660,8 +721,13 @@ void attn_bwd_row(const AttnBwdRowArgs& a, cudaStream_t s) {
     const int HD = c.H * c.D;
 #define GT_LAUNCH_ROW(TT, CPL)                                                           \
     do {                                                                                 \
-        set_smem(attn_bwd_row_kernel<TT, CPL>, sm);                                      \
-        attn_bwd_row_kernel<TT, CPL><<<blocks, kWarpsPerBlock * 32, sm, s>>>(a);         \
+        if (c.score == SCORE_GATED) {                                                    \
+            set_smem(attn_bwd_row_kernel<TT, CPL, true>, sm);                            \
+            attn_bwd_row_kernel<TT, CPL, true><<<blocks, kWarpsPerBlock * 32, sm, s>>>(a);   \
+        } else {                                                                         \
+            set_smem(attn_bwd_row_kernel<TT, CPL, false>, sm);                           \
+            attn_bwd_row_kernel<TT, CPL, false><<<blocks, kWarpsPerBlock * 32, sm, s>>>(a);  \
+        }                                                                                \
         if (c.plan.n_split > 0)                                                          \
             sum_slots_kernel<TT><<<c.plan.n_split, 256, 0, s>>>(c.plan, c.scratch, HD, a.row_map,                       \
                 a.accumulate_dq ? nullptr : static_cast<TT*>(a.dq), a.accumulate_dq ? static_cast<float*>(a.dq) : nullptr, \
@@ -675,7 +741,8 @@ void attn_bwd_row(const AttnBwdRowArgs& a, cudaStream_t s) {
 void attn_bwd_col(const AttnBwdColArgs& a, cudaStream_t s) {
     const AttnCommon& c = a.c;
     if (c.plan.n_seg == 0) return;
-    const int blocks = (c.plan.n_seg + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    int blocks = (c.plan.n_seg + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    if (blocks > 148 * 24) blocks = 148 * 24;
     const size_t sm = table_bytes(c);
     const int cpl = cpl_of(c.H, c.D);
     const int HD = c.H * c.D;
@@ -694,7 +761,7 @@ void attn_bwd_col(const AttnBwdColArgs& a, cudaStream_t s) {
 
 void reduce_partials(const float* part, int n_blocks, int width, float* out, cudaStream_t s) {
     if (width <= 0) return;
-    reduce_partials_kernel<<<(width + 255) / 256, 256, 0, s>>>(part, n_blocks, width, out);
+    reduce_partials_kernel<<<(width + 31) / 32, dim3(32, 8), 0, s>>>(part, n_blocks, width, out);
 }
 
 }  // namespace gt

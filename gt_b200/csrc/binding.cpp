@@ -117,13 +117,16 @@ void reduce_partials(Tensor part, Tensor out) {
 
 bool attn_shape_supported(int64_t H, int64_t D, int64_t T) { return gt::attn_shape_supported((int)H, (int)D, (int)T); }
 
-void spmm(Tensor ptr, Tensor idx, OptT w, Tensor x, Tensor out, bool accumulate) {
+void spmm(Tensor ptr, Tensor idx, OptT w, Tensor x, Tensor out, bool accumulate, std::vector<Tensor> plan, OptT scratch) {
     c10::cuda::CUDAGuard guard(x.device());
     check_cuda_contig(x, "x");
     TORCH_CHECK(x.size(1) % 8 == 0 && x.size(1) <= 1024, "feature width must be a multiple of 8 and <= 1024");
     gt::SpmmArgs a{};
     a.dtype = dt(x); a.ptr = ptr.data_ptr<int>(); a.idx = idx.data_ptr<int>(); a.w = cptr<float>(w);
     a.x = x.data_ptr(); a.out = out.data_ptr(); a.n_out = (int)out.size(0); a.d = (int)x.size(1); a.accumulate = accumulate ? 1 : 0;
+    a.use_plan = plan.empty() ? 0 : 1;
+    if (a.use_plan) a.plan = make_plan(plan);
+    a.scratch = scratch.has_value() && scratch->defined() ? scratch->data_ptr<float>() : nullptr;
     gt::spmm(a, stream());
 }
 

@@ -34,6 +34,19 @@ template <> struct Vec8<__nv_bfloat16> {
             f[2 * i + 1] = x.y;
         }
     }
+    // raw 16-byte register form of a chunk: gathers are held packed and converted on use (4 registers instead of 8)
+    using Raw = uint4;
+    static __device__ __forceinline__ Raw load_raw(const __nv_bfloat16* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+    static __device__ __forceinline__ Raw zero_raw() { return make_uint4(0u, 0u, 0u, 0u); }
+    static __device__ __forceinline__ void unpack(const Raw& u, float (&f)[8]) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 x = __bfloat1622float2(h[i]);
+            f[2 * i] = x.x;
+            f[2 * i + 1] = x.y;
+        }
+    }
     static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&f)[8]) {
         uint4 u;
         __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
@@ -51,6 +64,22 @@ template <> struct Vec8<float> {
     static __device__ __forceinline__ void load_nc(const float* p, float (&f)[8]) {
         float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p + 4));
         f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    }
+    struct Raw { float4 a, b; };
+    static __device__ __forceinline__ Raw load_raw(const float* p) {
+        Raw r;
+        r.a = __ldg(reinterpret_cast<const float4*>(p));
+        r.b = __ldg(reinterpret_cast<const float4*>(p + 4));
+        return r;
+    }
+    static __device__ __forceinline__ Raw zero_raw() {
+        Raw r;
+        r.a = make_float4(0.f, 0.f, 0.f, 0.f);
+        r.b = r.a;
+        return r;
+    }
+    static __device__ __forceinline__ void unpack(const Raw& r, float (&f)[8]) {
+        f[0] = r.a.x; f[1] = r.a.y; f[2] = r.a.z; f[3] = r.a.w; f[4] = r.b.x; f[5] = r.b.y; f[6] = r.b.z; f[7] = r.b.w;
     }
     static __device__ __forceinline__ void store(float* p, const float (&f)[8]) {
         *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);

@@ -90,6 +90,9 @@ struct SpmmArgs {
     void* out;              // [n_out, d]
     int n_out, d;
     int accumulate;
+    int use_plan;           // 1: one warp per plan segment (hub rows are cut and merged through `scratch`), 0: one warp per row
+    SegPlan plan;
+    float* scratch;         // [n_slots, d] fp32
 };
 void spmm(const SpmmArgs& a, cudaStream_t s);
 // out[r] = sum_{k in [ptr[r], ptr[r+1])} rows[perm[k]]   (deterministic segmented row sum)

@@ -314,7 +314,10 @@ void layer_norm_fwd(const LayerNormArgs& a, cudaStream_t s) {
     else ln_fwd_kernel<float><<<blocks, kWarps * 32, 0, s>>>(a);
 }
 
-int layer_norm_bwd_blocks(int n) { return grid_for(n, kWarps * 8); }
+int layer_norm_bwd_blocks(int n) {
+    int b = grid_for(n, kWarps * 8);
+    return b > 148 * 4 ? 148 * 4 : b;                  // few, fat blocks: the partial buffers stay small
+}
 
 void layer_norm_bwd(const LayerNormBwdArgs& a, cudaStream_t s) {
     if (a.n <= 0) return;
@@ -336,7 +339,10 @@ void bias_act_dropout(int dtype, const void* in, const float* bias, void* out, l
                                                               act, p, seed, stream_id);
 }
 
-int colsum_blocks(long long n) { return grid_for(n, 64); }
+int colsum_blocks(long long n) {
+    int b = grid_for(n, 64);
+    return b > 148 * 4 ? 148 * 4 : b;
+}
 
 void bias_act_dropout_bwd(int dtype, const void* dout, const void* in, const float* bias, void* dz, long long n, int d, int act,
                           float p, const long long* seed, long long stream_id, float* dbias_part, int n_blocks, cudaStream_t s) {

@@ -23,6 +23,34 @@ _EXT = [None]
 _GEMM_IMPL = os.environ.get("GT_GEMM", "tcgen05")      # "tcgen05" (default) | "cublas" (debug / comparison only)
 
 
+LAUNCHES = {}          # entry point -> number of calls (every call enqueues at least one kernel of this package)
+
+
+class _CountingExt:
+    """Thin proxy of the extension module that counts the calls per entry point (the launch census of bench.py)."""
+
+    def __init__(self, mod):
+        self._mod = mod
+        self._cache = {}
+
+    def __getattr__(self, name):
+        fn = self._cache.get(name)
+        if fn is None:
+            raw = getattr(self._mod, name)
+
+            def fn(*a, _raw=raw, _name=name, **kw):
+                LAUNCHES[_name] = LAUNCHES.get(_name, 0) + 1
+                return _raw(*a, **kw)
+            self._cache[name] = fn
+        return fn
+
+
+def launch_count() -> int:
+    """Kernel-launching calls made so far (host-side helpers such as heap management are not counted)."""
+    skip = ("heap_", "tensor_from_ptr", "attn_shape_supported", "_blocks")
+    return sum(v for k, v in LAUNCHES.items() if not any(s in k for s in skip))
+
+
 def ext():
     """The native module; raises if it has not been built."""
     if _EXT[0] is None:
@@ -31,7 +59,7 @@ def ext():
         if mod is None:
             raise RuntimeError("gt_b200 native extension is not built: run `python -m gt_b200.build_ext` "
                                "(or __graft_entry__.build()) before using CUDA tensors")
-        _EXT[0] = mod
+        _EXT[0] = _CountingExt(mod)
     return _EXT[0]
 
 
@@ -279,6 +307,9 @@ def gated_residual(r, o, gate_weight, gate_bias, ln_weight, ln_bias, eps, p):
     return torch.nn.functional.dropout(out, p, True) if p > 0 else out
 
 
+SPMM_SEG = 256          # rows longer than this are cut into segments handled by separate warps
+
+
 # ---- sparse ------------------------------------------------------------------------------------------------------------------
 def spmm(blk, x, transpose=False, out=None):
     """``A @ x`` or ``A^T @ x`` for a BlockCSR with fp32 weights; ``out`` is accumulated into when given."""
@@ -291,15 +322,17 @@ def spmm(blk, x, transpose=False, out=None):
         return _spmm_torch(cols_of, rowidx.long(), w_t, x, blk.n_cols, out)
     x = x.contiguous()
     if not transpose:
-        ptr, idx, w, n_out = blk.crow, blk.col, blk.weight, blk.n_rows
+        ptr, idx, w, n_out, plan = blk.crow, blk.col, blk.weight, blk.n_rows, blk.row_plan(SPMM_SEG)
     else:
         ptr, idx, _, _, w = blk.csc()
-        n_out = blk.n_cols
+        n_out, plan = blk.n_cols, blk.col_plan(SPMM_SEG)
     w = w if w.dtype == torch.float32 else w.float()
     acc = out is not None
     if out is None:
         out = torch.empty(n_out, x.shape[1], dtype=x.dtype, device=x.device)
-    ext().spmm(ptr, idx, w, x, out, acc)
+    scratch = torch.empty(plan.num_slots, x.shape[1], dtype=torch.float32, device=x.device) if plan.num_slots else None
+    ext().spmm(ptr, idx, w, x, out, acc, [plan.seg_row, plan.seg_beg, plan.seg_end, plan.seg_slot, plan.split_rows, plan.split_ptr],
+               scratch)
     return out
 
 
@@ -308,5 +341,5 @@ def segment_sum_rows(rows, perm, ptr, out):
     if rows.shape[1] % 8 or rows.shape[1] > 1024 or not _dt_ok(rows):
         seg = torch.repeat_interleave(torch.arange(out.shape[0], device=rows.device), (ptr[1:] - ptr[:-1]).long())
         return out.zero_().index_add_(0, seg, rows[perm.long()])
-    ext().spmm(ptr, perm, None, rows.contiguous(), out, False)
+    ext().spmm(ptr, perm, None, rows.contiguous(), out, False, [], None)
     return out
