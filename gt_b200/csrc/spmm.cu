@@ -3,8 +3,11 @@
 // 16-byte chunks, LPR = min(32, pow2ceil(d/8)) lanes per row, several edges per warp iteration when d < 256, fp32
 // accumulation.  Bandwidth-bound gather like the attention kernels (replaces cuSPARSE CSR SpMM of the reference,
 // gt3d/gt3d/dist/layers.py:53-64, and the ones-valued SpMM of sparse_comm.py:190-202).
+#include <stdio.h>
+
 #include "common.cuh"
 #include "kernels.h"
+#include "noalloc.h"
 
 namespace gt {
 namespace {
@@ -130,3 +133,62 @@ void segment_sum_rows(int dtype, const void* rows, const int* perm, const int* p
 }
 
 }  // namespace gt
+
+// ---- allocation-free entry point (see noalloc.h) -------------------------------------------------------------------------
+// The scratch of the split-row merge as a file-scope device array.  In host code the name `gt_noalloc_scratch` is only a
+// handle for the runtime, not a device address: the address is obtained per device with cudaGetSymbolAddress below.
+static __device__ __align__(256) float gt_noalloc_scratch[GT_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {};
+thread_local char g_noalloc_err[256] = "";
+
+int noalloc_fail(int code, const char* msg, const char* detail = "") {
+    snprintf(g_noalloc_err, sizeof(g_noalloc_err), "%s%s", msg, detail);
+    return code;
+}
+}  // namespace
+
+extern "C" const char* gt_noalloc_last_error(void) { return g_noalloc_err; }
+
+extern "C" size_t gt_noalloc_scratch_floats(void) { return (size_t)GT_NOALLOC_SCRATCH_FLOATS; }
+
+extern "C" int gt_spmm_csr_noalloc(int dtype, const int* ptr, const int* idx, const float* w, const void* x, void* out, int n_out, int d,
+                                   const int* seg_row, const int* seg_beg, const int* seg_end, const int* seg_slot, int n_seg,
+                                   const int* split_rows, const int* split_ptr, int n_split, int n_slots, void* stream) {
+    g_noalloc_err[0] = 0;
+    if (dtype != gt::DT_F32 && dtype != gt::DT_BF16) return noalloc_fail(GT_NOALLOC_ERR_ARGUMENT, "dtype must be 0 (float32) or 1 (bfloat16)");
+    if (n_out < 0 || n_seg < 0 || n_split < 0 || n_slots < 0 || d <= 0 || (d % 8) || d > 1024)
+        return noalloc_fail(GT_NOALLOC_ERR_ARGUMENT, "need n_out, n_seg, n_split, n_slots >= 0 and d a multiple of 8 in [8, 1024]");
+    if (!ptr || !idx || !x || !out || !seg_row || !seg_beg || !seg_end || !seg_slot || (n_split > 0 && (!split_rows || !split_ptr)))
+        return noalloc_fail(GT_NOALLOC_ERR_ARGUMENT, "null pointer argument");
+    if ((size_t)n_slots * (size_t)d > (size_t)GT_NOALLOC_SCRATCH_FLOATS) {
+        char detail[96];
+        snprintf(detail, sizeof(detail), " (requested %d slots x %d floats, capacity %u floats)", n_slots, d, GT_NOALLOC_SCRATCH_FLOATS);
+        return noalloc_fail(GT_NOALLOC_ERR_CAPACITY, "split-row scratch exceeds the built-in array", detail);
+    }
+    if (n_out == 0 || n_seg == 0) return GT_NOALLOC_OK;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return noalloc_fail(GT_NOALLOC_ERR_CUDA, "cudaGetDevice failed: ", cudaGetErrorString(e));
+    if (dev < 0 || dev >= kMaxDevices) return noalloc_fail(GT_NOALLOC_ERR_ARGUMENT, "device index out of range");
+    if (g_noalloc_ptr[dev] == nullptr) {
+        // one-time set-up for this device (the device is current): translate the symbol into its device address
+        float* p = nullptr;
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), gt_noalloc_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return noalloc_fail(GT_NOALLOC_ERR_CUDA, "cudaGetSymbolAddress(gt_noalloc_scratch) failed: ", cudaGetErrorString(e));
+        g_noalloc_ptr[dev] = p;
+    }
+    gt::SpmmArgs a{};
+    a.dtype = dtype; a.ptr = ptr; a.idx = idx; a.w = w; a.x = x; a.out = out; a.n_out = n_out; a.d = d; a.accumulate = 0;
+    a.use_plan = 1;
+    a.plan.seg_row = seg_row; a.plan.seg_beg = seg_beg; a.plan.seg_end = seg_end; a.plan.seg_slot = seg_slot; a.plan.n_seg = n_seg;
+    a.plan.split_rows = split_rows; a.plan.split_ptr = split_ptr; a.plan.n_split = n_split;
+    a.scratch = g_noalloc_ptr[dev];
+    gt::spmm(a, static_cast<cudaStream_t>(stream));
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return noalloc_fail(GT_NOALLOC_ERR_CUDA, "kernel launch failed: ", cudaGetErrorString(e));
+    return GT_NOALLOC_OK;
+}
