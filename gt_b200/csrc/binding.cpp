@@ -288,6 +288,12 @@ void wait_flags(Tensor my_flags, int64_t n_peers, int64_t value, int64_t max_spi
     gt::wait_flags(my_flags.data_ptr<int>(), (int)n_peers, (int)value, max_spins, status.data_ptr<int>(), stream());
 }
 
+void group_barrier(Tensor peer_flag_ptrs, Tensor my_flags, Tensor counter, int64_t my_index, int64_t max_spins, Tensor status) {
+    c10::cuda::CUDAGuard guard(my_flags.device());
+    gt::group_barrier(reinterpret_cast<int* const*>(peer_flag_ptrs.data_ptr()), my_flags.data_ptr<int>(), counter.data_ptr<int>(),
+                      (int)peer_flag_ptrs.numel(), (int)my_index, max_spins, status.data_ptr<int>(), stream());
+}
+
 void pull_gather_rows(Tensor peer_ptrs, Tensor owner, Tensor row, Tensor out) {
     c10::cuda::CUDAGuard guard(out.device());
     const int row_bytes = (int)(out.numel() / std::max<int64_t>(out.size(0), 1) * out.element_size());
@@ -353,6 +359,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("tensor_from_ptr", &tensor_from_ptr);
     m.def("signal_peers", &signal_peers);
     m.def("wait_flags", &wait_flags);
+    m.def("group_barrier", &group_barrier);
     m.def("pull_gather_rows", &pull_gather_rows);
     m.def("pull_reduce_rows", &pull_reduce_rows);
     m.def("pull_all_gather", &pull_all_gather);

@@ -192,5 +192,8 @@ void pull_all_reduce(int dtype, const void* const* peers, int n_peers, void* out
 // signal / wait on epoch flags in peer memory with a bounded spin; status != 0 on expiry
 void signal_peers(int* const* peer_flags, int n_peers, int my_index, int value, cudaStream_t s);
 void wait_flags(const int* my_flags, int n_peers, int value, long long max_spins, int* status, cudaStream_t s);
+// signal + wait with a device-resident epoch counter (safe to replay inside a CUDA graph)
+void group_barrier(int* const* peer_flags, const int* my_flags, int* counter, int n_peers, int my_index, long long max_spins,
+                   int* status, cudaStream_t s);
 
 }  // namespace gt

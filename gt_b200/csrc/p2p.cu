@@ -42,6 +42,28 @@ __global__ void wait_kernel(const int* my_flags, int n_peers, int value, long lo
     }
 }
 
+// Group barrier whose epoch lives in device memory: the kernel itself advances the counter, so the same captured kernel is
+// correct on every replay of a CUDA graph.  Thread 0 bumps the epoch, every thread p < n publishes it to peer p (release,
+// system scope) and then waits (bounded) until peer p has published the same epoch to this rank.
+__global__ void barrier_kernel(int* const* peer_flags, const int* my_flags, int* counter, int n_peers, int my_index,
+                               long long max_spins, int* status) {
+    __shared__ int epoch;
+    if (threadIdx.x == 0) { epoch = *counter + 1; *counter = epoch; }
+    __syncthreads();
+    __threadfence_system();
+    const int p = threadIdx.x;
+    if (p >= n_peers) return;
+    st_release_sys(peer_flags[p] + my_index, epoch);
+    long long spins = 0;
+    while (ld_acquire_sys(my_flags + p) < epoch) {
+        if (++spins > max_spins) {
+            atomicExch(status, 100 + p);
+            return;
+        }
+        __nanosleep(32);
+    }
+}
+
 // warp per row: out[k] = peers[owner[k]][row[k]]
 __global__ void pull_gather_kernel(const void* const* peers, const int* owner, const int* row, uint8_t* out, int n, int row_bytes) {
     const int warps = (blockDim.x >> 5) * gridDim.x;
@@ -134,6 +156,11 @@ void signal_peers(int* const* peer_flags, int n_peers, int my_index, int value, 
 
 void wait_flags(const int* my_flags, int n_peers, int value, long long max_spins, int* status, cudaStream_t s) {
     wait_kernel<<<1, 32, 0, s>>>(my_flags, n_peers, value, max_spins, status);
+}
+
+void group_barrier(int* const* peer_flags, const int* my_flags, int* counter, int n_peers, int my_index, long long max_spins,
+                   int* status, cudaStream_t s) {
+    barrier_kernel<<<1, 32, 0, s>>>(peer_flags, my_flags, counter, n_peers, my_index, max_spins, status);
 }
 
 void pull_gather_rows(const void* const* peers, const int* owner, const int* row, void* out, int n, int row_bytes, cudaStream_t s) {

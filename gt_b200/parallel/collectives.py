@@ -22,6 +22,21 @@ from ..utils.timers import timers
 from .grid import group_name, group_size
 
 _STATS_HOOK = [None]          # set by utils.collstats to time every raw collective
+_HEAP = [None]                # symmetric heap: when set, CUDA row collectives run on the package's peer-memory kernels
+
+
+def set_transport(heap):
+    """Route the dense row collectives of CUDA tensors through ``heap`` (a :class:`~gt_b200.parallel.symm.SymmetricHeap`);
+    ``None`` restores NCCL."""
+    _HEAP[0] = heap
+
+
+def _p2p_ok(x, group, rows_out):
+    h = _HEAP[0]
+    if h is None or not x.is_cuda or x.dtype not in (torch.float32, torch.bfloat16):
+        return False
+    per_rank = x.numel() // (group_size(group) if rows_out else 1)
+    return (per_rank * x.element_size()) % 16 == 0 and per_rank % 8 == 0
 
 
 def _instrument(kind, group, nbytes, fn):
@@ -41,6 +56,9 @@ def raw_all_gather_rows(x, group, async_op=False):
     if g == 1:
         return (None, x) if async_op else x
     x = x.contiguous()
+    if _p2p_ok(x, group, False):
+        out = _instrument("all_gather", group, g * x.numel() * x.element_size(), lambda: _HEAP[0].all_gather(x, group))
+        return (None, out) if async_op else out
     out = x.new_empty((g * x.shape[0],) + tuple(x.shape[1:]))
     if async_op:
         return dist.all_gather_into_tensor(out, x, group=group, async_op=True), out
@@ -56,6 +74,9 @@ def raw_reduce_scatter_rows(x, group, async_op=False):
         return (None, x) if async_op else x
     x = x.contiguous()
     n = x.shape[0] // g
+    if _p2p_ok(x, group, True):
+        out = _instrument("reduce_scatter", group, x.numel() * x.element_size(), lambda: _HEAP[0].reduce_scatter(x, group))
+        return (None, out) if async_op else out
     if _is_gloo(group):
         def run():
             y = x.clone() if x.dtype != torch.bfloat16 else x.float()

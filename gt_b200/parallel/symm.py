@@ -1,0 +1,225 @@
+"""Symmetric heap and peer-memory collectives (NVLink 5 / NVSwitch, one process per GPU on one node).
+
+Every rank ``cudaMalloc``s one heap of the same size, exports it with CUDA IPC and opens the heaps of all peers, so
+every kernel can be given a table of peer base addresses.  Allocation inside the heap is a bump allocator that all
+ranks drive with the same sequence of requests: an object therefore lives at the same offset on every rank
+("symmetric").  NCCL / gloo is only used once, to exchange the 64-byte IPC handles.
+
+Collectives are *receiver driven*: a rank publishes its contribution in a staging buffer of the heap, a group barrier
+orders the publication, and the rank's own kernel then reads what it needs from the peers' buffers
+(``csrc/p2p.cu``): dense all-gather / reduce-scatter / all-reduce, and the sparse ``pull_gather`` / ``pull_reduce`` that
+move only the rows a tile references.  Reductions sum in fp32 in a fixed peer order.
+
+Synchronisation.  One barrier per collective: a kernel that publishes a device-resident epoch into every peer's flag
+array and waits (bounded) for the peers' epochs.  The epoch counter lives in device memory, so a captured CUDA graph
+replays correctly.  Staging buffers are keyed by the position of the collective inside the step (``begin_step`` resets
+the position and issues one extra barrier), so a buffer is rewritten only after at least one later barrier, which
+implies that every peer has finished reading the previous contents.  A wait that expires writes the peer index to the
+status word (``gt_b200.ops.native.check_status`` raises on the host); nothing spins forever.
+"""
+import torch
+import torch.distributed as dist
+
+from ..ops import native
+
+_DT = {torch.float32: 0, torch.bfloat16: 1, torch.int32: 2, torch.int64: 3, torch.uint8: 4}
+MAX_SPINS = 5_000_000          # ~1 s of polling before a barrier gives up
+
+
+class GroupContext:
+    """Peers of one process group: index of this rank, global ranks, flag array and barrier counter."""
+
+    def __init__(self, heap, group, name):
+        self.heap, self.group, self.name = heap, group, name
+        self.size = dist.get_world_size(group)
+        self.me = dist.get_rank(group)
+        self.ranks = [dist.get_global_rank(group, i) if group is not None else i for i in range(self.size)]
+        self.flags_off = heap.alloc(4 * 64)                     # int32[64] epoch flags written by the peers
+        self.flags = heap.view(self.flags_off, (64,), torch.int32)
+        self.counter = torch.zeros(1, dtype=torch.int32, device=heap.device)
+        self.peer_flag_ptrs = heap.peer_table(self.flags_off, self.ranks)
+        self.seq = 0
+        self.buffers = {}                                       # (seq, kind) -> (offset, nbytes)
+
+    def barrier(self):
+        native.ext().group_barrier(self.peer_flag_ptrs, self.flags, self.counter, self.me, MAX_SPINS, native.status(self.heap.device))
+
+    def staging(self, nbytes, kind):
+        """Staging buffer of this call site (same offset on all ranks of the group)."""
+        key = (self.seq, kind)
+        self.seq += 1
+        buf = self.buffers.get(key)
+        if buf is None or buf[1] < nbytes:
+            buf = (self.heap.alloc(nbytes), nbytes)
+            self.buffers[key] = buf
+        return buf[0]
+
+
+class SymmetricHeap:
+    def __init__(self, device, bytes_=1 << 30):
+        if not dist.is_initialized():
+            raise RuntimeError("the symmetric heap needs an initialised process group (IPC handle exchange)")
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        e = native.ext()
+        self.bytes = int(bytes_)
+        self.base = e.heap_alloc(self.bytes)
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        handles = [None] * self.world
+        dist.all_gather_object(handles, (self.rank, e.heap_ipc_handle(self.base)))
+        self.peer_base = [0] * self.world
+        for r, h in handles:
+            self.peer_base[r] = self.base if r == self.rank else e.heap_open(h)
+        self.top = 0
+        self.groups = {}
+        self.named = {}
+        dist.barrier()
+
+    # ---- allocation ------------------------------------------------------------------------------------------------------
+    def alloc(self, nbytes, align=256):
+        off = -(-self.top // align) * align
+        if off + nbytes > self.bytes:
+            raise MemoryError(f"symmetric heap exhausted: need {off + nbytes} bytes, have {self.bytes} (raise --heap_mb)")
+        self.top = off + nbytes
+        return off
+
+    def view(self, off, shape, dtype):
+        return native.ext().tensor_from_ptr(self.base + off, list(shape), _DT[dtype], self.device.index or 0)
+
+    def empty(self, numel, dtype, name=None):
+        """A tensor inside the heap (same offset on every rank when all ranks allocate in the same order)."""
+        nbytes = numel * torch.empty(0, dtype=dtype).element_size()
+        off = self.alloc(nbytes)
+        t = self.view(off, (numel,), dtype)
+        if name is not None:
+            self.named[name] = (off, nbytes)
+        return t
+
+    def peer_table(self, off, ranks):
+        """int64 device tensor with the address of offset ``off`` in the heap of every rank of ``ranks``."""
+        return torch.tensor([self.peer_base[r] + off for r in ranks], dtype=torch.int64, device=self.device)
+
+    def ctx(self, group):
+        key = id(group) if group is not None else None
+        c = self.groups.get(key)
+        if c is None:
+            c = self.groups[key] = GroupContext(self, group, str(key))
+        return c
+
+    def begin_step(self):
+        """Call at the start of every step (before capture / replay): resets the call-site positions."""
+        for c in self.groups.values():
+            c.seq = 0
+            c.barrier()
+
+    # ---- dense collectives ------------------------------------------------------------------------------------------------
+    def all_gather(self, x, group):
+        c = self.ctx(group)
+        x = x.contiguous()
+        nbytes = x.numel() * x.element_size()
+        if nbytes % 16:
+            raise ValueError("all_gather payload must be a multiple of 16 bytes per rank")
+        off = c.staging(nbytes, "ag")
+        self.view(off, x.shape, x.dtype).copy_(x)
+        c.barrier()
+        out = torch.empty((c.size * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        native.ext().pull_all_gather(self.peer_table_cached(c, off), out)
+        return out
+
+    def reduce_scatter(self, x, group):
+        c = self.ctx(group)
+        x = x.contiguous()
+        if x.dtype not in (torch.float32, torch.bfloat16) or (x.numel() // c.size) % 8:
+            raise ValueError("reduce_scatter needs fp32 / bf16 chunks that are multiples of 8 elements")
+        nbytes = x.numel() * x.element_size()
+        off = c.staging(nbytes, "rs")
+        self.view(off, x.shape, x.dtype).copy_(x)
+        c.barrier()
+        out = torch.empty((x.shape[0] // c.size,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        native.ext().pull_reduce_scatter(self.peer_table_cached(c, off), c.me, out)
+        return out
+
+    def all_reduce(self, x, out, name=None, group=None):
+        """``out = sum over ranks of x``; ``x`` should live in the heap (``heap.empty``), otherwise it is staged."""
+        c = self.ctx(group)
+        if name is not None and name in self.named:
+            off = self.named[name][0]
+            c.seq += 1
+        else:
+            off = c.staging(x.numel() * x.element_size(), "ar")
+            self.view(off, x.shape, x.dtype).copy_(x)
+        c.barrier()
+        native.ext().pull_all_reduce(self.peer_table_cached(c, off), out)
+        c.barrier()                      # x (the gradient buffer) is rewritten right away by the next step's zero-fill
+        return out
+
+    def peer_table_cached(self, c, off):
+        key = ("tbl", off)
+        t = c.buffers.get(key)
+        if t is None:
+            t = c.buffers[key] = self.peer_table(off, c.ranks)
+        return t
+
+    # ---- sparse collectives (SparseRowPlan transports) -----------------------------------------------------------------------
+    def _plan_state(self, plan):
+        st = getattr(plan, "_pull", None)
+        if st is None:
+            c = self.ctx(plan.group)
+            # owner-side table of the reduce: for every peer p and owned row r, the compact row of p that holds a partial of r
+            dev = self.device
+            src = torch.full((c.size, plan.rows_per_rank), -1, dtype=torch.int32, device=dev)
+            mine = torch.full((plan.rows_per_rank,), -1, dtype=torch.int32, device=dev)
+            sel = plan.need_owner == c.me
+            mine[plan.need_row[sel].long()] = torch.nonzero(sel).squeeze(1).to(torch.int32)
+            rows = [torch.empty_like(mine) for _ in range(c.size)]
+            dist.all_to_all(rows, [self._compact_index_for(plan, p, dev) for p in range(c.size)], group=plan.group)
+            for p in range(c.size):
+                src[p] = rows[p]
+            n_max = torch.tensor([plan.n_need], device=dev)
+            dist.all_reduce(n_max, op=dist.ReduceOp.MAX, group=plan.group)
+            st = plan._pull = dict(ctx=c, src=src.contiguous(), n_max=int(n_max.item()))
+        return st
+
+    @staticmethod
+    def _compact_index_for(plan, p, dev):
+        """For owner ``p``: compact row (in my need set) of each of p's rows, -1 where I hold no partial."""
+        out = torch.full((plan.rows_per_rank,), -1, dtype=torch.int32, device=dev)
+        sel = plan.need_owner == p
+        out[plan.need_row[sel].long()] = torch.nonzero(sel).squeeze(1).to(torch.int32)
+        return out
+
+    def pull_gather(self, x2, plan):
+        """``x2 [rows_per_rank, F]`` (my chunk) -> ``[n_need, F]``: the rows of the block this rank's tile references."""
+        st = self._plan_state(plan)
+        c = st["ctx"]
+        nbytes = x2.numel() * x2.element_size()
+        if (x2.shape[1] * x2.element_size()) % 16:
+            raise ValueError("rows must be a multiple of 16 bytes")
+        off = c.staging(nbytes, "pg")
+        self.view(off, x2.shape, x2.dtype).copy_(x2)
+        c.barrier()
+        out = torch.empty(plan.n_need, x2.shape[1], dtype=x2.dtype, device=x2.device)
+        native.ext().pull_gather_rows(self.peer_table_cached(c, off), plan.need_owner, plan.need_row, out)
+        return out
+
+    def pull_reduce(self, y2, plan):
+        """``y2 [n_need, F]`` partial rows -> ``[rows_per_rank, F]``: sum of the partials the peers hold for my rows."""
+        st = self._plan_state(plan)
+        c = st["ctx"]
+        if y2.shape[1] % 8 or y2.dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError("pull_reduce needs fp32 / bf16 rows with a width that is a multiple of 8")
+        nbytes = max(st["n_max"], 1) * y2.shape[1] * y2.element_size()
+        off = c.staging(nbytes, "pr")
+        if plan.n_need:
+            self.view(off, y2.shape, y2.dtype).copy_(y2)
+        c.barrier()
+        out = torch.empty(plan.rows_per_rank, y2.shape[1], dtype=y2.dtype, device=y2.device)
+        native.ext().pull_reduce_rows(self.peer_table_cached(c, off), st["src"], out)
+        return out
+
+    def close(self):
+        e = native.ext()
+        for r, p in enumerate(self.peer_base):
+            if r != self.rank and p:
+                e.heap_close(p)
+        e.heap_free(self.base)

@@ -47,6 +47,9 @@ class TrainEngine:
         self.lr, self.wd, self.total, self.warmup = lr, weight_decay, total_steps, warmup
         self.max_norm, self.betas, self.eps = max_grad_norm, betas, eps
         self.group, self.heap = group, heap
+        if heap is not None:
+            from ..parallel.collectives import set_transport
+            set_transport(heap)
         self.step_count = 0
         dev = self.params[0].device
         self.device = dev
@@ -119,6 +122,8 @@ class TrainEngine:
         self.flat_p.addcdiv_(self.flat_m / (1 - b1 ** t), denom, value=-self.cur_lr)
 
     def _body(self, loss_fn):
+        if self.heap is not None:
+            self.heap.begin_step()
         self.flat_g.zero_()
         loss = loss_fn()
         loss.backward()

@@ -1,0 +1,119 @@
+"""Peer-memory collectives and the distributed model on >= 2 real GPUs (NCCL for bootstrap and as the comparison).
+Child processes, one per GPU; skipped when the box has a single GPU."""
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _spawn(fn, world, *args):
+    import tempfile
+    import torch.multiprocessing as mp
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    with tempfile.TemporaryDirectory() as tmp:
+        mp.spawn(fn, args=(world, os.path.join(tmp, "store")) + args, nprocs=world, join=True)
+
+
+def _init(rank, world, store):
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", init_method=f"file://{store}", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    return torch.device("cuda", rank)
+
+
+def _collectives_worker(rank, world, store):
+    import torch.distributed as dist
+    from gt_b200.ops import native
+    from gt_b200.parallel.sparse_comm import SparseRowPlan
+    from gt_b200.parallel.symm import SymmetricHeap
+    dev = _init(rank, world, store)
+    heap = SymmetricHeap(dev, 256 << 20)
+    torch.manual_seed(rank)
+    for dtype in (torch.float32, torch.bfloat16):
+        for rep in range(3):                       # repeated use of the same call sites (staging reuse across "steps")
+            heap.begin_step()
+            x = torch.randn(1000, 64, device=dev).to(dtype)
+            ref = torch.empty(world * 1000, 64, device=dev, dtype=dtype)
+            dist.all_gather_into_tensor(ref, x)
+            assert torch.equal(heap.all_gather(x, None), ref)
+            y = torch.randn(world * 504, 72, device=dev).to(dtype)
+            ref = torch.empty(504, 72, device=dev, dtype=torch.float32)
+            dist.reduce_scatter_tensor(ref, y.float())
+            got = heap.reduce_scatter(y, None)
+            assert (got.float() - ref).abs().max() < (1e-5 if dtype == torch.float32 else 0.1)
+    g = heap.empty(4096, torch.float32, "grads")
+    out = torch.empty_like(g)
+    for rep in range(2):
+        heap.begin_step()
+        g.copy_(torch.randn(4096, device=dev))
+        ref = g.clone()
+        dist.all_reduce(ref)
+        heap.all_reduce(g, out, "grads")
+        assert (out - ref).abs().max() < 1e-5
+    # sparse plan: pull transport vs all-to-all-v transport
+    need = torch.unique(torch.randint(0, world * 300, (200,), device=dev))
+    plan_a = SparseRowPlan(None, 300, need, "t", "a2a")
+    plan_p = SparseRowPlan(None, 300, need, "t", "pull", heap)
+    for rep in range(2):
+        heap.begin_step()
+        x = torch.randn(300, 64, device=dev).bfloat16()
+        assert torch.equal(plan_p.gather(x), plan_a.gather(x))
+        yv = torch.randn(plan_a.n_need, 64, device=dev)
+        assert (plan_p.reduce_scatter(yv) - plan_a.reduce_scatter(yv)).abs().max() < 1e-4
+    torch.cuda.synchronize()
+    native.check_status(dev)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _model_worker(rank, world, store, grid_shape):
+    import torch.distributed as dist
+    from gt_b200.ops import native
+    from gt_b200.parallel.collectives import set_transport
+    from gt_b200.parallel.layers import dist_cross_entropy
+    from gt_b200.parallel.symm import SymmetricHeap
+    from gt_b200.train.engine import TrainEngine
+    from gt_b200.train.workloads import exphormer_workload
+    dev = _init(rank, world, store)
+    losses = {}
+    for comm in ("nccl", "p2p"):
+        heap = SymmetricHeap(dev, 512 << 20) if comm == "p2p" else None
+        set_transport(heap)
+        wl = exphormer_workload("exphormer_arxiv", grid_shape, dev, torch.bfloat16, scale_down=32, layers=2, hidden=128, heads=4,
+                                dropout=0.0, heap=heap)
+        model = wl["model"]
+        for p in model.parameters():
+            dist.broadcast(p.data, src=0)
+        eng = TrainEngine(model, total_steps=10, warmup=1, heap=heap, use_graph=(comm == "p2p"), graph_warmup=2)
+        x, y, m = wl["x"].to(dev), wl["y"].to(dev), wl["masks"]["train"].to(dev)
+        out = []
+        for _ in range(5):
+            out.append(eng.train_step(lambda: dist_cross_entropy(model(x), y, m, wl["n_train"])).clone())
+        torch.cuda.synchronize()
+        native.check_status(dev)
+        tot = torch.stack(out)
+        dist.all_reduce(tot)
+        losses[comm] = tot.cpu()
+        set_transport(None)
+    assert torch.isfinite(losses["p2p"]).all()
+    assert (losses["p2p"] - losses["nccl"]).abs().max() < 5e-2, (losses["p2p"], losses["nccl"])
+    assert losses["nccl"][-1] < losses["nccl"][0]
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_peer_memory_collectives_match_nccl():
+    _spawn(_collectives_worker, 2)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_dist_model_p2p_matches_nccl_2gpu():
+    _spawn(_model_worker, 2, (2, 1))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs >= 4 GPUs")
+def test_dist_model_p2p_matches_nccl_4gpu():
+    _spawn(_model_worker, 4, (2, 2))
