@@ -151,5 +151,5 @@ def run_reference(args):
             "e2e": {"value": edges_layers / (ms_e2e * 1e-3), "unit": "edges/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": 4, "clocks": clocks2},
             "loss": float(loss)}), flush=True)
-    dist.barrier()
-    dist.destroy_process_group()
+    from bench import finish
+    finish(dist)

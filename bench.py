@@ -178,8 +178,23 @@ def run_ours(args):
             "loss": float(loss), "peak_gb": peak.item(), "impl": "gt_b200",
         }
         print(json.dumps(out), flush=True)
-    dist.barrier()
-    dist.destroy_process_group()
+    finish(dist)
+
+
+def finish(dist):
+    """Leave without waiting on communicator teardown: a process group whose collectives were captured in a CUDA graph can
+    block in destroy_process_group; the result line is already printed, so synchronise, meet at a barrier and exit."""
+    import torch
+    torch.cuda.synchronize()
+    watchdog = threading.Timer(20.0, lambda: os._exit(0))
+    watchdog.daemon = True
+    watchdog.start()
+    try:
+        dist.barrier()
+    finally:
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():

@@ -23,14 +23,19 @@ import torch
 
 
 def build_csr(edge_index: torch.Tensor, num_rows: int, edge_type: Optional[torch.Tensor] = None):
-    """Sort edges by (destination, source).  Returns ``(crow[int64 n+1], col[int64 E], etype or None, perm)`` where
-    ``perm`` maps CSR position -> position in the input edge list."""
+    """Sort edges by (destination, edge type, source).  Returns ``(crow[int64 n+1], col[int64 E], etype or None, perm)``
+    where ``perm`` maps CSR position -> position in the input edge list.  Grouping a row's edges by type lets the kernels
+    keep the per-type gate slice in registers and reload it only when the type changes."""
     src, dst = edge_index[0].long(), edge_index[1].long()
     if src.numel() == 0:
         z = torch.zeros(0, dtype=torch.long, device=edge_index.device)
         return torch.zeros(num_rows + 1, dtype=torch.long, device=edge_index.device), z, (z if edge_type is not None else None), z
     width = int(src.max().item()) + 1
-    perm = torch.argsort(dst * width + src, stable=True)
+    if edge_type is not None:
+        nt = int(edge_type.max().item()) + 1
+        perm = torch.argsort((dst * nt + edge_type.long()) * width + src, stable=True)
+    else:
+        perm = torch.argsort(dst * width + src, stable=True)
     counts = torch.bincount(dst, minlength=num_rows)
     crow = torch.zeros(num_rows + 1, dtype=torch.long, device=edge_index.device)
     torch.cumsum(counts, 0, out=crow[1:])
@@ -160,7 +165,11 @@ class BlockCSR:
         column, destinations ascending inside a column; ``pos`` is the CSR position of every CSC entry."""
         if "csc" not in self._cache:
             col = self.col.long()
-            pos = torch.argsort(col, stable=True)
+            if self.etype is not None:                     # inside a column: grouped by type, then destination ascending
+                nt = int(self.etype.max().item()) + 1 if self.etype.numel() else 1
+                pos = torch.argsort(col * nt + self.etype.long(), stable=True)
+            else:
+                pos = torch.argsort(col, stable=True)
             ccol = torch.zeros(self.n_cols + 1, dtype=torch.long, device=self.device)
             torch.cumsum(torch.bincount(col, minlength=self.n_cols), 0, out=ccol[1:])
             rowidx = self.rows()[pos]

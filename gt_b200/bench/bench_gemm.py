@@ -1,0 +1,59 @@
+"""GEMM microbenchmark: the package's tcgen05 kernels against cuBLAS (torch.matmul) on the Linear shapes of the models
+(the GEMM TFLOPS constants of the performance model; counterpart of the GEMM section of the reference's
+``gt3d/bench/hw_constants.py``).  One ``GEMM`` line per shape: ms, TFLOP/s and effective GB/s for forward (NT), input
+gradient (NT on the transposed weight) and weight gradient (TN), and the cuBLAS time of the same product.
+
+    python -m gt_b200.bench.bench_gemm --rows 169344 --dims 256:768 256:256 256:512 512:256
+"""
+import argparse
+import json
+
+import torch
+
+
+def timeit(fn, iters, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(iters):
+        fn()
+    t1.record()
+    torch.cuda.synchronize()
+    return t0.elapsed_time(t1) / iters
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--rows", type=int, default=169344)
+    ap.add_argument("--dims", nargs="+", default=["256:768", "256:256", "256:512", "512:256", "128:256"])
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--only", default=None, choices=[None, "nt", "tn"])
+    args = ap.parse_args()
+    from ..ops import native
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    m = args.rows
+    for spec in args.dims:
+        k, n = (int(v) for v in spec.split(":"))
+        x = torch.randn(m, k, device=dev).bfloat16()
+        w = torch.randn(n, k, device=dev).bfloat16()
+        dy = torch.randn(m, n, device=dev).bfloat16()
+        flops = 2.0 * m * n * k
+        out = dict(M=m, K=k, N=n)
+        if args.only in (None, "nt"):
+            ms = timeit(lambda: native.gemm_nt(x, w), args.iters, args.warmup)
+            ms_ref = timeit(lambda: x @ w.t(), args.iters, args.warmup)
+            out.update(nt_ms=ms, nt_tflops=flops / ms / 1e9, nt_gbs=(m * k + m * n + n * k) * 2 / ms / 1e6, cublas_nt_ms=ms_ref)
+        if args.only in (None, "tn"):
+            ms = timeit(lambda: native.gemm_tn(dy, x), args.iters, args.warmup)
+            ms_ref = timeit(lambda: dy.t() @ x, args.iters, args.warmup)
+            out.update(tn_ms=ms, tn_tflops=flops / ms / 1e9, cublas_tn_ms=ms_ref)
+        native.check_status(dev)
+        print("GEMM " + json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

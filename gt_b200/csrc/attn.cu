@@ -106,6 +106,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 6 : 3)) attn_
             l[i] = 0.f;
             m[i] = softmax ? -INFINITY : 0.f;
         }
+        float qg[CPL][8];                 // q * scale * gate[type] of the type currently cached
+        int gt_cached = -1;
         // indices of the first group; every iteration prefetches the next group's indices before it touches K / V
         int jn[U], tn[U];
 #pragma unroll
@@ -147,15 +149,23 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 6 : 3)) attn_
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const bool ok = j[u] >= 0;
+                if (c.score == SCORE_GATED && t[u] != gt_cached) {      // edges of a row are grouped by type: rare reload
+                    gt_cached = t[u];
+#pragma unroll
+                    for (int i = 0; i < CPL; ++i) {
+                        const float* g = s_gate + gt_cached * HD + foff[i];
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) qg[i][x] = qf[i][x] * g[x];
+                    }
+                }
 #pragma unroll
                 for (int i = 0; i < CPL; ++i) {
                     float kf[8], vf[8];
                     Vec8<T>::unpack(kr[u][i], kf);
                     float s = 0.f;
                     if (c.score == SCORE_GATED) {
-                        const float* g = s_gate + t[u] * HD + foff[i];
 #pragma unroll
-                        for (int x = 0; x < 8; ++x) s = fmaf(qf[i][x] * kf[x], g[x], s);
+                        for (int x = 0; x < 8; ++x) s = fmaf(qg[i][x], kf[x], s);
                     } else {
 #pragma unroll
                         for (int x = 0; x < 8; ++x) s = fmaf(qf[i][x], kf[x], s);
@@ -318,6 +328,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 4 : 2)) attn_
 #pragma unroll
             for (int tt = 0; tt < kMaxTypesReg; ++tt) db[tt][i] = 0.f;
         }
+        float qg[CPL][8];
+        int gt_cached = -1;
         int jn[U], tn[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -352,6 +364,15 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 4 : 2)) attn_
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const bool ok = j[u] >= 0;
+                if (GATED && t[u] != gt_cached) {                       // edges of a row are grouped by type: rare reload
+                    gt_cached = t[u];
+#pragma unroll
+                    for (int i = 0; i < CPL; ++i) {
+                        const float* g = s_gate + gt_cached * HD + foff[i];
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) qg[i][x] = qf[i][x] * g[x];
+                    }
+                }
 #pragma unroll
                 for (int i = 0; i < CPL; ++i) {
                     float kf[8], vf[8];
@@ -359,9 +380,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 4 : 2)) attn_
                     Vec8<T>::unpack(vr[u][i], vf);
                     float s = 0.f, dp = 0.f;
                     if (GATED) {
-                        const float* g = s_gate + t[u] * HD + foff[i];
 #pragma unroll
-                        for (int x = 0; x < 8; ++x) s = fmaf(qf[i][x] * kf[x], g[x], s);
+                        for (int x = 0; x < 8; ++x) s = fmaf(qg[i][x], kf[x], s);
                     } else {
 #pragma unroll
                         for (int x = 0; x < 8; ++x) s = fmaf(qf[i][x], kf[x], s);
@@ -516,6 +536,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 5 : 2)) attn_
 #pragma unroll
             for (int x = 0; x < 8; ++x) { dk[i][x] = 0.f; dv[i][x] = 0.f; }
         }
+        float gc[CPL][8], kg[CPL][8];       // cached gate slice and k * gate of the type currently being walked
+        int gt_cached = -1;
         int rn[U], tn[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -555,16 +577,24 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 5 : 2)) attn_
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const bool ok = r[u] >= 0;
+                if (c.score == SCORE_GATED && t[u] != gt_cached) {      // a column's entries are grouped by type: rare reload
+                    gt_cached = t[u];
+#pragma unroll
+                    for (int i = 0; i < CPL; ++i) {
+                        const float* g = s_gate + gt_cached * HD + foff[i];
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) { gc[i][x] = g[x]; kg[i][x] = kf[i][x] * g[x]; }
+                    }
+                }
 #pragma unroll
                 for (int i = 0; i < CPL; ++i) {
                     float qf[8], rv[8];
                     Vec8<T>::unpack(qr[u][i], qf);
                     Vec8<T>::unpack(rr[u][i], rv);
-                    const float* g = s_gate + t[u] * HD + foff[i];
                     float s = 0.f, dp = 0.f;
                     if (c.score == SCORE_GATED) {
 #pragma unroll
-                        for (int x = 0; x < 8; ++x) s = fmaf(qf[x] * kf[i][x], g[x], s);
+                        for (int x = 0; x < 8; ++x) s = fmaf(qf[x], kg[i][x], s);
                     } else {
 #pragma unroll
                         for (int x = 0; x < 8; ++x) s = fmaf(qf[x], kf[i][x], s);
@@ -590,7 +620,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 5 : 2)) attn_
                     for (int x = 0; x < 8; ++x) dv[i][x] = fmaf(P, rv[x], dv[i][x]);
                     if (c.score == SCORE_GATED) {
 #pragma unroll
-                        for (int x = 0; x < 8; ++x) dk[i][x] = fmaf(ds * qf[x], g[x], dk[i][x]);
+                        for (int x = 0; x < 8; ++x) dk[i][x] = fmaf(ds * qf[x], gc[i][x], dk[i][x]);
                     } else {
 #pragma unroll
                         for (int x = 0; x < 8; ++x) dk[i][x] = fmaf(ds, qf[x], dk[i][x]);

@@ -19,6 +19,8 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <stdlib.h>
+
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -151,6 +153,39 @@ __device__ __forceinline__ uint64_t site_seed(const long long* seed, long long s
     return s0 + 0x9E3779B97F4A7C15ull * (s1 * 4096ull + (uint64_t)stream_id + 1ull);
 }
 
+// Epilogue arithmetic on one 32-column chunk of an accumulator row.  Every condition (bias present, activation, dropout,
+// partial tile) is tested once per chunk, never per element: the element loops are branch-free.
+__device__ __forceinline__ void epilogue_math(const uint32_t (&r)[32], float (&v)[32], int row, int col0, const GemmArgs& g,
+                                              uint64_t sd, float inv_keep) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+    const bool full = col0 + 32 <= g.N;
+    if (g.bias) {
+        if (full && (reinterpret_cast<uintptr_t>(g.bias) & 15) == 0) {      // parameter views are only 4-byte aligned in general
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                const float4 b = __ldg(reinterpret_cast<const float4*>(g.bias + col0 + j));
+                v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += (col0 + j < g.N) ? g.bias[col0 + j] : 0.f;
+        }
+    }
+    if (g.act == 1) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+    } else if (g.act == 2) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = gelu_f(v[j]);
+    }
+    if (g.p > 0.f) {
+        const uint64_t base = (uint64_t)row * g.N + col0;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = uniform01(sd, base + j) >= g.p ? v[j] * inv_keep : 0.f;
+    }
+}
+
 // ------------------------------------------------------------------------------------------------------------------
 // C = A * B^T (K-major operands)
 // ------------------------------------------------------------------------------------------------------------------
@@ -221,35 +256,29 @@ __global__ void __launch_bounds__(kThreads) gemm_nt_kernel(const __grid_constant
             const int row = m0 + quad * 32 + lane;
             const uint64_t sd = site_seed(g.seed, g.stream_id);
             const float inv_keep = g.p > 0.f ? 1.f / (1.f - g.p) : 1.f;
+            // bf16 results of full-width-aligned tiles go through shared memory (the pipeline stages are free once the
+            // accumulator is complete) so that global stores are whole 256-byte row segments instead of one row per lane
+            const bool staged = g.c_dtype == DT_BF16 && (g.ldc & 7) == 0 && (g.N & 7) == 0;
+            constexpr int kStageStride = BN * 2 + 16;              // bytes per staged row: +16 keeps 16-byte writes conflict-free
+            uint8_t* stage = reinterpret_cast<uint8_t*>(sh.a) + (size_t)quad * 32 * kStageStride;
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
+                __syncwarp();                                 // lanes that skipped the previous chunk rejoin before the aligned load
                 tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + c0, r);     // whole warp: sync.aligned
-                if (row >= g.M) continue;
                 const int col0 = n0 + c0;
-                if (col0 >= g.N) continue;
+                if (!staged && (row >= g.M || col0 >= g.N)) continue;
                 float v[32];
+                epilogue_math(r, v, row, col0, g, sd, inv_keep);
+                if (staged) {
+                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(stage + (size_t)lane * kStageStride) + c0;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int col = col0 + j;
-                    if (col < g.N) {
-                        float t = v[j] + (g.bias ? g.bias[col] : 0.f);
-                        if (g.act == 1) t = fmaxf(t, 0.f);
-                        else if (g.act == 2) t = gelu_f(t);
-                        if (g.p > 0.f) t = uniform01(sd, (uint64_t)row * g.N + col) >= g.p ? t * inv_keep : 0.f;
-                        v[j] = t;
-                    }
+                    for (int j = 0; j < 32; j += 8) Vec8<__nv_bfloat16>::store(dst + j, *reinterpret_cast<float(*)[8]>(&v[j]));
+                    continue;
                 }
                 const bool full = col0 + 32 <= g.N;
                 if (g.c_dtype == DT_BF16) {
                     __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(g.c) + (size_t)row * g.ldc + col0;
-                    if (full && (g.ldc & 7) == 0) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 8) Vec8<__nv_bfloat16>::store(dst + j, *reinterpret_cast<float(*)[8]>(&v[j]));
-                    } else {
-                        for (int j = 0; j < 32 && col0 + j < g.N; ++j) dst[j] = __float2bfloat16(v[j]);
-                    }
+                    for (int j = 0; j < 32 && col0 + j < g.N; ++j) dst[j] = __float2bfloat16(v[j]);
                 } else {
                     float* dst = static_cast<float*>(g.c) + (size_t)row * g.ldc + col0;
                     if (full && (g.ldc & 3) == 0) {
@@ -267,11 +296,198 @@ __global__ void __launch_bounds__(kThreads) gemm_nt_kernel(const __grid_constant
                     }
                 }
             }
+            if (staged) {
+                __syncwarp();
+                // 16 lanes cover one 256-byte row: two rows per instruction, 16 instructions for the warp's 32 rows
+                const int cchunk = lane & 15;
+                const bool col_ok = n0 + cchunk * 8 + 8 <= g.N;
+#pragma unroll 4
+                for (int it = 0; it < 16; ++it) {
+                    const int rr = it * 2 + (lane >> 4);
+                    const int grow = m0 + quad * 32 + rr;
+                    if (grow < g.M && col_ok) {
+                        const uint4 val = *reinterpret_cast<const uint4*>(stage + (size_t)rr * kStageStride + cchunk * 16);
+                        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(g.c) + (size_t)grow * g.ldc + n0 + cchunk * 8) = val;
+                    }
+                }
+            }
         }
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Persistent variant of C = A * B^T.  One CTA per SM walks the output tiles (n fastest, so CTAs running at the same time share
+// the A rows in L2).  Tensor memory holds TWO accumulators (2 x 128 columns): while the epilogue warps drain tile i, the MMA
+// thread already accumulates tile i + 1, and the TMA producer runs ahead through a 5-stage ring that is shared by all tiles
+// (stage indices and phases continue across tile boundaries).  TMEM allocation, barrier initialisation and pipeline fill are
+// paid once per CTA instead of once per tile, which is what bounds the short-K (128..512) GEMMs of these models.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int P_STAGES = 5;
+constexpr int kStageStrideP = BN * 2 + 16;               // staged C row: +16 bytes keeps 16-byte writes conflict-free
+
+struct __align__(1024) PersistentStorage {
+    __nv_bfloat16 a[P_STAGES][BM * BK];
+    __nv_bfloat16 b[P_STAGES][BN * BK];
+    uint8_t stage_c[4 * 32 * kStageStrideP];
+    uint64_t full[P_STAGES];
+    uint64_t empty[P_STAGES];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1) gemm_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                         const __grid_constant__ CUtensorMap map_b, GemmArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    PersistentStorage& sh = *reinterpret_cast<PersistentStorage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_n = (g.N + BN - 1) / BN, tiles_m = (g.M + BM - 1) / BM;
+    const int n_tiles = tiles_n * tiles_m;
+    const int nkb = (g.K + BK - 1) / BK;
+    volatile int* abort_flag = &sh.abort_flag;
+
+    if (threadIdx.x == 0) {
+        sh.abort_flag = 0;
+        for (int s = 0; s < P_STAGES; ++s) { mbar_init(&sh.full[s], 1); mbar_init(&sh.empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&sh.tmem_full[b], 1); mbar_init(&sh.tmem_empty[b], 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(&sh.tmem_base, 2 * kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh.tmem_base;
+
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer ----
+        int it = 0, issued_from = 0;
+        bool okay = true;
+        for (int tile = blockIdx.x; tile < n_tiles && okay; tile += gridDim.x) {
+            const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
+                const int s = it % P_STAGES;
+                okay = mbar_wait(&sh.empty[s], ((it / P_STAGES) & 1) ^ 1, abort_flag, g.status, 1);
+                if (!okay) break;
+                mbar_expect_tx(&sh.full[s], (BM + BN) * BK * 2);
+                tma_load_2d(sh.a[s], &map_a, kb * BK, m0, &sh.full[s]);
+                tma_load_2d(sh.b[s], &map_b, kb * BK, n0, &sh.full[s]);
+            }
+        }
+        if (*abort_flag) {
+            // drain: the copies issued into the last P_STAGES ring slots must land before the CTA may exit
+            issued_from = it > P_STAGES ? it - P_STAGES : 0;
+            for (int k = issued_from; k < it; ++k) {
+                const long long t0 = clock64();
+                while (!mbar_try_wait(&sh.full[k % P_STAGES], (k / P_STAGES) & 1) && clock64() - t0 < kWaitCycles) {}
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer ----
+        const uint32_t idesc = make_idesc(BM, BN, 0, 0);
+        int it = 0, ti = 0;
+        bool okay = true;
+        for (int tile = blockIdx.x; tile < n_tiles && okay; tile += gridDim.x, ++ti) {
+            const int b = ti & 1;
+            okay = mbar_wait(&sh.tmem_empty[b], ((ti >> 1) & 1) ^ 1, abort_flag, g.status, 2);   // epilogue drained this accumulator
+            if (!okay) break;
+            tc_fence_after();
+            const uint32_t acc = tmem + (uint32_t)(b * BN);
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
+                const int s = it % P_STAGES;
+                okay = mbar_wait(&sh.full[s], (it / P_STAGES) & 1, abort_flag, g.status, 2);
+                if (!okay) break;
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(sh.a[s]), b_addr = smem_u32(sh.b[s]);
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k)
+                    umma_bf16(acc, make_desc(a_addr + k * 32, 16, 1024), make_desc(b_addr + k * 32, 16, 1024), idesc, (kb | k) != 0);
+                umma_commit(&sh.empty[s]);
+            }
+            if (okay) umma_commit(&sh.tmem_full[b]);
+        }
+    } else if (warp >= 2) {
+        // ---- epilogue ----
+        const int quad = warp & 3;
+        const uint64_t sd = site_seed(g.seed, g.stream_id);
+        const float inv_keep = g.p > 0.f ? 1.f / (1.f - g.p) : 1.f;
+        const bool staged = g.c_dtype == DT_BF16 && (g.ldc & 7) == 0 && (g.N & 7) == 0;
+        uint8_t* stage = sh.stage_c + (size_t)quad * 32 * kStageStrideP;
+        int ti = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++ti) {
+            const int b = ti & 1;
+            const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+            if (!mbar_wait(&sh.tmem_full[b], (ti >> 1) & 1, abort_flag, g.status, 3)) break;
+            tc_fence_after();
+            const int row = m0 + quad * 32 + lane;
+            const uint32_t acc = tmem + (uint32_t)(b * BN) + ((uint32_t)(quad * 32) << 16);
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                __syncwarp();                                 // lanes that skipped the previous chunk rejoin before the aligned load
+                tmem_ld32(acc + c0, r);
+                if (c0 + 32 >= BN) {
+                    // last chunk read: hand the accumulator back to the MMA thread before the (slow) global stores
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sh.tmem_empty[b]);
+                }
+                const int col0 = n0 + c0;
+                if (!staged && (row >= g.M || col0 >= g.N)) continue;
+                float v[32];
+                epilogue_math(r, v, row, col0, g, sd, inv_keep);
+                if (staged) {
+                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(stage + (size_t)lane * kStageStrideP) + c0;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) Vec8<__nv_bfloat16>::store(dst + j, *reinterpret_cast<float(*)[8]>(&v[j]));
+                    continue;
+                }
+                if (g.c_dtype == DT_BF16) {
+                    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(g.c) + (size_t)row * g.ldc + col0;
+                    for (int j = 0; j < 32 && col0 + j < g.N; ++j) dst[j] = __float2bfloat16(v[j]);
+                } else {
+                    float* dst = static_cast<float*>(g.c) + (size_t)row * g.ldc + col0;
+                    if (col0 + 32 <= g.N && (g.ldc & 3) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                            if (g.accumulate) {
+                                const float4 old = *reinterpret_cast<float4*>(dst + j);
+                                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                            }
+                            *reinterpret_cast<float4*>(dst + j) = o;
+                        }
+                    } else {
+                        for (int j = 0; j < 32 && col0 + j < g.N; ++j) dst[j] = g.accumulate ? dst[j] + v[j] : v[j];
+                    }
+                }
+            }
+            if (staged) {
+                __syncwarp();
+                const int cchunk = lane & 15;
+                const bool col_ok = n0 + cchunk * 8 + 8 <= g.N;
+#pragma unroll 4
+                for (int i2 = 0; i2 < 16; ++i2) {
+                    const int rr = i2 * 2 + (lane >> 4);
+                    const int grow = m0 + quad * 32 + rr;
+                    if (grow < g.M && col_ok) {
+                        const uint4 val = *reinterpret_cast<const uint4*>(stage + (size_t)rr * kStageStrideP + cchunk * 16);
+                        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(g.c) + (size_t)grow * g.ldc + n0 + cchunk * 8) = val;
+                    }
+                }
+                __syncwarp();                                 // the staging rows are rewritten by the next tile
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, 2 * kTmemCols);
 }
 
 // ------------------------------------------------------------------------------------------------------------------
@@ -422,8 +638,23 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
         cudaFuncSetAttribute(gemm_nt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
         attr = true;
     }
-    dim3 grid((g.N + BN - 1) / BN, (g.M + BM - 1) / BM);
-    gemm_nt_kernel<<<grid, kThreads, kSmemBytes, s>>>(ma, mb, g);
+    static int n_sm = 0;
+    static bool simple = false;
+    if (n_sm == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+        const char* env = getenv("GT_GEMM_KERNEL");
+        simple = env && env[0] == 's';                    // "simple": the one-tile-per-CTA kernel (comparison / debugging)
+        cudaFuncSetAttribute(gemm_nt_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(PersistentStorage) + 1024));
+    }
+    if (simple) {
+        dim3 grid((g.N + BN - 1) / BN, (g.M + BM - 1) / BM);
+        gemm_nt_kernel<<<grid, kThreads, kSmemBytes, s>>>(ma, mb, g);
+    } else {
+        const int tiles = ((g.N + BN - 1) / BN) * ((g.M + BM - 1) / BM);
+        gemm_nt_persistent_kernel<<<tiles < n_sm ? tiles : n_sm, kThreads, sizeof(PersistentStorage) + 1024, s>>>(ma, mb, g);
+    }
     return (int)cudaGetLastError();
 }
 

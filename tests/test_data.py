@@ -1,0 +1,75 @@
+"""Expander generation, synthetic graphs, partitioner + loaders (pure host, no process group)."""
+import os
+
+import torch
+
+from gt_b200.data.expander import KeyedPermutation, block_expander_edges, keyed_expander_edges
+from gt_b200.data.loader import load_partition, read_meta
+from gt_b200.data.partition import partition_2d
+from gt_b200.data.synthetic import chung_lu, degrees, khop_edges, rmat, symmetrize, workload_graph
+from gt_b200.parallel.grid import BlockGrid
+
+
+def test_keyed_permutation_is_bijection_for_odd_sizes():
+    for n in (1, 2, 7, 1000, 4097):
+        img = KeyedPermutation(n, seed=3, index=1)(torch.arange(n))
+        assert img.unique().numel() == n and int(img.max()) == n - 1
+
+
+def test_block_expander_equals_global_on_several_grids():
+    n, deg = 1013, 3
+    glob = keyed_expander_edges(n, deg, seed=5)
+    key = lambda e: torch.unique(e[1] * 4096 + e[0])          # noqa: E731
+    for shape in ((2, 2, 1), (4, 1, 1), (1, 3, 1), (2, 1, 2)):
+        world = shape[0] * shape[1] * shape[2]
+        got = []
+        for rank in range(world):
+            g = BlockGrid.virtual(shape[0], shape[1], n, rank, p_heads=shape[2])
+            loc = block_expander_edges(g, n, deg, seed=5)
+            ref_loc, _ = g.local_block(glob)
+            assert torch.equal(key(loc), key(ref_loc)), (shape, rank)
+            got.append(loc.shape[1])
+        assert sum(got) == glob.shape[1] * shape[2]             # head-group ranks hold the same block
+
+
+def test_synthetic_generators_shapes_and_determinism():
+    a = chung_lu(2000, 9000, 2.1, seed=1)
+    assert torch.equal(a, chung_lu(2000, 9000, 2.1, seed=1)) and int(a.max()) < 2000
+    ind, _ = degrees(symmetrize(a, 2000), 2000)
+    assert ind.max() > 20 * ind.float().mean()                   # heavy tail
+    r = rmat(10, 5000, seed=2)
+    assert int(r.max()) < 1024 and r.shape[1] > 4000
+    ei, bucket = khop_edges(symmetrize(r, 1024), 1024)
+    assert set(bucket.unique().tolist()) == {0, 1, 2}
+    wl = workload_graph("cpu_small")
+    assert wl["n"] == 2000 and wl["x"].shape == (2000, 32)
+
+
+def test_partition_roundtrip_and_resume(tmp_path):
+    wl = workload_graph("cpu_small", seed=1)
+    n, ei = wl["n"], wl["edge_index"]
+    w = torch.rand(ei.shape[1])
+    out = str(tmp_path / "part")
+    meta = partition_2d(wl["x"], wl["y"], wl["masks"], ei, 10, out, p_part=4, edge_weight=w, pad_multiple=8, log=lambda *a: None)
+    assert read_meta(out)["n_pad"] == meta["n_pad"] and meta["n_pad"] % 8 == 0
+    os.remove(os.path.join(out, "blocks", "row_2.done"))          # an interrupted run: row 2 is redone, the others are skipped
+    logs = []
+    partition_2d(wl["x"], wl["y"], wl["masks"], ei, 10, out, p_part=4, edge_weight=w, pad_multiple=8, log=logs.append)
+    assert sum("skipped" in l for l in logs) == 3
+    for shape in ((2, 2), (1, 2), (8, 1), (2, 1, 2)):
+        world = 1
+        for s in shape:
+            world *= s
+        tot_e, tot_x = 0, 0
+        for rank in range(world):
+            g = BlockGrid.virtual(shape[0], shape[1], n, rank, p_heads=shape[2] if len(shape) == 3 else 1, n_pad=meta["n_pad"])
+            part = load_partition(out, g, "cpu")
+            ref_ei, _, ref_w = g.local_block(ei, None, w)
+            k = lambda e: e[1] * 100000 + e[0]                   # noqa: E731
+            o1, o2 = torch.argsort(k(part["edge_index"])), torch.argsort(k(ref_ei))
+            assert torch.equal(part["edge_index"][:, o1], ref_ei[:, o2]) and torch.allclose(part["weight"][o1], ref_w[o2])
+            assert torch.equal(part["x"], g.take_owned(wl["x"])) and torch.equal(part["y"], g.take_owned(wl["y"]))
+            tot_e += part["num_local_edges"]
+            tot_x += int(part["masks"]["train"].sum())
+        assert tot_e == ei.shape[1] * (shape[2] if len(shape) == 3 else 1)
+        assert tot_x == int(wl["masks"]["train"].sum())
