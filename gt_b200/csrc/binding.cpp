@@ -131,7 +131,7 @@ void spmm(Tensor ptr, Tensor idx, OptT w, Tensor x, Tensor out, bool accumulate,
 }
 
 void layer_norm_fwd(Tensor y, OptT x, OptT ybias, Tensor gamma, Tensor beta, Tensor out, OptT mean_rstd, double eps, double p,
-                    OptT seed, int64_t stream_id) {
+                    OptT seed, int64_t stream_id, OptT acc, OptT l, double eps_l) {
     c10::cuda::CUDAGuard guard(y.device());
     check_cuda_contig(y, "y");
     TORCH_CHECK(y.size(1) % 8 == 0 && y.size(1) <= 1024, "LayerNorm width must be a multiple of 8 and <= 1024");
@@ -141,13 +141,16 @@ void layer_norm_fwd(Tensor y, OptT x, OptT ybias, Tensor gamma, Tensor beta, Ten
     a.out = out.data_ptr(); a.mean_rstd = mean_rstd.has_value() && mean_rstd->defined() ? mean_rstd->data_ptr<float>() : nullptr;
     a.n = (int)y.size(0); a.d = (int)y.size(1); a.eps = (float)eps; a.p = (float)p;
     a.seed = cptr<long long>(seed); a.stream_id = stream_id;
+    a.acc = cptr<float>(acc); a.l = cptr<float>(l); a.H = a.l ? (int)l->size(1) : 1; a.eps_l = (float)eps_l;
+    if (a.acc) TORCH_CHECK((a.d / a.H) % 8 == 0 && (((a.d / a.H) / 8) & ((a.d / a.H) / 8 - 1)) == 0, "head width must be 8 * 2^k");
     gt::layer_norm_fwd(a, stream());
 }
 
 int64_t layer_norm_bwd_blocks(int64_t n) { return gt::layer_norm_bwd_blocks((int)n); }
 
 void layer_norm_bwd(Tensor dout, Tensor y, OptT x, OptT ybias, Tensor gamma, Tensor mean_rstd, Tensor dy, OptT dx, bool accumulate_dx,
-                    Tensor dgamma_part, Tensor dbeta_part, OptT dybias_part, double p, OptT seed, int64_t stream_id) {
+                    Tensor dgamma_part, Tensor dbeta_part, OptT dybias_part, double p, OptT seed, int64_t stream_id, OptT acc, OptT l,
+                    double eps_l, OptT dacc, OptT dl) {
     c10::cuda::CUDAGuard guard(y.device());
     gt::LayerNormBwdArgs a{};
     a.dtype = dt(y); a.dout = dout.data_ptr(); a.y = y.data_ptr(); a.x = x.has_value() && x->defined() ? x->data_ptr() : nullptr;
@@ -157,6 +160,9 @@ void layer_norm_bwd(Tensor dout, Tensor y, OptT x, OptT ybias, Tensor gamma, Ten
     a.dybias_part = dybias_part.has_value() && dybias_part->defined() ? dybias_part->data_ptr<float>() : nullptr;
     a.n_blocks = (int)dgamma_part.size(0);
     a.n = (int)y.size(0); a.d = (int)y.size(1); a.p = (float)p; a.seed = cptr<long long>(seed); a.stream_id = stream_id;
+    a.acc = cptr<float>(acc); a.l = cptr<float>(l); a.H = a.l ? (int)l->size(1) : 1; a.eps_l = (float)eps_l;
+    a.dacc = dacc.has_value() && dacc->defined() ? dacc->data_ptr<float>() : nullptr;
+    a.dl = dl.has_value() && dl->defined() ? dl->data_ptr<float>() : nullptr;
     gt::layer_norm_bwd(a, stream());
 }
 

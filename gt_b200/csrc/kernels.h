@@ -111,6 +111,8 @@ struct LayerNormArgs {
     float p;                // dropout probability (0 = none)
     const long long* seed;  // device pointer: {seed, offset}
     long long stream_id;    // distinguishes the dropout sites of a step
+    // optional fused attention normalisation: y = acc / (l[head] + eps_l) with acc fp32 [n, d], l fp32 [n, H] (y is ignored)
+    const float* acc; const float* l; int H; float eps_l;
 };
 void layer_norm_fwd(const LayerNormArgs& a, cudaStream_t s);
 struct LayerNormBwdArgs {
@@ -125,6 +127,8 @@ struct LayerNormBwdArgs {
     float* dgamma_part; float* dbeta_part; float* dybias_part;   // [n_blocks, d] partials (dybias nullable)
     int n_blocks;
     int n, d; float p; const long long* seed; long long stream_id;
+    // fused attention normalisation (see LayerNormArgs): gradients w.r.t. acc [n, d] and l [n, H] instead of dy
+    const float* acc; const float* l; int H; float eps_l; float* dacc; float* dl;
 };
 void layer_norm_bwd(const LayerNormBwdArgs& a, cudaStream_t s);
 int layer_norm_bwd_blocks(int n);

@@ -24,9 +24,15 @@ __device__ __forceinline__ float gelu_grad(float x) {
 // z = x + dropout(y + ybias) for one 8-chunk
 template <typename T>
 __device__ __forceinline__ void load_z(const T* y, const T* x, const float* ybias, size_t row, int d, int f, float p, uint64_t sd,
-                                       float (&z)[8], float (&keep)[8]) {
+                                       float (&z)[8], float (&keep)[8], const float* acc = nullptr, float inv_l = 1.f) {
     float yv[8];
-    Vec8<T>::load(y + row * d + f, yv);
+    if (acc) {
+        Vec8<float>::load(acc + row * d + f, yv);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) yv[k] *= inv_l;
+    } else {
+        Vec8<T>::load(y + row * d + f, yv);
+    }
     const float inv = p > 0.f ? 1.f / (1.f - p) : 1.f;
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
@@ -54,7 +60,8 @@ __global__ void __launch_bounds__(kWarps * 32) ln_fwd_kernel(LayerNormArgs a) {
     for (int i = 0; i < kMaxCpl; ++i) {
         int ch = lane + 32 * i;
         if (ch < nch) {
-            load_z<T>(static_cast<const T*>(a.y), static_cast<const T*>(a.x), a.ybias, row, a.d, ch << 3, a.p, sd, z[i], keep);
+            const float inv_l = a.acc ? 1.f / (a.l[(size_t)row * a.H + ((ch << 3) / (a.d / a.H))] + a.eps_l) : 1.f;
+            load_z<T>(static_cast<const T*>(a.y), static_cast<const T*>(a.x), a.ybias, row, a.d, ch << 3, a.p, sd, z[i], keep, a.acc, inv_l);
 #pragma unroll
             for (int k = 0; k < 8; ++k) sum += z[i][k];
         }
@@ -103,7 +110,8 @@ __global__ void __launch_bounds__(kWarps * 32) ln_bwd_kernel(LayerNormBwdArgs a)
             if (ch < nch) {
                 int f = ch << 3;
                 float z[8], go[8];
-                load_z<T>(static_cast<const T*>(a.y), static_cast<const T*>(a.x), a.ybias, row, a.d, f, a.p, sd, z, keep[i]);
+                const float inv_l = a.acc ? 1.f / (a.l[(size_t)row * a.H + (f / (a.d / a.H))] + a.eps_l) : 1.f;
+                load_z<T>(static_cast<const T*>(a.y), static_cast<const T*>(a.x), a.ybias, row, a.d, f, a.p, sd, z, keep[i], a.acc, inv_l);
                 Vec8<T>::load(static_cast<const T*>(a.dout) + (size_t)row * a.d + f, go);
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
@@ -118,6 +126,7 @@ __global__ void __launch_bounds__(kWarps * 32) ln_bwd_kernel(LayerNormBwdArgs a)
         }
         s1 = warp_sum(s1) / a.d;
         s2 = warp_sum(s2) / a.d;
+        float dl_part[kMaxCpl] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int i = 0; i < kMaxCpl; ++i) {
             int ch = lane + 32 * i;
@@ -130,7 +139,20 @@ __global__ void __launch_bounds__(kWarps * 32) ln_bwd_kernel(LayerNormBwdArgs a)
                     dy[k] = dz[k] * keep[i][k];
                     dyb[i][k] += dy[k];
                 }
-                Vec8<T>::store(static_cast<T*>(a.dy) + (size_t)row * a.d + f, dy);
+                if (a.acc) {
+                    // dacc = dy / (l + eps);  dl[head] = -sum_f dy * acc / (l + eps)^2 (summed over the head's lanes below)
+                    const int hd = a.d / a.H;
+                    const float inv_l = 1.f / (a.l[(size_t)row * a.H + f / hd] + a.eps_l);
+                    float av[8], da[8];
+                    Vec8<float>::load(a.acc + (size_t)row * a.d + f, av);
+                    float part = 0.f;
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) { da[k] = dy[k] * inv_l; part = fmaf(dy[k], av[k], part); }
+                    Vec8<float>::store(a.dacc + (size_t)row * a.d + f, da);
+                    dl_part[i] = -part * inv_l * inv_l;
+                } else {
+                    Vec8<T>::store(static_cast<T*>(a.dy) + (size_t)row * a.d + f, dy);
+                }
                 if (a.dx) {
                     T* dxp = static_cast<T*>(a.dx) + (size_t)row * a.d + f;
                     if (a.accumulate_dx) {
@@ -141,6 +163,17 @@ __global__ void __launch_bounds__(kWarps * 32) ln_bwd_kernel(LayerNormBwdArgs a)
                     }
                     Vec8<T>::store(dxp, dz);
                 }
+            }
+        }
+        if (a.acc) {
+            // a head spans (d / H) / 8 consecutive lanes (a power of two): finish dl with xor shuffles, all lanes take part
+            const int lph = (a.d / a.H) >> 3;
+#pragma unroll
+            for (int i = 0; i < kMaxCpl; ++i) {
+                float v = dl_part[i];
+                for (int o = lph >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(GT_FULL_MASK, v, o);
+                const int ch = lane + 32 * i;
+                if (ch < nch && (ch & (lph - 1)) == 0) a.dl[(size_t)row * a.H + (ch << 3) / (a.d / a.H)] = v;
             }
         }
     }
@@ -316,7 +349,7 @@ void layer_norm_fwd(const LayerNormArgs& a, cudaStream_t s) {
 
 int layer_norm_bwd_blocks(int n) {
     int b = grid_for(n, kWarps * 8);
-    return b > 148 * 4 ? 148 * 4 : b;                  // few, fat blocks: the partial buffers stay small
+    return b > 148 * 12 ? 148 * 12 : b;                // enough resident warps to hide the row latency
 }
 
 void layer_norm_bwd(const LayerNormBwdArgs& a, cudaStream_t s) {

@@ -83,17 +83,21 @@ class _LayerBase(nn.Module):
     def gate(self, edge_type_emb):
         return K.linear(edge_type_emb, self.e.weight).view(-1, self.num_heads, self.d_head)
 
-    def tail(self, x, o=None, agg=None, agg_has_bias=False):
-        """``o [n, dim]``: normalised attention output; ``agg [n, dim]``: GCN aggregation (bias added here)."""
+    def tail(self, x, o=None, agg=None, agg_has_bias=False, l=None):
+        """``o [n, dim]``: normalised attention output, or with ``l [n, H]`` the unnormalised accumulator (clamp-exp:
+        ``o / (l + 1e-6)`` is then fused into the norm kernel); ``agg [n, dim]``: GCN aggregation (bias added here)."""
         p, tr = self.dropout, self.training
         h_attn = h_local = None
+        if l is not None and not isinstance(self.bn_attn, K.LayerNorm):
+            o = (o.reshape(o.shape[0], l.shape[1], -1) / (l + 1e-6).unsqueeze(-1)).reshape(o.shape[0], -1)
+            l = None
         if self.with_attn and self.with_gcn and BN_PAIR and isinstance(self.bn_local, DistBatchNorm1d):
             a = x + F.dropout(o.to(x.dtype), p, tr)
             b = x + F.dropout(agg.to(x.dtype) if agg_has_bias else agg.to(x.dtype) + self.gcn.bias.to(x.dtype), p, tr)
             h_local, h_attn = dist_batchnorm_pair(self.bn_local, b, self.bn_attn, a)
         else:
             if self.with_attn:
-                h_attn = K.dropout_add_norm(self.bn_attn, o, x, None, p, tr)
+                h_attn = K.dropout_add_norm(self.bn_attn, o, x, None, p, tr, l=l)
             if self.with_gcn:
                 h_local = K.dropout_add_norm(self.bn_local, agg, x, None if agg_has_bias else self.gcn.bias, p, tr)
         hh = h_attn if h_local is None else (h_local if h_attn is None else h_local + h_attn)
@@ -180,13 +184,14 @@ class DistExphormerLayerFused(_LayerBase):
         acc, l, m = self.attn(q, k, v, gate)
         t.stop("attention partial")
         t.start("reduce-scatter")
-        o, agg_o = combine_partials(acc, l, m, g, "clampexp", 1e-6, extra=agg, rs_dtype=self.rs_dtype, plan=self.sp_row)
+        (acc_o, l_o), agg_o = combine_partials(acc, l, m, g, "clampexp", 1e-6, extra=agg, rs_dtype=self.rs_dtype, plan=self.sp_row,
+                                               normalize=False)
         t.stop("reduce-scatter")
-        return o.reshape(o.shape[0], hd), agg_o
+        return (acc_o, l_o), agg_o
 
     def forward(self, x, edge_type_emb):
-        o, agg_o = self.branches(x, edge_type_emb)
-        return self.tail(x, o, agg_o)
+        (acc_o, l_o), agg_o = self.branches(x, edge_type_emb)
+        return self.tail(x, acc_o, agg_o, l=l_o)
 
 
 class DistExphormerLayerHead(_LayerBase):
@@ -285,8 +290,7 @@ class DistExphormerLayerPipelined(DistExphormerLayerFused):
                 msg = kvg[:, 2 * hd:].contiguous()
                 agg_s = spmm(self.gcn_blocks[s].matrix(msg.dtype, msg.device), msg)
                 agg = agg_s if agg is None else agg + agg_s
-        o, agg_o = combine_partials(acc, l, torch.zeros_like(l), g, "clampexp", 1e-6, extra=agg, rs_dtype=self.rs_dtype)
-        return o.reshape(o.shape[0], hd), agg_o
+        return combine_partials(acc, l, torch.zeros_like(l), g, "clampexp", 1e-6, extra=agg, rs_dtype=self.rs_dtype, normalize=False)
 
 
 class _StreamedAttnGCN(torch.autograd.Function):

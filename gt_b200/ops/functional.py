@@ -73,11 +73,18 @@ class LayerNorm(nn.LayerNorm):
         return F.layer_norm(x, self.normalized_shape, self.weight.to(x.dtype), self.bias.to(x.dtype), self.eps)
 
 
-def dropout_add_norm(norm, y, x, bias=None, p=0.0, training=False):
-    """``norm(x + dropout(y + bias))``: the residual step of every branch.  Fused into one kernel for LayerNorm on CUDA."""
+def dropout_add_norm(norm, y, x, bias=None, p=0.0, training=False, l=None, eps_l=1e-6):
+    """``norm(x + dropout(y + bias))``: the residual step of every branch.  Fused into one kernel for LayerNorm on CUDA.
+    With ``l [n, H]`` given, ``y`` is the unnormalised attention accumulator ``[n, H * d_h]`` and is divided by
+    ``l + eps_l`` per head first (inside the same kernel on CUDA)."""
     p = p if training else 0.0
     if isinstance(norm, LayerNorm) and _use_native(x):
+        if l is not None:
+            return _native().layer_norm(y.float(), x, bias, norm.weight, norm.bias, norm.eps, p, l.float(), eps_l)
         return _native().layer_norm(y.to(x.dtype), x, bias, norm.weight, norm.bias, norm.eps, p)
+    if l is not None:
+        h = l.shape[1]
+        y = (y.reshape(y.shape[0], h, -1) / (l + eps_l).unsqueeze(-1)).reshape(y.shape[0], -1)
     y = y.to(x.dtype)
     if bias is not None:
         y = y + bias.to(x.dtype)

@@ -250,51 +250,70 @@ def linear(x, weight, bias=None, activation=None, dropout=0.0):
 
 # ---- fused dropout + bias + residual + LayerNorm -----------------------------------------------------------------------------
 class _LayerNorm(torch.autograd.Function):
-    """out = LN(x + dropout(y + ybias)).  ``x`` / ``ybias`` may be None.  Saved: y, x, the row statistics."""
+    """out = LN(x + dropout(y + ybias)).  ``x`` / ``ybias`` may be None.  With ``l`` given, ``y`` is the fp32 unnormalised
+    attention accumulator ``acc [n, H * d_h]`` and the kernel uses ``y = acc / (l[head] + eps_l)`` (the attention
+    normalisation is fused into the LayerNorm pass, forward and backward).  Saved: y, x, l, the row statistics."""
 
     @staticmethod
-    def forward(ctx, y, x, ybias, gamma, beta, eps, p, site):
+    def forward(ctx, y, x, ybias, gamma, beta, eps, p, site, l, eps_l):
         y = y.contiguous()
         x = x.contiguous() if x is not None else None
-        out = torch.empty_like(y)
+        acc_mode = l is not None
+        like = x if acc_mode else y
+        out = torch.empty_like(like)
         stats = torch.empty(y.shape[0], 2, dtype=torch.float32, device=y.device)
         yb = ybias.float() if ybias is not None else None
-        ext().layer_norm_fwd(y, x, yb, gamma.float(), beta.float(), out, stats, float(eps), float(p),
-                             rng_state(y.device) if p > 0 else None, int(site))
-        ctx.save_for_backward(y, x, yb, gamma, stats)
-        ctx.cfg = (float(p), int(site), ybias is not None, beta.dtype)
+        lc = l.contiguous() if acc_mode else None
+        ext().layer_norm_fwd(like if acc_mode else y, x, yb, gamma.float(), beta.float(), out, stats, float(eps), float(p),
+                             rng_state(y.device) if p > 0 else None, int(site), y if acc_mode else None, lc, float(eps_l))
+        ctx.save_for_backward(y, x, yb, gamma, stats, lc)
+        ctx.cfg = (float(p), int(site), ybias is not None, beta.dtype, float(eps_l))
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        y, x, yb, gamma, stats = ctx.saved_tensors
-        p, site, has_yb, pdt = ctx.cfg
+        y, x, yb, gamma, stats, l = ctx.saved_tensors
+        p, site, has_yb, pdt, eps_l = ctx.cfg
         e = ext()
         dout = dout.contiguous()
         n, d = y.shape
+        acc_mode = l is not None
+        like = x if acc_mode else y
         nb = e.layer_norm_bwd_blocks(n)
         parts = torch.empty(3, nb, d, dtype=torch.float32, device=y.device)
-        dy = torch.empty_like(y)
-        dx = torch.empty_like(y) if x is not None else None
-        e.layer_norm_bwd(dout, y, x, yb, gamma.float(), stats, dy, dx, False, parts[0], parts[1], parts[2] if has_yb else None,
-                         p, rng_state(y.device) if p > 0 else None, site)
+        dy = torch.empty_like(y)                                  # acc mode: this is dacc (fp32)
+        dl = torch.empty_like(l) if acc_mode else None
+        dx = torch.empty_like(x) if x is not None else None
+        e.layer_norm_bwd(dout, like if acc_mode else y, x, yb, gamma.float(), stats, like if acc_mode else dy, dx, False, parts[0], parts[1],
+                         parts[2] if has_yb else None, p, rng_state(y.device) if p > 0 else None, site,
+                         y if acc_mode else None, l, eps_l, dy if acc_mode else None, dl)
         red = torch.empty(3, d, dtype=torch.float32, device=y.device)
         e.reduce_partials(parts[0], red[0])
         e.reduce_partials(parts[1], red[1])
         if has_yb:
             e.reduce_partials(parts[2], red[2])
-        return dy, dx, (red[2].to(pdt) if has_yb else None), red[0].to(gamma.dtype), red[1].to(pdt), None, None, None
+        return dy, dx, (red[2].to(pdt) if has_yb else None), red[0].to(gamma.dtype), red[1].to(pdt), None, None, None, dl, None
 
 
-def layer_norm(y, x, ybias, gamma, beta, eps, p):
-    """``LayerNorm(x + dropout(y + ybias))`` over the last dimension of ``[n, d]`` tensors (d % 8 == 0, d <= 1024)."""
-    if y.shape[-1] % 8 or y.shape[-1] > 1024:
+def layer_norm(y, x, ybias, gamma, beta, eps, p, l=None, eps_l=1e-6):
+    """``LayerNorm(x + dropout(y + ybias))`` over the last dimension of ``[n, d]`` tensors (d % 8 == 0, d <= 1024).
+    ``l [n, H]``: ``y`` is an fp32 attention accumulator to be divided by ``l + eps_l`` per head first."""
+    d = y.shape[-1]
+    fused_ok = d % 8 == 0 and d <= 1024
+    if l is not None:
+        hd = d // l.shape[1]
+        fused_ok = fused_ok and x is not None and y.dtype == torch.float32 and hd % 8 == 0 and ((hd // 8) & (hd // 8 - 1)) == 0
+        if not fused_ok:
+            y = (y.view(y.shape[0], l.shape[1], hd) / (l + eps_l).unsqueeze(-1)).reshape(y.shape).to(x.dtype if x is not None else y.dtype)
+            l = None
+            fused_ok = d % 8 == 0 and d <= 1024
+    if not fused_ok:
         z = y + ybias.to(y.dtype) if ybias is not None else y
         z = torch.nn.functional.dropout(z, p, True) if p > 0 else z
         z = z + x if x is not None else z
         return torch.nn.functional.layer_norm(z, z.shape[-1:], gamma.to(z.dtype), beta.to(z.dtype), eps)
     site = gamma.data_ptr() & 0xFFFFFFFFFF
-    return _LayerNorm.apply(y, x, ybias, gamma, beta, float(eps), float(p), site)
+    return _LayerNorm.apply(y, x, ybias, gamma, beta, float(eps), float(p), site, l, float(eps_l))
 
 
 def gated_residual(r, o, gate_weight, gate_bias, ln_weight, ln_bias, eps, p):

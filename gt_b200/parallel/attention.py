@@ -210,13 +210,14 @@ class DistAttentionPartial(_OpBase):
         return _AttnPartial.apply(q_blk.contiguous(), k_blk.contiguous(), v_blk.contiguous(), gate, bias, self)
 
 
-def combine_partials(acc, l, m, grid, norm, eps, extra=None, rs_dtype=None, plan=None):
+def combine_partials(acc, l, m, grid, norm, eps, extra=None, rs_dtype=None, plan=None, normalize=True):
     """Merge the block partials of a row group onto the owner of every row; returns ``(o_owned, extra_owned)``.
 
     softmax: the partials are first rescaled to the row-group maximum of ``m`` (one MAX all-reduce; no gradient flows
     through ``m``).  ``extra [rows, F]`` (e.g. the GCN aggregation partial) rides in the same reduce-scatter.
     ``rs_dtype`` reduces the payload in low precision.  ``plan``: a :class:`~gt_b200.parallel.sparse_comm.SparseRowPlan`
-    of the row group; the partials are then given for the plan's compact rows only."""
+    of the row group; the partials are then given for the plan's compact rows only.  ``normalize=False`` returns
+    ``((acc_owned [n, H d], l_owned [n, H]), extra_owned)`` so that the division can be fused into the consumer."""
     if norm == "softmax" and group_size(grid.row_group) > 1:
         if plan is None:
             m_glob = m.detach().clone()
@@ -229,6 +230,13 @@ def combine_partials(acc, l, m, grid, norm, eps, extra=None, rs_dtype=None, plan
         w = torch.exp(m.detach() - m_glob)
         acc, l = acc * w.unsqueeze(-1), l * w
     n_rows, h, d = acc.shape
+    if group_size(grid.row_group) == 1 and plan is None:
+        # one rank per row group: nothing to reduce, so the [acc | l | extra] payload is never built
+        acc_o, l_o, extra_o = acc, l, extra
+        if not normalize:
+            return (acc_o.reshape(n_rows, h * d), l_o), extra_o
+        o = acc_o / (torch.where(l_o > 0, l_o, torch.ones_like(l_o)) if norm == "softmax" else (l_o + eps)).unsqueeze(-1)
+        return o, extra_o
     parts, width = [acc.reshape(n_rows, h * d), l], h * d + h
     if extra is not None:
         parts.append(extra.to(acc.dtype))
@@ -240,6 +248,8 @@ def combine_partials(acc, l, m, grid, norm, eps, extra=None, rs_dtype=None, plan
         from .sparse_comm import sparse_reduce_scatter
         packed = sparse_reduce_scatter(packed, plan, rs_dtype)
     acc_o, l_o = packed[:, :h * d].reshape(-1, h, d), packed[:, h * d:h * d + h]
+    if not normalize:
+        return (packed[:, :h * d], l_o.contiguous()), (packed[:, h * d + h:width] if extra is not None else None)
     if norm == "softmax":
         o = acc_o / torch.where(l_o > 0, l_o, torch.ones_like(l_o)).unsqueeze(-1)
     else:

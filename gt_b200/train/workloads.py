@@ -62,3 +62,59 @@ def exphormer_workload(name="exphormer_arxiv", grid_shape=None, device="cpu", dt
                masks={k: grid.take_owned(m.to(torch.uint8)).bool() & grid.valid_mask.cpu() for k, m in masks.items()},
                n_train=int(masks["train"].sum()), in_degree=degrees(ei, n)[0])
     return out
+
+
+def variant_workload(model="unimp", name=None, grid_shape=None, device="cpu", dtype=torch.float32, seed=0, scale_down=1,
+                     dropout=0.3, backend=None, comm_bf16=False, khop=False, max_two_hop=64, label_input=False,
+                     layers=None, hidden=None, heads=None, max_degree=None, ffn_mult=2, checkpoint=False):
+    """UniMP or Graphormer-node on a named graph (defaults: ``unimp_products`` / ``graphormer_rmat``).  ``khop``: the 2-hop mask
+    with distance-bucket bias and in/out-degree embeddings (clipped at ``max_degree``, default 512); otherwise the 1-hop mask
+    with a global token.  Returns the same dict as ``exphormer_workload`` plus ``degree`` / ``out_degree`` of the owned rows."""
+    from ..models import gt_variants as gv
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    grid_shape = tuple(grid_shape or DEFAULT_GRIDS[world])
+    name = name or ("unimp_products" if model == "unimp" else "graphormer_rmat")
+    wl = workload_graph(name, seed=seed, scale_down=scale_down)
+    cfg, n, ei = wl["cfg"], wl["n"], wl["edge_index"]
+    dev = torch.device(device)
+    backend = backend or ("cuda" if dev.type == "cuda" else "torch")
+    token = model == "graphormer" and not khop
+    n_tot = n + (1 if token else 0)
+    if model == "unimp":
+        a_ei, a_et = gv.typed_graph_edges(ei, n)
+        nb_type, n_types = 0, 2
+    elif khop:
+        a_ei, a_et = gv.khop_typed_edges(ei, n, max_two_hop=max_two_hop, seed=seed)
+        nb_type, n_types = 1, 3
+    else:
+        a_ei, a_et = gv.graphormer_edges(ei, n)
+        nb_type, n_types = 0, 4
+    n_pad = pad_to(n_tot + (0 if not token else 0), 8 * world)
+    if token and n_pad == n_tot:
+        n_pad += 8 * world
+    grid = make_grid(grid_shape, n_tot if not token else n, n_pad=n_pad).to(device)
+    b_ei, b_et = grid.local_block(a_ei, a_et)
+    kw = dict(model=model, dropout=dropout, backend=backend, checkpoint=checkpoint,
+              comm_dtype=torch.bfloat16 if (comm_bf16 and dev.type == "cuda") else None,
+              rs_dtype=torch.bfloat16 if (comm_bf16 and dev.type == "cuda" and world > 1) else None)
+    if model == "unimp":
+        kw.update(num_classes_label=cfg["classes"] if label_input else None)
+    else:
+        kw.update(max_degree=max_degree or (512 if khop else 64), num_edge_types=n_types, out_degree=khop, ffn_mult=ffn_mult,
+                  token_row=gv.token_owned_row(grid, n) if token else None)
+    torch.manual_seed(seed)
+    net = gv.DistGTVariant(grid, b_ei.to(dev), b_et.to(dev), cfg["features"], hidden or cfg["hidden"], cfg["classes"],
+                           layers or cfg["layers"], heads or cfg["heads"], **kw).to(dev)
+    rows = n_pad
+    x = torch.zeros(rows, wl["x"].shape[1]); x[:n] = wl["x"]
+    y = torch.zeros(rows, dtype=torch.long); y[:n] = wl["y"]
+    masks = {}
+    for k, m in wl["masks"].items():
+        mm = torch.zeros(rows, dtype=torch.bool); mm[:n] = m
+        masks[k] = grid.take_owned(mm.to(torch.uint8)).bool()
+    out = dict(grid=grid, model=net, cfg=cfg, num_nodes=n_tot, num_attn_edges=int(a_ei.shape[1]), x=grid.take_owned(x).to(dtype),
+               y=grid.take_owned(y), masks=masks, n_train=int(wl["masks"]["train"].sum()))
+    if model == "graphormer":
+        d_in, d_out = gv.owned_degrees(grid, b_ei.to(dev), b_et.to(dev), dev, neighbour_type=nb_type)
+        out.update(degree=d_in, out_degree=d_out if khop else None)
+    return out

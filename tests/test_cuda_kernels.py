@@ -221,3 +221,25 @@ def test_whole_step_matches_cpu_oracle_and_graph_replay():
     """fp32 Exphormer step on the native kernels vs the CPU torch backend, then bf16 + CUDA-graph replay stays finite."""
     from gt_b200.train.engine import smoke_step
     smoke_step(_dev())
+
+
+def test_layer_norm_with_fused_attention_normalisation():
+    from gt_b200.ops import native
+    dev = _dev()
+    torch.manual_seed(0)
+    n, h, dh = 257, 8, 32
+    d = h * dh
+    acc = torch.randn(n, d, device=dev, requires_grad=True)
+    l = (torch.rand(n, h, device=dev) * 3).requires_grad_()
+    x = torch.randn(n, d, device=dev).bfloat16().requires_grad_()
+    gam, bet = torch.randn(d, device=dev).requires_grad_(), torch.randn(d, device=dev).requires_grad_()
+    out = native.layer_norm(acc, x, None, gam, bet, 1e-5, 0.0, l, 1e-6)
+    g = torch.randn(n, d, device=dev)
+    out.backward(g.bfloat16())
+    a2, l2, x2, g2, b2 = (t.detach().float().requires_grad_() for t in (acc, l, x, gam, bet))
+    o = (a2.view(n, h, dh) / (l2 + 1e-6).unsqueeze(-1)).reshape(n, d)
+    ref = torch.nn.functional.layer_norm(x2 + o, (d,), g2, b2, 1e-5)
+    ref.backward(g.bfloat16().float())
+    assert _rel(out, ref) < 2e-2
+    for a, b, name in ((acc.grad, a2.grad, "dacc"), (l.grad, l2.grad, "dl"), (x.grad, x2.grad, "dx"), (gam.grad, g2.grad, "dgamma")):
+        assert _rel(a, b) < 3e-2, name

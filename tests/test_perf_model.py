@@ -1,0 +1,86 @@
+"""Sanity and selection behaviour of the white-box time / memory model (pure host arithmetic)."""
+import pytest
+
+from gt_b200.perf import grid_select as gs
+
+ARXIV = gs.Graph(169_344, gs.attention_edges(169_343, 2_332_486, 4) + 2 * 169_343, 2_332_486 + 169_344, 128, "arxiv", exp_deg=4)
+PAPERS = gs.Graph(111_059_956, gs.attention_edges(111_059_956, 3_231_371_744, 3), 3_231_371_744 + 111_059_956, 128, "papers100M", classes=172)
+M256 = gs.Model(256, 8, 4)
+
+
+def test_placement_inside_and_across_nodes():
+    assert gs.placement(2, 4) == dict(head=(1, 1), row=(4, 1), col=(2, 1))
+    pl = gs.placement(4, 8)                                     # 32 GPUs: rows fill a node, columns cross nodes
+    assert pl["row"] == (8, 1) and pl["col"] == (1, 4)
+    assert gs.cross_node_groups(4, 8) == 1 and gs.cross_node_groups(2, 2, 2) == 0
+    assert gs.placement(2, 2, 4)["head"] == (4, 1) and gs.placement(2, 2, 4)["col"][1] == 2
+
+
+def test_collective_cost_monotone_and_zero_for_singletons():
+    assert gs.coll_ms("ag", (1, 1), 1e9) == 0.0
+    small, big = gs.coll_ms("ag", (8, 1), 1e6), gs.coll_ms("ag", (8, 1), 1e9)
+    assert 0 < small < big
+    assert gs.coll_ms("ag", (1, 4), 1e9) > gs.coll_ms("ag", (4, 1), 1e9)          # the NIC is slower than NVLink
+    assert gs.coll_ms("ag", (8, 1), 1e6, "p2p") < gs.coll_ms("ag", (8, 1), 1e6)   # lower latency of the peer-memory kernels
+
+
+def test_sparse_share_limits():
+    assert gs.sparse_share(ARXIV, 1) == 1.0
+    s2, s8, s64 = (gs.sparse_share(ARXIV, p) for p in (2, 8, 64))
+    assert 1.0 > s2 > s8 > s64 > 0.0
+
+
+def test_one_gpu_prediction_is_in_the_measured_range():
+    ms, parts = gs.predict_fused_ms(1, 1, ARXIV, M256, breakdown=True)
+    assert 15.0 < ms < 90.0                                     # measured on B200: 43 ms per step
+    assert parts["gather"] == 0.0 and parts["bwd attn"] > parts["attn"] > 0
+
+
+def test_more_gpus_help_a_large_graph_and_memory_shrinks():
+    t = [gs.select_grid(w, PAPERS, M256, n_sub=16, streamed=True).ms for w in (64, 128, 256)]
+    assert t[0] > t[1] > t[2]
+    gb = [gs.peak_memory_bytes(pd, po, PAPERS, M256) / gs.GB for pd, po in ((4, 4), (8, 8), (16, 16))]
+    assert gb[0] > gb[1] > gb[2]
+    assert gs.peak_memory_bytes(8, 8, PAPERS, M256, layer_ckpt=True) < gs.peak_memory_bytes(8, 8, PAPERS, M256)
+    assert gs.peak_memory_bytes(8, 8, PAPERS, M256, n_sub=16, streamed=True) < gs.peak_memory_bytes(8, 8, PAPERS, M256, layer_ckpt=True)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8, 16, 64])
+def test_selected_grids_are_admissible(world):
+    best = gs.select_grid(world, ARXIV, M256)
+    assert best.grid[0] * best.grid[1] == world and best.fits and best.ranked[0] is best
+    lay = gs.select_layout(world, ARXIV, M256)
+    p = 1
+    for s in lay.grid:
+        p *= s
+    assert p == world and (len(lay.grid) == 2 or M256.heads % lay.grid[2] == 0)
+
+
+def test_memory_infeasible_raises_and_streaming_rescues():
+    with pytest.raises(MemoryError):
+        gs.select_grid(8, PAPERS, M256)
+    best = gs.select_grid_streamed(64, PAPERS, M256)
+    assert best is not None and best.family == "streamed" and best.gb <= gs.CAPACITY_GB * gs.HEADROOM
+    assert gs.auto_checkpoint(2, 4, PAPERS, M256) and not gs.auto_checkpoint(1, 1, ARXIV, M256)
+
+
+def test_head_and_ring_models():
+    h = gs.select_grid_head(8, ARXIV, M256)
+    assert h is not None and len(h.grid) == 3 and M256.heads % h.grid[2] == 0
+    assert gs.candidate_grids_3d(8, 2) == [(1, 4, 2), (2, 2, 2), (4, 1, 2)]
+    ring, parts = gs.predict_ring_ms(8, ARXIV, M256, breakdown=True)
+    assert ring > 0 and set(parts) == {"ring fwd", "ring bwd", "tail", "fixed"}
+    assert gs.peak_memory_ring_bytes(8, PAPERS, M256) < gs.peak_memory_bytes(8, 1, PAPERS, M256)
+
+
+def test_constants_overlay(tmp_path):
+    import json
+    p = tmp_path / "c.json"
+    p.write_text(json.dumps({"hbm_gbs": 1234.0, "coll": {"ag": [9.0, 99.0]}, "gemm_tflops": {"256": [1.0, 1.0, 1.0]}}))
+    keep = {k: (dict(v) if isinstance(v, dict) else v) for k, v in gs.HW.items()}
+    try:
+        assert gs.load_constants(str(p)) == ["coll", "gemm_tflops", "hbm_gbs"]
+        assert gs.HW["hbm_gbs"] == 1234.0 and gs.HW["coll"]["ag"] == (9.0, 99.0) and gs.HW["coll"]["rs"] == keep["coll"]["rs"]
+        assert gs.gemm_ms(2e9, 256) == pytest.approx(2.0)
+    finally:
+        gs.HW.clear(); gs.HW.update(keep)
