@@ -247,6 +247,59 @@ void gemm_tn(Tensor a, Tensor b, Tensor c, bool accumulate, Tensor status) {
     TORCH_CHECK(rc == 0, "tcgen05 TN GEMM launch failed with code ", rc);
 }
 
+// C[g * chunk, N] = epilogue(gathered(A) @ B[N, K]^T): rank p's [chunk, K] rows of A are read from peer_ptrs[p] (addresses
+// inside the peers' symmetric heaps, row stride lda) by TMA inside the GEMM; `gathered` (optional) receives the gathered A.
+void gemm_nt_gather(std::vector<int64_t> peer_ptrs, int64_t chunk, int64_t k, int64_t lda, Tensor b, Tensor c, OptT bias, int64_t act,
+                    double p, OptT seed, int64_t stream_id, OptT gathered, Tensor status) {
+    c10::cuda::CUDAGuard guard(b.device());
+    TORCH_CHECK(b.scalar_type() == torch::kBFloat16 && b.stride(1) == 1 && c.stride(1) == 1, "bf16 row-major operands expected");
+    const int n_peers = (int)peer_ptrs.size();
+    TORCH_CHECK(b.size(1) == k && c.size(0) == chunk * n_peers && c.size(1) == b.size(0), "shape mismatch");
+    gt::GemmArgs g{};
+    g.a = nullptr; g.b = b.data_ptr(); g.c = c.data_ptr();
+    g.M = (int)(chunk * n_peers); g.K = (int)k; g.N = (int)b.size(0);
+    g.lda = (int)lda; g.ldb = (int)b.stride(0); g.ldc = (int)c.stride(0);
+    g.c_dtype = dt(c); g.bias = cptr<float>(bias); g.act = (int)act; g.p = (float)p; g.seed = cptr<long long>(seed);
+    g.stream_id = stream_id; g.accumulate = 0; g.status = status.data_ptr<int>();
+    std::vector<const void*> peers(n_peers);
+    for (int i = 0; i < n_peers; ++i) peers[i] = reinterpret_cast<const void*>(peer_ptrs[i]);
+    void* gat = nullptr;
+    if (gathered.has_value() && gathered->defined()) {
+        TORCH_CHECK(gathered->scalar_type() == torch::kBFloat16 && gathered->size(0) == chunk * n_peers && gathered->size(1) == k &&
+                    gathered->stride(0) == lda && gathered->stride(1) == 1, "gathered copy must be [g * chunk, K] bf16 with row stride lda");
+        gat = gathered->data_ptr();
+    }
+    int rc = gt::gemm_nt_gather(g, peers.data(), n_peers, (int)chunk, gat, stream());
+    TORCH_CHECK(rc == 0, "fused all-gather GEMM failed with code ", rc);
+}
+
+// Row block p of A[M, K] @ B[N, K]^T (bf16) is written into slot_ptrs[p] ([chunk, N], row stride ldc) in rank p's memory.
+void gemm_nt_scatter(Tensor a, Tensor b, std::vector<int64_t> slot_ptrs, int64_t chunk, int64_t ldc, Tensor status) {
+    c10::cuda::CUDAGuard guard(a.device());
+    TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16, "bf16 operands expected");
+    TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && b.size(1) == a.size(1), "row-major operands with equal K expected");
+    const int n_peers = (int)slot_ptrs.size();
+    TORCH_CHECK(a.size(0) == chunk * n_peers, "A must have n_peers * chunk rows");
+    gt::GemmArgs g{};
+    g.a = a.data_ptr(); g.b = b.data_ptr(); g.c = nullptr;
+    g.M = (int)a.size(0); g.K = (int)a.size(1); g.N = (int)b.size(0);
+    g.lda = (int)a.stride(0); g.ldb = (int)b.stride(0); g.ldc = (int)ldc;
+    g.c_dtype = gt::DT_BF16; g.status = status.data_ptr<int>();
+    std::vector<void*> slots(n_peers);
+    for (int i = 0; i < n_peers; ++i) slots[i] = reinterpret_cast<void*>(slot_ptrs[i]);
+    int rc = gt::gemm_nt_scatter(g, slots.data(), n_peers, (int)chunk, stream());
+    TORCH_CHECK(rc == 0, "fused GEMM reduce-scatter failed with code ", rc);
+}
+
+// out (+)= sum over the leading dimension of slots [n, ...] (bf16 slots, fp32 accumulation)
+void sum_slots(Tensor slots, Tensor out, bool accumulate) {
+    c10::cuda::CUDAGuard guard(slots.device());
+    TORCH_CHECK(slots.scalar_type() == torch::kBFloat16 && slots.is_contiguous() && out.is_contiguous(), "contiguous bf16 slots expected");
+    const int64_t n = slots.size(0), elems = slots.numel() / n;
+    TORCH_CHECK(out.numel() == elems && elems % 8 == 0, "slot size must equal the output size and be a multiple of 8");
+    gt::sum_slots(slots.data_ptr(), (int)n, elems, out.data_ptr(), dt(out), accumulate ? 1 : 0, stream());
+}
+
 // ---- symmetric heap: cudaMalloc + CUDA IPC ----------------------------------------------------------------------------
 int64_t heap_alloc(int64_t bytes) {
     void* p = nullptr;
@@ -357,6 +410,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("cast_bf16", &cast_bf16);
     m.def("gemm_nt", &gemm_nt);
     m.def("gemm_tn", &gemm_tn);
+    m.def("gemm_nt_gather", &gemm_nt_gather);
+    m.def("gemm_nt_scatter", &gemm_nt_scatter);
+    m.def("sum_slots", &sum_slots);
     m.def("heap_alloc", &heap_alloc);
     m.def("heap_free", &heap_free);
     m.def("heap_ipc_handle", &heap_ipc_handle);

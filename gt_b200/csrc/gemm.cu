@@ -20,6 +20,7 @@
 #include <cudaTypedefs.h>
 
 #include <stdlib.h>
+#include <string.h>
 
 #include <map>
 #include <mutex>
@@ -491,6 +492,395 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nt_persistent_kernel(const _
 }
 
 // ------------------------------------------------------------------------------------------------------------------
+// All-gather fused into C = A * B^T.  The rows of A are spread over the ranks of a group: rank p holds rows
+// [p * chunk, (p + 1) * chunk) in ITS OWN memory (a symmetric-heap buffer), and every rank needs the product of the whole
+// gathered A with its weights.  Instead of all-gathering A and then running a GEMM, each CTA loads its A tiles straight from
+// the owner's memory over NVLink with (non-multicast) TMA loads through one tensor map per peer, so the transfer of tile
+// i + 1 overlaps the MMAs of tile i and the gathered matrix is never written unless the caller asks for it.
+//
+// The kernel is A-stationary: a 128-row A tile ([128, K], K <= 512) is fetched ONCE into shared memory and multiplied with
+// every 128-column tile of B (the weights stream from L2 through a small ring), because a remote tile must cross the link
+// only once.  With K <= 256 two A buffers alternate, so the remote fetch of the next tile runs during the current one.
+// Roles (224 threads): warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 epilogue (two TMEM accumulators, as in the
+// persistent kernel), warp 6 optional "copier" that TMA-stores each fetched A tile into a local gathered copy (what backward
+// needs for the weight gradient) - the copy rides on data that is already in shared memory.
+// m-tiles are dealt round-robin over the peers so all links (and the local HBM) are busy at the same time.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int kMaxPeers = 8;
+constexpr int kGatherThreads = 224;
+constexpr int G_MAX_B = 5;
+
+struct GatherMaps {
+    CUtensorMap a[kMaxPeers];
+    CUtensorMap out[kMaxPeers];
+};
+
+struct GatherCfg {
+    int chunk, n_peers, tiles_per_peer, copy_out;
+    int nkb, n_abuf, n_b;             // k-blocks per tile, A buffers (1 or 2), B ring stages
+};
+
+struct GatherBars {
+    uint64_t a_full[2], a_empty[2];
+    uint64_t b_full[G_MAX_B], b_empty[G_MAX_B];
+    uint64_t tmem_full[2], tmem_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(smem_src))
+                 : "memory");
+}
+
+__global__ void __launch_bounds__(kGatherThreads, 1) gemm_nt_gather_kernel(const __grid_constant__ GatherMaps maps,
+                                                                           const __grid_constant__ CUtensorMap map_b, GemmArgs g,
+                                                                           GatherCfg cfg) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int kTile = BM * BK * 2;                      // 16 KB
+    uint8_t* a_sm = base;                                   // [n_abuf][nkb] tiles
+    uint8_t* b_sm = a_sm + (size_t)cfg.n_abuf * cfg.nkb * kTile;
+    uint8_t* stage_c = b_sm + (size_t)cfg.n_b * kTile;
+    GatherBars& bars = *reinterpret_cast<GatherBars*>(stage_c + 4 * 32 * kStageStrideP);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_n = (g.N + BN - 1) / BN;
+    const int n_mtiles = cfg.n_peers * cfg.tiles_per_peer;
+    const int nkb = cfg.nkb;
+    volatile int* abort_flag = &bars.abort_flag;
+
+    if (threadIdx.x == 0) {
+        bars.abort_flag = 0;
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bars.a_full[i], 1);
+            mbar_init(&bars.a_empty[i], cfg.copy_out ? 2 : 1);
+            mbar_init(&bars.tmem_full[i], 1);
+            mbar_init(&bars.tmem_empty[i], 4);
+        }
+        for (int s = 0; s < G_MAX_B; ++s) { mbar_init(&bars.b_full[s], 1); mbar_init(&bars.b_empty[s], 1); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(&bars.tmem_base, 2 * kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = bars.tmem_base;
+
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer: A tiles from the owners' memory, B tiles from the local weights ----
+        int ai = 0, it = 0;
+        bool okay = true;
+        auto load_a = [&](int mt, int idx) -> bool {
+            const int buf = idx % cfg.n_abuf;
+            if (!mbar_wait(&bars.a_empty[buf], ((idx / cfg.n_abuf) & 1) ^ 1, abort_flag, g.status, 1)) return false;
+            const int peer = mt % cfg.n_peers, m0 = (mt / cfg.n_peers) * BM;
+            mbar_expect_tx(&bars.a_full[buf], (uint32_t)nkb * kTile);
+            for (int kb = 0; kb < nkb; ++kb)
+                tma_load_2d(a_sm + ((size_t)buf * nkb + kb) * kTile, &maps.a[peer], kb * BK, m0, &bars.a_full[buf]);
+            return true;
+        };
+        int a_issued = 0;
+        if ((int)blockIdx.x < n_mtiles) { okay = load_a(blockIdx.x, 0); a_issued = okay ? 1 : 0; }
+        for (int mt = blockIdx.x; mt < n_mtiles && okay; mt += gridDim.x, ++ai) {
+            for (int nt = 0; nt < tiles_n && okay; ++nt) {
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % cfg.n_b;
+                    okay = mbar_wait(&bars.b_empty[s], ((it / cfg.n_b) & 1) ^ 1, abort_flag, g.status, 1);
+                    if (!okay) break;
+                    mbar_expect_tx(&bars.b_full[s], kTile);
+                    tma_load_2d(b_sm + (size_t)s * kTile, &map_b, kb * BK, nt * BN, &bars.b_full[s]);
+                }
+                // the next A tile is requested after the first column tile's weights are on their way (two A buffers), or
+                // after the last one (one buffer: the wait below then covers the whole current tile)
+                const bool prefetch_now = cfg.n_abuf == 2 ? nt == 0 : nt == tiles_n - 1;
+                const int next = mt + gridDim.x;
+                if (okay && prefetch_now && next < n_mtiles) {
+                    okay = load_a(next, ai + 1);
+                    if (okay) a_issued = ai + 2;
+                }
+            }
+        }
+        if (*abort_flag) {
+            // drain: copies in flight must land before the CTA may exit
+            for (int k = (it > cfg.n_b ? it - cfg.n_b : 0); k < it; ++k) {
+                const long long t0 = clock64();
+                while (!mbar_try_wait(&bars.b_full[k % cfg.n_b], (k / cfg.n_b) & 1) && clock64() - t0 < kWaitCycles) {}
+            }
+            for (int k = (a_issued > cfg.n_abuf ? a_issued - cfg.n_abuf : 0); k < a_issued; ++k) {
+                const long long t0 = clock64();
+                while (!mbar_try_wait(&bars.a_full[k % cfg.n_abuf], (k / cfg.n_abuf) & 1) && clock64() - t0 < kWaitCycles) {}
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer ----
+        const uint32_t idesc = make_idesc(BM, BN, 0, 0);
+        int ai = 0, it = 0, ti = 0;
+        bool okay = true;
+        for (int mt = blockIdx.x; mt < n_mtiles && okay; mt += gridDim.x, ++ai) {
+            const int buf = ai % cfg.n_abuf;
+            okay = mbar_wait(&bars.a_full[buf], (ai / cfg.n_abuf) & 1, abort_flag, g.status, 2);
+            if (!okay) break;
+            const uint32_t a_base = smem_u32(a_sm + (size_t)buf * nkb * kTile);
+            for (int nt = 0; nt < tiles_n && okay; ++nt, ++ti) {
+                const int b = ti & 1;
+                okay = mbar_wait(&bars.tmem_empty[b], ((ti >> 1) & 1) ^ 1, abort_flag, g.status, 2);
+                if (!okay) break;
+                tc_fence_after();
+                const uint32_t acc = tmem + (uint32_t)(b * BN);
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % cfg.n_b;
+                    okay = mbar_wait(&bars.b_full[s], (it / cfg.n_b) & 1, abort_flag, g.status, 2);
+                    if (!okay) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = a_base + kb * kTile, b_addr = smem_u32(b_sm + (size_t)s * kTile);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_bf16(acc, make_desc(a_addr + k * 32, 16, 1024), make_desc(b_addr + k * 32, 16, 1024), idesc, (kb | k) != 0);
+                    umma_commit(&bars.b_empty[s]);
+                }
+                if (okay) umma_commit(&bars.tmem_full[b]);
+            }
+            if (okay) umma_commit(&bars.a_empty[buf]);    // every MMA that reads this A buffer has completed
+        }
+    } else if (warp >= 2 && warp < 6) {
+        // ---- epilogue ----
+        const int quad = warp & 3;
+        const uint64_t sd = site_seed(g.seed, g.stream_id);
+        const float inv_keep = g.p > 0.f ? 1.f / (1.f - g.p) : 1.f;
+        const bool staged = g.c_dtype == DT_BF16 && (g.ldc & 7) == 0 && (g.N & 7) == 0;
+        uint8_t* stage = stage_c + (size_t)quad * 32 * kStageStrideP;
+        int ti = 0;
+        bool okay = true;
+        for (int mt = blockIdx.x; mt < n_mtiles && okay; mt += gridDim.x) {
+            const int peer = mt % cfg.n_peers, m0 = (mt / cfg.n_peers) * BM;
+            const long long row_base = (long long)peer * cfg.chunk;
+            for (int nt = 0; nt < tiles_n; ++nt, ++ti) {
+                const int b = ti & 1, n0 = nt * BN;
+                okay = mbar_wait(&bars.tmem_full[b], (ti >> 1) & 1, abort_flag, g.status, 3);
+                if (!okay) break;
+                tc_fence_after();
+                const int lrow = m0 + quad * 32 + lane;
+                const long long row = row_base + lrow;
+                const uint32_t acc = tmem + (uint32_t)(b * BN) + ((uint32_t)(quad * 32) << 16);
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t r[32];
+                    __syncwarp();
+                    tmem_ld32(acc + c0, r);
+                    if (c0 + 32 >= BN) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&bars.tmem_empty[b]);
+                    }
+                    const int col0 = n0 + c0;
+                    if (!staged && (lrow >= cfg.chunk || col0 >= g.N)) continue;
+                    float v[32];
+                    epilogue_math(r, v, (int)row, col0, g, sd, inv_keep);
+                    if (staged) {
+                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(stage + (size_t)lane * kStageStrideP) + c0;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) Vec8<__nv_bfloat16>::store(dst + j, *reinterpret_cast<float(*)[8]>(&v[j]));
+                        continue;
+                    }
+                    if (g.c_dtype == DT_BF16) {
+                        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(g.c) + (size_t)row * g.ldc + col0;
+                        for (int j = 0; j < 32 && col0 + j < g.N; ++j) dst[j] = __float2bfloat16(v[j]);
+                    } else {
+                        float* dst = static_cast<float*>(g.c) + (size_t)row * g.ldc + col0;
+                        for (int j = 0; j < 32 && col0 + j < g.N; ++j) dst[j] = v[j];
+                    }
+                }
+                if (staged) {
+                    __syncwarp();
+                    const int cchunk = lane & 15;
+                    const bool col_ok = n0 + cchunk * 8 + 8 <= g.N;
+#pragma unroll 4
+                    for (int i2 = 0; i2 < 16; ++i2) {
+                        const int rr = i2 * 2 + (lane >> 4);
+                        const int lr = m0 + quad * 32 + rr;
+                        if (lr < cfg.chunk && col_ok) {
+                            const uint4 val = *reinterpret_cast<const uint4*>(stage + (size_t)rr * kStageStrideP + cchunk * 16);
+                            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(g.c) + (size_t)(row_base + lr) * g.ldc + n0 + cchunk * 8) = val;
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
+        }
+    } else if (warp == 6 && lane == 0 && cfg.copy_out) {
+        // ---- copier: the fetched A tile also lands in the local gathered matrix (rows past the chunk are clipped by the map) ----
+        int ai = 0;
+        for (int mt = blockIdx.x; mt < n_mtiles; mt += gridDim.x, ++ai) {
+            const int buf = ai % cfg.n_abuf;
+            if (!mbar_wait(&bars.a_full[buf], (ai / cfg.n_abuf) & 1, abort_flag, g.status, 4)) break;
+            const int peer = mt % cfg.n_peers, m0 = (mt / cfg.n_peers) * BM;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            for (int kb = 0; kb < nkb; ++kb) tma_store_2d(&maps.out[peer], a_sm + ((size_t)buf * nkb + kb) * kTile, kb * BK, m0);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");      // shared memory has been read: the buffer may be refilled
+            mbar_arrive(&bars.a_empty[buf]);
+        }
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, 2 * kTmemCols);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Reduce-scatter fused into C = A * B^T.  Every rank of a group computes a partial product for ALL rows, and rows
+// [p * chunk, (p + 1) * chunk) are owned by rank p, which needs the sum of the partials.  The epilogue of this kernel writes
+// each finished tile straight into the OWNER's memory (plain peer stores over NVLink, whole 256-byte row segments), into
+// slot `my_pos` of the owner's staging area [n_peers][chunk][N]; the transfer therefore overlaps the MMAs of the following
+// tiles and the partial product never exists in local memory.  After a group barrier the owner adds its n_peers slots
+// (sum_slots_kernel).  Same pipeline as the persistent kernel.
+// ------------------------------------------------------------------------------------------------------------------
+struct ScatterCfg {
+    void* slots[kMaxPeers];           // slots[p] = address of my slot inside rank p's staging area
+    int chunk, n_peers;
+};
+
+__global__ void __launch_bounds__(kThreads, 1) gemm_nt_scatter_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                      const __grid_constant__ CUtensorMap map_b, GemmArgs g,
+                                                                      const __grid_constant__ ScatterCfg cfg) {
+    extern __shared__ uint8_t smem_raw[];
+    PersistentStorage& sh = *reinterpret_cast<PersistentStorage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_n = (g.N + BN - 1) / BN, tiles_m = (g.M + BM - 1) / BM;
+    const int n_tiles = tiles_n * tiles_m;
+    const int nkb = (g.K + BK - 1) / BK;
+    volatile int* abort_flag = &sh.abort_flag;
+
+    if (threadIdx.x == 0) {
+        sh.abort_flag = 0;
+        for (int s = 0; s < P_STAGES; ++s) { mbar_init(&sh.full[s], 1); mbar_init(&sh.empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&sh.tmem_full[b], 1); mbar_init(&sh.tmem_empty[b], 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(&sh.tmem_base, 2 * kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh.tmem_base;
+
+    if (warp == 0 && lane == 0) {
+        int it = 0;
+        bool okay = true;
+        for (int tile = blockIdx.x; tile < n_tiles && okay; tile += gridDim.x) {
+            const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
+                const int s = it % P_STAGES;
+                okay = mbar_wait(&sh.empty[s], ((it / P_STAGES) & 1) ^ 1, abort_flag, g.status, 1);
+                if (!okay) break;
+                mbar_expect_tx(&sh.full[s], (BM + BN) * BK * 2);
+                tma_load_2d(sh.a[s], &map_a, kb * BK, m0, &sh.full[s]);
+                tma_load_2d(sh.b[s], &map_b, kb * BK, n0, &sh.full[s]);
+            }
+        }
+        if (*abort_flag) {
+            for (int k = (it > P_STAGES ? it - P_STAGES : 0); k < it; ++k) {
+                const long long t0 = clock64();
+                while (!mbar_try_wait(&sh.full[k % P_STAGES], (k / P_STAGES) & 1) && clock64() - t0 < kWaitCycles) {}
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        const uint32_t idesc = make_idesc(BM, BN, 0, 0);
+        int it = 0, ti = 0;
+        bool okay = true;
+        for (int tile = blockIdx.x; tile < n_tiles && okay; tile += gridDim.x, ++ti) {
+            const int b = ti & 1;
+            okay = mbar_wait(&sh.tmem_empty[b], ((ti >> 1) & 1) ^ 1, abort_flag, g.status, 2);
+            if (!okay) break;
+            tc_fence_after();
+            const uint32_t acc = tmem + (uint32_t)(b * BN);
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
+                const int s = it % P_STAGES;
+                okay = mbar_wait(&sh.full[s], (it / P_STAGES) & 1, abort_flag, g.status, 2);
+                if (!okay) break;
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(sh.a[s]), b_addr = smem_u32(sh.b[s]);
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k)
+                    umma_bf16(acc, make_desc(a_addr + k * 32, 16, 1024), make_desc(b_addr + k * 32, 16, 1024), idesc, (kb | k) != 0);
+                umma_commit(&sh.empty[s]);
+            }
+            if (okay) umma_commit(&sh.tmem_full[b]);
+        }
+    } else if (warp >= 2) {
+        // ---- epilogue: bf16 tile -> shared staging -> the owner's slot, 256-byte row segments ----
+        const int quad = warp & 3;
+        uint8_t* stage = sh.stage_c + (size_t)quad * 32 * kStageStrideP;
+        int ti = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++ti) {
+            const int b = ti & 1;
+            const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+            if (!mbar_wait(&sh.tmem_full[b], (ti >> 1) & 1, abort_flag, g.status, 3)) break;
+            tc_fence_after();
+            const uint32_t acc = tmem + (uint32_t)(b * BN) + ((uint32_t)(quad * 32) << 16);
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                __syncwarp();
+                tmem_ld32(acc + c0, r);
+                if (c0 + 32 >= BN) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sh.tmem_empty[b]);
+                }
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(stage + (size_t)lane * kStageStrideP) + c0;
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                    float v[8];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) v[q] = __uint_as_float(r[j + q]);
+                    Vec8<__nv_bfloat16>::store(dst + j, v);
+                }
+            }
+            __syncwarp();
+            const int cchunk = lane & 15;
+            const bool col_ok = n0 + cchunk * 8 + 8 <= g.N;
+#pragma unroll 4
+            for (int i2 = 0; i2 < 16; ++i2) {
+                const int rr = i2 * 2 + (lane >> 4);
+                const int grow = m0 + quad * 32 + rr;
+                if (grow < g.M && col_ok) {
+                    const int owner = grow / cfg.chunk, lrow = grow - owner * cfg.chunk;
+                    const uint4 val = *reinterpret_cast<const uint4*>(stage + (size_t)rr * kStageStrideP + cchunk * 16);
+                    *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(cfg.slots[owner]) + (size_t)lrow * g.ldc + n0 + cchunk * 8) = val;
+                }
+            }
+            __syncwarp();
+        }
+        __threadfence_system();                               // the tiles must be visible to the owners after the group barrier
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, 2 * kTmemCols);
+}
+
+// out[r, :] = sum over slots p (fixed order, fp32 accumulation) of slots[p][r, :]   (bf16 in; bf16 or fp32 out)
+template <typename TO>
+__global__ void sum_slots_kernel(const __nv_bfloat16* __restrict__ slots, int n_slots, long long slot_elems, TO* __restrict__ out,
+                                 int accumulate) {
+    const long long n8 = slot_elems / 8;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int p = 0; p < n_slots; ++p) {
+            float v[8];
+            Vec8<__nv_bfloat16>::load(slots + (size_t)p * slot_elems + i * 8, v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += v[j];
+        }
+        if (accumulate) {
+            float o[8];
+            Vec8<TO>::load(out + i * 8, o);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += o[j];
+        }
+        Vec8<TO>::store(out + i * 8, acc);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
 // C[N, K] += A[M, N]^T * B[M, K]  (MN-major operands, reduction over rows split across gridDim.z)
 // ------------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads) gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a,
@@ -680,6 +1070,89 @@ int gemm_tn_tcgen05(const GemmTNArgs& g, cudaStream_t s) {
     dim3 grid((g.K + BN - 1) / BN, (g.N + BM - 1) / BM, splits);
     gemm_tn_kernel<<<grid, kThreads, kSmemBytes, s>>>(ma, mb, g, rows_per_split);
     return (int)cudaGetLastError();
+}
+
+
+// A rows come from the peers' buffers (a_peers[p]: [chunk, K] bf16, row stride lda); g.a is ignored, g.M = n_peers * chunk.
+// gathered != nullptr additionally receives the gathered A ([n_peers * chunk, K], row stride lda).
+int gemm_nt_gather(const GemmArgs& g, const void* const* a_peers, int n_peers, int chunk, void* gathered, cudaStream_t s) {
+    if (n_peers < 1 || n_peers > kMaxPeers) return -5;
+    const int nkb = (g.K + BK - 1) / BK;
+    if (nkb > 8 || (g.K % 8) || (g.lda % 8) || (g.ldb % 8)) return -4;
+    if (reinterpret_cast<uintptr_t>(g.b) & 15) return -2;
+    GatherMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    for (int p = 0; p < n_peers; ++p) {
+        if (reinterpret_cast<uintptr_t>(a_peers[p]) & 15) return -2;
+        if (!make_map(&maps.a[p], a_peers[p], chunk, g.K, g.lda, BM, BK)) return -1;
+        if (gathered) {
+            const void* base = static_cast<const __nv_bfloat16*>(gathered) + (size_t)p * chunk * g.lda;
+            if (reinterpret_cast<uintptr_t>(base) & 15) return -2;
+            if (!make_map(&maps.out[p], base, chunk, g.K, g.lda, BM, BK)) return -1;
+        }
+    }
+    CUtensorMap mb;
+    if (!make_map(&mb, g.b, g.N, g.K, g.ldb, BN, BK)) return -1;
+    constexpr int kTile = BM * BK * 2;
+    const int fixed = 4 * 32 * kStageStrideP + (int)sizeof(GatherBars) + 1024;
+    const int slots = (232448 - fixed) / kTile;
+    GatherCfg cfg;
+    cfg.chunk = chunk; cfg.n_peers = n_peers; cfg.tiles_per_peer = (chunk + BM - 1) / BM; cfg.copy_out = gathered != nullptr;
+    cfg.nkb = nkb;
+    cfg.n_abuf = (2 * nkb + 3 <= slots) ? 2 : 1;
+    cfg.n_b = slots - cfg.n_abuf * nkb;
+    if (cfg.n_b > G_MAX_B) cfg.n_b = G_MAX_B;
+    if (cfg.n_b < 2) return -4;
+    const int smem = (cfg.n_abuf * nkb + cfg.n_b) * kTile + fixed;
+    static int n_sm = 0;
+    if (n_sm == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+        cudaFuncSetAttribute(gemm_nt_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+    }
+    const int n_mtiles = n_peers * cfg.tiles_per_peer;
+    gemm_nt_gather_kernel<<<n_mtiles < n_sm ? n_mtiles : n_sm, kGatherThreads, smem, s>>>(maps, mb, g, cfg);
+    return (int)cudaGetLastError();
+}
+
+// The product's row block p goes to slots[p] (my slot in rank p's staging area, [chunk, N] bf16 with row stride g.ldc).
+int gemm_nt_scatter(const GemmArgs& g, void* const* slots, int n_peers, int chunk, cudaStream_t s) {
+    if (n_peers < 1 || n_peers > kMaxPeers) return -5;
+    if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.b) & 15)) return -2;
+    if ((g.N % 8) || (g.ldc % 8) || (g.K % 8) || (g.lda % 8) || (g.ldb % 8)) return -4;
+    CUtensorMap ma, mb;
+    if (!make_map(&ma, g.a, g.M, g.K, g.lda, BM, BK)) return -1;
+    if (!make_map(&mb, g.b, g.N, g.K, g.ldb, BN, BK)) return -1;
+    ScatterCfg cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    for (int p = 0; p < n_peers; ++p) {
+        if (reinterpret_cast<uintptr_t>(slots[p]) & 15) return -2;
+        cfg.slots[p] = slots[p];
+    }
+    cfg.chunk = chunk; cfg.n_peers = n_peers;
+    static int n_sm = 0;
+    if (n_sm == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+        cudaFuncSetAttribute(gemm_nt_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(PersistentStorage) + 1024));
+    }
+    const int tiles = ((g.N + BN - 1) / BN) * ((g.M + BM - 1) / BM);
+    gemm_nt_scatter_kernel<<<tiles < n_sm ? tiles : n_sm, kThreads, sizeof(PersistentStorage) + 1024, s>>>(ma, mb, g, cfg);
+    return (int)cudaGetLastError();
+}
+
+void sum_slots(const void* slots, int n_slots, long long slot_elems, void* out, int out_dtype, int accumulate, cudaStream_t s) {
+    const long long n8 = slot_elems / 8;
+    const int blocks = (int)((n8 + 255) / 256 < 148 * 8 ? (n8 + 255) / 256 : 148 * 8);
+    if (blocks <= 0) return;
+    if (out_dtype == DT_BF16)
+        sum_slots_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(slots), n_slots, slot_elems,
+                                                              static_cast<__nv_bfloat16*>(out), accumulate);
+    else
+        sum_slots_kernel<float><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(slots), n_slots, slot_elems, static_cast<float*>(out),
+                                                      accumulate);
 }
 
 }  // namespace gt

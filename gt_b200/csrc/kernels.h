@@ -182,6 +182,12 @@ struct GemmTNArgs {
     int* status;
 };
 int gemm_tn_tcgen05(const GemmTNArgs& g, cudaStream_t s);
+// Collective-fused GEMMs over peer memory (symmetric heap).  Return 0, a CUDA error code, or a negative "unsupported" code.
+//   gather : C = gathered(A) * B^T where rank p's rows of A are read from a_peers[p] by TMA; optional gathered copy of A
+//   scatter: row block p of A * B^T is stored into slots[p] (my slot in rank p's staging area); sum_slots adds the slots
+int gemm_nt_gather(const GemmArgs& g, const void* const* a_peers, int n_peers, int chunk, void* gathered, cudaStream_t s);
+int gemm_nt_scatter(const GemmArgs& g, void* const* slots, int n_peers, int chunk, cudaStream_t s);
+void sum_slots(const void* slots, int n_slots, long long slot_elems, void* out, int out_dtype, int accumulate, cudaStream_t s);
 
 // ---- peer-memory kernels (NVLink) ------------------------------------------------------------------------------------
 // out[k] = peers[owner[k]][row[k]]  : receiver-driven gather of rows from the peers' buffers

@@ -31,6 +31,7 @@ from ..parallel.attention import (AttentionBlock, DistAttentionPartial, DistMask
                                   split_block_by_column_subblocks, split_block_by_source_chunk)
 from ..parallel.collectives import (all_gather_rows, all_gather_rows_start, heads_to_rows, raw_all_gather_rows,
                                     raw_reduce_scatter_rows, rows_to_heads, wait_gather)
+from ..parallel.fused_comm import fused_ok, linear_gather
 from ..parallel.grid import group_size
 from ..parallel.layers import DistBatchNorm1d, DistGCNConv, GCNBlock, dist_batchnorm_pair
 from ..parallel.sparse_comm import build_sparse_comm, sparse_all_gather, wait_work
@@ -164,15 +165,19 @@ class DistExphormerLayerFused(_LayerBase):
                 msg = kvg[:, 2 * hd:].contiguous()
                 agg = spmm(self.gcn_block.matrix(msg.dtype, msg.device), msg)
         else:
-            t.start("gather x")
-            x_col = _gather_rows(x, g.col_group, self.sp_col, self.comm_dtype)
-            x_row = _gather_rows(x, g.row_group, self.sp_row, self.comm_dtype)
-            t.stop("gather x")
-            t.start("qkv proj")
             ws = [self.k.weight, self.v.weight] + ([self.gcn.lin.weight] if self.with_gcn else [])
-            kvg = K.linear(x_col, torch.cat(ws, dim=0))               # one GEMM for K | V | GCN message
-            q = K.linear(x_row, self.q.weight).to(kdt).view(-1, h, d)
-            t.stop("qkv proj")
+            w_kvg = torch.cat(ws, dim=0)                               # one GEMM for K | V | GCN message
+            t.start("gather x + qkv proj")
+            # dense groups on the peer-memory transport: the all-gather happens inside the GEMM (TMA loads from the owners)
+            if self.sp_col is None and fused_ok(x, w_kvg, g.col_group):
+                kvg = linear_gather(x, w_kvg, g.col_group)
+            else:
+                kvg = K.linear(_gather_rows(x, g.col_group, self.sp_col, self.comm_dtype), w_kvg)
+            if self.sp_row is None and fused_ok(x, self.q.weight, g.row_group):
+                q = linear_gather(x, self.q.weight, g.row_group).to(kdt).view(-1, h, d)
+            else:
+                q = K.linear(_gather_rows(x, g.row_group, self.sp_row, self.comm_dtype), self.q.weight).to(kdt).view(-1, h, d)
+            t.stop("gather x + qkv proj")
             k = kvg[:, :hd].to(kdt).contiguous().view(-1, h, d)
             v = kvg[:, hd:2 * hd].to(kdt).contiguous().view(-1, h, d)
             if self.with_gcn:

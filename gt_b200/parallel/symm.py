@@ -139,6 +139,37 @@ class SymmetricHeap:
         native.ext().pull_reduce_scatter(self.peer_table_cached(c, off), c.me, out)
         return out
 
+    # ---- collectives fused into the tensor-core GEMMs ------------------------------------------------------------------------
+    def linear_gather(self, x, w, group, bias=None, act=None, want_gathered=True):
+        """``all_gather(x) @ w^T`` in one kernel: the GEMM's TMA loads read each rank's ``x [chunk, K]`` (bf16) from the
+        owner's heap, tile by tile.  Returns ``(y [G * chunk, N], gathered x or None)``."""
+        c = self.ctx(group)
+        x = x.contiguous()
+        chunk, k = x.shape
+        off = c.staging(x.numel() * 2, "agg")
+        self.view(off, x.shape, torch.bfloat16).copy_(x)
+        c.barrier()                                               # every rank's x is in place
+        y = torch.empty(c.size * chunk, w.shape[0], dtype=torch.bfloat16, device=x.device)
+        xg = torch.empty(c.size * chunk, k, dtype=torch.bfloat16, device=x.device) if want_gathered else None
+        native.ext().gemm_nt_gather([self.peer_base[r] + off for r in c.ranks], chunk, k, k, w, y, bias, {None: 0, "relu": 1, "gelu": 2}[act],
+                                    0.0, None, 0, xg, native.status(self.device))
+        return y, xg
+
+    def linear_scatter(self, a, w, group, out_dtype=torch.bfloat16, out=None, accumulate=False):
+        """``reduce_scatter(a @ w^T)`` with the scatter in the GEMM epilogue: finished tiles are stored straight into the
+        owning rank's heap; after a barrier the owner adds the ``G`` slots.  ``a [G * chunk, K]``, ``w [N, K]`` bf16."""
+        c = self.ctx(group)
+        chunk, n = a.shape[0] // c.size, w.shape[0]
+        slot = chunk * n * 2
+        off = c.staging(c.size * slot, "grs")
+        native.ext().gemm_nt_scatter(a, w, [self.peer_base[r] + off + c.me * slot for r in c.ranks], chunk, n, native.status(self.device))
+        c.barrier()                                               # every rank's tiles have landed in my slots
+        if out is None:
+            out = torch.empty(chunk, n, dtype=out_dtype, device=a.device)
+            accumulate = False
+        native.ext().sum_slots(self.view(off, (c.size, chunk, n), torch.bfloat16), out, accumulate)
+        return out
+
     def all_reduce(self, x, out, name=None, group=None):
         """``out = sum over ranks of x``; ``x`` should live in the heap (``heap.empty``), otherwise it is staged."""
         c = self.ctx(group)

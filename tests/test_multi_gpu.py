@@ -68,6 +68,49 @@ def _collectives_worker(rank, world, store):
     dist.destroy_process_group()
 
 
+def _fused_gemm_worker(rank, world, store):
+    """All-gather fused into the GEMM (TMA loads from peer memory) and reduce-scatter fused into the GEMM epilogue (peer
+    stores) against the unfused NCCL + GEMM pair, forward and backward, on shapes with ragged tile edges."""
+    import torch.distributed as dist
+    from gt_b200.ops import native
+    from gt_b200.parallel.collectives import all_gather_rows, set_transport
+    from gt_b200.parallel.fused_comm import fused_ok, linear_gather
+    from gt_b200.parallel.symm import SymmetricHeap
+    dev = _init(rank, world, store)
+    heap = SymmetricHeap(dev, 512 << 20)
+    for chunk, k, n in ((1000, 256, 768), (4104, 128, 256), (520, 512, 136), (37000, 256, 768)):
+        torch.manual_seed(7)
+        w = (torch.randn(n, k, device=dev) * k ** -0.5).requires_grad_()
+        torch.manual_seed(100 + rank)
+        x = torch.randn(chunk, k, device=dev).bfloat16().requires_grad_()
+        gy = torch.randn(world * chunk, n, device=dev).bfloat16()
+        set_transport(None)
+        ref = native.linear(all_gather_rows(x, None), w)
+        ref.backward(gy)
+        gx_ref, gw_ref = x.grad.clone(), w.grad.clone()
+        x.grad = w.grad = None
+        set_transport(heap)
+        assert fused_ok(x, w, None)
+        for rep in range(2):                                    # twice: the staging buffers of a call site are reused
+            heap.begin_step()
+            out = linear_gather(x, w, None)
+            out.backward(gy)
+            assert (out.float() - ref.float()).abs().max() <= 2e-2 * ref.float().abs().max(), (chunk, k, n)
+            assert (x.grad.float() - gx_ref.float()).abs().max() <= 3e-2 * gx_ref.float().abs().max() + 1e-3, (chunk, k, n)
+            assert (w.grad - gw_ref).abs().max() <= 2e-2 * gw_ref.abs().max() + 1e-3, (chunk, k, n)
+            x.grad = w.grad = None
+        # the gathered by-product equals the all-gather
+        heap.begin_step()
+        y, xg = heap.linear_gather(x.detach(), w.detach().bfloat16(), None, want_gathered=True)
+        set_transport(None)
+        assert torch.equal(xg, all_gather_rows(x.detach(), None))
+    torch.cuda.synchronize()
+    native.check_status(dev)
+    set_transport(None)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def _model_worker(rank, world, store, grid_shape):
     import torch.distributed as dist
     from gt_b200.ops import native
@@ -107,6 +150,11 @@ def _model_worker(rank, world, store, grid_shape):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
 def test_peer_memory_collectives_match_nccl():
     _spawn(_collectives_worker, 2)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_collective_fused_gemms_match_unfused():
+    _spawn(_fused_gemm_worker, 2)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
