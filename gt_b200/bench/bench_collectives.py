@@ -70,6 +70,26 @@ def main(argv=None):
             return heap.reduce_scatter(full, None)
         res["ag_heap"], res["rs_heap"] = t(ag_heap), t(rs_heap)
         assert torch.equal(ag_heap(), raw_all_gather_rows(x, None)), "heap all-gather differs from NCCL"
+    # projection with its collective: NCCL all-gather + GEMM vs the GEMM that gathers through TMA loads from peer memory,
+    # and GEMM + NCCL reduce-scatter vs the GEMM whose epilogue stores into the owners' memory
+    if heap is not None and cuda and args.width <= 512:
+        from ..ops import native
+        n_out = 3 * args.width
+        w = (torch.randn(n_out, args.width, device=dev) * args.width ** -0.5).bfloat16()
+        wt = w.t().contiguous()
+        dy = torch.randn(per * world, n_out, device=dev).bfloat16()
+        res["ag_then_gemm_nccl"] = t(lambda: native.gemm_nt(raw_all_gather_rows(x, None), w))
+        res["gemm_then_rs_nccl"] = t(lambda: raw_reduce_scatter_rows(native.gemm_nt(dy, wt), None))
+
+        def fused_ag():
+            heap.begin_step()
+            return heap.linear_gather(x, w, None, want_gathered=True)
+
+        def fused_rs():
+            heap.begin_step()
+            return heap.linear_scatter(dy, wt, None)
+        res["ag_gemm_fused"], res["gemm_rs_fused"] = t(fused_ag), t(fused_rs)
+        res["gemm_only"] = t(lambda: native.gemm_nt(full, w))
     # sparse: a random share of the block
     g = torch.Generator().manual_seed(100 + rank)
     need = torch.randperm(per * world, generator=g)[:max(int(args.share * per * world), 1)].sort().values.to(dev)

@@ -30,7 +30,10 @@ def main():
     ap.add_argument("--dims", nargs="+", default=["256:768", "256:256", "256:512", "512:256", "128:256"])
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--only", default=None, choices=[None, "nt", "tn"])
+    ap.add_argument("--only", default=None, choices=[None, "nt", "tn", "gather"])
+    ap.add_argument("--gather", type=int, default=0, metavar="G",
+                    help="also time the all-gather-fused kernel with G row chunks that all live on this GPU (the kernel's own "
+                         "efficiency without the link; multi-GPU timing is in bench_collectives)")
     args = ap.parse_args()
     from ..ops import native
     dev = torch.device("cuda", 0)
@@ -51,6 +54,20 @@ def main():
             ms = timeit(lambda: native.gemm_tn(dy, x), args.iters, args.warmup)
             ms_ref = timeit(lambda: dy.t() @ x, args.iters, args.warmup)
             out.update(tn_ms=ms, tn_tflops=flops / ms / 1e9, cublas_tn_ms=ms_ref)
+        if args.gather and k <= 512 and m % args.gather == 0:
+            chunk = m // args.gather
+            y = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+            xg = torch.empty_like(x)
+            ptrs = [x[i * chunk:].data_ptr() for i in range(args.gather)]
+            e = native.ext()
+
+            def fused(copy):
+                e.gemm_nt_gather(ptrs, chunk, k, k, w, y, None, 0, 0.0, None, 0, xg if copy else None, native.status(dev))
+            ms = timeit(lambda: fused(False), args.iters, args.warmup)
+            ms_c = timeit(lambda: fused(True), args.iters, args.warmup)
+            fused(True)
+            ok = bool(torch.equal(xg, x)) and float((y.float() - (x @ w.t()).float()).abs().max()) < 0.05 * float((x @ w.t()).float().abs().max())
+            out.update(gather_chunks=args.gather, gather_ms=ms, gather_tflops=flops / ms / 1e9, gather_copy_ms=ms_c, gather_ok=ok)
         native.check_status(dev)
         print("GEMM " + json.dumps(out), flush=True)
 

@@ -214,6 +214,26 @@ void cast_bf16(Tensor in, Tensor out) {
     gt::cast_f32_to_bf16(in.data_ptr<float>(), out.data_ptr(), in.numel(), stream());
 }
 
+// parts[i] [n, w_i] (fp32 / bf16, unit column stride) <-> packed [n, sum w_i]; to_packed selects the direction
+void pack_cols(std::vector<Tensor> parts, Tensor packed, bool to_packed) {
+    c10::cuda::CUDAGuard guard(packed.device());
+    TORCH_CHECK(parts.size() >= 1 && parts.size() <= 4, "1..4 parts");
+    gt::PackColsArgs a{};
+    a.n_seg = (int)parts.size();
+    int w = 0;
+    for (int i = 0; i < a.n_seg; ++i) {
+        Tensor& t = parts[i];
+        TORCH_CHECK(t.dim() == 2 && t.stride(1) == 1 && t.size(0) == packed.size(0) && t.size(1) % 8 == 0 && t.stride(0) % 8 == 0 &&
+                    (reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0, "parts must be [n, w] with w, row stride % 8 == 0, 16-byte aligned");
+        a.seg[i] = gt::PackColSeg{t.data_ptr(), (int)t.size(1), dt(t), (int)t.stride(0)};
+        w += (int)t.size(1);
+    }
+    TORCH_CHECK(packed.dim() == 2 && packed.stride(1) == 1 && packed.size(1) >= w && packed.stride(0) % 8 == 0, "packed shape");
+    a.packed = packed.data_ptr(); a.packed_dtype = dt(packed); a.ld_packed = (int)packed.stride(0); a.width = w;
+    a.n_rows = packed.size(0); a.dir = to_packed ? 0 : 1;
+    gt::pack_cols(a, stream());
+}
+
 // C[M, N] = epilogue(A[M, K] @ B[N, K]^T)
 void gemm_nt(Tensor a, Tensor b, Tensor c, OptT bias, int64_t act, double p, OptT seed, int64_t stream_id, bool accumulate, Tensor status) {
     c10::cuda::CUDAGuard guard(a.device());
@@ -408,6 +428,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("adamw_step", &adamw_step);
     m.def("sq_norm", &sq_norm);
     m.def("cast_bf16", &cast_bf16);
+    m.def("pack_cols", &pack_cols);
     m.def("gemm_nt", &gemm_nt);
     m.def("gemm_tn", &gemm_tn);
     m.def("gemm_nt_gather", &gemm_nt_gather);

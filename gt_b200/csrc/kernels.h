@@ -158,6 +158,15 @@ void adamw_step(const AdamWArgs& a, cudaStream_t s);
 void sq_norm(const float* g, long long n, float* out, cudaStream_t s);
 void cast_f32_to_bf16(const float* in, void* out, long long n, cudaStream_t s);
 
+// packed[r, :] = concat_i seg_i[r, :] with conversion (dir 0), or seg_i[r, :] = packed[r, off_i : off_i + w_i] (dir 1)
+struct PackColSeg { void* p; int width; int dtype; int ld; };
+struct PackColsArgs {
+    PackColSeg seg[4]; int n_seg;
+    void* packed; int packed_dtype; int ld_packed; int width;    // width = sum of the segment widths (<= ld_packed)
+    long long n_rows; int dir;
+};
+void pack_cols(const PackColsArgs& a, cudaStream_t s);
+
 // ---- tcgen05 GEMM -----------------------------------------------------------------------------------------------------
 // C[M, N] = A[M, K] * B[N, K]^T  (both operands K-major bf16, fp32 accumulation in tensor memory)
 struct GemmArgs {

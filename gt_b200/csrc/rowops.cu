@@ -48,16 +48,16 @@ __device__ __forceinline__ void load_z(const T* y, const T* x, const float* ybia
     }
 }
 
-template <typename T>
+template <typename T, int CPL>
 __global__ void __launch_bounds__(kWarps * 32) ln_fwd_kernel(LayerNormArgs a) {
     const int row = blockIdx.x * kWarps + (threadIdx.x >> 5);
     if (row >= a.n) return;
     const int lane = threadIdx.x & 31, nch = a.d >> 3;
     const uint64_t sd = site_seed(a.seed, a.stream_id);
-    float z[kMaxCpl][8], keep[8];
+    float z[CPL][8], keep[8];
     float sum = 0.f;
 #pragma unroll
-    for (int i = 0; i < kMaxCpl; ++i) {
+    for (int i = 0; i < CPL; ++i) {
         int ch = lane + 32 * i;
         if (ch < nch) {
             const float inv_l = a.acc ? 1.f / (a.l[(size_t)row * a.H + ((ch << 3) / (a.d / a.H))] + a.eps_l) : 1.f;
@@ -69,13 +69,13 @@ __global__ void __launch_bounds__(kWarps * 32) ln_fwd_kernel(LayerNormArgs a) {
     const float mean = warp_sum(sum) / a.d;
     float var = 0.f;
 #pragma unroll
-    for (int i = 0; i < kMaxCpl; ++i)
+    for (int i = 0; i < CPL; ++i)
         if (lane + 32 * i < nch)
 #pragma unroll
             for (int k = 0; k < 8; ++k) { float t = z[i][k] - mean; var = fmaf(t, t, var); }
     const float rstd = rsqrtf(warp_sum(var) / a.d + a.eps);
 #pragma unroll
-    for (int i = 0; i < kMaxCpl; ++i) {
+    for (int i = 0; i < CPL; ++i) {
         int ch = lane + 32 * i;
         if (ch < nch) {
             int f = ch << 3;
@@ -88,35 +88,45 @@ __global__ void __launch_bounds__(kWarps * 32) ln_fwd_kernel(LayerNormArgs a) {
     if (lane == 0 && a.mean_rstd) { a.mean_rstd[2 * row] = mean; a.mean_rstd[2 * row + 1] = rstd; }
 }
 
-template <typename T>
+template <typename T, int CPL>
 __global__ void __launch_bounds__(kWarps * 32) ln_bwd_kernel(LayerNormBwdArgs a) {
     extern __shared__ float smem[];                    // [3][d] block accumulators: dgamma, dbeta, dybias
     const int lane = threadIdx.x & 31, nch = a.d >> 3;
     for (int i = threadIdx.x; i < 3 * a.d; i += blockDim.x) smem[i] = 0.f;
     __syncthreads();
     const uint64_t sd = site_seed(a.seed, a.stream_id);
-    float dgam[kMaxCpl][8], dbet[kMaxCpl][8], dyb[kMaxCpl][8];
+    const float inv_keep = a.p > 0.f ? 1.f / (1.f - a.p) : 1.f;
+    float dgam[CPL][8], dbet[CPL][8], dyb[CPL][8];
 #pragma unroll
-    for (int i = 0; i < kMaxCpl; ++i)
+    for (int i = 0; i < CPL; ++i)
 #pragma unroll
         for (int k = 0; k < 8; ++k) { dgam[i][k] = 0.f; dbet[i][k] = 0.f; dyb[i][k] = 0.f; }
+    float gam[CPL][8];
+#pragma unroll
+    for (int i = 0; i < CPL; ++i)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) gam[i][k] = (lane + 32 * i) < nch ? a.gamma[((lane + 32 * i) << 3) + k] : 0.f;
     for (int row = blockIdx.x * kWarps + (threadIdx.x >> 5); row < a.n; row += gridDim.x * kWarps) {
         const float mean = a.mean_rstd[2 * row], rstd = a.mean_rstd[2 * row + 1];
-        float zh[kMaxCpl][8], dzh[kMaxCpl][8], keep[kMaxCpl][8];
+        float zh[CPL][8], dzh[CPL][8];
+        uint32_t keep_bits[CPL];                       // dropout mask of the lane's chunk, one bit per element
         float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-        for (int i = 0; i < kMaxCpl; ++i) {
+        for (int i = 0; i < CPL; ++i) {
             int ch = lane + 32 * i;
             if (ch < nch) {
                 int f = ch << 3;
-                float z[8], go[8];
+                float z[8], go[8], keep[8];
                 const float inv_l = a.acc ? 1.f / (a.l[(size_t)row * a.H + (f / (a.d / a.H))] + a.eps_l) : 1.f;
-                load_z<T>(static_cast<const T*>(a.y), static_cast<const T*>(a.x), a.ybias, row, a.d, f, a.p, sd, z, keep[i], a.acc, inv_l);
+                load_z<T>(static_cast<const T*>(a.y), static_cast<const T*>(a.x), a.ybias, row, a.d, f, a.p, sd, z, keep, a.acc, inv_l);
+                keep_bits[i] = 0u;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) keep_bits[i] |= (keep[k] != 0.f ? 1u : 0u) << k;
                 Vec8<T>::load(static_cast<const T*>(a.dout) + (size_t)row * a.d + f, go);
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
                     zh[i][k] = (z[k] - mean) * rstd;
-                    dzh[i][k] = go[k] * a.gamma[f + k];
+                    dzh[i][k] = go[k] * gam[i][k];
                     s1 += dzh[i][k];
                     s2 = fmaf(dzh[i][k], zh[i][k], s2);
                     dgam[i][k] = fmaf(go[k], zh[i][k], dgam[i][k]);
@@ -126,9 +136,11 @@ __global__ void __launch_bounds__(kWarps * 32) ln_bwd_kernel(LayerNormBwdArgs a)
         }
         s1 = warp_sum(s1) / a.d;
         s2 = warp_sum(s2) / a.d;
-        float dl_part[kMaxCpl] = {0.f, 0.f, 0.f, 0.f};
+        float dl_part[CPL];
 #pragma unroll
-        for (int i = 0; i < kMaxCpl; ++i) {
+        for (int i = 0; i < CPL; ++i) dl_part[i] = 0.f;
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) {
             int ch = lane + 32 * i;
             if (ch < nch) {
                 int f = ch << 3;
@@ -136,7 +148,7 @@ __global__ void __launch_bounds__(kWarps * 32) ln_bwd_kernel(LayerNormBwdArgs a)
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
                     dz[k] = rstd * (dzh[i][k] - s1 - zh[i][k] * s2);
-                    dy[k] = dz[k] * keep[i][k];
+                    dy[k] = ((keep_bits[i] >> k) & 1u) ? dz[k] * inv_keep : 0.f;
                     dyb[i][k] += dy[k];
                 }
                 if (a.acc) {
@@ -169,7 +181,7 @@ __global__ void __launch_bounds__(kWarps * 32) ln_bwd_kernel(LayerNormBwdArgs a)
             // a head spans (d / H) / 8 consecutive lanes (a power of two): finish dl with xor shuffles, all lanes take part
             const int lph = (a.d / a.H) >> 3;
 #pragma unroll
-            for (int i = 0; i < kMaxCpl; ++i) {
+            for (int i = 0; i < CPL; ++i) {
                 float v = dl_part[i];
                 for (int o = lph >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(GT_FULL_MASK, v, o);
                 const int ch = lane + 32 * i;
@@ -178,7 +190,7 @@ __global__ void __launch_bounds__(kWarps * 32) ln_bwd_kernel(LayerNormBwdArgs a)
         }
     }
 #pragma unroll
-    for (int i = 0; i < kMaxCpl; ++i) {
+    for (int i = 0; i < CPL; ++i) {
         int ch = lane + 32 * i;
         if (ch < nch) {
             int f = ch << 3;
@@ -338,13 +350,55 @@ int grid_for(long long work_items, int per_block) {
     return (int)(b < 1 ? 1 : (b > cap ? cap : b));
 }
 
+// Column-wise concatenation with conversion: packed[r, off_i : off_i + w_i] = seg_i[r, :] (dir 0) or the reverse (dir 1).
+// One thread moves one 8-element chunk; every width and row stride is a multiple of 8 elements.
+template <typename TP>
+__global__ void pack_cols_kernel(PackColsArgs a) {
+    const int cpr = a.width >> 3;
+    const long long total = a.n_rows * cpr;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long row = i / cpr;
+        int col = (int)(i - row * cpr) << 3;
+        TP* pk = static_cast<TP*>(a.packed) + row * a.ld_packed + col;
+        int sgi = 0;
+        while (sgi + 1 < a.n_seg && col >= a.seg[sgi].width) { col -= a.seg[sgi].width; ++sgi; }
+        const PackColSeg& sg = a.seg[sgi];
+        float v[8];
+        if (a.dir == 0) {
+            if (sg.dtype == DT_BF16) Vec8<__nv_bfloat16>::load(static_cast<const __nv_bfloat16*>(sg.p) + row * sg.ld + col, v);
+            else Vec8<float>::load(static_cast<const float*>(sg.p) + row * sg.ld + col, v);
+            Vec8<TP>::store(pk, v);
+        } else {
+            Vec8<TP>::load(pk, v);
+            if (sg.dtype == DT_BF16) Vec8<__nv_bfloat16>::store(static_cast<__nv_bfloat16*>(sg.p) + row * sg.ld + col, v);
+            else Vec8<float>::store(static_cast<float*>(sg.p) + row * sg.ld + col, v);
+        }
+    }
+}
+
 }  // namespace
+
+void pack_cols(const PackColsArgs& a, cudaStream_t s) {
+    const long long chunks = a.n_rows * (a.width >> 3);
+    if (chunks <= 0) return;
+    const int blocks = grid_for(chunks, 256);
+    if (a.packed_dtype == DT_BF16) pack_cols_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(a);
+    else pack_cols_kernel<float><<<blocks, 256, 0, s>>>(a);
+}
 
 void layer_norm_fwd(const LayerNormArgs& a, cudaStream_t s) {
     if (a.n <= 0) return;
     const int blocks = (a.n + kWarps - 1) / kWarps;
-    if (a.dtype == DT_BF16) ln_fwd_kernel<__nv_bfloat16><<<blocks, kWarps * 32, 0, s>>>(a);
-    else ln_fwd_kernel<float><<<blocks, kWarps * 32, 0, s>>>(a);
+    // chunks of 8 features per lane: the kernel is instantiated for 1, 2 or 4 so narrow rows do not pay for wide registers
+#define GT_LN_FWD(T)                                                                   \
+    do {                                                                               \
+        if (a.d <= 256) ln_fwd_kernel<T, 1><<<blocks, kWarps * 32, 0, s>>>(a);         \
+        else if (a.d <= 512) ln_fwd_kernel<T, 2><<<blocks, kWarps * 32, 0, s>>>(a);    \
+        else ln_fwd_kernel<T, 4><<<blocks, kWarps * 32, 0, s>>>(a);                    \
+    } while (0)
+    if (a.dtype == DT_BF16) GT_LN_FWD(__nv_bfloat16);
+    else GT_LN_FWD(float);
+#undef GT_LN_FWD
 }
 
 int layer_norm_bwd_blocks(int n) {
@@ -355,8 +409,15 @@ int layer_norm_bwd_blocks(int n) {
 void layer_norm_bwd(const LayerNormBwdArgs& a, cudaStream_t s) {
     if (a.n <= 0) return;
     const size_t sm = 3 * (size_t)a.d * sizeof(float);
-    if (a.dtype == DT_BF16) ln_bwd_kernel<__nv_bfloat16><<<a.n_blocks, kWarps * 32, sm, s>>>(a);
-    else ln_bwd_kernel<float><<<a.n_blocks, kWarps * 32, sm, s>>>(a);
+#define GT_LN_BWD(T)                                                                          \
+    do {                                                                                      \
+        if (a.d <= 256) ln_bwd_kernel<T, 1><<<a.n_blocks, kWarps * 32, sm, s>>>(a);           \
+        else if (a.d <= 512) ln_bwd_kernel<T, 2><<<a.n_blocks, kWarps * 32, sm, s>>>(a);      \
+        else ln_bwd_kernel<T, 4><<<a.n_blocks, kWarps * 32, sm, s>>>(a);                      \
+    } while (0)
+    if (a.dtype == DT_BF16) GT_LN_BWD(__nv_bfloat16);
+    else GT_LN_BWD(float);
+#undef GT_LN_BWD
 }
 
 void bias_act_dropout(int dtype, const void* in, const float* bias, void* out, long long n, int d, int act, float p,

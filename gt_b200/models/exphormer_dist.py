@@ -159,10 +159,10 @@ class DistExphormerLayerFused(_LayerBase):
             q = _gather_rows(q_loc, g.row_group, self.sp_row, self.comm_dtype).to(kdt).view(-1, h, d)
             kvg = _gather_rows(kvg_loc, g.col_group, self.sp_col, self.comm_dtype)
             t.stop("gather x")
-            k = kvg[:, :hd].to(kdt).contiguous().view(-1, h, d)
-            v = kvg[:, hd:2 * hd].to(kdt).contiguous().view(-1, h, d)
+            pieces = K.split_columns(kvg, [hd, hd] + ([kvg.shape[1] - 2 * hd] if self.with_gcn else []))
+            k, v = pieces[0].to(kdt).view(-1, h, d), pieces[1].to(kdt).view(-1, h, d)
             if self.with_gcn:
-                msg = kvg[:, 2 * hd:].contiguous()
+                msg = pieces[2]
                 agg = spmm(self.gcn_block.matrix(msg.dtype, msg.device), msg)
         else:
             ws = [self.k.weight, self.v.weight] + ([self.gcn.lin.weight] if self.with_gcn else [])
@@ -178,11 +178,11 @@ class DistExphormerLayerFused(_LayerBase):
             else:
                 q = K.linear(_gather_rows(x, g.row_group, self.sp_row, self.comm_dtype), self.q.weight).to(kdt).view(-1, h, d)
             t.stop("gather x + qkv proj")
-            k = kvg[:, :hd].to(kdt).contiguous().view(-1, h, d)
-            v = kvg[:, hd:2 * hd].to(kdt).contiguous().view(-1, h, d)
+            pieces = K.split_columns(kvg, [hd, hd] + ([kvg.shape[1] - 2 * hd] if self.with_gcn else []))
+            k, v = pieces[0].to(kdt).view(-1, h, d), pieces[1].to(kdt).view(-1, h, d)
             if self.with_gcn:
                 t.start("gcn spmm")
-                msg = kvg[:, 2 * hd:].contiguous()
+                msg = pieces[2]
                 agg = spmm(self.gcn_block.matrix(msg.dtype, msg.device), msg)
                 t.stop("gcn spmm")
         t.start("attention partial")
@@ -287,12 +287,12 @@ class DistExphormerLayerPipelined(DistExphormerLayerFused):
             kvg = K.linear(xs, ws)
             if q is None:
                 q = K.linear(wait_gather(row_handle), self.q.weight).to(kdt).view(-1, h, d)
-            acc_s, l_s, _ = self.attns[s](q, kvg[:, :hd].to(kdt).contiguous().view(-1, h, d),
-                                          kvg[:, hd:2 * hd].to(kdt).contiguous().view(-1, h, d), gate)
+            pieces = K.split_columns(kvg, [hd, hd] + ([kvg.shape[1] - 2 * hd] if self.with_gcn else []))
+            acc_s, l_s, _ = self.attns[s](q, pieces[0].to(kdt).view(-1, h, d), pieces[1].to(kdt).view(-1, h, d), gate)
             acc = acc_s if acc is None else acc + acc_s
             l = l_s if l is None else l + l_s
             if self.with_gcn:
-                msg = kvg[:, 2 * hd:].contiguous()
+                msg = pieces[2]
                 agg_s = spmm(self.gcn_blocks[s].matrix(msg.dtype, msg.device), msg)
                 agg = agg_s if agg is None else agg + agg_s
         return combine_partials(acc, l, torch.zeros_like(l), g, "clampexp", 1e-6, extra=agg, rs_dtype=self.rs_dtype, normalize=False)

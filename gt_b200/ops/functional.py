@@ -108,3 +108,30 @@ def gated_residual(r, o, gate_weight, gate_bias, ln, p=0.0, training=False):
     beta = torch.sigmoid(logit).unsqueeze(-1)
     out = F.relu(ln(beta * r + (1.0 - beta) * o))
     return F.dropout(out, p, training) if p > 0 else out
+
+
+class _SplitColumns(torch.autograd.Function):
+    """Contiguous copies of consecutive column ranges of a 2-D tensor.  Backward is ONE concatenation of the pieces'
+    gradients; autograd's own slice backward would allocate a zero matrix per piece and add them up."""
+
+    @staticmethod
+    def forward(ctx, x, *widths):
+        ctx.widths, ctx.dtype = widths, x.dtype
+        outs, c = [], 0
+        for w in widths:
+            outs.append(x[:, c:c + w].contiguous())
+            c += w
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        ref = next(g for g in grads if g is not None)
+        parts = [g if g is not None else ref.new_zeros(ref.shape[0], w) for g, w in zip(grads, ctx.widths)]
+        return (torch.cat([p.to(ctx.dtype) for p in parts], dim=1),) + (None,) * len(ctx.widths)
+
+
+def split_columns(x, widths):
+    """``x [n, sum(widths)] -> tuple of contiguous [n, w]`` pieces."""
+    if len(widths) == 1:
+        return (x,)
+    return _SplitColumns.apply(x, *widths)

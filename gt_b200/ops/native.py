@@ -362,3 +362,27 @@ def segment_sum_rows(rows, perm, ptr, out):
         return out.zero_().index_add_(0, seg, rows[perm.long()])
     ext().spmm(ptr, perm, None, rows.contiguous(), out, False, [], None)
     return out
+
+
+# ---- column packing (payloads of the row collectives) ---------------------------------------------------------------------
+def pack_ok(parts):
+    return all(t.is_cuda and t.dim() == 2 and t.dtype in (torch.float32, torch.bfloat16) and t.shape[1] % 8 == 0 for t in parts) \
+        and 1 <= len(parts) <= 4
+
+
+def pack_columns(parts, dtype):
+    """``concat(parts, dim=1)`` converted to ``dtype`` in one pass (``parts``: ``[n, w_i]`` fp32 / bf16, ``w_i % 8 == 0``)."""
+    parts = [_rowmajor(t) for t in parts]
+    out = torch.empty(parts[0].shape[0], sum(t.shape[1] for t in parts), dtype=dtype, device=parts[0].device)
+    if out.numel():
+        ext().pack_cols(parts, out, True)
+    return out
+
+
+def unpack_columns(packed, widths, dtypes):
+    """Inverse of :func:`pack_columns`: contiguous pieces ``[n, w_i]`` of the given dtypes."""
+    packed = _rowmajor(packed)
+    outs = [torch.empty(packed.shape[0], w, dtype=dt, device=packed.device) for w, dt in zip(widths, dtypes)]
+    if packed.numel():
+        ext().pack_cols(outs, packed, False)
+    return outs

@@ -210,6 +210,37 @@ class DistAttentionPartial(_OpBase):
         return _AttnPartial.apply(q_blk.contiguous(), k_blk.contiguous(), v_blk.contiguous(), gate, bias, self)
 
 
+def _pack_ok(parts):
+    if not parts[0].is_cuda:
+        return False
+    from ..ops import native
+    return native.pack_ok(parts)
+
+
+class _PackedReduceScatter(torch.autograd.Function):
+    """Reduce-scatter of several column blocks in ONE payload: ``parts [rows, w_i]`` are packed into the wire dtype by one
+    kernel, reduced over the group, and unpacked to the parts' own dtypes; backward is pack -> all-gather -> unpack."""
+
+    @staticmethod
+    def forward(ctx, group, wire, *parts):
+        from ..ops import native
+        wire = wire or torch.float32
+        ctx.group, ctx.wire = group, wire
+        ctx.widths, ctx.dtypes = [p.shape[1] for p in parts], [p.dtype for p in parts]
+        packed = native.pack_columns([p.detach() for p in parts], wire)
+        out = raw_reduce_scatter_rows(packed, group)
+        return tuple(native.unpack_columns(out, ctx.widths, ctx.dtypes))
+
+    @staticmethod
+    def backward(ctx, *grads):
+        from ..ops import native
+        ref = next(g for g in grads if g is not None)
+        grads = [g if g is not None else ref.new_zeros(ref.shape[0], w) for g, w in zip(grads, ctx.widths)]
+        packed = native.pack_columns(grads, ctx.wire)
+        full = raw_all_gather_rows(packed, ctx.group)
+        return (None, None) + tuple(native.unpack_columns(full, ctx.widths, ctx.dtypes))
+
+
 def combine_partials(acc, l, m, grid, norm, eps, extra=None, rs_dtype=None, plan=None, normalize=True):
     """Merge the block partials of a row group onto the owner of every row; returns ``(o_owned, extra_owned)``.
 
@@ -235,6 +266,15 @@ def combine_partials(acc, l, m, grid, norm, eps, extra=None, rs_dtype=None, plan
         acc_o, l_o, extra_o = acc, l, extra
         if not normalize:
             return (acc_o.reshape(n_rows, h * d), l_o), extra_o
+        o = acc_o / (torch.where(l_o > 0, l_o, torch.ones_like(l_o)) if norm == "softmax" else (l_o + eps)).unsqueeze(-1)
+        return o, extra_o
+    if plan is None and _pack_ok([acc.reshape(n_rows, h * d), l] + ([extra] if extra is not None else [])):
+        # one packing pass into the wire dtype, the collective, one unpacking pass (instead of cat / cast / slice / cast)
+        outs = _PackedReduceScatter.apply(grid.row_group, rs_dtype, acc.reshape(n_rows, h * d), l, *([extra] if extra is not None else []))
+        acc_o, l_o, extra_o = outs[0], outs[1], (outs[2] if extra is not None else None)
+        if not normalize:
+            return (acc_o, l_o), extra_o
+        acc_o = acc_o.reshape(-1, h, d)
         o = acc_o / (torch.where(l_o > 0, l_o, torch.ones_like(l_o)) if norm == "softmax" else (l_o + eps)).unsqueeze(-1)
         return o, extra_o
     parts, width = [acc.reshape(n_rows, h * d), l], h * d + h

@@ -243,3 +243,19 @@ def test_layer_norm_with_fused_attention_normalisation():
     assert _rel(out, ref) < 2e-2
     for a, b, name in ((acc.grad, a2.grad, "dacc"), (l.grad, l2.grad, "dl"), (x.grad, x2.grad, "dx"), (gam.grad, g2.grad, "dgamma")):
         assert _rel(a, b) < 3e-2, name
+
+
+def test_pack_and_unpack_columns():
+    from gt_b200.ops import native
+    DEV = _dev()
+    torch.manual_seed(0)
+    a = torch.randn(1001, 256, device=DEV)
+    l = torch.rand(1001, 8, device=DEV)
+    e = torch.randn(1001, 264, device=DEV).bfloat16()[:, :256]              # a strided view: row stride 264
+    for wire in (torch.bfloat16, torch.float32):
+        packed = native.pack_columns([a, l, e], wire)
+        ref = torch.cat([a, l, e.float()], dim=1).to(wire)
+        assert torch.equal(packed, ref)
+        a2, l2, e2 = native.unpack_columns(packed, [256, 8, 256], [torch.float32, torch.float32, torch.bfloat16])
+        assert torch.equal(a2, ref[:, :256].float()) and torch.equal(l2, ref[:, 256:264].float()) and torch.equal(e2, ref[:, 264:].bfloat16())
+    native.check_status(DEV)

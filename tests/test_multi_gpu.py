@@ -52,6 +52,23 @@ def _collectives_worker(rank, world, store):
         dist.all_reduce(ref)
         heap.all_reduce(g, out, "grads")
         assert (out - ref).abs().max() < 1e-5
+    # several column blocks reduced in one packed payload (forward) / gathered (backward) vs the concatenated reference
+    from gt_b200.parallel.attention import _PackedReduceScatter
+    from gt_b200.parallel.collectives import reduce_scatter_rows
+    heap.begin_step()
+    acc = torch.randn(world * 512, 64, device=dev, requires_grad=True)
+    l = torch.rand(world * 512, 8, device=dev, requires_grad=True)
+    ex = torch.randn(world * 512, 32, device=dev).bfloat16().requires_grad_()
+    o = _PackedReduceScatter.apply(None, torch.bfloat16, acc, l, ex)
+    w = [torch.randn_like(t) for t in o]
+    sum((a_ * b_).sum() for a_, b_ in zip(o, w)).backward()
+    got = [acc.grad.clone(), l.grad.clone(), ex.grad.clone()]
+    acc.grad = l.grad = ex.grad = None
+    ref = reduce_scatter_rows(torch.cat([acc, l, ex.float()], dim=1), None, torch.bfloat16)
+    assert (torch.cat([o[0], o[1], o[2].float()], dim=1) - ref).abs().max() < 0.1
+    (ref * torch.cat([w[0], w[1], w[2].float()], dim=1)).sum().backward()
+    for g_, r_ in zip(got, (acc.grad, l.grad, ex.grad)):
+        assert (g_.float() - r_.float()).abs().max() < 0.05
     # sparse plan: pull transport vs all-to-all-v transport
     need = torch.unique(torch.randint(0, world * 300, (200,), device=dev))
     plan_a = SparseRowPlan(None, 300, need, "t", "a2a")
