@@ -1018,6 +1018,14 @@ bool gemm_tcgen05_supported(int M, int N, int K, int lda, int ldb, int ldc) {
     return M > 0 && N > 0 && K > 0 && (lda % 8) == 0 && (ldb % 8) == 0 && (K % 8) == 0;
 }
 
+int gemm_nt_gather(const GemmArgs& g, const void* const* a_peers, int n_peers, int chunk, void* gathered, cudaStream_t s);
+
+// GT_GEMM_KERNEL: "simple" = one tile per CTA, "persistent" = the tile-walking kernel for every shape (comparison runs)
+static char env_kernel() {
+    const char* env = getenv("GT_GEMM_KERNEL");
+    return env ? env[0] : 0;
+}
+
 int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
     if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.b) & 15)) return -2;
     CUtensorMap ma, mb;
@@ -1037,6 +1045,13 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
         const char* env = getenv("GT_GEMM_KERNEL");
         simple = env && env[0] == 's';                    // "simple": the one-tile-per-CTA kernel (comparison / debugging)
         cudaFuncSetAttribute(gemm_nt_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(PersistentStorage) + 1024));
+    }
+    // short-K products with several column tiles: the A-stationary kernel (one "peer": this GPU) reads every A tile once
+    // instead of once per column tile
+    static const bool a_stationary = !(env_kernel() == 'p');
+    if (!simple && a_stationary && !g.accumulate && g.K <= 512 && g.N > BN) {
+        const void* self[1] = {g.a};
+        return gemm_nt_gather(g, self, 1, g.M, nullptr, s);
     }
     if (simple) {
         dim3 grid((g.N + BN - 1) / BN, (g.M + BM - 1) / BM);

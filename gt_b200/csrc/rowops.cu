@@ -50,10 +50,10 @@ __device__ __forceinline__ void load_z(const T* y, const T* x, const float* ybia
 
 template <typename T, int CPL>
 __global__ void __launch_bounds__(kWarps * 32) ln_fwd_kernel(LayerNormArgs a) {
-    const int row = blockIdx.x * kWarps + (threadIdx.x >> 5);
-    if (row >= a.n) return;
     const int lane = threadIdx.x & 31, nch = a.d >> 3;
     const uint64_t sd = site_seed(a.seed, a.stream_id);
+    // a block walks rows with a grid stride: a few thousand resident blocks instead of one short-lived block per four rows
+    for (int row = blockIdx.x * kWarps + (threadIdx.x >> 5); row < a.n; row += gridDim.x * kWarps) {
     float z[CPL][8], keep[8];
     float sum = 0.f;
 #pragma unroll
@@ -86,6 +86,7 @@ __global__ void __launch_bounds__(kWarps * 32) ln_fwd_kernel(LayerNormArgs a) {
         }
     }
     if (lane == 0 && a.mean_rstd) { a.mean_rstd[2 * row] = mean; a.mean_rstd[2 * row + 1] = rstd; }
+    }
 }
 
 template <typename T, int CPL>
@@ -388,7 +389,8 @@ void pack_cols(const PackColsArgs& a, cudaStream_t s) {
 
 void layer_norm_fwd(const LayerNormArgs& a, cudaStream_t s) {
     if (a.n <= 0) return;
-    const int blocks = (a.n + kWarps - 1) / kWarps;
+    int blocks = (a.n + kWarps - 1) / kWarps;
+    if (blocks > 148 * 16) blocks = 148 * 16;
     // chunks of 8 features per lane: the kernel is instantiated for 1, 2 or 4 so narrow rows do not pay for wide registers
 #define GT_LN_FWD(T)                                                                   \
     do {                                                                               \

@@ -254,3 +254,39 @@ class SymmetricHeap:
             if r != self.rank and p:
                 e.heap_close(p)
         e.heap_free(self.base)
+
+
+def selftest():
+    """``torchrun --nproc-per-node N -m gt_b200.parallel.symm``: heap set-up, IPC mapping, barrier and one collective of
+    each kind against NCCL (the role of the reference's ``gt3d/gt3d/dist/pullcomm/selftest.cu``)."""
+    import os
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    rank, world = dist.get_rank(), dist.get_world_size()
+    heap = SymmetricHeap(dev, 64 << 20)
+    ok = True
+    for rep in range(3):
+        heap.begin_step()
+        x = torch.full((1024, 16), float(rank + rep), device=dev)
+        ref = torch.empty(world * 1024, 16, device=dev)
+        dist.all_gather_into_tensor(ref, x)
+        ok &= bool(torch.equal(heap.all_gather(x, None), ref))
+        y = torch.randn(world * 256, 16, device=dev)
+        ref = torch.empty(256, 16, device=dev)
+        dist.reduce_scatter_tensor(ref, y)
+        ok &= bool((heap.reduce_scatter(y, None) - ref).abs().max() < 1e-4)
+    torch.cuda.synchronize()
+    native.check_status(dev)
+    flag = torch.tensor([int(ok)], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print(f"symmetric heap selftest on {world} GPUs: {'ALL PASSED' if int(flag) else 'FAILED'}", flush=True)
+    dist.barrier()
+    torch.cuda.synchronize()
+    os._exit(0 if int(flag) else 1)
+
+
+if __name__ == "__main__":
+    selftest()
