@@ -1,11 +1,16 @@
 """Measured epoch times the performance model is checked against (never fitted to): one row per run of
 ``bench.py`` / ``train_dist`` on B200, device time, max over ranks.  Add rows as measurements come in."""
 
-ARXIV_CL = dict(name="exphormer_arxiv", n=169_344, e_graph=2_332_486, f_in=128, exp_deg=4, virtual_node=True, classes=40)
+# ``skew``: time of the attention kernels on this graph's blocks over their time on random blocks of the same shape
+# (gt_b200.bench.bench_attention_single_gpu --graph exphormer_arxiv vs --random 169344 4025926): a power-law graph with a
+# global token has hub rows and columns that a uniformly random block does not.
+ARXIV_CL = dict(name="exphormer_arxiv", n=169_344, e_graph=2_332_486, f_in=128, exp_deg=4, virtual_node=True, classes=40, skew=1.3)
 
 MEASURED = [
     # graph, (hidden, heads, layers), grid, transport, measured ms per step
-    dict(graph=ARXIV_CL, model=(256, 8, 4), grid=(1, 1), transport="nccl", ms=43.5),
-    dict(graph=ARXIV_CL, model=(256, 8, 4), grid=(2, 1), transport="nccl", ms=41.9),
-    dict(graph=ARXIV_CL, model=(256, 8, 4), grid=(2, 1), transport="p2p", ms=41.6),
+    dict(graph=ARXIV_CL, model=(256, 8, 4), grid=(1, 1), transport="nccl", ms=38.5),
+    dict(graph=ARXIV_CL, model=(256, 8, 4), grid=(2, 1), transport="nccl", ms=26.0),
+    dict(graph=ARXIV_CL, model=(256, 8, 4), grid=(2, 1), transport="p2p", ms=25.2),
+    dict(graph=ARXIV_CL, model=(256, 8, 4), grid=(2, 2), transport="nccl", ms=23.2),
+    dict(graph=ARXIV_CL, model=(256, 8, 4), grid=(2, 2), transport="p2p", ms=22.1),
 ]

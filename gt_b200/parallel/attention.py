@@ -199,6 +199,52 @@ class _AttnPartial(torch.autograd.Function):
                 dbias.to(ctx.bias_dtype) if dbias is not None and ctx.bias_dtype is not None else None, None)
 
 
+class _AttnPullKV(torch.autograd.Function):
+    """Block attention whose forward kernel reads the K / V rows it needs straight from the owners' memory (receiver-driven
+    pull over NVLink inside the gather loop): the column-group all-gather of K and V does not exist in the forward.
+    Backward gathers K and V once (peer-memory all-gather) for the row and column passes and reduce-scatters dK, dV.
+    Worth it when a tile references few of the block's rows (each needed row crosses the link once per referencing edge)."""
+
+    @staticmethod
+    def forward(ctx, q_blk, k_loc, v_loc, gate, mod):
+        from ..attention import backend_cuda as bc
+        heap, g = mod.heap, mod.grid
+        _, k_tab = heap.publish(k_loc, g.col_group, "pull_k")
+        _, v_tab = heap.publish(v_loc, g.col_group, "pull_v")
+        gate_c = gate.float() if gate is not None else None
+        acc, l, m = bc.attn_fwd_partial_pull(q_blk, k_tab, v_tab, k_loc.shape[0], mod.block.csr, gate_c, None, score=mod.score,
+                                             norm=mod.norm, clamp=mod.clamp, scale=mod.scale)
+        ctx.mod, ctx.gate_dtype = mod, gate.dtype if gate is not None else None
+        ctx.save_for_backward(q_blk, k_loc, v_loc, m, gate_c)
+        ctx.mark_non_differentiable(m)
+        return acc, l, m
+
+    @staticmethod
+    def backward(ctx, dacc, dl, _dm):
+        from ..attention import backend_cuda as bc
+        mod = ctx.mod
+        q_blk, k_loc, v_loc, m, gate_c = ctx.saved_tensors
+        g = mod.grid
+        k_blk, v_blk = raw_all_gather_rows(k_loc, g.col_group), raw_all_gather_rows(v_loc, g.col_group)
+        dq, dk, dv, dgate, _ = bc.attn_bwd_partial(q_blk, k_blk, v_blk, mod.block.csr, gate_c, None, m, dacc.contiguous(), dl.contiguous(),
+                                                   score=mod.score, norm=mod.norm, clamp=mod.clamp, scale=mod.scale)
+        dk = raw_reduce_scatter_rows(dk.to(k_loc.dtype), g.col_group)
+        dv = raw_reduce_scatter_rows(dv.to(v_loc.dtype), g.col_group)
+        return dq.to(q_blk.dtype), dk, dv, (dgate.to(ctx.gate_dtype) if dgate is not None and ctx.gate_dtype is not None else None), None
+
+
+class DistAttentionPullKV(_OpBase):
+    """``q_blk [rows, H, d]`` (gathered over the row group), ``k_loc, v_loc [chunk, H, d]`` (OWNED rows, projected by the
+    owner) -> unnormalised ``(acc, l, m)`` of the block; K / V rows are pulled from peer memory inside the kernel."""
+
+    def __init__(self, grid, block, num_heads, head_dim, heap, score="gated", norm="clampexp", clamp=(-5.0, 5.0)):
+        super().__init__(grid, block, num_heads, head_dim, "cuda", score, norm, clamp, 1e-6)
+        self.heap = heap
+
+    def forward(self, q_blk, k_loc, v_loc, gate=None):
+        return _AttnPullKV.apply(q_blk.contiguous(), k_loc.contiguous(), v_loc.contiguous(), gate, self)
+
+
 class DistAttentionPartial(_OpBase):
     """Unnormalised block attention on gathered operands: ``q [rows, H, d]``, ``k, v [cols, H, d]`` -> ``(acc, l, m)``."""
 

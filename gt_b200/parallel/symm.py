@@ -170,6 +170,16 @@ class SymmetricHeap:
         native.ext().sum_slots(self.view(off, (c.size, chunk, n), torch.bfloat16), out, accumulate)
         return out
 
+    def publish(self, x, group, kind="pub"):
+        """Copy ``x`` into this call site's staging buffer and return ``(offset, int64 device table of the peers' addresses)``
+        after a barrier: every rank of the group may then read every rank's ``x`` in place."""
+        c = self.ctx(group)
+        x = x.contiguous()
+        off = c.staging(x.numel() * x.element_size(), kind)
+        self.view(off, x.shape, x.dtype).copy_(x)
+        c.barrier()
+        return off, self.peer_table_cached(c, off)
+
     def all_reduce(self, x, out, name=None, group=None):
         """``out = sum over ranks of x``; ``x`` should live in the heap (``heap.empty``), otherwise it is staged."""
         c = self.ctx(group)

@@ -89,6 +89,7 @@ class Graph:
     classes: int = 40
     exp_deg: int = 3
     kappa: float = 0.8             # dispersion of the degree distribution (negative binomial); None: Poisson
+    skew: float = 1.0              # sparse-kernel time on this graph's blocks / on random blocks of the same shape (measured)
 
     @property
     def deg_attn(self):
@@ -215,7 +216,7 @@ def _resident(cols, width_bytes):
     return 1.0 if ws <= lo else 0.0 if ws >= hi else (hi - ws) / (hi - lo)
 
 
-def attn_ms(e, rows, cols, heads, d_head, direction):
+def attn_ms(e, rows, cols, heads, d_head, direction, skew=1.0):
     """Gather-attention kernels on a block with ``e`` edges, ``rows`` destination rows, ``cols`` source rows."""
     width = heads * d_head
     scale = width / HW["attn_ref_width"]
@@ -223,13 +224,13 @@ def attn_ms(e, rows, cols, heads, d_head, direction):
     a, b = HW["attn"][direction]["l2"], HW["attn"][direction]["hbm"]
     ce, cr, cc = (w * x + (1 - w) * y for x, y in zip(a, b))
     n_k = 1 if direction == "fwd" else 3
-    return (ce * e + cr * rows + cc * cols) * scale / 1e6 + n_k * HW["kernel_gap_us"] / 1e3
+    return (ce * e * skew + cr * rows + cc * cols) * scale / 1e6 + n_k * HW["kernel_gap_us"] / 1e3
 
 
-def spmm_ms(e, rows, cols, d):
+def spmm_ms(e, rows, cols, d, skew=1.0):
     w = _resident(cols, d * 2)
     ce = w * HW["spmm"]["l2"] + (1 - w) * HW["spmm"]["hbm"]
-    return (ce * e + HW["spmm"]["row_ns"] * rows) * (d / 256.0) / 1e6 + HW["kernel_gap_us"] / 1e3
+    return (ce * e * skew + HW["spmm"]["row_ns"] * rows) * (d / 256.0) / 1e6 + HW["kernel_gap_us"] / 1e3
 
 
 # ----------------------------------------------------------------------------------------------------------------------
@@ -249,14 +250,14 @@ def fused_layer_ms(pd, po, g: Graph, m: Model, gpn=GPUS_PER_NODE):
     f, bw = {}, {}
     f["gather"] = sparse_coll_ms("ag", pl["col"], (C - O) * d * b, sh_c, m) + sparse_coll_ms("ag", pl["row"], (R - O) * d * b, sh_r, m)
     f["gemm"] = gemm_ms(proj, d, 0)
-    f["spmm"] = spmm_ms(eg, R, C, d) if m.with_gcn else 0.0
-    f["attn"] = attn_ms(ea, R, C, H, d // H, "fwd")
+    f["spmm"] = spmm_ms(eg, R, C, d, g.skew) if m.with_gcn else 0.0
+    f["attn"] = attn_ms(ea, R, C, H, d // H, "fwd", g.skew)
     f["combine"] = sparse_coll_ms("rs", pl["row"], (R - O) * w * b, sh_r, m) + (ew_ms(R * w * (4 + b), 1) if po > 1 else 0.0)
     f["tail"] = ew_ms(O * d * a * 10, 3) + gemm_ms(2 * O * d * d * 2 * m.ffn_mult, d, 0)
     bw["tail"] = ew_ms(O * d * a * 16, 4) + gemm_ms(2 * O * d * d * 2 * m.ffn_mult, d, 1) + gemm_ms(2 * O * d * d * 2 * m.ffn_mult, d, 2)
     bw["combine"] = sparse_coll_ms("ag", pl["row"], (R - O) * w * b, sh_r, m)
-    bw["attn"] = attn_ms(ea, R, C, H, d // H, "bwd")
-    bw["spmm"] = spmm_ms(eg, C, R, d) if m.with_gcn else 0.0
+    bw["attn"] = attn_ms(ea, R, C, H, d // H, "bwd", g.skew)
+    bw["spmm"] = spmm_ms(eg, C, R, d, g.skew) if m.with_gcn else 0.0
     bw["gemm"] = gemm_ms(proj, d, 1) + gemm_ms(proj, d, 2)
     bw["dx"] = sparse_coll_ms("rs", pl["col"], (C - O) * d * b, sh_c, m) + sparse_coll_ms("rs", pl["row"], (R - O) * d * b, sh_r, m) \
         + ew_ms((C + R) * d * a * 2 + O * d * a * 3, 3)
@@ -299,8 +300,8 @@ def attn_operator_ms(pd, po, pi, g: Graph, m: Model, family="fused", gpn=GPUS_PE
         ea, w = g.e_attn / P, d + 2 * H
         proj = 2 * d * d * (2 * C + R)
         fwd = sparse_coll_ms("ag", pl["col"], (C - O) * d * b, sh_c, m) + sparse_coll_ms("ag", pl["row"], (R - O) * d * b, sh_r, m) \
-            + gemm_ms(proj, d, 0) + attn_ms(ea, R, C, H, d // H, "fwd") + sparse_coll_ms("rs", pl["row"], (R - O) * w * b, sh_r, m)
-        bwd = sparse_coll_ms("ag", pl["row"], (R - O) * w * b, sh_r, m) + attn_ms(ea, R, C, H, d // H, "bwd") \
+            + gemm_ms(proj, d, 0) + attn_ms(ea, R, C, H, d // H, "fwd", g.skew) + sparse_coll_ms("rs", pl["row"], (R - O) * w * b, sh_r, m)
+        bwd = sparse_coll_ms("ag", pl["row"], (R - O) * w * b, sh_r, m) + attn_ms(ea, R, C, H, d // H, "bwd", g.skew) \
             + gemm_ms(proj, d, 1) + gemm_ms(proj, d, 2) + sparse_coll_ms("rs", pl["col"], (C - O) * d * b, sh_c, m) \
             + sparse_coll_ms("rs", pl["row"], (R - O) * d * b, sh_r, m) + ew_ms((C + R) * d * 4, 2)
         return fwd + bwd
@@ -308,9 +309,9 @@ def attn_operator_ms(pd, po, pi, g: Graph, m: Model, family="fused", gpn=GPUS_PE
     ea, w = g.e_attn / (pd * po), d / pi + 2 * Hs
     a2a = lambda nb: coll_ms("a2a", pl["head"], nb * (1 - 1 / pi)) if pi > 1 else 0.0      # noqa: E731
     fwd = gemm_ms(3 * 2 * O * d * d, d, 0) + 3 * a2a(O * d * b) + 2 * sparse_coll_ms("ag", pl["col"], (Rkv - O * pi) * ds * b, sh_c, m) \
-        + sparse_coll_ms("ag", pl["row"], (Rq - O * pi) * ds * b, sh_r, m) + attn_ms(ea, Rq, Rkv, Hs, d // H, "fwd") \
+        + sparse_coll_ms("ag", pl["row"], (Rq - O * pi) * ds * b, sh_r, m) + attn_ms(ea, Rq, Rkv, Hs, d // H, "fwd", g.skew) \
         + sparse_coll_ms("rs", pl["row"], (Rq - O * pi) * w * b, sh_r, m) + a2a(O * d * b) + ew_ms(O * d * b * 8, 4)
-    bwd = a2a(O * d * b) + sparse_coll_ms("ag", pl["row"], (Rq - O * pi) * w * b, sh_r, m) + attn_ms(ea, Rq, Rkv, Hs, d // H, "bwd") \
+    bwd = a2a(O * d * b) + sparse_coll_ms("ag", pl["row"], (Rq - O * pi) * w * b, sh_r, m) + attn_ms(ea, Rq, Rkv, Hs, d // H, "bwd", g.skew) \
         + sparse_coll_ms("rs", pl["row"], (Rq - O * pi) * ds * b, sh_r, m) + 2 * sparse_coll_ms("rs", pl["col"], (Rkv - O * pi) * ds * b, sh_c, m) \
         + 3 * a2a(O * d * b) + gemm_ms(3 * 2 * O * d * d, d, 1) + gemm_ms(3 * 2 * O * d * d, d, 2) + ew_ms(O * d * b * 8, 4)
     return fwd + bwd
@@ -326,7 +327,7 @@ def head_gcn_ms(pd, po, pi, g: Graph, m: Model, gpn=GPUS_PER_NODE):
     sh_c, sh_r = sparse_share(g, pd), sparse_share(g, po)
     a2a = lambda nb: coll_ms("a2a", pl["head"], nb * (1 - 1 / pi)) if pi > 1 else 0.0      # noqa: E731
     one_way = gemm_ms(2 * O * d * d, d, 0) + a2a(O * d * b) + sparse_coll_ms("ag", pl["col"], (Rkv - O * pi) * ds * b, sh_c, m) \
-        + spmm_ms(eg, Rq, Rkv, ds) + sparse_coll_ms("rs", pl["row"], (Rq - O * pi) * ds * b, sh_r, m) + a2a(O * d * b)
+        + spmm_ms(eg, Rq, Rkv, ds, g.skew) + sparse_coll_ms("rs", pl["row"], (Rq - O * pi) * ds * b, sh_r, m) + a2a(O * d * b)
     return 2 * one_way + gemm_ms(2 * O * d * d, d, 2)
 
 
@@ -356,8 +357,8 @@ def ring_layer_ms(P, g: Graph, m: Model, gpn=GPUS_PER_NODE):
     lay = (min(P, gpn), max(1, P // gpn))
     hop = coll_ms("ag", (2, 1) if lay[1] == 1 else (1, 2), O * d * b, "p2p" if m.transport == "p2p" else "nccl")
     nproj = 3 if m.with_gcn else 2
-    step_f = gemm_ms(2 * O * d * d * nproj, d, 0) + attn_ms(ea, O, O, H, d // H, "fwd") + (spmm_ms(eg, O, O, d) if m.with_gcn else 0.0)
-    step_b = gemm_ms(2 * O * d * d * nproj, d, 0) + attn_ms(ea, O, O, H, d // H, "bwd") + (spmm_ms(eg, O, O, d) if m.with_gcn else 0.0) \
+    step_f = gemm_ms(2 * O * d * d * nproj, d, 0) + attn_ms(ea, O, O, H, d // H, "fwd", g.skew) + (spmm_ms(eg, O, O, d, g.skew) if m.with_gcn else 0.0)
+    step_b = gemm_ms(2 * O * d * d * nproj, d, 0) + attn_ms(ea, O, O, H, d // H, "bwd", g.skew) + (spmm_ms(eg, O, O, d, g.skew) if m.with_gcn else 0.0) \
         + gemm_ms(2 * O * d * d * nproj, d, 1) + gemm_ms(2 * O * d * d * nproj, d, 2) + ew_ms(O * d * 4 * 3, 2)
     fwd = gemm_ms(2 * O * d * d, d, 0) + P * max(step_f, hop) + hop
     bwd = P * max(step_b, 2 * hop) + 2 * hop + gemm_ms(2 * O * d * d, d, 1) + gemm_ms(2 * O * d * d, d, 2)
@@ -388,8 +389,8 @@ def streamed_layer_ms(pd, po, n_sub, g: Graph, m: Model, gpn=GPUS_PER_NODE, over
     nproj = 3 if m.with_gcn else 2
     live = nonempty_fraction(g.deg_attn / (po * n_sub), g.kappa)              # rows of the tile that a sub-block touches
     gat = sparse_coll_ms("ag", pl["col"], cs * (1 - 1 / pd) * d * b, sh_s, m)
-    comp_f = gemm_ms(2 * cs * d * d * nproj, d, 0) + attn_ms(ea, R * live, cs, H, d // H, "fwd") + (spmm_ms(eg, R * live, cs, d) if m.with_gcn else 0.0)
-    comp_b = comp_f + attn_ms(ea, R * live, cs, H, d // H, "bwd") + (spmm_ms(eg, cs, R * live, d) if m.with_gcn else 0.0) \
+    comp_f = gemm_ms(2 * cs * d * d * nproj, d, 0) + attn_ms(ea, R * live, cs, H, d // H, "fwd", g.skew) + (spmm_ms(eg, R * live, cs, d, g.skew) if m.with_gcn else 0.0)
+    comp_b = comp_f + attn_ms(ea, R * live, cs, H, d // H, "bwd", g.skew) + (spmm_ms(eg, cs, R * live, d, g.skew) if m.with_gcn else 0.0) \
         + gemm_ms(2 * cs * d * d * nproj, d, 1) + gemm_ms(2 * cs * d * d * nproj, d, 2)
     rs_sub = sparse_coll_ms("rs", pl["col"], cs * (1 - 1 / pd) * d * b, sh_s, m)
     row = sparse_coll_ms("ag", pl["row"], (R - O) * d * b, sh_r, m) + gemm_ms(2 * R * d * d, d, 0)

@@ -128,6 +128,48 @@ def _fused_gemm_worker(rank, world, store):
     dist.destroy_process_group()
 
 
+def _pull_attention_worker(rank, world, store):
+    """Attention whose kernel pulls K / V rows from the owners' memory vs the gathered-operand operator (forward and backward)."""
+    import torch.distributed as dist
+    from gt_b200.ops import native
+    from gt_b200.parallel import attention as pa
+    from gt_b200.parallel.collectives import all_gather_rows, set_transport
+    from gt_b200.parallel.grid import make_grid
+    from gt_b200.parallel.symm import SymmetricHeap
+    dev = _init(rank, world, store)
+    heap = SymmetricHeap(dev, 256 << 20)
+    set_transport(heap)
+    n, h, d = 4096, 4, 32
+    g = torch.Generator().manual_seed(3)
+    ei = torch.randint(0, n, (2, 40000), generator=g)
+    et = torch.randint(0, 2, (40000,), generator=g)
+    grid = make_grid((world, 1), n, n_pad=n).to(dev)
+    b_ei, b_et = grid.local_block(ei, et)
+    block = pa.AttentionBlock(grid, b_ei.to(dev), b_et.to(dev))
+    torch.manual_seed(rank)
+    q, k, v = (torch.randn(grid.chunk, h, d, device=dev).bfloat16().requires_grad_() for _ in range(3))
+    gate = torch.randn(2, h, d, device=dev, requires_grad=True)
+    ref_op = pa.DistAttentionPartial(grid, block, h, d)
+    pull_op = pa.DistAttentionPullKV(grid, block, h, d, heap)
+    outs = {}
+    for name in ("ref", "pull"):
+        heap.begin_step()
+        if name == "ref":
+            acc, l, m = ref_op(q, all_gather_rows(k, grid.col_group), all_gather_rows(v, grid.col_group), gate)
+        else:
+            acc, l, m = pull_op(q, k, v, gate)
+        ((acc * 0.01).sum() + l.sum()).backward()
+        outs[name] = [t.detach().float().clone() for t in (acc, l, q.grad, k.grad, v.grad, gate.grad)]
+        q.grad = k.grad = v.grad = gate.grad = None
+    for a_, b_ in zip(outs["ref"], outs["pull"]):
+        assert (a_ - b_).abs().max() <= 2e-2 * a_.abs().max() + 1e-4
+    torch.cuda.synchronize()
+    native.check_status(dev)
+    set_transport(None)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def _model_worker(rank, world, store, grid_shape):
     import torch.distributed as dist
     from gt_b200.ops import native
@@ -172,6 +214,11 @@ def test_peer_memory_collectives_match_nccl():
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
 def test_collective_fused_gemms_match_unfused():
     _spawn(_fused_gemm_worker, 2)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_attention_pulling_kv_from_peer_memory():
+    _spawn(_pull_attention_worker, 2)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
