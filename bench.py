@@ -92,8 +92,18 @@ def run_ours(args):
     rank = dist.get_rank()
     heap = None
     if world > 1 and args.comm == "p2p":
+        # the peer-memory transport needs CUDA IPC between the ranks' devices; all ranks fall back to NCCL together if any fails
         from gt_b200.parallel.symm import SymmetricHeap
-        heap = SymmetricHeap(dev, bytes_=args.heap_mb << 20)
+        ok = torch.ones(1, device=dev)
+        try:
+            heap = SymmetricHeap(dev, bytes_=args.heap_mb << 20)
+        except Exception as exc:                             # noqa: BLE001
+            ok.zero_()
+            if rank == 0:
+                print(f"[bench] symmetric heap unavailable ({exc}); using NCCL", file=sys.stderr, flush=True)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if not bool(ok.item()):
+            heap, args.comm = None, "nccl"
     wl = exphormer_workload(WORKLOAD, GRIDS[world], dev, torch.bfloat16, seed=0, heap=heap, scale_down=args.scale_down)
     model, grid = wl["model"], wl["grid"]
     for p in model.parameters():
@@ -203,7 +213,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--comm", default="nccl", choices=["nccl", "p2p"], help="grid collectives: NCCL or the package's peer-memory kernels")
+    ap.add_argument("--comm", default="p2p", choices=["nccl", "p2p"], help="grid collectives: NCCL or the package's peer-memory kernels")
     ap.add_argument("--heap_mb", type=int, default=2048)
     ap.add_argument("--no_graph", action="store_true", help="run the step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--scale_down", type=int, default=1, help="divide the graph size (profiling captures only; invalid as a bench value)")

@@ -278,6 +278,24 @@ __global__ void attn_fwd_combine_kernel(AttnFwdArgs a) {
 // Per row and edge type t the kernel accumulates A_t = sum_{edges of type t} ds_ij k_j.  Then dq_i = scale * sum_t g_t * A_t
 // and the row's contribution to the gate gradient is q_i * scale * A_t: the per-edge work is one FMA set, and the per-type
 // gradients are flushed to shared memory once per row instead of being carried in registers.
+// End of a run of edges of one type in the row pass: dq += g_t * A, the gate gradient of the block += q * A, A = 0.
+template <int CPL>
+__device__ __forceinline__ void flush_type_run(const float* s_gate, float* s_dg, int t, int HD, const int (&foff)[CPL], const float (&qf)[CPL][8],
+                                               float (&A)[CPL][8], float (&dqa)[CPL][8], bool want_dg) {
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) {
+        const float* g = s_gate + t * HD + foff[i];
+#pragma unroll
+        for (int x = 0; x < 8; ++x) dqa[i][x] = fmaf(g[x], A[i][x], dqa[i][x]);
+        if (want_dg) {
+#pragma unroll
+            for (int x = 0; x < 8; ++x) atomicAdd(&s_dg[t * HD + foff[i] + x], qf[i][x] * A[i][x]);
+        }
+#pragma unroll
+        for (int x = 0; x < 8; ++x) A[i][x] = 0.f;
+    }
+}
+
 template <typename T, int CPL, bool GATED>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 4 : 2)) attn_bwd_row_kernel(AttnBwdRowArgs a) {
     extern __shared__ float smem[];
@@ -301,7 +319,6 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 4 : 2)) attn_
     const bool head_writer = (L.ll & (L.lph - 1)) == 0;
     using Raw = typename Vec8<T>::Raw;
     constexpr int U = kUnrollRow;
-    constexpr int NT = GATED ? kMaxTypesReg : 1;
 
     int foff[CPL], head[CPL];
 #pragma unroll
@@ -312,7 +329,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 4 : 2)) attn_
         const int row = c.plan.seg_row[seg], beg = c.plan.seg_beg[seg], end = c.plan.seg_end[seg];
         const int slot = c.plan.seg_slot[seg];
         const long long srow = a.row_map ? a.row_map[row] : row;     // row of q / row_vec / stat / dq
-        float qf[CPL][8], rv[CPL][8], A[NT][CPL][8], db[kMaxTypesReg][CPL], mrow[CPL], rb[CPL], ps[CPL];
+        // A: sum of ds * k over the edges of the CURRENT type run (gated) or of the whole row; dqa: dq accumulated over finished runs
+        float qf[CPL][8], rv[CPL][8], A[CPL][8], dqa[CPL][8], db[kMaxTypesReg][CPL], mrow[CPL], rb[CPL], ps[CPL];
 #pragma unroll
         for (int i = 0; i < CPL; ++i) {
             Vec8<T>::load(q + srow * HD + foff[i], qf[i]);
@@ -322,9 +340,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 4 : 2)) attn_
 #pragma unroll
             for (int x = 0; x < 8; ++x) qf[i][x] *= c.scale;
 #pragma unroll
-            for (int tt = 0; tt < NT; ++tt)
-#pragma unroll
-                for (int x = 0; x < 8; ++x) A[tt][i][x] = 0.f;
+            for (int x = 0; x < 8; ++x) { A[i][x] = 0.f; dqa[i][x] = 0.f; }
 #pragma unroll
             for (int tt = 0; tt < kMaxTypesReg; ++tt) db[tt][i] = 0.f;
         }
@@ -364,7 +380,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 4 : 2)) attn_
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const bool ok = j[u] >= 0;
-                if (GATED && t[u] != gt_cached) {                       // edges of a row are grouped by type: rare reload
+                if (GATED && ok && t[u] != gt_cached) {                 // edges of a row are grouped by type: a run ends (rare)
+                    if (gt_cached >= 0) flush_type_run<CPL>(s_gate, s_dg, gt_cached, HD, foff, qf, A, dqa, want_dg);
                     gt_cached = t[u];
 #pragma unroll
                     for (int i = 0; i < CPL; ++i) {
@@ -401,16 +418,9 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 4 : 2)) attn_
                         mask = (s >= c.lo && s <= c.hi) ? 1.f : 0.f;
                     }
                     const float ds = ok ? p * ps[i] * (dp + rb[i]) * mask : 0.f;
-                    if (GATED) {
 #pragma unroll
-                        for (int tt = 0; tt < NT; ++tt)
-                            if (t[u] == tt) {
-#pragma unroll
-                                for (int x = 0; x < 8; ++x) A[tt][i][x] = fmaf(ds, kf[x], A[tt][i][x]);
-                            }
-                    } else {
-#pragma unroll
-                        for (int x = 0; x < 8; ++x) A[0][i][x] = fmaf(ds, kf[x], A[0][i][x]);
+                    for (int x = 0; x < 8; ++x) A[i][x] = fmaf(ds, kf[x], A[i][x]);
+                    if (!GATED) {
                         if (want_db) {
 #pragma unroll
                             for (int tt = 0; tt < kMaxTypesReg; ++tt)
@@ -420,14 +430,20 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 4 : 2)) attn_
                 }
             }
         }
+        if (GATED) {
+            if (gt_cached >= 0) flush_type_run<CPL>(s_gate, s_dg, gt_cached, HD, foff, qf, A, dqa, want_dg);
+        } else {
+#pragma unroll
+            for (int i = 0; i < CPL; ++i)
+#pragma unroll
+                for (int x = 0; x < 8; ++x) dqa[i][x] = A[i][x];
+        }
         // merge the edge slots of the warp
         for (int off = L.lpr; off < 32; off <<= 1) {
 #pragma unroll
-            for (int tt = 0; tt < NT; ++tt)
+            for (int i = 0; i < CPL; ++i)
 #pragma unroll
-                for (int i = 0; i < CPL; ++i)
-#pragma unroll
-                    for (int x = 0; x < 8; ++x) A[tt][i][x] += __shfl_xor_sync(GT_FULL_MASK, A[tt][i][x], off);
+                for (int x = 0; x < 8; ++x) dqa[i][x] += __shfl_xor_sync(GT_FULL_MASK, dqa[i][x], off);
             if (want_db) {
 #pragma unroll
                 for (int tt = 0; tt < kMaxTypesReg; ++tt)
@@ -440,27 +456,11 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 4 : 2)) attn_
         for (int i = 0; i < CPL; ++i) {
             float dq[8];
 #pragma unroll
-            for (int x = 0; x < 8; ++x) dq[x] = 0.f;
-            if (GATED) {
+            for (int x = 0; x < 8; ++x) dq[x] = dqa[i][x];
+            if (!GATED && want_db && head_writer) {
 #pragma unroll
-                for (int tt = 0; tt < NT; ++tt)
-                    if (tt < c.T) {
-                        const float* g = s_gate + tt * HD + foff[i];
-#pragma unroll
-                        for (int x = 0; x < 8; ++x) dq[x] = fmaf(g[x], A[tt][i][x], dq[x]);
-                        if (want_dg) {
-#pragma unroll
-                            for (int x = 0; x < 8; ++x) atomicAdd(&s_dg[tt * HD + foff[i] + x], qf[i][x] * A[tt][i][x]);
-                        }
-                    }
-            } else {
-#pragma unroll
-                for (int x = 0; x < 8; ++x) dq[x] = A[0][i][x];
-                if (want_db && head_writer) {
-#pragma unroll
-                    for (int tt = 0; tt < kMaxTypesReg; ++tt)
-                        if (tt < c.T) atomicAdd(&s_dg[tt * H + head[i]], db[tt][i]);
-                }
+                for (int tt = 0; tt < kMaxTypesReg; ++tt)
+                    if (tt < c.T) atomicAdd(&s_dg[tt * H + head[i]], db[tt][i]);
             }
 #pragma unroll
             for (int x = 0; x < 8; ++x) dq[x] *= c.scale;

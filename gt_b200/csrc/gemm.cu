@@ -118,6 +118,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// eight fp32 values -> eight bf16 in one 16-byte store; takes the values by value so that the caller's accumulator array never
+// has its address taken (an escaped array is spilled to local memory at every asm statement with a memory clobber)
+__device__ __forceinline__ void st_bf16x8(void* p, float a0, float a1, float a2, float a3, float a4, float a5, float a6, float a7) {
+    uint4 u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+    h[0] = __floats2bfloat162_rn(a0, a1);
+    h[1] = __floats2bfloat162_rn(a2, a3);
+    h[2] = __floats2bfloat162_rn(a4, a5);
+    h[3] = __floats2bfloat162_rn(a6, a7);
+    *reinterpret_cast<uint4*>(p) = u;
+}
+
 // shared-memory matrix descriptor of a 128-byte-swizzled operand tile
 //   K-major : rows of 128 bytes (64 bf16 along K), 8-row groups 1024 bytes apart (SBO), LBO unused (=1)
 //   MN-major: rows of 128 bytes (64 bf16 along M/N), 8 K-rows per 1024-byte group (SBO), 64-element MN blocks LBO bytes apart
@@ -273,13 +285,14 @@ __global__ void __launch_bounds__(kThreads) gemm_nt_kernel(const __grid_constant
                 if (staged) {
                     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(stage + (size_t)lane * kStageStride) + c0;
 #pragma unroll
-                    for (int j = 0; j < 32; j += 8) Vec8<__nv_bfloat16>::store(dst + j, *reinterpret_cast<float(*)[8]>(&v[j]));
+                    for (int j = 0; j < 32; j += 8) st_bf16x8(dst + j, v[j], v[j + 1], v[j + 2], v[j + 3], v[j + 4], v[j + 5], v[j + 6], v[j + 7]);
                     continue;
                 }
                 const bool full = col0 + 32 <= g.N;
                 if (g.c_dtype == DT_BF16) {
                     __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(g.c) + (size_t)row * g.ldc + col0;
-                    for (int j = 0; j < 32 && col0 + j < g.N; ++j) dst[j] = __float2bfloat16(v[j]);
+                    _Pragma("unroll") for (int j = 0; j < 32; ++j)
+                        if (col0 + j < g.N) dst[j] = __float2bfloat16(v[j]);
                 } else {
                     float* dst = static_cast<float*>(g.c) + (size_t)row * g.ldc + col0;
                     if (full && (g.ldc & 3) == 0) {
@@ -293,7 +306,8 @@ __global__ void __launch_bounds__(kThreads) gemm_nt_kernel(const __grid_constant
                             *reinterpret_cast<float4*>(dst + j) = o;
                         }
                     } else {
-                        for (int j = 0; j < 32 && col0 + j < g.N; ++j) dst[j] = g.accumulate ? dst[j] + v[j] : v[j];
+                        _Pragma("unroll") for (int j = 0; j < 32; ++j)
+                            if (col0 + j < g.N) dst[j] = g.accumulate ? dst[j] + v[j] : v[j];
                     }
                 }
             }
@@ -446,12 +460,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nt_persistent_kernel(const _
                 if (staged) {
                     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(stage + (size_t)lane * kStageStrideP) + c0;
 #pragma unroll
-                    for (int j = 0; j < 32; j += 8) Vec8<__nv_bfloat16>::store(dst + j, *reinterpret_cast<float(*)[8]>(&v[j]));
+                    for (int j = 0; j < 32; j += 8) st_bf16x8(dst + j, v[j], v[j + 1], v[j + 2], v[j + 3], v[j + 4], v[j + 5], v[j + 6], v[j + 7]);
                     continue;
                 }
                 if (g.c_dtype == DT_BF16) {
                     __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(g.c) + (size_t)row * g.ldc + col0;
-                    for (int j = 0; j < 32 && col0 + j < g.N; ++j) dst[j] = __float2bfloat16(v[j]);
+                    _Pragma("unroll") for (int j = 0; j < 32; ++j)
+                        if (col0 + j < g.N) dst[j] = __float2bfloat16(v[j]);
                 } else {
                     float* dst = static_cast<float*>(g.c) + (size_t)row * g.ldc + col0;
                     if (col0 + 32 <= g.N && (g.ldc & 3) == 0) {
@@ -465,7 +480,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nt_persistent_kernel(const _
                             *reinterpret_cast<float4*>(dst + j) = o;
                         }
                     } else {
-                        for (int j = 0; j < 32 && col0 + j < g.N; ++j) dst[j] = g.accumulate ? dst[j] + v[j] : v[j];
+                        _Pragma("unroll") for (int j = 0; j < 32; ++j)
+                            if (col0 + j < g.N) dst[j] = g.accumulate ? dst[j] + v[j] : v[j];
                     }
                 }
             }
@@ -513,11 +529,13 @@ constexpr int G_MAX_B = 5;
 struct GatherMaps {
     CUtensorMap a[kMaxPeers];
     CUtensorMap out[kMaxPeers];
+    CUtensorMap c[kMaxPeers];         // result rows of peer p's block, box 32 rows x 64 columns (TMA-store epilogue)
 };
 
 struct GatherCfg {
     int chunk, n_peers, tiles_per_peer, copy_out;
     int nkb, n_abuf, n_b;             // k-blocks per tile, A buffers (1 or 2), B ring stages
+    int tma_store;                    // bf16 result through swizzled shared memory + cp.async.bulk.tensor stores
 };
 
 struct GatherBars {
@@ -649,7 +667,9 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gemm_nt_gather_kernel(const
         const uint64_t sd = site_seed(g.seed, g.stream_id);
         const float inv_keep = g.p > 0.f ? 1.f / (1.f - g.p) : 1.f;
         const bool staged = g.c_dtype == DT_BF16 && (g.ldc & 7) == 0 && (g.N & 7) == 0;
-        uint8_t* stage = stage_c + (size_t)quad * 32 * kStageStrideP;
+        const bool tma_out = cfg.tma_store != 0;
+        // TMA-store path: each warp owns two 32 x 64 boxes (4 KB each, 128-byte rows, 128-byte swizzle) of the staging area
+        uint8_t* stage = tma_out ? stage_c + (size_t)quad * 8192 : stage_c + (size_t)quad * 32 * kStageStrideP;
         int ti = 0;
         bool okay = true;
         for (int mt = blockIdx.x; mt < n_mtiles && okay; mt += gridDim.x) {
@@ -663,6 +683,11 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gemm_nt_gather_kernel(const
                 const int lrow = m0 + quad * 32 + lane;
                 const long long row = row_base + lrow;
                 const uint32_t acc = tmem + (uint32_t)(b * BN) + ((uint32_t)(quad * 32) << 16);
+                if (tma_out) {
+                    // the boxes of the previous tile must have been read by the TMA engine before they are overwritten
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    __syncwarp();
+                }
                 for (int c0 = 0; c0 < BN; c0 += 32) {
                     uint32_t r[32];
                     __syncwarp();
@@ -676,21 +701,40 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gemm_nt_gather_kernel(const
                     if (!staged && (lrow >= cfg.chunk || col0 >= g.N)) continue;
                     float v[32];
                     epilogue_math(r, v, (int)row, col0, g, sd, inv_keep);
+                    if (tma_out) {
+                        uint8_t* box = stage + (c0 >> 6) * 4096 + lane * 128;
+                        const int cbase = (c0 & 63) >> 3;                       // first 16-byte chunk of this 32-column group
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            st_bf16x8(box + (((cbase + j) ^ (lane & 7)) << 4), v[j * 8], v[j * 8 + 1], v[j * 8 + 2], v[j * 8 + 3], v[j * 8 + 4],
+                                      v[j * 8 + 5], v[j * 8 + 6], v[j * 8 + 7]);
+                        continue;
+                    }
                     if (staged) {
                         __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(stage + (size_t)lane * kStageStrideP) + c0;
 #pragma unroll
-                        for (int j = 0; j < 32; j += 8) Vec8<__nv_bfloat16>::store(dst + j, *reinterpret_cast<float(*)[8]>(&v[j]));
+                        for (int j = 0; j < 32; j += 8) st_bf16x8(dst + j, v[j], v[j + 1], v[j + 2], v[j + 3], v[j + 4], v[j + 5], v[j + 6], v[j + 7]);
                         continue;
                     }
                     if (g.c_dtype == DT_BF16) {
                         __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(g.c) + (size_t)row * g.ldc + col0;
-                        for (int j = 0; j < 32 && col0 + j < g.N; ++j) dst[j] = __float2bfloat16(v[j]);
+                        _Pragma("unroll") for (int j = 0; j < 32; ++j)
+                            if (col0 + j < g.N) dst[j] = __float2bfloat16(v[j]);
                     } else {
                         float* dst = static_cast<float*>(g.c) + (size_t)row * g.ldc + col0;
-                        for (int j = 0; j < 32 && col0 + j < g.N; ++j) dst[j] = v[j];
+                        _Pragma("unroll") for (int j = 0; j < 32; ++j)
+                            if (col0 + j < g.N) dst[j] = v[j];
                     }
                 }
-                if (staged) {
+                if (tma_out) {
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the TMA engine
+                    __syncwarp();
+                    if (lane == 0 && m0 + quad * 32 < cfg.chunk) {
+                        if (n0 < g.N) tma_store_2d(&maps.c[peer], stage, n0, m0 + quad * 32);
+                        if (n0 + 64 < g.N) tma_store_2d(&maps.c[peer], stage + 4096, n0 + 64, m0 + quad * 32);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                } else if (staged) {
                     __syncwarp();
                     const int cchunk = lane & 15;
                     const bool col_ok = n0 + cchunk * 8 + 8 <= g.N;
@@ -707,6 +751,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gemm_nt_gather_kernel(const
                 }
             }
         }
+        if (tma_out && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     } else if (warp == 6 && lane == 0 && cfg.copy_out) {
         // ---- copier: the fetched A tile also lands in the local gathered matrix (rows past the chunk are clipped by the map) ----
         int ai = 0;
@@ -828,12 +873,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nt_scatter_kernel(const __gr
                 }
                 __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(stage + (size_t)lane * kStageStrideP) + c0;
 #pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                    float v[8];
-#pragma unroll
-                    for (int q = 0; q < 8; ++q) v[q] = __uint_as_float(r[j + q]);
-                    Vec8<__nv_bfloat16>::store(dst + j, v);
-                }
+                for (int j = 0; j < 32; j += 8)
+                    st_bf16x8(dst + j, __uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]),
+                              __uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]), __uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
             }
             __syncwarp();
             const int cchunk = lane & 15;
@@ -1108,12 +1150,18 @@ int gemm_nt_gather(const GemmArgs& g, const void* const* a_peers, int n_peers, i
     }
     CUtensorMap mb;
     if (!make_map(&mb, g.b, g.N, g.K, g.ldb, BN, BK)) return -1;
+    const bool tma_store = g.c_dtype == DT_BF16 && (g.ldc % 8) == 0 && (g.N % 8) == 0 && (reinterpret_cast<uintptr_t>(g.c) & 15) == 0 &&
+                           ((size_t)chunk * g.ldc * 2) % 16 == 0 && env_kernel() != 'l';      // GT_GEMM_KERNEL=lsu: plain-store epilogue
+    if (tma_store)
+        for (int p = 0; p < n_peers; ++p)
+            if (!make_map(&maps.c[p], static_cast<const __nv_bfloat16*>(g.c) + (size_t)p * chunk * g.ldc, chunk, g.N, g.ldc, 32, 64)) return -1;
     constexpr int kTile = BM * BK * 2;
     const int fixed = 4 * 32 * kStageStrideP + (int)sizeof(GatherBars) + 1024;
     const int slots = (232448 - fixed) / kTile;
     GatherCfg cfg;
     cfg.chunk = chunk; cfg.n_peers = n_peers; cfg.tiles_per_peer = (chunk + BM - 1) / BM; cfg.copy_out = gathered != nullptr;
     cfg.nkb = nkb;
+    cfg.tma_store = tma_store ? 1 : 0;
     cfg.n_abuf = (2 * nkb + 3 <= slots) ? 2 : 1;
     cfg.n_b = slots - cfg.n_abuf * nkb;
     if (cfg.n_b > G_MAX_B) cfg.n_b = G_MAX_B;
