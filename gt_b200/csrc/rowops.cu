@@ -48,55 +48,85 @@ __device__ __forceinline__ void load_z(const T* y, const T* x, const float* ybia
     }
 }
 
+// Rows in flight per warp: a row is one dependent chain (load -> two warp reductions -> store), so bandwidth comes from
+// running several rows' loads at once; narrow rows leave registers for 4 (forward) / 2 (backward) of them.
 template <typename T, int CPL>
 __global__ void __launch_bounds__(kWarps * 32) ln_fwd_kernel(LayerNormArgs a) {
+    constexpr int R = CPL == 1 ? 4 : (CPL == 2 ? 2 : 1);
     const int lane = threadIdx.x & 31, nch = a.d >> 3;
     const uint64_t sd = site_seed(a.seed, a.stream_id);
-    // a block walks rows with a grid stride: a few thousand resident blocks instead of one short-lived block per four rows
-    for (int row = blockIdx.x * kWarps + (threadIdx.x >> 5); row < a.n; row += gridDim.x * kWarps) {
-    float z[CPL][8], keep[8];
-    float sum = 0.f;
+    const int n_warps = gridDim.x * kWarps;
+    for (int row0 = (blockIdx.x * kWarps + (threadIdx.x >> 5)) * R; row0 < a.n; row0 += n_warps * R) {
+        float z[R][CPL][8], sum[R], var[R], mean[R], rstd[R];
 #pragma unroll
-    for (int i = 0; i < CPL; ++i) {
-        int ch = lane + 32 * i;
-        if (ch < nch) {
-            const float inv_l = a.acc ? 1.f / (a.l[(size_t)row * a.H + ((ch << 3) / (a.d / a.H))] + a.eps_l) : 1.f;
-            load_z<T>(static_cast<const T*>(a.y), static_cast<const T*>(a.x), a.ybias, row, a.d, ch << 3, a.p, sd, z[i], keep, a.acc, inv_l);
+        for (int r = 0; r < R; ++r) {
+            sum[r] = 0.f;
+            const int row = row0 + r;
 #pragma unroll
-            for (int k = 0; k < 8; ++k) sum += z[i][k];
+            for (int i = 0; i < CPL; ++i) {
+                const int ch = lane + 32 * i;
+                if (row < a.n && ch < nch) {
+                    float keep[8];
+                    const float inv_l = a.acc ? 1.f / (a.l[(size_t)row * a.H + ((ch << 3) / (a.d / a.H))] + a.eps_l) : 1.f;
+                    load_z<T>(static_cast<const T*>(a.y), static_cast<const T*>(a.x), a.ybias, row, a.d, ch << 3, a.p, sd, z[r][i], keep, a.acc, inv_l);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) sum[r] += z[r][i][k];
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) z[r][i][k] = 0.f;
+                }
+            }
         }
-    }
-    const float mean = warp_sum(sum) / a.d;
-    float var = 0.f;
 #pragma unroll
-    for (int i = 0; i < CPL; ++i)
-        if (lane + 32 * i < nch)
+        for (int r = 0; r < R; ++r) mean[r] = warp_sum(sum[r]) / a.d;
 #pragma unroll
-            for (int k = 0; k < 8; ++k) { float t = z[i][k] - mean; var = fmaf(t, t, var); }
-    const float rstd = rsqrtf(warp_sum(var) / a.d + a.eps);
+        for (int r = 0; r < R; ++r) {
+            var[r] = 0.f;
 #pragma unroll
-    for (int i = 0; i < CPL; ++i) {
-        int ch = lane + 32 * i;
-        if (ch < nch) {
-            int f = ch << 3;
-            float o[8];
+            for (int i = 0; i < CPL; ++i)
+                if (lane + 32 * i < nch)
 #pragma unroll
-            for (int k = 0; k < 8; ++k) o[k] = (z[i][k] - mean) * rstd * a.gamma[f + k] + a.beta[f + k];
-            Vec8<T>::store(static_cast<T*>(a.out) + (size_t)row * a.d + f, o);
+                    for (int k = 0; k < 8; ++k) { const float t = z[r][i][k] - mean[r]; var[r] = fmaf(t, t, var[r]); }
         }
-    }
-    if (lane == 0 && a.mean_rstd) { a.mean_rstd[2 * row] = mean; a.mean_rstd[2 * row + 1] = rstd; }
+#pragma unroll
+        for (int r = 0; r < R; ++r) rstd[r] = rsqrtf(warp_sum(var[r]) / a.d + a.eps);
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) {
+            const int ch = lane + 32 * i;
+            if (ch < nch) {
+                const int f = ch << 3;
+                float gam[8], bet[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) { gam[k] = a.gamma[f + k]; bet[k] = a.beta[f + k]; }
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    if (row0 + r < a.n) {
+                        float o[8];
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) o[k] = (z[r][i][k] - mean[r]) * rstd[r] * gam[k] + bet[k];
+                        Vec8<T>::store(static_cast<T*>(a.out) + (size_t)(row0 + r) * a.d + f, o);
+                    }
+                }
+            }
+        }
+        if (lane == 0 && a.mean_rstd) {
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+                if (row0 + r < a.n) { a.mean_rstd[2 * (row0 + r)] = mean[r]; a.mean_rstd[2 * (row0 + r) + 1] = rstd[r]; }
+        }
     }
 }
 
 template <typename T, int CPL>
 __global__ void __launch_bounds__(kWarps * 32) ln_bwd_kernel(LayerNormBwdArgs a) {
+    constexpr int R = CPL == 1 ? 2 : 1;
     extern __shared__ float smem[];                    // [3][d] block accumulators: dgamma, dbeta, dybias
     const int lane = threadIdx.x & 31, nch = a.d >> 3;
     for (int i = threadIdx.x; i < 3 * a.d; i += blockDim.x) smem[i] = 0.f;
     __syncthreads();
     const uint64_t sd = site_seed(a.seed, a.stream_id);
     const float inv_keep = a.p > 0.f ? 1.f / (1.f - a.p) : 1.f;
+    const int hd = a.acc ? a.d / a.H : a.d;
     float dgam[CPL][8], dbet[CPL][8], dyb[CPL][8];
 #pragma unroll
     for (int i = 0; i < CPL; ++i)
@@ -107,86 +137,99 @@ __global__ void __launch_bounds__(kWarps * 32) ln_bwd_kernel(LayerNormBwdArgs a)
     for (int i = 0; i < CPL; ++i)
 #pragma unroll
         for (int k = 0; k < 8; ++k) gam[i][k] = (lane + 32 * i) < nch ? a.gamma[((lane + 32 * i) << 3) + k] : 0.f;
-    for (int row = blockIdx.x * kWarps + (threadIdx.x >> 5); row < a.n; row += gridDim.x * kWarps) {
-        const float mean = a.mean_rstd[2 * row], rstd = a.mean_rstd[2 * row + 1];
-        float zh[CPL][8], dzh[CPL][8];
-        uint32_t keep_bits[CPL];                       // dropout mask of the lane's chunk, one bit per element
-        float s1 = 0.f, s2 = 0.f;
+    const int n_warps = gridDim.x * kWarps;
+    for (int row0 = (blockIdx.x * kWarps + (threadIdx.x >> 5)) * R; row0 < a.n; row0 += n_warps * R) {
+        float zh[R][CPL][8], dzh[R][CPL][8], rstd[R], s1[R], s2[R], inv_l[R][CPL];
+        uint32_t keep_bits[R][CPL];                    // dropout mask of the lane's chunk, one bit per element
 #pragma unroll
-        for (int i = 0; i < CPL; ++i) {
-            int ch = lane + 32 * i;
-            if (ch < nch) {
-                int f = ch << 3;
-                float z[8], go[8], keep[8];
-                const float inv_l = a.acc ? 1.f / (a.l[(size_t)row * a.H + (f / (a.d / a.H))] + a.eps_l) : 1.f;
-                load_z<T>(static_cast<const T*>(a.y), static_cast<const T*>(a.x), a.ybias, row, a.d, f, a.p, sd, z, keep, a.acc, inv_l);
-                keep_bits[i] = 0u;
-#pragma unroll
-                for (int k = 0; k < 8; ++k) keep_bits[i] |= (keep[k] != 0.f ? 1u : 0u) << k;
-                Vec8<T>::load(static_cast<const T*>(a.dout) + (size_t)row * a.d + f, go);
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    zh[i][k] = (z[k] - mean) * rstd;
-                    dzh[i][k] = go[k] * gam[i][k];
-                    s1 += dzh[i][k];
-                    s2 = fmaf(dzh[i][k], zh[i][k], s2);
-                    dgam[i][k] = fmaf(go[k], zh[i][k], dgam[i][k]);
-                    dbet[i][k] += go[k];
-                }
-            }
-        }
-        s1 = warp_sum(s1) / a.d;
-        s2 = warp_sum(s2) / a.d;
-        float dl_part[CPL];
-#pragma unroll
-        for (int i = 0; i < CPL; ++i) dl_part[i] = 0.f;
-#pragma unroll
-        for (int i = 0; i < CPL; ++i) {
-            int ch = lane + 32 * i;
-            if (ch < nch) {
-                int f = ch << 3;
-                float dz[8], dy[8];
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    dz[k] = rstd * (dzh[i][k] - s1 - zh[i][k] * s2);
-                    dy[k] = ((keep_bits[i] >> k) & 1u) ? dz[k] * inv_keep : 0.f;
-                    dyb[i][k] += dy[k];
-                }
-                if (a.acc) {
-                    // dacc = dy / (l + eps);  dl[head] = -sum_f dy * acc / (l + eps)^2 (summed over the head's lanes below)
-                    const int hd = a.d / a.H;
-                    const float inv_l = 1.f / (a.l[(size_t)row * a.H + f / hd] + a.eps_l);
-                    float av[8], da[8];
-                    Vec8<float>::load(a.acc + (size_t)row * a.d + f, av);
-                    float part = 0.f;
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) { da[k] = dy[k] * inv_l; part = fmaf(dy[k], av[k], part); }
-                    Vec8<float>::store(a.dacc + (size_t)row * a.d + f, da);
-                    dl_part[i] = -part * inv_l * inv_l;
-                } else {
-                    Vec8<T>::store(static_cast<T*>(a.dy) + (size_t)row * a.d + f, dy);
-                }
-                if (a.dx) {
-                    T* dxp = static_cast<T*>(a.dx) + (size_t)row * a.d + f;
-                    if (a.accumulate_dx) {
-                        float old[8];
-                        Vec8<T>::load(dxp, old);
-#pragma unroll
-                        for (int k = 0; k < 8; ++k) dz[k] += old[k];
-                    }
-                    Vec8<T>::store(dxp, dz);
-                }
-            }
-        }
-        if (a.acc) {
-            // a head spans (d / H) / 8 consecutive lanes (a power of two): finish dl with xor shuffles, all lanes take part
-            const int lph = (a.d / a.H) >> 3;
+        for (int r = 0; r < R; ++r) {
+            const int row = row0 + r;
+            const bool live = row < a.n;
+            const float mean = live ? a.mean_rstd[2 * row] : 0.f;
+            rstd[r] = live ? a.mean_rstd[2 * row + 1] : 0.f;
+            s1[r] = 0.f; s2[r] = 0.f;
 #pragma unroll
             for (int i = 0; i < CPL; ++i) {
-                float v = dl_part[i];
-                for (int o = lph >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(GT_FULL_MASK, v, o);
                 const int ch = lane + 32 * i;
-                if (ch < nch && (ch & (lph - 1)) == 0) a.dl[(size_t)row * a.H + (ch << 3) / (a.d / a.H)] = v;
+                keep_bits[r][i] = 0u;
+                inv_l[r][i] = 1.f;
+                if (live && ch < nch) {
+                    const int f = ch << 3;
+                    float z[8], go[8], keep[8];
+                    if (a.acc) inv_l[r][i] = 1.f / (a.l[(size_t)row * a.H + f / hd] + a.eps_l);
+                    load_z<T>(static_cast<const T*>(a.y), static_cast<const T*>(a.x), a.ybias, row, a.d, f, a.p, sd, z, keep, a.acc, inv_l[r][i]);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) keep_bits[r][i] |= (keep[k] != 0.f ? 1u : 0u) << k;
+                    Vec8<T>::load(static_cast<const T*>(a.dout) + (size_t)row * a.d + f, go);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        zh[r][i][k] = (z[k] - mean) * rstd[r];
+                        dzh[r][i][k] = go[k] * gam[i][k];
+                        s1[r] += dzh[r][i][k];
+                        s2[r] = fmaf(dzh[r][i][k], zh[r][i][k], s2[r]);
+                        dgam[i][k] = fmaf(go[k], zh[r][i][k], dgam[i][k]);
+                        dbet[i][k] += go[k];
+                    }
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) { zh[r][i][k] = 0.f; dzh[r][i][k] = 0.f; }
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) { s1[r] = warp_sum(s1[r]) / a.d; s2[r] = warp_sum(s2[r]) / a.d; }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int row = row0 + r;
+            const bool live = row < a.n;
+            float dl_part[CPL];
+#pragma unroll
+            for (int i = 0; i < CPL; ++i) {
+                dl_part[i] = 0.f;
+                const int ch = lane + 32 * i;
+                if (live && ch < nch) {
+                    const int f = ch << 3;
+                    float dz[8], dy[8];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        dz[k] = rstd[r] * (dzh[r][i][k] - s1[r] - zh[r][i][k] * s2[r]);
+                        dy[k] = ((keep_bits[r][i] >> k) & 1u) ? dz[k] * inv_keep : 0.f;
+                        dyb[i][k] += dy[k];
+                    }
+                    if (a.acc) {
+                        // dacc = dy / (l + eps);  dl[head] = -sum_f dy * acc / (l + eps)^2 (summed over the head's lanes below)
+                        float av[8], da[8];
+                        Vec8<float>::load(a.acc + (size_t)row * a.d + f, av);
+                        float part = 0.f;
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) { da[k] = dy[k] * inv_l[r][i]; part = fmaf(dy[k], av[k], part); }
+                        Vec8<float>::store(a.dacc + (size_t)row * a.d + f, da);
+                        dl_part[i] = -part * inv_l[r][i] * inv_l[r][i];
+                    } else {
+                        Vec8<T>::store(static_cast<T*>(a.dy) + (size_t)row * a.d + f, dy);
+                    }
+                    if (a.dx) {
+                        T* dxp = static_cast<T*>(a.dx) + (size_t)row * a.d + f;
+                        if (a.accumulate_dx) {
+                            float old[8];
+                            Vec8<T>::load(dxp, old);
+#pragma unroll
+                            for (int k = 0; k < 8; ++k) dz[k] += old[k];
+                        }
+                        Vec8<T>::store(dxp, dz);
+                    }
+                }
+            }
+            if (a.acc) {
+                // a head spans (d / H) / 8 consecutive lanes (a power of two): finish dl with xor shuffles, all lanes take part
+                const int lph = hd >> 3;
+#pragma unroll
+                for (int i = 0; i < CPL; ++i) {
+                    float v = dl_part[i];
+                    for (int o = lph >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(GT_FULL_MASK, v, o);
+                    const int ch = lane + 32 * i;
+                    if (live && ch < nch && (ch & (lph - 1)) == 0) a.dl[(size_t)row * a.H + (ch << 3) / hd] = v;
+                }
             }
         }
     }
