@@ -241,6 +241,47 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 6 : 3)) attn_
     }
 }
 
+// Sum of column f over the slots [s0, s1) of a scratch area of row width W, computed by a (32, 8) thread block: the 8 thread
+// rows stride over the slots (8 independent loads in flight per column instead of one dependent chain over hundreds of
+// slots of a hub row) and are folded through shared memory in a fixed order.  The result is valid for threadIdx.y == 0.
+__device__ __forceinline__ float tile_slot_sum(const float* scratch, int s0, int s1, int W, int f, bool valid, float (&sm)[8][33]) {
+    float v = 0.f;
+    if (valid)
+        for (int s = s0 + threadIdx.y; s < s1; s += 8) v += scratch[(size_t)s * W + f];
+    __syncthreads();                                    // the previous use of sm is complete
+    sm[threadIdx.y][threadIdx.x] = v;
+    __syncthreads();
+    float t = 0.f;
+    if (threadIdx.y == 0) {
+#pragma unroll
+        for (int y = 0; y < 8; ++y) t += sm[y][threadIdx.x];
+    }
+    return t;
+}
+
+// clamp-exp partials add without rescaling: grid (split rows, 32-column groups of [acc | l]), block (32, 8)
+__global__ void attn_fwd_combine_sum_kernel(AttnFwdArgs a) {
+    __shared__ float sm[8][33];
+    const AttnCommon& c = a.c;
+    const int H = c.H, HD = H * c.D, W = (HD + 2 * H + 3) & ~3;
+    const int r = blockIdx.x;
+    const int row = c.plan.split_rows[r];
+    const long long orow = a.row_map ? a.row_map[row] : row;
+    const int s0 = c.plan.split_ptr[r], s1 = c.plan.split_ptr[r + 1];
+    const int f = blockIdx.y * 32 + threadIdx.x;
+    const float v = tile_slot_sum(c.scratch, s0, s1, W, f, f < HD + H, sm);
+    if (threadIdx.y != 0 || f >= HD + H) return;
+    if (f < HD) {
+        float* dst = a.acc + orow * a.acc_stride + f;
+        *dst = a.accumulate ? *dst + v : v;
+    } else {
+        const int h = f - HD;
+        float* lp = a.l + orow * a.l_stride + h;
+        *lp = a.accumulate ? *lp + v : v;
+        if (a.m) a.m[orow * H + h] = 0.f;
+    }
+}
+
 // merge the slots of the split rows: one block per split row, one thread per feature
 __global__ void attn_fwd_combine_kernel(AttnFwdArgs a) {
     const AttnCommon& c = a.c;
@@ -483,23 +524,23 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 4 : 2)) attn_
     for (int i = threadIdx.x; i < acc_n; i += blockDim.x) part[i] = s_dg[i];
 }
 
-// out[row] (+)= sum of the row's slots
+// out[row] (+)= sum of the row's slots; grid (split rows, 32-column groups), block (32, 8)
 template <typename T>
 __global__ void sum_slots_kernel(const SegPlan plan, const float* scratch, int width, const int* row_map, T* out, float* out_f32,
                                  int accumulate) {
+    __shared__ float sm[8][33];
     const int r = blockIdx.x;
     const int row = plan.split_rows[r];
     const long long orow = row_map ? row_map[row] : row;
     const int s0 = plan.split_ptr[r], s1 = plan.split_ptr[r + 1];
-    for (int f = threadIdx.x; f < width; f += blockDim.x) {
-        float v = 0.f;
-        for (int s = s0; s < s1; ++s) v += scratch[(size_t)s * width + f];
-        if (out_f32) {
-            float* d = out_f32 + orow * width + f;
-            *d = accumulate ? *d + v : v;
-        } else {
-            out[orow * width + f] = from_float<T>(v);
-        }
+    const int f = blockIdx.y * 32 + threadIdx.x;
+    const float v = tile_slot_sum(scratch, s0, s1, width, f, f < width, sm);
+    if (threadIdx.y != 0 || f >= width) return;
+    if (out_f32) {
+        float* d = out_f32 + orow * width + f;
+        *d = accumulate ? *d + v : v;
+    } else {
+        out[orow * width + f] = from_float<T>(v);
     }
 }
 
@@ -652,15 +693,15 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 5 : 2)) attn_
 
 template <typename T>
 __global__ void sum_slots_kv_kernel(const SegPlan plan, const float* scratch, int HD, T* dk, T* dv) {
+    __shared__ float sm[8][33];
     const int r = blockIdx.x;
     const int colj = plan.split_rows[r];
     const int s0 = plan.split_ptr[r], s1 = plan.split_ptr[r + 1];
-    for (int f = threadIdx.x; f < 2 * HD; f += blockDim.x) {
-        float v = 0.f;
-        for (int s = s0; s < s1; ++s) v += scratch[(size_t)s * 2 * HD + f];
-        if (f < HD) dk[(size_t)colj * HD + f] = from_float<T>(v);
-        else dv[(size_t)colj * HD + f - HD] = from_float<T>(v);
-    }
+    const int f = blockIdx.y * 32 + threadIdx.x;
+    const float v = tile_slot_sum(scratch, s0, s1, 2 * HD, f, f < 2 * HD, sm);
+    if (threadIdx.y != 0 || f >= 2 * HD) return;
+    if (f < HD) dk[(size_t)colj * HD + f] = from_float<T>(v);
+    else dv[(size_t)colj * HD + f - HD] = from_float<T>(v);
 }
 
 // out[i] = sum_b part[b, i]: a block owns 32 columns, its 8 thread rows stride over the partial blocks (coalesced
@@ -737,7 +778,12 @@ void attn_fwd(const AttnFwdArgs& a, cudaStream_t s) {
         else          { if (peer) GT_LAUNCH_FWD(float, 2, true); else GT_LAUNCH_FWD(float, 2, false); }
     }
 #undef GT_LAUNCH_FWD
-    if (c.plan.n_split > 0) attn_fwd_combine_kernel<<<c.plan.n_split, 256, 0, s>>>(a);
+    if (c.plan.n_split > 0) {
+        if (c.norm == NORM_CLAMPEXP)
+            attn_fwd_combine_sum_kernel<<<dim3(c.plan.n_split, (c.H * c.D + c.H + 31) / 32), dim3(32, 8), 0, s>>>(a);
+        else
+            attn_fwd_combine_kernel<<<c.plan.n_split, 256, 0, s>>>(a);
+    }
 }
 
 void attn_bwd_row(const AttnBwdRowArgs& a, cudaStream_t s) {
@@ -759,7 +805,7 @@ void attn_bwd_row(const AttnBwdRowArgs& a, cudaStream_t s) {
             attn_bwd_row_kernel<TT, CPL, false><<<blocks, kWarpsPerBlock * 32, sm, s>>>(a);  \
         }                                                                                \
         if (c.plan.n_split > 0)                                                          \
-            sum_slots_kernel<TT><<<c.plan.n_split, 256, 0, s>>>(c.plan, c.scratch, HD, a.row_map,                       \
+            sum_slots_kernel<TT><<<dim3(c.plan.n_split, (HD + 31) / 32), dim3(32, 8), 0, s>>>(c.plan, c.scratch, HD, a.row_map,                       \
                 a.accumulate_dq ? nullptr : static_cast<TT*>(a.dq), a.accumulate_dq ? static_cast<float*>(a.dq) : nullptr, \
                 a.accumulate_dq);                                                        \
     } while (0)
@@ -781,7 +827,7 @@ void attn_bwd_col(const AttnBwdColArgs& a, cudaStream_t s) {
         set_smem(attn_bwd_col_kernel<TT, CPL>, sm);                                      \
         attn_bwd_col_kernel<TT, CPL><<<blocks, kWarpsPerBlock * 32, sm, s>>>(a);         \
         if (c.plan.n_split > 0)                                                          \
-            sum_slots_kv_kernel<TT><<<c.plan.n_split, 256, 0, s>>>(c.plan, c.scratch, HD, static_cast<TT*>(a.dk),       \
+            sum_slots_kv_kernel<TT><<<dim3(c.plan.n_split, (2 * HD + 31) / 32), dim3(32, 8), 0, s>>>(c.plan, c.scratch, HD, static_cast<TT*>(a.dk),       \
                                                                    static_cast<TT*>(a.dv));                              \
     } while (0)
     if (c.dtype == DT_BF16) { if (cpl == 1) GT_LAUNCH_COL(__nv_bfloat16, 1); else GT_LAUNCH_COL(__nv_bfloat16, 2); }
