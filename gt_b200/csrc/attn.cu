@@ -18,6 +18,8 @@
 //
 // Semantics follow the operator specification in gt_b200/attention/ref.py (reference kernels:
 // gt3d/gt3d/attention/triton_kernel.py:38-284, triton_tiled.py:157-479).
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -29,6 +31,14 @@ constexpr int kWarpsPerBlock = 4;
 constexpr int kMaxTypesReg = 4;     // edge types whose gate / bias gradients are kept in registers
 // edge groups in flight per warp (memory-level parallelism)
 constexpr int kUnrollFwd = 2, kUnrollRow = 2, kUnrollCol = 2;
+
+constexpr int kAsyncStages = 4;     // ring depth of the cp.async forward variant
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+template <typename T> __device__ __forceinline__ typename Vec8<T>::Raw as_raw(const uint4& u);
+template <> __device__ __forceinline__ Vec8<__nv_bfloat16>::Raw as_raw<__nv_bfloat16>(const uint4& u) { return u; }
 
 struct Lanes {
     int lpr;     // lanes per feature row
@@ -59,6 +69,10 @@ __device__ __forceinline__ float safe_exp_diff(float a, float b) {   // exp(a - 
     return (a == -INFINITY) ? 0.f : __expf(a - b);
 }
 
+__device__ __forceinline__ int table_floats(const AttnCommon& c) {
+    return (c.score == SCORE_GATED ? c.T * c.H * c.D : 0) + (c.score == SCORE_BIASED ? c.T * c.H : 0);
+}
+
 // shared-memory tables: gate [T, HD] and bias [T, H]
 __device__ __forceinline__ void load_tables(const AttnCommon& c, float* s_gate, float* s_bias) {
     int HD = c.H * c.D;
@@ -72,11 +86,12 @@ __device__ __forceinline__ void load_tables(const AttnCommon& c, float* s_gate, 
 // ------------------------------------------------------------------------------------------------------------------
 // forward
 // ------------------------------------------------------------------------------------------------------------------
-template <typename T, int CPL, bool PEER>
+template <typename T, int CPL, bool PEER, int SPEC = 0>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 6 : 3)) attn_fwd_kernel(AttnFwdArgs a) {
     extern __shared__ float smem[];
     const AttnCommon& c = a.c;
-    const int H = c.H, D = c.D, HD = H * D;
+    // SPEC = 1: 8 heads x 32 (the lane layout and every loop bound become compile-time constants)
+    const int H = SPEC ? 8 : c.H, D = SPEC ? 32 : c.D, HD = H * D;
     float* s_gate = smem;
     float* s_bias = smem + (c.score == SCORE_GATED ? c.T * HD : 0);
     load_tables(c, s_gate, s_bias);
@@ -145,6 +160,183 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 6 : 3)) attn_
                 const int e = base + (U + u) * L.epw + L.sub;
                 jn[u] = e < end ? c.idx[e] : -1;
                 tn[u] = (e < end && c.etype) ? c.etype[e] : 0;
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const bool ok = j[u] >= 0;
+                if (c.score == SCORE_GATED && t[u] != gt_cached) {      // edges of a row are grouped by type: rare reload
+                    gt_cached = t[u];
+#pragma unroll
+                    for (int i = 0; i < CPL; ++i) {
+                        const float* g = s_gate + gt_cached * HD + foff[i];
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) qg[i][x] = qf[i][x] * g[x];
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < CPL; ++i) {
+                    float kf[8], vf[8];
+                    Vec8<T>::unpack(kr[u][i], kf);
+                    float s = 0.f;
+                    if (c.score == SCORE_GATED) {
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) s = fmaf(qg[i][x], kf[x], s);
+                    } else {
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) s = fmaf(qf[i][x], kf[x], s);
+                    }
+                    s = head_sum(s, L.lph);
+                    if (c.score == SCORE_BIASED) s += s_bias[t[u] * H + head[i]];
+                    Vec8<T>::unpack(vr[u][i], vf);
+                    if (softmax) {
+                        const float mn = ok ? fmaxf(m[i], s) : m[i];
+                        const float corr = safe_exp_diff(m[i], mn);
+                        const float p = ok ? __expf(s - mn) : 0.f;
+                        l[i] = l[i] * corr + p;
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) acc[i][x] = fmaf(acc[i][x], corr, p * vf[x]);
+                        m[i] = mn;
+                    } else {
+                        const float p = ok ? __expf(fminf(fmaxf(s, c.lo), c.hi)) : 0.f;
+                        l[i] += p;
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) acc[i][x] = fmaf(p, vf[x], acc[i][x]);
+                    }
+                }
+            }
+        }
+        // merge the edge slots of the warp
+        for (int off = L.lpr; off < 32; off <<= 1) {
+#pragma unroll
+            for (int i = 0; i < CPL; ++i) {
+                const float mo = __shfl_xor_sync(GT_FULL_MASK, m[i], off);
+                const float lo_ = __shfl_xor_sync(GT_FULL_MASK, l[i], off);
+                float wa = 1.f, wb = 1.f;
+                if (softmax) {
+                    const float mn = fmaxf(m[i], mo);
+                    wa = safe_exp_diff(m[i], mn);
+                    wb = safe_exp_diff(mo, mn);
+                    m[i] = mn;
+                }
+                l[i] = l[i] * wa + lo_ * wb;
+#pragma unroll
+                for (int x = 0; x < 8; ++x) {
+                    const float ao = __shfl_xor_sync(GT_FULL_MASK, acc[i][x], off);
+                    acc[i][x] = acc[i][x] * wa + ao * wb;
+                }
+            }
+        }
+        if (L.sub != 0) continue;
+        if (slot < 0) {
+            const long long orow = a.row_map ? a.row_map[row] : row;
+#pragma unroll
+            for (int i = 0; i < CPL; ++i) {
+                float* dst = a.acc + orow * a.acc_stride + foff[i];
+                if (a.accumulate) {
+                    float old[8];
+                    Vec8<float>::load(dst, old);
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) acc[i][x] += old[x];
+                }
+                Vec8<float>::store(dst, acc[i]);
+                if (head_writer) {
+                    float* lp = a.l + orow * a.l_stride + head[i];
+                    *lp = a.accumulate ? *lp + l[i] : l[i];
+                    if (a.m) a.m[orow * H + head[i]] = (m[i] == -INFINITY) ? 0.f : m[i];
+                }
+            }
+        } else {
+            float* sc = c.scratch + (size_t)slot * ((HD + 2 * H + 3) & ~3);
+#pragma unroll
+            for (int i = 0; i < CPL; ++i) {
+                Vec8<float>::store(sc + foff[i], acc[i]);
+                if (head_writer) { sc[HD + head[i]] = l[i]; sc[HD + H + head[i]] = m[i]; }
+            }
+        }
+    }
+}
+
+// Variant of the forward kernel whose K / V gathers go through a per-thread ring in shared memory filled by cp.async: the rows
+// of kAsyncStages - 1 edge groups are in flight per warp without occupying registers (the register variant holds one group).
+// Every lane copies and later reads only its own 16-byte chunks, so no synchronisation between lanes is needed.
+template <typename T, int CPL, int SPEC = 0>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 6 : 3)) attn_fwd_async_kernel(AttnFwdArgs a) {
+    extern __shared__ float smem[];
+    const AttnCommon& c = a.c;
+    // SPEC = 1: 8 heads x 32 (the lane layout and every loop bound become compile-time constants)
+    const int H = SPEC ? 8 : c.H, D = SPEC ? 32 : c.D, HD = H * D;
+    float* s_gate = smem;
+    float* s_bias = smem + (c.score == SCORE_GATED ? c.T * HD : 0);
+    load_tables(c, s_gate, s_bias);
+    // ring: [stage][edge slot u][chunk i][K | V][thread] x 16 bytes, after the tables (16-byte aligned)
+    uint4* ring = reinterpret_cast<uint4*>(smem + ((table_floats(c) + 3) & ~3));
+    constexpr int NST = kAsyncStages;
+    const Lanes L = make_lanes(HD, D);
+    const T* q = static_cast<const T*>(a.q);
+    const T* kb = static_cast<const T*>(a.k);
+    const T* vb = static_cast<const T*>(a.v);
+    const bool softmax = c.norm == NORM_SOFTMAX;
+    const bool head_writer = (L.ll & (L.lph - 1)) == 0;
+    using Raw = typename Vec8<T>::Raw;
+    constexpr int U = kUnrollFwd;
+    int foff[CPL], head[CPL];
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) { foff[i] = (L.ll + L.lpr * i) << 3; head[i] = foff[i] / D; }
+
+    // persistent blocks: the tables are loaded once, warps stride over the segments
+    const int n_warps = gridDim.x * kWarpsPerBlock;
+    for (int seg = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); seg < c.plan.n_seg; seg += n_warps) {
+        const int row = c.plan.seg_row[seg], beg = c.plan.seg_beg[seg], end = c.plan.seg_end[seg];
+        const int slot = c.plan.seg_slot[seg];
+        float qf[CPL][8], acc[CPL][8], l[CPL], m[CPL];
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) {
+            Vec8<T>::load(q + (size_t)row * HD + foff[i], qf[i]);
+#pragma unroll
+            for (int x = 0; x < 8; ++x) { qf[i][x] *= c.scale; acc[i][x] = 0.f; }
+            l[i] = 0.f;
+            m[i] = softmax ? -INFINITY : 0.f;
+        }
+        float qg[CPL][8];                 // q * scale * gate[type] of the type currently cached
+        int gt_cached = -1;
+        const int n_it = (end - beg + U * L.epw - 1) / (U * L.epw);
+        // issue(it): start the copies of group `it` into ring stage it % NST (one commit group per call, also when empty)
+        auto issue = [&](int it) {
+            if (it < n_it) {
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int e = beg + (it * U + u) * L.epw + L.sub;
+                    const int jj = e < end ? c.idx[e] : c.idx[beg];            // padding slots copy a valid row; their weight is zero
+                    const T* kp = kb + (size_t)jj * HD;
+                    const T* vp = vb + (size_t)jj * HD;
+#pragma unroll
+                    for (int i = 0; i < CPL; ++i) {
+                        uint4* dst = ring + ((((it % NST) * U + u) * CPL + i) * 2) * (kWarpsPerBlock * 32) + threadIdx.x;
+                        cp_async16(dst, kp + foff[i]);
+                        cp_async16(dst + kWarpsPerBlock * 32, vp + foff[i]);
+                    }
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+#pragma unroll
+        for (int it = 0; it < NST - 1; ++it) issue(it);
+        for (int it = 0; it < n_it; ++it) {
+            issue(it + NST - 1);
+            asm volatile("cp.async.wait_group %0;" ::"n"(NST - 1) : "memory");
+            int j[U], t[U];
+            Raw kr[U][CPL], vr[U][CPL];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int e = beg + (it * U + u) * L.epw + L.sub;
+                j[u] = e < end ? 0 : -1;
+                t[u] = (e < end && c.etype) ? c.etype[e] : (gt_cached >= 0 ? gt_cached : 0);
+#pragma unroll
+                for (int i = 0; i < CPL; ++i) {
+                    const uint4* src = ring + ((((it % NST) * U + u) * CPL + i) * 2) * (kWarpsPerBlock * 32) + threadIdx.x;
+                    kr[u][i] = as_raw<T>(src[0]);
+                    vr[u][i] = as_raw<T>(src[kWarpsPerBlock * 32]);
+                }
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
@@ -337,11 +529,12 @@ __device__ __forceinline__ void flush_type_run(const float* s_gate, float* s_dg,
     }
 }
 
-template <typename T, int CPL, bool GATED>
+template <typename T, int CPL, bool GATED, int SPEC = 0>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 4 : 2)) attn_bwd_row_kernel(AttnBwdRowArgs a) {
     extern __shared__ float smem[];
     const AttnCommon& c = a.c;
-    const int H = c.H, D = c.D, HD = H * D;
+    // SPEC = 1: 8 heads x 32 (the lane layout and every loop bound become compile-time constants)
+    const int H = SPEC ? 8 : c.H, D = SPEC ? 32 : c.D, HD = H * D;
     float* s_gate = smem;
     float* s_bias = smem + (c.score == SCORE_GATED ? c.T * HD : 0);
     float* s_dg = s_bias + (c.score == SCORE_BIASED ? c.T * H : 0);      // [T, HD] or [T, H] block accumulators
@@ -547,11 +740,12 @@ __global__ void sum_slots_kernel(const SegPlan plan, const float* scratch, int w
 // ------------------------------------------------------------------------------------------------------------------
 // backward, column pass: dK, dV over the CSC (no atomics)
 // ------------------------------------------------------------------------------------------------------------------
-template <typename T, int CPL>
+template <typename T, int CPL, int SPEC = 0>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 5 : 2)) attn_bwd_col_kernel(AttnBwdColArgs a) {
     extern __shared__ float smem[];
     const AttnCommon& c = a.c;
-    const int H = c.H, D = c.D, HD = H * D;
+    // SPEC = 1: 8 heads x 32 (the lane layout and every loop bound become compile-time constants)
+    const int H = SPEC ? 8 : c.H, D = SPEC ? 32 : c.D, HD = H * D;
     float* s_gate = smem;
     float* s_bias = smem + (c.score == SCORE_GATED ? c.T * HD : 0);
     load_tables(c, s_gate, s_bias);
@@ -765,6 +959,28 @@ void attn_fwd(const AttnFwdArgs& a, cudaStream_t s) {
     const size_t sm = table_bytes(c);
     const bool peer = a.k_peers != nullptr;
     const int cpl = cpl_of(c.H, c.D);
+    static const bool use_async = [] { const char* e = getenv("GT_ATTN_ASYNC"); return !(e && e[0] == '0'); }();
+    if (use_async && !peer && c.dtype == DT_BF16) {
+        const size_t ring = (size_t)kAsyncStages * kUnrollFwd * cpl * 2 * kWarpsPerBlock * 32 * 16;
+        const size_t sma = ((sm + 15) & ~size_t(15)) + ring;
+        if (cpl == 1 && c.H == 8 && c.D == 32) {
+            set_smem(attn_fwd_async_kernel<__nv_bfloat16, 1, 1>, sma);
+            attn_fwd_async_kernel<__nv_bfloat16, 1, 1><<<blocks, kWarpsPerBlock * 32, sma, s>>>(a);
+        } else if (cpl == 1) {
+            set_smem(attn_fwd_async_kernel<__nv_bfloat16, 1>, sma);
+            attn_fwd_async_kernel<__nv_bfloat16, 1><<<blocks, kWarpsPerBlock * 32, sma, s>>>(a);
+        } else {
+            set_smem(attn_fwd_async_kernel<__nv_bfloat16, 2>, sma);
+            attn_fwd_async_kernel<__nv_bfloat16, 2><<<blocks, kWarpsPerBlock * 32, sma, s>>>(a);
+        }
+        if (c.plan.n_split > 0) {
+            if (c.norm == NORM_CLAMPEXP)
+                attn_fwd_combine_sum_kernel<<<dim3(c.plan.n_split, (c.H * c.D + c.H + 31) / 32), dim3(32, 8), 0, s>>>(a);
+            else
+                attn_fwd_combine_kernel<<<c.plan.n_split, 256, 0, s>>>(a);
+        }
+        return;
+    }
 #define GT_LAUNCH_FWD(TT, CPL, PEER)                                                     \
     do {                                                                                 \
         set_smem(attn_fwd_kernel<TT, CPL, PEER>, sm);                                    \
@@ -795,11 +1011,11 @@ void attn_bwd_row(const AttnBwdRowArgs& a, cudaStream_t s) {
     if (c.score == SCORE_BIASED && a.dbias_part) sm += (size_t)c.T * c.H * sizeof(float);
     const int cpl = cpl_of(c.H, c.D);
     const int HD = c.H * c.D;
-#define GT_LAUNCH_ROW(TT, CPL)                                                           \
+#define GT_LAUNCH_ROW(TT, CPL, SP)                                                        \
     do {                                                                                 \
         if (c.score == SCORE_GATED) {                                                    \
-            set_smem(attn_bwd_row_kernel<TT, CPL, true>, sm);                            \
-            attn_bwd_row_kernel<TT, CPL, true><<<blocks, kWarpsPerBlock * 32, sm, s>>>(a);   \
+            set_smem(attn_bwd_row_kernel<TT, CPL, true, SP>, sm);                        \
+            attn_bwd_row_kernel<TT, CPL, true, SP><<<blocks, kWarpsPerBlock * 32, sm, s>>>(a);   \
         } else {                                                                         \
             set_smem(attn_bwd_row_kernel<TT, CPL, false>, sm);                           \
             attn_bwd_row_kernel<TT, CPL, false><<<blocks, kWarpsPerBlock * 32, sm, s>>>(a);  \
@@ -809,8 +1025,14 @@ void attn_bwd_row(const AttnBwdRowArgs& a, cudaStream_t s) {
                 a.accumulate_dq ? nullptr : static_cast<TT*>(a.dq), a.accumulate_dq ? static_cast<float*>(a.dq) : nullptr, \
                 a.accumulate_dq);                                                        \
     } while (0)
-    if (c.dtype == DT_BF16) { if (cpl == 1) GT_LAUNCH_ROW(__nv_bfloat16, 1); else GT_LAUNCH_ROW(__nv_bfloat16, 2); }
-    else                    { if (cpl == 1) GT_LAUNCH_ROW(float, 1); else GT_LAUNCH_ROW(float, 2); }
+    const bool spec = c.H == 8 && c.D == 32;
+    if (c.dtype == DT_BF16) {
+        if (cpl == 1 && spec) GT_LAUNCH_ROW(__nv_bfloat16, 1, 1);
+        else if (cpl == 1) GT_LAUNCH_ROW(__nv_bfloat16, 1, 0);
+        else GT_LAUNCH_ROW(__nv_bfloat16, 2, 0);
+    } else {
+        if (cpl == 1) GT_LAUNCH_ROW(float, 1, 0); else GT_LAUNCH_ROW(float, 2, 0);
+    }
 #undef GT_LAUNCH_ROW
 }
 
@@ -822,16 +1044,22 @@ void attn_bwd_col(const AttnBwdColArgs& a, cudaStream_t s) {
     const size_t sm = table_bytes(c);
     const int cpl = cpl_of(c.H, c.D);
     const int HD = c.H * c.D;
-#define GT_LAUNCH_COL(TT, CPL)                                                           \
+#define GT_LAUNCH_COL(TT, CPL, SP)                                                        \
     do {                                                                                 \
-        set_smem(attn_bwd_col_kernel<TT, CPL>, sm);                                      \
-        attn_bwd_col_kernel<TT, CPL><<<blocks, kWarpsPerBlock * 32, sm, s>>>(a);         \
+        set_smem(attn_bwd_col_kernel<TT, CPL, SP>, sm);                                  \
+        attn_bwd_col_kernel<TT, CPL, SP><<<blocks, kWarpsPerBlock * 32, sm, s>>>(a);     \
         if (c.plan.n_split > 0)                                                          \
             sum_slots_kv_kernel<TT><<<dim3(c.plan.n_split, (2 * HD + 31) / 32), dim3(32, 8), 0, s>>>(c.plan, c.scratch, HD, static_cast<TT*>(a.dk),       \
                                                                    static_cast<TT*>(a.dv));                              \
     } while (0)
-    if (c.dtype == DT_BF16) { if (cpl == 1) GT_LAUNCH_COL(__nv_bfloat16, 1); else GT_LAUNCH_COL(__nv_bfloat16, 2); }
-    else                    { if (cpl == 1) GT_LAUNCH_COL(float, 1); else GT_LAUNCH_COL(float, 2); }
+    const bool spec = c.H == 8 && c.D == 32;
+    if (c.dtype == DT_BF16) {
+        if (cpl == 1 && spec) GT_LAUNCH_COL(__nv_bfloat16, 1, 1);
+        else if (cpl == 1) GT_LAUNCH_COL(__nv_bfloat16, 1, 0);
+        else GT_LAUNCH_COL(__nv_bfloat16, 2, 0);
+    } else {
+        if (cpl == 1) GT_LAUNCH_COL(float, 1, 0); else GT_LAUNCH_COL(float, 2, 0);
+    }
 #undef GT_LAUNCH_COL
 }
 
