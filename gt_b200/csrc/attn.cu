@@ -529,7 +529,7 @@ __device__ __forceinline__ void flush_type_run(const float* s_gate, float* s_dg,
     }
 }
 
-template <typename T, int CPL, bool GATED, int SPEC = 0>
+template <typename T, int CPL, bool GATED, int SPEC = 0, bool ASYNC = false>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 4 : 2)) attn_bwd_row_kernel(AttnBwdRowArgs a) {
     extern __shared__ float smem[];
     const AttnCommon& c = a.c;
@@ -553,6 +553,9 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 4 : 2)) attn_
     const bool head_writer = (L.ll & (L.lph - 1)) == 0;
     using Raw = typename Vec8<T>::Raw;
     constexpr int U = kUnrollRow;
+    constexpr int NST = kAsyncStages;
+    // ASYNC: K / V gathers through a per-thread cp.async ring placed after the tables and the block accumulators
+    uint4* ring = reinterpret_cast<uint4*>(smem + ((table_floats(c) + acc_n + 3) & ~3));
 
     int foff[CPL], head[CPL];
 #pragma unroll
@@ -580,36 +583,76 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 4 : 2)) attn_
         }
         float qg[CPL][8];
         int gt_cached = -1;
-        int jn[U], tn[U];
+        const int n_it = (end - beg + U * L.epw - 1) / (U * L.epw);
+        auto issue = [&](int it) {                      // ASYNC: start the copies of edge group `it` (one commit group per call)
+            if (it < n_it) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int e = beg + u * L.epw + L.sub;
-            jn[u] = e < end ? c.idx[e] : -1;
-            tn[u] = (e < end && c.etype) ? c.etype[e] : 0;
-        }
-        for (int base = beg; base < end; base += U * L.epw) {
-            int j[U], t[U];
-            Raw kr[U][CPL], vr[U][CPL];
-#pragma unroll
-            for (int u = 0; u < U; ++u) { j[u] = jn[u]; t[u] = tn[u]; }
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                if (j[u] >= 0) {
+                for (int u = 0; u < U; ++u) {
+                    const int e = beg + (it * U + u) * L.epw + L.sub;
+                    const int jj = e < end ? c.idx[e] : c.idx[beg];            // padding slots copy a valid row; their weight is zero
 #pragma unroll
                     for (int i = 0; i < CPL; ++i) {
-                        kr[u][i] = Vec8<T>::load_raw(kb + (size_t)j[u] * HD + foff[i]);
-                        vr[u][i] = Vec8<T>::load_raw(vb + (size_t)j[u] * HD + foff[i]);
+                        uint4* dst = ring + ((((it % NST) * U + u) * CPL + i) * 2) * (kWarpsPerBlock * 32) + threadIdx.x;
+                        cp_async16(dst, kb + (size_t)jj * HD + foff[i]);
+                        cp_async16(dst + kWarpsPerBlock * 32, vb + (size_t)jj * HD + foff[i]);
                     }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < CPL; ++i) { kr[u][i] = Vec8<T>::zero_raw(); vr[u][i] = Vec8<T>::zero_raw(); }
                 }
             }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        int jn[U], tn[U];
+        if constexpr (ASYNC) {
+#pragma unroll
+            for (int it = 0; it < NST - 1; ++it) issue(it);
+        } else {
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                const int e = base + (U + u) * L.epw + L.sub;
+                const int e = beg + u * L.epw + L.sub;
                 jn[u] = e < end ? c.idx[e] : -1;
                 tn[u] = (e < end && c.etype) ? c.etype[e] : 0;
+            }
+        }
+        for (int it = 0; it < n_it; ++it) {
+            const int base = beg + it * U * L.epw;
+            int j[U], t[U];
+            Raw kr[U][CPL], vr[U][CPL];
+            if constexpr (ASYNC) {
+                issue(it + NST - 1);
+                asm volatile("cp.async.wait_group %0;" ::"n"(NST - 1) : "memory");
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int e = base + u * L.epw + L.sub;
+                    j[u] = e < end ? 0 : -1;
+                    t[u] = (e < end && c.etype) ? c.etype[e] : 0;
+#pragma unroll
+                    for (int i = 0; i < CPL; ++i) {
+                        const uint4* src = ring + ((((it % NST) * U + u) * CPL + i) * 2) * (kWarpsPerBlock * 32) + threadIdx.x;
+                        kr[u][i] = as_raw<T>(src[0]);
+                        vr[u][i] = as_raw<T>(src[kWarpsPerBlock * 32]);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int u = 0; u < U; ++u) { j[u] = jn[u]; t[u] = tn[u]; }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    if (j[u] >= 0) {
+#pragma unroll
+                        for (int i = 0; i < CPL; ++i) {
+                            kr[u][i] = Vec8<T>::load_raw(kb + (size_t)j[u] * HD + foff[i]);
+                            vr[u][i] = Vec8<T>::load_raw(vb + (size_t)j[u] * HD + foff[i]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < CPL; ++i) { kr[u][i] = Vec8<T>::zero_raw(); vr[u][i] = Vec8<T>::zero_raw(); }
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int e = base + (U + u) * L.epw + L.sub;
+                    jn[u] = e < end ? c.idx[e] : -1;
+                    tn[u] = (e < end && c.etype) ? c.etype[e] : 0;
+                }
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
@@ -740,8 +783,8 @@ __global__ void sum_slots_kernel(const SegPlan plan, const float* scratch, int w
 // ------------------------------------------------------------------------------------------------------------------
 // backward, column pass: dK, dV over the CSC (no atomics)
 // ------------------------------------------------------------------------------------------------------------------
-template <typename T, int CPL, int SPEC = 0>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 5 : 2)) attn_bwd_col_kernel(AttnBwdColArgs a) {
+template <typename T, int CPL, int SPEC = 0, bool ASYNC = false>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 4 : 5) : 2)) attn_bwd_col_kernel(AttnBwdColArgs a) {
     extern __shared__ float smem[];
     const AttnCommon& c = a.c;
     // SPEC = 1: 8 heads x 32 (the lane layout and every loop bound become compile-time constants)
@@ -755,6 +798,9 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 5 : 2)) attn_
     const T* rvb = static_cast<const T*>(a.row_vec);
     using Raw = typename Vec8<T>::Raw;
     constexpr int U = kUnrollCol;
+    constexpr int NST = kAsyncStages;
+    // ASYNC: q / row-vector / row-statistics gathers through a per-thread cp.async ring placed after the tables
+    uint4* ring = reinterpret_cast<uint4*>(smem + ((table_floats(c) + 3) & ~3));
     int foff[CPL], head[CPL];
 #pragma unroll
     for (int i = 0; i < CPL; ++i) { foff[i] = (L.ll + L.lpr * i) << 3; head[i] = foff[i] / D; }
@@ -773,41 +819,84 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 5 : 2)) attn_
         }
         float gc[CPL][8], kg[CPL][8];       // cached gate slice and k * gate of the type currently being walked
         int gt_cached = -1;
-        int rn[U], tn[U];
+        const int n_it = (end - beg + U * L.epw - 1) / (U * L.epw);
+        auto issue = [&](int it) {                      // ASYNC: start the copies of entry group `it` (one commit group per call)
+            if (it < n_it) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int e = beg + u * L.epw + L.sub;
-            rn[u] = e < end ? c.idx[e] : -1;
-            tn[u] = (e < end && c.etype) ? c.etype[e] : 0;
-        }
-        for (int base = beg; base < end; base += U * L.epw) {
-            int r[U], t[U];
-            Raw qr[U][CPL], rr[U][CPL];
-            float4 st[U][CPL];
-#pragma unroll
-            for (int u = 0; u < U; ++u) { r[u] = rn[u]; t[u] = tn[u]; }
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                if (r[u] >= 0) {
+                for (int u = 0; u < U; ++u) {
+                    const int e = beg + (it * U + u) * L.epw + L.sub;
+                    const int rr_ = e < end ? c.idx[e] : c.idx[beg];           // padding slots copy a valid row; their weight is zero
 #pragma unroll
                     for (int i = 0; i < CPL; ++i) {
-                        qr[u][i] = Vec8<T>::load_raw(qb + (size_t)r[u] * HD + foff[i]);
-                        rr[u][i] = Vec8<T>::load_raw(rvb + (size_t)r[u] * HD + foff[i]);
-                        st[u][i] = __ldg(a.stat + (size_t)r[u] * H + head[i]);
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < CPL; ++i) {
-                        qr[u][i] = Vec8<T>::zero_raw(); rr[u][i] = Vec8<T>::zero_raw();
-                        st[u][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        uint4* dst = ring + ((((it % NST) * U + u) * CPL + i) * 3) * (kWarpsPerBlock * 32) + threadIdx.x;
+                        cp_async16(dst, qb + (size_t)rr_ * HD + foff[i]);
+                        cp_async16(dst + kWarpsPerBlock * 32, rvb + (size_t)rr_ * HD + foff[i]);
+                        cp_async16(dst + 2 * kWarpsPerBlock * 32, a.stat + (size_t)rr_ * H + head[i]);
                     }
                 }
             }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        int rn[U], tn[U];
+        if constexpr (ASYNC) {
+#pragma unroll
+            for (int it = 0; it < NST - 1; ++it) issue(it);
+        } else {
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                const int e = base + (U + u) * L.epw + L.sub;
+                const int e = beg + u * L.epw + L.sub;
                 rn[u] = e < end ? c.idx[e] : -1;
                 tn[u] = (e < end && c.etype) ? c.etype[e] : 0;
+            }
+        }
+        for (int it = 0; it < n_it; ++it) {
+            const int base = beg + it * U * L.epw;
+            int r[U], t[U];
+            Raw qr[U][CPL], rr[U][CPL];
+            float4 st[U][CPL];
+            if constexpr (ASYNC) {
+                issue(it + NST - 1);
+                asm volatile("cp.async.wait_group %0;" ::"n"(NST - 1) : "memory");
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int e = base + u * L.epw + L.sub;
+                    r[u] = e < end ? 0 : -1;
+                    t[u] = (e < end && c.etype) ? c.etype[e] : (gt_cached >= 0 ? gt_cached : 0);
+#pragma unroll
+                    for (int i = 0; i < CPL; ++i) {
+                        const uint4* src = ring + ((((it % NST) * U + u) * CPL + i) * 3) * (kWarpsPerBlock * 32) + threadIdx.x;
+                        qr[u][i] = as_raw<T>(src[0]);
+                        rr[u][i] = as_raw<T>(src[kWarpsPerBlock * 32]);
+                        const uint4 sv = src[2 * kWarpsPerBlock * 32];
+                        st[u][i] = make_float4(__uint_as_float(sv.x), __uint_as_float(sv.y), __uint_as_float(sv.z), __uint_as_float(sv.w));
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int u = 0; u < U; ++u) { r[u] = rn[u]; t[u] = tn[u]; }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    if (r[u] >= 0) {
+#pragma unroll
+                        for (int i = 0; i < CPL; ++i) {
+                            qr[u][i] = Vec8<T>::load_raw(qb + (size_t)r[u] * HD + foff[i]);
+                            rr[u][i] = Vec8<T>::load_raw(rvb + (size_t)r[u] * HD + foff[i]);
+                            st[u][i] = __ldg(a.stat + (size_t)r[u] * H + head[i]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < CPL; ++i) {
+                            qr[u][i] = Vec8<T>::zero_raw(); rr[u][i] = Vec8<T>::zero_raw();
+                            st[u][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int e = base + (U + u) * L.epw + L.sub;
+                    rn[u] = e < end ? c.idx[e] : -1;
+                    tn[u] = (e < end && c.etype) ? c.etype[e] : 0;
+                }
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
@@ -1011,11 +1100,14 @@ void attn_bwd_row(const AttnBwdRowArgs& a, cudaStream_t s) {
     if (c.score == SCORE_BIASED && a.dbias_part) sm += (size_t)c.T * c.H * sizeof(float);
     const int cpl = cpl_of(c.H, c.D);
     const int HD = c.H * c.D;
-#define GT_LAUNCH_ROW(TT, CPL, SP)                                                        \
+    static const bool use_async = [] { const char* e = getenv("GT_ATTN_ASYNC"); return !(e && e[0] == '0'); }();
+    const size_t ring_bytes = (size_t)kAsyncStages * kUnrollRow * cpl * 2 * kWarpsPerBlock * 32 * 16;
+#define GT_LAUNCH_ROW(TT, CPL, SP, AS)                                                        \
     do {                                                                                 \
         if (c.score == SCORE_GATED) {                                                    \
-            set_smem(attn_bwd_row_kernel<TT, CPL, true, SP>, sm);                        \
-            attn_bwd_row_kernel<TT, CPL, true, SP><<<blocks, kWarpsPerBlock * 32, sm, s>>>(a);   \
+            const size_t smr = AS ? ((sm + 15) & ~size_t(15)) + ring_bytes : sm;         \
+            set_smem(attn_bwd_row_kernel<TT, CPL, true, SP, AS>, smr);                   \
+            attn_bwd_row_kernel<TT, CPL, true, SP, AS><<<blocks, kWarpsPerBlock * 32, smr, s>>>(a);   \
         } else {                                                                         \
             set_smem(attn_bwd_row_kernel<TT, CPL, false>, sm);                           \
             attn_bwd_row_kernel<TT, CPL, false><<<blocks, kWarpsPerBlock * 32, sm, s>>>(a);  \
@@ -1027,11 +1119,13 @@ void attn_bwd_row(const AttnBwdRowArgs& a, cudaStream_t s) {
     } while (0)
     const bool spec = c.H == 8 && c.D == 32;
     if (c.dtype == DT_BF16) {
-        if (cpl == 1 && spec) GT_LAUNCH_ROW(__nv_bfloat16, 1, 1);
-        else if (cpl == 1) GT_LAUNCH_ROW(__nv_bfloat16, 1, 0);
-        else GT_LAUNCH_ROW(__nv_bfloat16, 2, 0);
+        if (cpl == 1 && spec && use_async) GT_LAUNCH_ROW(__nv_bfloat16, 1, 1, true);
+        else if (cpl == 1 && spec) GT_LAUNCH_ROW(__nv_bfloat16, 1, 1, false);
+        else if (cpl == 1 && use_async) GT_LAUNCH_ROW(__nv_bfloat16, 1, 0, true);
+        else if (cpl == 1) GT_LAUNCH_ROW(__nv_bfloat16, 1, 0, false);
+        else GT_LAUNCH_ROW(__nv_bfloat16, 2, 0, false);
     } else {
-        if (cpl == 1) GT_LAUNCH_ROW(float, 1, 0); else GT_LAUNCH_ROW(float, 2, 0);
+        if (cpl == 1) GT_LAUNCH_ROW(float, 1, 0, false); else GT_LAUNCH_ROW(float, 2, 0, false);
     }
 #undef GT_LAUNCH_ROW
 }
@@ -1044,21 +1138,26 @@ void attn_bwd_col(const AttnBwdColArgs& a, cudaStream_t s) {
     const size_t sm = table_bytes(c);
     const int cpl = cpl_of(c.H, c.D);
     const int HD = c.H * c.D;
-#define GT_LAUNCH_COL(TT, CPL, SP)                                                        \
+    static const bool use_async = [] { const char* e = getenv("GT_ATTN_ASYNC"); return !(e && e[0] == '0'); }();
+    const size_t ring_bytes = (size_t)kAsyncStages * kUnrollCol * cpl * 3 * kWarpsPerBlock * 32 * 16;
+#define GT_LAUNCH_COL(TT, CPL, SP, AS)                                                        \
     do {                                                                                 \
-        set_smem(attn_bwd_col_kernel<TT, CPL, SP>, sm);                                  \
-        attn_bwd_col_kernel<TT, CPL, SP><<<blocks, kWarpsPerBlock * 32, sm, s>>>(a);     \
+        const size_t smc = AS ? ((sm + 15) & ~size_t(15)) + ring_bytes : sm;             \
+        set_smem(attn_bwd_col_kernel<TT, CPL, SP, AS>, smc);                             \
+        attn_bwd_col_kernel<TT, CPL, SP, AS><<<blocks, kWarpsPerBlock * 32, smc, s>>>(a); \
         if (c.plan.n_split > 0)                                                          \
             sum_slots_kv_kernel<TT><<<dim3(c.plan.n_split, (2 * HD + 31) / 32), dim3(32, 8), 0, s>>>(c.plan, c.scratch, HD, static_cast<TT*>(a.dk),       \
                                                                    static_cast<TT*>(a.dv));                              \
     } while (0)
     const bool spec = c.H == 8 && c.D == 32;
     if (c.dtype == DT_BF16) {
-        if (cpl == 1 && spec) GT_LAUNCH_COL(__nv_bfloat16, 1, 1);
-        else if (cpl == 1) GT_LAUNCH_COL(__nv_bfloat16, 1, 0);
-        else GT_LAUNCH_COL(__nv_bfloat16, 2, 0);
+        if (cpl == 1 && spec && use_async) GT_LAUNCH_COL(__nv_bfloat16, 1, 1, true);
+        else if (cpl == 1 && spec) GT_LAUNCH_COL(__nv_bfloat16, 1, 1, false);
+        else if (cpl == 1 && use_async) GT_LAUNCH_COL(__nv_bfloat16, 1, 0, true);
+        else if (cpl == 1) GT_LAUNCH_COL(__nv_bfloat16, 1, 0, false);
+        else GT_LAUNCH_COL(__nv_bfloat16, 2, 0, false);
     } else {
-        if (cpl == 1) GT_LAUNCH_COL(float, 1, 0); else GT_LAUNCH_COL(float, 2, 0);
+        if (cpl == 1) GT_LAUNCH_COL(float, 1, 0, false); else GT_LAUNCH_COL(float, 2, 0, false);
     }
 #undef GT_LAUNCH_COL
 }
