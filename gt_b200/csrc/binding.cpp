@@ -159,6 +159,8 @@ void layer_norm_bwd(Tensor dout, Tensor y, OptT x, OptT ybias, Tensor gamma, Ten
     a.dgamma_part = dgamma_part.data_ptr<float>(); a.dbeta_part = dbeta_part.data_ptr<float>();
     a.dybias_part = dybias_part.has_value() && dybias_part->defined() ? dybias_part->data_ptr<float>() : nullptr;
     a.n_blocks = (int)dgamma_part.size(0);
+    a.part_stride = (int)dgamma_part.stride(0);
+    TORCH_CHECK(dbeta_part.stride(0) == dgamma_part.stride(0), "the partial buffers must share one row stride");
     a.n = (int)y.size(0); a.d = (int)y.size(1); a.p = (float)p; a.seed = cptr<long long>(seed); a.stream_id = stream_id;
     a.acc = cptr<float>(acc); a.l = cptr<float>(l); a.H = a.l ? (int)l->size(1) : 1; a.eps_l = (float)eps_l;
     a.dacc = dacc.has_value() && dacc->defined() ? dacc->data_ptr<float>() : nullptr;

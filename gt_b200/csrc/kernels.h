@@ -124,7 +124,8 @@ struct LayerNormBwdArgs {
     void* dy;               // [n, d] dtype (gradient w.r.t. y, dropout mask applied)
     void* dx;               // [n, d] dtype, nullable; accumulate_dx adds dz to it instead of overwriting
     int accumulate_dx;
-    float* dgamma_part; float* dbeta_part; float* dybias_part;   // [n_blocks, d] partials (dybias nullable)
+    float* dgamma_part; float* dbeta_part; float* dybias_part;   // [n_blocks, d] partials, row stride part_stride (dybias nullable)
+    int part_stride;
     int n_blocks;
     int n, d; float p; const long long* seed; long long stream_id;
     // fused attention normalisation (see LayerNormArgs): gradients w.r.t. acc [n, d] and l [n, H] instead of dy

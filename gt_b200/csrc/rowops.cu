@@ -248,9 +248,9 @@ __global__ void __launch_bounds__(kWarps * 32) ln_bwd_kernel(LayerNormBwdArgs a)
     }
     __syncthreads();
     for (int i = threadIdx.x; i < a.d; i += blockDim.x) {
-        a.dgamma_part[(size_t)blockIdx.x * a.d + i] = smem[i];
-        a.dbeta_part[(size_t)blockIdx.x * a.d + i] = smem[a.d + i];
-        if (a.dybias_part) a.dybias_part[(size_t)blockIdx.x * a.d + i] = smem[2 * a.d + i];
+        a.dgamma_part[(size_t)blockIdx.x * a.part_stride + i] = smem[i];
+        a.dbeta_part[(size_t)blockIdx.x * a.part_stride + i] = smem[a.d + i];
+        if (a.dybias_part) a.dybias_part[(size_t)blockIdx.x * a.part_stride + i] = smem[2 * a.d + i];
     }
 }
 

@@ -280,18 +280,15 @@ class _LayerNorm(torch.autograd.Function):
         acc_mode = l is not None
         like = x if acc_mode else y
         nb = e.layer_norm_bwd_blocks(n)
-        parts = torch.empty(3, nb, d, dtype=torch.float32, device=y.device)
+        parts = torch.empty(nb, 3, d, dtype=torch.float32, device=y.device)      # the block partials of all three sums side by side
         dy = torch.empty_like(y)                                  # acc mode: this is dacc (fp32)
         dl = torch.empty_like(l) if acc_mode else None
         dx = torch.empty_like(x) if x is not None else None
-        e.layer_norm_bwd(dout, like if acc_mode else y, x, yb, gamma.float(), stats, like if acc_mode else dy, dx, False, parts[0], parts[1],
-                         parts[2] if has_yb else None, p, rng_state(y.device) if p > 0 else None, site,
+        e.layer_norm_bwd(dout, like if acc_mode else y, x, yb, gamma.float(), stats, like if acc_mode else dy, dx, False, parts[:, 0], parts[:, 1],
+                         parts[:, 2], p, rng_state(y.device) if p > 0 else None, site,
                          y if acc_mode else None, l, eps_l, dy if acc_mode else None, dl)
         red = torch.empty(3, d, dtype=torch.float32, device=y.device)
-        e.reduce_partials(parts[0], red[0])
-        e.reduce_partials(parts[1], red[1])
-        if has_yb:
-            e.reduce_partials(parts[2], red[2])
+        e.reduce_partials(parts.view(nb, 3 * d), red.view(3 * d))                # one reduction for dgamma | dbeta | dybias
         return dy, dx, (red[2].to(pdt) if has_yb else None), red[0].to(gamma.dtype), red[1].to(pdt), None, None, None, dl, None
 
 
