@@ -524,7 +524,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nt_persistent_kernel(const _
 // ------------------------------------------------------------------------------------------------------------------
 constexpr int kMaxPeers = 8;
 constexpr int kGatherThreads = 224;
-constexpr int G_MAX_B = 5;
+constexpr int G_MAX_B = 8;
 
 struct GatherMaps {
     CUtensorMap a[kMaxPeers];
@@ -1162,6 +1162,8 @@ int gemm_nt_gather(const GemmArgs& g, const void* const* a_peers, int n_peers, i
     cfg.chunk = chunk; cfg.n_peers = n_peers; cfg.tiles_per_peer = (chunk + BM - 1) / BM; cfg.copy_out = gathered != nullptr;
     cfg.nkb = nkb;
     cfg.tma_store = tma_store ? 1 : 0;
+    // two A buffers whenever they fit: the fetch of the next row tile overlaps the MMAs of the current one (measured: worth more
+    // than a deeper ring for the weight tiles)
     cfg.n_abuf = (2 * nkb + 3 <= slots) ? 2 : 1;
     cfg.n_b = slots - cfg.n_abuf * nkb;
     if (cfg.n_b > G_MAX_B) cfg.n_b = G_MAX_B;
