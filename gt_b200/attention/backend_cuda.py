@@ -1,8 +1,9 @@
 """Attention back-end on the hand-written sm_100a kernels (``csrc/attn.cu``).
 
 Same contract as :mod:`gt_b200.attention.backend_torch`.  ``q / k / v`` are bf16 or fp32 ``[n, H, d]`` (fp32
-accumulation inside), the partials ``(acc, l, m)`` are fp32.  Shapes the kernels do not tile (a head dim that is not a
-power of two >= 8, ``H * d`` not in {32, 64, 128, 256, 512}, more than 4 edge types) run on the torch-op backend on
+accumulation inside), the partials ``(acc, l, m)`` are fp32.  A head dim that is not a power of two (2 x 40 of the
+GraphGPS recipe) runs on the kernels with zero-padded heads.  Shapes the kernels do not tile even then (``H * d`` not
+in {32, 64, 128, 256, 512}, more than 4 edge types) run on the torch-op backend on
 the same device; that is a shape restriction, not a missing-extension fallback: if the extension is not built, every
 call raises.
 
@@ -28,6 +29,21 @@ def _supported(q, gate, bias):
     h, d = q.shape[1], q.shape[2]
     t = gate.shape[0] if gate is not None else (bias.shape[0] if bias is not None else 1)
     return q.dtype in (torch.bfloat16, torch.float32) and native.ext().attn_shape_supported(h, d, t)
+
+
+def _padded_dim(q, gate, bias):
+    """Head dims that are not a power of two (e.g. 2 x 40) run on the kernels with zero-padded heads: padded K columns add
+    nothing to the scores and padded V columns produce zeros that are sliced away.  Returns the padded dim or None."""
+    h, d = q.shape[1], q.shape[2]
+    dp = max(8, 1 << (d - 1).bit_length())
+    t = gate.shape[0] if gate is not None else (bias.shape[0] if bias is not None else 1)
+    if dp != d and q.dtype in (torch.bfloat16, torch.float32) and native.ext().attn_shape_supported(h, dp, t):
+        return dp
+    return None
+
+
+def _pad(t, dp):
+    return torch.nn.functional.pad(t, (0, dp - t.shape[-1])) if t is not None else None
 
 
 def _cfg(q, score, norm, clamp, scale):
@@ -62,6 +78,11 @@ def _dcsr_plan(blk: BlockCSR, seg_edges):
 
 def attn_fwd_partial(q, k, v, blk: BlockCSR, gate=None, bias=None, *, score="dot", norm="softmax", clamp=(-5.0, 5.0),
                      scale=None, seg_edges=SEG_EDGES, k_peers=None, v_peers=None, rows_per_peer=0):
+    if not _supported(q, gate, bias) and k is not None and _padded_dim(q, gate, bias):
+        dp, d0 = _padded_dim(q, gate, bias), q.shape[-1]
+        acc, l, m = attn_fwd_partial(_pad(q, dp), _pad(k, dp), _pad(v, dp), blk, _pad(gate, dp) if score == "gated" else gate, bias, score=score,
+                                     norm=norm, clamp=clamp, scale=(1.0 / math.sqrt(d0) if scale is None else scale), seg_edges=seg_edges)
+        return acc[..., :d0].contiguous(), l, m
     if not _supported(q, gate, bias):
         acc, l, m = _bt.attn_fwd_partial(q.float(), k.float(), v.float(), blk, gate.float() if gate is not None else None,
                                          bias.float() if bias is not None else None, score=score, norm=norm, clamp=clamp, scale=scale)
@@ -157,6 +178,13 @@ def _bwd(q, k, v, blk, gate, bias, row_vec, stat, score, norm, clamp, scale, seg
 
 def attn_bwd_partial(q, k, v, blk: BlockCSR, gate, bias, m, dacc, dl, *, score="dot", norm="softmax", clamp=(-5.0, 5.0),
                      scale=None, seg_edges=SEG_EDGES):
+    if not _supported(q, gate, bias) and _padded_dim(q, gate, bias):
+        dp, d0 = _padded_dim(q, gate, bias), q.shape[-1]
+        dq, dk, dv, dgate, dbias = attn_bwd_partial(_pad(q, dp), _pad(k, dp), _pad(v, dp), blk, _pad(gate, dp) if score == "gated" else gate, bias, m,
+                                                    _pad(dacc.reshape(q.shape), dp), dl, score=score, norm=norm, clamp=clamp,
+                                                    scale=(1.0 / math.sqrt(d0) if scale is None else scale), seg_edges=seg_edges)
+        return (dq[..., :d0].contiguous(), dk[..., :d0].contiguous(), dv[..., :d0].contiguous(),
+                dgate[..., :d0].contiguous() if dgate is not None else None, dbias)
     if not _supported(q, gate, bias):
         f = lambda t: t.float() if t is not None else None          # noqa: E731
         return _bt.attn_bwd_partial(f(q), f(k), f(v), blk, f(gate), f(bias), f(m), f(dacc), f(dl), score=score, norm=norm,
@@ -167,6 +195,13 @@ def attn_bwd_partial(q, k, v, blk: BlockCSR, gate, bias, m, dacc, dl, *, score="
 
 def attn_bwd(q, k, v, blk: BlockCSR, gate, bias, o, l, m, do, *, score="dot", norm="softmax", clamp=(-5.0, 5.0), eps=1e-6,
              scale=None, seg_edges=SEG_EDGES):
+    if not _supported(q, gate, bias) and _padded_dim(q, gate, bias):
+        dp, d0 = _padded_dim(q, gate, bias), q.shape[-1]
+        dq, dk, dv, dgate, dbias = attn_bwd(_pad(q, dp), _pad(k, dp), _pad(v, dp), blk, _pad(gate, dp) if score == "gated" else gate, bias,
+                                            _pad(o, dp), l, m, _pad(do.reshape(q.shape), dp), score=score, norm=norm, clamp=clamp, eps=eps,
+                                            scale=(1.0 / math.sqrt(d0) if scale is None else scale), seg_edges=seg_edges)
+        return (dq[..., :d0].contiguous(), dk[..., :d0].contiguous(), dv[..., :d0].contiguous(),
+                dgate[..., :d0].contiguous() if dgate is not None else None, dbias)
     if not _supported(q, gate, bias):
         f = lambda t: t.float() if t is not None else None          # noqa: E731
         return _bt.attn_bwd(f(q), f(k), f(v), blk, f(gate), f(bias), f(o), f(l), f(m), f(do), score=score, norm=norm, clamp=clamp,

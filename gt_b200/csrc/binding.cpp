@@ -146,6 +146,31 @@ void layer_norm_fwd(Tensor y, OptT x, OptT ybias, Tensor gamma, Tensor beta, Ten
     gt::layer_norm_fwd(a, stream());
 }
 
+int64_t premp_blocks(int64_t n) { return gt::premp_blocks((int)n); }
+
+void premp_fwd(Tensor h, Tensor gamma, Tensor beta, Tensor out, Tensor stats, double eps, double p, OptT seed, int64_t stream_id, bool l2norm) {
+    c10::cuda::CUDAGuard guard(h.device());
+    check_cuda_contig(h, "h");
+    TORCH_CHECK(h.size(1) % 8 == 0 && h.size(1) <= 1024, "width must be a multiple of 8 and <= 1024");
+    gt::PreMpArgs a{};
+    a.dtype = dt(h); a.h = h.data_ptr(); a.gamma = gamma.data_ptr<float>(); a.beta = beta.data_ptr<float>(); a.out = out.data_ptr();
+    a.stats = stats.data_ptr<float>(); a.n = (int)h.size(0); a.d = (int)h.size(1); a.eps = (float)eps; a.p = (float)p;
+    a.seed = cptr<long long>(seed); a.stream_id = stream_id; a.l2norm = l2norm ? 1 : 0;
+    gt::premp(a, false, stream());
+}
+
+void premp_bwd(Tensor h, Tensor dout, Tensor gamma, Tensor beta, Tensor stats, Tensor dh, Tensor part, double p, OptT seed, int64_t stream_id,
+               bool l2norm) {
+    c10::cuda::CUDAGuard guard(h.device());
+    check_cuda_contig(h, "h"); check_cuda_contig(dout, "dout");
+    gt::PreMpArgs a{};
+    a.dtype = dt(h); a.h = h.data_ptr(); a.dout = dout.data_ptr(); a.gamma = gamma.data_ptr<float>(); a.beta = beta.data_ptr<float>();
+    a.stats = stats.data_ptr<float>(); a.dh = dh.data_ptr(); a.part = part.data_ptr<float>(); a.n_blocks = (int)part.size(0);
+    a.n = (int)h.size(0); a.d = (int)h.size(1); a.p = (float)p; a.seed = cptr<long long>(seed); a.stream_id = stream_id;
+    a.l2norm = l2norm ? 1 : 0;
+    gt::premp(a, true, stream());
+}
+
 int64_t layer_norm_bwd_blocks(int64_t n) { return gt::layer_norm_bwd_blocks((int)n); }
 
 void layer_norm_bwd(Tensor dout, Tensor y, OptT x, OptT ybias, Tensor gamma, Tensor mean_rstd, Tensor dy, OptT dx, bool accumulate_dx,
@@ -431,6 +456,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("sq_norm", &sq_norm);
     m.def("cast_bf16", &cast_bf16);
     m.def("pack_cols", &pack_cols);
+    m.def("premp_blocks", &premp_blocks);
+    m.def("premp_fwd", &premp_fwd);
+    m.def("premp_bwd", &premp_bwd);
     m.def("gemm_nt", &gemm_nt);
     m.def("gemm_tn", &gemm_tn);
     m.def("gemm_nt_gather", &gemm_nt_gather);

@@ -115,6 +115,15 @@ struct LayerNormArgs {
     const float* acc; const float* l; int H; float eps_l;
 };
 void layer_norm_fwd(const LayerNormArgs& a, cudaStream_t s);
+// out = l2normalize(relu(dropout(LayerNorm(h))))  (input stage of the models); stats [n, 3] = mean, rstd, norm
+struct PreMpArgs {
+    int dtype; const void* h; const float* gamma; const float* beta; void* out; float* stats;
+    int n, d; float eps; float p; const long long* seed; long long stream_id; int l2norm;
+    const void* dout; void* dh; float* part; int n_blocks;      // backward: part [n_blocks, 2 d] (dgamma | dbeta)
+};
+int premp_blocks(int n);
+void premp(const PreMpArgs& a, bool backward, cudaStream_t s);
+
 struct LayerNormBwdArgs {
     int dtype;
     const void* dout;       // [n, d]

@@ -254,6 +254,155 @@ __global__ void __launch_bounds__(kWarps * 32) ln_bwd_kernel(LayerNormBwdArgs a)
     }
 }
 
+// Input stage of the models in one pass per direction: out = l2normalize(relu(dropout(LayerNorm(h)))) (dropout AFTER the norm,
+// optional L2 normalisation).  Warp per row; the backward recomputes everything from h and the saved (mean, rstd, norm).
+template <typename T, int CPL>
+__global__ void __launch_bounds__(kWarps * 32) premp_fwd_kernel(PreMpArgs a) {
+    const int lane = threadIdx.x & 31, nch = a.d >> 3;
+    const uint64_t sd = site_seed(a.seed, a.stream_id);
+    const float inv_keep = a.p > 0.f ? 1.f / (1.f - a.p) : 1.f;
+    for (int row = blockIdx.x * kWarps + (threadIdx.x >> 5); row < a.n; row += gridDim.x * kWarps) {
+        float z[CPL][8];
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) {
+            const int ch = lane + 32 * i;
+            if (ch < nch) {
+                Vec8<T>::load(static_cast<const T*>(a.h) + (size_t)row * a.d + (ch << 3), z[i]);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) sum += z[i][k];
+            } else {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) z[i][k] = 0.f;
+            }
+        }
+        const float mean = warp_sum(sum) / a.d;
+        float var = 0.f;
+#pragma unroll
+        for (int i = 0; i < CPL; ++i)
+            if (lane + 32 * i < nch)
+#pragma unroll
+                for (int k = 0; k < 8; ++k) { const float t = z[i][k] - mean; var = fmaf(t, t, var); }
+        const float rstd = rsqrtf(warp_sum(var) / a.d + a.eps);
+        float sq = 0.f;
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) {
+            const int ch = lane + 32 * i;
+            if (ch < nch) {
+                const int f = ch << 3;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    float u = (z[i][k] - mean) * rstd * a.gamma[f + k] + a.beta[f + k];
+                    if (a.p > 0.f) u = uniform01(sd, (uint64_t)row * a.d + f + k) >= a.p ? u * inv_keep : 0.f;
+                    u = fmaxf(u, 0.f);
+                    z[i][k] = u;
+                    sq = fmaf(u, u, sq);
+                }
+            }
+        }
+        const float nrm = a.l2norm ? fmaxf(sqrtf(warp_sum(sq)), 1e-12f) : 1.f;
+        const float inv = 1.f / nrm;
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) {
+            const int ch = lane + 32 * i;
+            if (ch < nch) {
+                float o[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) o[k] = z[i][k] * inv;
+                Vec8<T>::store(static_cast<T*>(a.out) + (size_t)row * a.d + (ch << 3), o);
+            }
+        }
+        if (lane == 0 && a.stats) { a.stats[3 * (size_t)row] = mean; a.stats[3 * (size_t)row + 1] = rstd; a.stats[3 * (size_t)row + 2] = nrm; }
+    }
+}
+
+template <typename T, int CPL>
+__global__ void __launch_bounds__(kWarps * 32) premp_bwd_kernel(PreMpArgs a) {
+    extern __shared__ float smem[];                    // [2][d] block accumulators: dgamma, dbeta
+    const int lane = threadIdx.x & 31, nch = a.d >> 3;
+    for (int i = threadIdx.x; i < 2 * a.d; i += blockDim.x) smem[i] = 0.f;
+    __syncthreads();
+    const uint64_t sd = site_seed(a.seed, a.stream_id);
+    const float inv_keep = a.p > 0.f ? 1.f / (1.f - a.p) : 1.f;
+    float dgam[CPL][8], dbet[CPL][8], gam[CPL][8];
+#pragma unroll
+    for (int i = 0; i < CPL; ++i)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            dgam[i][k] = 0.f; dbet[i][k] = 0.f;
+            gam[i][k] = (lane + 32 * i) < nch ? a.gamma[((lane + 32 * i) << 3) + k] : 0.f;
+        }
+    for (int row = blockIdx.x * kWarps + (threadIdx.x >> 5); row < a.n; row += gridDim.x * kWarps) {
+        const float mean = a.stats[3 * (size_t)row], rstd = a.stats[3 * (size_t)row + 1], nrm = a.stats[3 * (size_t)row + 2];
+        const float inv = nrm > 1e-12f ? 1.f / nrm : 0.f;
+        float zh[CPL][8], go[CPL][8], o[CPL][8], live[CPL][8];
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) {
+            const int ch = lane + 32 * i;
+            if (ch < nch) {
+                const int f = ch << 3;
+                float hv[8];
+                Vec8<T>::load(static_cast<const T*>(a.h) + (size_t)row * a.d + f, hv);
+                Vec8<T>::load(static_cast<const T*>(a.dout) + (size_t)row * a.d + f, go[i]);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    zh[i][k] = (hv[k] - mean) * rstd;
+                    float keep = 1.f;
+                    if (a.p > 0.f) keep = uniform01(sd, (uint64_t)row * a.d + f + k) >= a.p ? inv_keep : 0.f;
+                    const float u = (zh[i][k] * gam[i][k] + a.beta[f + k]) * keep;
+                    live[i][k] = u > 0.f ? keep : 0.f;                            // ReLU gate times the dropout scale
+                    o[i][k] = fmaxf(u, 0.f) * inv;
+                    dot = fmaf(o[i][k], go[i][k], dot);
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) { zh[i][k] = 0.f; go[i][k] = 0.f; o[i][k] = 0.f; live[i][k] = 0.f; }
+            }
+        }
+        if (a.l2norm) dot = warp_sum(dot);
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < CPL; ++i)
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float gr = a.l2norm ? (go[i][k] - o[i][k] * dot) * inv : go[i][k];
+                const float gz = gr * live[i][k];
+                dgam[i][k] = fmaf(gz, zh[i][k], dgam[i][k]);
+                dbet[i][k] += gz;
+                const float dzh = gz * gam[i][k];
+                go[i][k] = dzh;
+                s1 += dzh;
+                s2 = fmaf(dzh, zh[i][k], s2);
+            }
+        s1 = warp_sum(s1) / a.d;
+        s2 = warp_sum(s2) / a.d;
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) {
+            const int ch = lane + 32 * i;
+            if (ch < nch) {
+                float dh[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) dh[k] = rstd * (go[i][k] - s1 - zh[i][k] * s2);
+                Vec8<T>::store(static_cast<T*>(a.dh) + (size_t)row * a.d + (ch << 3), dh);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) {
+        const int ch = lane + 32 * i;
+        if (ch < nch) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                atomicAdd(&smem[(ch << 3) + k], dgam[i][k]);
+                atomicAdd(&smem[a.d + (ch << 3) + k], dbet[i][k]);
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 2 * a.d; i += blockDim.x) a.part[(size_t)blockIdx.x * 2 * a.d + i] = smem[i];
+}
+
 // out = dropout(act(in + bias)) on [n, d] (d % 8 == 0), grid-stride over 8-chunks
 template <typename T>
 __global__ void bias_act_dropout_kernel(const T* in, const float* bias, T* out, long long n_chunks, int d, int act, float p,
@@ -428,6 +577,25 @@ void pack_cols(const PackColsArgs& a, cudaStream_t s) {
     const int blocks = grid_for(chunks, 256);
     if (a.packed_dtype == DT_BF16) pack_cols_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(a);
     else pack_cols_kernel<float><<<blocks, 256, 0, s>>>(a);
+}
+
+int premp_blocks(int n) {
+    int b = grid_for(n, kWarps * 8);
+    return b > 148 * 8 ? 148 * 8 : b;
+}
+
+void premp(const PreMpArgs& a, bool backward, cudaStream_t s) {
+    if (a.n <= 0) return;
+    const int blocks = backward ? a.n_blocks : premp_blocks(a.n) * 2;
+    const size_t sm = backward ? 2 * (size_t)a.d * sizeof(float) : 0;
+#define GT_PREMP(T, CPL)                                                                          \
+    do {                                                                                          \
+        if (backward) premp_bwd_kernel<T, CPL><<<blocks, kWarps * 32, sm, s>>>(a);                \
+        else premp_fwd_kernel<T, CPL><<<blocks, kWarps * 32, 0, s>>>(a);                          \
+    } while (0)
+    if (a.dtype == DT_BF16) { if (a.d <= 256) GT_PREMP(__nv_bfloat16, 1); else if (a.d <= 512) GT_PREMP(__nv_bfloat16, 2); else GT_PREMP(__nv_bfloat16, 4); }
+    else                    { if (a.d <= 256) GT_PREMP(float, 1); else if (a.d <= 512) GT_PREMP(float, 2); else GT_PREMP(float, 4); }
+#undef GT_PREMP
 }
 
 void layer_norm_fwd(const LayerNormArgs& a, cudaStream_t s) {

@@ -625,6 +625,9 @@ class DistExphormer(nn.Module):
 
     def pre_mp(self, x):
         h = K.linear(x, self.pre_lin.weight)
+        if isinstance(self.pre_bn, K.LayerNorm) and K.native_ok(h):
+            # LayerNorm -> dropout -> ReLU -> L2 normalise in one kernel per direction
+            return K.pre_mp(h, self.pre_bn, self.gnn_dropout if self.training else 0.0, self.pre_l2norm)
         h = F.relu(F.dropout(self.pre_bn(h), self.gnn_dropout, self.training))
         return F.normalize(h, p=2, dim=1) if self.pre_l2norm else h
 

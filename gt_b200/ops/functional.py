@@ -135,3 +135,13 @@ def split_columns(x, widths):
     if len(widths) == 1:
         return (x,)
     return _SplitColumns.apply(x, *widths)
+
+
+def native_ok(x):
+    """True when ``x`` takes the native row kernels (CUDA, bf16 / fp32, width a multiple of 8 up to 1024)."""
+    return _use_native(x) and x.dim() == 2 and x.shape[1] % 8 == 0 and x.shape[1] <= 1024
+
+
+def pre_mp(h, norm, p, l2norm=True):
+    """Input stage ``l2normalize(relu(dropout(norm(h))))`` (dropout after the norm) as one native kernel per direction."""
+    return _native().pre_mp(h, norm.weight, norm.bias, norm.eps, p, l2norm)

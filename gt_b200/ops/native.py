@@ -383,3 +383,37 @@ def unpack_columns(packed, widths, dtypes):
     if packed.numel():
         ext().pack_cols(outs, packed, False)
     return outs
+
+
+# ---- input stage: LayerNorm -> dropout -> ReLU -> L2 normalise in one kernel per direction ------------------------------------
+class _PreMp(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h, gamma, beta, eps, p, site, l2norm):
+        h = h.contiguous()
+        out = torch.empty_like(h)
+        stats = torch.empty(h.shape[0], 3, dtype=torch.float32, device=h.device)
+        ext().premp_fwd(h, gamma.float(), beta.float(), out, stats, float(eps), float(p), rng_state(h.device) if p > 0 else None, int(site),
+                        bool(l2norm))
+        ctx.save_for_backward(h, gamma, beta, stats)
+        ctx.cfg = (float(p), int(site), bool(l2norm))
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        h, gamma, beta, stats = ctx.saved_tensors
+        p, site, l2norm = ctx.cfg
+        e = ext()
+        d = h.shape[1]
+        nb = e.premp_blocks(h.shape[0])
+        part = torch.empty(nb, 2 * d, dtype=torch.float32, device=h.device)
+        dh = torch.empty_like(h)
+        e.premp_bwd(h, dout.contiguous(), gamma.float(), beta.float(), stats, dh, part, p, rng_state(h.device) if p > 0 else None, site, l2norm)
+        red = torch.empty(2 * d, dtype=torch.float32, device=h.device)
+        e.reduce_partials(part, red)
+        return dh, red[:d].to(gamma.dtype), red[d:].to(beta.dtype), None, None, None, None
+
+
+def pre_mp(h, gamma, beta, eps, p, l2norm=True):
+    """``l2normalize(relu(dropout(LayerNorm(h))))`` over the last dimension of ``[n, d]`` (d % 8 == 0, d <= 1024)."""
+    site = (gamma.data_ptr() ^ 0x5bd1e995) & 0xFFFFFFFFFF
+    return _PreMp.apply(h, gamma, beta, eps, float(p), site, bool(l2norm))

@@ -259,3 +259,56 @@ def test_pack_and_unpack_columns():
         a2, l2, e2 = native.unpack_columns(packed, [256, 8, 256], [torch.float32, torch.float32, torch.bfloat16])
         assert torch.equal(a2, ref[:, :256].float()) and torch.equal(l2, ref[:, 256:264].float()) and torch.equal(e2, ref[:, 264:].bfloat16())
     native.check_status(DEV)
+
+
+def test_head_dim_40_runs_on_the_kernels_with_padded_heads():
+    """2 heads x 40 (the GraphGPS Exphormer recipe): forward and backward against the edge-list oracle in fp64."""
+    from gt_b200.attention import BlockCSR, masked_sparse_attention_ref
+    from gt_b200.attention.backend_cuda import _padded_dim, masked_sparse_attention_cuda
+    dev = _dev()
+    torch.manual_seed(0)
+    n, h, d, t = 300, 2, 40, 2
+    ei = torch.randint(0, n, (2, 2500))
+    et = torch.randint(0, t, (2500,))
+    q, k, v = (torch.randn(n, h, d, device=dev, requires_grad=True) for _ in range(3))
+    gate = torch.randn(t, h, d, device=dev, requires_grad=True)
+    assert _padded_dim(q, gate, None) == 64
+    blk = BlockCSR.from_edges(ei, n, n, et).to(dev)
+    o = masked_sparse_attention_cuda(q, k, v, blk, gate=gate, score="gated", norm="clampexp")
+    w = torch.randn_like(o)
+    (o * w).sum().backward()
+    leaves = [x.detach().double().cpu().requires_grad_() for x in (q, k, v, gate)]
+    o_ref = masked_sparse_attention_ref(leaves[0], leaves[1], leaves[2], ei, edge_type=et, gate=leaves[3], score="gated", norm="clampexp")
+    (o_ref * w.double().cpu()).sum().backward()
+    assert _rel(o.cpu(), o_ref) < 2e-4
+    for a_, b_ in zip((q, k, v, gate), leaves):
+        assert _rel(a_.grad.cpu(), b_.grad) < 5e-4
+
+
+@pytest.mark.parametrize("l2norm,d", [(True, 256), (False, 128), (True, 512)])
+def test_fused_input_stage_matches_torch(l2norm, d):
+    import torch.nn.functional as F
+    from gt_b200.ops import native
+    dev = _dev()
+    torch.manual_seed(0)
+    n = 777
+    h = torch.randn(n, d, device=dev, requires_grad=True)
+    gamma = (torch.rand(d, device=dev) + 0.5).requires_grad_()
+    beta = (torch.randn(d, device=dev) * 0.1).requires_grad_()
+    w = torch.randn(n, d, device=dev)
+    out = native.pre_mp(h, gamma, beta, 1e-5, 0.0, l2norm)
+    (out * w).sum().backward()
+    got = [out.detach().clone(), h.grad.clone(), gamma.grad.clone(), beta.grad.clone()]
+    h.grad = gamma.grad = beta.grad = None
+    ref = F.relu(F.layer_norm(h, (d,), gamma, beta, 1e-5))
+    ref = F.normalize(ref, p=2, dim=1) if l2norm else ref
+    (ref * w).sum().backward()
+    for a_, b_ in zip(got, (ref.detach(), h.grad, gamma.grad, beta.grad)):
+        assert _rel(a_, b_) < 2e-4
+    # dropout: the backward regenerates the forward's mask (gradient is zero exactly where the output is zero)
+    hb = torch.randn(n, d, device=dev).bfloat16().requires_grad_()
+    ob = native.pre_mp(hb, gamma, beta, 1e-5, 0.3, l2norm)
+    ob.sum().backward()
+    dropped = (ob == 0).float().mean().item()
+    assert 0.55 < dropped < 0.75                                   # ~half by ReLU of what 30 % dropout leaves
+    native.check_status(dev)
