@@ -119,4 +119,28 @@ __device__ __forceinline__ float uniform01(uint64_t seed, uint64_t idx) {
     return (float)(x >> 8) * (1.0f / 16777216.0f);
 }
 
+// Dropout masks are drawn per CHUNK of 8 consecutive elements (flattened index i: chunk i >> 3, byte i & 7): three hash rounds
+// give 8 random bytes, element k is kept iff byte k >= thr.  The drop probability is therefore quantised to thr / 256 and
+// the kept values are scaled by 256 / (256 - thr), so the expectation is exact.  One hash chain per 8 elements instead of
+// one per element: the per-element generator made the row kernels instruction-bound.  Every kernel that applies or
+// regenerates a mask uses these three functions, so forward and backward always agree.
+__device__ __forceinline__ uint32_t drop_threshold(float p) {
+    return p > 0.f ? (uint32_t)fminf(p * 256.f + 0.5f, 255.f) : 0u;
+}
+__device__ __forceinline__ float keep_scale(float p) { return 256.f / (256.f - (float)drop_threshold(p)); }
+__device__ __forceinline__ uint32_t keep_bits8(uint64_t seed, uint64_t chunk, uint32_t thr) {
+    const uint32_t lo = (uint32_t)chunk, hi = (uint32_t)(chunk >> 32);
+    uint32_t x = mix32(lo ^ (uint32_t)seed) + 0x9e3779b9u * (hi + 1u);
+    x = mix32(x ^ (uint32_t)(seed >> 32));
+    const uint32_t y = mix32(x + 0x68bc21ebu);
+    const uint32_t t4 = thr * 0x01010101u;
+    const uint32_t a = __vcmpgeu4(x, t4), b = __vcmpgeu4(y, t4);                 // 0xff in every byte that is kept
+    return (a & 1u) | ((a >> 7) & 2u) | ((a >> 14) & 4u) | ((a >> 21) & 8u) |
+           ((b & 1u) << 4) | ((b >> 3) & 32u) | ((b >> 10) & 64u) | ((b >> 17) & 128u);
+}
+// mask bit of ONE element (slow path for unaligned chunks)
+__device__ __forceinline__ bool keep_element(uint64_t seed, uint64_t idx, uint32_t thr) {
+    return (keep_bits8(seed, idx >> 3, thr) >> (idx & 7)) & 1u;
+}
+
 }  // namespace gt

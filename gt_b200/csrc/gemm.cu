@@ -194,8 +194,18 @@ __device__ __forceinline__ void epilogue_math(const uint32_t (&r)[32], float (&v
     }
     if (g.p > 0.f) {
         const uint64_t base = (uint64_t)row * g.N + col0;
+        const uint32_t thr = drop_threshold(g.p);
+        if ((base & 7) == 0) {                                 // four aligned 8-element chunks: one mask word each
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = uniform01(sd, base + j) >= g.p ? v[j] * inv_keep : 0.f;
+            for (int c8 = 0; c8 < 4; ++c8) {
+                const uint32_t kb = keep_bits8(sd, (base >> 3) + c8, thr);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v[c8 * 8 + k] = ((kb >> k) & 1u) ? v[c8 * 8 + k] * inv_keep : 0.f;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = keep_element(sd, base + j, thr) ? v[j] * inv_keep : 0.f;
+        }
     }
 }
 
@@ -268,7 +278,7 @@ __global__ void __launch_bounds__(kThreads) gemm_nt_kernel(const __grid_constant
             const int quad = warp & 3;                     // TMEM lanes [32 * quad, 32 * quad + 32)
             const int row = m0 + quad * 32 + lane;
             const uint64_t sd = site_seed(g.seed, g.stream_id);
-            const float inv_keep = g.p > 0.f ? 1.f / (1.f - g.p) : 1.f;
+            const float inv_keep = g.p > 0.f ? keep_scale(g.p) : 1.f;
             // bf16 results of full-width-aligned tiles go through shared memory (the pipeline stages are free once the
             // accumulator is complete) so that global stores are whole 256-byte row segments instead of one row per lane
             const bool staged = g.c_dtype == DT_BF16 && (g.ldc & 7) == 0 && (g.N & 7) == 0;
@@ -432,7 +442,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nt_persistent_kernel(const _
         // ---- epilogue ----
         const int quad = warp & 3;
         const uint64_t sd = site_seed(g.seed, g.stream_id);
-        const float inv_keep = g.p > 0.f ? 1.f / (1.f - g.p) : 1.f;
+        const float inv_keep = g.p > 0.f ? keep_scale(g.p) : 1.f;
         const bool staged = g.c_dtype == DT_BF16 && (g.ldc & 7) == 0 && (g.N & 7) == 0;
         uint8_t* stage = sh.stage_c + (size_t)quad * 32 * kStageStrideP;
         int ti = 0;
@@ -665,7 +675,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gemm_nt_gather_kernel(const
         // ---- epilogue ----
         const int quad = warp & 3;
         const uint64_t sd = site_seed(g.seed, g.stream_id);
-        const float inv_keep = g.p > 0.f ? 1.f / (1.f - g.p) : 1.f;
+        const float inv_keep = g.p > 0.f ? keep_scale(g.p) : 1.f;
         const bool staged = g.c_dtype == DT_BF16 && (g.ldc & 7) == 0 && (g.N & 7) == 0;
         const bool tma_out = cfg.tma_store != 0;
         // TMA-store path: each warp owns two 32 x 64 boxes (4 KB each, 128-byte rows, 128-byte swizzle) of the staging area

@@ -2,6 +2,8 @@
 // dropout epilogues, masked cross-entropy forward + backward, multi-tensor AdamW with global-norm clipping, casts.
 // One warp per row, 16-byte vector accesses, fp32 arithmetic; per-block partial sums for the parameter gradients are
 // written to a [n_blocks, d] buffer and folded by reduce_partials (deterministic, no global atomics).
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -33,11 +35,12 @@ __device__ __forceinline__ void load_z(const T* y, const T* x, const float* ybia
     } else {
         Vec8<T>::load(y + row * d + f, yv);
     }
-    const float inv = p > 0.f ? 1.f / (1.f - p) : 1.f;
+    const float inv = p > 0.f ? keep_scale(p) : 1.f;
+    const uint32_t kb = p > 0.f ? keep_bits8(sd, (row * d + f) >> 3, drop_threshold(p)) : 0xffu;
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
         if (ybias) yv[k] += ybias[f + k];
-        keep[k] = (p > 0.f) ? (uniform01(sd, row * d + f + k) >= p ? inv : 0.f) : 1.f;
+        keep[k] = ((kb >> k) & 1u) ? inv : 0.f;
         z[k] = yv[k] * keep[k];
     }
     if (x) {
@@ -125,7 +128,7 @@ __global__ void __launch_bounds__(kWarps * 32) ln_bwd_kernel(LayerNormBwdArgs a)
     for (int i = threadIdx.x; i < 3 * a.d; i += blockDim.x) smem[i] = 0.f;
     __syncthreads();
     const uint64_t sd = site_seed(a.seed, a.stream_id);
-    const float inv_keep = a.p > 0.f ? 1.f / (1.f - a.p) : 1.f;
+    const float inv_keep = a.p > 0.f ? keep_scale(a.p) : 1.f;
     const int hd = a.acc ? a.d / a.H : a.d;
     float dgam[CPL][8], dbet[CPL][8], dyb[CPL][8];
 #pragma unroll
@@ -254,13 +257,273 @@ __global__ void __launch_bounds__(kWarps * 32) ln_bwd_kernel(LayerNormBwdArgs a)
     }
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// LayerNorm kernels for rows of up to 256 bf16 features whose operands arrive through a per-thread cp.async ring in shared
+// memory: a warp keeps the loads of kLnStages - 1 future rows in flight without holding them in registers (a row is a
+// dependent chain of load -> two warp reductions -> store, so bandwidth comes only from rows in flight).  Every lane copies and
+// later reads only its own chunks: no synchronisation between lanes.  Same arithmetic as ln_fwd_kernel / ln_bwd_kernel.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int kLnStages = 8;
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_8(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_4(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void unpack_bf16x8(const uint4& u, float (&f)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 x = __bfloat1622float2(h[i]); f[2 * i] = x.x; f[2 * i + 1] = x.y; }
+}
+
+// ring layout per block: uint4 [stage][slot][thread] followed by float2 [stage][thread] (mean, rstd) and float [stage][thread] (l)
+template <bool ACC, bool BWD>
+struct LnRing {
+    static constexpr int kSlots = (ACC ? 2 : 1) + 1 + (BWD ? 1 : 0);            // y (or acc lo / hi), x, dout
+    static constexpr int kThreads = kWarps * 32;
+    static constexpr size_t kBytes = (size_t)kLnStages * kThreads * (kSlots * 16 + 8 + 4);
+    uint4* data; float2* stat; float* lv;
+    __device__ LnRing(uint8_t* base) {
+        data = reinterpret_cast<uint4*>(base);
+        stat = reinterpret_cast<float2*>(base + (size_t)kLnStages * kThreads * kSlots * 16);
+        lv = reinterpret_cast<float*>(base + (size_t)kLnStages * kThreads * (kSlots * 16 + 8));
+    }
+    __device__ uint4* slot(int stage, int s) const { return data + ((size_t)stage * kSlots + s) * kThreads + threadIdx.x; }
+};
+
+template <bool ACC>
+__global__ void __launch_bounds__(kWarps * 32) ln_fwd_ring_kernel(LayerNormArgs a) {
+    extern __shared__ __align__(16) uint8_t ring_raw[];
+    using Ring = LnRing<ACC, false>;
+    Ring ring(ring_raw);
+    constexpr int NS = kLnStages, SX = ACC ? 2 : 1;
+    const int lane = threadIdx.x & 31, nch = a.d >> 3, f = lane << 3;
+    const bool active = lane < nch;
+    const uint64_t sd = site_seed(a.seed, a.stream_id);
+    const float inv_keep = a.p > 0.f ? keep_scale(a.p) : 1.f;
+    const int hd = ACC ? a.d / a.H : a.d;
+    const __nv_bfloat16* yb16 = static_cast<const __nv_bfloat16*>(a.y);
+    const __nv_bfloat16* xb16 = static_cast<const __nv_bfloat16*>(a.x);
+    float gam[8], bet[8], ybv[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        gam[k] = active ? a.gamma[f + k] : 0.f;
+        bet[k] = active ? a.beta[f + k] : 0.f;
+        ybv[k] = (active && a.ybias) ? a.ybias[f + k] : 0.f;
+    }
+    const int n_warps = gridDim.x * kWarps, w = blockIdx.x * kWarps + (threadIdx.x >> 5);
+    const int n_k = w < a.n ? (a.n - w + n_warps - 1) / n_warps : 0;
+    auto issue = [&](int k) {
+        if (k < n_k && active) {
+            const size_t row = (size_t)w + (size_t)k * n_warps;
+            const int st = k % NS;
+            if (ACC) {
+                cp_async_16(ring.slot(st, 0), a.acc + row * a.d + f);
+                cp_async_16(ring.slot(st, 1), a.acc + row * a.d + f + 4);
+                cp_async_4(ring.lv + st * Ring::kThreads + threadIdx.x, a.l + row * a.H + f / hd);
+            } else {
+                cp_async_16(ring.slot(st, 0), yb16 + row * a.d + f);
+            }
+            if (a.x) cp_async_16(ring.slot(st, SX), xb16 + row * a.d + f);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+#pragma unroll
+    for (int k = 0; k < NS - 1; ++k) issue(k);
+    for (int k = 0; k < n_k; ++k) {
+        issue(k + NS - 1);
+        asm volatile("cp.async.wait_group %0;" ::"n"(NS - 1) : "memory");
+        const size_t row = (size_t)w + (size_t)k * n_warps;
+        const int st = k % NS;
+        float z[8];
+        float sum = 0.f;
+        if (active) {
+            float yv[8];
+            if (ACC) {
+                const float4 lo = *reinterpret_cast<const float4*>(ring.slot(st, 0)), hi = *reinterpret_cast<const float4*>(ring.slot(st, 1));
+                const float inv_l = 1.f / (ring.lv[st * Ring::kThreads + threadIdx.x] + a.eps_l);
+                yv[0] = lo.x * inv_l; yv[1] = lo.y * inv_l; yv[2] = lo.z * inv_l; yv[3] = lo.w * inv_l;
+                yv[4] = hi.x * inv_l; yv[5] = hi.y * inv_l; yv[6] = hi.z * inv_l; yv[7] = hi.w * inv_l;
+            } else {
+                unpack_bf16x8(*ring.slot(st, 0), yv);
+            }
+            float xv[8];
+            if (a.x) unpack_bf16x8(*ring.slot(st, SX), xv);
+            const uint32_t kb = a.p > 0.f ? keep_bits8(sd, (row * a.d + f) >> 3, drop_threshold(a.p)) : 0xffu;
+#pragma unroll
+            for (int k2 = 0; k2 < 8; ++k2) {
+                float v = yv[k2] + ybv[k2];
+                v = ((kb >> k2) & 1u) ? v * inv_keep : 0.f;
+                z[k2] = a.x ? v + xv[k2] : v;
+                sum += z[k2];
+            }
+        } else {
+#pragma unroll
+            for (int k2 = 0; k2 < 8; ++k2) z[k2] = 0.f;
+        }
+        const float mean = warp_sum(sum) / a.d;
+        float var = 0.f;
+        if (active)
+#pragma unroll
+            for (int k2 = 0; k2 < 8; ++k2) { const float t = z[k2] - mean; var = fmaf(t, t, var); }
+        const float rstd = rsqrtf(warp_sum(var) / a.d + a.eps);
+        if (active) {
+            float o[8];
+#pragma unroll
+            for (int k2 = 0; k2 < 8; ++k2) o[k2] = (z[k2] - mean) * rstd * gam[k2] + bet[k2];
+            Vec8<__nv_bfloat16>::store(static_cast<__nv_bfloat16*>(a.out) + row * a.d + f, o);
+        }
+        if (lane == 0 && a.mean_rstd) { a.mean_rstd[2 * row] = mean; a.mean_rstd[2 * row + 1] = rstd; }
+    }
+}
+
+template <bool ACC>
+__global__ void __launch_bounds__(kWarps * 32) ln_bwd_ring_kernel(LayerNormBwdArgs a) {
+    extern __shared__ __align__(16) uint8_t ring_raw[];
+    using Ring = LnRing<ACC, true>;
+    float* acc_sm = reinterpret_cast<float*>(ring_raw);                          // [3][d] block accumulators first, the ring after them
+    Ring ring(ring_raw + ((3 * (size_t)a.d * sizeof(float) + 15) & ~size_t(15)));
+    constexpr int NS = kLnStages, SX = ACC ? 2 : 1, SD = SX + 1;
+    const int lane = threadIdx.x & 31, nch = a.d >> 3, f = lane << 3;
+    const bool active = lane < nch;
+    for (int i = threadIdx.x; i < 3 * a.d; i += blockDim.x) acc_sm[i] = 0.f;
+    __syncthreads();
+    const uint64_t sd = site_seed(a.seed, a.stream_id);
+    const float inv_keep = a.p > 0.f ? keep_scale(a.p) : 1.f;
+    const int hd = ACC ? a.d / a.H : a.d;
+    const __nv_bfloat16* yb16 = static_cast<const __nv_bfloat16*>(a.y);
+    const __nv_bfloat16* xb16 = static_cast<const __nv_bfloat16*>(a.x);
+    const __nv_bfloat16* gob16 = static_cast<const __nv_bfloat16*>(a.dout);
+    float gam[8], ybv[8], dgam[8], dbet[8], dyb[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        gam[k] = active ? a.gamma[f + k] : 0.f;
+        ybv[k] = (active && a.ybias) ? a.ybias[f + k] : 0.f;
+        dgam[k] = 0.f; dbet[k] = 0.f; dyb[k] = 0.f;
+    }
+    const int n_warps = gridDim.x * kWarps, w = blockIdx.x * kWarps + (threadIdx.x >> 5);
+    const int n_k = w < a.n ? (a.n - w + n_warps - 1) / n_warps : 0;
+    auto issue = [&](int k) {
+        if (k < n_k && active) {
+            const size_t row = (size_t)w + (size_t)k * n_warps;
+            const int st = k % NS;
+            if (ACC) {
+                cp_async_16(ring.slot(st, 0), a.acc + row * a.d + f);
+                cp_async_16(ring.slot(st, 1), a.acc + row * a.d + f + 4);
+                cp_async_4(ring.lv + st * Ring::kThreads + threadIdx.x, a.l + row * a.H + f / hd);
+            } else {
+                cp_async_16(ring.slot(st, 0), yb16 + row * a.d + f);
+            }
+            if (a.x) cp_async_16(ring.slot(st, SX), xb16 + row * a.d + f);
+            cp_async_16(ring.slot(st, SD), gob16 + row * a.d + f);
+            cp_async_8(ring.stat + st * Ring::kThreads + threadIdx.x, a.mean_rstd + 2 * row);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+#pragma unroll
+    for (int k = 0; k < NS - 1; ++k) issue(k);
+    for (int k = 0; k < n_k; ++k) {
+        issue(k + NS - 1);
+        asm volatile("cp.async.wait_group %0;" ::"n"(NS - 1) : "memory");
+        const size_t row = (size_t)w + (size_t)k * n_warps;
+        const int st = k % NS;
+        float zh[8], dzh[8], av[8];
+        uint32_t keep_bits = 0u;
+        float s1 = 0.f, s2 = 0.f, rstd = 0.f, inv_l = 1.f;
+        if (active) {
+            const float2 ms = ring.stat[st * Ring::kThreads + threadIdx.x];
+            rstd = ms.y;
+            float yv[8], go[8], xv[8];
+            if (ACC) {
+                const float4 lo = *reinterpret_cast<const float4*>(ring.slot(st, 0)), hi = *reinterpret_cast<const float4*>(ring.slot(st, 1));
+                inv_l = 1.f / (ring.lv[st * Ring::kThreads + threadIdx.x] + a.eps_l);
+                av[0] = lo.x; av[1] = lo.y; av[2] = lo.z; av[3] = lo.w; av[4] = hi.x; av[5] = hi.y; av[6] = hi.z; av[7] = hi.w;
+#pragma unroll
+                for (int k2 = 0; k2 < 8; ++k2) yv[k2] = av[k2] * inv_l;
+            } else {
+                unpack_bf16x8(*ring.slot(st, 0), yv);
+            }
+            if (a.x) unpack_bf16x8(*ring.slot(st, SX), xv);
+            unpack_bf16x8(*ring.slot(st, SD), go);
+            keep_bits = a.p > 0.f ? keep_bits8(sd, (row * a.d + f) >> 3, drop_threshold(a.p)) : 0xffu;
+#pragma unroll
+            for (int k2 = 0; k2 < 8; ++k2) {
+                float v = yv[k2] + ybv[k2];
+                v = ((keep_bits >> k2) & 1u) ? v * inv_keep : 0.f;
+                const float z = a.x ? v + xv[k2] : v;
+                zh[k2] = (z - ms.x) * rstd;
+                dzh[k2] = go[k2] * gam[k2];
+                s1 += dzh[k2];
+                s2 = fmaf(dzh[k2], zh[k2], s2);
+                dgam[k2] = fmaf(go[k2], zh[k2], dgam[k2]);
+                dbet[k2] += go[k2];
+            }
+        }
+        s1 = warp_sum(s1) / a.d;
+        s2 = warp_sum(s2) / a.d;
+        float dl_part = 0.f;
+        if (active) {
+            float dz[8], dy[8];
+#pragma unroll
+            for (int k2 = 0; k2 < 8; ++k2) {
+                dz[k2] = rstd * (dzh[k2] - s1 - zh[k2] * s2);
+                dy[k2] = ((keep_bits >> k2) & 1u) ? dz[k2] * inv_keep : 0.f;
+                dyb[k2] += dy[k2];
+            }
+            if (ACC) {
+                float da[8], part = 0.f;
+#pragma unroll
+                for (int k2 = 0; k2 < 8; ++k2) { da[k2] = dy[k2] * inv_l; part = fmaf(dy[k2], av[k2], part); }
+                Vec8<float>::store(a.dacc + row * a.d + f, da);
+                dl_part = -part * inv_l * inv_l;
+            } else {
+                Vec8<__nv_bfloat16>::store(static_cast<__nv_bfloat16*>(a.dy) + row * a.d + f, dy);
+            }
+            if (a.dx) {
+                __nv_bfloat16* dxp = static_cast<__nv_bfloat16*>(a.dx) + row * a.d + f;
+                if (a.accumulate_dx) {
+                    float old[8];
+                    Vec8<__nv_bfloat16>::load(dxp, old);
+#pragma unroll
+                    for (int k2 = 0; k2 < 8; ++k2) dz[k2] += old[k2];
+                }
+                Vec8<__nv_bfloat16>::store(dxp, dz);
+            }
+        }
+        if (ACC) {
+            const int lph = hd >> 3;
+            float v = dl_part;
+            for (int o = lph >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(GT_FULL_MASK, v, o);
+            if (active && (lane & (lph - 1)) == 0) a.dl[row * a.H + f / hd] = v;
+        }
+    }
+    if (active) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            atomicAdd(&acc_sm[f + k], dgam[k]);
+            atomicAdd(&acc_sm[a.d + f + k], dbet[k]);
+            atomicAdd(&acc_sm[2 * a.d + f + k], dyb[k]);
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < a.d; i += blockDim.x) {
+        a.dgamma_part[(size_t)blockIdx.x * a.part_stride + i] = acc_sm[i];
+        a.dbeta_part[(size_t)blockIdx.x * a.part_stride + i] = acc_sm[a.d + i];
+        if (a.dybias_part) a.dybias_part[(size_t)blockIdx.x * a.part_stride + i] = acc_sm[2 * a.d + i];
+    }
+}
+
 // Input stage of the models in one pass per direction: out = l2normalize(relu(dropout(LayerNorm(h)))) (dropout AFTER the norm,
 // optional L2 normalisation).  Warp per row; the backward recomputes everything from h and the saved (mean, rstd, norm).
 template <typename T, int CPL>
 __global__ void __launch_bounds__(kWarps * 32) premp_fwd_kernel(PreMpArgs a) {
     const int lane = threadIdx.x & 31, nch = a.d >> 3;
     const uint64_t sd = site_seed(a.seed, a.stream_id);
-    const float inv_keep = a.p > 0.f ? 1.f / (1.f - a.p) : 1.f;
+    const float inv_keep = a.p > 0.f ? keep_scale(a.p) : 1.f;
     for (int row = blockIdx.x * kWarps + (threadIdx.x >> 5); row < a.n; row += gridDim.x * kWarps) {
         float z[CPL][8];
         float sum = 0.f;
@@ -290,10 +553,11 @@ __global__ void __launch_bounds__(kWarps * 32) premp_fwd_kernel(PreMpArgs a) {
             const int ch = lane + 32 * i;
             if (ch < nch) {
                 const int f = ch << 3;
+                const uint32_t kb = a.p > 0.f ? keep_bits8(sd, ((uint64_t)row * a.d + f) >> 3, drop_threshold(a.p)) : 0xffu;
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
                     float u = (z[i][k] - mean) * rstd * a.gamma[f + k] + a.beta[f + k];
-                    if (a.p > 0.f) u = uniform01(sd, (uint64_t)row * a.d + f + k) >= a.p ? u * inv_keep : 0.f;
+                    u = ((kb >> k) & 1u) ? u * inv_keep : 0.f;
                     u = fmaxf(u, 0.f);
                     z[i][k] = u;
                     sq = fmaf(u, u, sq);
@@ -323,7 +587,7 @@ __global__ void __launch_bounds__(kWarps * 32) premp_bwd_kernel(PreMpArgs a) {
     for (int i = threadIdx.x; i < 2 * a.d; i += blockDim.x) smem[i] = 0.f;
     __syncthreads();
     const uint64_t sd = site_seed(a.seed, a.stream_id);
-    const float inv_keep = a.p > 0.f ? 1.f / (1.f - a.p) : 1.f;
+    const float inv_keep = a.p > 0.f ? keep_scale(a.p) : 1.f;
     float dgam[CPL][8], dbet[CPL][8], gam[CPL][8];
 #pragma unroll
     for (int i = 0; i < CPL; ++i)
@@ -345,11 +609,11 @@ __global__ void __launch_bounds__(kWarps * 32) premp_bwd_kernel(PreMpArgs a) {
                 float hv[8];
                 Vec8<T>::load(static_cast<const T*>(a.h) + (size_t)row * a.d + f, hv);
                 Vec8<T>::load(static_cast<const T*>(a.dout) + (size_t)row * a.d + f, go[i]);
+                const uint32_t kb = a.p > 0.f ? keep_bits8(sd, ((uint64_t)row * a.d + f) >> 3, drop_threshold(a.p)) : 0xffu;
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
                     zh[i][k] = (hv[k] - mean) * rstd;
-                    float keep = 1.f;
-                    if (a.p > 0.f) keep = uniform01(sd, (uint64_t)row * a.d + f + k) >= a.p ? inv_keep : 0.f;
+                    const float keep = ((kb >> k) & 1u) ? inv_keep : 0.f;
                     const float u = (zh[i][k] * gam[i][k] + a.beta[f + k]) * keep;
                     live[i][k] = u > 0.f ? keep : 0.f;                            // ReLU gate times the dropout scale
                     o[i][k] = fmaxf(u, 0.f) * inv;
@@ -408,18 +672,19 @@ template <typename T>
 __global__ void bias_act_dropout_kernel(const T* in, const float* bias, T* out, long long n_chunks, int d, int act, float p,
                                         const long long* seed, long long stream_id) {
     const uint64_t sd = site_seed(seed, stream_id);
-    const float inv = p > 0.f ? 1.f / (1.f - p) : 1.f;
+    const float inv = p > 0.f ? keep_scale(p) : 1.f;
     for (long long c = blockIdx.x * (long long)blockDim.x + threadIdx.x; c < n_chunks; c += (long long)gridDim.x * blockDim.x) {
         long long e = c << 3;
         int f = (int)(e % d);
         float v[8];
         Vec8<T>::load(in + e, v);
+        const uint32_t kb = p > 0.f ? keep_bits8(sd, (uint64_t)c, drop_threshold(p)) : 0xffu;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
             float t = v[k] + (bias ? bias[f + k] : 0.f);
             if (act == 1) t = fmaxf(t, 0.f);
             else if (act == 2) t = gelu_f(t);
-            if (p > 0.f) t = uniform01(sd, e + k) >= p ? t * inv : 0.f;
+            t = ((kb >> k) & 1u) ? t * inv : 0.f;
             v[k] = t;
         }
         Vec8<T>::store(out + e, v);
@@ -436,7 +701,7 @@ __global__ void bias_act_dropout_bwd_kernel(const T* dout, const T* in, const fl
     for (int i = threadIdx.x; i < d; i += blockDim.x) s_db[i] = 0.f;
     __syncthreads();
     const uint64_t sd = site_seed(seed, stream_id);
-    const float inv = p > 0.f ? 1.f / (1.f - p) : 1.f;
+    const float inv = p > 0.f ? keep_scale(p) : 1.f;
     const int nch = d >> 3;
     // thread t handles chunk column (t % nch) of rows (t / nch) + k * rows_per_pass: a thread keeps one column group
     const int tpb = blockDim.x;
@@ -450,12 +715,13 @@ __global__ void bias_act_dropout_bwd_kernel(const T* dout, const T* in, const fl
             float g[8], v[8], o[8];
             Vec8<T>::load(dout + e, g);
             if (act != 0) Vec8<T>::load(in + e, v);
+            const uint32_t kb = (act == 0 && p > 0.f) ? keep_bits8(sd, (uint64_t)e >> 3, drop_threshold(p)) : 0xffu;
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
                 float t;
                 if (act == 1) t = v[k] > 0.f ? g[k] * inv : 0.f;
                 else if (act == 2) t = g[k] * gelu_grad(v[k] + (bias ? bias[(colc << 3) + k] : 0.f));
-                else t = (p > 0.f) ? (uniform01(sd, e + k) >= p ? g[k] * inv : 0.f) : g[k];
+                else t = ((kb >> k) & 1u) ? g[k] * inv : 0.f;
                 o[k] = t;
                 db[k] += t;
             }
@@ -602,6 +868,24 @@ void layer_norm_fwd(const LayerNormArgs& a, cudaStream_t s) {
     if (a.n <= 0) return;
     int blocks = (a.n + kWarps - 1) / kWarps;
     if (blocks > 148 * 16) blocks = 148 * 16;
+    static const bool use_ring = [] { const char* e = getenv("GT_LN_RING"); return !(e && e[0] == '0'); }();
+    const bool aligned = (reinterpret_cast<uintptr_t>(a.y) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 &&
+                         (reinterpret_cast<uintptr_t>(a.acc) & 15) == 0;
+    if (use_ring && a.dtype == DT_BF16 && a.d <= 256 && aligned) {
+        // operands through the cp.async ring; 5 blocks of 4 warps per SM fit next to their rings
+        int rb = (a.n + kWarps - 1) / kWarps;
+        if (rb > 148 * 5) rb = 148 * 5;
+        if (a.acc) {
+            static bool once = (cudaFuncSetAttribute(ln_fwd_ring_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)LnRing<true, false>::kBytes), true);
+            (void)once;
+            ln_fwd_ring_kernel<true><<<rb, kWarps * 32, LnRing<true, false>::kBytes, s>>>(a);
+        } else {
+            static bool once = (cudaFuncSetAttribute(ln_fwd_ring_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)LnRing<false, false>::kBytes), true);
+            (void)once;
+            ln_fwd_ring_kernel<false><<<rb, kWarps * 32, LnRing<false, false>::kBytes, s>>>(a);
+        }
+        return;
+    }
     // chunks of 8 features per lane: the kernel is instantiated for 1, 2 or 4 so narrow rows do not pay for wide registers
 #define GT_LN_FWD(T)                                                                   \
     do {                                                                               \
@@ -622,6 +906,22 @@ int layer_norm_bwd_blocks(int n) {
 void layer_norm_bwd(const LayerNormBwdArgs& a, cudaStream_t s) {
     if (a.n <= 0) return;
     const size_t sm = 3 * (size_t)a.d * sizeof(float);
+    static const bool use_ring = [] { const char* e = getenv("GT_LN_RING"); return !(e && e[0] == '0'); }();
+    const bool aligned = (reinterpret_cast<uintptr_t>(a.y) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 &&
+                         (reinterpret_cast<uintptr_t>(a.acc) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.dout) & 15) == 0;
+    if (use_ring && a.dtype == DT_BF16 && a.d <= 256 && aligned) {
+        const size_t head = (sm + 15) & ~size_t(15);
+        if (a.acc) {
+            static bool once = (cudaFuncSetAttribute(ln_bwd_ring_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(LnRing<true, true>::kBytes + 4096)), true);
+            (void)once;
+            ln_bwd_ring_kernel<true><<<a.n_blocks, kWarps * 32, head + LnRing<true, true>::kBytes, s>>>(a);
+        } else {
+            static bool once = (cudaFuncSetAttribute(ln_bwd_ring_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(LnRing<false, true>::kBytes + 4096)), true);
+            (void)once;
+            ln_bwd_ring_kernel<false><<<a.n_blocks, kWarps * 32, head + LnRing<false, true>::kBytes, s>>>(a);
+        }
+        return;
+    }
 #define GT_LN_BWD(T)                                                                          \
     do {                                                                                      \
         if (a.d <= 256) ln_bwd_kernel<T, 1><<<a.n_blocks, kWarps * 32, sm, s>>>(a);           \
