@@ -48,6 +48,9 @@ def load_checkpoint(path, model, engine=None, strict=True):
     unexpected = [k for k in sd if k not in own]
     if strict and (missing or unexpected):
         raise KeyError(f"checkpoint mismatch: missing {missing[:5]}, unexpected {unexpected[:5]}")
+    bad = [f"{k}: checkpoint {tuple(sd[k].shape)} vs model {tuple(own[k].shape)}" for k in sd if k in own and sd[k].shape != own[k].shape]
+    if bad:
+        raise ValueError("checkpoint was written for a different configuration: " + "; ".join(bad[:4]))
     with torch.no_grad():
         for k, v in sd.items():
             if k in own:

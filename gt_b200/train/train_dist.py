@@ -243,6 +243,8 @@ def main(argv=None):
                 extra_fw = dict(degree_loc=wl["degree"], out_degree_loc=wl.get("out_degree"))
             label_classes = wl["cfg"]["classes"]
         grid, model = wl["grid"], wl["model"]
+        args.hidden, args.layers, args.heads = (args.hidden or wl["cfg"]["hidden"], args.layers or wl["cfg"]["layers"],
+                                                args.heads or wl["cfg"]["heads"])
         x_loc, y_loc = wl["x"].to(dev), wl["y"].to(dev)
         masks = {k: v.to(dev) for k, v in wl["masks"].items()}
         n, n_train, e_total = wl["num_nodes"], wl["n_train"], wl["num_attn_edges"]
@@ -265,6 +267,7 @@ def main(argv=None):
         dist.all_reduce(cnt)
         n_train, e_total = int(cnt[0]), int(cnt[1]) // max(getattr(grid, "p_heads", 1), 1)
         hidden, heads, layers = args.hidden or 80, args.heads or 2, args.layers or 4
+        args.hidden, args.heads, args.layers = hidden, heads, layers
         if args.model == "exphormer":
             exp_blk = block_expander_edges(grid, n, args.exp_deg, seed=args.seed, device=dev)
             a_blk = torch.cat([gcn_blk, exp_blk], dim=1)
