@@ -146,6 +146,49 @@ void layer_norm_fwd(Tensor y, OptT x, OptT ybias, Tensor gamma, Tensor beta, Ten
     gt::layer_norm_fwd(a, stream());
 }
 
+void embed_add(Tensor x, Tensor tab_a, Tensor idx_a, int64_t pad_a, OptT tab_b, OptT idx_b, int64_t pad_b, Tensor out) {
+    c10::cuda::CUDAGuard guard(x.device());
+    check_cuda_contig(x, "x");
+    TORCH_CHECK(x.size(1) % 8 == 0 && tab_a.scalar_type() == torch::kFloat32 && tab_a.is_contiguous() && idx_a.scalar_type() == torch::kInt64,
+                "embed_add: width % 8 == 0, fp32 tables, int64 indices");
+    const bool two = tab_b.has_value() && tab_b->defined();
+    gt::embed_add(dt(x), x.data_ptr(), tab_a.data_ptr<float>(), idx_a.data_ptr<int64_t>() ? reinterpret_cast<const long long*>(idx_a.data_ptr<int64_t>()) : nullptr,
+                  pad_a, two ? tab_b->data_ptr<float>() : nullptr, two ? reinterpret_cast<const long long*>(idx_b->data_ptr<int64_t>()) : nullptr, pad_b,
+                  out.data_ptr(), x.size(0), (int)x.size(1), stream());
+}
+
+void embed_add_bwd(Tensor dout, Tensor idx, int64_t pad, Tensor dtab) {
+    c10::cuda::CUDAGuard guard(dout.device());
+    check_cuda_contig(dout, "dout");
+    gt::embed_add_bwd(dt(dout), dout.data_ptr(), reinterpret_cast<const long long*>(idx.data_ptr<int64_t>()), pad, dtab.data_ptr<float>(),
+                      dout.size(0), (int)dout.size(1), stream());
+}
+
+void gated_res_fwd(Tensor r, Tensor o, Tensor wa, Tensor wb, Tensor gate_bias, Tensor gamma, Tensor beta, Tensor out, Tensor stats, double eps,
+                   double p, OptT seed, int64_t stream_id) {
+    c10::cuda::CUDAGuard guard(r.device());
+    check_cuda_contig(r, "r"); check_cuda_contig(o, "o");
+    TORCH_CHECK(r.size(1) % 8 == 0 && r.size(1) <= 256, "gated residual kernel: width % 8 == 0 and <= 256");
+    gt::GatedResArgs a{};
+    a.dtype = dt(r); a.r = r.data_ptr(); a.o = o.data_ptr(); a.wa = wa.data_ptr<float>(); a.wb = wb.data_ptr<float>();
+    a.gate_bias = gate_bias.data_ptr<float>(); a.gamma = gamma.data_ptr<float>(); a.beta = beta.data_ptr<float>(); a.out = out.data_ptr();
+    a.stats = stats.data_ptr<float>(); a.n = r.size(0); a.d = (int)r.size(1); a.eps = (float)eps; a.p = (float)p;
+    a.seed = cptr<long long>(seed); a.stream_id = stream_id;
+    gt::gated_residual(a, false, stream());
+}
+
+void gated_res_bwd(Tensor r, Tensor o, Tensor dout, Tensor wa, Tensor wb, Tensor gamma, Tensor beta, Tensor stats, Tensor dr, Tensor d_o,
+                   Tensor part, double p, OptT seed, int64_t stream_id) {
+    c10::cuda::CUDAGuard guard(r.device());
+    check_cuda_contig(dout, "dout");
+    gt::GatedResArgs a{};
+    a.dtype = dt(r); a.r = r.data_ptr(); a.o = o.data_ptr(); a.dout = dout.data_ptr(); a.wa = wa.data_ptr<float>(); a.wb = wb.data_ptr<float>();
+    a.gamma = gamma.data_ptr<float>(); a.beta = beta.data_ptr<float>(); a.stats = stats.data_ptr<float>(); a.dr = dr.data_ptr();
+    a.d_o = d_o.data_ptr(); a.part = part.data_ptr<float>(); a.part_stride = (int)part.stride(0); a.n_blocks = (int)part.size(0);
+    a.n = r.size(0); a.d = (int)r.size(1); a.p = (float)p; a.seed = cptr<long long>(seed); a.stream_id = stream_id;
+    gt::gated_residual(a, true, stream());
+}
+
 int64_t premp_blocks(int64_t n) { return gt::premp_blocks((int)n); }
 
 void premp_fwd(Tensor h, Tensor gamma, Tensor beta, Tensor out, Tensor stats, double eps, double p, OptT seed, int64_t stream_id, bool l2norm) {
@@ -457,6 +500,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("cast_bf16", &cast_bf16);
     m.def("pack_cols", &pack_cols);
     m.def("premp_blocks", &premp_blocks);
+    m.def("embed_add", &embed_add);
+    m.def("embed_add_bwd", &embed_add_bwd);
+    m.def("gated_res_fwd", &gated_res_fwd);
+    m.def("gated_res_bwd", &gated_res_bwd);
     m.def("premp_fwd", &premp_fwd);
     m.def("premp_bwd", &premp_bwd);
     m.def("gemm_nt", &gemm_nt);

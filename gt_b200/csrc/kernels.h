@@ -121,6 +121,18 @@ struct PreMpArgs {
     int n, d; float eps; float p; const long long* seed; long long stream_id; int l2norm;
     const void* dout; void* dh; float* part; int n_blocks;      // backward: part [n_blocks, 2 d] (dgamma | dbeta)
 };
+// out = x + tab_a[idx_a] (+ tab_b[idx_b]) row-wise (embedding lookups folded into one pass); tables fp32 [*, d]
+void embed_add(int dtype, const void* x, const float* tab_a, const long long* idx_a, long long pad_a, const float* tab_b,
+               const long long* idx_b, long long pad_b, void* out, long long n, int d, cudaStream_t s);
+void embed_add_bwd(int dtype, const void* dout, const long long* idx, long long pad, float* dtab, long long n, int d, cudaStream_t s);
+// UniMP gated residual: out = dropout(relu(LN(beta r + (1 - beta) o))), beta = sigmoid(r . wa + o . wb + b); d <= 256
+struct GatedResArgs {
+    int dtype; const void* r; const void* o; const float* wa; const float* wb; const float* gate_bias;
+    const float* gamma; const float* beta; void* out; float* stats;      // stats [n, 3] = mean, rstd, beta
+    long long n; int d; float eps; float p; const long long* seed; long long stream_id;
+    const void* dout; void* dr; void* d_o; float* part; int part_stride; int n_blocks;   // backward: part [n_blocks, 4 d + 1]
+};
+void gated_residual(const GatedResArgs& a, bool backward, cudaStream_t s);
 int premp_blocks(int n);
 void premp(const PreMpArgs& a, bool backward, cudaStream_t s);
 

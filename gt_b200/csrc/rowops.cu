@@ -517,6 +517,183 @@ __global__ void __launch_bounds__(kWarps * 32) ln_bwd_ring_kernel(LayerNormBwdAr
     }
 }
 
+// out[r, :] = x[r, :] + tab_a[idx_a[r], :] (+ tab_b[idx_b[r], :]): embedding lookups added to a feature matrix in one pass
+// (degree / label / token embeddings).  idx < 0 or == pad adds nothing.  Backward of the tables: fp32 atomics per row.
+template <typename T>
+__global__ void embed_add_kernel(const T* x, const float* tab_a, const long long* idx_a, long long pad_a, const float* tab_b,
+                                 const long long* idx_b, long long pad_b, T* out, long long n, int d) {
+    const int cpr = d >> 3;
+    const long long total = n * cpr;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / cpr;
+        const int f = (int)(i - r * cpr) << 3;
+        float v[8];
+        Vec8<T>::load(x + r * d + f, v);
+        const long long ia = idx_a[r];
+        if (ia >= 0 && ia != pad_a) {
+            float e[8];
+            Vec8<float>::load(tab_a + ia * d + f, e);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] += e[k];
+        }
+        if (tab_b) {
+            const long long ib = idx_b[r];
+            if (ib >= 0 && ib != pad_b) {
+                float e[8];
+                Vec8<float>::load(tab_b + ib * d + f, e);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v[k] += e[k];
+            }
+        }
+        Vec8<T>::store(out + r * d + f, v);
+    }
+}
+
+template <typename T>
+__global__ void embed_add_bwd_kernel(const T* dout, const long long* idx, long long pad, float* dtab, long long n, int d) {
+    const int cpr = d >> 3;
+    const long long total = n * cpr;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / cpr;
+        const long long ix = idx[r];
+        if (ix < 0 || ix == pad) continue;
+        const int f = (int)(i - r * cpr) << 3;
+        float g[8];
+        Vec8<T>::load(dout + r * d + f, g);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) atomicAdd(dtab + ix * d + f + k, g[k]);
+    }
+}
+
+// UniMP combine in one pass per direction: beta = sigmoid(r . wa + o . wb + b), h = beta r + (1 - beta) o,
+// out = dropout(relu(LayerNorm(h))).  wa = W_g[0] + W_g[2], wb = W_g[1] - W_g[2] of the reference's W_g [1, 3 d] applied to
+// [r | o | r - o].  Warp per row, d <= 256 (one 8-chunk per lane).  The backward recomputes from r and o.
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32) gated_res_fwd_kernel(GatedResArgs a) {
+    const int lane = threadIdx.x & 31, nch = a.d >> 3, f = lane << 3;
+    const bool active = lane < nch;
+    const uint64_t sd = site_seed(a.seed, a.stream_id);
+    const float inv_keep = a.p > 0.f ? keep_scale(a.p) : 1.f;
+    float wa[8], wb[8], gam[8], bet[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        wa[k] = active ? a.wa[f + k] : 0.f; wb[k] = active ? a.wb[f + k] : 0.f;
+        gam[k] = active ? a.gamma[f + k] : 0.f; bet[k] = active ? a.beta[f + k] : 0.f;
+    }
+    const float gb = a.gate_bias[0];
+    for (long long row = blockIdx.x * kWarps + (threadIdx.x >> 5); row < a.n; row += (long long)gridDim.x * kWarps) {
+        float rv[8], ov[8], h[8];
+        float dot = 0.f;
+        if (active) {
+            Vec8<T>::load(static_cast<const T*>(a.r) + row * a.d + f, rv);
+            Vec8<T>::load(static_cast<const T*>(a.o) + row * a.d + f, ov);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) dot = fmaf(rv[k], wa[k], fmaf(ov[k], wb[k], dot));
+        }
+        const float beta_g = 1.f / (1.f + __expf(-(warp_sum(dot) + gb)));
+        float sum = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { h[k] = active ? beta_g * rv[k] + (1.f - beta_g) * ov[k] : 0.f; sum += h[k]; }
+        const float mean = warp_sum(sum) / a.d;
+        float var = 0.f;
+        if (active)
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { const float t = h[k] - mean; var = fmaf(t, t, var); }
+        const float rstd = rsqrtf(warp_sum(var) / a.d + a.eps);
+        if (active) {
+            const uint32_t kb = a.p > 0.f ? keep_bits8(sd, (uint64_t)(row * a.d + f) >> 3, drop_threshold(a.p)) : 0xffu;
+            float out[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float u = fmaxf((h[k] - mean) * rstd * gam[k] + bet[k], 0.f);
+                out[k] = ((kb >> k) & 1u) ? u * inv_keep : 0.f;
+            }
+            Vec8<T>::store(static_cast<T*>(a.out) + row * a.d + f, out);
+        }
+        if (lane == 0) { a.stats[3 * row] = mean; a.stats[3 * row + 1] = rstd; a.stats[3 * row + 2] = beta_g; }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32) gated_res_bwd_kernel(GatedResArgs a) {
+    extern __shared__ float smem[];                    // [4][d] + 1: dgamma, dbeta, dwa, dwb, dbias
+    const int lane = threadIdx.x & 31, nch = a.d >> 3, f = lane << 3;
+    const bool active = lane < nch;
+    for (int i = threadIdx.x; i < 4 * a.d + 1; i += blockDim.x) smem[i] = 0.f;
+    __syncthreads();
+    const uint64_t sd = site_seed(a.seed, a.stream_id);
+    const float inv_keep = a.p > 0.f ? keep_scale(a.p) : 1.f;
+    float wa[8], wb[8], gam[8], bet[8], dgam[8], dbet[8], dwa[8], dwb[8];
+    float dgb = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        wa[k] = active ? a.wa[f + k] : 0.f; wb[k] = active ? a.wb[f + k] : 0.f;
+        gam[k] = active ? a.gamma[f + k] : 0.f; bet[k] = active ? a.beta[f + k] : 0.f;
+        dgam[k] = 0.f; dbet[k] = 0.f; dwa[k] = 0.f; dwb[k] = 0.f;
+    }
+    for (long long row = blockIdx.x * kWarps + (threadIdx.x >> 5); row < a.n; row += (long long)gridDim.x * kWarps) {
+        const float mean = a.stats[3 * row], rstd = a.stats[3 * row + 1], beta_g = a.stats[3 * row + 2];
+        float rv[8], ov[8], zh[8], dzh[8];
+        float s1 = 0.f, s2 = 0.f;
+        if (active) {
+            float go[8];
+            Vec8<T>::load(static_cast<const T*>(a.r) + row * a.d + f, rv);
+            Vec8<T>::load(static_cast<const T*>(a.o) + row * a.d + f, ov);
+            Vec8<T>::load(static_cast<const T*>(a.dout) + row * a.d + f, go);
+            const uint32_t kb = a.p > 0.f ? keep_bits8(sd, (uint64_t)(row * a.d + f) >> 3, drop_threshold(a.p)) : 0xffu;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float h = beta_g * rv[k] + (1.f - beta_g) * ov[k];
+                zh[k] = (h - mean) * rstd;
+                const float u = zh[k] * gam[k] + bet[k];
+                const float gz = (u > 0.f && ((kb >> k) & 1u)) ? go[k] * inv_keep : 0.f;   // through dropout and ReLU
+                dgam[k] = fmaf(gz, zh[k], dgam[k]);
+                dbet[k] += gz;
+                dzh[k] = gz * gam[k];
+                s1 += dzh[k];
+                s2 = fmaf(dzh[k], zh[k], s2);
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { rv[k] = 0.f; ov[k] = 0.f; zh[k] = 0.f; dzh[k] = 0.f; }
+        }
+        s1 = warp_sum(s1) / a.d;
+        s2 = warp_sum(s2) / a.d;
+        float dh[8], dbeta_part = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            dh[k] = rstd * (dzh[k] - s1 - zh[k] * s2);
+            dbeta_part = fmaf(dh[k], rv[k] - ov[k], dbeta_part);
+        }
+        const float dlogit = warp_sum(dbeta_part) * beta_g * (1.f - beta_g);
+        if (active) {
+            float dr[8], dov[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                dr[k] = beta_g * dh[k] + dlogit * wa[k];
+                dov[k] = (1.f - beta_g) * dh[k] + dlogit * wb[k];
+                dwa[k] = fmaf(dlogit, rv[k], dwa[k]);
+                dwb[k] = fmaf(dlogit, ov[k], dwb[k]);
+            }
+            Vec8<T>::store(static_cast<T*>(a.dr) + row * a.d + f, dr);
+            Vec8<T>::store(static_cast<T*>(a.d_o) + row * a.d + f, dov);
+        }
+        if (lane == 0) dgb += dlogit;
+    }
+    if (active) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            atomicAdd(&smem[f + k], dgam[k]);
+            atomicAdd(&smem[a.d + f + k], dbet[k]);
+            atomicAdd(&smem[2 * a.d + f + k], dwa[k]);
+            atomicAdd(&smem[3 * a.d + f + k], dwb[k]);
+        }
+    }
+    if (lane == 0) atomicAdd(&smem[4 * a.d], dgb);
+    __syncthreads();
+    for (int i = threadIdx.x; i < 4 * a.d + 1; i += blockDim.x) a.part[(size_t)blockIdx.x * a.part_stride + i] = smem[i];
+}
+
 // Input stage of the models in one pass per direction: out = l2normalize(relu(dropout(LayerNorm(h)))) (dropout AFTER the norm,
 // optional L2 normalisation).  Warp per row; the backward recomputes everything from h and the saved (mean, rstd, norm).
 template <typename T, int CPL>
@@ -862,6 +1039,38 @@ void premp(const PreMpArgs& a, bool backward, cudaStream_t s) {
     if (a.dtype == DT_BF16) { if (a.d <= 256) GT_PREMP(__nv_bfloat16, 1); else if (a.d <= 512) GT_PREMP(__nv_bfloat16, 2); else GT_PREMP(__nv_bfloat16, 4); }
     else                    { if (a.d <= 256) GT_PREMP(float, 1); else if (a.d <= 512) GT_PREMP(float, 2); else GT_PREMP(float, 4); }
 #undef GT_PREMP
+}
+
+void embed_add(int dtype, const void* x, const float* tab_a, const long long* idx_a, long long pad_a, const float* tab_b,
+               const long long* idx_b, long long pad_b, void* out, long long n, int d, cudaStream_t s) {
+    if (n <= 0) return;
+    const int blocks = grid_for(n * (d / 8), 256);
+    if (dtype == DT_BF16)
+        embed_add_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), tab_a, idx_a, pad_a, tab_b, idx_b, pad_b,
+                                                               static_cast<__nv_bfloat16*>(out), n, d);
+    else
+        embed_add_kernel<float><<<blocks, 256, 0, s>>>(static_cast<const float*>(x), tab_a, idx_a, pad_a, tab_b, idx_b, pad_b,
+                                                       static_cast<float*>(out), n, d);
+}
+
+void embed_add_bwd(int dtype, const void* dout, const long long* idx, long long pad, float* dtab, long long n, int d, cudaStream_t s) {
+    if (n <= 0) return;
+    const int blocks = grid_for(n * (d / 8), 256);
+    if (dtype == DT_BF16) embed_add_bwd_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(dout), idx, pad, dtab, n, d);
+    else embed_add_bwd_kernel<float><<<blocks, 256, 0, s>>>(static_cast<const float*>(dout), idx, pad, dtab, n, d);
+}
+
+void gated_residual(const GatedResArgs& a, bool backward, cudaStream_t s) {
+    if (a.n <= 0) return;
+    if (backward) {
+        const size_t sm = (4 * (size_t)a.d + 1) * sizeof(float);
+        if (a.dtype == DT_BF16) gated_res_bwd_kernel<__nv_bfloat16><<<a.n_blocks, kWarps * 32, sm, s>>>(a);
+        else gated_res_bwd_kernel<float><<<a.n_blocks, kWarps * 32, sm, s>>>(a);
+    } else {
+        const int blocks = premp_blocks((int)a.n) * 2;
+        if (a.dtype == DT_BF16) gated_res_fwd_kernel<__nv_bfloat16><<<blocks, kWarps * 32, 0, s>>>(a);
+        else gated_res_fwd_kernel<float><<<blocks, kWarps * 32, 0, s>>>(a);
+    }
 }
 
 void layer_norm_fwd(const LayerNormArgs& a, cudaStream_t s) {

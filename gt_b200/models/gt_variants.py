@@ -210,9 +210,11 @@ class GraphormerNodeRef(nn.Module):
     def embed(self, x, degree, out_degree=None, token_row=None):
         h = K.linear(x, self.pre_lin.weight, self.pre_lin.bias)
         if degree is not None:
-            h = h + self.degree_emb(degree.clamp(max=self.max_degree)).to(h.dtype)
-        if self.out_degree_emb is not None and out_degree is not None:
-            h = h + self.out_degree_emb(out_degree.clamp(max=self.max_degree)).to(h.dtype)
+            two = self.out_degree_emb is not None and out_degree is not None
+            h = K.embed_add(h, self.degree_emb, degree.clamp(max=self.max_degree), self.out_degree_emb if two else None,
+                            out_degree.clamp(max=self.max_degree) if two else None)
+        elif self.out_degree_emb is not None and out_degree is not None:
+            h = K.embed_add(h, self.out_degree_emb, out_degree.clamp(max=self.max_degree))
         if token_row is not None:
             h = torch.cat([h[:token_row], self.graph_token.weight.to(h.dtype), h[token_row + 1:]], dim=0)
         else:
@@ -309,7 +311,7 @@ class DistGTVariant(nn.Module):
         if self.model == "unimp":
             h = K.linear(x_loc, self.pre_lin.weight, self.pre_lin.bias)
             if self.label_emb is not None and label_feat is not None:
-                h = h + self.label_emb(label_feat).to(h.dtype)
+                h = K.embed_add(h, self.label_emb, label_feat)
             h = F.dropout(h, self.dropout, self.training)
         else:
             h = self._embed(self, x_loc, degree_loc, out_degree_loc, self.token_row)

@@ -145,3 +145,15 @@ def native_ok(x):
 def pre_mp(h, norm, p, l2norm=True):
     """Input stage ``l2normalize(relu(dropout(norm(h))))`` (dropout after the norm) as one native kernel per direction."""
     return _native().pre_mp(h, norm.weight, norm.bias, norm.eps, p, l2norm)
+
+
+def embed_add(x, emb_a, idx_a, emb_b=None, idx_b=None):
+    """``x + emb_a(idx_a) (+ emb_b(idx_b))`` for ``nn.Embedding`` modules (padding indices add nothing): one native pass on CUDA."""
+    if native_ok(x):
+        pad_a = emb_a.padding_idx if emb_a.padding_idx is not None else -1
+        pad_b = emb_b.padding_idx if (emb_b is not None and emb_b.padding_idx is not None) else -1
+        return _native().embed_add(x, emb_a.weight, idx_a, pad_a, emb_b.weight if emb_b is not None else None, idx_b, pad_b)
+    out = x + emb_a(idx_a).to(x.dtype)
+    if emb_b is not None:
+        out = out + emb_b(idx_b).to(x.dtype)
+    return out

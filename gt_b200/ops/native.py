@@ -313,14 +313,87 @@ def layer_norm(y, x, ybias, gamma, beta, eps, p, l=None, eps_l=1e-6):
     return _LayerNorm.apply(y, x, ybias, gamma, beta, float(eps), float(p), site, l, float(eps_l))
 
 
+class _GatedResidual(torch.autograd.Function):
+    """UniMP combine in one kernel per direction (rows of up to 256 features); see ``csrc/rowops.cu``."""
+
+    @staticmethod
+    def forward(ctx, r, o, gate_weight, gate_bias, ln_weight, ln_bias, eps, p, site):
+        d = r.shape[1]
+        w = gate_weight.float().view(3, d)
+        wa, wb = (w[0] + w[2]).contiguous(), (w[1] - w[2]).contiguous()
+        r, o = r.contiguous(), o.to(r.dtype).contiguous()
+        out = torch.empty_like(r)
+        stats = torch.empty(r.shape[0], 3, dtype=torch.float32, device=r.device)
+        ext().gated_res_fwd(r, o, wa, wb, gate_bias.float().reshape(1), ln_weight.float(), ln_bias.float(), out, stats, float(eps), float(p),
+                            rng_state(r.device) if p > 0 else None, int(site))
+        ctx.save_for_backward(r, o, wa, wb, ln_weight, ln_bias, stats)
+        ctx.cfg = (float(p), int(site), gate_weight.dtype, gate_bias.dtype, gate_weight.shape)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        r, o, wa, wb, gamma, beta, stats = ctx.saved_tensors
+        p, site, wdt, bdt, wshape = ctx.cfg
+        e = ext()
+        d = r.shape[1]
+        nb = e.premp_blocks(r.shape[0])
+        part = torch.empty(nb, 4 * d + 8, dtype=torch.float32, device=r.device)
+        dr, do_ = torch.empty_like(r), torch.empty_like(o)
+        e.gated_res_bwd(r, o, dout.contiguous(), wa, wb, gamma.float(), beta.float(), stats, dr, do_, part, p,
+                        rng_state(r.device) if p > 0 else None, site)
+        red = torch.empty(4 * d + 8, dtype=torch.float32, device=r.device)
+        e.reduce_partials(part, red)
+        dwa, dwb = red[2 * d:3 * d], red[3 * d:4 * d]
+        # wa = w0 + w2, wb = w1 - w2  ->  dw0 = dwa, dw1 = dwb, dw2 = dwa - dwb
+        dw = torch.stack([dwa, dwb, dwa - dwb]).reshape(wshape).to(wdt)
+        return dr, do_, dw, red[4 * d:4 * d + 1].to(bdt), red[:d].to(gamma.dtype), red[d:2 * d].to(beta.dtype), None, None, None
+
+
 def gated_residual(r, o, gate_weight, gate_bias, ln_weight, ln_bias, eps, p):
-    """UniMP combine; the gate logit is two mat-vec products, the blend feeds the fused LayerNorm kernel."""
+    """UniMP combine ``drop(relu(LN(beta r + (1 - beta) o)))`` with ``beta = sigmoid(W_g [r | o | r - o] + b)``: one fused kernel per
+    direction for rows of up to 256 features, otherwise two mat-vec products feeding the fused LayerNorm kernel."""
     d = r.shape[1]
+    if d <= 256 and d % 8 == 0 and _dt_ok(r):
+        site = (gate_weight.data_ptr() ^ 0x2545f491) & 0xFFFFFFFFFF
+        return _GatedResidual.apply(r, o, gate_weight, gate_bias, ln_weight, ln_bias, eps, float(p), site)
     w = gate_weight.to(r.dtype).view(3, d)
     logit = r @ (w[0] + w[2]) + o @ (w[1] - w[2]) + gate_bias.to(r.dtype)
     beta = torch.sigmoid(logit).unsqueeze(-1)
     out = torch.relu(layer_norm(beta * r + (1.0 - beta) * o, None, None, ln_weight, ln_bias, eps, 0.0))
     return torch.nn.functional.dropout(out, p, True) if p > 0 else out
+
+
+class _EmbedAdd(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, tab_a, idx_a, pad_a, tab_b, idx_b, pad_b):
+        x = x.contiguous()
+        out = torch.empty_like(x)
+        ta = tab_a.float().contiguous()
+        tb = tab_b.float().contiguous() if tab_b is not None else None
+        ext().embed_add(x, ta, idx_a.contiguous(), int(pad_a), tb, idx_b.contiguous() if idx_b is not None else None, int(pad_b), out)
+        ctx.save_for_backward(idx_a, idx_b)
+        ctx.cfg = (tab_a.shape, tab_a.dtype, pad_a, tab_b.shape if tab_b is not None else None, tab_b.dtype if tab_b is not None else None, pad_b)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        idx_a, idx_b = ctx.saved_tensors
+        sa, da, pad_a, sb, db, pad_b = ctx.cfg
+        dout = dout.contiguous()
+        e = ext()
+        dta = torch.zeros(sa, dtype=torch.float32, device=dout.device)
+        e.embed_add_bwd(dout, idx_a.contiguous(), int(pad_a), dta)
+        dtb = None
+        if sb is not None:
+            dtb = torch.zeros(sb, dtype=torch.float32, device=dout.device)
+            e.embed_add_bwd(dout, idx_b.contiguous(), int(pad_b), dtb)
+            dtb = dtb.to(db)
+        return dout, dta.to(da), None, None, dtb, None, None
+
+
+def embed_add(x, tab_a, idx_a, pad_a=-1, tab_b=None, idx_b=None, pad_b=-1):
+    """``x + tab_a[idx_a] (+ tab_b[idx_b])`` row-wise in one pass; rows whose index is negative or equals ``pad`` get nothing."""
+    return _EmbedAdd.apply(x, tab_a, idx_a, pad_a, tab_b, idx_b, pad_b)
 
 
 SPMM_SEG = 256          # rows longer than this are cut into segments handled by separate warps

@@ -312,3 +312,41 @@ def test_fused_input_stage_matches_torch(l2norm, d):
     dropped = (ob == 0).float().mean().item()
     assert 0.55 < dropped < 0.75                                   # ~half by ReLU of what 30 % dropout leaves
     native.check_status(dev)
+
+
+def test_embed_add_and_gated_residual_kernels():
+    import torch.nn as nn
+    from gt_b200.ops import functional as K
+    dev = _dev()
+    torch.manual_seed(0)
+    n, d = 1003, 128
+    # embedding lookups folded into one pass (padding index adds nothing), gradients of the tables by atomics
+    x = torch.randn(n, d, device=dev, requires_grad=True)
+    ea, eb = nn.Embedding(20, d, padding_idx=19).to(dev), nn.Embedding(7, d).to(dev)
+    ia, ib = torch.randint(0, 20, (n,), device=dev), torch.randint(0, 7, (n,), device=dev)
+    w = torch.randn(n, d, device=dev)
+    out = K.embed_add(x, ea, ia, eb, ib)
+    (out * w).sum().backward()
+    got = [out.detach().clone(), x.grad.clone(), ea.weight.grad.clone(), eb.weight.grad.clone()]
+    x.grad = None; ea.weight.grad = None; eb.weight.grad = None
+    ref = x + ea(ia) + eb(ib)
+    (ref * w).sum().backward()
+    for a_, b_ in zip(got, (ref.detach(), x.grad, ea.weight.grad, eb.weight.grad)):
+        assert _rel(a_, b_) < 1e-5
+    # UniMP gated residual vs the composed torch expression
+    r = torch.randn(n, d, device=dev, requires_grad=True)
+    o = torch.randn(n, d, device=dev, requires_grad=True)
+    gate, ln = nn.Linear(3 * d, 1).to(dev), K.LayerNorm(d).to(dev)
+    with torch.no_grad():
+        ln.weight.uniform_(0.5, 1.5); ln.bias.normal_(0, 0.1)
+    out = K.gated_residual(r, o, gate.weight, gate.bias, ln, 0.0, True)
+    (out * w).sum().backward()
+    params = (r, o, gate.weight, gate.bias, ln.weight, ln.bias)
+    got = [out.detach().clone()] + [p_.grad.clone() for p_ in params]
+    for p_ in params:
+        p_.grad = None
+    beta = torch.sigmoid(gate(torch.cat([r, o, r - o], dim=1)))
+    ref = torch.relu(torch.nn.functional.layer_norm(beta * r + (1 - beta) * o, (d,), ln.weight, ln.bias, ln.eps))
+    (ref * w).sum().backward()
+    for a_, b_ in zip(got, [ref.detach()] + [p_.grad for p_ in params]):
+        assert _rel(a_, b_) < 5e-4
