@@ -443,6 +443,13 @@ void group_barrier(Tensor peer_flag_ptrs, Tensor my_flags, Tensor counter, int64
                       (int)peer_flag_ptrs.numel(), (int)my_index, max_spins, status.data_ptr<int>(), stream());
 }
 
+void pull_all_to_all(Tensor peer_ptrs, int64_t me, int64_t rows, int64_t slab_bytes, bool to_heads, Tensor out) {
+    c10::cuda::CUDAGuard guard(out.device());
+    TORCH_CHECK(slab_bytes % 16 == 0, "head slabs must be a multiple of 16 bytes");
+    gt::pull_all_to_all(reinterpret_cast<const void* const*>(peer_ptrs.data_ptr()), (int)peer_ptrs.numel(), (int)me, rows, slab_bytes, to_heads,
+                        out.data_ptr(), stream());
+}
+
 void pull_gather_rows(Tensor peer_ptrs, Tensor owner, Tensor row, Tensor out) {
     c10::cuda::CUDAGuard guard(out.device());
     const int row_bytes = (int)(out.numel() / std::max<int64_t>(out.size(0), 1) * out.element_size());
@@ -521,6 +528,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("wait_flags", &wait_flags);
     m.def("group_barrier", &group_barrier);
     m.def("pull_gather_rows", &pull_gather_rows);
+    m.def("pull_all_to_all", &pull_all_to_all);
     m.def("pull_reduce_rows", &pull_reduce_rows);
     m.def("pull_all_gather", &pull_all_gather);
     m.def("pull_reduce_scatter", &pull_reduce_scatter);

@@ -227,6 +227,9 @@ void pull_gather_rows(const void* const* peers, const int* owner, const int* row
 void pull_reduce_rows(int dtype, const void* const* peers, int n_peers, const int* src, void* out, int n_rows, int width, cudaStream_t s);
 // dense variants: all-gather / reduce-scatter of equal chunks by direct peer reads
 void pull_all_gather(const void* const* peers, int n_peers, void* out, long long chunk_bytes, cudaStream_t s);
+// Ulysses all-to-all (rows <-> head slabs) by strided peer reads; slab_bytes % 16 == 0
+void pull_all_to_all(const void* const* peers, int n_peers, int me, long long rows, long long slab_bytes, bool to_heads, void* out,
+                     cudaStream_t s);
 void pull_reduce_scatter(int dtype, const void* const* peers, int n_peers, int my_index, void* out, long long chunk_elems, cudaStream_t s);
 // out = sum over peers of their buffers (one-shot all-reduce by peer reads), fp32 or bf16 payload with fp32 accumulation
 void pull_all_reduce(int dtype, const void* const* peers, int n_peers, void* out, long long n, cudaStream_t s);

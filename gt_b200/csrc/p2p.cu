@@ -142,6 +142,28 @@ __global__ void pull_all_reduce_kernel(const void* const* peers, int n_peers, T*
     }
 }
 
+// Ulysses all-to-all by peer reads, both directions, in 16-byte units.
+//   to_heads: out[p * rows + r][:]              = peers[p][r * (n_peers * slab) + me * slab : +slab]     (rows of peer p, my head slab)
+//   to_rows : out[r][p * slab : (p + 1) * slab] = peers[p][(me * rows + r) * slab : +slab]               (my rows, peer p's head slab)
+// The transposes that the NCCL path does with extra copies happen in the address arithmetic of the reads.
+__global__ void pull_all_to_all_kernel(const void* const* peers, int n_peers, int me, long long rows, int slab_vec, int to_heads,
+                                       uint4* out) {
+    const long long total = rows * n_peers * slab_vec;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int v = (int)(i % slab_vec);
+        const long long t = i / slab_vec;
+        if (to_heads) {
+            const long long r = t % rows;
+            const int p = (int)(t / rows);
+            out[i] = static_cast<const uint4*>(peers[p])[(r * n_peers + me) * slab_vec + v];
+        } else {
+            const int p = (int)(t % n_peers);
+            const long long r = t / n_peers;
+            out[i] = static_cast<const uint4*>(peers[p])[((long long)me * rows + r) * slab_vec + v];
+        }
+    }
+}
+
 int grid_for(long long items, int per_block) {
     long long b = (items + per_block - 1) / per_block;
     long long cap = 148LL * 8;
@@ -174,6 +196,14 @@ void pull_reduce_rows(int dtype, const void* const* peers, int n_peers, const in
         pull_reduce_kernel<__nv_bfloat16><<<grid_for(n_rows, 8), 256, 0, s>>>(peers, n_peers, src, static_cast<__nv_bfloat16*>(out), n_rows, width);
     else
         pull_reduce_kernel<float><<<grid_for(n_rows, 8), 256, 0, s>>>(peers, n_peers, src, static_cast<float*>(out), n_rows, width);
+}
+
+void pull_all_to_all(const void* const* peers, int n_peers, int me, long long rows, long long slab_bytes, bool to_heads, void* out,
+                     cudaStream_t s) {
+    const long long vecs = rows * n_peers * (slab_bytes / 16);
+    if (vecs <= 0) return;
+    pull_all_to_all_kernel<<<grid_for(vecs, 1024), 256, 0, s>>>(peers, n_peers, me, rows, (int)(slab_bytes / 16), to_heads ? 1 : 0,
+                                                                static_cast<uint4*>(out));
 }
 
 void pull_all_gather(const void* const* peers, int n_peers, void* out, long long chunk_bytes, cudaStream_t s) {

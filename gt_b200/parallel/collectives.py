@@ -39,6 +39,10 @@ def _p2p_ok(x, group, rows_out):
     return (per_rank * x.element_size()) % 16 == 0 and per_rank % 8 == 0
 
 
+def _a2a_p2p_ok(x, slab_elems):
+    return _HEAP[0] is not None and x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and (slab_elems * x.element_size()) % 16 == 0
+
+
 def _instrument(kind, group, nbytes, fn):
     hook = _STATS_HOOK[0]
     if hook is None:
@@ -108,6 +112,8 @@ def raw_rows_to_heads(x, group, p):
     if p == 1:
         return x
     chunk, h, d = x.shape
+    if _a2a_p2p_ok(x, (h // p) * d):
+        return _HEAP[0].rows_to_heads(x.contiguous(), group)
     send = x.view(chunk, p, h // p, d).transpose(0, 1).contiguous()
     return raw_all_to_all(send, group).view(p * chunk, h // p, d)
 
@@ -118,6 +124,8 @@ def raw_heads_to_rows(y, group, p):
         return y
     n, hg, d = y.shape
     chunk = n // p
+    if _a2a_p2p_ok(y, hg * d):
+        return _HEAP[0].heads_to_rows(y.contiguous(), group)
     recv = raw_all_to_all(y.contiguous().view(p, chunk, hg, d), group)
     return recv.transpose(0, 1).contiguous().view(chunk, p * hg, d)
 

@@ -180,6 +180,27 @@ class SymmetricHeap:
         c.barrier()
         return off, self.peer_table_cached(c, off)
 
+    def rows_to_heads(self, x, group):
+        """Ulysses all-to-all ``[chunk, H, d] -> [P * chunk, H / P, d]`` by strided peer reads (no transposed staging copies)."""
+        c = self.ctx(group)
+        chunk, h, d = x.shape
+        slab = (h // c.size) * d * x.element_size()
+        _, table = self.publish(x, group, "a2a_h")
+        out = torch.empty(c.size * chunk, h // c.size, d, dtype=x.dtype, device=x.device)
+        native.ext().pull_all_to_all(table, c.me, chunk, slab, True, out)
+        return out
+
+    def heads_to_rows(self, y, group):
+        """Inverse: ``[P * chunk, H / P, d] -> [chunk, H, d]``."""
+        c = self.ctx(group)
+        n, hg, d = y.shape
+        chunk = n // c.size
+        slab = hg * d * y.element_size()
+        _, table = self.publish(y, group, "a2a_r")
+        out = torch.empty(chunk, c.size * hg, d, dtype=y.dtype, device=y.device)
+        native.ext().pull_all_to_all(table, c.me, chunk, slab, False, out)
+        return out
+
     def all_reduce(self, x, out, name=None, group=None):
         """``out = sum over ranks of x``; ``x`` should live in the heap (``heap.empty``), otherwise it is staged."""
         c = self.ctx(group)

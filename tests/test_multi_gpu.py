@@ -69,6 +69,18 @@ def _collectives_worker(rank, world, store):
     (ref * torch.cat([w[0], w[1], w[2].float()], dim=1)).sum().backward()
     for g_, r_ in zip(got, (acc.grad, l.grad, ex.grad)):
         assert (g_.float() - r_.float()).abs().max() < 0.05
+    # Ulysses all-to-all by strided peer reads vs the NCCL all-to-all with transposes
+    from gt_b200.parallel.collectives import raw_heads_to_rows, raw_rows_to_heads, set_transport
+    xa = torch.randn(96, 4 * world, 16, device=dev).bfloat16()
+    set_transport(None)
+    ref_h = raw_rows_to_heads(xa, None, world)
+    ref_r = raw_heads_to_rows(ref_h, None, world)
+    set_transport(heap)
+    heap.begin_step()
+    got_h = raw_rows_to_heads(xa, None, world)
+    got_r = raw_heads_to_rows(got_h, None, world)
+    set_transport(None)
+    assert torch.equal(got_h, ref_h) and torch.equal(got_r, ref_r) and torch.equal(got_r, xa)
     # sparse plan: pull transport vs all-to-all-v transport
     need = torch.unique(torch.randint(0, world * 300, (200,), device=dev))
     plan_a = SparseRowPlan(None, 300, need, "t", "a2a")
