@@ -30,7 +30,9 @@ def main():
     ap.add_argument("--dims", nargs="+", default=["256:768", "256:256", "256:512", "512:256", "128:256"])
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--only", default=None, choices=[None, "nt", "tn", "gather"])
+    ap.add_argument("--only", default=None, choices=[None, "nt", "tn", "gather", "scatter"])
+    ap.add_argument("--scatter", type=int, default=0, metavar="G",
+                    help="also time the reduce-scatter-fused kernel with G owner slots that all live on this GPU")
     ap.add_argument("--gather", type=int, default=0, metavar="G",
                     help="also time the all-gather-fused kernel with G row chunks that all live on this GPU (the kernel's own "
                          "efficiency without the link; multi-GPU timing is in bench_collectives)")
@@ -68,6 +70,16 @@ def main():
             fused(True)
             ok = bool(torch.equal(xg, x)) and float((y.float() - (x @ w.t()).float()).abs().max()) < 0.05 * float((x @ w.t()).float().abs().max())
             out.update(gather_chunks=args.gather, gather_ms=ms, gather_tflops=flops / ms / 1e9, gather_copy_ms=ms_c, gather_ok=ok)
+        if args.scatter and m % args.scatter == 0 and n % 8 == 0:
+            g_ = args.scatter
+            chunk = m // g_
+            slots = torch.empty(g_, chunk, n, dtype=torch.bfloat16, device=dev)       # slot p = "owner p's" staging area for this rank
+            ptrs = [slots[i].data_ptr() for i in range(g_)]
+            e = native.ext()
+            ms = timeit(lambda: e.gemm_nt_scatter(x, w, ptrs, chunk, n, native.status(dev)), args.iters, args.warmup)
+            ref = (x @ w.t()).view(g_, chunk, n)
+            ok = float((slots.float() - ref.float()).abs().max()) < 0.05 * float(ref.float().abs().max())
+            out.update(scatter_slots=g_, scatter_ms=ms, scatter_tflops=flops / ms / 1e9, scatter_ok=ok)
         native.check_status(dev)
         print("GEMM " + json.dumps(out), flush=True)
 
