@@ -11,7 +11,17 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def install(src="/root/reference"):
+def reference_source():
+    """Where the reference checkout lives: ``GT_REFERENCE_SRC`` or the ``reference_path`` recorded in ``BASELINE.json``."""
+    if os.environ.get("GT_REFERENCE_SRC"):
+        return os.environ["GT_REFERENCE_SRC"]
+    import json
+    with open(os.path.join(os.path.dirname(HERE), "BASELINE.json")) as f:
+        return json.load(f)["reference_path"]
+
+
+def install(src=None):
+    src = src or reference_source()
     dst = os.path.join(HERE, "_ref")
     pkg = os.path.join(src, "gt3d", "gt3d")
     if not os.path.isdir(pkg):

@@ -30,7 +30,7 @@ def run_reference(args):
             from baseline.install_reference import install
             install()
         except SystemExit:
-            _unavailable("reference source not present: baseline/_ref missing and /root/reference not mounted")
+            _unavailable("reference source not present: baseline/_ref missing and the reference checkout is not mounted")
     sys.path.insert(0, os.path.join(HERE, "shims"))
     sys.path.insert(0, ref_dir)
     import torch
