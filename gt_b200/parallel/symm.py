@@ -38,16 +38,22 @@ class GroupContext:
         self.flags = heap.view(self.flags_off, (64,), torch.int32)
         self.counter = torch.zeros(1, dtype=torch.int32, device=heap.device)
         self.peer_flag_ptrs = heap.peer_table(self.flags_off, self.ranks)
-        self.seq = 0
-        self.buffers = {}                                       # (seq, kind) -> (offset, nbytes)
+        self.kind_count = {}                                    # collectives of each kind issued since begin_step
+        self.buffers = {}                                       # (kind, parity) -> (offset, nbytes)
 
     def barrier(self):
         native.ext().group_barrier(self.peer_flag_ptrs, self.flags, self.counter, self.me, MAX_SPINS, native.status(self.heap.device))
 
     def staging(self, nbytes, kind):
-        """Staging buffer of this call site (same offset on all ranks of the group)."""
-        key = (self.seq, kind)
-        self.seq += 1
+        """Staging buffer for the next collective of ``kind`` on this group (same offset on all ranks of the group).
+
+        Two buffers per kind are used alternately.  Every collective here is "write the buffer, group barrier, peers read (or:
+        peers write, barrier, owner reads)", so when a buffer comes up again two uses later, the barrier of the use in between
+        has been passed by every peer after it finished with the buffer: two buffers per kind are enough however many layers
+        a step has, and the heap does not grow with the depth of the model."""
+        n = self.kind_count.get(kind, 0)
+        self.kind_count[kind] = n + 1
+        key = (kind, n & 1)
         buf = self.buffers.get(key)
         if buf is None or buf[1] < nbytes:
             buf = (self.heap.alloc(nbytes), nbytes)
@@ -107,9 +113,10 @@ class SymmetricHeap:
         return c
 
     def begin_step(self):
-        """Call at the start of every step (before capture / replay): resets the call-site positions."""
+        """Call at the start of every step (before capture / replay): restarts the alternation of the staging buffers, so that
+        every step (eager, captured or replayed) uses the same offsets, and synchronises the groups."""
         for c in self.groups.values():
-            c.seq = 0
+            c.kind_count.clear()
             c.barrier()
 
     # ---- dense collectives ------------------------------------------------------------------------------------------------
@@ -206,7 +213,6 @@ class SymmetricHeap:
         c = self.ctx(group)
         if name is not None and name in self.named:
             off = self.named[name][0]
-            c.seq += 1
         else:
             off = c.staging(x.numel() * x.element_size(), "ar")
             self.view(off, x.shape, x.dtype).copy_(x)
