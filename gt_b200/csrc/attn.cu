@@ -90,8 +90,9 @@ template <typename T, int CPL, bool PEER, int SPEC = 0>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 6 : 3)) attn_fwd_kernel(AttnFwdArgs a) {
     extern __shared__ float smem[];
     const AttnCommon& c = a.c;
-    // SPEC = 1: 8 heads x 32 (the lane layout and every loop bound become compile-time constants)
-    const int H = SPEC ? 8 : c.H, D = SPEC ? 32 : c.D, HD = H * D;
+    // SPEC = number of heads of a specialised instance with head dim 32 (4, 8 or 16): the lane layout and every loop bound
+    // become compile-time constants; 0 = generic
+    const int H = SPEC ? SPEC : c.H, D = SPEC ? 32 : c.D, HD = H * D;
     float* s_gate = smem;
     float* s_bias = smem + (c.score == SCORE_GATED ? c.T * HD : 0);
     load_tables(c, s_gate, s_bias);
@@ -263,8 +264,9 @@ template <typename T, int CPL, int SPEC = 0>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 6 : 3)) attn_fwd_async_kernel(AttnFwdArgs a) {
     extern __shared__ float smem[];
     const AttnCommon& c = a.c;
-    // SPEC = 1: 8 heads x 32 (the lane layout and every loop bound become compile-time constants)
-    const int H = SPEC ? 8 : c.H, D = SPEC ? 32 : c.D, HD = H * D;
+    // SPEC = number of heads of a specialised instance with head dim 32 (4, 8 or 16): the lane layout and every loop bound
+    // become compile-time constants; 0 = generic
+    const int H = SPEC ? SPEC : c.H, D = SPEC ? 32 : c.D, HD = H * D;
     float* s_gate = smem;
     float* s_bias = smem + (c.score == SCORE_GATED ? c.T * HD : 0);
     load_tables(c, s_gate, s_bias);
@@ -533,8 +535,9 @@ template <typename T, int CPL, bool GATED, int SPEC = 0, bool ASYNC = false>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 4 : 2)) attn_bwd_row_kernel(AttnBwdRowArgs a) {
     extern __shared__ float smem[];
     const AttnCommon& c = a.c;
-    // SPEC = 1: 8 heads x 32 (the lane layout and every loop bound become compile-time constants)
-    const int H = SPEC ? 8 : c.H, D = SPEC ? 32 : c.D, HD = H * D;
+    // SPEC = number of heads of a specialised instance with head dim 32 (4, 8 or 16): the lane layout and every loop bound
+    // become compile-time constants; 0 = generic
+    const int H = SPEC ? SPEC : c.H, D = SPEC ? 32 : c.D, HD = H * D;
     float* s_gate = smem;
     float* s_bias = smem + (c.score == SCORE_GATED ? c.T * HD : 0);
     float* s_dg = s_bias + (c.score == SCORE_BIASED ? c.T * H : 0);      // [T, HD] or [T, H] block accumulators
@@ -787,8 +790,9 @@ template <typename T, int CPL, int SPEC = 0, bool ASYNC = false>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 4 : 5) : 2)) attn_bwd_col_kernel(AttnBwdColArgs a) {
     extern __shared__ float smem[];
     const AttnCommon& c = a.c;
-    // SPEC = 1: 8 heads x 32 (the lane layout and every loop bound become compile-time constants)
-    const int H = SPEC ? 8 : c.H, D = SPEC ? 32 : c.D, HD = H * D;
+    // SPEC = number of heads of a specialised instance with head dim 32 (4, 8 or 16): the lane layout and every loop bound
+    // become compile-time constants; 0 = generic
+    const int H = SPEC ? SPEC : c.H, D = SPEC ? 32 : c.D, HD = H * D;
     float* s_gate = smem;
     float* s_bias = smem + (c.score == SCORE_GATED ? c.T * HD : 0);
     load_tables(c, s_gate, s_bias);
@@ -1014,6 +1018,9 @@ size_t table_bytes(const AttnCommon& c) {
 
 int cpl_of(int H, int D) { return (H * D / 8) > 32 ? (H * D / 8) / 32 : 1; }
 
+// head count of a specialised kernel instance (head dim 32 and 4, 8 or 16 heads), else 0
+int spec_heads(int H, int D) { return (D == 32 && (H == 4 || H == 8 || H == 16)) ? H : 0; }
+
 template <typename K>
 void set_smem(K kernel, size_t bytes) {
     if (bytes > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
@@ -1052,16 +1059,18 @@ void attn_fwd(const AttnFwdArgs& a, cudaStream_t s) {
     if (use_async && !peer && c.dtype == DT_BF16) {
         const size_t ring = (size_t)kAsyncStages * kUnrollFwd * cpl * 2 * kWarpsPerBlock * 32 * 16;
         const size_t sma = ((sm + 15) & ~size_t(15)) + ring;
-        if (cpl == 1 && c.H == 8 && c.D == 32) {
-            set_smem(attn_fwd_async_kernel<__nv_bfloat16, 1, 1>, sma);
-            attn_fwd_async_kernel<__nv_bfloat16, 1, 1><<<blocks, kWarpsPerBlock * 32, sma, s>>>(a);
-        } else if (cpl == 1) {
-            set_smem(attn_fwd_async_kernel<__nv_bfloat16, 1>, sma);
-            attn_fwd_async_kernel<__nv_bfloat16, 1><<<blocks, kWarpsPerBlock * 32, sma, s>>>(a);
-        } else {
-            set_smem(attn_fwd_async_kernel<__nv_bfloat16, 2>, sma);
-            attn_fwd_async_kernel<__nv_bfloat16, 2><<<blocks, kWarpsPerBlock * 32, sma, s>>>(a);
-        }
+#define GT_LAUNCH_FWD_ASYNC(CPL, SP)                                                                  \
+    do {                                                                                              \
+        set_smem(attn_fwd_async_kernel<__nv_bfloat16, CPL, SP>, sma);                                 \
+        attn_fwd_async_kernel<__nv_bfloat16, CPL, SP><<<blocks, kWarpsPerBlock * 32, sma, s>>>(a);    \
+    } while (0)
+        const int sp = spec_heads(c.H, c.D);
+        if (cpl == 1 && sp == 8) GT_LAUNCH_FWD_ASYNC(1, 8);
+        else if (cpl == 1 && sp == 4) GT_LAUNCH_FWD_ASYNC(1, 4);
+        else if (cpl == 1) GT_LAUNCH_FWD_ASYNC(1, 0);
+        else if (sp == 16) GT_LAUNCH_FWD_ASYNC(2, 16);
+        else GT_LAUNCH_FWD_ASYNC(2, 0);
+#undef GT_LAUNCH_FWD_ASYNC
         if (c.plan.n_split > 0) {
             if (c.norm == NORM_CLAMPEXP)
                 attn_fwd_combine_sum_kernel<<<dim3(c.plan.n_split, (c.H * c.D + c.H + 31) / 32), dim3(32, 8), 0, s>>>(a);
@@ -1117,12 +1126,15 @@ void attn_bwd_row(const AttnBwdRowArgs& a, cudaStream_t s) {
                 a.accumulate_dq ? nullptr : static_cast<TT*>(a.dq), a.accumulate_dq ? static_cast<float*>(a.dq) : nullptr, \
                 a.accumulate_dq);                                                        \
     } while (0)
-    const bool spec = c.H == 8 && c.D == 32;
+    const int spec = spec_heads(c.H, c.D);
     if (c.dtype == DT_BF16) {
-        if (cpl == 1 && spec && use_async) GT_LAUNCH_ROW(__nv_bfloat16, 1, 1, true);
-        else if (cpl == 1 && spec) GT_LAUNCH_ROW(__nv_bfloat16, 1, 1, false);
+        if (cpl == 1 && spec == 8 && use_async) GT_LAUNCH_ROW(__nv_bfloat16, 1, 8, true);
+        else if (cpl == 1 && spec == 8) GT_LAUNCH_ROW(__nv_bfloat16, 1, 8, false);
+        else if (cpl == 1 && spec == 4 && use_async) GT_LAUNCH_ROW(__nv_bfloat16, 1, 4, true);
         else if (cpl == 1 && use_async) GT_LAUNCH_ROW(__nv_bfloat16, 1, 0, true);
         else if (cpl == 1) GT_LAUNCH_ROW(__nv_bfloat16, 1, 0, false);
+        else if (spec == 16 && use_async) GT_LAUNCH_ROW(__nv_bfloat16, 2, 16, true);
+        else if (use_async) GT_LAUNCH_ROW(__nv_bfloat16, 2, 0, true);
         else GT_LAUNCH_ROW(__nv_bfloat16, 2, 0, false);
     } else {
         if (cpl == 1) GT_LAUNCH_ROW(float, 1, 0, false); else GT_LAUNCH_ROW(float, 2, 0, false);
@@ -1149,12 +1161,15 @@ void attn_bwd_col(const AttnBwdColArgs& a, cudaStream_t s) {
             sum_slots_kv_kernel<TT><<<dim3(c.plan.n_split, (2 * HD + 31) / 32), dim3(32, 8), 0, s>>>(c.plan, c.scratch, HD, static_cast<TT*>(a.dk),       \
                                                                    static_cast<TT*>(a.dv));                              \
     } while (0)
-    const bool spec = c.H == 8 && c.D == 32;
+    const int spec = spec_heads(c.H, c.D);
     if (c.dtype == DT_BF16) {
-        if (cpl == 1 && spec && use_async) GT_LAUNCH_COL(__nv_bfloat16, 1, 1, true);
-        else if (cpl == 1 && spec) GT_LAUNCH_COL(__nv_bfloat16, 1, 1, false);
+        if (cpl == 1 && spec == 8 && use_async) GT_LAUNCH_COL(__nv_bfloat16, 1, 8, true);
+        else if (cpl == 1 && spec == 8) GT_LAUNCH_COL(__nv_bfloat16, 1, 8, false);
+        else if (cpl == 1 && spec == 4 && use_async) GT_LAUNCH_COL(__nv_bfloat16, 1, 4, true);
         else if (cpl == 1 && use_async) GT_LAUNCH_COL(__nv_bfloat16, 1, 0, true);
         else if (cpl == 1) GT_LAUNCH_COL(__nv_bfloat16, 1, 0, false);
+        else if (spec == 16 && use_async) GT_LAUNCH_COL(__nv_bfloat16, 2, 16, true);
+        else if (use_async) GT_LAUNCH_COL(__nv_bfloat16, 2, 0, true);
         else GT_LAUNCH_COL(__nv_bfloat16, 2, 0, false);
     } else {
         if (cpl == 1) GT_LAUNCH_COL(float, 1, 0, false); else GT_LAUNCH_COL(float, 2, 0, false);
