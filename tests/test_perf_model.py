@@ -84,3 +84,14 @@ def test_constants_overlay(tmp_path):
         assert gs.gemm_ms(2e9, 256) == pytest.approx(2.0)
     finally:
         gs.HW.clear(); gs.HW.update(keep)
+
+
+def test_model_tracks_the_measured_table():
+    """The shipped constants keep the model within a factor 1.6 of every measured row and rank the measured grids alike."""
+    from gt_b200.bench.model_validation_data import MEASURED
+    from gt_b200.bench.validate_model import predict
+    for row in MEASURED:
+        r = predict(row) / row["ms"]
+        assert 1 / 1.6 < r < 1.6, (row["grid"], r)
+    ms = [predict(r) for r in MEASURED if r["transport"] == "p2p"]
+    assert ms == sorted(ms, reverse=True)                        # more GPUs -> faster, as measured
