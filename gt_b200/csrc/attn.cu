@@ -260,8 +260,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 6 : 3)) attn_
 // Variant of the forward kernel whose K / V gathers go through a per-thread ring in shared memory filled by cp.async: the rows
 // of kAsyncStages - 1 edge groups are in flight per warp without occupying registers (the register variant holds one group).
 // Every lane copies and later reads only its own 16-byte chunks, so no synchronisation between lanes is needed.
-template <typename T, int CPL, int SPEC = 0>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 6 : 3)) attn_fwd_async_kernel(AttnFwdArgs a) {
+// (Measured on the arxiv-shaped block, 8 heads x 32: 2 edge groups x 4 stages 1.080 ms; 3 x 3 1.081; 4 x 3 1.213; 4 x 2 1.215;
+// 2 x 6 1.333: deeper rings cost resident blocks.)
+template <typename T, int CPL, int SPEC = 0, int UU = kUnrollFwd, int NSTG = kAsyncStages>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (UU * NSTG <= 8 ? 6 : 4) : 3)) attn_fwd_async_kernel(AttnFwdArgs a) {
     extern __shared__ float smem[];
     const AttnCommon& c = a.c;
     // SPEC = number of heads of a specialised instance with head dim 32 (4, 8 or 16): the lane layout and every loop bound
@@ -272,7 +274,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 6 : 3)) attn_
     load_tables(c, s_gate, s_bias);
     // ring: [stage][edge slot u][chunk i][K | V][thread] x 16 bytes, after the tables (16-byte aligned)
     uint4* ring = reinterpret_cast<uint4*>(smem + ((table_floats(c) + 3) & ~3));
-    constexpr int NST = kAsyncStages;
+    constexpr int NST = NSTG;
     const Lanes L = make_lanes(HD, D);
     const T* q = static_cast<const T*>(a.q);
     const T* kb = static_cast<const T*>(a.k);
@@ -280,7 +282,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 6 : 3)) attn_
     const bool softmax = c.norm == NORM_SOFTMAX;
     const bool head_writer = (L.ll & (L.lph - 1)) == 0;
     using Raw = typename Vec8<T>::Raw;
-    constexpr int U = kUnrollFwd;
+    constexpr int U = UU;
     int foff[CPL], head[CPL];
 #pragma unroll
     for (int i = 0; i < CPL; ++i) { foff[i] = (L.ll + L.lpr * i) << 3; head[i] = foff[i] / D; }
