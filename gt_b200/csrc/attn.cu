@@ -275,6 +275,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (UU * NSTG <=
     // ring: [stage][edge slot u][chunk i][K | V][thread] x 16 bytes, after the tables (16-byte aligned)
     uint4* ring = reinterpret_cast<uint4*>(smem + ((table_floats(c) + 3) & ~3));
     constexpr int NST = NSTG;
+    int* tring = reinterpret_cast<int*>(ring + (size_t)NSTG * UU * CPL * 2 * (kWarpsPerBlock * 32));      // edge types of the groups in flight
     const Lanes L = make_lanes(HD, D);
     const T* q = static_cast<const T*>(a.q);
     const T* kb = static_cast<const T*>(a.k);
@@ -304,25 +305,37 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (UU * NSTG <=
         float qg[CPL][8];                 // q * scale * gate[type] of the type currently cached
         int gt_cached = -1;
         const int n_it = (end - beg + U * L.epw - 1) / (U * L.epw);
-        // issue(it): start the copies of group `it` into ring stage it % NST (one commit group per call, also when empty)
-        auto issue = [&](int it) {
-            if (it < n_it) {
+        // Software pipeline: fetch(g) loads the source indices / types of edge group g into registers one iteration before
+        // issue(g) starts that group's copies into ring stage g % NST and parks the types next to them, so neither the copies
+        // nor the arithmetic ever wait on an index load.  One commit group per issue() call, also when it is empty.
+        int jn[U], tn[U];
+        auto fetch = [&](int g) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int e = min(beg + (g * U + u) * L.epw + L.sub, end - 1);  // padding slots reuse the last edge; their weight is zero
+                jn[u] = c.idx[e];
+                tn[u] = c.etype ? c.etype[e] : 0;
+            }
+        };
+        auto issue = [&](int g) {
+            if (g < n_it) {
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
-                    const int e = beg + (it * U + u) * L.epw + L.sub;
-                    const int jj = e < end ? c.idx[e] : c.idx[beg];            // padding slots copy a valid row; their weight is zero
-                    const T* kp = kb + (size_t)jj * HD;
-                    const T* vp = vb + (size_t)jj * HD;
+                    const T* kp = kb + (size_t)jn[u] * HD;
+                    const T* vp = vb + (size_t)jn[u] * HD;
 #pragma unroll
                     for (int i = 0; i < CPL; ++i) {
-                        uint4* dst = ring + ((((it % NST) * U + u) * CPL + i) * 2) * (kWarpsPerBlock * 32) + threadIdx.x;
+                        uint4* dst = ring + ((((g % NST) * U + u) * CPL + i) * 2) * (kWarpsPerBlock * 32) + threadIdx.x;
                         cp_async16(dst, kp + foff[i]);
                         cp_async16(dst + kWarpsPerBlock * 32, vp + foff[i]);
                     }
+                    tring[((g % NST) * U + u) * (kWarpsPerBlock * 32) + threadIdx.x] = tn[u];
                 }
+                if (g + 1 < n_it) fetch(g + 1);
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
+        fetch(0);
 #pragma unroll
         for (int it = 0; it < NST - 1; ++it) issue(it);
         for (int it = 0; it < n_it; ++it) {
@@ -334,7 +347,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (UU * NSTG <=
             for (int u = 0; u < U; ++u) {
                 const int e = beg + (it * U + u) * L.epw + L.sub;
                 j[u] = e < end ? 0 : -1;
-                t[u] = (e < end && c.etype) ? c.etype[e] : (gt_cached >= 0 ? gt_cached : 0);
+                t[u] = tring[((it % NST) * U + u) * (kWarpsPerBlock * 32) + threadIdx.x];
 #pragma unroll
                 for (int i = 0; i < CPL; ++i) {
                     const uint4* src = ring + ((((it % NST) * U + u) * CPL + i) * 2) * (kWarpsPerBlock * 32) + threadIdx.x;
@@ -1059,7 +1072,7 @@ void attn_fwd(const AttnFwdArgs& a, cudaStream_t s) {
     const int cpl = cpl_of(c.H, c.D);
     static const bool use_async = [] { const char* e = getenv("GT_ATTN_ASYNC"); return !(e && e[0] == '0'); }();
     if (use_async && !peer && c.dtype == DT_BF16) {
-        const size_t ring = (size_t)kAsyncStages * kUnrollFwd * cpl * 2 * kWarpsPerBlock * 32 * 16;
+        const size_t ring = (size_t)kAsyncStages * kUnrollFwd * (cpl * 2 * 16 + 4) * kWarpsPerBlock * 32;   // data ring + type ring
         const size_t sma = ((sm + 15) & ~size_t(15)) + ring;
 #define GT_LAUNCH_FWD_ASYNC(CPL, SP)                                                                  \
     do {                                                                                              \
