@@ -574,6 +574,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 4 : 2)) attn_
     constexpr int NST = kAsyncStages;
     // ASYNC: K / V gathers through a per-thread cp.async ring placed after the tables and the block accumulators
     uint4* ring = reinterpret_cast<uint4*>(smem + ((table_floats(c) + acc_n + 3) & ~3));
+    int* tring = reinterpret_cast<int*>(ring + (size_t)kAsyncStages * kUnrollRow * CPL * 2 * (kWarpsPerBlock * 32));   // types of the groups in flight
 
     int foff[CPL], head[CPL];
 #pragma unroll
@@ -602,24 +603,33 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 4 : 2)) attn_
         float qg[CPL][8];
         int gt_cached = -1;
         const int n_it = (end - beg + U * L.epw - 1) / (U * L.epw);
-        auto issue = [&](int it) {                      // ASYNC: start the copies of edge group `it` (one commit group per call)
-            if (it < n_it) {
+        int jn[U], tn[U];
+        auto fetch = [&](int g) {                       // ASYNC: indices / types of edge group g, one iteration ahead of issue(g)
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int e = min(beg + (g * U + u) * L.epw + L.sub, end - 1);  // padding slots reuse the last edge; their weight is zero
+                jn[u] = c.idx[e];
+                tn[u] = c.etype ? c.etype[e] : 0;
+            }
+        };
+        auto issue = [&](int g) {                       // ASYNC: start the copies of edge group g (one commit group per call)
+            if (g < n_it) {
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
-                    const int e = beg + (it * U + u) * L.epw + L.sub;
-                    const int jj = e < end ? c.idx[e] : c.idx[beg];            // padding slots copy a valid row; their weight is zero
 #pragma unroll
                     for (int i = 0; i < CPL; ++i) {
-                        uint4* dst = ring + ((((it % NST) * U + u) * CPL + i) * 2) * (kWarpsPerBlock * 32) + threadIdx.x;
-                        cp_async16(dst, kb + (size_t)jj * HD + foff[i]);
-                        cp_async16(dst + kWarpsPerBlock * 32, vb + (size_t)jj * HD + foff[i]);
+                        uint4* dst = ring + ((((g % NST) * U + u) * CPL + i) * 2) * (kWarpsPerBlock * 32) + threadIdx.x;
+                        cp_async16(dst, kb + (size_t)jn[u] * HD + foff[i]);
+                        cp_async16(dst + kWarpsPerBlock * 32, vb + (size_t)jn[u] * HD + foff[i]);
                     }
+                    tring[((g % NST) * U + u) * (kWarpsPerBlock * 32) + threadIdx.x] = tn[u];
                 }
+                if (g + 1 < n_it) fetch(g + 1);
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
-        int jn[U], tn[U];
         if constexpr (ASYNC) {
+            fetch(0);
 #pragma unroll
             for (int it = 0; it < NST - 1; ++it) issue(it);
         } else {
@@ -641,7 +651,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 4 : 2)) attn_
                 for (int u = 0; u < U; ++u) {
                     const int e = base + u * L.epw + L.sub;
                     j[u] = e < end ? 0 : -1;
-                    t[u] = (e < end && c.etype) ? c.etype[e] : 0;
+                    t[u] = tring[((it % NST) * U + u) * (kWarpsPerBlock * 32) + threadIdx.x];
 #pragma unroll
                     for (int i = 0; i < CPL; ++i) {
                         const uint4* src = ring + ((((it % NST) * U + u) * CPL + i) * 2) * (kWarpsPerBlock * 32) + threadIdx.x;
@@ -820,6 +830,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 4 : 
     constexpr int NST = kAsyncStages;
     // ASYNC: q / row-vector / row-statistics gathers through a per-thread cp.async ring placed after the tables
     uint4* ring = reinterpret_cast<uint4*>(smem + ((table_floats(c) + 3) & ~3));
+    int* tring = reinterpret_cast<int*>(ring + (size_t)kAsyncStages * kUnrollCol * CPL * 3 * (kWarpsPerBlock * 32));   // types of the groups in flight
     int foff[CPL], head[CPL];
 #pragma unroll
     for (int i = 0; i < CPL; ++i) { foff[i] = (L.ll + L.lpr * i) << 3; head[i] = foff[i] / D; }
@@ -839,25 +850,34 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 4 : 
         float gc[CPL][8], kg[CPL][8];       // cached gate slice and k * gate of the type currently being walked
         int gt_cached = -1;
         const int n_it = (end - beg + U * L.epw - 1) / (U * L.epw);
-        auto issue = [&](int it) {                      // ASYNC: start the copies of entry group `it` (one commit group per call)
-            if (it < n_it) {
+        int rn[U], tn[U];
+        auto fetch = [&](int g) {                       // ASYNC: row indices / types of entry group g, one iteration ahead of issue(g)
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int e = min(beg + (g * U + u) * L.epw + L.sub, end - 1);  // padding slots reuse the last entry; their weight is zero
+                rn[u] = c.idx[e];
+                tn[u] = c.etype ? c.etype[e] : 0;
+            }
+        };
+        auto issue = [&](int g) {                       // ASYNC: start the copies of entry group g (one commit group per call)
+            if (g < n_it) {
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
-                    const int e = beg + (it * U + u) * L.epw + L.sub;
-                    const int rr_ = e < end ? c.idx[e] : c.idx[beg];           // padding slots copy a valid row; their weight is zero
 #pragma unroll
                     for (int i = 0; i < CPL; ++i) {
-                        uint4* dst = ring + ((((it % NST) * U + u) * CPL + i) * 3) * (kWarpsPerBlock * 32) + threadIdx.x;
-                        cp_async16(dst, qb + (size_t)rr_ * HD + foff[i]);
-                        cp_async16(dst + kWarpsPerBlock * 32, rvb + (size_t)rr_ * HD + foff[i]);
-                        cp_async16(dst + 2 * kWarpsPerBlock * 32, a.stat + (size_t)rr_ * H + head[i]);
+                        uint4* dst = ring + ((((g % NST) * U + u) * CPL + i) * 3) * (kWarpsPerBlock * 32) + threadIdx.x;
+                        cp_async16(dst, qb + (size_t)rn[u] * HD + foff[i]);
+                        cp_async16(dst + kWarpsPerBlock * 32, rvb + (size_t)rn[u] * HD + foff[i]);
+                        cp_async16(dst + 2 * kWarpsPerBlock * 32, a.stat + (size_t)rn[u] * H + head[i]);
                     }
+                    tring[((g % NST) * U + u) * (kWarpsPerBlock * 32) + threadIdx.x] = tn[u];
                 }
+                if (g + 1 < n_it) fetch(g + 1);
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
-        int rn[U], tn[U];
         if constexpr (ASYNC) {
+            fetch(0);
 #pragma unroll
             for (int it = 0; it < NST - 1; ++it) issue(it);
         } else {
@@ -880,7 +900,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 4 : 
                 for (int u = 0; u < U; ++u) {
                     const int e = base + u * L.epw + L.sub;
                     r[u] = e < end ? 0 : -1;
-                    t[u] = (e < end && c.etype) ? c.etype[e] : (gt_cached >= 0 ? gt_cached : 0);
+                    t[u] = tring[((it % NST) * U + u) * (kWarpsPerBlock * 32) + threadIdx.x];
 #pragma unroll
                     for (int i = 0; i < CPL; ++i) {
                         const uint4* src = ring + ((((it % NST) * U + u) * CPL + i) * 3) * (kWarpsPerBlock * 32) + threadIdx.x;
@@ -1125,7 +1145,7 @@ void attn_bwd_row(const AttnBwdRowArgs& a, cudaStream_t s) {
     const int cpl = cpl_of(c.H, c.D);
     const int HD = c.H * c.D;
     static const bool use_async = [] { const char* e = getenv("GT_ATTN_ASYNC"); return !(e && e[0] == '0'); }();
-    const size_t ring_bytes = (size_t)kAsyncStages * kUnrollRow * cpl * 2 * kWarpsPerBlock * 32 * 16;
+    const size_t ring_bytes = (size_t)kAsyncStages * kUnrollRow * (cpl * 2 * 16 + 4) * kWarpsPerBlock * 32;   // data ring + type ring
 #define GT_LAUNCH_ROW(TT, CPL, SP, AS)                                                        \
     do {                                                                                 \
         if (c.score == SCORE_GATED) {                                                    \
@@ -1166,7 +1186,7 @@ void attn_bwd_col(const AttnBwdColArgs& a, cudaStream_t s) {
     const int cpl = cpl_of(c.H, c.D);
     const int HD = c.H * c.D;
     static const bool use_async = [] { const char* e = getenv("GT_ATTN_ASYNC"); return !(e && e[0] == '0'); }();
-    const size_t ring_bytes = (size_t)kAsyncStages * kUnrollCol * cpl * 3 * kWarpsPerBlock * 32 * 16;
+    const size_t ring_bytes = (size_t)kAsyncStages * kUnrollCol * (cpl * 3 * 16 + 4) * kWarpsPerBlock * 32;   // data ring + type ring
 #define GT_LAUNCH_COL(TT, CPL, SP, AS)                                                        \
     do {                                                                                 \
         const size_t smc = AS ? ((sm + 15) & ~size_t(15)) + ring_bytes : sm;             \
