@@ -547,7 +547,7 @@ __device__ __forceinline__ void flush_type_run(const float* s_gate, float* s_dg,
 }
 
 template <typename T, int CPL, bool GATED, int SPEC = 0, bool ASYNC = false>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 4 : 2)) attn_bwd_row_kernel(AttnBwdRowArgs a) {
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 5 : 4) : 2)) attn_bwd_row_kernel(AttnBwdRowArgs a) {
     extern __shared__ float smem[];
     const AttnCommon& c = a.c;
     // SPEC = number of heads of a specialised instance with head dim 32 (4, 8 or 16): the lane layout and every loop bound
