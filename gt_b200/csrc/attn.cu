@@ -1212,6 +1212,39 @@ void attn_bwd_col(const AttnBwdColArgs& a, cudaStream_t s) {
 #undef GT_LAUNCH_COL
 }
 
+namespace {
+template <typename K>
+KernelInfo info_of(const char* name, K kernel, size_t dyn_smem) {
+    KernelInfo r{name, 0, 0, 0, (int)dyn_smem, 0};
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, kernel) != cudaSuccess) { cudaGetLastError(); return r; }
+    set_smem(kernel, dyn_smem);
+    r.regs = fa.numRegs; r.local_bytes = (int)fa.localSizeBytes; r.static_smem = (int)fa.sharedSizeBytes;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&r.blocks_per_sm, kernel, kWarpsPerBlock * 32, dyn_smem) != cudaSuccess) cudaGetLastError();
+    return r;
+}
+}  // namespace
+
+// Compiled resources of the attention kernels that serve bf16 operands with 8 heads of 32 (the specialised instances) and of
+// the generic instances: registers per thread, local-memory bytes, shared memory and resident blocks per SM.
+std::vector<KernelInfo> attn_kernel_info() {
+    const size_t tbl = (size_t)3 * 256 * sizeof(float);                     // gate table of 3 edge types x 256 channels
+    const size_t per_thread = (size_t)kWarpsPerBlock * 32;
+    const size_t ring_f = (size_t)kAsyncStages * kUnrollFwd * (2 * 16 + 4) * per_thread;
+    const size_t ring_r = (size_t)kAsyncStages * kUnrollRow * (2 * 16 + 4) * per_thread;
+    const size_t ring_c = (size_t)kAsyncStages * kUnrollCol * (3 * 16 + 4) * per_thread;
+    std::vector<KernelInfo> v;
+    v.push_back(info_of("fwd_ring_bf16_8x32", attn_fwd_async_kernel<__nv_bfloat16, 1, 8>, tbl + ring_f));
+    v.push_back(info_of("fwd_ring_bf16_generic", attn_fwd_async_kernel<__nv_bfloat16, 1, 0>, tbl + ring_f));
+    v.push_back(info_of("fwd_regs_bf16", attn_fwd_kernel<__nv_bfloat16, 1, false>, tbl));
+    v.push_back(info_of("fwd_regs_fp32", attn_fwd_kernel<float, 1, false>, tbl));
+    v.push_back(info_of("row_ring_bf16_8x32", attn_bwd_row_kernel<__nv_bfloat16, 1, true, 8, true>, 2 * tbl + ring_r));
+    v.push_back(info_of("row_regs_bf16_8x32", attn_bwd_row_kernel<__nv_bfloat16, 1, true, 8, false>, 2 * tbl));
+    v.push_back(info_of("col_ring_bf16_8x32", attn_bwd_col_kernel<__nv_bfloat16, 1, 8, true>, tbl + ring_c));
+    v.push_back(info_of("col_regs_bf16_8x32", attn_bwd_col_kernel<__nv_bfloat16, 1, 8, false>, tbl));
+    return v;
+}
+
 void reduce_partials(const float* part, int n_blocks, int width, float* out, cudaStream_t s) {
     if (width <= 0) return;
     reduce_partials_kernel<<<(width + 31) / 32, dim3(32, 8), 0, s>>>(part, n_blocks, width, out);

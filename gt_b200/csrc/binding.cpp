@@ -115,6 +115,14 @@ void reduce_partials(Tensor part, Tensor out) {
     gt::reduce_partials(part.data_ptr<float>(), (int)part.size(0), (int)out.numel(), out.data_ptr<float>(), stream());
 }
 
+// (name, registers, local bytes, static shared, dynamic shared, resident blocks per SM) of the main attention kernel instances
+std::vector<std::tuple<std::string, int64_t, int64_t, int64_t, int64_t, int64_t>> attn_kernel_info() {
+    std::vector<std::tuple<std::string, int64_t, int64_t, int64_t, int64_t, int64_t>> out;
+    for (const auto& k : gt::attn_kernel_info())
+        out.emplace_back(std::string(k.name), k.regs, k.local_bytes, k.static_smem, k.dyn_smem, k.blocks_per_sm);
+    return out;
+}
+
 bool attn_shape_supported(int64_t H, int64_t D, int64_t T) { return gt::attn_shape_supported((int)H, (int)D, (int)T); }
 
 void spmm(Tensor ptr, Tensor idx, OptT w, Tensor x, Tensor out, bool accumulate, std::vector<Tensor> plan, OptT scratch) {
@@ -493,6 +501,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("attn_bwd_row_blocks", &attn_bwd_row_blocks);
     m.def("attn_bwd_col", &attn_bwd_col);
     m.def("attn_shape_supported", &attn_shape_supported);
+    m.def("attn_kernel_info", &attn_kernel_info);
     m.def("reduce_partials", &reduce_partials);
     m.def("spmm", &spmm);
     m.def("layer_norm_fwd", &layer_norm_fwd);

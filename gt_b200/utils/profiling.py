@@ -2,13 +2,15 @@
 
 ``kernel_profile`` is the ``--profile`` switch of the trainer (reference: ``_profile_totals``,
 ``gt3d/gt3d/train/train_dist.py:29-75``): device time per kernel name for one epoch, grouped into the categories the
-performance model uses (attention, SpMM, GEMM, norm / elementwise, collectives, optimizer, other).
+performance model uses (attention, SpMM, GEMM, norm / elementwise, collectives, optimizer, other).  With the environment
+variable ``GT_PROF_TRACE=<prefix>`` it also writes the chrome trace of the epoch to ``<prefix>_rank<r>.json``.
 ``saved_tensor_census`` is ``--saved_census`` (reference ``_saved_census``, ``train_dist.py:78-118``): every tensor saved
 for backward during one forward, deduplicated by storage, in units of one fp32 owned chunk ``[N/P, d]``; the memory
 model's per-layer multipliers are read off this table.
 """
 import collections
 import contextlib
+import os
 
 import torch
 import torch.distributed as dist
@@ -39,6 +41,9 @@ def kernel_profile(rank=0, world=1, top=25, file=None):
         yield
         if torch.cuda.is_available():
             torch.cuda.synchronize()
+    trace = os.environ.get("GT_PROF_TRACE")
+    if trace:                                       # chrome trace per rank, for gt_b200.bench.analyze_trace
+        prof.export_chrome_trace(f"{trace}_rank{rank}.json")
     per_kernel, per_cat = collections.Counter(), collections.Counter()
     calls = collections.Counter()
     for ev in prof.events():
