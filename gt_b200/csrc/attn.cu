@@ -335,7 +335,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (UU * NSTG <=
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
-        fetch(0);
+        if (n_it > 0) fetch(0);             // an empty segment has no edge to read, and idx[beg - 1] may lie before the array
 #pragma unroll
         for (int it = 0; it < NST - 1; ++it) issue(it);
         for (int it = 0; it < n_it; ++it) {
@@ -629,7 +629,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 5 : 
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
         if constexpr (ASYNC) {
-            fetch(0);
+            if (n_it > 0) fetch(0);
 #pragma unroll
             for (int it = 0; it < NST - 1; ++it) issue(it);
         } else {
@@ -877,7 +877,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 4 : 
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
         if constexpr (ASYNC) {
-            fetch(0);
+            if (n_it > 0) fetch(0);
 #pragma unroll
             for (int it = 0; it < NST - 1; ++it) issue(it);
         } else {

@@ -54,7 +54,7 @@ gt::AttnCommon make_common(const Tensor& q, int64_t H, int64_t D, const Tensor& 
     c.plan = make_plan(plan);
     c.scratch = scratch.has_value() && scratch->defined() ? scratch->data_ptr<float>() : nullptr;
     TORCH_CHECK(gt::attn_shape_supported(c.H, c.D, c.T), "attention shape (H=", H, ", D=", D, ", T=", c.T, ") not supported by the kernels");
-    if (c.score != gt::SCORE_DOT) TORCH_CHECK(c.etype != nullptr, "gated / biased scores need edge types");
+    if (c.score != gt::SCORE_DOT && idx.numel() > 0) TORCH_CHECK(c.etype != nullptr, "gated / biased scores need edge types");
     return c;
 }
 

@@ -50,6 +50,9 @@ HW = dict(
     # tensors kept for backward per layer, in units of one bf16 block of the named extent x d
     saved=dict(own=11.0, own_mask=0.0, row=2.0, col=3.0, head_own=14.0, stats_per_row=12.0),
     struct_bytes_per_edge=22.0,     # CSR + CSC (int32 indices, uint8 types, int32 permutation) + segment plans
+    # analytic model of a gather pass (attn_theory_ms): fixed ns per row and achieved share of hbm_gbs on long rows, from the
+    # regular-block degree sweep of gt_b200.bench.kernel_theory (262,144 rows, 8 x 32 bf16)
+    theory=dict(fwd=dict(tau_ns=0.41, bw_eff=0.89), bwd=dict(tau_ns=1.30, bw_eff=0.68)),
 )
 
 _DEFAULT_JSON = os.path.join(os.path.dirname(__file__), "b200_constants.json")
@@ -225,6 +228,26 @@ def attn_ms(e, rows, cols, heads, d_head, direction, skew=1.0):
     ce, cr, cc = (w * x + (1 - w) * y for x, y in zip(a, b))
     n_k = 1 if direction == "fwd" else 3
     return (ce * e * skew + cr * rows + cc * cols) * scale / 1e6 + n_k * HW["kernel_gap_us"] / 1e3
+
+
+def attn_theory_bytes(e, rows, width, direction, elem=2):
+    """Bytes an ideal gather pass without cache reuse moves: per edge the gathered rows and index / type words, per row
+    its own operands and results (forward: K and V per edge, q in, fp32 acc + statistics out; backward: twice that per
+    edge for the row and the column pass, six operand / result rows per node)."""
+    if direction == "fwd":
+        return e * (2 * width * elem + 8) + rows * (width * elem + width * 4 + 32)
+    return 2 * e * (2 * width * elem + 8) + rows * (6 * width * elem + 64)
+
+
+def attn_theory_ms(e, rows, heads, d_head, direction):
+    """First-principles time of a gather pass on operands larger than L2: a fixed cost per row (the latency of the row's
+    pointer / q / result chain, ``tau_ns``) plus the pass's bytes over the achieved share of the memory bandwidth.  Two
+    constants per pass instead of the fitted slopes of ``attn_ms``; it extrapolates over widths (bytes scale, ``tau``
+    does not) and is exact to a few percent on the forward sweep (reference: ``THEORY`` / ``_theory_pass_ms``,
+    ``gt3d/gt3d/perf/grid_select.py:376-426``)."""
+    th = HW["theory"][direction]
+    nbytes = attn_theory_bytes(e, rows, heads * d_head, direction)
+    return (rows * th["tau_ns"] + nbytes / (HW["hbm_gbs"] * th["bw_eff"])) / 1e6
 
 
 def spmm_ms(e, rows, cols, d, skew=1.0):

@@ -95,3 +95,24 @@ def test_model_tracks_the_measured_table():
         assert 1 / 1.6 < r < 1.6, (row["grid"], r)
     ms = [predict(r) for r in MEASURED if r["transport"] == "p2p"]
     assert ms == sorted(ms, reverse=True)                        # more GPUs -> faster, as measured
+
+
+def test_analytic_gather_model_against_the_measured_degree_sweep():
+    """``attn_theory_ms`` (two constants per pass) against the regular-block sweep measured on a B200."""
+    import json
+    import os
+    import gt_b200.bench as bench_pkg
+    from gt_b200.perf import grid_select as gs
+    with open(os.path.join(os.path.dirname(bench_pkg.__file__), "kernel_theory_b200.json")) as f:
+        sweep = json.load(f)
+    n = sweep["rows"]
+    for row in sweep["sweep"]:
+        fwd = gs.attn_theory_ms(row["edges"], n, sweep["heads"], sweep["head_dim"], "fwd")
+        bwd = gs.attn_theory_ms(row["edges"], n, sweep["heads"], sweep["head_dim"], "bwd")
+        assert abs(fwd / row["fwd_ms"] - 1) < 0.20, (row["degree"], fwd, row["fwd_ms"])
+        assert abs(bwd / row["bwd_ms"] - 1) < 0.32, (row["degree"], bwd, row["bwd_ms"])
+        if row["degree"] >= 32:
+            assert abs(fwd / row["fwd_ms"] - 1) < 0.06 and abs(bwd / row["bwd_ms"] - 1) < 0.06
+    # bytes scale with the width, the per-row latency does not
+    wide = gs.attn_theory_ms(n * 64, n, 16, 32, "fwd")
+    assert 1.9 < wide / gs.attn_theory_ms(n * 64, n, 8, 32, "fwd") < 2.0
