@@ -263,6 +263,20 @@ def heads_to_rows(y, group, p):
     return _HeadsToRows.apply(y, group, p)
 
 
+def _sum_over_ranks(x, group):
+    """Sum of ``x`` over the group in a new tensor.  Small CUDA payloads (normalisation statistics, loss terms) take the
+    one-shot peer-memory all-reduce when the peer-memory transport is on: one kernel that reads every rank's buffer."""
+    if group_size(group) == 1:
+        return x.clone()
+    h = _HEAP[0]
+    if h is not None and x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and x.numel() % 8 == 0 and x.numel() > 0:
+        x = x.contiguous()
+        return _instrument("all_reduce", group, x.numel() * x.element_size(), lambda: h.all_reduce(x, torch.empty_like(x), group=group))
+    y = x.clone()
+    dist.all_reduce(y, group=group)
+    return y
+
+
 class _AllReduceSum(torch.autograd.Function):
     """``y = sum over ranks of x`` where every rank consumes ``y``: the gradient w.r.t. the local ``x`` is the sum over
     ranks of the upstream gradients."""
@@ -270,17 +284,11 @@ class _AllReduceSum(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, group):
         ctx.group = group
-        y = x.clone()
-        if group_size(group) > 1:
-            dist.all_reduce(y, group=group)
-        return y
+        return _sum_over_ranks(x, group)
 
     @staticmethod
     def backward(ctx, g):
-        g = g.contiguous().clone()
-        if group_size(ctx.group) > 1:
-            dist.all_reduce(g, group=ctx.group)
-        return g, None
+        return _sum_over_ranks(g.contiguous(), ctx.group), None
 
 
 def all_reduce_sum(x, group=None):

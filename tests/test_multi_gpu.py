@@ -81,6 +81,20 @@ def _collectives_worker(rank, world, store):
     got_r = raw_heads_to_rows(got_h, None, world)
     set_transport(None)
     assert torch.equal(got_h, ref_h) and torch.equal(got_r, ref_r) and torch.equal(got_r, xa)
+    # statistics all-reduce (BatchNorm sums) by the one-shot peer kernel, forward and backward, vs NCCL
+    from gt_b200.parallel.collectives import all_reduce_sum
+    st = torch.randn(4 * 64, device=dev)
+    res = {}
+    for name, tr in (("nccl", None), ("p2p", heap)):
+        set_transport(tr)
+        heap.begin_step()
+        leaf = st.clone().requires_grad_()
+        y = all_reduce_sum(leaf)
+        (y * (rank + 1.0)).sum().backward()
+        res[name] = (y.detach().clone(), leaf.grad.clone())
+    set_transport(None)
+    assert (res["p2p"][0] - res["nccl"][0]).abs().max() < 1e-5 and (res["p2p"][1] - res["nccl"][1]).abs().max() < 1e-5
+    assert abs(float(res["p2p"][1][0]) - world * (world + 1) / 2) < 1e-5
     # sparse plan: pull transport vs all-to-all-v transport
     need = torch.unique(torch.randint(0, world * 300, (200,), device=dev))
     plan_a = SparseRowPlan(None, 300, need, "t", "a2a")
