@@ -1,7 +1,8 @@
 """Per-epoch census of the collectives a training step issues: calls, payload bytes and (on GPUs) device time per kind
 and group size.  The counterpart of the reference trainer's ``--coll_stats`` (``gt3d/gt3d/train/train_dist.py:120-190``),
-which patches ``torch.distributed``; here the peer-memory transport (``gt_b200.parallel.symm``) is counted too, so both
-``--comm nccl`` and ``--comm p2p`` runs report the same table.
+which patches ``torch.distributed``; here the methods of the peer-memory transport (``gt_b200.parallel.symm.SymmetricHeap``)
+are patched the same way and reported under ``p2p_*`` kinds (the collectives fused into GEMMs included), so ``--comm nccl``
+and ``--comm p2p`` runs both give a complete table.
 
 Device time is taken with one CUDA-event pair per call (recorded on the launching stream, read after the epoch), so the
 census itself adds no host synchronisation inside the step; it is not usable under CUDA-graph capture.
@@ -21,6 +22,20 @@ _KINDS = {
 }
 
 
+# methods of the symmetric heap (peer-memory transport): name -> (kind, where the group is: argument index or "plan")
+_HEAP_KINDS = {
+    "all_gather": ("p2p_all_gather", 1),
+    "reduce_scatter": ("p2p_reduce_scatter", 1),
+    "all_reduce": ("p2p_all_reduce", 3),
+    "rows_to_heads": ("p2p_all_to_all", 1),
+    "heads_to_rows": ("p2p_all_to_all", 1),
+    "linear_gather": ("p2p_gather+gemm", 2),
+    "linear_scatter": ("p2p_gemm+scatter", 2),
+    "pull_gather": ("p2p_sparse_gather", "plan"),
+    "pull_reduce": ("p2p_sparse_reduce", "plan"),
+}
+
+
 def _group_size(kw):
     g = kw.get("group")
     return dist.get_world_size(g) if g is not None else dist.get_world_size()
@@ -34,6 +49,7 @@ class CollectiveStats:
         self.epochs = 0
         self._pending = []
         self._orig = {}
+        self._orig_heap = {}
         self._cur = None
 
     # ---- patching ------------------------------------------------------------------------------------------------------
@@ -55,6 +71,26 @@ class CollectiveStats:
             return out
         return wrapped
 
+    def _wrap_heap(self, name, fn, kind, where):
+        def wrapped(heap, *a, **kw):
+            t = a[0]
+            if where == "plan":
+                group = a[1].group
+            else:
+                group = kw.get("group", a[where] if len(a) > where else None)
+            key = (kind, heap.ctx(group).size)
+            ev = None
+            if t.is_cuda and not torch.cuda.is_current_stream_capturing():
+                ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                ev[0].record()
+            out = fn(heap, *a, **kw)
+            if ev is not None:
+                ev[1].record()
+            if self._cur is not None:
+                self._cur.append((key, t.numel() * t.element_size(), ev))
+            return out
+        return wrapped
+
     def record(self, kind, group_size, nbytes, events=None):
         """Entry point for transports that do not go through ``torch.distributed`` (the symmetric-heap kernels)."""
         if self._cur is not None:
@@ -65,6 +101,11 @@ class CollectiveStats:
         for name, (kind, pick) in _KINDS.items():
             self._orig[name] = getattr(dist, name)
             setattr(dist, name, self._wrap(name, self._orig[name], kind, pick))
+        from ..parallel.symm import SymmetricHeap
+        for name, (kind, where) in _HEAP_KINDS.items():
+            if hasattr(SymmetricHeap, name):
+                self._orig_heap[name] = getattr(SymmetricHeap, name)
+                setattr(SymmetricHeap, name, self._wrap_heap(name, self._orig_heap[name], kind, where))
         global ACTIVE
         ACTIVE = self
 
@@ -74,6 +115,11 @@ class CollectiveStats:
         for name, fn in self._orig.items():
             setattr(dist, name, fn)
         self._orig = {}
+        if self._orig_heap:
+            from ..parallel.symm import SymmetricHeap
+            for name, fn in self._orig_heap.items():
+                setattr(SymmetricHeap, name, fn)
+            self._orig_heap = {}
         cur, self._cur = self._cur, None
         if not keep:
             return

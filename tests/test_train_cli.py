@@ -94,3 +94,28 @@ def test_single_gpu_trainer_learns_on_cpu(tmp_path, capsys):
              train_idx=torch.arange(0, 30), valid_idx=torch.arange(30, 40), test_idx=torch.arange(40, 50))
     torch.save(g, str(tmp_path / "g.pt"))
     main(["--graph", str(tmp_path / "g.pt"), "--epochs", "2", "--hidden", "16", "--heads", "2", "--layers", "1", "--backend", "ref"])
+
+
+def test_collective_census_counts_the_peer_memory_transport(monkeypatch):
+    """``CollectiveStats`` patches the symmetric heap's methods like it patches ``torch.distributed``."""
+    import types
+    import torch
+    from gt_b200.parallel.symm import SymmetricHeap
+    from gt_b200.utils.collstats import CollectiveStats
+    monkeypatch.setattr(SymmetricHeap, "all_gather", lambda self, x, group: x.repeat(2, 1))
+    monkeypatch.setattr(SymmetricHeap, "all_reduce", lambda self, x, out, name=None, group=None: out.copy_(2 * x))
+    monkeypatch.setattr(SymmetricHeap, "pull_gather", lambda self, x2, plan: x2[:3])
+    heap = SymmetricHeap.__new__(SymmetricHeap)
+    heap.ctx = lambda group: types.SimpleNamespace(size=4 if group == "row" else 2)
+    plain = SymmetricHeap.all_gather
+    st = CollectiveStats()
+    for _ in range(2):
+        st.begin_epoch()
+        assert heap.all_gather(torch.ones(4, 4), "row").shape == (8, 4)
+        heap.all_reduce(torch.ones(8), torch.empty(8), "grads")
+        heap.pull_gather(torch.ones(5, 2), types.SimpleNamespace(group=None))
+        st.end_epoch()
+    assert SymmetricHeap.all_gather is plain                                   # patches are removed after every epoch
+    t = st.table()
+    assert t[("p2p_all_gather", 4)] == dict(calls=1.0, mbytes=64 / 2 ** 20, ms=0.0)
+    assert t[("p2p_all_reduce", 2)]["calls"] == 1.0 and t[("p2p_sparse_gather", 2)]["mbytes"] == 40 / 2 ** 20
