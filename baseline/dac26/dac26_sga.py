@@ -181,6 +181,7 @@ def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--graph", default="cpu_small", help="synthetic workload name (gt_b200.data.synthetic.WORKLOADS)")
     ap.add_argument("--scale_down", type=int, default=1)
+    ap.add_argument("--graph_file", default=None, help="graph written by prepare_graphs.py (random features and labels)")
     ap.add_argument("--strategy", default="single", choices=["single", "gp_ag", "gp_a2a"])
     ap.add_argument("--hidden", type=int, default=128)
     ap.add_argument("--heads", type=int, default=8)
@@ -204,7 +205,14 @@ def main(argv=None):
         raise SystemExit("--strategy single runs as one process")
     if args.strategy == "gp_a2a" and args.heads % p:
         raise SystemExit("gp_a2a needs the number of ranks to divide the number of heads")
-    wl = workload_graph(args.graph, seed=args.seed, scale_down=args.scale_down)
+    if args.graph_file:
+        from gt_b200.data.synthetic import node_data
+        g = torch.load(args.graph_file, weights_only=True)
+        x_, y_, masks_ = node_data(g["num_nodes"], 128, 40, seed=args.seed + 17)
+        wl = dict(n=g["num_nodes"], edge_index=g["edge_index"], x=x_, y=y_, masks=masks_, cfg=dict(features=128, classes=40))
+        args.graph = os.path.basename(args.graph_file)
+    else:
+        wl = workload_graph(args.graph, seed=args.seed, scale_down=args.scale_down)
     n, ei = wl["n"], add_self_loops(wl["edge_index"], wl["n"])
     n_pad = -(-n // p) * p
     per = n_pad // p

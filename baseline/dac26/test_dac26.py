@@ -32,3 +32,19 @@ def test_micro_and_kernel_modes():
     assert {"mm_ms", "sddmm_ms", "spmm_ms"} <= set(r)
     r = dac26_sga.main(["--graph", "cpu_small", "--scale_down", "4", "--kernel", "--hidden", "32", "--heads", "4", "--iters", "1", "--warmup", "0"])
     assert r["fwd_bwd_ms"] > 0
+
+
+def test_prepared_graph_files(tmp_path):
+    import torch
+    import dac26_sga
+    import prepare_graphs
+    paths = prepare_graphs.main(["--out", str(tmp_path), "--graphs", "proteins", "--scale_down", "400"])
+    g = torch.load(paths[0], weights_only=True)
+    assert g["num_nodes"] == 132_534 // 400 and g["edge_index"].shape[0] == 2 and int(g["edge_index"].max()) < g["num_nodes"]
+    assert torch.equal(torch.unique(g["edge_index"][1] * g["num_nodes"] + g["edge_index"][0]).sort()[0],
+                       torch.unique(g["edge_index"][0] * g["num_nodes"] + g["edge_index"][1]).sort()[0])      # symmetric
+    torch.save(g["edge_index"], tmp_path / "raw.pt")
+    again = prepare_graphs.main(["--out", str(tmp_path), "--name", "mine", "--edges", str(tmp_path / "raw.pt")])
+    assert torch.equal(torch.load(again[0], weights_only=True)["edge_index"], g["edge_index"])
+    r = dac26_sga.main(["--graph_file", paths[0], "--kernel", "--hidden", "32", "--heads", "4", "--iters", "1", "--warmup", "0"])
+    assert r["nodes"] == g["num_nodes"] and r["fwd_bwd_ms"] > 0

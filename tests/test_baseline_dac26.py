@@ -3,4 +3,4 @@ import os
 import sys
 
 sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "dac26"))
-from test_dac26 import test_micro_and_kernel_modes, test_strategies_match_single  # noqa: E402,F401
+from test_dac26 import test_micro_and_kernel_modes, test_prepared_graph_files, test_strategies_match_single  # noqa: E402,F401
