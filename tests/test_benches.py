@@ -208,3 +208,17 @@ def test_kernel_option_benches_on_gpu():
     by = {r["impl"]: r for r in rows}
     assert by["cuda"]["max_abs_diff_vs_edge_list"] < 0.05 and by["csr_torch"]["max_abs_diff_vs_edge_list"] < 1e-3
     assert "fwd_ms" in by["dense_sdpa"] and ("fwd_ms" in by["sparse_lib"] or "error" in by["sparse_lib"])
+
+
+def test_profile_exports_a_chrome_trace_for_analyze_trace(tmp_path, monkeypatch):
+    import io
+    import torch
+    from gt_b200.bench.analyze_trace import analyze
+    from gt_b200.utils.profiling import kernel_profile
+    monkeypatch.setenv("GT_PROF_TRACE", str(tmp_path / "step"))
+    with kernel_profile(rank=0, file=io.StringIO()):
+        torch.ones(64, 64) @ torch.ones(64, 64)
+    path = tmp_path / "step_rank0.json"
+    assert path.exists()
+    r = analyze(str(path))
+    assert r["kernels"] == 0 or r["busy_ms"] > 0            # CPU run: a valid trace without GPU events
