@@ -154,3 +154,45 @@ def test_dist_operator_matches_reference(case):
     for s in OPS[case]["grid"]:
         world *= s
     run_dist(_op_worker, world, case)
+
+
+def _torchgt_style_worker(rank, world, fused):
+    """``DistGraphormerNode`` (plain and fused routes) against ``GraphormerNode`` with the same weights, fp64, torch backend."""
+    import torch.distributed as dist
+    from gt_b200.bench.torchgt_batch_bench import torchgt_batch
+    from gt_b200.data.synthetic import erdos_renyi, symmetrize
+    from gt_b200.models.graphormer_node import DistGraphormerNode, GraphormerNode
+    from gt_b200.parallel.grid import Grid2D
+    from gt_b200.parallel.layers import allreduce_grads, dist_cross_entropy
+    n0, f, hid, classes = 40, 6, 16, 3
+    torch.manual_seed(3)
+    ei = symmetrize(erdos_renyi(n0, 3, seed=2), n0)
+    x, y = torch.randn(n0, f, dtype=torch.float64), torch.randint(0, classes, (n0,))
+    xb, yb, eb, n = torchgt_batch(x, y, ei, torch.arange(n0), 30, seed=1)
+    ref = GraphormerNode(f, hid, 24, 4, 2, classes, eb, n, dropout=0.0, input_dropout=0.0, backend="torch").double()
+    loss_ref = torch.nn.functional.cross_entropy(ref(xb), yb)
+    loss_ref.backward()
+    grid = Grid2D(2, 1, n) if not fused else Grid2D(1, 2, n)
+    b_ei, _ = grid.local_block(eb)
+    model = DistGraphormerNode(grid, (b_ei, None), f, hid, 24, 4, 2, classes, dropout=0.0, input_dropout=0.0, backend="torch", fused=fused).double()
+    missing = model.load_state_dict(ref.state_dict(), strict=True)
+    assert not missing.missing_keys and not missing.unexpected_keys
+    x_loc = grid.take_owned(torch.cat([torch.zeros(1, f, dtype=torch.float64), xb]))
+    y_loc = grid.take_owned(torch.cat([torch.zeros(1, dtype=torch.long), yb]))
+    mask = grid.valid_mask.clone()
+    if grid.owned_range()[0] == 0:
+        mask[0] = False
+    loss = dist_cross_entropy(model(x_loc), y_loc, mask, n - 1)
+    loss.backward()
+    params = list(model.parameters())
+    allreduce_grads(params)
+    tot = loss.detach().clone()
+    dist.all_reduce(tot)
+    assert abs(float(tot) - float(loss_ref)) < 1e-9
+    for (name, p), q in zip(model.named_parameters(), ref.parameters()):
+        assert (p.grad - q.grad).abs().max() < 1e-8, name
+
+
+@pytest.mark.parametrize("fused", [False, True], ids=["plain", "fused"])
+def test_torchgt_style_graphormer_matches_single_device(fused):
+    run_dist(_torchgt_style_worker, 2, fused)
