@@ -51,69 +51,88 @@ def evaluate(model, x, graph, y, split):
     return {k: (pred[idx] == y[idx]).float().mean().item() for k, idx in split.items()}
 
 
-def main(argv=None):
+def build_parser():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--backend", default=None, choices=["ref", "torch", "cuda", "triton"], help="'triton' is an alias of 'cuda'")
-    ap.add_argument("--graph", default=None)
-    ap.add_argument("--synthetic", default="cpu_small")
-    ap.add_argument("--scale_down", type=int, default=1)
-    ap.add_argument("--epochs", type=int, default=600)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--hidden", type=int, default=80)
-    ap.add_argument("--heads", type=int, default=2)
-    ap.add_argument("--layers", type=int, default=4)
-    ap.add_argument("--dropout", type=float, default=0.3)
-    ap.add_argument("--lr", type=float, default=1e-3)
-    ap.add_argument("--weight_decay", type=float, default=1e-3)
-    ap.add_argument("--exp_deg", type=int, default=3)
-    ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--eval_every", type=int, default=1)
-    ap.add_argument("--norm", default="bn", choices=["bn", "ln", "rms"])
-    ap.add_argument("--no_self_loops", action="store_true")
-    args = ap.parse_args(argv)
+    a = ap.add_argument
+    a("--backend", default=None, choices=["ref", "torch", "cuda", "triton"], help="'triton' is an alias of 'cuda'")
+    a("--graph", default=None)
+    a("--synthetic", default="cpu_small")
+    a("--scale_down", type=int, default=1)
+    a("--no_self_loops", action="store_true")
+    a("--exp_deg", type=int, default=3)
+    a("--seed", type=int, default=0)
+    for flag, kind, value in (("--hidden", int, 80), ("--heads", int, 2), ("--layers", int, 4), ("--dropout", float, 0.3),
+                              ("--epochs", int, 600), ("--warmup", int, 5), ("--lr", float, 1e-3), ("--weight_decay", float, 1e-3),
+                              ("--eval_every", int, 1)):
+        a(flag, type=kind, default=value)
+    a("--norm", default="bn", choices=["bn", "ln", "rms"])
+    return ap
+
+
+class _Stopwatch:
+    """Accumulates seconds per phase; synchronises the device at both ends of a phase so that the host clock brackets the
+    device work of exactly that phase."""
+
+    def __init__(self, cuda):
+        self.cuda, self.total = cuda, {}
+
+    def run(self, phase, fn):
+        if self.cuda:
+            torch.cuda.synchronize()
+        began = time.perf_counter()
+        out = fn()
+        if self.cuda:
+            torch.cuda.synchronize()
+        self.total[phase] = self.total.get(phase, 0.0) + time.perf_counter() - began
+        return out
+
+
+def train_epoch(model, opt, sched, x, graph, y, train_idx, clip=1.0):
+    """One full-graph step: loss on the train split, clipped gradients, AdamW and schedule step.  Returns the loss tensor."""
+    model.train()
+    opt.zero_grad(set_to_none=True)
+    loss = F.cross_entropy(model(x, graph)[train_idx], y[train_idx])
+    loss.backward()
+    torch.nn.utils.clip_grad_norm_(model.parameters(), clip)
+    opt.step()
+    sched.step()
+    return loss
+
+
+def main(argv=None):
+    args = build_parser().parse_args(argv)
     torch.manual_seed(args.seed)
     cuda = torch.cuda.is_available()
     dev = torch.device("cuda" if cuda else "cpu")
-    backend = {"triton": "cuda", None: "cuda" if cuda else "torch"}.get(args.backend, args.backend)
-    if args.graph:
-        n, x, y, ei, split, classes = load_graph_file(args.graph, dev, not args.no_self_loops)
-    else:
-        n, x, y, ei, split, classes = load_synthetic(args.synthetic, dev, args.seed, args.scale_down, not args.no_self_loops)
-    exp = random_regular_expander_edges(n, args.exp_deg, seed=args.seed, device=dev)
-    graph = AttentionGraph(ei, exp, n).to(dev)
+    backend = args.backend or ("cuda" if cuda else "torch")
+    backend = "cuda" if backend == "triton" else backend
+    loops = not args.no_self_loops
+    data = load_graph_file(args.graph, dev, loops) if args.graph else load_synthetic(args.synthetic, dev, args.seed, args.scale_down, loops)
+    n, x, y, ei, split, classes = data
+    graph = AttentionGraph(ei, random_regular_expander_edges(n, args.exp_deg, seed=args.seed, device=dev), n).to(dev)
     print(f"graph: N={n} E_gcn={ei.shape[1]} E_attn={graph.edge_index.shape[1]} classes={classes} backend={backend}", flush=True)
     model = Exphormer(x.shape[1], args.hidden, classes, args.layers, args.heads, dropout=args.dropout, gnn_dropout=args.dropout,
                       backend=backend, norm=args.norm).to(dev)
     print(f"params: {sum(p.numel() for p in model.parameters())}", flush=True)
     opt = torch.optim.AdamW(model.parameters(), lr=args.lr, weight_decay=args.weight_decay)
     sched = torch.optim.lr_scheduler.LambdaLR(opt, lambda s: cosine_with_warmup(s, args.warmup, args.epochs))
-
-    def sync():
-        if cuda:
-            torch.cuda.synchronize()
+    watch = _Stopwatch(cuda)
     best = dict(val=-1.0, test=0.0, epoch=-1)
-    t_train = t_eval = 0.0
     if cuda:
         torch.cuda.reset_peak_memory_stats()
+    last = args.epochs - 1
     for epoch in range(args.epochs):
-        sync(); t0 = time.perf_counter()
-        model.train()
-        opt.zero_grad(set_to_none=True)
-        loss = F.cross_entropy(model(x, graph)[split["train"]], y[split["train"]])
-        loss.backward()
-        torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
-        opt.step()
-        sched.step()
-        sync(); t1 = time.perf_counter(); t_train += t1 - t0
-        if epoch % args.eval_every == 0 or epoch == args.epochs - 1:
-            acc = evaluate(model, x, graph, y, split)
-            sync(); t_eval += time.perf_counter() - t1
-            if acc["valid"] > best["val"]:
-                best = dict(val=acc["valid"], test=acc["test"], epoch=epoch)
-            if epoch % 10 == 0 or epoch == args.epochs - 1:
-                print(f"epoch {epoch:4d} loss {loss.item():.4f} train {acc['train']:.4f} val {acc['valid']:.4f} test {acc['test']:.4f} "
-                      f"| best val {best['val']:.4f} test {best['test']:.4f} @ {best['epoch']} | {t_train / (epoch + 1) * 1e3:.1f} ms/epoch train, "
-                      f"lr {sched.get_last_lr()[0]:.2e}", flush=True)
+        loss = watch.run("train", lambda: train_epoch(model, opt, sched, x, graph, y, split["train"]))
+        if epoch % args.eval_every and epoch != last:
+            continue
+        acc = watch.run("eval", lambda: evaluate(model, x, graph, y, split))
+        if acc["valid"] > best["val"]:
+            best = dict(val=acc["valid"], test=acc["test"], epoch=epoch)
+        if epoch % 10 == 0 or epoch == last:
+            print(f"epoch {epoch:4d} loss {loss.item():.4f} train {acc['train']:.4f} val {acc['valid']:.4f} test {acc['test']:.4f} "
+                  f"| best val {best['val']:.4f} test {best['test']:.4f} @ {best['epoch']} | "
+                  f"{watch.total['train'] / (epoch + 1) * 1e3:.1f} ms/epoch train, lr {sched.get_last_lr()[0]:.2e}", flush=True)
+    t_train, t_eval = watch.total.get("train", 0.0), watch.total.get("eval", 0.0)
     peak = torch.cuda.max_memory_allocated() / 2 ** 30 if cuda else 0.0
     print(f"FINAL backend={backend} best_val={best['val']:.4f} test@best_val={best['test']:.4f} epoch={best['epoch']} "
           f"train_time={t_train:.1f}s ({t_train / max(args.epochs, 1) * 1e3:.1f} ms/epoch) eval_time={t_eval:.1f}s peak_mem={peak:.2f}GB", flush=True)
