@@ -29,32 +29,44 @@ class AttentionGraph:
         return self
 
 
+def _attend(backend, q, k, v, graph, gate):
+    """Gated clamp-exp attention over the graph's attention edges on the chosen back-end."""
+    opts = dict(gate=gate, score="gated", norm="clampexp")
+    if backend == "ref":
+        return masked_sparse_attention_ref(q, k, v, graph.edge_index, edge_type=graph.etype, **opts)
+    if backend == "torch":
+        return masked_sparse_attention_torch(q, k, v, graph.csr, **opts)
+    from ..attention.backend_cuda import masked_sparse_attention_cuda
+    return masked_sparse_attention_cuda(q, k, v, graph.csr, **opts)
+
+
 class ExphormerLayer(ExphormerLayerRef):
+    """The reference layer's parameters; the bias-free projections that read ``x`` (Q, K, V and the GCN message) run as ONE
+    GEMM on the stacked weights, each branch ends in its own residual + norm, then the FFN."""
+
     def __init__(self, *args, backend="cuda", **kwargs):
         super().__init__(*args, **kwargs)
         self.backend = backend
 
+    def _projected(self, x):
+        mats = ([self.q.weight, self.k.weight, self.v.weight] if self.with_attn else []) + ([self.gcn.lin.weight] if self.with_gcn else [])
+        out = F.linear(x, torch.cat(mats, 0) if len(mats) > 1 else mats[0])
+        return out.split(x.shape[1], dim=1)
+
     def forward(self, x, graph: AttentionGraph, edge_type_emb):
-        n, h, d = x.shape[0], self.num_heads, self.d_head
-        drop = lambda t: F.dropout(t, self.dropout, self.training)                 # noqa: E731
-        parts = []
+        rows, heads = x.shape[0], (self.num_heads, self.d_head)
+        pieces = list(self._projected(x))
+        branch_sum = None
         if self.with_attn:
-            q, k, v = self.q(x).view(n, h, d), self.k(x).view(n, h, d), self.v(x).view(n, h, d)
-            gate = self.e(edge_type_emb).view(-1, h, d)
-            kw = dict(gate=gate, score="gated", norm="clampexp")
-            if self.backend == "ref":
-                o = masked_sparse_attention_ref(q, k, v, graph.edge_index, edge_type=graph.etype, **kw)
-            elif self.backend == "torch":
-                o = masked_sparse_attention_torch(q, k, v, graph.csr, **kw)
-            else:
-                from ..attention.backend_cuda import masked_sparse_attention_cuda
-                o = masked_sparse_attention_cuda(q, k, v, graph.csr, **kw)
-            parts.append(self.bn_attn(x + drop(o.reshape(n, h * d).to(x.dtype))))
+            q, k, v = (pieces.pop(0).reshape(rows, *heads) for _ in range(3))
+            o = _attend(self.backend, q, k, v, graph, self.e(edge_type_emb).view(-1, *heads))
+            branch_sum = self.bn_attn(x + F.dropout(o.reshape(rows, -1).to(x.dtype), self.dropout, self.training))
         if self.with_gcn:
-            agg = spmm(graph.gcn, self.gcn.lin(x)) + self.gcn.bias
-            parts.append(self.bn_local(x + drop(agg)))
-        hh = parts[0] if len(parts) == 1 else parts[0] + parts[1]
-        return self.bn_ff(hh + drop(self.ff2(drop(F.relu(self.ff1(hh))))))
+            agg = spmm(graph.gcn, pieces.pop(0).contiguous()) + self.gcn.bias
+            local = self.bn_local(x + F.dropout(agg, self.dropout, self.training))
+            branch_sum = local if branch_sum is None else branch_sum + local
+        ffn = F.dropout(F.relu(self.ff1(branch_sum)), self.dropout, self.training)
+        return self.bn_ff(branch_sum + F.dropout(self.ff2(ffn), self.dropout, self.training))
 
 
 class Exphormer(ExphormerRef):
