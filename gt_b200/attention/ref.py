@@ -55,6 +55,19 @@ def edge_scores(q, k, src, dst, edge_type, gate, bias, score, scale):
     raise ValueError(f"unknown score mode {score!r}")
 
 
+def edge_weights(s, dst, n, norm, clamp, eps):
+    """Unnormalised attention weight of every edge, ``(p [E, H], m, floor)``: for ``softmax`` ``p = exp(s - m[dst])`` with
+    the row maximum ``m`` (0 for rows without in-edges) and nothing added to the normaliser; for ``clampexp``
+    ``p = exp(clamp(s))``, no maximum, and ``eps`` added to the normaliser."""
+    if norm == "softmax":
+        m = segment_max(s, dst, n)
+        m = torch.where(torch.isfinite(m), m, torch.zeros_like(m))
+        return torch.exp(s - m[dst]), m, 0.0
+    if norm == "clampexp":
+        return torch.exp(s.clamp(clamp[0], clamp[1])), None, eps
+    raise ValueError(f"unknown norm mode {norm!r}")
+
+
 def masked_sparse_attention_ref(q, k, v, edge_index, *, edge_type=None, gate=None, bias=None, score="dot",
                                 norm="softmax", clamp=(-5.0, 5.0), eps=1e-6, scale=None, return_stats=False):
     """Masked sparse attention on an edge list; returns ``o [N, H, d]``.
@@ -69,18 +82,7 @@ def masked_sparse_attention_ref(q, k, v, edge_index, *, edge_type=None, gate=Non
     scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
     et = edge_type.long() if edge_type is not None else None
     s = edge_scores(q, k, src, dst, et, gate, bias, score, scale)
-    v_e = v[src]
-    if norm == "softmax":
-        m = segment_max(s, dst, n)
-        m = torch.where(torch.isfinite(m), m, torch.zeros_like(m))
-        p = torch.exp(s - m[dst])
-        z = segment_sum(p, dst, n)
-        o = segment_sum(p.unsqueeze(-1) * v_e, dst, n) / z.clamp_min(torch.finfo(z.dtype).tiny).unsqueeze(-1)
-    elif norm == "clampexp":
-        m = None
-        p = torch.exp(s.clamp(clamp[0], clamp[1]))
-        z = segment_sum(p, dst, n)
-        o = segment_sum(p.unsqueeze(-1) * v_e, dst, n) / (z + eps).unsqueeze(-1)
-    else:
-        raise ValueError(f"unknown norm mode {norm!r}")
+    p, m, floor = edge_weights(s, dst, n, norm, clamp, eps)
+    z = segment_sum(p, dst, n)
+    o = segment_sum(p.unsqueeze(-1) * v[src], dst, n) / (z + floor).clamp_min(torch.finfo(z.dtype).tiny).unsqueeze(-1)
     return (o, (z, m)) if return_stats else o

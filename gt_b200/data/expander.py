@@ -15,17 +15,17 @@ import torch
 _M32 = 0xFFFFFFFF
 
 
+def _union_both_ways(ids: torch.Tensor, images) -> torch.Tensor:
+    """Edge list of ``i -> image(i)`` and ``image(i) -> i`` for every image vector, fixed points dropped."""
+    fwd = torch.cat([torch.stack([ids, img]) for img in images], dim=1)
+    both = torch.cat([fwd, fwd.flip(0)], dim=1)
+    return both[:, both[0] != both[1]]
+
+
 def random_regular_expander_edges(num_nodes: int, degree: int, seed: int = 0, device="cpu") -> torch.Tensor:
-    g = torch.Generator().manual_seed(int(seed))
-    ident = torch.arange(num_nodes)
-    a, b = [], []
-    for _ in range(degree):
-        pi = torch.randperm(num_nodes, generator=g)
-        a += [ident, pi]
-        b += [pi, ident]
-    src, dst = torch.cat(a), torch.cat(b)
-    keep = src != dst
-    return torch.stack([src[keep], dst[keep]]).to(device)
+    gen = torch.Generator().manual_seed(int(seed))
+    images = [torch.randperm(num_nodes, generator=gen) for _ in range(degree)]
+    return _union_both_ways(torch.arange(num_nodes), images).to(device)
 
 
 def _round_fn(x: torch.Tensor, key: int) -> torch.Tensor:
@@ -65,14 +65,7 @@ class KeyedPermutation:
 def keyed_expander_edges(num_nodes: int, degree: int, seed: int = 0, device="cpu") -> torch.Tensor:
     """Global edge list of the union of ``degree`` keyed permutations (both directions, no self loops)."""
     ids = torch.arange(num_nodes, device=device)
-    a, b = [], []
-    for idx in range(degree):
-        img = KeyedPermutation(num_nodes, seed, idx)(ids)
-        a += [ids, img]
-        b += [img, ids]
-    src, dst = torch.cat(a), torch.cat(b)
-    keep = src != dst
-    return torch.stack([src[keep], dst[keep]])
+    return _union_both_ways(ids, [KeyedPermutation(num_nodes, seed, which)(ids) for which in range(degree)])
 
 
 def block_expander_edges(grid, num_nodes: int, degree: int, seed: int = 0, device="cpu") -> torch.Tensor:
