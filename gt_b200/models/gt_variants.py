@@ -24,7 +24,7 @@ import torch.distributed as dist
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..data.synthetic import khop_edges
+from ..data.synthetic import add_self_loops, khop_edges, virtual_node_edges
 from ..ops import functional as K
 from ..parallel.attention import AttentionBlock, DistAttentionPartial, DistHeadSparseAttention, combine_partials
 from ..parallel.collectives import all_gather_rows
@@ -36,24 +36,19 @@ ET_NEIGHBOUR, ET_SELF, ET_TO_TOKEN, ET_FROM_TOKEN = 0, 1, 2, 3
 # ---- edge sets ------------------------------------------------------------------------------------------------------
 def typed_graph_edges(edge_index, num_nodes):
     """Graph edges + exactly one self loop per node, typed 0 (neighbour) / 1 (self)."""
-    dev = edge_index.device
-    keep = edge_index[0] != edge_index[1]
-    loops = torch.arange(num_nodes, device=dev)
-    ei = torch.cat([edge_index[:, keep], torch.stack([loops, loops])], dim=1)
-    et = torch.cat([torch.zeros(int(keep.sum()), dtype=torch.long, device=dev), torch.ones(num_nodes, dtype=torch.long, device=dev)])
+    ei = add_self_loops(edge_index, num_nodes)                      # existing loops dropped, one loop per node appended last
+    et = torch.full((ei.shape[1],), ET_NEIGHBOUR, dtype=torch.long, device=ei.device)
+    et[ei.shape[1] - num_nodes:] = ET_SELF
     return ei, et
 
 
 def graphormer_edges(edge_index, num_nodes):
     """``typed_graph_edges`` plus the global token ``T = num_nodes``: (i -> T) type 2, (T -> i) type 3, (T -> T) type 1."""
-    dev = edge_index.device
     ei, et = typed_graph_edges(edge_index, num_nodes)
-    nodes = torch.arange(num_nodes, device=dev)
-    tok = torch.full((num_nodes,), num_nodes, device=dev)
-    ei = torch.cat([ei, torch.stack([nodes, tok]), torch.stack([tok, nodes]), torch.full((2, 1), num_nodes, device=dev)], dim=1)
-    et = torch.cat([et, torch.full((num_nodes,), ET_TO_TOKEN, device=dev), torch.full((num_nodes,), ET_FROM_TOKEN, device=dev),
-                    torch.tensor([ET_SELF], device=dev)])
-    return ei, et
+    tok_ei, to_token = virtual_node_edges(num_nodes, device=ei.device)
+    tok_et = torch.where(to_token, ET_TO_TOKEN, ET_FROM_TOKEN)
+    loop = torch.full((2, 1), num_nodes, device=ei.device)
+    return torch.cat([ei, tok_ei, loop], dim=1), torch.cat([et, tok_et, tok_et.new_tensor([ET_SELF])])
 
 
 def khop_typed_edges(edge_index, num_nodes, max_two_hop=None, seed=0):
@@ -76,24 +71,25 @@ def token_edges_local(grid, num_nodes, device):
     c_lo, c_hi = grid.col_block_range()
     row_ids = grid.row_block_ids().to(device)
     real_rows = torch.nonzero(row_ids < num_nodes).squeeze(1)
-    srcs, dsts, types = [], [], []
-    tok_in_col = c_lo <= T < c_hi
-    tok_in_row = int(grid.owner_of(torch.tensor([T]))[0][0]) == grid.r
-    t_col = T - c_lo
-    if tok_in_col:
-        srcs.append(torch.full_like(real_rows, t_col)); dsts.append(real_rows)
-        types.append(torch.full_like(real_rows, ET_FROM_TOKEN))
-    if tok_in_row:
+    found = []                                   # (sources, destinations, type) triples in local numbering
+
+    def emit(src, dst, kind):
+        src, dst = torch.broadcast_tensors(torch.as_tensor(src, device=device), torch.as_tensor(dst, device=device))
+        found.append((src.reshape(-1), dst.reshape(-1), torch.full((src.numel(),), kind, dtype=torch.long, device=device)))
+    token_is_my_column = c_lo <= T < c_hi
+    token_is_my_row = int(grid.owner_of(torch.tensor([T]))[0][0]) == grid.r
+    if token_is_my_column:                       # the token feeds every real row of my row block
+        emit(T - c_lo, real_rows, ET_FROM_TOKEN)
+    if token_is_my_row:                          # every real column of my column block feeds the token's row
         t_row = int(grid.global_to_row_local(torch.tensor([T]))[0])
-        cols = torch.arange(0, max(min(c_hi, num_nodes) - c_lo, 0), device=device)
-        srcs.append(cols); dsts.append(torch.full_like(cols, t_row)); types.append(torch.full_like(cols, ET_TO_TOKEN))
-        if tok_in_col:
-            srcs.append(torch.tensor([t_col], device=device)); dsts.append(torch.tensor([t_row], device=device))
-            types.append(torch.tensor([ET_SELF], device=device))
-    if not srcs:
-        z = torch.zeros(0, dtype=torch.long, device=device)
-        return torch.stack([z, z]), z
-    return torch.stack([torch.cat(srcs), torch.cat(dsts)]), torch.cat(types)
+        emit(torch.arange(0, max(min(c_hi, num_nodes) - c_lo, 0), device=device), t_row, ET_TO_TOKEN)
+        if token_is_my_column:
+            emit([T - c_lo], [t_row], ET_SELF)
+    if not found:
+        none = torch.zeros(0, dtype=torch.long, device=device)
+        return torch.stack([none, none]), none
+    src, dst, kinds = (torch.cat(part) for part in zip(*found))
+    return torch.stack([src, dst]), kinds
 
 
 def owned_degrees(grid, block_edge_index, block_edge_type, device, neighbour_type=ET_NEIGHBOUR):
@@ -131,6 +127,11 @@ def ref_attention(q, k, v, edge_index, etype=None, bias=None, scale=None):
                                        norm="softmax", scale=scale)
 
 
+def _per_head(mod, rows):
+    """``(q, k, v)`` of ``rows`` by the module's three projections, each viewed as ``[n, heads, head dim]``."""
+    return tuple(proj(rows).view(rows.shape[0], mod.h, mod.d) for proj in (mod.q, mod.k, mod.v))
+
+
 class UniMPLayerRef(nn.Module):
     def __init__(self, dim, heads, dropout):
         super().__init__()
@@ -144,28 +145,32 @@ class UniMPLayerRef(nn.Module):
         return K.gated_residual(r, o.to(r.dtype), self.gate.weight, self.gate.bias, self.ln, self.dropout, self.training)
 
     def forward(self, x, edge_index):
-        n = x.shape[0]
-        o = ref_attention(self.q(x).view(n, self.h, self.d), self.k(x).view(n, self.h, self.d), self.v(x).view(n, self.h, self.d), edge_index)
-        return self.combine(x, o.reshape(n, -1))
+        return self.combine(x, ref_attention(*_per_head(self, x), edge_index).flatten(1))
 
 
 class UniMPRef(nn.Module):
+    """Label-aware input (a class embedding added where a training label is visible; the padding row means "hidden"),
+    ``num_layers`` gated-residual attention layers, linear classifier."""
+
     def __init__(self, dim_in, dim_hidden, dim_out, num_layers, num_heads, dropout=0.3, num_classes_label=None):
         super().__init__()
-        self.dropout = dropout
-        self.pre_lin = nn.Linear(dim_in, dim_hidden)
-        self.label_emb = nn.Embedding(num_classes_label + 1, dim_hidden, padding_idx=num_classes_label) if num_classes_label else None
-        self.layers = nn.ModuleList([UniMPLayerRef(dim_hidden, num_heads, dropout) for _ in range(num_layers)])
-        self.head = nn.Linear(dim_hidden, dim_out)
+        self.pre_lin, self.head, self.dropout = nn.Linear(dim_in, dim_hidden), nn.Linear(dim_hidden, dim_out), dropout
+        self.label_emb = None
+        if num_classes_label:
+            self.label_emb = nn.Embedding(num_classes_label + 1, dim_hidden, padding_idx=num_classes_label)
+        self.layers = nn.ModuleList(UniMPLayerRef(dim_hidden, num_heads, dropout) for _ in range(num_layers))
+
+    def inputs(self, x, label_feat=None):
+        rows = self.pre_lin(x)
+        if label_feat is not None and self.label_emb is not None:
+            rows = rows + self.label_emb(label_feat)
+        return F.dropout(rows, self.dropout, self.training)
 
     def forward(self, x, edge_index, label_feat=None):
-        h = self.pre_lin(x)
-        if self.label_emb is not None and label_feat is not None:
-            h = h + self.label_emb(label_feat)
-        h = F.dropout(h, self.dropout, self.training)
+        rows = self.inputs(x, label_feat)
         for layer in self.layers:
-            h = layer(h, edge_index)
-        return self.head(h)
+            rows = layer(rows, edge_index)
+        return self.head(rows)
 
 
 class GraphormerBlockRef(nn.Module):
@@ -184,11 +189,8 @@ class GraphormerBlockRef(nn.Module):
         return x + F.dropout(y, self.dropout, self.training)
 
     def forward(self, x, edge_index, etype, attn_bias):
-        n = x.shape[0]
-        y = self.ln1(x)
-        o = ref_attention(self.q(y).view(n, self.h, self.d), self.k(y).view(n, self.h, self.d), self.v(y).view(n, self.h, self.d),
-                          edge_index, etype, attn_bias)
-        return self.finish(x, o.reshape(n, -1))
+        mixed = ref_attention(*_per_head(self, self.ln1(x)), edge_index, etype, attn_bias)
+        return self.finish(x, mixed.flatten(1))
 
 
 class GraphormerNodeRef(nn.Module):
