@@ -164,6 +164,14 @@ def run_ours(args):
     ms_dev, _, clocks, loss = timed(step_device, args.steps)
     _, ms_e2e, clocks_e2e, loss_e2e = timed(step_e2e, args.steps)
     native.check_status(dev)
+    if args.profile:
+        # per-kernel device time of ONE more step of the same kind (a graph replay unless --no_graph), after the timed region
+        from gt_b200.utils.profiling import kernel_profile
+        dist.barrier()
+        torch.cuda.synchronize()
+        with open(f"{args.profile}.rank{rank}.txt", "w") as fh:
+            with kernel_profile(0, world, top=45, file=fh):
+                step_device()
     edges_layers = wl["num_attn_edges"] * wl["cfg"]["layers"]
     peak = torch.tensor([torch.cuda.max_memory_allocated() / 2 ** 30], device=dev)
     dist.all_reduce(peak, op=dist.ReduceOp.MAX)
@@ -188,23 +196,44 @@ def run_ours(args):
             "loss": float(loss), "peak_gb": peak.item(), "impl": "gt_b200",
         }
         print(json.dumps(out), flush=True)
-    finish(dist)
+    finish(dist, [eng] + ([heap] if heap is not None else []))
 
 
-def finish(dist):
-    """Leave without waiting on communicator teardown: a process group whose collectives were captured in a CUDA graph can
-    block in destroy_process_group; the result line is already printed, so synchronise, meet at a barrier and exit."""
+def finish(dist, release=()):
+    """Orderly exit: drop the captured CUDA graph (it keeps the communicator's captured collectives alive, and a communicator
+    with live captured work can block in its teardown), close the symmetric heap, synchronise, meet at a barrier, destroy the
+    process group in a helper thread and leave through the interpreter's normal shutdown.  Only if the teardown does not
+    return within 20 s is the process ended without it (the result line is already printed)."""
+    import gc
     import torch
     torch.cuda.synchronize()
-    watchdog = threading.Timer(20.0, lambda: os._exit(0))
-    watchdog.daemon = True
-    watchdog.start()
-    try:
-        dist.barrier()
-    finally:
-        sys.stdout.flush()
-        sys.stderr.flush()
+    for obj in release:
+        if hasattr(obj, "release_graph"):
+            obj.release_graph()
+    gc.collect()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    for obj in release:
+        if hasattr(obj, "close"):
+            obj.close()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    done = threading.Event()
+
+    def teardown():
+        try:
+            dist.destroy_process_group()
+        finally:
+            done.set()
+
+    th = threading.Thread(target=teardown, daemon=True)
+    th.start()
+    th.join(timeout=20.0)
+    if not done.is_set():
+        print("[bench] destroy_process_group did not return within 20 s; exiting without it", file=sys.stderr, flush=True)
         os._exit(0)
+    sys.exit(0)
 
 
 def main():
@@ -216,6 +245,8 @@ def main():
     ap.add_argument("--comm", default="p2p", choices=["nccl", "p2p"], help="grid collectives: NCCL or the package's peer-memory kernels")
     ap.add_argument("--heap_mb", type=int, default=2048)
     ap.add_argument("--no_graph", action="store_true", help="run the step eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--profile", default=None, metavar="PREFIX",
+                    help="after timing, write the per-kernel device time of one more step to PREFIX.rank<r>.txt (not part of the timed region)")
     ap.add_argument("--scale_down", type=int, default=1, help="divide the graph size (profiling captures only; invalid as a bench value)")
     args = ap.parse_args()
     if args.impl == "reference":

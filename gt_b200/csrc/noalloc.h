@@ -18,6 +18,12 @@
 // Rules of use.
 //  * Capacity: n_slots * d must not exceed GT_NOALLOC_SCRATCH_FLOATS; a larger request is rejected with
 //    GT_NOALLOC_ERR_CAPACITY and nothing is launched.  gt_noalloc_last_error() returns a readable message.
+//  * The plan must agree with n_slots: n_slots has to equal split_ptr[n_split] (= max(seg_slot) + 1), and EVERY seg_slot[i]
+//    must be < n_slots.  The check above is made on the host scalar, while the kernels index the scratch with the slot
+//    numbers stored in the device arrays, which host code cannot read without a copy: a plan whose slot numbers exceed the
+//    declared n_slots writes past the array.  Validate plans on the host before uploading them
+//    (gt_b200.utils.checks.validate_segment_plan does).
+//  * A plan without segments (n_seg == 0) describes a matrix without entries: the call fills `out` with zeros.
 //  * First call on a device: the call looks up the device address of the scratch array (cudaGetSymbolAddress, with that
 //    device current) and caches it per device.  Make this first call outside any stream capture.
 //  * The scratch is shared by all calls and keeps the previous call's contents.  Every slot a call reads was written by the

@@ -168,7 +168,11 @@ extern "C" int gt_spmm_csr_noalloc(int dtype, const int* ptr, const int* idx, co
         snprintf(detail, sizeof(detail), " (requested %d slots x %d floats, capacity %u floats)", n_slots, d, GT_NOALLOC_SCRATCH_FLOATS);
         return noalloc_fail(GT_NOALLOC_ERR_CAPACITY, "split-row scratch exceeds the built-in array", detail);
     }
-    if (n_out == 0 || n_seg == 0) return GT_NOALLOC_OK;
+    if (n_out == 0) return GT_NOALLOC_OK;
+    if (n_seg == 0) {            // no entries at all: the product is zero (a fill of the caller's buffer, nothing is allocated)
+        cudaError_t ez = cudaMemsetAsync(out, 0, (size_t)n_out * d * (dtype == gt::DT_BF16 ? 2 : 4), static_cast<cudaStream_t>(stream));
+        return ez == cudaSuccess ? GT_NOALLOC_OK : noalloc_fail(GT_NOALLOC_ERR_CUDA, "cudaMemsetAsync failed: ", cudaGetErrorString(ez));
+    }
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return noalloc_fail(GT_NOALLOC_ERR_CUDA, "cudaGetDevice failed: ", cudaGetErrorString(e));

@@ -23,7 +23,11 @@ import torch.distributed as dist
 from ..ops import native
 
 _DT = {torch.float32: 0, torch.bfloat16: 1, torch.int32: 2, torch.int64: 3, torch.uint8: 4}
-MAX_SPINS = 5_000_000          # ~1 s of polling before a barrier gives up
+import os
+
+# polls before a wait on a peer gives up (~1 s at the default).  A rank-local stall longer than this (first-launch module
+# loading, a slow evaluation on one rank) makes the wait expire, so runs with long rank-local phases raise it.
+MAX_SPINS = int(os.environ.get("GT_PEER_WAIT_SPINS", "5000000"))
 
 
 class GroupContext:

@@ -41,7 +41,7 @@ def save_checkpoint(path, model, engine=None, epoch=0, extra=None):
 
 def load_checkpoint(path, model, engine=None, strict=True):
     """Load on every rank; returns ``(epoch, extra)``.  A bare state dict (e.g. saved from a reference model) is accepted."""
-    blob = torch.load(path, map_location="cpu", weights_only=False)
+    blob = torch.load(path, map_location="cpu", weights_only=True)      # tensors, dicts, lists, numbers and strings only
     sd = blob["model"] if isinstance(blob, dict) and "model" in blob and "format_version" in blob else blob
     own = model.state_dict()
     missing = [k for k in own if k not in sd]
@@ -58,6 +58,14 @@ def load_checkpoint(path, model, engine=None, strict=True):
     if sd is blob:
         return 0, {}
     if engine is not None and "optimizer" in blob:
+        opt = blob["optimizer"]
+        names = [n for n, p in model.named_parameters() if p.requires_grad]
+        if "names" in opt and list(opt["names"]) != names:
+            raise ValueError("checkpoint was written for a different configuration: the optimizer state covers other parameters "
+                             f"(or another order) than this model: first difference near {next((a, b) for a, b in zip(list(opt['names']) + [None], names + [None]) if a != b)}")
+        if opt["m"].numel() != engine.numel or opt["v"].numel() != engine.numel:
+            raise ValueError(f"checkpoint was written for a different configuration: optimizer moments of {opt['m'].numel()} elements, "
+                             f"model has {engine.numel} trainable elements")
         engine.load_state_dict(dict(step=blob["optimizer"]["step"], m=blob["optimizer"]["m"].to(engine.device),
                                     v=blob["optimizer"]["v"].to(engine.device)))
     if "rng_cpu" in blob:

@@ -40,6 +40,8 @@ def init_single_process_group(backend=None):
 
 
 class TrainEngine:
+    HYPER_SLOTS = 32
+
     def __init__(self, model, lr=1e-3, weight_decay=1e-3, total_steps=100, warmup=5, max_grad_norm=1.0, betas=(0.9, 0.999),
                  eps=1e-8, group=None, use_graph=False, graph_warmup=3, heap=None):
         self.model = model
@@ -72,12 +74,17 @@ class TrainEngine:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         if self.cuda:
             self.hyper = torch.zeros(9, dtype=torch.float32, device=dev)
-            self.hyper_host = torch.zeros(9, dtype=torch.float32).pin_memory()
+            # The host may run many steps ahead of the device (graph replays are enqueued without a sync), and an asynchronous
+            # host-to-device copy reads pinned memory when it EXECUTES: each step therefore writes its own pinned slot, and a
+            # slot is rewritten only after the event recorded behind its previous copy has completed.
+            self._hyper_slots = torch.zeros(self.HYPER_SLOTS, 8, dtype=torch.float32).pin_memory()
+            self._hyper_events = [None] * self.HYPER_SLOTS
             self.g_sum = torch.zeros_like(self.flat_g) if heap is not None else None
         self.use_graph = use_graph and self.cuda
         self.graph_warmup = graph_warmup
         self._graph = None
         self._static_loss = None
+        self._warm_done = 0          # eager steps run by THIS engine (a resumed step_count must not skip the warm-up)
 
     # ---- pieces of a step --------------------------------------------------------------------------------------------
     def _set_hyper(self):
@@ -85,17 +92,23 @@ class TrainEngine:
         lr = self.lr * cosine_with_warmup(self.step_count, self.warmup, self.total)
         self.cur_lr = lr
         if self.cuda:
-            h = self.hyper_host
+            i = self._hyper_cursor = (getattr(self, "_hyper_cursor", -1) + 1) % self.HYPER_SLOTS
+            if self._hyper_events[i] is not None:
+                self._hyper_events[i].synchronize()
+            h = self._hyper_slots[i]
             h[0], h[1], h[2], h[3], h[4] = lr, self.betas[0], self.betas[1], self.eps, self.wd
             h[5], h[6] = 1.0 - self.betas[0] ** t, 1.0 - self.betas[1] ** t
             h[7] = self.max_norm if self.max_norm else 0.0
-            self.hyper[:8].copy_(h[:8], non_blocking=True)
+            self.hyper[:8].copy_(h, non_blocking=True)
+            ev = self._hyper_events[i] or torch.cuda.Event()
+            ev.record()
+            self._hyper_events[i] = ev
 
     def _reduce_grads(self):
         if self.world == 1:
             return self.flat_g
         if self.heap is not None and self.cuda:
-            return self.heap.all_reduce(self.flat_g, self.g_sum, "grads")
+            return self.heap.all_reduce(self.flat_g, self.g_sum, "grads", group=self.group)
         dist.all_reduce(self.flat_g, group=self.group)
         return self.flat_g
 
@@ -138,12 +151,13 @@ class TrainEngine:
         self._set_hyper()
         if not self.use_graph:
             loss = self._body(loss_fn)
-        elif self._graph is None and self.step_count < self.graph_warmup:
+        elif self._graph is None and self._warm_done < self.graph_warmup:
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
                 loss = self._body(loss_fn)
             torch.cuda.current_stream().wait_stream(side)
+            self._warm_done += 1
         else:
             if self._graph is None:
                 self._graph = torch.cuda.CUDAGraph()
@@ -153,6 +167,12 @@ class TrainEngine:
             loss = self._static_loss
         self.step_count += 1
         return loss
+
+    def release_graph(self):
+        """Drop the captured step (and the collectives recorded in it); the next ``train_step`` runs eagerly and re-captures."""
+        self._graph = None
+        self._static_loss = None
+        self._warm_done = 0
 
     def state_dict(self):
         return dict(step=self.step_count, m=self.flat_m[:self.numel].clone(), v=self.flat_v[:self.numel].clone())

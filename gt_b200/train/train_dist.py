@@ -148,6 +148,23 @@ def device_epoch_ms(fn, dev):
     return out, float(t.item())
 
 
+def check_status_all_ranks(dev, world):
+    """Read the device status word (an expired bounded wait of a peer-memory kernel) and make every rank stop together:
+    the code is all-reduced with MAX, so a rank whose own waits were fine does not train on against a peer that gave up."""
+    from ..ops import native
+    code = int(native.status(dev).item())
+    if world > 1:
+        t = torch.tensor([code], dtype=torch.int32, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        worst = int(t.item())
+    else:
+        worst = code
+    if worst != 0:
+        native.status(dev).zero_()
+        raise RuntimeError(f"gt_b200: a peer-memory wait expired on some rank (code {worst}; this rank's code {code}): the step that "
+                           "followed read incomplete buffers, so training stops before its results are used or saved")
+
+
 def _auto_grid(args, world, n, e_graph, f_in, rank):
     """--grid_auto / --head_auto: the white-box model's choice for this world size."""
     from ..perf import grid_select as gs
@@ -360,6 +377,8 @@ def main(argv=None):
         if cstats is not None:
             cstats.end_epoch(keep=epoch >= start_epoch + 2)
         epoch_ms.append(ms)
+        if cuda:
+            check_status_all_ranks(dev, world)            # device_epoch_ms has synchronised: the status word is final for this epoch
         if epoch in (start_epoch, start_epoch + 2):
             mem(f"after step (epoch {epoch})", model)
         if epoch % args.eval_every == 0 or epoch == args.epochs - 1:
@@ -376,10 +395,13 @@ def main(argv=None):
                       f"| best val {best['val']:.4f} test {best['test']:.4f} @ {best['epoch']} | {sum(epoch_ms) / len(epoch_ms):.1f} ms/epoch train",
                       flush=True)
         if args.save and args.save_every and (epoch + 1) % args.save_every == 0:
+            if cuda:
+                torch.cuda.synchronize()
+                check_status_all_ranks(dev, world)        # never write a checkpoint from a step whose peer wait expired
             save_checkpoint(args.save, model, eng, epoch + 1, dict(best=best))
     if cuda:
         torch.cuda.synchronize()
-        native.check_status(dev)
+        check_status_all_ranks(dev, world)
     if args.save:
         save_checkpoint(args.save, model, eng, args.epochs, dict(best=best))
     if cstats is not None:

@@ -34,18 +34,20 @@ def _lib():
     return lib
 
 
-def _call(lib, blk, plan, x, out, n_slots=None):
+def _call(lib, blk, plan, x, out, n_slots=None, use_weight=True):
     ptr = lambda t: ctypes.c_void_p(t.data_ptr())          # noqa: E731
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     dtype = 1 if x.dtype == torch.bfloat16 else 0
-    return lib.gt_spmm_csr_noalloc(dtype, ptr(blk.crow), ptr(blk.col), ptr(blk.weight), ptr(x), ptr(out), blk.n_rows, x.shape[1],
+    w = ptr(blk.weight) if use_weight else ctypes.c_void_p(0)
+    return lib.gt_spmm_csr_noalloc(dtype, ptr(blk.crow), ptr(blk.col), w, ptr(x), ptr(out), blk.n_rows, x.shape[1],
                                    ptr(plan.seg_row), ptr(plan.seg_beg), ptr(plan.seg_end), ptr(plan.seg_slot), plan.num_segments,
                                    ptr(plan.split_rows), ptr(plan.split_ptr), int(plan.split_rows.numel()),
                                    plan.num_slots if n_slots is None else n_slots, stream)
 
 
-@pytest.mark.parametrize("dtype,d", [(torch.float32, 128), (torch.bfloat16, 256)])
-def test_noalloc_matches_regular_entry_point_twice(dtype, d):
+@pytest.mark.parametrize("dtype,d,weighted", [(torch.float32, 128, True), (torch.bfloat16, 256, True), (torch.bfloat16, 512, True),
+                                              (torch.float32, 1024, True), (torch.bfloat16, 256, False)])
+def test_noalloc_matches_regular_entry_point_twice(dtype, d, weighted):
     from gt_b200.attention import BlockCSR
     from gt_b200.ops import native
     dev = torch.device("cuda:0")
@@ -53,7 +55,8 @@ def test_noalloc_matches_regular_entry_point_twice(dtype, d):
     lib = _lib()
     n = 1500
     ei, _ = random_graph(n, 5, seed=11)                      # node 1 is a hub row with n in-edges -> split rows
-    blk = BlockCSR.from_edges(ei, n, n, weight=torch.rand(ei.shape[1])).to(dev)
+    # w = NULL means "all weights one": the regular entry point is then given a block whose weights are ones
+    blk = BlockCSR.from_edges(ei, n, n, weight=torch.rand(ei.shape[1]) if weighted else torch.ones(ei.shape[1])).to(dev)
     plan = blk.row_plan(64)
     assert plan.num_slots > 0 and plan.num_slots * d <= lib.gt_noalloc_scratch_floats()
     tol = 1e-5 if dtype == torch.float32 else 2e-2
@@ -61,11 +64,29 @@ def test_noalloc_matches_regular_entry_point_twice(dtype, d):
         x = torch.randn(n, d, device=dev, generator=torch.Generator(device=dev).manual_seed(trial)).to(dtype)
         ref = native.spmm(blk, x)                            # regular entry point (scratch from the caching allocator)
         out = torch.full_like(ref, float("nan"))
-        rc = _call(lib, blk, plan, x, out)
+        rc = _call(lib, blk, plan, x, out, use_weight=weighted)
         torch.cuda.synchronize()
         assert rc == 0, lib.gt_noalloc_last_error().decode()
         err = (out.float() - ref.float()).abs().max().item() / max(ref.float().abs().max().item(), 1e-6)
         assert err < tol, (trial, err)
+
+
+def test_noalloc_empty_plan_zero_fills():
+    from gt_b200.attention import BlockCSR
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    lib = _lib()
+    ei, _ = random_graph(64, 3, seed=5)
+    blk = BlockCSR.from_edges(ei, 64, 64, weight=torch.rand(ei.shape[1])).to(dev)
+    plan = blk.row_plan(16)
+    x = torch.randn(64, 32, device=dev)
+    out = torch.full((64, 32), float("nan"), device=dev)
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr())          # noqa: E731
+    rc = lib.gt_spmm_csr_noalloc(0, ptr(blk.crow), ptr(blk.col), ptr(blk.weight), ptr(x), ptr(out), 64, 32, ptr(plan.seg_row),
+                                 ptr(plan.seg_beg), ptr(plan.seg_end), ptr(plan.seg_slot), 0, ptr(plan.split_rows), ptr(plan.split_ptr),
+                                 0, 0, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert rc == 0 and out.abs().max().item() == 0
 
 
 def test_noalloc_rejects_oversized_scratch():
