@@ -97,7 +97,7 @@ def attn_fwd_partial(q, k, v, blk: BlockCSR, gate=None, bias=None, *, score="dot
     g, b = _tables(gate, bias, score)
     native.ext().attn_fwd(q.contiguous(), k.contiguous() if k is not None else None, v.contiguous() if v is not None else None,
                           blk.col, blk.etype, g, b, _plan_list(plan), None, acc, l, m, scratch, h, d, sc, nm, scale, lo, hi,
-                          h * d, h, False, k_peers, v_peers, int(rows_per_peer))
+                          h * d, h, False, k_peers, v_peers, int(rows_per_peer), 0, 0, [], 0, 0, 0)
     return acc, l, m
 
 
@@ -127,7 +127,7 @@ def attn_fwd_partial_accum(q, k, v, blk: BlockCSR, gate, bias, packed, hd, *, sc
     qc = q.reshape(n, hd)[rows.long()].contiguous()
     stride = packed.stride(0)
     native.ext().attn_fwd(qc, k.contiguous(), v.contiguous(), blk.col, blk.etype, g, b, _plan_list(plan), rows,
-                          packed, packed[:, hd:], None, scratch, h, d, sc, nm, scale, lo, hi, stride, stride, True, None, None, 0)
+                          packed, packed[:, hd:], None, scratch, h, d, sc, nm, scale, lo, hi, stride, stride, True, None, None, 0, 0, 0, [], 0, 0, 0)
 
 
 def normalize(acc, l, norm, eps=1e-6, dtype=None):
@@ -157,22 +157,22 @@ def _bwd(q, k, v, blk, gate, bias, row_vec, stat, score, norm, clamp, scale, seg
     dbp = torch.empty(nb, t * h, dtype=torch.float32, device=q.device) if b is not None else None
     scratch = torch.empty(plan.num_slots, h * d, dtype=torch.float32, device=q.device) if plan.num_slots else None
     e.attn_bwd_row(q, k, v, rv, stat, blk.col, blk.etype, g, b, _plan_list(plan), None, dq, False, dgp, dbp, nb, scratch,
-                   h, d, sc, nm, scale, lo, hi)
+                   h, d, sc, nm, scale, lo, hi, 0, 0, 0, 0)
     dgate = dbias = None
     if g is not None:
         dgate = torch.empty(t * h * d, dtype=torch.float32, device=q.device)
-        e.reduce_partials(dgp, dgate)
+        e.reduce_partials(dgp, dgate, False)
         dgate = dgate.view(t, h, d)
     if b is not None:
         dbias = torch.empty(t * h, dtype=torch.float32, device=q.device)
-        e.reduce_partials(dbp, dbias)
+        e.reduce_partials(dbp, dbias, False)
         dbias = dbias.view(t, h)
     # column pass over the transposed structure
     _, rowidx, et_t, _, _ = blk.csc()
     cplan = blk.col_plan(seg_edges)
     dk, dv = torch.empty(nc, h, d, dtype=q.dtype, device=q.device), torch.empty(nc, h, d, dtype=q.dtype, device=q.device)
     cscratch = torch.empty(cplan.num_slots, 2 * h * d, dtype=torch.float32, device=q.device) if cplan.num_slots else None
-    e.attn_bwd_col(q, k, v, rv, stat, rowidx, et_t, g, b, _plan_list(cplan), dk, dv, cscratch, h, d, sc, nm, scale, lo, hi)
+    e.attn_bwd_col(q, k, v, rv, stat, rowidx, et_t, g, b, _plan_list(cplan), dk, dv, cscratch, h, d, sc, nm, scale, lo, hi, 0, 0, 0, 0)
     return dq, dk, dv, dgate, dbias
 
 

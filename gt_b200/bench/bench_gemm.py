@@ -64,7 +64,7 @@ def main():
             e = native.ext()
 
             def fused(copy):
-                e.gemm_nt_gather(ptrs, chunk, k, k, w, y, None, 0, 0.0, None, 0, xg if copy else None, native.status(dev))
+                e.gemm_nt_gather(ptrs, chunk, k, k, w, y, None, 0, 0.0, None, 0, xg if copy else None, native.status(dev), None, None, 0, 0)
             ms = timeit(lambda: fused(False), args.iters, args.warmup)
             ms_c = timeit(lambda: fused(True), args.iters, args.warmup)
             fused(True)

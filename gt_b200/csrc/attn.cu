@@ -83,6 +83,38 @@ __device__ __forceinline__ void load_tables(const AttnCommon& c, float* s_gate, 
     __syncthreads();
 }
 
+// Reduce-scatter fused into the forward epilogue: the finished partial row [acc | l] goes, as bf16, straight into the slot
+// that the row's OWNER keeps for this rank (a[r, 0 : H*D] = acc, a[r, l_off : l_off + H] = l; 16-byte peer stores over NVLink),
+// so the packed payload never exists in local memory and no separate collective moves it.  Called by all 32 lanes.
+template <int CPL>
+__device__ __forceinline__ void push_partial_row(const AttnFwdArgs& a, long long orow, const Lanes& L, int H, const int (&foff)[CPL],
+                                                 const float (&acc)[CPL][8], const float (&l)[CPL]) {
+    const int owner = (int)(orow / a.push_rows);
+    const long long r = orow - (long long)owner * a.push_rows;
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.push_slot[owner]) + r * a.push_ld;
+    const int lane = threadIdx.x & 31;
+    const int Hp = (H + 7) & ~7;
+    for (int g8 = 0; g8 < Hp; g8 += 8) {                 // the heads' l values are collected in lane 0, eight per 16-byte store
+        float lv[8];
+#pragma unroll
+        for (int x = 0; x < 8; ++x) {
+            const int chunk = (g8 + x) * L.lph;          // first 8-element chunk of head g8 + x
+            const int src = chunk & 31, ci = chunk >> 5;
+            float val = 0.f;
+#pragma unroll
+            for (int i = 0; i < CPL; ++i) {
+                const float t = __shfl_sync(GT_FULL_MASK, l[i], src);
+                if (i == ci) val = t;
+            }
+            lv[x] = (g8 + x) < H ? val : 0.f;
+        }
+        if (lane == 0) Vec8<__nv_bfloat16>::store(dst + a.push_l_off + g8, lv);
+    }
+    if (L.sub != 0) return;
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) Vec8<__nv_bfloat16>::store(dst + foff[i], acc[i]);
+}
+
 // ------------------------------------------------------------------------------------------------------------------
 // forward
 // ------------------------------------------------------------------------------------------------------------------
@@ -97,6 +129,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 6 : 3)) attn_
     float* s_bias = smem + (c.score == SCORE_GATED ? c.T * HD : 0);
     load_tables(c, s_gate, s_bias);
     const Lanes L = make_lanes(HD, D);
+    // row strides in elements (0 = dense rows of H*D): operands may be column slices of wider matrices, e.g. K | V | message
+    const size_t ldq = c.ldq ? (size_t)c.ldq : (size_t)HD, ldk = c.ldk ? (size_t)c.ldk : (size_t)HD;
+    const size_t ldr = c.ldr ? (size_t)c.ldr : (size_t)HD, ldo = c.ldo ? (size_t)c.ldo : (size_t)HD;
+    (void)ldq; (void)ldk; (void)ldr; (void)ldo;
     const T* q = static_cast<const T*>(a.q);
     const T* kb = static_cast<const T*>(a.k);
     const T* vb = static_cast<const T*>(a.v);
@@ -116,7 +152,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 6 : 3)) attn_
         float qf[CPL][8], acc[CPL][8], l[CPL], m[CPL];
 #pragma unroll
         for (int i = 0; i < CPL; ++i) {
-            Vec8<T>::load(q + (size_t)row * HD + foff[i], qf[i]);
+            Vec8<T>::load(q + (size_t)row * ldq + foff[i], qf[i]);
 #pragma unroll
             for (int x = 0; x < 8; ++x) { qf[i][x] *= c.scale; acc[i][x] = 0.f; }
             l[i] = 0.f;
@@ -143,11 +179,11 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 6 : 3)) attn_
                     const T* kp; const T* vp;
                     if (PEER) {
                         const int p = j[u] / a.rows_per_peer, r = j[u] - p * a.rows_per_peer;
-                        kp = static_cast<const T*>(a.k_peers[p]) + (size_t)r * HD;
-                        vp = static_cast<const T*>(a.v_peers[p]) + (size_t)r * HD;
+                        kp = static_cast<const T*>(a.k_peers[p]) + (size_t)r * ldk;
+                        vp = static_cast<const T*>(a.v_peers[p]) + (size_t)r * ldk;
                     } else {
-                        kp = kb + (size_t)j[u] * HD;
-                        vp = vb + (size_t)j[u] * HD;
+                        kp = kb + (size_t)j[u] * ldk;
+                        vp = vb + (size_t)j[u] * ldk;
                     }
 #pragma unroll
                     for (int i = 0; i < CPL; ++i) { kr[u][i] = Vec8<T>::load_raw(kp + foff[i]); vr[u][i] = Vec8<T>::load_raw(vp + foff[i]); }
@@ -227,6 +263,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 6 : 3)) attn_
                 }
             }
         }
+        if (a.push_n > 0 && slot < 0) {
+            push_partial_row<CPL>(a, a.row_map ? a.row_map[row] : row, L, H, foff, acc, l);
+            continue;
+        }
         if (L.sub != 0) continue;
         if (slot < 0) {
             const long long orow = a.row_map ? a.row_map[row] : row;
@@ -277,6 +317,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (UU * NSTG <=
     constexpr int NST = NSTG;
     int* tring = reinterpret_cast<int*>(ring + (size_t)NSTG * UU * CPL * 2 * (kWarpsPerBlock * 32));      // edge types of the groups in flight
     const Lanes L = make_lanes(HD, D);
+    // row strides in elements (0 = dense rows of H*D): operands may be column slices of wider matrices, e.g. K | V | message
+    const size_t ldq = c.ldq ? (size_t)c.ldq : (size_t)HD, ldk = c.ldk ? (size_t)c.ldk : (size_t)HD;
+    const size_t ldr = c.ldr ? (size_t)c.ldr : (size_t)HD, ldo = c.ldo ? (size_t)c.ldo : (size_t)HD;
+    (void)ldq; (void)ldk; (void)ldr; (void)ldo;
     const T* q = static_cast<const T*>(a.q);
     const T* kb = static_cast<const T*>(a.k);
     const T* vb = static_cast<const T*>(a.v);
@@ -296,7 +340,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (UU * NSTG <=
         float qf[CPL][8], acc[CPL][8], l[CPL], m[CPL];
 #pragma unroll
         for (int i = 0; i < CPL; ++i) {
-            Vec8<T>::load(q + (size_t)row * HD + foff[i], qf[i]);
+            Vec8<T>::load(q + (size_t)row * ldq + foff[i], qf[i]);
 #pragma unroll
             for (int x = 0; x < 8; ++x) { qf[i][x] *= c.scale; acc[i][x] = 0.f; }
             l[i] = 0.f;
@@ -321,8 +365,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (UU * NSTG <=
             if (g < n_it) {
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
-                    const T* kp = kb + (size_t)jn[u] * HD;
-                    const T* vp = vb + (size_t)jn[u] * HD;
+                    const T* kp = kb + (size_t)jn[u] * ldk;
+                    const T* vp = vb + (size_t)jn[u] * ldk;
 #pragma unroll
                     for (int i = 0; i < CPL; ++i) {
                         uint4* dst = ring + ((((g % NST) * U + u) * CPL + i) * 2) * (kWarpsPerBlock * 32) + threadIdx.x;
@@ -420,6 +464,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (UU * NSTG <=
                 }
             }
         }
+        if (a.push_n > 0 && slot < 0) {
+            push_partial_row<CPL>(a, a.row_map ? a.row_map[row] : row, L, H, foff, acc, l);
+            continue;
+        }
         if (L.sub != 0) continue;
         if (slot < 0) {
             const long long orow = a.row_map ? a.row_map[row] : row;
@@ -480,6 +528,12 @@ __global__ void attn_fwd_combine_sum_kernel(AttnFwdArgs a) {
     const int f = blockIdx.y * 32 + threadIdx.x;
     const float v = tile_slot_sum(c.scratch, s0, s1, W, f, f < HD + H, sm);
     if (threadIdx.y != 0 || f >= HD + H) return;
+    if (a.push_n > 0) {                                  // split rows of the fused reduce-scatter: the merged row goes to its owner
+        const int owner = (int)(orow / a.push_rows);
+        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.push_slot[owner]) + (orow - (long long)owner * a.push_rows) * a.push_ld;
+        dst[f < HD ? f : a.push_l_off + (f - HD)] = __float2bfloat16(v);
+        return;
+    }
     if (f < HD) {
         float* dst = a.acc + orow * a.acc_stride + f;
         *dst = a.accumulate ? *dst + v : v;
@@ -563,6 +617,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 5 : 
     for (int i = threadIdx.x; i < acc_n; i += blockDim.x) s_dg[i] = 0.f;
     __syncthreads();
     const Lanes L = make_lanes(HD, D);
+    // row strides in elements (0 = dense rows of H*D): operands may be column slices of wider matrices, e.g. K | V | message
+    const size_t ldq = c.ldq ? (size_t)c.ldq : (size_t)HD, ldk = c.ldk ? (size_t)c.ldk : (size_t)HD;
+    const size_t ldr = c.ldr ? (size_t)c.ldr : (size_t)HD, ldo = c.ldo ? (size_t)c.ldo : (size_t)HD;
+    (void)ldq; (void)ldk; (void)ldr; (void)ldo;
     const bool softmax = c.norm == NORM_SOFTMAX;
     const T* q = static_cast<const T*>(a.q);
     const T* kb = static_cast<const T*>(a.k);
@@ -589,8 +647,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 5 : 
         float qf[CPL][8], rv[CPL][8], A[CPL][8], dqa[CPL][8], db[kMaxTypesReg][CPL], mrow[CPL], rb[CPL], ps[CPL];
 #pragma unroll
         for (int i = 0; i < CPL; ++i) {
-            Vec8<T>::load(q + srow * HD + foff[i], qf[i]);
-            Vec8<T>::load(rvb + srow * HD + foff[i], rv[i]);
+            Vec8<T>::load(q + srow * ldq + foff[i], qf[i]);
+            Vec8<T>::load(rvb + srow * ldr + foff[i], rv[i]);
             const float4 st = a.stat[srow * H + head[i]];
             mrow[i] = st.x; rb[i] = st.y; ps[i] = st.z;
 #pragma unroll
@@ -619,8 +677,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 5 : 
 #pragma unroll
                     for (int i = 0; i < CPL; ++i) {
                         uint4* dst = ring + ((((g % NST) * U + u) * CPL + i) * 2) * (kWarpsPerBlock * 32) + threadIdx.x;
-                        cp_async16(dst, kb + (size_t)jn[u] * HD + foff[i]);
-                        cp_async16(dst + kWarpsPerBlock * 32, vb + (size_t)jn[u] * HD + foff[i]);
+                        cp_async16(dst, kb + (size_t)jn[u] * ldk + foff[i]);
+                        cp_async16(dst + kWarpsPerBlock * 32, vb + (size_t)jn[u] * ldk + foff[i]);
                     }
                     tring[((g % NST) * U + u) * (kWarpsPerBlock * 32) + threadIdx.x] = tn[u];
                 }
@@ -667,8 +725,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 5 : 
                     if (j[u] >= 0) {
 #pragma unroll
                         for (int i = 0; i < CPL; ++i) {
-                            kr[u][i] = Vec8<T>::load_raw(kb + (size_t)j[u] * HD + foff[i]);
-                            vr[u][i] = Vec8<T>::load_raw(vb + (size_t)j[u] * HD + foff[i]);
+                            kr[u][i] = Vec8<T>::load_raw(kb + (size_t)j[u] * ldk + foff[i]);
+                            vr[u][i] = Vec8<T>::load_raw(vb + (size_t)j[u] * ldk + foff[i]);
                         }
                     } else {
 #pragma unroll
@@ -772,14 +830,14 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 5 : 
             if (slot >= 0) {
                 Vec8<float>::store(c.scratch + (size_t)slot * HD + foff[i], dq);
             } else if (a.accumulate_dq) {
-                float* dst = static_cast<float*>(a.dq) + srow * HD + foff[i];
+                float* dst = static_cast<float*>(a.dq) + srow * ldo + foff[i];
                 float old[8];
                 Vec8<float>::load(dst, old);
 #pragma unroll
                 for (int x = 0; x < 8; ++x) old[x] += dq[x];
                 Vec8<float>::store(dst, old);
             } else {
-                Vec8<T>::store(static_cast<T*>(a.dq) + srow * HD + foff[i], dq);
+                Vec8<T>::store(static_cast<T*>(a.dq) + srow * ldo + foff[i], dq);
             }
         }
     }
@@ -791,7 +849,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 5 : 
 // out[row] (+)= sum of the row's slots; grid (split rows, 32-column groups), block (32, 8)
 template <typename T>
 __global__ void sum_slots_kernel(const SegPlan plan, const float* scratch, int width, const int* row_map, T* out, float* out_f32,
-                                 int accumulate) {
+                                 int accumulate, long long ld) {
     __shared__ float sm[8][33];
     const int r = blockIdx.x;
     const int row = plan.split_rows[r];
@@ -801,10 +859,10 @@ __global__ void sum_slots_kernel(const SegPlan plan, const float* scratch, int w
     const float v = tile_slot_sum(scratch, s0, s1, width, f, f < width, sm);
     if (threadIdx.y != 0 || f >= width) return;
     if (out_f32) {
-        float* d = out_f32 + orow * width + f;
+        float* d = out_f32 + orow * ld + f;
         *d = accumulate ? *d + v : v;
     } else {
-        out[orow * width + f] = from_float<T>(v);
+        out[orow * ld + f] = from_float<T>(v);
     }
 }
 
@@ -822,6 +880,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 4 : 
     float* s_bias = smem + (c.score == SCORE_GATED ? c.T * HD : 0);
     load_tables(c, s_gate, s_bias);
     const Lanes L = make_lanes(HD, D);
+    // row strides in elements (0 = dense rows of H*D): operands may be column slices of wider matrices, e.g. K | V | message
+    const size_t ldq = c.ldq ? (size_t)c.ldq : (size_t)HD, ldk = c.ldk ? (size_t)c.ldk : (size_t)HD;
+    const size_t ldr = c.ldr ? (size_t)c.ldr : (size_t)HD, ldo = c.ldo ? (size_t)c.ldo : (size_t)HD;
+    (void)ldq; (void)ldk; (void)ldr; (void)ldo;
     const bool softmax = c.norm == NORM_SOFTMAX;
     const T* qb = static_cast<const T*>(a.q);
     const T* rvb = static_cast<const T*>(a.row_vec);
@@ -842,8 +904,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 4 : 
         float kf[CPL][8], vf[CPL][8], dk[CPL][8], dv[CPL][8];
 #pragma unroll
         for (int i = 0; i < CPL; ++i) {
-            Vec8<T>::load(static_cast<const T*>(a.k) + (size_t)colj * HD + foff[i], kf[i]);
-            Vec8<T>::load(static_cast<const T*>(a.v) + (size_t)colj * HD + foff[i], vf[i]);
+            Vec8<T>::load(static_cast<const T*>(a.k) + (size_t)colj * ldk + foff[i], kf[i]);
+            Vec8<T>::load(static_cast<const T*>(a.v) + (size_t)colj * ldk + foff[i], vf[i]);
 #pragma unroll
             for (int x = 0; x < 8; ++x) { dk[i][x] = 0.f; dv[i][x] = 0.f; }
         }
@@ -866,8 +928,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 4 : 
 #pragma unroll
                     for (int i = 0; i < CPL; ++i) {
                         uint4* dst = ring + ((((g % NST) * U + u) * CPL + i) * 3) * (kWarpsPerBlock * 32) + threadIdx.x;
-                        cp_async16(dst, qb + (size_t)rn[u] * HD + foff[i]);
-                        cp_async16(dst + kWarpsPerBlock * 32, rvb + (size_t)rn[u] * HD + foff[i]);
+                        cp_async16(dst, qb + (size_t)rn[u] * ldq + foff[i]);
+                        cp_async16(dst + kWarpsPerBlock * 32, rvb + (size_t)rn[u] * ldr + foff[i]);
                         cp_async16(dst + 2 * kWarpsPerBlock * 32, a.stat + (size_t)rn[u] * H + head[i]);
                     }
                     tring[((g % NST) * U + u) * (kWarpsPerBlock * 32) + threadIdx.x] = tn[u];
@@ -918,8 +980,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 4 : 
                     if (r[u] >= 0) {
 #pragma unroll
                         for (int i = 0; i < CPL; ++i) {
-                            qr[u][i] = Vec8<T>::load_raw(qb + (size_t)r[u] * HD + foff[i]);
-                            rr[u][i] = Vec8<T>::load_raw(rvb + (size_t)r[u] * HD + foff[i]);
+                            qr[u][i] = Vec8<T>::load_raw(qb + (size_t)r[u] * ldq + foff[i]);
+                            rr[u][i] = Vec8<T>::load_raw(rvb + (size_t)r[u] * ldr + foff[i]);
                             st[u][i] = __ldg(a.stat + (size_t)r[u] * H + head[i]);
                         }
                     } else {
@@ -1006,15 +1068,15 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 4 : 
                 Vec8<float>::store(c.scratch + (size_t)slot * 2 * HD + foff[i], dk[i]);
                 Vec8<float>::store(c.scratch + (size_t)slot * 2 * HD + HD + foff[i], dv[i]);
             } else {
-                Vec8<T>::store(static_cast<T*>(a.dk) + (size_t)colj * HD + foff[i], dk[i]);
-                Vec8<T>::store(static_cast<T*>(a.dv) + (size_t)colj * HD + foff[i], dv[i]);
+                Vec8<T>::store(static_cast<T*>(a.dk) + (size_t)colj * ldo + foff[i], dk[i]);
+                Vec8<T>::store(static_cast<T*>(a.dv) + (size_t)colj * ldo + foff[i], dv[i]);
             }
         }
     }
 }
 
 template <typename T>
-__global__ void sum_slots_kv_kernel(const SegPlan plan, const float* scratch, int HD, T* dk, T* dv) {
+__global__ void sum_slots_kv_kernel(const SegPlan plan, const float* scratch, int HD, T* dk, T* dv, long long ld) {
     __shared__ float sm[8][33];
     const int r = blockIdx.x;
     const int colj = plan.split_rows[r];
@@ -1022,13 +1084,13 @@ __global__ void sum_slots_kv_kernel(const SegPlan plan, const float* scratch, in
     const int f = blockIdx.y * 32 + threadIdx.x;
     const float v = tile_slot_sum(scratch, s0, s1, 2 * HD, f, f < 2 * HD, sm);
     if (threadIdx.y != 0 || f >= 2 * HD) return;
-    if (f < HD) dk[(size_t)colj * HD + f] = from_float<T>(v);
-    else dv[(size_t)colj * HD + f - HD] = from_float<T>(v);
+    if (f < HD) dk[(size_t)colj * ld + f] = from_float<T>(v);
+    else dv[(size_t)colj * ld + f - HD] = from_float<T>(v);
 }
 
 // out[i] = sum_b part[b, i]: a block owns 32 columns, its 8 thread rows stride over the partial blocks (coalesced
 // 128-byte reads), the 8 sums are folded through shared memory in a fixed order (deterministic)
-__global__ void reduce_partials_kernel(const float* part, int n_blocks, int width, float* out) {
+__global__ void reduce_partials_kernel(const float* part, int n_blocks, int width, float* out, int accumulate) {
     __shared__ float sm[8][33];
     const int i = blockIdx.x * 32 + threadIdx.x;
     float v = 0.f;
@@ -1040,7 +1102,7 @@ __global__ void reduce_partials_kernel(const float* part, int n_blocks, int widt
         float t = 0.f;
 #pragma unroll
         for (int y = 0; y < 8; ++y) t += sm[y][threadIdx.x];
-        out[i] = t;
+        out[i] = accumulate ? out[i] + t : t;
     }
 }
 
@@ -1159,7 +1221,7 @@ void attn_bwd_row(const AttnBwdRowArgs& a, cudaStream_t s) {
         if (c.plan.n_split > 0)                                                          \
             sum_slots_kernel<TT><<<dim3(c.plan.n_split, (HD + 31) / 32), dim3(32, 8), 0, s>>>(c.plan, c.scratch, HD, a.row_map,                       \
                 a.accumulate_dq ? nullptr : static_cast<TT*>(a.dq), a.accumulate_dq ? static_cast<float*>(a.dq) : nullptr, \
-                a.accumulate_dq);                                                        \
+                a.accumulate_dq, c.ldo ? c.ldo : HD);                                    \
     } while (0)
     const int spec = spec_heads(c.H, c.D);
     if (c.dtype == DT_BF16) {
@@ -1194,7 +1256,7 @@ void attn_bwd_col(const AttnBwdColArgs& a, cudaStream_t s) {
         attn_bwd_col_kernel<TT, CPL, SP, AS><<<blocks, kWarpsPerBlock * 32, smc, s>>>(a); \
         if (c.plan.n_split > 0)                                                          \
             sum_slots_kv_kernel<TT><<<dim3(c.plan.n_split, (2 * HD + 31) / 32), dim3(32, 8), 0, s>>>(c.plan, c.scratch, HD, static_cast<TT*>(a.dk),       \
-                                                                   static_cast<TT*>(a.dv));                              \
+                                                                   static_cast<TT*>(a.dv), c.ldo ? c.ldo : HD);          \
     } while (0)
     const int spec = spec_heads(c.H, c.D);
     if (c.dtype == DT_BF16) {
@@ -1245,9 +1307,9 @@ std::vector<KernelInfo> attn_kernel_info() {
     return v;
 }
 
-void reduce_partials(const float* part, int n_blocks, int width, float* out, cudaStream_t s) {
+void reduce_partials(const float* part, int n_blocks, int width, float* out, cudaStream_t s, int accumulate) {
     if (width <= 0) return;
-    reduce_partials_kernel<<<(width + 31) / 32, dim3(32, 8), 0, s>>>(part, n_blocks, width, out);
+    reduce_partials_kernel<<<(width + 31) / 32, dim3(32, 8), 0, s>>>(part, n_blocks, width, out, accumulate);
 }
 
 }  // namespace gt

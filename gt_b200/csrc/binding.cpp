@@ -60,11 +60,22 @@ gt::AttnCommon make_common(const Tensor& q, int64_t H, int64_t D, const Tensor& 
 
 void attn_fwd(Tensor q, OptT k, OptT v, Tensor idx, OptT etype, OptT gate, OptT bias, std::vector<Tensor> plan, OptT row_map,
               Tensor acc, Tensor l, OptT m, OptT scratch, int64_t H, int64_t D, int64_t score, int64_t norm, double scale, double lo,
-              double hi, int64_t acc_stride, int64_t l_stride, bool accumulate, OptT k_peers, OptT v_peers, int64_t rows_per_peer) {
+              double hi, int64_t acc_stride, int64_t l_stride, bool accumulate, OptT k_peers, OptT v_peers, int64_t rows_per_peer,
+              int64_t ldq, int64_t ldk, std::vector<int64_t> push_ptrs, int64_t push_rows, int64_t push_ld, int64_t push_l_off) {
     c10::cuda::CUDAGuard guard(q.device());
-    check_cuda_contig(q, "q");
+    TORCH_CHECK(q.is_cuda(), "q must be a CUDA tensor");
+    if (ldq == 0) check_cuda_contig(q, "q");
     gt::AttnFwdArgs a{};
     a.c = make_common(q, H, D, idx, etype, gate, bias, plan, scratch, score, norm, scale, lo, hi);
+    a.c.ldq = ldq; a.c.ldk = ldk;
+    TORCH_CHECK(ldq % 8 == 0 && ldk % 8 == 0, "row strides must be multiples of 8 elements");
+    a.push_n = (int)push_ptrs.size();
+    if (a.push_n > 0) {
+        TORCH_CHECK(a.push_n <= 8 && norm == gt::NORM_CLAMPEXP && push_rows > 0 && push_ld % 8 == 0 && push_l_off % 8 == 0 && !accumulate,
+                    "pushed partials: at most 8 owners, clamp-exp, 16-byte aligned payload columns");
+        for (int i = 0; i < a.push_n; ++i) a.push_slot[i] = reinterpret_cast<void*>(push_ptrs[i]);
+        a.push_rows = (int)push_rows; a.push_ld = push_ld; a.push_l_off = (int)push_l_off;
+    }
     a.q = q.data_ptr();
     a.k = k.has_value() ? k->data_ptr() : nullptr;
     a.v = v.has_value() ? v->data_ptr() : nullptr;
@@ -73,7 +84,7 @@ void attn_fwd(Tensor q, OptT k, OptT v, Tensor idx, OptT etype, OptT gate, OptT 
     a.rows_per_peer = (int)rows_per_peer;
     TORCH_CHECK(a.k_peers != nullptr || (a.k != nullptr && a.v != nullptr), "k / v or their peer tables are required");
     a.row_map = cptr<int>(row_map);
-    a.acc = acc.data_ptr<float>(); a.l = l.data_ptr<float>();
+    a.acc = a.push_n > 0 ? nullptr : acc.data_ptr<float>(); a.l = a.push_n > 0 ? nullptr : l.data_ptr<float>();
     a.m = m.has_value() && m->defined() ? m->data_ptr<float>() : nullptr;
     a.acc_stride = acc_stride; a.l_stride = l_stride; a.accumulate = accumulate ? 1 : 0;
     gt::attn_fwd(a, stream());
@@ -83,10 +94,13 @@ int64_t attn_bwd_row_blocks(int64_t n_seg) { return gt::attn_bwd_row_blocks((int
 
 void attn_bwd_row(Tensor q, Tensor k, Tensor v, Tensor row_vec, Tensor stat, Tensor idx, OptT etype, OptT gate, OptT bias,
                   std::vector<Tensor> plan, OptT row_map, Tensor dq, bool accumulate_dq, OptT dgate_part, OptT dbias_part,
-                  int64_t n_blocks, OptT scratch, int64_t H, int64_t D, int64_t score, int64_t norm, double scale, double lo, double hi) {
+                  int64_t n_blocks, OptT scratch, int64_t H, int64_t D, int64_t score, int64_t norm, double scale, double lo, double hi,
+                  int64_t ldq, int64_t ldk, int64_t ldr, int64_t ldo) {
     c10::cuda::CUDAGuard guard(q.device());
     gt::AttnBwdRowArgs a{};
     a.c = make_common(q, H, D, idx, etype, gate, bias, plan, scratch, score, norm, scale, lo, hi);
+    a.c.ldq = ldq; a.c.ldk = ldk; a.c.ldr = ldr; a.c.ldo = ldo;
+    TORCH_CHECK(ldq % 8 == 0 && ldk % 8 == 0 && ldr % 8 == 0 && ldo % 8 == 0, "row strides must be multiples of 8 elements");
     TORCH_CHECK(row_vec.scalar_type() == q.scalar_type(), "row_vec must have the dtype of q");
     a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr(); a.row_vec = row_vec.data_ptr();
     a.stat = reinterpret_cast<const float4*>(stat.data_ptr<float>());
@@ -100,19 +114,22 @@ void attn_bwd_row(Tensor q, Tensor k, Tensor v, Tensor row_vec, Tensor stat, Ten
 
 void attn_bwd_col(Tensor q, Tensor k, Tensor v, Tensor row_vec, Tensor stat, Tensor rowidx, OptT etype_t, OptT gate, OptT bias,
                   std::vector<Tensor> plan, Tensor dk, Tensor dv, OptT scratch, int64_t H, int64_t D, int64_t score, int64_t norm,
-                  double scale, double lo, double hi) {
+                  double scale, double lo, double hi, int64_t ldq, int64_t ldk, int64_t ldr, int64_t ldo) {
     c10::cuda::CUDAGuard guard(q.device());
     gt::AttnBwdColArgs a{};
     a.c = make_common(q, H, D, rowidx, etype_t, gate, bias, plan, scratch, score, norm, scale, lo, hi);
+    a.c.ldq = ldq; a.c.ldk = ldk; a.c.ldr = ldr; a.c.ldo = ldo;
+    TORCH_CHECK(ldq % 8 == 0 && ldk % 8 == 0 && ldr % 8 == 0 && ldo % 8 == 0, "row strides must be multiples of 8 elements");
     a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr(); a.row_vec = row_vec.data_ptr();
     a.stat = reinterpret_cast<const float4*>(stat.data_ptr<float>());
     a.dk = dk.data_ptr(); a.dv = dv.data_ptr();
     gt::attn_bwd_col(a, stream());
 }
 
-void reduce_partials(Tensor part, Tensor out) {
+void reduce_partials(Tensor part, Tensor out, bool accumulate) {
     c10::cuda::CUDAGuard guard(part.device());
-    gt::reduce_partials(part.data_ptr<float>(), (int)part.size(0), (int)out.numel(), out.data_ptr<float>(), stream());
+    TORCH_CHECK(out.is_contiguous() && out.scalar_type() == torch::kFloat32, "fp32 contiguous output expected");
+    gt::reduce_partials(part.data_ptr<float>(), (int)part.size(0), (int)out.numel(), out.data_ptr<float>(), stream(), accumulate ? 1 : 0);
 }
 
 // (name, registers, local bytes, static shared, dynamic shared, resident blocks per SM) of the main attention kernel instances
@@ -125,13 +142,26 @@ std::vector<std::tuple<std::string, int64_t, int64_t, int64_t, int64_t, int64_t>
 
 bool attn_shape_supported(int64_t H, int64_t D, int64_t T) { return gt::attn_shape_supported((int)H, (int)D, (int)T); }
 
-void spmm(Tensor ptr, Tensor idx, OptT w, Tensor x, Tensor out, bool accumulate, std::vector<Tensor> plan, OptT scratch) {
+void spmm(Tensor ptr, Tensor idx, OptT w, Tensor x, Tensor out, bool accumulate, std::vector<Tensor> plan, OptT scratch,
+          std::vector<int64_t> push_ptrs, int64_t push_rows, int64_t push_ld, int64_t n_out) {
     c10::cuda::CUDAGuard guard(x.device());
-    check_cuda_contig(x, "x");
+    TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1 && x.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0,
+                "x must be a CUDA matrix with unit column stride, a row stride that is a multiple of 8 and a 16-byte aligned base");
     TORCH_CHECK(x.size(1) % 8 == 0 && x.size(1) <= 1024, "feature width must be a multiple of 8 and <= 1024");
     gt::SpmmArgs a{};
     a.dtype = dt(x); a.ptr = ptr.data_ptr<int>(); a.idx = idx.data_ptr<int>(); a.w = cptr<float>(w);
-    a.x = x.data_ptr(); a.out = out.data_ptr(); a.n_out = (int)out.size(0); a.d = (int)x.size(1); a.accumulate = accumulate ? 1 : 0;
+    a.x = x.data_ptr(); a.d = (int)x.size(1); a.accumulate = accumulate ? 1 : 0;
+    a.ldx = x.stride(0);
+    a.push_n = (int)push_ptrs.size();
+    if (a.push_n > 0) {
+        TORCH_CHECK(a.push_n <= 8 && push_rows > 0 && push_ld % 8 == 0 && !accumulate && n_out > 0, "pushed rows: at most 8 owners, aligned payload rows");
+        for (int i = 0; i < a.push_n; ++i) a.push_slot[i] = reinterpret_cast<void*>(push_ptrs[i]);
+        a.push_rows = (int)push_rows; a.ldo = push_ld; a.out = nullptr; a.n_out = (int)n_out;
+    } else {
+        TORCH_CHECK(out.dim() == 2 && out.stride(1) == 1 && out.stride(0) % 8 == 0 && out.size(1) == x.size(1) && out.scalar_type() == x.scalar_type(),
+                    "out must be [n_out, d] of x's dtype with unit column stride");
+        a.out = out.data_ptr(); a.n_out = (int)out.size(0); a.ldo = out.stride(0);
+    }
     a.use_plan = plan.empty() ? 0 : 1;
     if (a.use_plan) a.plan = make_plan(plan);
     a.scratch = scratch.has_value() && scratch->defined() ? scratch->data_ptr<float>() : nullptr;
@@ -348,7 +378,8 @@ void gemm_tn(Tensor a, Tensor b, Tensor c, bool accumulate, Tensor status) {
 // C[g * chunk, N] = epilogue(gathered(A) @ B[N, K]^T): rank p's [chunk, K] rows of A are read from peer_ptrs[p] (addresses
 // inside the peers' symmetric heaps, row stride lda) by TMA inside the GEMM; `gathered` (optional) receives the gathered A.
 void gemm_nt_gather(std::vector<int64_t> peer_ptrs, int64_t chunk, int64_t k, int64_t lda, Tensor b, Tensor c, OptT bias, int64_t act,
-                    double p, OptT seed, int64_t stream_id, OptT gathered, Tensor status) {
+                    double p, OptT seed, int64_t stream_id, OptT gathered, Tensor status, OptT wait_flags, OptT wait_counter, int64_t max_spins,
+                    int64_t self_index) {
     c10::cuda::CUDAGuard guard(b.device());
     TORCH_CHECK(b.scalar_type() == torch::kBFloat16 && b.stride(1) == 1 && c.stride(1) == 1, "bf16 row-major operands expected");
     const int n_peers = (int)peer_ptrs.size();
@@ -367,7 +398,9 @@ void gemm_nt_gather(std::vector<int64_t> peer_ptrs, int64_t chunk, int64_t k, in
                     gathered->stride(0) == lda && gathered->stride(1) == 1, "gathered copy must be [g * chunk, K] bf16 with row stride lda");
         gat = gathered->data_ptr();
     }
-    int rc = gt::gemm_nt_gather(g, peers.data(), n_peers, (int)chunk, gat, stream());
+    gt::GatherWait wait{cptr<int>(wait_flags), cptr<int>(wait_counter), (long long)max_spins, (int)self_index};
+    TORCH_CHECK((wait.flags == nullptr) == (wait.counter == nullptr), "wait flags and counter come together");
+    int rc = gt::gemm_nt_gather(g, peers.data(), n_peers, (int)chunk, gat, stream(), wait.flags ? &wait : (self_index ? &wait : nullptr));
     TORCH_CHECK(rc == 0, "fused all-gather GEMM failed with code ", rc);
 }
 
@@ -396,6 +429,64 @@ void sum_slots(Tensor slots, Tensor out, bool accumulate) {
     const int64_t n = slots.size(0), elems = slots.numel() / n;
     TORCH_CHECK(out.numel() == elems && elems % 8 == 0, "slot size must equal the output size and be a multiple of 8");
     gt::sum_slots(slots.data_ptr(), (int)n, elems, out.data_ptr(), dt(out), accumulate ? 1 : 0, stream());
+}
+
+// ---- epoch channels ------------------------------------------------------------------------------------------------------
+void channel_signal(std::vector<int64_t> peer_flag_ptrs, int64_t my_index, Tensor counter) {
+    c10::cuda::CUDAGuard guard(counter.device());
+    TORCH_CHECK(peer_flag_ptrs.size() <= 8, "at most 8 group members");
+    std::vector<int*> pf(peer_flag_ptrs.size());
+    for (size_t i = 0; i < pf.size(); ++i) pf[i] = reinterpret_cast<int*>(peer_flag_ptrs[i]);
+    gt::channel_signal(pf.data(), (int)pf.size(), (int)my_index, counter.data_ptr<int>(), stream());
+}
+
+// slots [n_slots, rows, W] bf16 (this rank's staging area) -> acc fp32 [rows, HD], l fp32 [rows, H], agg bf16 [rows, d_agg] (optional)
+void sum_payload(Tensor slots, Tensor acc, Tensor l, OptT agg, int64_t l_off, int64_t agg_off, OptT flags, OptT counter, int64_t max_spins,
+                 Tensor status) {
+    c10::cuda::CUDAGuard guard(slots.device());
+    TORCH_CHECK(slots.dim() == 3 && slots.is_contiguous() && slots.scalar_type() == torch::kBFloat16 && slots.size(2) % 8 == 0, "slots [n, rows, W] bf16");
+    TORCH_CHECK(acc.is_contiguous() && l.is_contiguous() && acc.size(0) == slots.size(1) && acc.size(1) % 8 == 0 && l_off % 8 == 0 && agg_off % 8 == 0,
+                "payload columns must be 16-byte aligned");
+    const bool has_agg = agg.has_value() && agg->defined();
+    if (has_agg) TORCH_CHECK(agg->is_contiguous() && agg->scalar_type() == torch::kBFloat16 && agg->size(1) % 8 == 0, "agg [rows, d] bf16");
+    gt::sum_payload(slots.data_ptr(), (int)slots.size(0), slots.size(1), (int)slots.size(2), (int)acc.size(1), (int)l.size(1), (int)l_off,
+                    (int)agg_off, has_agg ? (int)agg->size(1) : 0, acc.data_ptr<float>(), l.data_ptr<float>(), has_agg ? agg->data_ptr() : nullptr,
+                    cptr<int>(flags), cptr<int>(counter), max_spins, status.data_ptr<int>(), stream());
+}
+
+// peers' payload gradients [rows_per_peer, W] bf16 at src_ptrs -> row_vec bf16 [P * rows, HD], stat fp32 [P * rows, H, 4], dagg bf16 (optional)
+void pull_unpack(std::vector<int64_t> src_ptrs, int64_t rows_per_peer, int64_t W, Tensor row_vec, Tensor stat, OptT dagg, int64_t l_off,
+                 int64_t agg_off, OptT flags, OptT counter, int64_t max_spins, Tensor status) {
+    c10::cuda::CUDAGuard guard(row_vec.device());
+    const int n = (int)src_ptrs.size();
+    TORCH_CHECK(n >= 1 && n <= 8 && W % 8 == 0 && l_off % 8 == 0 && agg_off % 8 == 0, "at most 8 peers, aligned payload");
+    TORCH_CHECK(row_vec.is_contiguous() && row_vec.scalar_type() == torch::kBFloat16 && row_vec.size(0) == rows_per_peer * n && stat.is_contiguous() &&
+                stat.scalar_type() == torch::kFloat32 && stat.size(0) == row_vec.size(0) && stat.size(2) == 4, "row_vec [P rows, HD] bf16, stat [P rows, H, 4] fp32");
+    const bool has = dagg.has_value() && dagg->defined();
+    if (has) TORCH_CHECK(dagg->is_contiguous() && dagg->scalar_type() == torch::kBFloat16 && dagg->size(0) == row_vec.size(0), "dagg [P rows, d] bf16");
+    std::vector<void*> src(n);
+    for (int i = 0; i < n; ++i) src[i] = reinterpret_cast<void*>(src_ptrs[i]);
+    gt::pull_unpack(src.data(), n, rows_per_peer, (int)W, (int)row_vec.size(1), (int)stat.size(1), (int)l_off, (int)agg_off, has ? (int)dagg->size(1) : 0,
+                    row_vec.data_ptr(), stat.data_ptr(), has ? dagg->data_ptr() : nullptr, cptr<int>(flags), cptr<int>(counter), max_spins,
+                    status.data_ptr<int>(), stream());
+}
+
+void attn_bwd_prep(Tensor dacc, Tensor dl, Tensor row_vec, Tensor stat) {
+    c10::cuda::CUDAGuard guard(dacc.device());
+    TORCH_CHECK(dacc.is_contiguous() && dl.is_contiguous() && row_vec.is_contiguous() && stat.is_contiguous() && dacc.scalar_type() == torch::kFloat32 &&
+                dl.scalar_type() == torch::kFloat32 && row_vec.scalar_type() == torch::kBFloat16 && stat.scalar_type() == torch::kFloat32 &&
+                dacc.size(1) % 8 == 0, "dacc fp32 [n, HD], dl fp32 [n, H] -> row_vec bf16 [n, HD], stat fp32 [n, H, 4]");
+    gt::attn_bwd_prep(dacc.data_ptr<float>(), dl.data_ptr<float>(), dacc.size(0), (int)dacc.size(1), (int)dl.size(1), row_vec.data_ptr(),
+                      stat.data_ptr(), stream());
+}
+
+void sum_slots_wait(Tensor slots, Tensor out, bool accumulate, OptT flags, OptT counter, int64_t max_spins, Tensor status) {
+    c10::cuda::CUDAGuard guard(slots.device());
+    TORCH_CHECK(slots.scalar_type() == torch::kBFloat16 && slots.is_contiguous() && out.is_contiguous(), "contiguous bf16 slots expected");
+    const int64_t n = slots.size(0), elems = slots.numel() / n;
+    TORCH_CHECK(out.numel() == elems && elems % 8 == 0, "slot size must equal the output size and be a multiple of 8");
+    gt::sum_slots_wait(slots.data_ptr(), (int)n, elems, out.data_ptr(), dt(out), accumulate ? 1 : 0, cptr<int>(flags), cptr<int>(counter), max_spins,
+                       status.data_ptr<int>(), stream());
 }
 
 // ---- symmetric heap: cudaMalloc + CUDA IPC ----------------------------------------------------------------------------
@@ -536,6 +627,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("signal_peers", &signal_peers);
     m.def("wait_flags", &wait_flags);
     m.def("group_barrier", &group_barrier);
+    m.def("channel_signal", &channel_signal);
+    m.def("sum_payload", &sum_payload);
+    m.def("pull_unpack", &pull_unpack);
+    m.def("attn_bwd_prep", &attn_bwd_prep);
+    m.def("sum_slots_wait", &sum_slots_wait);
     m.def("pull_gather_rows", &pull_gather_rows);
     m.def("pull_all_to_all", &pull_all_to_all);
     m.def("pull_reduce_rows", &pull_reduce_rows);

@@ -73,6 +73,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
 }
 
+__device__ __forceinline__ int ld_acquire_sys_s32(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -546,7 +552,21 @@ struct GatherCfg {
     int chunk, n_peers, tiles_per_peer, copy_out;
     int nkb, n_abuf, n_b;             // k-blocks per tile, A buffers (1 or 2), B ring stages
     int tma_store;                    // bf16 result through swizzled shared memory + cp.async.bulk.tensor stores
+    // epoch channel of the gathered operand (nullable): before the first tile of peer p is fetched the producer waits, bounded,
+    // until wait_flags[p] has reached *wait_counter (the owner has published its rows)
+    const int* wait_flags; const int* wait_counter; long long max_spins;
+    int self;                         // this rank's index in the group: row tiles are walked peer by peer starting with the own rows
 };
+
+// Row tile mt -> (peer, first row inside the peer's chunk).  Tiles are ordered peer by peer, starting at this rank and going
+// round the group: every CTA first works on rows that are already local, and at any moment the ranks of a group read from
+// different owners (rank r is on peer r + k while rank r + 1 is on peer r + 1 + k), so no owner's link is read by all at once.
+__device__ __forceinline__ void gather_tile(const GatherCfg& cfg, int mt, int& peer, int& m0) {
+    const int slot = mt / cfg.tiles_per_peer;
+    peer = cfg.self + slot;
+    if (peer >= cfg.n_peers) peer -= cfg.n_peers;
+    m0 = (mt - slot * cfg.tiles_per_peer) * BM;
+}
 
 struct GatherBars {
     uint64_t a_full[2], a_empty[2];
@@ -599,10 +619,27 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gemm_nt_gather_kernel(const
         // ---- TMA producer: A tiles from the owners' memory, B tiles from the local weights ----
         int ai = 0, it = 0;
         bool okay = true;
+        uint32_t ready = cfg.wait_flags ? (1u << cfg.self) : 0xffffffffu;      // peers whose rows are known to be published
         auto load_a = [&](int mt, int idx) -> bool {
             const int buf = idx % cfg.n_abuf;
             if (!mbar_wait(&bars.a_empty[buf], ((idx / cfg.n_abuf) & 1) ^ 1, abort_flag, g.status, 1)) return false;
-            const int peer = mt % cfg.n_peers, m0 = (mt / cfg.n_peers) * BM;
+            int peer, m0;
+            gather_tile(cfg, mt, peer, m0);
+            if (!((ready >> peer) & 1u)) {
+                const int want = *cfg.wait_counter;
+                long long spins = 0;
+                while (ld_acquire_sys_s32(cfg.wait_flags + peer) < want) {
+                    if (*abort_flag) return false;
+                    if (++spins > cfg.max_spins) {
+                        *abort_flag = 1;
+                        if (g.status) atomicExch(g.status, 100 + peer);
+                        return false;
+                    }
+                    __nanosleep(40);
+                }
+                asm volatile("fence.proxy.async;" ::: "memory");     // the acquire orders the generic proxy; the TMA reads go through the async proxy
+                ready |= 1u << peer;
+            }
             mbar_expect_tx(&bars.a_full[buf], (uint32_t)nkb * kTile);
             for (int kb = 0; kb < nkb; ++kb)
                 tma_load_2d(a_sm + ((size_t)buf * nkb + kb) * kTile, &maps.a[peer], kb * BK, m0, &bars.a_full[buf]);
@@ -683,7 +720,8 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gemm_nt_gather_kernel(const
         int ti = 0;
         bool okay = true;
         for (int mt = blockIdx.x; mt < n_mtiles && okay; mt += gridDim.x) {
-            const int peer = mt % cfg.n_peers, m0 = (mt / cfg.n_peers) * BM;
+            int peer, m0;
+            gather_tile(cfg, mt, peer, m0);
             const long long row_base = (long long)peer * cfg.chunk;
             for (int nt = 0; nt < tiles_n; ++nt, ++ti) {
                 const int b = ti & 1, n0 = nt * BN;
@@ -768,7 +806,8 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gemm_nt_gather_kernel(const
         for (int mt = blockIdx.x; mt < n_mtiles; mt += gridDim.x, ++ai) {
             const int buf = ai % cfg.n_abuf;
             if (!mbar_wait(&bars.a_full[buf], (ai / cfg.n_abuf) & 1, abort_flag, g.status, 4)) break;
-            const int peer = mt % cfg.n_peers, m0 = (mt / cfg.n_peers) * BM;
+            int peer, m0;
+            gather_tile(cfg, mt, peer, m0);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             for (int kb = 0; kb < nkb; ++kb) tma_store_2d(&maps.out[peer], a_sm + ((size_t)buf * nkb + kb) * kTile, kb * BK, m0);
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
@@ -1070,7 +1109,8 @@ bool gemm_tcgen05_supported(int M, int N, int K, int lda, int ldb, int ldc) {
     return M > 0 && N > 0 && K > 0 && (lda % 8) == 0 && (ldb % 8) == 0 && (K % 8) == 0;
 }
 
-int gemm_nt_gather(const GemmArgs& g, const void* const* a_peers, int n_peers, int chunk, void* gathered, cudaStream_t s);
+int gemm_nt_gather(const GemmArgs& g, const void* const* a_peers, int n_peers, int chunk, void* gathered, cudaStream_t s,
+                   const GatherWait* wait);
 
 // GT_GEMM_KERNEL: "simple" = one tile per CTA, "persistent" = the tile-walking kernel for every shape (comparison runs)
 static char env_kernel() {
@@ -1103,7 +1143,7 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
     static const bool a_stationary = !(env_kernel() == 'p');
     if (!simple && a_stationary && !g.accumulate && g.K <= 512 && g.N > BN) {
         const void* self[1] = {g.a};
-        return gemm_nt_gather(g, self, 1, g.M, nullptr, s);
+        return gemm_nt_gather(g, self, 1, g.M, nullptr, s, nullptr);
     }
     if (simple) {
         dim3 grid((g.N + BN - 1) / BN, (g.M + BM - 1) / BM);
@@ -1142,7 +1182,8 @@ int gemm_tn_tcgen05(const GemmTNArgs& g, cudaStream_t s) {
 
 // A rows come from the peers' buffers (a_peers[p]: [chunk, K] bf16, row stride lda); g.a is ignored, g.M = n_peers * chunk.
 // gathered != nullptr additionally receives the gathered A ([n_peers * chunk, K], row stride lda).
-int gemm_nt_gather(const GemmArgs& g, const void* const* a_peers, int n_peers, int chunk, void* gathered, cudaStream_t s) {
+int gemm_nt_gather(const GemmArgs& g, const void* const* a_peers, int n_peers, int chunk, void* gathered, cudaStream_t s,
+                   const GatherWait* wait) {
     if (n_peers < 1 || n_peers > kMaxPeers) return -5;
     const int nkb = (g.K + BK - 1) / BK;
     if (nkb > 8 || (g.K % 8) || (g.lda % 8) || (g.ldb % 8)) return -4;
@@ -1172,6 +1213,11 @@ int gemm_nt_gather(const GemmArgs& g, const void* const* a_peers, int n_peers, i
     cfg.chunk = chunk; cfg.n_peers = n_peers; cfg.tiles_per_peer = (chunk + BM - 1) / BM; cfg.copy_out = gathered != nullptr;
     cfg.nkb = nkb;
     cfg.tma_store = tma_store ? 1 : 0;
+    cfg.wait_flags = wait ? wait->flags : nullptr;
+    cfg.wait_counter = wait ? wait->counter : nullptr;
+    cfg.max_spins = wait ? wait->max_spins : 0;
+    cfg.self = wait ? wait->self : 0;
+    if (cfg.self < 0 || cfg.self >= n_peers) return -5;
     // two A buffers whenever they fit: the fetch of the next row tile overlaps the MMAs of the current one (measured: worth more
     // than a deeper ring for the weight tiles)
     cfg.n_abuf = (2 * nkb + 3 <= slots) ? 2 : 1;

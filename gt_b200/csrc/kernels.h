@@ -34,6 +34,9 @@ struct AttnCommon {
     const float* bias;      // [T, H]   fp32, nullable
     SegPlan plan;
     float* scratch;         // [n_slots, scratch_width] fp32
+    // row strides in elements, 0 = dense rows of H*D: q (and the q-side of the passes), k / v, row_vec, and the gradient
+    // outputs (dq of the row pass, dk / dv of the column pass).  Operands may be column slices of wider matrices.
+    long long ldq, ldk, ldr, ldo;
 };
 
 struct AttnFwdArgs {
@@ -49,6 +52,13 @@ struct AttnFwdArgs {
     float* acc; float* l; float* m;   // outputs (m nullable)
     long long acc_stride, l_stride;   // elements between consecutive output rows
     int accumulate;         // add into acc / l instead of overwriting
+    // reduce-scatter fused into the epilogue (clamp-exp partials): output row r belongs to rank r / push_rows of the row group and
+    // is stored as bf16 [acc | .. | l] into push_slot[owner] + (r % push_rows) * push_ld; acc / l / m are then unused
+    int push_n;             // 0 = off, else the number of owners
+    void* push_slot[8];
+    int push_rows;          // rows per owner
+    long long push_ld;      // bf16 elements per payload row
+    int push_l_off;         // column of l inside the payload row (multiple of 8)
 };
 
 struct AttnBwdRowArgs {
@@ -81,7 +91,7 @@ struct KernelInfo { const char* name; int regs; int local_bytes; int static_smem
 std::vector<KernelInfo> attn_kernel_info();            // compiled resources of the main attention kernel instances
 int attn_bwd_row_blocks(int n_seg);                    // grid size attn_bwd_row will use for n_seg segments
 // sum of per-block partials: out[i] = sum_b part[b, i]
-void reduce_partials(const float* part, int n_blocks, int width, float* out, cudaStream_t s);
+void reduce_partials(const float* part, int n_blocks, int width, float* out, cudaStream_t s, int accumulate = 0);   // accumulate: out += sum
 
 // ---- sparse aggregation ---------------------------------------------------------------------------------------------
 struct SpmmArgs {
@@ -96,6 +106,10 @@ struct SpmmArgs {
     int use_plan;           // 1: one warp per plan segment (hub rows are cut and merged through `scratch`), 0: one warp per row
     SegPlan plan;
     float* scratch;         // [n_slots, d] fp32
+    long long ldx, ldo;     // row strides of x / out in elements (0 = d): either may be a column slice of a wider matrix
+    // reduce-scatter fused into the store: output row r belongs to rank r / push_rows and is written to
+    // push_slot[owner] + (r % push_rows) * ldo instead of `out` (push_slot already points at the column of the slice)
+    int push_n; void* push_slot[8]; int push_rows;
 };
 void spmm(const SpmmArgs& a, cudaStream_t s);
 // out[r] = sum_{k in [ptr[r], ptr[r+1])} rows[perm[k]]   (deterministic segmented row sum)
@@ -219,7 +233,11 @@ int gemm_tn_tcgen05(const GemmTNArgs& g, cudaStream_t s);
 // Collective-fused GEMMs over peer memory (symmetric heap).  Return 0, a CUDA error code, or a negative "unsupported" code.
 //   gather : C = gathered(A) * B^T where rank p's rows of A are read from a_peers[p] by TMA; optional gathered copy of A
 //   scatter: row block p of A * B^T is stored into slots[p] (my slot in rank p's staging area); sum_slots adds the slots
-int gemm_nt_gather(const GemmArgs& g, const void* const* a_peers, int n_peers, int chunk, void* gathered, cudaStream_t s);
+// `wait` (nullable): epoch channel of the gathered operand; the kernel waits per peer, inside its TMA producer, until
+// flags[p] >= *counter before it touches peer p's rows (no barrier kernel in front of the GEMM).  `self` = this rank's index.
+struct GatherWait { const int* flags; const int* counter; long long max_spins; int self; };
+int gemm_nt_gather(const GemmArgs& g, const void* const* a_peers, int n_peers, int chunk, void* gathered, cudaStream_t s,
+                   const GatherWait* wait = nullptr);
 int gemm_nt_scatter(const GemmArgs& g, void* const* slots, int n_peers, int chunk, cudaStream_t s);
 void sum_slots(const void* slots, int n_slots, long long slot_elems, void* out, int out_dtype, int accumulate, cudaStream_t s);
 
@@ -242,5 +260,19 @@ void wait_flags(const int* my_flags, int n_peers, int value, long long max_spins
 // signal + wait with a device-resident epoch counter (safe to replay inside a CUDA graph)
 void group_barrier(int* const* peer_flags, const int* my_flags, int* counter, int n_peers, int my_index, long long max_spins,
                    int* status, cudaStream_t s);
+
+// ---- epoch channels (signal now, wait inside the consumer) and the collectives built on them ------------------------------
+// bump the channel's device-resident epoch and publish it to every member (release, system scope); never waits
+void channel_signal(int* const* peer_flags, int n_peers, int my_index, int* counter, cudaStream_t s);
+// owner side of the pushed reduce-scatter: wait for the members, sum the n_slots bf16 payload rows [acc | l | agg], unpack
+void sum_payload(const void* slots, int n_slots, long long rows, int W, int HD, int H, int l_off, int agg_off, int d_agg, float* acc, float* l,
+                 void* agg, const int* flags, const int* counter, long long max_spins, int* status, cudaStream_t s);
+// backward mirror: wait, read the owners' bf16 payload gradient rows [dacc | dl | dagg] of the whole row block, unpack into the
+// row vector (bf16), the statistics float4 {0, dl, 1, 0} and the aggregation gradient (bf16)
+void pull_unpack(void* const* src, int n_peers, long long rows_per_peer, int W, int HD, int H, int l_off, int agg_off, int d_agg, void* row_vec,
+                 void* stat, void* dagg, const int* flags, const int* counter, long long max_spins, int* status, cudaStream_t s);
+void attn_bwd_prep(const float* dacc, const float* dl, long long n, int HD, int H, void* row_vec, void* stat, cudaStream_t s);
+void sum_slots_wait(const void* slots, int n_slots, long long slot_elems, void* out, int out_dtype, int accumulate, const int* flags,
+                    const int* counter, long long max_spins, int* status, cudaStream_t s);
 
 }  // namespace gt

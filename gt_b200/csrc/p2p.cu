@@ -164,6 +164,142 @@ __global__ void pull_all_to_all_kernel(const void* const* peers, int n_peers, in
     }
 }
 
+// ---- epoch channels: signal without waiting, wait inside the consumer -------------------------------------------------
+// A channel is {flags[n] in every member's symmetric heap, one counter in this rank's memory}.  `signal` bumps the counter and
+// publishes the new epoch into slot `my_index` of every member's flag array (release, system scope) after this stream's earlier
+// kernels (the producers) have completed; it never waits.  A consumer kernel later reads the SAME counter (its own rank signalled
+// the same use earlier in stream order) and waits, bounded, until the members it reads from have published that epoch.  The
+// counter lives in device memory and is advanced by the kernel itself, so a captured CUDA graph replays correctly.
+struct PeerFlags { int* p[8]; };
+
+__global__ void channel_signal_kernel(PeerFlags peers, int n_peers, int my_index, int* counter) {
+    __shared__ int epoch;
+    if (threadIdx.x == 0) { epoch = *counter + 1; *counter = epoch; }
+    __syncthreads();
+    __threadfence_system();
+    const int p = threadIdx.x;
+    if (p < n_peers) st_release_sys(peers.p[p] + my_index, epoch);
+}
+
+// Block-wide bounded wait: thread p < n_peers polls flags[p] until it reaches *counter.  Returns after a __syncthreads().
+__device__ __forceinline__ void block_wait_channel(const int* flags, const int* counter, int n_peers, long long max_spins, int* status) {
+    if (flags != nullptr && (int)threadIdx.x < n_peers) {
+        const int want = *counter;
+        long long spins = 0;
+        while (ld_acquire_sys(flags + threadIdx.x) < want) {
+            if (++spins > max_spins) { atomicExch(status, 100 + (int)threadIdx.x); break; }
+            __nanosleep(40);
+        }
+    }
+    __syncthreads();
+}
+
+// Owner side of the reduce-scatter that the attention / aggregation kernels push into: sums the n_slots bf16 payload rows
+// [acc (HD) | l (Hp) | agg (d_agg)] that the row group wrote into this rank's slots and unpacks them (fp32 acc and l, bf16 agg).
+__global__ void sum_payload_kernel(const __nv_bfloat16* __restrict__ slots, int n_slots, long long rows, int W, int HD, int H, int l_off,
+                                   int agg_off, int d_agg, float* __restrict__ acc, float* __restrict__ l, __nv_bfloat16* __restrict__ agg,
+                                   const int* flags, const int* counter, long long max_spins, int* status) {
+    block_wait_channel(flags, counter, n_slots, max_spins, status);
+    const int cpr = W >> 3;                                   // 8-element chunks per payload row
+    const long long total = rows * cpr;
+    const long long slot_elems = rows * (long long)W;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / cpr;
+        const int c = (int)(i - r * cpr) << 3;
+        float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int p = 0; p < n_slots; ++p) {
+            float v[8];
+            Vec8<__nv_bfloat16>::load(slots + (size_t)p * slot_elems + (size_t)r * W + c, v);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) s[k] += v[k];
+        }
+        if (c < HD) {
+            Vec8<float>::store(acc + (size_t)r * HD + c, s);
+        } else if (c >= l_off && c < l_off + H) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (c - l_off + k < H) l[(size_t)r * H + (c - l_off) + k] = s[k];
+        } else if (agg != nullptr && c >= agg_off && c < agg_off + d_agg) {
+            Vec8<__nv_bfloat16>::store(agg + (size_t)r * d_agg + (c - agg_off), s);
+        }
+    }
+}
+
+// Backward mirror (an all-gather over the row group, fused with the unpacking): every owner has published the bf16 payload
+// gradient [dacc (HD) | dl (Hp) | dagg (d_agg)] of its rows; this rank reads the rows of its whole row block from the owners'
+// memory and writes what the backward kernels consume: the row vector (bf16 dacc), the per-(row, head) statistics
+// {m = 0, row bias = dl, p scale = 1, 0} and the aggregation gradient.
+__global__ void pull_unpack_kernel(PeerFlags src, int n_peers, long long rows_per_peer, int W, int HD, int H, int l_off, int agg_off,
+                                   int d_agg, __nv_bfloat16* __restrict__ row_vec, float4* __restrict__ stat, __nv_bfloat16* __restrict__ dagg,
+                                   const int* flags, const int* counter, long long max_spins, int* status) {
+    block_wait_channel(flags, counter, n_peers, max_spins, status);
+    const int cpr = W >> 3;
+    const long long total = rows_per_peer * n_peers * cpr;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long row = i / cpr;
+        const int c = (int)(i - row * cpr) << 3;
+        const int p = (int)(row / rows_per_peer);
+        const long long r = row - (long long)p * rows_per_peer;
+        const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(src.p[p]) + (size_t)r * W + c);
+        if (c < HD) {
+            *reinterpret_cast<uint4*>(row_vec + (size_t)row * HD + c) = raw;
+        } else if (c >= l_off && c < l_off + H) {
+            float v[8];
+            Vec8<__nv_bfloat16>::unpack(raw, v);
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (c - l_off + k < H) stat[(size_t)row * H + (c - l_off) + k] = make_float4(0.f, v[k], 1.f, 0.f);
+        } else if (dagg != nullptr && c >= agg_off && c < agg_off + d_agg) {
+            *reinterpret_cast<uint4*>(dagg + (size_t)row * d_agg + (c - agg_off)) = raw;
+        }
+    }
+}
+
+// One-GPU form of the same preparation: dacc fp32 [n, HD] -> bf16 row vector, dl fp32 [n, H] -> statistics.
+__global__ void attn_bwd_prep_kernel(const float* __restrict__ dacc, const float* __restrict__ dl, long long n, int HD, int H,
+                                     __nv_bfloat16* __restrict__ row_vec, float4* __restrict__ stat) {
+    const int cpr = (HD >> 3) + ((H + 7) >> 3);
+    const long long total = n * cpr;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / cpr;
+        const int c = (int)(i - r * cpr);
+        if (c < (HD >> 3)) {
+            float v[8];
+            Vec8<float>::load(dacc + (size_t)r * HD + (c << 3), v);
+            Vec8<__nv_bfloat16>::store(row_vec + (size_t)r * HD + (c << 3), v);
+        } else {
+            const int h0 = (c - (HD >> 3)) << 3;
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (h0 + k < H) stat[(size_t)r * H + h0 + k] = make_float4(0.f, dl[(size_t)r * H + h0 + k], 1.f, 0.f);
+        }
+    }
+}
+
+// out (+)= sum of the n_slots bf16 slots after the members of the channel have signalled (GEMM -> reduce-scatter epilogue)
+template <typename TO>
+__global__ void sum_slots_wait_kernel(const __nv_bfloat16* __restrict__ slots, int n_slots, long long slot_elems, TO* __restrict__ out,
+                                      int accumulate, const int* flags, const int* counter, long long max_spins, int* status) {
+    block_wait_channel(flags, counter, n_slots, max_spins, status);
+    const long long n8 = slot_elems / 8;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int p = 0; p < n_slots; ++p) {
+            float v[8];
+            Vec8<__nv_bfloat16>::load(slots + (size_t)p * slot_elems + i * 8, v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += v[j];
+        }
+        if (accumulate) {
+            float o[8];
+            Vec8<TO>::load(out + i * 8, o);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += o[j];
+        }
+        Vec8<TO>::store(out + i * 8, acc);
+    }
+}
+
 int grid_for(long long items, int per_block) {
     long long b = (items + per_block - 1) / per_block;
     long long cap = 148LL * 8;
@@ -183,6 +319,49 @@ void wait_flags(const int* my_flags, int n_peers, int value, long long max_spins
 void group_barrier(int* const* peer_flags, const int* my_flags, int* counter, int n_peers, int my_index, long long max_spins,
                    int* status, cudaStream_t s) {
     barrier_kernel<<<1, 32, 0, s>>>(peer_flags, my_flags, counter, n_peers, my_index, max_spins, status);
+}
+
+void channel_signal(int* const* peer_flags, int n_peers, int my_index, int* counter, cudaStream_t s) {
+    PeerFlags pf{};
+    for (int p = 0; p < n_peers && p < 8; ++p) pf.p[p] = peer_flags[p];
+    channel_signal_kernel<<<1, 32, 0, s>>>(pf, n_peers, my_index, counter);
+}
+
+void sum_payload(const void* slots, int n_slots, long long rows, int W, int HD, int H, int l_off, int agg_off, int d_agg, float* acc, float* l,
+                 void* agg, const int* flags, const int* counter, long long max_spins, int* status, cudaStream_t s) {
+    if (rows <= 0) return;
+    sum_payload_kernel<<<grid_for(rows * (W / 8), 1024), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(slots), n_slots, rows, W, HD, H, l_off,
+                                                                     agg_off, d_agg, acc, l, static_cast<__nv_bfloat16*>(agg), flags, counter,
+                                                                     max_spins, status);
+}
+
+void pull_unpack(void* const* src, int n_peers, long long rows_per_peer, int W, int HD, int H, int l_off, int agg_off, int d_agg, void* row_vec,
+                 void* stat, void* dagg, const int* flags, const int* counter, long long max_spins, int* status, cudaStream_t s) {
+    if (rows_per_peer <= 0) return;
+    PeerFlags pf{};
+    for (int p = 0; p < n_peers && p < 8; ++p) pf.p[p] = static_cast<int*>(src[p]);
+    pull_unpack_kernel<<<grid_for(rows_per_peer * n_peers * (W / 8), 1024), 256, 0, s>>>(
+        pf, n_peers, rows_per_peer, W, HD, H, l_off, agg_off, d_agg, static_cast<__nv_bfloat16*>(row_vec), static_cast<float4*>(stat),
+        static_cast<__nv_bfloat16*>(dagg), flags, counter, max_spins, status);
+}
+
+void attn_bwd_prep(const float* dacc, const float* dl, long long n, int HD, int H, void* row_vec, void* stat, cudaStream_t s) {
+    if (n <= 0) return;
+    attn_bwd_prep_kernel<<<grid_for(n * (HD / 8 + (H + 7) / 8), 1024), 256, 0, s>>>(dacc, dl, n, HD, H, static_cast<__nv_bfloat16*>(row_vec),
+                                                                                    static_cast<float4*>(stat));
+}
+
+void sum_slots_wait(const void* slots, int n_slots, long long slot_elems, void* out, int out_dtype, int accumulate, const int* flags,
+                    const int* counter, long long max_spins, int* status, cudaStream_t s) {
+    const long long n8 = slot_elems / 8;
+    if (n8 <= 0) return;
+    if (out_dtype == DT_BF16)
+        sum_slots_wait_kernel<__nv_bfloat16><<<grid_for(n8, 256), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(slots), n_slots, slot_elems,
+                                                                               static_cast<__nv_bfloat16*>(out), accumulate, flags, counter,
+                                                                               max_spins, status);
+    else
+        sum_slots_wait_kernel<float><<<grid_for(n8, 256), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(slots), n_slots, slot_elems,
+                                                                       static_cast<float*>(out), accumulate, flags, counter, max_spins, status);
 }
 
 void pull_gather_rows(const void* const* peers, const int* owner, const int* row, void* out, int n, int row_bytes, cudaStream_t s) {

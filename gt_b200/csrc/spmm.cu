@@ -31,6 +31,7 @@ __global__ void __launch_bounds__(kWarps * 32) spmm_kernel(SpmmArgs a, const int
     while (lpr < nch && lpr < 32) lpr <<= 1;
     const int epw = 32 / lpr, sub = lane / lpr, ll = lane - sub * lpr;
     const T* x = static_cast<const T*>(a.x);
+    const size_t ldx = a.ldx ? (size_t)a.ldx : (size_t)a.d, ldo = a.ldo ? (size_t)a.ldo : (size_t)a.d;
     float acc[CPL][8];
     bool act[CPL];
 #pragma unroll
@@ -53,7 +54,7 @@ __global__ void __launch_bounds__(kWarps * 32) spmm_kernel(SpmmArgs a, const int
         for (int u = 0; u < 2; ++u)
 #pragma unroll
             for (int i = 0; i < CPL; ++i) {
-                if (j[u] >= 0 && act[i]) Vec8<T>::load_nc(x + (size_t)j[u] * a.d + ((ll + 32 * i) << 3), xf[u][i]);
+                if (j[u] >= 0 && act[i]) Vec8<T>::load_nc(x + (size_t)j[u] * ldx + ((ll + 32 * i) << 3), xf[u][i]);
                 else {
 #pragma unroll
                     for (int k = 0; k < 8; ++k) xf[u][i][k] = 0.f;
@@ -78,7 +79,13 @@ __global__ void __launch_bounds__(kWarps * 32) spmm_kernel(SpmmArgs a, const int
             if (act[i]) Vec8<float>::store(a.scratch + (size_t)slot * a.d + ((ll + 32 * i) << 3), acc[i]);
         return;
     }
-    T* out = static_cast<T*>(a.out) + (size_t)row * a.d;
+    T* out;
+    if (a.push_n > 0) {          // reduce-scatter fused into the store: the row goes into the slot its owner keeps for this rank
+        const int owner = row / a.push_rows;
+        out = static_cast<T*>(a.push_slot[owner]) + (size_t)(row - owner * a.push_rows) * ldo;
+    } else {
+        out = static_cast<T*>(a.out) + (size_t)row * ldo;
+    }
 #pragma unroll
     for (int i = 0; i < CPL; ++i) {
         if (!act[i]) continue;
@@ -99,7 +106,14 @@ __global__ void spmm_combine_kernel(SpmmArgs a) {
     const int r = blockIdx.x;
     const int row = a.plan.split_rows[r];
     const int s0 = a.plan.split_ptr[r], s1 = a.plan.split_ptr[r + 1];
-    T* out = static_cast<T*>(a.out) + (size_t)row * a.d;
+    const size_t ldo = a.ldo ? (size_t)a.ldo : (size_t)a.d;
+    T* out;
+    if (a.push_n > 0) {
+        const int owner = row / a.push_rows;
+        out = static_cast<T*>(a.push_slot[owner]) + (size_t)(row - owner * a.push_rows) * ldo;
+    } else {
+        out = static_cast<T*>(a.out) + (size_t)row * ldo;
+    }
     for (int f = threadIdx.x; f < a.d; f += blockDim.x) {
         float v = a.accumulate ? to_float(out[f]) : 0.f;
         for (int s = s0; s < s1; ++s) v += a.scratch[(size_t)s * a.d + f];

@@ -195,8 +195,19 @@ class DistExphormerLayerFused(_LayerBase):
         return (acc_o, l_o), agg_o
 
     def forward(self, x, edge_type_emb):
+        if type(self) is DistExphormerLayerFused:
+            # the whole branch as one explicit-backward operator on the native kernels (collectives inside the kernels)
+            from ..parallel.fused_layer import fused_branch
+            out = fused_branch(self, x, self.gate(edge_type_emb))
+            if out is not None:
+                acc_o, l_o, agg_o = out
+                return self.tail(x, acc_o, agg_o, l=l_o)
         (acc_o, l_o), agg_o = self.branches(x, edge_type_emb)
         return self.tail(x, acc_o, agg_o, l=l_o)
+
+    def stacked_params(self):
+        """Parameters the fused operator reads as one stacked matrix (rows K | V | message | Q)."""
+        return [self.k.weight, self.v.weight] + ([self.gcn.lin.weight] if self.with_gcn else []) + [self.q.weight]
 
 
 class DistExphormerLayerHead(_LayerBase):
@@ -639,6 +650,26 @@ class DistExphormer(nn.Module):
             else:
                 h = layer(h, self.edge_type_emb.weight)
         return K.linear(h, self.head.weight, self.head.bias)
+
+    def flat_param_order(self):
+        """Parameters that must be adjacent in the training engine's flat buffers, group by group."""
+        out = []
+        for layer in self.layers:
+            if hasattr(layer, "stacked_params"):
+                out += layer.stacked_params()
+        return out
+
+    def on_flat_layout(self, engine):
+        """Called by the training engine once its flat buffers exist: hand every fused layer the stacked views."""
+        if not engine.cuda:
+            return
+        for layer in self.layers:
+            if hasattr(layer, "stacked_params"):
+                ps = layer.stacked_params()
+                try:
+                    layer._w_stack = (engine.span(ps, "bf16"), engine.span(ps, "grad"))
+                except ValueError:
+                    layer._w_stack = None
 
     def compaction_stats(self):
         """(row-block rows x sub-blocks, (row, sub-block) pairs owning an edge) of the first layer."""

@@ -113,6 +113,15 @@ def new_site() -> int:
     return next(_SITE)
 
 
+def site_of(param, salt=0):
+    """Dropout site id of the module that owns ``param``: the parameter's position in the training engine's flat space when
+    there is one (identical models then draw identical masks, whatever their addresses), else its address."""
+    base = getattr(param, "_site", None)
+    if base is None:
+        base = param.data_ptr()
+    return (int(base) ^ salt) & 0xFFFFFFFFFF
+
+
 def _dt_ok(t):
     return t.dtype in (torch.bfloat16, torch.float32)
 
@@ -189,6 +198,22 @@ def gemm_tn(a, b, out=None, accumulate=False):
     return out
 
 
+def weight_bf16(weight, dtype=torch.bfloat16):
+    """``weight`` in the compute dtype: the training engine's bf16 shadow when there is one (refreshed by the optimizer kernel,
+    so no cast runs per step), else a cast."""
+    sh = getattr(weight, "_bf16", None)
+    if sh is not None and dtype == torch.bfloat16:
+        return sh
+    return weight.to(dtype)
+
+
+def direct_grad(param):
+    """The fp32 gradient buffer a backward kernel may add into itself (the engine's flat gradient space), or None."""
+    if getattr(param, "_direct_grad", False) and param.grad is not None and param.grad.dtype == torch.float32 and param.grad.is_contiguous():
+        return param.grad
+    return None
+
+
 class _Linear(torch.autograd.Function):
     """y = drop(act(x W^T + b)).  Saved: x, W (bf16 copy), and y (ReLU: mask and dropout are read off y) or the
     pre-activation (GELU)."""
@@ -197,7 +222,8 @@ class _Linear(torch.autograd.Function):
     def forward(ctx, x, weight, bias, act, p, site):
         shp = x.shape
         x2 = x.reshape(-1, shp[-1])
-        wb = weight.to(x2.dtype)
+        wb = weight_bf16(weight, x2.dtype)
+        ctx.weight, ctx.bias_param = weight, bias
         if act == "gelu":
             pre = gemm_nt(x2, wb, bias)
             y = torch.empty_like(pre)
@@ -230,8 +256,12 @@ class _Linear(torch.autograd.Function):
                 e.bias_act_dropout_bwd(dy2, src, None, dz, code, p if code != 2 else 0.0, rng_state(dy2.device) if p > 0 else None,
                                        site, part)
                 if has_bias:
-                    dbias = torch.empty(dy2.shape[1], dtype=torch.float32, device=dy2.device)
-                    e.reduce_partials(part, dbias)
+                    gb = direct_grad(ctx.bias_param)
+                    if gb is not None:
+                        e.reduce_partials(part, gb, True)          # straight into the flat gradient buffer
+                    else:
+                        dbias = torch.empty(dy2.shape[1], dtype=torch.float32, device=dy2.device)
+                        e.reduce_partials(part, dbias, False)
             else:
                 dz = dy2
                 if has_bias:
@@ -239,12 +269,18 @@ class _Linear(torch.autograd.Function):
         else:
             dz = dy2
         dx = gemm_nn(dz, wb) if ctx.needs_input_grad[0] else None
-        dw = gemm_tn(dz, x2).to(wdt) if ctx.needs_input_grad[1] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            gw = direct_grad(ctx.weight)
+            if gw is not None and dz.dtype == torch.bfloat16 and _GEMM_IMPL != "cublas" and dz.shape[1] % 8 == 0 and x2.shape[1] % 8 == 0:
+                gemm_tn(dz, x2, out=gw, accumulate=True)              # dW lands in the flat gradient buffer: no autograd add
+            else:
+                dw = gemm_tn(dz, x2).to(wdt)
         return (dx.view(shp) if dx is not None else None), dw, dbias, None, None, None
 
 
 def linear(x, weight, bias=None, activation=None, dropout=0.0):
-    site = weight.data_ptr() & 0xFFFFFFFFFF
+    site = site_of(weight)
     return _Linear.apply(x, weight, bias, activation, float(dropout), site)
 
 
@@ -288,7 +324,7 @@ class _LayerNorm(torch.autograd.Function):
                          parts[:, 2], p, rng_state(y.device) if p > 0 else None, site,
                          y if acc_mode else None, l, eps_l, dy if acc_mode else None, dl)
         red = torch.empty(3, d, dtype=torch.float32, device=y.device)
-        e.reduce_partials(parts.view(nb, 3 * d), red.view(3 * d))                # one reduction for dgamma | dbeta | dybias
+        e.reduce_partials(parts.view(nb, 3 * d), red.view(3 * d), False)                # one reduction for dgamma | dbeta | dybias
         return dy, dx, (red[2].to(pdt) if has_yb else None), red[0].to(gamma.dtype), red[1].to(pdt), None, None, None, dl, None
 
 
@@ -309,7 +345,7 @@ def layer_norm(y, x, ybias, gamma, beta, eps, p, l=None, eps_l=1e-6):
         z = torch.nn.functional.dropout(z, p, True) if p > 0 else z
         z = z + x if x is not None else z
         return torch.nn.functional.layer_norm(z, z.shape[-1:], gamma.to(z.dtype), beta.to(z.dtype), eps)
-    site = gamma.data_ptr() & 0xFFFFFFFFFF
+    site = site_of(gamma)
     return _LayerNorm.apply(y, x, ybias, gamma, beta, float(eps), float(p), site, l, float(eps_l))
 
 
@@ -342,7 +378,7 @@ class _GatedResidual(torch.autograd.Function):
         e.gated_res_bwd(r, o, dout.contiguous(), wa, wb, gamma.float(), beta.float(), stats, dr, do_, part, p,
                         rng_state(r.device) if p > 0 else None, site)
         red = torch.empty(4 * d + 8, dtype=torch.float32, device=r.device)
-        e.reduce_partials(part, red)
+        e.reduce_partials(part, red, False)
         dwa, dwb = red[2 * d:3 * d], red[3 * d:4 * d]
         # wa = w0 + w2, wb = w1 - w2  ->  dw0 = dwa, dw1 = dwb, dw2 = dwa - dwb
         dw = torch.stack([dwa, dwb, dwa - dwb]).reshape(wshape).to(wdt)
@@ -354,7 +390,7 @@ def gated_residual(r, o, gate_weight, gate_bias, ln_weight, ln_bias, eps, p):
     direction for rows of up to 256 features, otherwise two mat-vec products feeding the fused LayerNorm kernel."""
     d = r.shape[1]
     if d <= 256 and d % 8 == 0 and _dt_ok(r):
-        site = (gate_weight.data_ptr() ^ 0x2545f491) & 0xFFFFFFFFFF
+        site = site_of(gate_weight, 0x2545f491)
         return _GatedResidual.apply(r, o, gate_weight, gate_bias, ln_weight, ln_bias, eps, float(p), site)
     w = gate_weight.to(r.dtype).view(3, d)
     logit = r @ (w[0] + w[2]) + o @ (w[1] - w[2]) + gate_bias.to(r.dtype)
@@ -421,7 +457,7 @@ def spmm(blk, x, transpose=False, out=None):
         out = torch.empty(n_out, x.shape[1], dtype=x.dtype, device=x.device)
     scratch = torch.empty(plan.num_slots, x.shape[1], dtype=torch.float32, device=x.device) if plan.num_slots else None
     ext().spmm(ptr, idx, w, x, out, acc, [plan.seg_row, plan.seg_beg, plan.seg_end, plan.seg_slot, plan.split_rows, plan.split_ptr],
-               scratch)
+               scratch, [], 0, 0, 0)
     return out
 
 
@@ -430,7 +466,7 @@ def segment_sum_rows(rows, perm, ptr, out):
     if rows.shape[1] % 8 or rows.shape[1] > 1024 or not _dt_ok(rows):
         seg = torch.repeat_interleave(torch.arange(out.shape[0], device=rows.device), (ptr[1:] - ptr[:-1]).long())
         return out.zero_().index_add_(0, seg, rows[perm.long()])
-    ext().spmm(ptr, perm, None, rows.contiguous(), out, False, [], None)
+    ext().spmm(ptr, perm, None, rows.contiguous(), out, False, [], None, [], 0, 0, 0)
     return out
 
 
@@ -482,11 +518,11 @@ class _PreMp(torch.autograd.Function):
         dh = torch.empty_like(h)
         e.premp_bwd(h, dout.contiguous(), gamma.float(), beta.float(), stats, dh, part, p, rng_state(h.device) if p > 0 else None, site, l2norm)
         red = torch.empty(2 * d, dtype=torch.float32, device=h.device)
-        e.reduce_partials(part, red)
+        e.reduce_partials(part, red, False)
         return dh, red[:d].to(gamma.dtype), red[d:].to(beta.dtype), None, None, None, None
 
 
 def pre_mp(h, gamma, beta, eps, p, l2norm=True):
     """``l2normalize(relu(dropout(LayerNorm(h))))`` over the last dimension of ``[n, d]`` (d % 8 == 0, d <= 1024)."""
-    site = (gamma.data_ptr() ^ 0x5bd1e995) & 0xFFFFFFFFFF
+    site = site_of(gamma, 0x5bd1e995)
     return _PreMp.apply(h, gamma, beta, eps, float(p), site, bool(l2norm))

@@ -109,7 +109,8 @@ class DistGCNConv(torch.nn.Module):
         self.bias = torch.nn.Parameter(torch.zeros(dim_out))
 
     def forward(self, x_loc):
-        h_blk = all_gather_rows(self.lin(x_loc), self.grid.col_group)
+        from ..ops import functional as K
+        h_blk = all_gather_rows(K.linear(x_loc, self.lin.weight), self.grid.col_group)
         agg = spmm(self.block.matrix(h_blk.dtype, h_blk.device), h_blk)
         return reduce_scatter_rows(agg, self.grid.row_group) + self.bias
 

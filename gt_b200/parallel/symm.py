@@ -163,7 +163,7 @@ class SymmetricHeap:
         y = torch.empty(c.size * chunk, w.shape[0], dtype=torch.bfloat16, device=x.device)
         xg = torch.empty(c.size * chunk, k, dtype=torch.bfloat16, device=x.device) if want_gathered else None
         native.ext().gemm_nt_gather([self.peer_base[r] + off for r in c.ranks], chunk, k, k, w, y, bias, {None: 0, "relu": 1, "gelu": 2}[act],
-                                    0.0, None, 0, xg, native.status(self.device))
+                                    0.0, None, 0, xg, native.status(self.device), None, None, 0, 0)
         return y, xg
 
     def linear_scatter(self, a, w, group, out_dtype=torch.bfloat16, out=None, accumulate=False):

@@ -15,6 +15,12 @@ import torch.distributed as dist
 FORMAT_VERSION = 1
 
 
+def _flat_names(model, engine):
+    """Parameter names in the order of the engine's flat buffers (the order of the saved AdamW moments)."""
+    by_id = {id(p): n for n, p in model.named_parameters()}
+    return [by_id[id(p)] for p in engine.params]
+
+
 def save_checkpoint(path, model, engine=None, epoch=0, extra=None):
     """Rank 0 writes ``path`` atomically; all ranks synchronise afterwards."""
     rank = dist.get_rank() if dist.is_initialized() else 0
@@ -25,7 +31,7 @@ def save_checkpoint(path, model, engine=None, epoch=0, extra=None):
         if engine is not None:
             es = engine.state_dict()
             blob["optimizer"] = dict(step=es["step"], m=es["m"].cpu(), v=es["v"].cpu(),
-                                     names=[n for n, p in model.named_parameters() if p.requires_grad])
+                                     names=_flat_names(model, engine))
         if torch.cuda.is_available():
             from ..ops import native
             try:
@@ -59,7 +65,7 @@ def load_checkpoint(path, model, engine=None, strict=True):
         return 0, {}
     if engine is not None and "optimizer" in blob:
         opt = blob["optimizer"]
-        names = [n for n, p in model.named_parameters() if p.requires_grad]
+        names = _flat_names(model, engine)
         if "names" in opt and list(opt["names"]) != names:
             raise ValueError("checkpoint was written for a different configuration: the optimizer state covers other parameters "
                              f"(or another order) than this model: first difference near {next((a, b) for a, b in zip(list(opt['names']) + [None], names + [None]) if a != b)}")

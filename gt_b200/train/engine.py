@@ -56,21 +56,40 @@ class TrainEngine:
         dev = self.params[0].device
         self.device = dev
         self.cuda = dev.type == "cuda"
-        n = sum(p.numel() for p in self.params)
-        pad = (-n) % 8
+        # Flat layout.  A model may name groups of parameters that must lie next to each other (``flat_param_order``): the
+        # fused layers read K | V | message | Q weights as ONE stacked matrix and write their gradients as one GEMM.  Every
+        # parameter starts on a multiple of 8 elements, so the bf16 shadow of any matrix is a legal (16-byte aligned) TMA operand.
+        order = list(model.flat_param_order()) if hasattr(model, "flat_param_order") else []
+        seen = {id(p) for p in order}
+        order += [p for p in self.params if id(p) not in seen]
+        order = [p for p in order if p.requires_grad]
+        self.params = order
+        self.offsets, n = {}, 0
+        for p in order:
+            n = -(-n // 8) * 8
+            self.offsets[id(p)] = n
+            n += p.numel()
+        n = -(-n // 8) * 8
         self.numel = n
-        self.flat_p = torch.zeros(n + pad, dtype=torch.float32, device=dev)
-        self.flat_g = heap.empty(n + pad, torch.float32, "grads") if (heap is not None and self.cuda) else \
-            torch.zeros(n + pad, dtype=torch.float32, device=dev)
+        self.flat_p = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.flat_g = heap.empty(n, torch.float32, "grads") if (heap is not None and self.cuda) else \
+            torch.zeros(n, dtype=torch.float32, device=dev)
         self.flat_m = torch.zeros_like(self.flat_p)
         self.flat_v = torch.zeros_like(self.flat_p)
-        off = 0
-        for p in self.params:
-            k = p.numel()
+        # bf16 shadow of the parameters, refreshed by the optimizer kernel: the GEMMs read it instead of casting every step
+        self.flat_p_bf16 = torch.zeros(n, dtype=torch.bfloat16, device=dev) if self.cuda else None
+        for p in order:
+            off, k = self.offsets[id(p)], p.numel()
             self.flat_p[off:off + k].copy_(p.data.reshape(-1).float())
             p.data = self.flat_p[off:off + k].view_as(p)
             p.grad = self.flat_g[off:off + k].view_as(p)
-            off += k
+            if self.cuda:
+                p._bf16 = self.flat_p_bf16[off:off + k].view_as(p)
+                p._direct_grad = True         # backward kernels may add into p.grad themselves and return no gradient to autograd
+                p._site = 0x51700000 + off    # dropout site id: position in the flat space, not an address
+        self.sync_shadow()
+        if hasattr(model, "on_flat_layout"):
+            model.on_flat_layout(self)
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         if self.cuda:
             self.hyper = torch.zeros(9, dtype=torch.float32, device=dev)
@@ -118,7 +137,7 @@ class TrainEngine:
             e = native.ext()
             self.hyper[8:9].zero_()
             e.sq_norm(g, self.hyper[8:9])
-            e.adamw_step(self.flat_p, g, self.flat_m, self.flat_v, None, self.hyper, None)
+            e.adamw_step(self.flat_p, g, self.flat_m, self.flat_v, self.flat_p_bf16, self.hyper, None)
             native.advance_rng(self.device)
             return
         b1, b2 = self.betas
@@ -168,6 +187,24 @@ class TrainEngine:
         self.step_count += 1
         return loss
 
+    def sync_shadow(self):
+        """Refresh the bf16 shadow after the fp32 parameters were written by anything but the optimizer kernel (a loaded
+        checkpoint, a broadcast)."""
+        if self.cuda:
+            self.flat_p_bf16.copy_(self.flat_p)
+
+    def span(self, params, what="bf16"):
+        """``[sum rows, cols]`` view of consecutive 2-D parameters of equal width in the flat space: their bf16 shadow
+        (``what='bf16'``), fp32 values (``'fp32'``) or gradient (``'grad'``).  Raises if they are not adjacent."""
+        off0 = self.offsets[id(params[0])]
+        off, cols = off0, params[0].shape[1]
+        for p in params:
+            if self.offsets[id(p)] != off or p.dim() != 2 or p.shape[1] != cols or (p.numel() % 8):
+                raise ValueError("parameters are not adjacent in the flat layout")
+            off += p.numel()
+        buf = {"bf16": self.flat_p_bf16, "fp32": self.flat_p, "grad": self.flat_g}[what]
+        return buf[off0:off].view(-1, cols)
+
     def release_graph(self):
         """Drop the captured step (and the collectives recorded in it); the next ``train_step`` runs eagerly and re-captures."""
         self._graph = None
@@ -181,6 +218,7 @@ class TrainEngine:
         self.step_count = int(sd["step"])
         self.flat_m[:self.numel].copy_(sd["m"])
         self.flat_v[:self.numel].copy_(sd["v"])
+        self.sync_shadow()
 
 
 def smoke_step(device):

@@ -217,8 +217,9 @@ def test_cross_entropy_and_adamw():
     assert _rel(p, pr.detach()) < 1e-5
 
 
-def test_whole_step_matches_cpu_oracle_and_graph_replay():
-    """fp32 Exphormer step on the native kernels vs the CPU torch backend, then bf16 + CUDA-graph replay stays finite."""
+def test_smoke_step_runs():
+    """The smoke entry point (two bf16 steps of a tiny Exphormer) finishes with a finite loss and a clean status word; the
+    comparison with the CPU oracle and the graph-replay check live in test_gpu_parity.py."""
     from gt_b200.train.engine import smoke_step
     smoke_step(_dev())
 
