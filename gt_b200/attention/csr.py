@@ -16,6 +16,7 @@ source (key / value) columns in block-local numbering.  ``BlockCSR`` owns every 
 
 All index arrays are int32 (a block never holds 2^31 edges); construction works on CPU or CUDA tensors.
 """
+import os
 from dataclasses import dataclass, field
 from typing import Optional
 
@@ -78,8 +79,33 @@ def _segments(ptr: torch.Tensor, seg_edges: int):
         slot_first[split_rows] = split_ptr[:-1]
         sel = is_split[seg_row]
         seg_slot[sel] = slot_first[seg_row[sel]] + k[sel]
+    if BALANCE_WARPS > 0 and seg_row.numel() > BALANCE_WARPS:
+        perm = _balanced_order(seg_end - seg_beg, BALANCE_WARPS)
+        seg_row, seg_beg, seg_end, seg_slot = seg_row[perm], seg_beg[perm], seg_end[perm], seg_slot[perm]
     i32 = torch.int32
     return (seg_row.to(i32), seg_beg.to(i32), seg_end.to(i32), seg_slot.to(i32), split_rows.to(i32), split_ptr.to(i32))
+
+
+# The kernels are persistent: warp w of a grid of BALANCE_WARPS warps walks the segments w, w + W, w + 2 W, ...  Degrees of real
+# graphs are heavy-tailed, so with the segments in row order a warp that happens to draw a few hub segments runs far longer than
+# the average and the launch ends with most SMs idle.  The segments are therefore sorted by length (longest first) and dealt to
+# the warps in serpentine order, which equalises the number of edges per warp to within one short segment (longest-processing-
+# time scheduling done once on the host; the kernels need no work queue and stay deterministic).  0 keeps the row order.
+BALANCE_WARPS = int(os.environ.get("GT_PLAN_BALANCE", str(148 * 24 * 4)))
+
+
+def _balanced_order(length: torch.Tensor, n_warps: int) -> torch.Tensor:
+    """Permutation ``perm`` such that ``segments[perm]`` walked with stride ``n_warps`` gives every warp the same work."""
+    n = length.numel()
+    order = torch.argsort(length, descending=True, stable=True)
+    p = torch.arange(n, device=length.device)
+    rnd, k = p // n_warps, p % n_warps
+    full = (rnd + 1) * n_warps <= n                                  # the last, partial round is dealt forwards
+    warp = torch.where(((rnd % 2) == 1) & full, n_warps - 1 - k, k)
+    pos = rnd * n_warps + warp
+    perm = torch.empty_like(order)
+    perm[pos] = order
+    return perm
 
 
 @dataclass

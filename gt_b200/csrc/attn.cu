@@ -18,6 +18,7 @@
 //
 // Semantics follow the operator specification in gt_b200/attention/ref.py (reference kernels:
 // gt3d/gt3d/attention/triton_kernel.py:38-284, triton_tiled.py:157-479).
+#include <stdio.h>
 #include <stdlib.h>
 
 #include "common.cuh"
@@ -1106,6 +1107,28 @@ __global__ void reduce_partials_kernel(const float* part, int n_blocks, int widt
     }
 }
 
+#include "attn_hl.cuh"
+
+// GT_ATTN_HL = "f,r,c": chunks per lane (2 or 4; 0 = use the chunk-per-lane kernels) of the head-lane forward, row-pass and
+// column-pass kernels.  Default "2,0,0": measured on the 169K-node benchmark block (8 heads x 32, 3.74 M edges) the forward with
+// 2 chunks per lane runs in 0.82 ms against 0.93 ms; 4 chunks per lane lose (1.22 ms: a lane's 16-byte pieces of a row are 64
+// bytes apart, so every copy instruction touches 32 sectors for 512 bytes), and the backward passes lose at either width
+// (3.10 ms against 2.58 ms: their 140-155 registers leave three blocks per SM).
+struct HlCfg { int ch[3]; };
+const HlCfg& hl_cfg() {
+    static const HlCfg cfg = [] {
+        HlCfg c{{2, 0, 0}};
+        const char* e = getenv("GT_ATTN_HL");
+        int a = 0, b = 0, d = 0;
+        if (e && sscanf(e, "%d,%d,%d", &a, &b, &d) == 3) {
+            const int v[3] = {a, b, d};
+            for (int i = 0; i < 3; ++i) c.ch[i] = (v[i] == 2 || v[i] == 4) ? v[i] : 0;
+        }
+        return c;
+    }();
+    return cfg;
+}
+
 size_t table_bytes(const AttnCommon& c) {
     size_t n = 0;
     if (c.score == SCORE_GATED) n += (size_t)c.T * c.H * c.D;
@@ -1148,11 +1171,29 @@ void attn_fwd(const AttnFwdArgs& a, cudaStream_t s) {
     const AttnCommon& c = a.c;
     if (c.plan.n_seg == 0) return;
     int blocks = (c.plan.n_seg + kWarpsPerBlock - 1) / kWarpsPerBlock;
-    if (blocks > 148 * 24) blocks = 148 * 24;          // persistent: a few waves of resident blocks stride over the segments
+    if (blocks > 148 * 24) blocks = 148 * 24;          // persistent: the grid the host-side segment balancing was made for
     const size_t sm = table_bytes(c);
     const bool peer = a.k_peers != nullptr;
     const int cpl = cpl_of(c.H, c.D);
     static const bool use_async = [] { const char* e = getenv("GT_ATTN_ASYNC"); return !(e && e[0] == '0'); }();
+    if (hl_cfg().ch[0] && !peer && hl::shape_ok(c) && (c.H >= 8 || getenv("GT_ATTN_HL"))) {   // 4 heads: measured slower (1.28 vs 1.20 ms)
+        constexpr int NST = 3;
+        const int ch = hl_cfg().ch[0];
+        const size_t ring = (size_t)NST * (2 * ch * 16 + 4) * hl::kThreads;
+        const size_t smh = ((sm + 15) & ~size_t(15)) + ring;
+#define GT_LAUNCH_FWD_HL(HH, CC)                                                                   \
+    do {                                                                                           \
+        set_smem(hl::attn_fwd_hl_kernel<HH, CC, NST>, smh);                                        \
+        hl::attn_fwd_hl_kernel<HH, CC, NST><<<blocks, hl::kThreads, smh, s>>>(a);                  \
+    } while (0)
+        if (c.H == 4) { if (ch == 4) GT_LAUNCH_FWD_HL(4, 4); else GT_LAUNCH_FWD_HL(4, 2); }
+        else if (c.H == 8) { if (ch == 4) GT_LAUNCH_FWD_HL(8, 4); else GT_LAUNCH_FWD_HL(8, 2); }
+        else { if (ch == 4) GT_LAUNCH_FWD_HL(16, 4); else GT_LAUNCH_FWD_HL(16, 2); }
+#undef GT_LAUNCH_FWD_HL
+        if (c.plan.n_split > 0)
+            attn_fwd_combine_sum_kernel<<<dim3(c.plan.n_split, (c.H * c.D + c.H + 31) / 32), dim3(32, 8), 0, s>>>(a);
+        return;
+    }
     if (use_async && !peer && c.dtype == DT_BF16) {
         const size_t ring = (size_t)kAsyncStages * kUnrollFwd * (cpl * 2 * 16 + 4) * kWarpsPerBlock * 32;   // data ring + type ring
         const size_t sma = ((sm + 15) & ~size_t(15)) + ring;
@@ -1224,6 +1265,26 @@ void attn_bwd_row(const AttnBwdRowArgs& a, cudaStream_t s) {
                 a.accumulate_dq, c.ldo ? c.ldo : HD);                                    \
     } while (0)
     const int spec = spec_heads(c.H, c.D);
+    if (hl_cfg().ch[1] && hl::shape_ok(c)) {
+        constexpr int NST = 3;
+        const int ch = hl_cfg().ch[1];
+        const size_t ring = (size_t)NST * (2 * ch * 16 + 4) * hl::kThreads;
+        const size_t smh = ((sm + 15) & ~size_t(15)) + ring;
+#define GT_LAUNCH_ROW_HL(HH, CC)                                                                   \
+    do {                                                                                           \
+        set_smem(hl::attn_bwd_row_hl_kernel<HH, CC, NST>, smh);                                    \
+        hl::attn_bwd_row_hl_kernel<HH, CC, NST><<<blocks, hl::kThreads, smh, s>>>(a);              \
+    } while (0)
+        if (c.H == 4) { if (ch == 4) GT_LAUNCH_ROW_HL(4, 4); else GT_LAUNCH_ROW_HL(4, 2); }
+        else if (c.H == 8) { if (ch == 4) GT_LAUNCH_ROW_HL(8, 4); else GT_LAUNCH_ROW_HL(8, 2); }
+        else { if (ch == 4) GT_LAUNCH_ROW_HL(16, 4); else GT_LAUNCH_ROW_HL(16, 2); }
+#undef GT_LAUNCH_ROW_HL
+        if (c.plan.n_split > 0)
+            sum_slots_kernel<__nv_bfloat16><<<dim3(c.plan.n_split, (HD + 31) / 32), dim3(32, 8), 0, s>>>(
+                c.plan, c.scratch, HD, a.row_map, a.accumulate_dq ? nullptr : static_cast<__nv_bfloat16*>(a.dq),
+                a.accumulate_dq ? static_cast<float*>(a.dq) : nullptr, a.accumulate_dq, c.ldo ? c.ldo : HD);
+        return;
+    }
     if (c.dtype == DT_BF16) {
         if (cpl == 1 && spec == 8 && use_async) GT_LAUNCH_ROW(__nv_bfloat16, 1, 8, true);
         else if (cpl == 1 && spec == 8) GT_LAUNCH_ROW(__nv_bfloat16, 1, 8, false);
@@ -1259,6 +1320,25 @@ void attn_bwd_col(const AttnBwdColArgs& a, cudaStream_t s) {
                                                                    static_cast<TT*>(a.dv), c.ldo ? c.ldo : HD);          \
     } while (0)
     const int spec = spec_heads(c.H, c.D);
+    if (hl_cfg().ch[2] && hl::shape_ok(c)) {
+        constexpr int NST = 3;
+        const int ch = hl_cfg().ch[2];
+        const size_t ring = (size_t)NST * ((2 * ch + 1) * 16 + 4) * hl::kThreads;
+        const size_t smh = ((sm + 15) & ~size_t(15)) + ring;
+#define GT_LAUNCH_COL_HL(HH, CC)                                                                   \
+    do {                                                                                           \
+        set_smem(hl::attn_bwd_col_hl_kernel<HH, CC, NST>, smh);                                    \
+        hl::attn_bwd_col_hl_kernel<HH, CC, NST><<<blocks, hl::kThreads, smh, s>>>(a);              \
+    } while (0)
+        if (c.H == 4) { if (ch == 4) GT_LAUNCH_COL_HL(4, 4); else GT_LAUNCH_COL_HL(4, 2); }
+        else if (c.H == 8) { if (ch == 4) GT_LAUNCH_COL_HL(8, 4); else GT_LAUNCH_COL_HL(8, 2); }
+        else { if (ch == 4) GT_LAUNCH_COL_HL(16, 4); else GT_LAUNCH_COL_HL(16, 2); }
+#undef GT_LAUNCH_COL_HL
+        if (c.plan.n_split > 0)
+            sum_slots_kv_kernel<__nv_bfloat16><<<dim3(c.plan.n_split, (2 * HD + 31) / 32), dim3(32, 8), 0, s>>>(
+                c.plan, c.scratch, HD, static_cast<__nv_bfloat16*>(a.dk), static_cast<__nv_bfloat16*>(a.dv), c.ldo ? c.ldo : HD);
+        return;
+    }
     if (c.dtype == DT_BF16) {
         if (cpl == 1 && spec == 8 && use_async) GT_LAUNCH_COL(__nv_bfloat16, 1, 8, true);
         else if (cpl == 1 && spec == 8) GT_LAUNCH_COL(__nv_bfloat16, 1, 8, false);
