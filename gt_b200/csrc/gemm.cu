@@ -1048,6 +1048,14 @@ __global__ void __launch_bounds__(kThreads) gemm_tn_kernel(const __grid_constant
                     tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + c0, r);
                     if (row >= g.N) continue;
                     float* dst = g.c + (size_t)row * g.ldc + k0 + c0;
+                    if (k0 + c0 + 32 <= g.K && (g.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(g.c) & 15) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)          // 16-byte vector reductions: a quarter of the atomic operations
+                            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "f"(__uint_as_float(r[j])),
+                                         "f"(__uint_as_float(r[j + 1])), "f"(__uint_as_float(r[j + 2])), "f"(__uint_as_float(r[j + 3]))
+                                         : "memory");
+                        continue;
+                    }
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
                         if (k0 + c0 + j < g.K) atomicAdd(dst + j, __uint_as_float(r[j]));
@@ -1058,6 +1066,117 @@ __global__ void __launch_bounds__(kThreads) gemm_tn_kernel(const __grid_constant
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
+
+// Wide-tile variant of the weight-gradient GEMM: one CTA owns a 256 x 256 tile of C (two 128-row accumulators of 256 columns
+// = all 512 TMEM columns) and a slice of the row range.  The 128 x 128 kernel above re-reads A once per column tile and B once
+// per row tile of C; for C = [1024, 256] over 169K rows that is 1.4 GB through L2 per product and the kernel runs at the L2's
+// speed.  256 x 256 tiles halve that traffic (each 64 KB stage of operands feeds four times the MMA work of a 32 KB stage).
+constexpr int TN2_STAGES = 3;
+struct __align__(1024) TN2Storage {
+    __nv_bfloat16 a[TN2_STAGES][BK * 256];                 // 4 boxes of [BK rows][64 columns], 8 KB each
+    __nv_bfloat16 b[TN2_STAGES][BK * 256];
+    uint64_t full[TN2_STAGES];
+    uint64_t empty[TN2_STAGES];
+    uint64_t tmem_full;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ void red_add_v4(float* dst, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(__uint_as_float(a)), "f"(__uint_as_float(b)),
+                 "f"(__uint_as_float(c)), "f"(__uint_as_float(d))
+                 : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1) gemm_tn256_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                 const __grid_constant__ CUtensorMap map_b, GemmTNArgs g, int rows_per_split) {
+    extern __shared__ uint8_t smem_raw[];
+    TN2Storage& sh = *reinterpret_cast<TN2Storage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k0 = blockIdx.x * 256;                       // output column tile (features of B)
+    const int n0 = blockIdx.y * 256;                       // output row tile (features of A)
+    const int r_beg = blockIdx.z * rows_per_split;
+    const int r_end = min(g.M, r_beg + rows_per_split);
+    const int nkb = r_end > r_beg ? (r_end - r_beg + BK - 1) / BK : 0;
+    volatile int* abort_flag = &sh.abort_flag;
+
+    if (threadIdx.x == 0) {
+        sh.abort_flag = 0;
+        for (int s = 0; s < TN2_STAGES; ++s) { mbar_init(&sh.full[s], 1); mbar_init(&sh.empty[s], 1); }
+        mbar_init(&sh.tmem_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(&sh.tmem_base, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh.tmem_base;
+    if (nkb > 0) {
+        if (warp == 0 && lane == 0) {
+            int issued = 0;
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % TN2_STAGES;
+                if (!mbar_wait(&sh.empty[s], ((kb / TN2_STAGES) & 1) ^ 1, abort_flag, g.status, 4)) break;
+                mbar_expect_tx(&sh.full[s], 2 * BK * 256 * 2);
+                const int r = r_beg + kb * BK;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    tma_load_2d(sh.a[s] + i * BK * 64, &map_a, n0 + 64 * i, r, &sh.full[s]);
+                    tma_load_2d(sh.b[s] + i * BK * 64, &map_b, k0 + 64 * i, r, &sh.full[s]);
+                }
+                issued = kb + 1;
+            }
+            if (*abort_flag) {
+                for (int kb = (issued > TN2_STAGES ? issued - TN2_STAGES : 0); kb < issued; ++kb) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(&sh.full[kb % TN2_STAGES], (kb / TN2_STAGES) & 1) && clock64() - t0 < kWaitCycles) {}
+                }
+            }
+        } else if (warp == 1 && lane == 0) {
+            const uint32_t idesc = make_idesc(128, 256, 1, 1);
+            bool okay = true;
+            for (int kb = 0; kb < nkb && okay; ++kb) {
+                const int s = kb % TN2_STAGES;
+                okay = mbar_wait(&sh.full[s], (kb / TN2_STAGES) & 1, abort_flag, g.status, 5);
+                if (!okay) break;
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(sh.a[s]), b_addr = smem_u32(sh.b[s]);
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k) {
+                    // 16 reduction rows = two 8-row groups of 1024 bytes; consecutive 64-wide MN blocks are BK * 128 bytes apart
+                    const uint64_t bd = make_desc(b_addr + k * 2048, BK * 128, 1024);
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint64_t ad = make_desc(a_addr + h * 2 * BK * 128 + k * 2048, BK * 128, 1024);
+                        umma_bf16(tmem + (uint32_t)(h * 256), ad, bd, idesc, (kb | k) != 0);
+                    }
+                }
+                umma_commit(&sh.empty[s]);
+            }
+            if (okay) umma_commit(&sh.tmem_full);
+        } else if (warp >= 2) {
+            const bool okay = mbar_wait(&sh.tmem_full, 0, abort_flag, g.status, 6);
+            tc_fence_after();
+            if (okay) {
+                const int quad = warp & 3;
+                for (int h = 0; h < 2; ++h) {
+                    const int row = n0 + h * 128 + quad * 32 + lane;
+                    for (int c0 = 0; c0 < 256; c0 += 32) {
+                        uint32_t r[32];
+                        tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(h * 256 + c0), r);
+                        if (row >= g.N) continue;
+                        float* dst = g.c + (size_t)row * g.ldc + k0 + c0;           // K % 256 == 0 and 16-byte aligned rows: whole vectors
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) red_add_v4(dst + j, r[j], r[j + 1], r[j + 2], r[j + 3]);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
 // ---- host side: tensor maps ------------------------------------------------------------------------------------------
@@ -1138,9 +1257,11 @@ int gemm_tcgen05(const GemmArgs& g, cudaStream_t s) {
         simple = env && env[0] == 's';                    // "simple": the one-tile-per-CTA kernel (comparison / debugging)
         cudaFuncSetAttribute(gemm_nt_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(PersistentStorage) + 1024));
     }
-    // short-K products with several column tiles: the A-stationary kernel (one "peer": this GPU) reads every A tile once
-    // instead of once per column tile
-    static const bool a_stationary = !(env_kernel() == 'p');
+    // GT_GEMM_KERNEL=a: run local short-K products on the A-stationary kernel of the fused all-gather (one "peer": this GPU).
+    // Measured on 169,344 x 256 -> 1024 / 512 / 256 and 512 -> 256: the tile-walking kernel is faster on every shape (0.142 /
+    // 0.074 / 0.040 / 0.062 ms against 0.155 / 0.086 / 0.051 / 0.094 ms): neighbouring CTAs work on the same row tile at the same
+    // time, so its re-reads of A hit L2, and its ring holds five whole k-steps.
+    static const bool a_stationary = env_kernel() == 'a';
     if (!simple && a_stationary && !g.accumulate && g.K <= 512 && g.N > BN) {
         const void* self[1] = {g.a};
         return gemm_nt_gather(g, self, 1, g.M, nullptr, s, nullptr);
@@ -1165,6 +1286,28 @@ int gemm_tn_tcgen05(const GemmTNArgs& g, cudaStream_t s) {
     if (!attr) {
         cudaFuncSetAttribute(gemm_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
         attr = true;
+    }
+    // 256 x 256 tiles when C has at least four of them (measured at 169K rows: [1024, 256] 0.085 ms against 0.132 ms with 128 x 128
+    // tiles; [512, 256] 0.063 against 0.057: too few tiles to fill the SMs without splitting the rows 70-fold).  GT_GEMM_TN=narrow
+    // / wide forces one kernel.
+    static const char tn_env = getenv("GT_GEMM_TN") ? getenv("GT_GEMM_TN")[0] : 0;
+    const bool wide_shape = (g.N % 256) == 0 && (g.K % 256) == 0 && g.M >= 148 * BK && (g.ldc % 4) == 0 && (reinterpret_cast<uintptr_t>(g.c) & 15) == 0;
+    if (wide_shape && tn_env != 'n' && ((g.N / 256) * (g.K / 256) >= 4 || tn_env == 'w')) {
+        static bool attr2 = false;
+        if (!attr2) {
+            cudaFuncSetAttribute(gemm_tn256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(TN2Storage) + 1024));
+            attr2 = true;
+        }
+        const int tiles2 = (g.K / 256) * (g.N / 256);
+        int splits2 = (148 + tiles2 - 1) / tiles2;
+        const int kblocks2 = (g.M + BK - 1) / BK;
+        if (splits2 > kblocks2) splits2 = kblocks2;
+        const int rows2 = ((kblocks2 + splits2 - 1) / splits2) * BK;
+        splits2 = (g.M + rows2 - 1) / rows2;
+        if (!g.accumulate) cudaMemsetAsync(g.c, 0, (size_t)g.N * g.ldc * sizeof(float), s);
+        dim3 grid2(g.K / 256, g.N / 256, splits2);
+        gemm_tn256_kernel<<<grid2, kThreads, sizeof(TN2Storage) + 1024, s>>>(ma, mb, g, rows2);
+        return (int)cudaGetLastError();
     }
     const int tiles = ((g.K + BN - 1) / BN) * ((g.N + BM - 1) / BM);
     int splits = (2 * 148 + tiles - 1) / tiles;
