@@ -104,7 +104,8 @@ def run_ours(args):
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         if not bool(ok.item()):
             heap, args.comm = None, "nccl"
-    wl = exphormer_workload(WORKLOAD, GRIDS[world], dev, torch.bfloat16, seed=0, heap=heap, scale_down=args.scale_down)
+    grid_shape = tuple(args.grid) if args.grid else GRIDS[world]
+    wl = exphormer_workload(WORKLOAD, grid_shape, dev, torch.bfloat16, seed=0, heap=heap, scale_down=args.scale_down)
     model, grid = wl["model"], wl["grid"]
     for p in model.parameters():
         dist.broadcast(p.data, src=0)
@@ -184,7 +185,8 @@ def run_ours(args):
             "dtype": "bf16", "data": "synthetic (seeded Chung-Lu graph, N(0,1) features, random-init weights)",
             "config": {"model": "Exphormer 4L h256 8 heads FFN2x dropout0.1 LayerNorm, fused 2D layer", "global_batch": wl["num_nodes"],
                        "seq_len": wl["num_nodes"], "nodes": wl["num_nodes"], "attn_edges": wl["num_attn_edges"],
-                       "parallelism": "grid %dx%d" % GRIDS[world], "comm": args.comm if world > 1 else "none",
+                       "parallelism": "grid " + "x".join(map(str, grid_shape)), "grid": list(grid_shape),
+                       "comm": args.comm if world > 1 else "none",
                        "cuda_graph": not args.no_graph, "scale_down": args.scale_down,
                        "l2": "step working set (>2 GB of activations) exceeds the 126 MB L2; no explicit flush"},
             "clocks": clocks,
@@ -244,6 +246,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--comm", default="p2p", choices=["nccl", "p2p"], help="grid collectives: NCCL or the package's peer-memory kernels")
     ap.add_argument("--heap_mb", type=int, default=2048)
+    ap.add_argument("--grid", type=int, nargs="+", default=None, metavar="P",
+                    help="process grid P_d P_o (default: 1x1, 2x1, 2x2, 2x4 for 1, 2, 4, 8 GPUs); used by the grid-ranking measurements")
     ap.add_argument("--no_graph", action="store_true", help="run the step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--profile", default=None, metavar="PREFIX",
                     help="after timing, write the per-kernel device time of one more step to PREFIX.rank<r>.txt (not part of the timed region)")

@@ -176,6 +176,55 @@ def _bwd(q, k, v, blk, gate, bias, row_vec, stat, score, norm, clamp, scale, seg
     return dq, dk, dv, dgate, dbias
 
 
+def attn_bwd_partial_accum(q, k, v, blk: BlockCSR, gate, bias, m, dacc, dl, dq_accum, *, score="gated", norm="clampexp",
+                           clamp=(-5.0, 5.0), scale=None, seg_edges=SEG_EDGES):
+    """Backward of one (hypersparse) sub-block whose query gradient is ADDED in place into ``dq_accum [rows, H d]`` (fp32):
+    the row pass walks the doubly-compressed row list, so rows without an edge in this sub-block are neither read nor written
+    and no ``[rows, H d]`` temporary + add exists per sub-block (the compact-accumulate backward of the reference,
+    ``gt3d/gt3d/attention/triton_tiled.py:566-590``, used by its streamed layer ``gt3d/gt3d/models/exphormer_dist.py:892-893``).
+    Returns ``(dk, dv, dgate, dbias)``."""
+    n, h, d = q.shape
+    if blk.num_edges == 0:
+        z = torch.zeros(k.shape, dtype=k.dtype, device=k.device)
+        return z, z.clone(), (torch.zeros_like(gate, dtype=torch.float32) if gate is not None else None), \
+            (torch.zeros_like(bias, dtype=torch.float32) if bias is not None else None)
+    if not _supported(q, gate, bias) or dq_accum.dtype != torch.float32 or not dq_accum.is_contiguous():
+        dq, dk, dv, dgate, dbias = attn_bwd_partial(q, k, v, blk, gate, bias, m, dacc, dl, score=score, norm=norm, clamp=clamp, scale=scale,
+                                                    seg_edges=seg_edges)
+        dq_accum += dq.reshape(dq_accum.shape).to(dq_accum.dtype)
+        return dk, dv, dgate, dbias
+    e = native.ext()
+    sc, nm, scale, lo, hi = _cfg(q, score, norm, clamp, scale)
+    g, b = _tables(gate, bias, score)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    rv = dacc.reshape(q.shape).to(q.dtype).contiguous()
+    stat = _pack_stat(m, dl, None)
+    plan, rows = _dcsr_plan(blk, seg_edges)
+    nb = e.attn_bwd_row_blocks(plan.num_segments)
+    t = g.shape[0] if g is not None else (b.shape[0] if b is not None else 0)
+    dgp = torch.empty(nb, t * h * d, dtype=torch.float32, device=q.device) if g is not None else None
+    dbp = torch.empty(nb, t * h, dtype=torch.float32, device=q.device) if b is not None else None
+    scratch = torch.empty(plan.num_slots, h * d, dtype=torch.float32, device=q.device) if plan.num_slots else None
+    e.attn_bwd_row(q, k, v, rv, stat, blk.col, blk.etype, g, b, _plan_list(plan), rows, dq_accum, True, dgp, dbp, nb, scratch,
+                   h, d, sc, nm, scale, lo, hi, 0, 0, 0, 0)
+    dgate = dbias = None
+    if g is not None:
+        dgate = torch.empty(t * h * d, dtype=torch.float32, device=q.device)
+        e.reduce_partials(dgp, dgate, False)
+        dgate = dgate.view(t, h, d)
+    if b is not None:
+        dbias = torch.empty(t * h, dtype=torch.float32, device=q.device)
+        e.reduce_partials(dbp, dbias, False)
+        dbias = dbias.view(t, h)
+    nc = k.shape[0]
+    _, rowidx, et_t, _, _ = blk.csc()
+    cplan = blk.col_plan(seg_edges)
+    dk, dv = torch.empty(nc, h, d, dtype=q.dtype, device=q.device), torch.empty(nc, h, d, dtype=q.dtype, device=q.device)
+    cscratch = torch.empty(cplan.num_slots, 2 * h * d, dtype=torch.float32, device=q.device) if cplan.num_slots else None
+    e.attn_bwd_col(q, k, v, rv, stat, rowidx, et_t, g, b, _plan_list(cplan), dk, dv, cscratch, h, d, sc, nm, scale, lo, hi, 0, 0, 0, 0)
+    return dk, dv, dgate, dbias
+
+
 def attn_bwd_partial(q, k, v, blk: BlockCSR, gate, bias, m, dacc, dl, *, score="dot", norm="softmax", clamp=(-5.0, 5.0),
                      scale=None, seg_edges=SEG_EDGES):
     if not _supported(q, gate, bias) and _padded_dim(q, gate, bias):

@@ -480,6 +480,25 @@ void attn_bwd_prep(Tensor dacc, Tensor dl, Tensor row_vec, Tensor stat) {
                       stat.data_ptr(), stream());
 }
 
+void allreduce_two_shot(std::vector<int64_t> src_ptrs, std::vector<int64_t> dst_ptrs, int64_t me, int64_t n, Tensor flags, Tensor counter,
+                        int64_t max_spins, Tensor status) {
+    c10::cuda::CUDAGuard guard(flags.device());
+    const int np = (int)src_ptrs.size();
+    TORCH_CHECK(np >= 1 && np <= 8 && dst_ptrs.size() == src_ptrs.size() && n % 4 == 0, "1..8 members, n a multiple of 4");
+    std::vector<void*> a(np), b(np);
+    for (int i = 0; i < np; ++i) {
+        a[i] = reinterpret_cast<void*>(src_ptrs[i]); b[i] = reinterpret_cast<void*>(dst_ptrs[i]);
+        TORCH_CHECK((src_ptrs[i] & 15) == 0 && (dst_ptrs[i] & 15) == 0, "buffers must be 16-byte aligned");
+    }
+    gt::allreduce_two_shot(a.data(), b.data(), np, (int)me, n, flags.data_ptr<int>(), counter.data_ptr<int>(), max_spins, status.data_ptr<int>(),
+                           stream());
+}
+
+void channel_wait(Tensor flags, Tensor counter, int64_t n_peers, int64_t max_spins, Tensor status) {
+    c10::cuda::CUDAGuard guard(flags.device());
+    gt::channel_wait(flags.data_ptr<int>(), counter.data_ptr<int>(), (int)n_peers, max_spins, status.data_ptr<int>(), stream());
+}
+
 void sum_slots_wait(Tensor slots, Tensor out, bool accumulate, OptT flags, OptT counter, int64_t max_spins, Tensor status) {
     c10::cuda::CUDAGuard guard(slots.device());
     TORCH_CHECK(slots.scalar_type() == torch::kBFloat16 && slots.is_contiguous() && out.is_contiguous(), "contiguous bf16 slots expected");
@@ -632,6 +651,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("pull_unpack", &pull_unpack);
     m.def("attn_bwd_prep", &attn_bwd_prep);
     m.def("sum_slots_wait", &sum_slots_wait);
+    m.def("allreduce_two_shot", &allreduce_two_shot);
+    m.def("channel_wait", &channel_wait);
     m.def("pull_gather_rows", &pull_gather_rows);
     m.def("pull_all_to_all", &pull_all_to_all);
     m.def("pull_reduce_rows", &pull_reduce_rows);

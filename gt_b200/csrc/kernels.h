@@ -272,6 +272,11 @@ void sum_payload(const void* slots, int n_slots, long long rows, int W, int HD, 
 void pull_unpack(void* const* src, int n_peers, long long rows_per_peer, int W, int HD, int H, int l_off, int agg_off, int d_agg, void* row_vec,
                  void* stat, void* dagg, const int* flags, const int* counter, long long max_spins, int* status, cudaStream_t s);
 void attn_bwd_prep(const float* dacc, const float* dl, long long n, int HD, int H, void* row_vec, void* stat, cudaStream_t s);
+// two-shot all-reduce (reduce my slice from every member, store it to every member) of n fp32 values, n % 4 == 0; waits on the
+// channel first.  channel_wait: a one-block bounded wait for consumers that cannot wait themselves.
+void allreduce_two_shot(void* const* src, void* const* dst, int n_peers, int me, long long n, const int* flags, const int* counter,
+                        long long max_spins, int* status, cudaStream_t s);
+void channel_wait(const int* flags, const int* counter, int n_peers, long long max_spins, int* status, cudaStream_t s);
 void sum_slots_wait(const void* slots, int n_slots, long long slot_elems, void* out, int out_dtype, int accumulate, const int* flags,
                     const int* counter, long long max_spins, int* status, cudaStream_t s);
 

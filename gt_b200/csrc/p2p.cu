@@ -300,6 +300,29 @@ __global__ void sum_slots_wait_kernel(const __nv_bfloat16* __restrict__ slots, i
     }
 }
 
+// Two-shot all-reduce of the flat fp32 gradient buffer over the data-parallel group, as ONE kernel per rank: after the group has
+// signalled "gradients final", rank r sums slice r of every member's buffer (peer reads, fixed order, fp32) and stores the
+// reduced slice into EVERY member's result buffer (peer stores): 2 n bytes cross this rank's links instead of P n for the
+// one-shot form, and no barrier kernel runs.  A second signal / wait pair tells the optimizer that all slices have landed.
+__global__ void allreduce_two_shot_kernel(PeerFlags src, PeerFlags dst, int n_peers, int me, long long n, long long chunk,
+                                          const int* flags, const int* counter, long long max_spins, int* status) {
+    block_wait_channel(flags, counter, n_peers, max_spins, status);
+    const long long lo = (long long)me * chunk, hi = lo + chunk < n ? lo + chunk : n;
+    for (long long i = lo / 4 + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < hi / 4; i += (long long)gridDim.x * blockDim.x) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int p = 0; p < n_peers; ++p) {
+            const float4 v = reinterpret_cast<const float4*>(src.p[p])[i];
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        for (int p = 0; p < n_peers; ++p) reinterpret_cast<float4*>(dst.p[p])[i] = acc;
+    }
+}
+
+// bounded wait of one block on a channel (used where the consumer is a library-free kernel that cannot take the wait itself)
+__global__ void channel_wait_kernel(const int* flags, const int* counter, int n_peers, long long max_spins, int* status) {
+    block_wait_channel(flags, counter, n_peers, max_spins, status);
+}
+
 int grid_for(long long items, int per_block) {
     long long b = (items + per_block - 1) / per_block;
     long long cap = 148LL * 8;
@@ -362,6 +385,20 @@ void sum_slots_wait(const void* slots, int n_slots, long long slot_elems, void* 
     else
         sum_slots_wait_kernel<float><<<grid_for(n8, 256), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(slots), n_slots, slot_elems,
                                                                        static_cast<float*>(out), accumulate, flags, counter, max_spins, status);
+}
+
+void allreduce_two_shot(void* const* src, void* const* dst, int n_peers, int me, long long n, const int* flags, const int* counter,
+                        long long max_spins, int* status, cudaStream_t s) {
+    if (n <= 0) return;
+    PeerFlags a{}, b{};
+    for (int p = 0; p < n_peers && p < 8; ++p) { a.p[p] = static_cast<int*>(src[p]); b.p[p] = static_cast<int*>(dst[p]); }
+    long long chunk = (n + n_peers - 1) / n_peers;
+    chunk = (chunk + 3) / 4 * 4;
+    allreduce_two_shot_kernel<<<grid_for(chunk / 4, 256), 256, 0, s>>>(a, b, n_peers, me, n, chunk, flags, counter, max_spins, status);
+}
+
+void channel_wait(const int* flags, const int* counter, int n_peers, long long max_spins, int* status, cudaStream_t s) {
+    channel_wait_kernel<<<1, 32, 0, s>>>(flags, counter, n_peers, max_spins, status);
 }
 
 void pull_gather_rows(const void* const* peers, const int* owner, const int* row, void* out, int n, int row_bytes, cudaStream_t s) {

@@ -463,9 +463,16 @@ class _StreamedAttnGCN(torch.autograd.Function):
                 blk = L.attns[s].block.csr
                 dxs = torch.zeros(xs.shape[0], x.shape[1], dtype=x.dtype, device=x.device)
                 if blk.num_edges:
-                    dq_s, dks, dvs, dgate_s, _ = be.attn_bwd_partial(q, ks, vs, blk, gate_c, None, m0, dacc, dl, score="gated",
-                                                                     norm="clampexp", clamp=L.attn_clamp, scale=L.attn_scale)
-                    dq += dq_s.to(pdt)
+                    if L.compact and hasattr(be, "attn_bwd_partial_accum") and x.is_cuda and pdt == torch.float32:
+                        # compact-accumulate backward: dq of the rows that own an edge in this sub-block is added in place
+                        dks, dvs, dgate_s, _ = be.attn_bwd_partial_accum(q, ks, vs, blk, gate_c, None, m0, dacc, dl, dq.view(rows, hd),
+                                                                         score="gated", norm="clampexp", clamp=L.attn_clamp,
+                                                                         scale=L.attn_scale)
+                    else:
+                        dq_s, dks, dvs, dgate_s, _ = be.attn_bwd_partial(q, ks, vs, blk, gate_c, None, m0, dacc, dl, score="gated",
+                                                                         norm="clampexp", clamp=L.attn_clamp, scale=L.attn_scale)
+                        dq += dq_s.to(pdt)
+                        del dq_s
                     if dgate_s is not None:
                         dgate = dgate_s if dgate is None else dgate + dgate_s
                     dks, dvs = dks.to(x.dtype).view(-1, hd), dvs.to(x.dtype).view(-1, hd)
@@ -473,7 +480,7 @@ class _StreamedAttnGCN(torch.autograd.Function):
                     dwv += K.matmul_tn(dvs, xs).to(dwv.dtype)
                     dxs += K.matmul_nn(dks, wk)
                     dxs += K.matmul_nn(dvs, wv)
-                    del dq_s, dks, dvs
+                    del dks, dvs
                 del ks, vs
                 if L.with_gcn:
                     gm = L.gcn_blocks[s].matrix(dagg.dtype, dagg.device)

@@ -134,7 +134,8 @@ class _FusedBranch(torch.autograd.Function):
         plan = blk.row_plan(SEG_EDGES)
         sc, nm, scale, lo, hi = _attn_cfg(layer)
         gate_c = gate.detach().float().contiguous().view(gate.shape[0], -1)
-        from .symm import MAX_SPINS
+        from .symm import wait_spins
+        MAX_SPINS = wait_spins()
         if comm is None:
             # ---- one rank: one GEMM for K | V | message | Q, kernels read its column slices ----
             qkvg = native.gemm_nt(x, w_stack)
@@ -222,7 +223,8 @@ class _FusedBranch(torch.autograd.Function):
         with_gcn = layer.with_gcn
         comm = _comm(layer)
         status = native.status(dev)
-        from .symm import MAX_SPINS
+        from .symm import wait_spins
+        MAX_SPINS = wait_spins()
         w_stack, g_stack = _stack(layer)
         blk = layer.attn.block.csr
         sc, nm, scale, lo, hi = _attn_cfg(layer)

@@ -111,6 +111,12 @@ class SparseRowPlan:
         pad = (-x.shape[1]) % unit
         return (torch.nn.functional.pad(x, (0, pad)) if pad else x), x.shape[1]
 
+    @staticmethod
+    def _pad8(x):
+        """Rows padded to a multiple of 8 elements (the peer-memory kernels move 8-element vectors)."""
+        pad = (-x.shape[1]) % 8
+        return (torch.nn.functional.pad(x, (0, pad)) if pad else x), x.shape[1]
+
     def gather(self, x, async_op=False):
         """``x [rows_per_rank, ...] -> [n_need, ...]``; ``async_op`` returns ``(work, finalize)``."""
         shp = tuple(x.shape[1:])
@@ -119,7 +125,8 @@ class SparseRowPlan:
             out = x2.index_select(0, self.send_idx.long()).view(-1, *shp)
             return (None, (lambda: out)) if async_op else out
         if self.transport == "pull" and x.is_cuda:
-            out = self.heap.pull_gather(x2, self).view(-1, *shp)
+            xp, width = self._pad8(x2)
+            out = self.heap.pull_gather(xp, self)[:, :width].reshape(-1, *shp)
             return (None, (lambda: out)) if async_op else out
         x2, width = self._pad16(x2)
         send = x2.index_select(0, self.send_idx.long())
@@ -137,7 +144,8 @@ class SparseRowPlan:
             out = self._accumulate(y2).view(-1, *shp)
             return (None, (lambda: out)) if async_op else out
         if self.transport == "pull" and y.is_cuda:
-            out = self.heap.pull_reduce(y2, self).view(-1, *shp)
+            yp, width = self._pad8(y2)
+            out = self.heap.pull_reduce(yp, self)[:, :width].reshape(-1, *shp)
             return (None, (lambda: out)) if async_op else out
         y2, width = self._pad16(y2)
         recv = y2.new_empty(self.n_send, y2.shape[1])

@@ -28,6 +28,15 @@ import os
 # polls before a wait on a peer gives up (~1 s at the default).  A rank-local stall longer than this (first-launch module
 # loading, a slow evaluation on one rank) makes the wait expire, so runs with long rank-local phases raise it.
 MAX_SPINS = int(os.environ.get("GT_PEER_WAIT_SPINS", "5000000"))
+# Eager steps (warm-up before a CUDA graph exists, tests, the first steps of a run) let the ranks' host code drift apart by whole
+# seconds: first-launch module loading, plan construction, a new communicator.  A wait enqueued eagerly therefore gets a longer
+# (still finite) limit than one recorded into a CUDA graph, whose launches are all enqueued at once.
+MAX_SPINS_EAGER = int(os.environ.get("GT_PEER_WAIT_SPINS_EAGER", str(20 * MAX_SPINS)))
+
+
+def wait_spins():
+    """Poll limit for a peer wait that is being enqueued now."""
+    return MAX_SPINS if torch.cuda.is_current_stream_capturing() else MAX_SPINS_EAGER
 
 
 class GroupContext:
@@ -46,7 +55,7 @@ class GroupContext:
         self.buffers = {}                                       # (kind, parity) -> (offset, nbytes)
 
     def barrier(self):
-        native.ext().group_barrier(self.peer_flag_ptrs, self.flags, self.counter, self.me, MAX_SPINS, native.status(self.heap.device))
+        native.ext().group_barrier(self.peer_flag_ptrs, self.flags, self.counter, self.me, wait_spins(), native.status(self.heap.device))
 
     def staging(self, nbytes, kind):
         """Staging buffer for the next collective of ``kind`` on this group (same offset on all ranks of the group).
@@ -224,6 +233,26 @@ class SymmetricHeap:
         native.ext().pull_all_reduce(self.peer_table_cached(c, off), out)
         c.barrier()                      # x (the gradient buffer) is rewritten right away by the next step's zero-fill
         return out
+
+    def all_reduce_two_shot(self, name, out_name, n, group=None):
+        """Sum of the heap tensor ``name`` (fp32, ``heap.empty(..., name)``) over the group into the heap tensor ``out_name`` on every
+        member: each rank reduces one slice from all members and stores it to all members; ordering by two epoch channels (no
+        barrier).  Returns after enqueueing; the result is complete on this rank once the second channel's wait has passed."""
+        from .fused_layer import Channel
+        c = self.ctx(group)
+        key = ("ar2", name, out_name)
+        st = c.buffers.get(key)
+        if st is None:
+            st = c.buffers[key] = (Channel(self, c), Channel(self, c))
+        ready, done = st
+        src, dst = self.named[name][0], self.named[out_name][0]
+        e = native.ext()
+        status = native.status(self.device)
+        ready.signal()                                            # my contribution is final
+        e.allreduce_two_shot([self.peer_base[r] + src for r in c.ranks], [self.peer_base[r] + dst for r in c.ranks], c.me, n,
+                             ready.flags, ready.counter, wait_spins(), status)
+        done.signal()                                             # my slice has been stored everywhere
+        e.channel_wait(done.flags, done.counter, c.size, wait_spins(), status)
 
     def peer_table_cached(self, c, off):
         key = ("tbl", off)

@@ -98,7 +98,7 @@ class TrainEngine:
             # slot is rewritten only after the event recorded behind its previous copy has completed.
             self._hyper_slots = torch.zeros(self.HYPER_SLOTS, 8, dtype=torch.float32).pin_memory()
             self._hyper_events = [None] * self.HYPER_SLOTS
-            self.g_sum = torch.zeros_like(self.flat_g) if heap is not None else None
+            self.g_sum = heap.empty(self.numel, torch.float32, "grads_sum") if heap is not None else None
         self.use_graph = use_graph and self.cuda
         self.graph_warmup = graph_warmup
         self._graph = None
@@ -127,6 +127,10 @@ class TrainEngine:
         if self.world == 1:
             return self.flat_g
         if self.heap is not None and self.cuda:
+            if self.world <= 8 and os.environ.get("GT_GRAD_ALLREDUCE", "two_shot") == "two_shot":
+                # one kernel per rank: reduce my slice from every member, store it to every member (2 n bytes per rank, no barrier)
+                self.heap.all_reduce_two_shot("grads", "grads_sum", self.numel, group=self.group)
+                return self.g_sum
             return self.heap.all_reduce(self.flat_g, self.g_sum, "grads", group=self.group)
         dist.all_reduce(self.flat_g, group=self.group)
         return self.flat_g

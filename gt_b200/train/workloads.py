@@ -20,6 +20,20 @@ def pad_to(n, mult):
     return -(-n // mult) * mult
 
 
+def _generate(name, seed, scale_down, device):
+    """The named base graph.  Graphs of half a million nodes and more are generated on the GPU when there is one (sorting 10^8
+    edges on one host core per rank would dominate a run); node data always comes back on the host.  The generators are
+    deterministic per device type, so every rank still builds the same graph."""
+    from ..data.synthetic import WORKLOADS
+    dev = torch.device(device)
+    big = WORKLOADS[name]["n"] // max(scale_down, 1) >= 500_000
+    gen_dev = dev if (dev.type == "cuda" and big) else torch.device("cpu")
+    wl = workload_graph(name, seed=seed, device=gen_dev, scale_down=scale_down)
+    wl["x"], wl["y"] = wl["x"].cpu(), wl["y"].cpu()
+    wl["masks"] = {k: m.cpu() for k, m in wl["masks"].items()}
+    return wl
+
+
 def exphormer_workload(name="exphormer_arxiv", grid_shape=None, device="cpu", dtype=torch.float32, seed=0, scale_down=1,
                        exp_deg=4, virtual_node=True, dropout=0.1, backend=None, layer="fused", norm="ln", stream_sub=1,
                        comm_bf16=True, heap=None, layers=None, hidden=None, heads=None, **model_kw):
@@ -28,13 +42,13 @@ def exphormer_workload(name="exphormer_arxiv", grid_shape=None, device="cpu", dt
     n_train, num_attn_edges, num_nodes, cfg``."""
     world = dist.get_world_size() if dist.is_initialized() else 1
     grid_shape = tuple(grid_shape or DEFAULT_GRIDS[world])
-    wl = workload_graph(name, seed=seed, scale_down=scale_down)
+    wl = _generate(name, seed, scale_down, device)
     cfg = wl["cfg"]
     n = wl["n"]
     n_tot = n + (1 if virtual_node else 0)                      # the token is node id n
     ei = wl["edge_index"]
-    exp = keyed_expander_edges(n, exp_deg, seed=seed)
-    tok = virtual_node_edges(n)[0] if virtual_node else None
+    exp = keyed_expander_edges(n, exp_deg, seed=seed, device=ei.device)
+    tok = virtual_node_edges(n)[0].to(ei.device) if virtual_node else None
     attn_ei, attn_et = ExphormerRef.build_attention_edges(ei, exp, tok)
     gcn_ei = gcn_edges_with_self_loops(ei, n_tot)
     n_pad = pad_to(n_tot, 8 * world * max(stream_sub, 1))
@@ -60,7 +74,7 @@ def exphormer_workload(name="exphormer_arxiv", grid_shape=None, device="cpu", dt
     out = dict(grid=grid, model=model, cfg=cfg, num_nodes=n_tot, num_attn_edges=int(attn_ei.shape[1]), num_gcn_edges=int(gcn_ei.shape[1]),
                x=grid.take_owned(x).to(dtype), y=grid.take_owned(y),
                masks={k: grid.take_owned(m.to(torch.uint8)).bool() & grid.valid_mask.cpu() for k, m in masks.items()},
-               n_train=int(masks["train"].sum()), in_degree=degrees(ei, n)[0])
+               n_train=int(masks["train"].sum()), in_degree=degrees(ei, n)[0].cpu())
     return out
 
 
@@ -74,7 +88,7 @@ def variant_workload(model="unimp", name=None, grid_shape=None, device="cpu", dt
     world = dist.get_world_size() if dist.is_initialized() else 1
     grid_shape = tuple(grid_shape or DEFAULT_GRIDS[world])
     name = name or ("unimp_products" if model == "unimp" else "graphormer_rmat")
-    wl = workload_graph(name, seed=seed, scale_down=scale_down)
+    wl = _generate(name, seed, scale_down, device)
     cfg, n, ei = wl["cfg"], wl["n"], wl["edge_index"]
     dev = torch.device(device)
     backend = backend or ("cuda" if dev.type == "cuda" else "torch")

@@ -83,6 +83,35 @@ def test_attention_accumulate_into_strided_payload():
     assert torch.equal(packed[:, hd + h:], before[:, hd + h:])
 
 
+def test_attention_backward_accumulates_dq_in_place():
+    """Compact-accumulate backward: dq of the rows that own an edge is added into an fp32 buffer (hub row cut into segments,
+    most rows empty and therefore untouched); dk / dv / dgate equal those of the plain partial backward."""
+    from gt_b200.attention import BlockCSR
+    from gt_b200.attention import backend_cuda as bc
+    dev = _dev()
+    torch.manual_seed(2)
+    n, nc, h, d = 500, 300, 8, 32
+    g = torch.Generator().manual_seed(5)
+    src, dst = torch.randint(0, nc, (400,), generator=g), torch.randint(0, n, (400,), generator=g)
+    src = torch.cat([src, torch.arange(nc)]); dst = torch.cat([dst, torch.full((nc,), 7)])
+    et = torch.randint(0, 3, (src.numel(),), generator=g)
+    blk = BlockCSR.from_edges(torch.stack([src, dst]), n, nc, et).to(dev)
+    q = torch.randn(n, h, d, device=dev).bfloat16()
+    k, v = torch.randn(nc, h, d, device=dev).bfloat16(), torch.randn(nc, h, d, device=dev).bfloat16()
+    gate = torch.randn(3, h, d, device=dev)
+    dacc, dl = torch.randn(n, h, d, device=dev), torch.randn(n, h, device=dev)
+    m0 = torch.zeros(n, h, device=dev)
+    kw = dict(score="gated", norm="clampexp", seg_edges=64)
+    dq_r, dk_r, dv_r, dg_r, _ = bc.attn_bwd_partial(q, k, v, blk, gate, None, m0, dacc, dl, **kw)
+    base = torch.randn(n, h * d, device=dev)
+    buf = base.clone()
+    dk, dv, dg, _ = bc.attn_bwd_partial_accum(q, k, v, blk, gate, None, m0, dacc, dl, buf, **kw)
+    assert _rel(buf - base, dq_r.float().reshape(n, h * d)) < 2e-2
+    empty = (blk.crow[1:] - blk.crow[:-1]) == 0
+    assert torch.equal(buf[empty], base[empty])                     # rows without an edge are not touched
+    assert _rel(dk, dk_r) < 1e-3 and _rel(dv, dv_r) < 1e-3 and _rel(dg, dg_r) < 1e-3
+
+
 @pytest.mark.parametrize("d,dtype", [(256, torch.bfloat16), (128, torch.float32), (80, torch.float32), (512, torch.bfloat16)])
 def test_spmm(d, dtype):
     from gt_b200.attention import BlockCSR

@@ -97,6 +97,9 @@ def _exphormer_case(dev, grid_shape, name, dtype, heap):
     out_ref = ref(x, ei, exp)
     loss_ref = torch.nn.functional.cross_entropy(out_ref[mask], y[mask], reduction="sum") / int(mask.sum())
     loss_ref.backward()
+    if world > 1:                       # ranks build their models at different speeds: start the step together
+        torch.cuda.synchronize()
+        dist.barrier()
     if heap is not None:
         heap.begin_step()
     eng.flat_g.zero_()
@@ -196,6 +199,9 @@ def _variant_case(dev, grid_shape, cfg, dtype, heap):
     loss_ref = torch.nn.functional.cross_entropy(out_ref[mask[:rows]], y[:rows][mask[:rows]], reduction="sum") / nm
     loss_ref.backward()
     model.train()
+    if world > 1:
+        torch.cuda.synchronize()
+        dist.barrier()
     if heap is not None:
         heap.begin_step()
     eng.flat_g.zero_()
@@ -338,13 +344,13 @@ def _multi_worker(rank, world, store, comm, dtype_name):
     for shape, name in MULTI[world]:
         try:
             _exphormer_case(dev, shape, name, dtype, heap)
-        except AssertionError as exc:
-            failures.append(str(exc))
+        except Exception as exc:                              # noqa: BLE001  (collected, reported together below)
+            failures.append(f"{name} on {shape}: {type(exc).__name__}: {exc}")
     for shape, cfg in MULTI_VARIANTS[world]:
         try:
             _variant_case(dev, shape, cfg, dtype, heap)
-        except AssertionError as exc:
-            failures.append(str(exc))
+        except Exception as exc:                              # noqa: BLE001
+            failures.append(f"{cfg} on {shape}: {type(exc).__name__}: {exc}")
     flag = torch.tensor([len(failures)], device=dev)
     dist.all_reduce(flag)
     torch.cuda.synchronize()
