@@ -35,8 +35,16 @@ constexpr int kUnrollFwd = 2, kUnrollRow = 2, kUnrollCol = 2;
 
 constexpr int kAsyncStages = 4;     // ring depth of the cp.async forward variant
 
+// 16-byte asynchronous copy global -> shared.  L2_ONLY selects cp.async.cg (the line is not allocated in L1): right where a warp
+// copies one whole 512-byte row per instruction and nothing is re-read through L1 (K / V / q / row-vector gathers of the
+// chunk-per-lane kernels: forward 0.63 ms against 0.72 ms on the 169K-node block, backward 2.1 ms against 2.27 ms); wrong where
+// lanes request the same or partial sectors (the column pass' per-head statistics, the head-lane kernels: 2.0 ms against 0.65 ms).
+template <bool L2_ONLY = false>
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+    if (L2_ONLY)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+    else
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
 }
 template <typename T> __device__ __forceinline__ typename Vec8<T>::Raw as_raw(const uint4& u);
 template <> __device__ __forceinline__ Vec8<__nv_bfloat16>::Raw as_raw<__nv_bfloat16>(const uint4& u) { return u; }
@@ -371,8 +379,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (UU * NSTG <=
 #pragma unroll
                     for (int i = 0; i < CPL; ++i) {
                         uint4* dst = ring + ((((g % NST) * U + u) * CPL + i) * 2) * (kWarpsPerBlock * 32) + threadIdx.x;
-                        cp_async16(dst, kp + foff[i]);
-                        cp_async16(dst + kWarpsPerBlock * 32, vp + foff[i]);
+                        cp_async16<true>(dst, kp + foff[i]);
+                        cp_async16<true>(dst + kWarpsPerBlock * 32, vp + foff[i]);
                     }
                     tring[((g % NST) * U + u) * (kWarpsPerBlock * 32) + threadIdx.x] = tn[u];
                 }
@@ -678,8 +686,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 5 : 
 #pragma unroll
                     for (int i = 0; i < CPL; ++i) {
                         uint4* dst = ring + ((((g % NST) * U + u) * CPL + i) * 2) * (kWarpsPerBlock * 32) + threadIdx.x;
-                        cp_async16(dst, kb + (size_t)jn[u] * ldk + foff[i]);
-                        cp_async16(dst + kWarpsPerBlock * 32, vb + (size_t)jn[u] * ldk + foff[i]);
+                        cp_async16<true>(dst, kb + (size_t)jn[u] * ldk + foff[i]);
+                        cp_async16<true>(dst + kWarpsPerBlock * 32, vb + (size_t)jn[u] * ldk + foff[i]);
                     }
                     tring[((g % NST) * U + u) * (kWarpsPerBlock * 32) + threadIdx.x] = tn[u];
                 }
@@ -929,8 +937,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 4 : 
 #pragma unroll
                     for (int i = 0; i < CPL; ++i) {
                         uint4* dst = ring + ((((g % NST) * U + u) * CPL + i) * 3) * (kWarpsPerBlock * 32) + threadIdx.x;
-                        cp_async16(dst, qb + (size_t)rn[u] * ldq + foff[i]);
-                        cp_async16(dst + kWarpsPerBlock * 32, rvb + (size_t)rn[u] * ldr + foff[i]);
+                        cp_async16<true>(dst, qb + (size_t)rn[u] * ldq + foff[i]);
+                        cp_async16<true>(dst + kWarpsPerBlock * 32, rvb + (size_t)rn[u] * ldr + foff[i]);
                         cp_async16(dst + 2 * kWarpsPerBlock * 32, a.stat + (size_t)rn[u] * H + head[i]);
                     }
                     tring[((g % NST) * U + u) * (kWarpsPerBlock * 32) + threadIdx.x] = tn[u];
@@ -1110,14 +1118,15 @@ __global__ void reduce_partials_kernel(const float* part, int n_blocks, int widt
 #include "attn_hl.cuh"
 
 // GT_ATTN_HL = "f,r,c": chunks per lane (2 or 4; 0 = use the chunk-per-lane kernels) of the head-lane forward, row-pass and
-// column-pass kernels.  Default "2,0,0": measured on the 169K-node benchmark block (8 heads x 32, 3.74 M edges) the forward with
-// 2 chunks per lane runs in 0.82 ms against 0.93 ms; 4 chunks per lane lose (1.22 ms: a lane's 16-byte pieces of a row are 64
-// bytes apart, so every copy instruction touches 32 sectors for 512 bytes), and the backward passes lose at either width
-// (3.10 ms against 2.58 ms: their 140-155 registers leave three blocks per SM).
+// column-pass kernels.  Default "0,0,0" (off).  Measured on the 169K-node benchmark block (8 heads x 32, 3.74 M edges): the forward
+// with 2 chunks per lane runs in 0.65 ms against 0.72 ms for the chunk-per-lane kernel with L1-allocating copies, but the latter
+// with L2-only copies takes 0.63 ms; 4 chunks per lane lose (1.22 ms: a lane's 16-byte pieces of a row are 64 bytes apart, so
+// every copy instruction touches 32 sectors for 512 bytes), and the backward passes lose at either width (3.10 ms against
+// 2.27 ms: their 140-155 registers leave three blocks per SM).
 struct HlCfg { int ch[3]; };
 const HlCfg& hl_cfg() {
     static const HlCfg cfg = [] {
-        HlCfg c{{2, 0, 0}};
+        HlCfg c{{0, 0, 0}};
         const char* e = getenv("GT_ATTN_HL");
         int a = 0, b = 0, d = 0;
         if (e && sscanf(e, "%d,%d,%d", &a, &b, &d) == 3) {
@@ -1167,7 +1176,8 @@ int attn_bwd_row_blocks(int n_seg) {
     return want < cap ? (want > 0 ? want : 1) : cap;
 }
 
-void attn_fwd(const AttnFwdArgs& a, cudaStream_t s) {
+void attn_fwd(const AttnFwdArgs& a_in, cudaStream_t s) {
+    const AttnFwdArgs& a = a_in;
     const AttnCommon& c = a.c;
     if (c.plan.n_seg == 0) return;
     int blocks = (c.plan.n_seg + kWarpsPerBlock - 1) / kWarpsPerBlock;
@@ -1238,7 +1248,8 @@ void attn_fwd(const AttnFwdArgs& a, cudaStream_t s) {
     }
 }
 
-void attn_bwd_row(const AttnBwdRowArgs& a, cudaStream_t s) {
+void attn_bwd_row(const AttnBwdRowArgs& a_in, cudaStream_t s) {
+    const AttnBwdRowArgs& a = a_in;
     const AttnCommon& c = a.c;
     if (c.plan.n_seg == 0) return;
     const int blocks = a.n_blocks > 0 ? a.n_blocks : attn_bwd_row_blocks(c.plan.n_seg);
@@ -1300,7 +1311,8 @@ void attn_bwd_row(const AttnBwdRowArgs& a, cudaStream_t s) {
 #undef GT_LAUNCH_ROW
 }
 
-void attn_bwd_col(const AttnBwdColArgs& a, cudaStream_t s) {
+void attn_bwd_col(const AttnBwdColArgs& a_in, cudaStream_t s) {
+    const AttnBwdColArgs& a = a_in;
     const AttnCommon& c = a.c;
     if (c.plan.n_seg == 0) return;
     int blocks = (c.plan.n_seg + kWarpsPerBlock - 1) / kWarpsPerBlock;
