@@ -46,6 +46,34 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
     else
         asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
 }
+// ---- bulk row copies (cp.async.bulk, completion on an mbarrier) --------------------------------------------------------
+// One instruction moves a whole gathered row global -> shared through the copy engine of the SM instead of 32 lanes x 16 bytes
+// through the load/store pipe, which is the busiest unit of these kernels (l1tex 93 % in the forward).
+__device__ int g_attn_status = 0;          // set when a bounded mbarrier wait expired (read by the host through attn_status())
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init1(uint64_t* bar) { asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(bar))); }
+__device__ __forceinline__ void mbar_expect(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_row(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(smem_dst)), "l"(gsrc),
+                 "r"(bytes), "r"(smem_addr(bar))
+                 : "memory");
+}
+// Bounded wait (about 50 ms).  After the first expiry `gave_up` makes every later wait of the thread return at once, so a fault
+// in the copy path ends the kernel quickly instead of adding one limit per edge group; the host raises after the step.
+__device__ __forceinline__ void mbar_wait_bounded(uint64_t* bar, uint32_t parity, bool& gave_up) {
+    if (gave_up) return;
+    for (uint32_t tries = 0; tries < (1u << 17); ++tries) {
+        uint32_t ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+        if (ok) return;
+    }
+    gave_up = true;
+    atomicExch(&g_attn_status, 7);
+}
+
 template <typename T> __device__ __forceinline__ typename Vec8<T>::Raw as_raw(const uint4& u);
 template <> __device__ __forceinline__ Vec8<__nv_bfloat16>::Raw as_raw<__nv_bfloat16>(const uint4& u) { return u; }
 
@@ -311,7 +339,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? 6 : 3)) attn_
 // Every lane copies and later reads only its own 16-byte chunks, so no synchronisation between lanes is needed.
 // (Measured on the arxiv-shaped block, 8 heads x 32: 2 edge groups x 4 stages 1.080 ms; 3 x 3 1.081; 4 x 3 1.213; 4 x 2 1.215;
 // 2 x 6 1.333: deeper rings cost resident blocks.)
-template <typename T, int CPL, int SPEC = 0, int UU = kUnrollFwd, int NSTG = kAsyncStages>
+template <typename T, int CPL, int SPEC = 0, int UU = kUnrollFwd, int NSTG = kAsyncStages, bool BULK = false>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (UU * NSTG <= 8 ? 6 : 4) : 3)) attn_fwd_async_kernel(AttnFwdArgs a) {
     extern __shared__ float smem[];
     const AttnCommon& c = a.c;
@@ -325,6 +353,18 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (UU * NSTG <=
     uint4* ring = reinterpret_cast<uint4*>(smem + ((table_floats(c) + 3) & ~3));
     constexpr int NST = NSTG;
     int* tring = reinterpret_cast<int*>(ring + (size_t)NSTG * UU * CPL * 2 * (kWarpsPerBlock * 32));      // edge types of the groups in flight
+    // BULK (rows of 32 x 16 bytes, one edge per warp iteration): the ring is [warp][stage][edge slot u][K | V] whole rows, filled
+    // by one bulk copy per row (lane 0) that completes on the (warp, stage) mbarrier; bit s of `phase` is the parity to wait for
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tring + (size_t)NSTG * UU * (kWarpsPerBlock * 32)) + (threadIdx.x >> 5) * NSTG;
+    uint4* wring = ring + (size_t)(threadIdx.x >> 5) * (NSTG * UU * 2 * 32);
+    uint32_t phase = 0;
+    bool gave_up = false;
+    if (BULK) {
+        if ((threadIdx.x & 31) == 0)
+            for (int st = 0; st < NSTG; ++st) mbar_init1(bars + st);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        __syncthreads();
+    }
     const Lanes L = make_lanes(HD, D);
     // row strides in elements (0 = dense rows of H*D): operands may be column slices of wider matrices, e.g. K | V | message
     const size_t ldq = c.ldq ? (size_t)c.ldq : (size_t)HD, ldk = c.ldk ? (size_t)c.ldk : (size_t)HD;
@@ -372,28 +412,48 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (UU * NSTG <=
         };
         auto issue = [&](int g) {
             if (g < n_it) {
+                if (BULK) {
+                    const int st = g % NST;
+                    __syncwarp();                           // every lane has finished reading the stage's previous rows
+                    if ((threadIdx.x & 31) == 0) {
+                        mbar_expect(bars + st, (uint32_t)(U * 2 * HD * sizeof(T)));
+#pragma unroll
+                        for (int u = 0; u < U; ++u) {
+                            bulk_row(wring + ((st * U + u) * 2) * 32, kb + (size_t)jn[u] * ldk, (uint32_t)(HD * sizeof(T)), bars + st);
+                            bulk_row(wring + ((st * U + u) * 2 + 1) * 32, vb + (size_t)jn[u] * ldk, (uint32_t)(HD * sizeof(T)), bars + st);
+                        }
+                    }
+                }
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
-                    const T* kp = kb + (size_t)jn[u] * ldk;
-                    const T* vp = vb + (size_t)jn[u] * ldk;
+                    if (!BULK) {
+                        const T* kp = kb + (size_t)jn[u] * ldk;
+                        const T* vp = vb + (size_t)jn[u] * ldk;
 #pragma unroll
-                    for (int i = 0; i < CPL; ++i) {
-                        uint4* dst = ring + ((((g % NST) * U + u) * CPL + i) * 2) * (kWarpsPerBlock * 32) + threadIdx.x;
-                        cp_async16<true>(dst, kp + foff[i]);
-                        cp_async16<true>(dst + kWarpsPerBlock * 32, vp + foff[i]);
+                        for (int i = 0; i < CPL; ++i) {
+                            uint4* dst = ring + ((((g % NST) * U + u) * CPL + i) * 2) * (kWarpsPerBlock * 32) + threadIdx.x;
+                            cp_async16<true>(dst, kp + foff[i]);
+                            cp_async16<true>(dst + kWarpsPerBlock * 32, vp + foff[i]);
+                        }
                     }
                     tring[((g % NST) * U + u) * (kWarpsPerBlock * 32) + threadIdx.x] = tn[u];
                 }
                 if (g + 1 < n_it) fetch(g + 1);
             }
-            asm volatile("cp.async.commit_group;" ::: "memory");
+            if (!BULK) asm volatile("cp.async.commit_group;" ::: "memory");
         };
         if (n_it > 0) fetch(0);             // an empty segment has no edge to read, and idx[beg - 1] may lie before the array
 #pragma unroll
         for (int it = 0; it < NST - 1; ++it) issue(it);
         for (int it = 0; it < n_it; ++it) {
             issue(it + NST - 1);
-            asm volatile("cp.async.wait_group %0;" ::"n"(NST - 1) : "memory");
+            if (BULK) {
+                const int st = it % NST;
+                mbar_wait_bounded(bars + st, (phase >> st) & 1u, gave_up);
+                phase ^= 1u << st;
+            } else {
+                asm volatile("cp.async.wait_group %0;" ::"n"(NST - 1) : "memory");
+            }
             int j[U], t[U];
             Raw kr[U][CPL], vr[U][CPL];
 #pragma unroll
@@ -403,9 +463,15 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (UU * NSTG <=
                 t[u] = tring[((it % NST) * U + u) * (kWarpsPerBlock * 32) + threadIdx.x];
 #pragma unroll
                 for (int i = 0; i < CPL; ++i) {
-                    const uint4* src = ring + ((((it % NST) * U + u) * CPL + i) * 2) * (kWarpsPerBlock * 32) + threadIdx.x;
-                    kr[u][i] = as_raw<T>(src[0]);
-                    vr[u][i] = as_raw<T>(src[kWarpsPerBlock * 32]);
+                    if (BULK) {
+                        const uint4* src = wring + (((it % NST) * U + u) * 2) * 32 + (threadIdx.x & 31);
+                        kr[u][i] = as_raw<T>(src[0]);
+                        vr[u][i] = as_raw<T>(src[32]);
+                    } else {
+                        const uint4* src = ring + ((((it % NST) * U + u) * CPL + i) * 2) * (kWarpsPerBlock * 32) + threadIdx.x;
+                        kr[u][i] = as_raw<T>(src[0]);
+                        vr[u][i] = as_raw<T>(src[kWarpsPerBlock * 32]);
+                    }
                 }
             }
 #pragma unroll
@@ -1213,7 +1279,15 @@ void attn_fwd(const AttnFwdArgs& a_in, cudaStream_t s) {
         attn_fwd_async_kernel<__nv_bfloat16, CPL, SP><<<blocks, kWarpsPerBlock * 32, sma, s>>>(a);    \
     } while (0)
         const int sp = spec_heads(c.H, c.D);
-        if (cpl == 1 && sp == 8) GT_LAUNCH_FWD_ASYNC(1, 8);
+        // GT_ATTN_BULK=1: rows by cp.async.bulk.  Off by default: measured 0.83 ms against 0.63 ms on the 169K-node block (7.5 M
+        // copies of 512 bytes per launch are more than the copy engine retires; it is made for tiles, not for rows).
+        static const bool use_bulk = [] { const char* e = getenv("GT_ATTN_BULK"); return e && e[0] == '1'; }();
+        const bool rows16 = ((reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v)) & 15) == 0 && ((c.ldk ? c.ldk : c.H * c.D) % 8) == 0;
+        if (cpl == 1 && sp == 8 && use_bulk && rows16) {
+            const size_t smb = sma + kWarpsPerBlock * kAsyncStages * sizeof(uint64_t);
+            set_smem(attn_fwd_async_kernel<__nv_bfloat16, 1, 8, kUnrollFwd, kAsyncStages, true>, smb);
+            attn_fwd_async_kernel<__nv_bfloat16, 1, 8, kUnrollFwd, kAsyncStages, true><<<blocks, kWarpsPerBlock * 32, smb, s>>>(a);
+        } else if (cpl == 1 && sp == 8) GT_LAUNCH_FWD_ASYNC(1, 8);
         else if (cpl == 1 && sp == 4) GT_LAUNCH_FWD_ASYNC(1, 4);
         else if (cpl == 1) GT_LAUNCH_FWD_ASYNC(1, 0);
         else if (sp == 16) GT_LAUNCH_FWD_ASYNC(2, 16);
@@ -1396,6 +1470,13 @@ std::vector<KernelInfo> attn_kernel_info() {
     v.push_back(info_of("row_regs_bf16_8x32", attn_bwd_row_kernel<__nv_bfloat16, 1, true, 8, false>, 2 * tbl));
     v.push_back(info_of("col_ring_bf16_8x32", attn_bwd_col_kernel<__nv_bfloat16, 1, 8, true>, tbl + ring_c));
     v.push_back(info_of("col_regs_bf16_8x32", attn_bwd_col_kernel<__nv_bfloat16, 1, 8, false>, tbl));
+    return v;
+}
+
+int attn_status() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_attn_status, sizeof(int)) != cudaSuccess) { cudaGetLastError(); return -1; }
+    if (v != 0) { const int z = 0; cudaMemcpyToSymbol(g_attn_status, &z, sizeof(int)); }
     return v;
 }
 

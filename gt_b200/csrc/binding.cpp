@@ -140,6 +140,8 @@ std::vector<std::tuple<std::string, int64_t, int64_t, int64_t, int64_t, int64_t>
     return out;
 }
 
+int64_t attn_status() { return gt::attn_status(); }
+
 bool attn_shape_supported(int64_t H, int64_t D, int64_t T) { return gt::attn_shape_supported((int)H, (int)D, (int)T); }
 
 void spmm(Tensor ptr, Tensor idx, OptT w, Tensor x, Tensor out, bool accumulate, std::vector<Tensor> plan, OptT scratch,
@@ -646,6 +648,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("signal_peers", &signal_peers);
     m.def("wait_flags", &wait_flags);
     m.def("group_barrier", &group_barrier);
+    m.def("attn_status", &attn_status);
     m.def("channel_signal", &channel_signal);
     m.def("sum_payload", &sum_payload);
     m.def("pull_unpack", &pull_unpack);

@@ -89,6 +89,7 @@ void attn_bwd_col(const AttnBwdColArgs& a, cudaStream_t s);
 bool attn_shape_supported(int H, int D, int T);
 struct KernelInfo { const char* name; int regs; int local_bytes; int static_smem; int dyn_smem; int blocks_per_sm; };
 std::vector<KernelInfo> attn_kernel_info();            // compiled resources of the main attention kernel instances
+int attn_status();                                     // nonzero once after a bounded copy wait of an attention kernel expired (synchronises)
 int attn_bwd_row_blocks(int n_seg);                    // grid size attn_bwd_row will use for n_seg segments
 // sum of per-block partials: out[i] = sum_b part[b, i]
 void reduce_partials(const float* part, int n_blocks, int width, float* out, cudaStream_t s, int accumulate = 0);   // accumulate: out += sum

@@ -85,10 +85,12 @@ def status(device=None):
 def check_status(device=None):
     """Raise if a kernel recorded an expired bounded wait (synchronises the device)."""
     code = int(status(device).item())
+    if code == 0 and hasattr(ext()._mod, "attn_status"):
+        code = int(ext()._mod.attn_status())           # bounded copy waits of the attention kernels (device-global word)
     if code != 0:
         status(device).zero_()
         raise RuntimeError(f"gt_b200 kernel reported an expired wait (code {code}): "
-                           "1-3 GEMM producer/MMA/epilogue, 4-6 TN GEMM, >=100 peer flag of rank code-100")
+                           "1-3 GEMM producer/MMA/epilogue, 4-6 TN GEMM, 7 attention row copy, >=100 peer flag of rank code-100")
 
 
 def rng_state(device=None):
