@@ -17,7 +17,7 @@ def graph_of(spec):
     n, e = spec["n"], spec["e_graph"]
     e_attn = gs.attention_edges(n, e, spec["exp_deg"]) - n + (2 * n if spec.get("virtual_node") else 0)
     return gs.Graph(n, e_attn, e + n, spec["f_in"], spec["name"], classes=spec.get("classes", 40), exp_deg=spec["exp_deg"],
-                    skew=spec.get("skew", 1.0))
+                    skew=spec.get("skew", 1.0), token=bool(spec.get("virtual_node")))
 
 
 def predict(row):

@@ -44,6 +44,13 @@ HW = dict(
     # collectives inside an NVSwitch node: latency (us) and per-rank payload rate (GB/s received or sent) at large sizes
     coll=dict(ag=(14.0, 560.0), rs=(14.0, 520.0), a2a=(16.0, 480.0), ar=(18.0, 360.0), p2p=(6.0, 700.0)),
     coll_half_mb=2.0,               # payload at which half the large-size rate is reached
+    # collectives issued from inside compute kernels over peer memory (epoch channel + loads / stores over NVLink): flag
+    # latency and achieved rate per rank
+    fused_coll=dict(alpha_us=6.0, gbs=600.0),
+    # arrival skew: ranks reach a wait at different times (unequal blocks, kernel tails on small blocks), and the step runs at the
+    # speed of the last one; measured as the share of the layers' time by which multi-rank steps exceed the sum of their parts
+    # (0.12 from the 2-, 4- and 8-GPU rows of bench/model_validation_data.py)
+    sync_skew=0.12,
     # across nodes: one 400 Gb/s NIC per GPU (nominal; not measured on this pool)
     inter=dict(alpha_us=28.0, gbs=46.0),
     a2a_over_ag=1.25,               # cost of moving the same bytes by all-to-all-v instead of a dense all-gather
@@ -93,6 +100,7 @@ class Graph:
     exp_deg: int = 3
     kappa: float = 0.8             # dispersion of the degree distribution (negative binomial); None: Poisson
     skew: float = 1.0              # sparse-kernel time on this graph's blocks / on random blocks of the same shape (measured)
+    token: bool = False            # a global token: one row and one column with n entries each (counted in e_attn)
 
     @property
     def deg_attn(self):
@@ -193,6 +201,15 @@ def sparse_coll_ms(kind, layout, nbytes, share, m: Model):
     return min(dense, sparse)
 
 
+def fused_coll_ms(nbytes, group, hidden_ms):
+    """A collective issued from inside a compute kernel over peer memory: flag latency plus the part of the transfer that the
+    issuing kernel (``hidden_ms``) does not cover; nothing for a group of one."""
+    if group <= 1 or nbytes <= 0:
+        return 0.0
+    fc = HW["fused_coll"]
+    return fc["alpha_us"] / 1e3 + max(nbytes / (fc["gbs"] * 1e6) - hidden_ms, 0.0)
+
+
 def gemm_ms(flops, d, which=0):
     tab = HW["gemm_tflops"]
     keys = sorted(tab)
@@ -266,24 +283,39 @@ def fused_layer_ms(pd, po, g: Graph, m: Model, gpn=GPUS_PER_NODE):
     d, H, b, a = m.hidden, m.heads, m.wire_bytes, m.act_bytes
     R, C, O = g.n / pd, g.n / po, g.n / P
     ea, eg = g.e_attn / P, g.e_gcn / P
+    if g.token and P > 1:
+        # The token's row lies in ONE row block (n / po entries for each rank of that row group) and its column in ONE column
+        # block (n / pd entries per rank of that column group): the rank that has both is the straggler every other rank waits
+        # for at the next collective, so the step runs at its speed.
+        ea = (g.e_attn - 2 * g.n) / P + g.n / po + g.n / pd
     pl = placement(pd, po, 1, gpn)
     sh_c, sh_r = sparse_share(g, pd), sparse_share(g, po)
     w = (2 * d if m.with_gcn else d) + 2 * H
     proj = 2 * d * d * ((3 if m.with_gcn else 2) * C + R)
     f, bw = {}, {}
-    f["gather"] = sparse_coll_ms("ag", pl["col"], (C - O) * d * b, sh_c, m) + sparse_coll_ms("ag", pl["row"], (R - O) * d * b, sh_r, m)
     f["gemm"] = gemm_ms(proj, d, 0)
     f["spmm"] = spmm_ms(eg, R, C, d, g.skew) if m.with_gcn else 0.0
     f["attn"] = attn_ms(ea, R, C, H, d // H, "fwd", g.skew)
-    f["combine"] = sparse_coll_ms("rs", pl["row"], (R - O) * w * b, sh_r, m) + (ew_ms(R * w * (4 + b), 1) if po > 1 else 0.0)
     f["tail"] = ew_ms(O * d * a * 10, 3) + gemm_ms(2 * O * d * d * 2 * m.ffn_mult, d, 0)
     bw["tail"] = ew_ms(O * d * a * 16, 4) + gemm_ms(2 * O * d * d * 2 * m.ffn_mult, d, 1) + gemm_ms(2 * O * d * d * 2 * m.ffn_mult, d, 2)
-    bw["combine"] = sparse_coll_ms("ag", pl["row"], (R - O) * w * b, sh_r, m)
     bw["attn"] = attn_ms(ea, R, C, H, d // H, "bwd", g.skew)
     bw["spmm"] = spmm_ms(eg, C, R, d, g.skew) if m.with_gcn else 0.0
     bw["gemm"] = gemm_ms(proj, d, 1) + gemm_ms(proj, d, 2)
-    bw["dx"] = sparse_coll_ms("rs", pl["col"], (C - O) * d * b, sh_c, m) + sparse_coll_ms("rs", pl["row"], (R - O) * d * b, sh_r, m) \
-        + ew_ms((C + R) * d * a * 2 + O * d * a * 3, 3)
+    if m.transport == "p2p" and not m.sparse_comm:
+        # collectives inside the compute kernels (peer memory, epoch channels): the transfer hides behind the kernel that
+        # issues it; what remains is the flag latency, the part of the transfer that outlasts the kernel, and the owner-side
+        # slot sums / unpacking passes
+        f["gather"] = fused_coll_ms((C - O) * d * b, pd, f["gemm"] * 0.75) + fused_coll_ms((R - O) * d * b, po, f["gemm"] * 0.25)
+        f["combine"] = fused_coll_ms((R - O) * w * b, po, f["attn"] + f["spmm"]) + (ew_ms(O * w * (po * b + 4), 1) if po > 1 else 0.0)
+        bw["combine"] = fused_coll_ms((R - O) * w * b, po, 0.0) + (ew_ms(R * w * (b + 3), 2) if po > 1 else 0.0)
+        bw["dx"] = fused_coll_ms((C - O) * d * b, pd, bw["gemm"] * 0.4) + fused_coll_ms((R - O) * d * b, po, bw["gemm"] * 0.1) \
+            + ew_ms(O * d * b * (pd + po + 1), (pd > 1) + (po > 1))
+    else:
+        f["gather"] = sparse_coll_ms("ag", pl["col"], (C - O) * d * b, sh_c, m) + sparse_coll_ms("ag", pl["row"], (R - O) * d * b, sh_r, m)
+        f["combine"] = sparse_coll_ms("rs", pl["row"], (R - O) * w * b, sh_r, m) + (ew_ms(R * w * (4 + b), 1) if po > 1 else 0.0)
+        bw["combine"] = sparse_coll_ms("ag", pl["row"], (R - O) * w * b, sh_r, m)
+        bw["dx"] = sparse_coll_ms("rs", pl["col"], (C - O) * d * b, sh_c, m) + sparse_coll_ms("rs", pl["row"], (R - O) * d * b, sh_r, m) \
+            + ew_ms((C + R) * d * a * 2 + O * d * a * 3, 3)
     return f, bw
 
 
@@ -302,11 +334,14 @@ def fixed_step_ms(P, g: Graph, m: Model, gpn=GPUS_PER_NODE):
 def predict_fused_ms(pd, po, g: Graph, m: Model, gpn=GPUS_PER_NODE, breakdown=False):
     f, bw = fused_layer_ms(pd, po, g, m, gpn)
     fixed = fixed_step_ms(pd * po, g, m, gpn)
-    total = m.layers * (sum(f.values()) + sum(bw.values())) + fixed
+    layers = m.layers * (sum(f.values()) + sum(bw.values()))
+    skew = HW["sync_skew"] * layers if pd * po > 1 else 0.0
+    total = layers + skew + fixed
     if breakdown:
         parts = {k: m.layers * v for k, v in f.items()}
         parts.update({"bwd " + k: m.layers * v for k, v in bw.items()})
         parts["fixed"] = fixed
+        parts["arrival skew"] = skew
         return total, parts
     return total
 

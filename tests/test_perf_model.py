@@ -87,14 +87,21 @@ def test_constants_overlay(tmp_path):
 
 
 def test_model_tracks_the_measured_table():
-    """The shipped constants keep the model within a factor 1.6 of every measured row and rank the measured grids alike."""
+    """The shipped constants keep the model within a factor 1.25 of every measured row, and for every world size the model
+    orders the measured grids exactly as the measurements do (the ranking is what --grid_auto relies on)."""
     from gt_b200.bench.model_validation_data import MEASURED
     from gt_b200.bench.validate_model import predict
+    by_world = {}
     for row in MEASURED:
         r = predict(row) / row["ms"]
-        assert 1 / 1.6 < r < 1.6, (row["grid"], r)
-    ms = [predict(r) for r in MEASURED if r["transport"] == "p2p"]
-    assert ms == sorted(ms, reverse=True)                        # more GPUs -> faster, as measured
+        assert 1 / 1.25 < r < 1.25, (row["grid"], r)
+        world = row["grid"][0] * row["grid"][1]
+        by_world.setdefault(world, []).append((row["grid"], row["ms"], predict(row)))
+    for world, rows in by_world.items():
+        measured = [g for g, _, _ in sorted(rows, key=lambda v: v[1])]
+        model = [g for g, _, _ in sorted(rows, key=lambda v: v[2])]
+        assert measured == model, (world, measured, model)
+    assert len(by_world[8]) >= 4 and len(by_world[4]) >= 3
 
 
 def test_analytic_gather_model_against_the_measured_degree_sweep():
