@@ -18,6 +18,7 @@ import torch
 
 from ..ops import native
 from . import backend_torch as _bt
+from . import tiles as _tiles
 from .csr import BlockCSR
 
 SEG_EDGES = 256
@@ -89,16 +90,47 @@ def attn_fwd_partial(q, k, v, blk: BlockCSR, gate=None, bias=None, *, score="dot
         return acc, l, m
     n, h, d = q.shape
     sc, nm, scale, lo, hi = _cfg(q, score, norm, clamp, scale)
-    plan = blk.row_plan(seg_edges)
-    acc = torch.empty(n, h, d, dtype=torch.float32, device=q.device)
-    l = torch.empty(n, h, dtype=torch.float32, device=q.device)
-    m = torch.empty(n, h, dtype=torch.float32, device=q.device)
-    scratch = torch.empty(plan.num_slots, (h * d + 2 * h + 3) // 4 * 4, dtype=torch.float32, device=q.device) if plan.num_slots else None
+    # density dispatch: dense 128 x 128 tiles of the mask go to the tensor-core kernel, everything else stays on the gathers
+    tiles = _tile_plan_for(q, k, blk, bias, score, k_peers)
+    if tiles is not None:
+        blk = tiles.residual
     g, b = _tables(gate, bias, score)
-    native.ext().attn_fwd(q.contiguous(), k.contiguous() if k is not None else None, v.contiguous() if v is not None else None,
-                          blk.col, blk.etype, g, b, _plan_list(plan), None, acc, l, m, scratch, h, d, sc, nm, scale, lo, hi,
-                          h * d, h, False, k_peers, v_peers, int(rows_per_peer), 0, 0, [], 0, 0, 0)
+    if tiles is not None and blk.num_edges == 0:
+        acc = torch.zeros(n, h, d, dtype=torch.float32, device=q.device)
+        l = torch.zeros(n, h, dtype=torch.float32, device=q.device)
+        m = torch.zeros(n, h, dtype=torch.float32, device=q.device)
+    else:
+        plan = blk.row_plan(seg_edges)
+        acc = torch.empty(n, h, d, dtype=torch.float32, device=q.device)
+        l = torch.empty(n, h, dtype=torch.float32, device=q.device)
+        m = torch.empty(n, h, dtype=torch.float32, device=q.device)
+        scratch = torch.empty(plan.num_slots, (h * d + 2 * h + 3) // 4 * 4, dtype=torch.float32, device=q.device) if plan.num_slots else None
+        native.ext().attn_fwd(q.contiguous(), k.contiguous() if k is not None else None, v.contiguous() if v is not None else None,
+                              blk.col, blk.etype, g, b, _plan_list(plan), None, acc, l, m, scratch, h, d, sc, nm, scale, lo, hi,
+                              h * d, h, False, k_peers, v_peers, int(rows_per_peer), 0, 0, [], 0, 0, 0)
+    if tiles is not None:
+        attn_tile_accumulate(q, k, v, tiles, b, acc, l, m, score=score, norm=norm, clamp=(lo, hi), scale=scale)
     return acc, l, m
+
+
+def _tile_plan_for(q, k, blk, bias, score, k_peers=None):
+    """The dense-tile split of ``blk`` when the tensor-core kernel can take it: bf16, heads of 32 in pairs, plain or biased
+    dot-product scores, K / V in local memory."""
+    if score == "gated" or k is None or k_peers is not None or q.dtype != torch.bfloat16:
+        return None
+    if q.shape[2] != 32 or q.shape[1] % 2 or (bias is not None and bias.shape[0] > _tiles.MAX_TYPES):
+        return None
+    return _tiles.tile_plan(blk)
+
+
+def attn_tile_accumulate(q, k, v, tiles, bias, acc, l, m, *, score="dot", norm="softmax", clamp=(-5.0, 5.0), scale=None, debug_scores=None):
+    """Merge the contribution of the dense tiles into the partial states ``(acc, l, m)`` in place (``csrc/attn_tile.cu``).
+    ``debug_scores``: optional fp32 ``[2, 128, 128]`` that receives the raw ``Q K^T`` of the first tile of the first head pair."""
+    n, h, d = q.shape
+    sc, nm, scale, lo, hi = _cfg(q, score, norm, clamp, scale)
+    b = bias.float().contiguous() if (score == "biased" and bias is not None) else None
+    native.ext().attn_tile_fwd(q.contiguous(), k.contiguous(), v.contiguous(), tiles.rb_ids, tiles.rb_ptr, tiles.tile_cb, tiles.mask, b,
+                               acc.view(n, h * d), l, m, h, sc, nm, scale, lo, hi, 0, 0, native.status(q.device), debug_scores)
 
 
 def attn_fwd_partial_pull(q, k_peers, v_peers, rows_per_peer, blk, gate=None, bias=None, **kw):

@@ -43,7 +43,7 @@ def rows_from_logs(paths):
                                  ms=float(mt.group(6))))
             elif line.startswith("{") and '"ms_per_step"' in line:
                 j = json.loads(line)
-                par = j.get("config", {}).get("grid") or {1: (1, 1), 2: (2, 1), 4: (2, 2), 8: (2, 4)}[j["n_gpus"]]
+                par = j.get("config", {}).get("grid") or {1: (1, 1), 2: (2, 1), 4: (2, 2), 8: (4, 2)}[j["n_gpus"]]
                 rows.append(dict(graph=ARXIV_CL, model=(256, 8, 4), grid=tuple(par), ms=j["ms_per_step"],
                                  transport=j.get("config", {}).get("comm", "nccl")))
     return rows

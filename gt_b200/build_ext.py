@@ -10,7 +10,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(ROOT, "csrc")
 BUILD = os.path.join(ROOT, "_ext")
 NAME = "gt_b200_native"
-CU = ["attn.cu", "spmm.cu", "rowops.cu", "gemm.cu", "p2p.cu"]
+CU = ["attn.cu", "attn_tile.cu", "spmm.cu", "rowops.cu", "gemm.cu", "p2p.cu"]
 
 
 def sources():

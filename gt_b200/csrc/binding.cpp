@@ -90,6 +90,38 @@ void attn_fwd(Tensor q, OptT k, OptT v, Tensor idx, OptT etype, OptT gate, OptT 
     gt::attn_fwd(a, stream());
 }
 
+// Dense 128 x 128 tiles of the mask on the tensor cores: merges their contribution into (acc, l, m) in place.
+void attn_tile_fwd(Tensor q, Tensor k, Tensor v, Tensor rb_ids, Tensor rb_ptr, Tensor tile_cb, Tensor mask, OptT bias, Tensor acc,
+                   Tensor l, OptT m, int64_t H, int64_t score, int64_t norm, double scale, double lo, double hi, int64_t ldq, int64_t ldk,
+                   Tensor status, OptT dbg_s) {
+    c10::cuda::CUDAGuard guard(q.device());
+    TORCH_CHECK(q.is_cuda() && q.scalar_type() == torch::kBFloat16 && k.scalar_type() == torch::kBFloat16 && v.scalar_type() == torch::kBFloat16,
+                "bf16 CUDA operands expected");
+    TORCH_CHECK(mask.scalar_type() == torch::kUInt8 && mask.is_contiguous() && mask.dim() == 3 && mask.size(1) == 128 && mask.size(2) == 128,
+                "mask must be uint8 [n_tiles, 128, 128]");
+    TORCH_CHECK(tile_cb.numel() == mask.size(0) && rb_ptr.numel() == rb_ids.numel() + 1, "tile plan arrays do not match");
+    TORCH_CHECK(acc.scalar_type() == torch::kFloat32 && l.scalar_type() == torch::kFloat32 && acc.stride(-1) == 1 && l.stride(-1) == 1,
+                "fp32 partial results expected");
+    TORCH_CHECK(score == gt::SCORE_DOT || score == gt::SCORE_BIASED, "tile attention evaluates plain or biased dot-product scores");
+    gt::AttnTileArgs a{};
+    a.H = (int)H; a.T = bias.has_value() && bias->defined() ? (int)bias->size(0) : 1;
+    a.score = (int)score; a.norm = (int)norm; a.scale = (float)scale; a.lo = (float)lo; a.hi = (float)hi;
+    a.bias = cptr<float>(bias);
+    TORCH_CHECK(gt::attn_tile_supported(a.H, 32, a.T), "tile attention needs an even number of heads of 32 and at most 15 edge types");
+    a.n_rb = (int)rb_ids.numel(); a.rb_ids = rb_ids.data_ptr<int>(); a.rb_ptr = rb_ptr.data_ptr<int>();
+    a.tile_cb = tile_cb.data_ptr<int>(); a.mask = mask.data_ptr<unsigned char>();
+    a.n_rows = (int)q.size(0); a.n_cols = (int)k.size(0);
+    a.acc = acc.data_ptr<float>(); a.l = l.data_ptr<float>();
+    a.m = m.has_value() && m->defined() ? m->data_ptr<float>() : nullptr;
+    TORCH_CHECK(norm != gt::NORM_SOFTMAX || a.m != nullptr, "softmax partials need the row maxima");
+    a.acc_stride = acc.stride(0); a.l_stride = l.stride(0);
+    a.status = status.data_ptr<int>();
+    a.dbg_s = dbg_s.has_value() && dbg_s->defined() ? dbg_s->data_ptr<float>() : nullptr;
+    const int64_t hd = H * 32;
+    int rc = gt::attn_tile_fwd(a, q.data_ptr(), k.data_ptr(), v.data_ptr(), ldq ? ldq : hd, ldk ? ldk : hd, stream());
+    TORCH_CHECK(rc == 0, "tile attention launch failed with code ", rc);
+}
+
 int64_t attn_bwd_row_blocks(int64_t n_seg) { return gt::attn_bwd_row_blocks((int)n_seg); }
 
 void attn_bwd_row(Tensor q, Tensor k, Tensor v, Tensor row_vec, Tensor stat, Tensor idx, OptT etype, OptT gate, OptT bias,
@@ -649,6 +681,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("wait_flags", &wait_flags);
     m.def("group_barrier", &group_barrier);
     m.def("attn_status", &attn_status);
+    m.def("attn_tile_fwd", &attn_tile_fwd);
     m.def("channel_signal", &channel_signal);
     m.def("sum_payload", &sum_payload);
     m.def("pull_unpack", &pull_unpack);

@@ -28,6 +28,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "tc05.cuh"
 
 namespace gt {
 namespace {
@@ -35,125 +36,6 @@ namespace {
 constexpr int BM = 128, BN = 128, BK = 64, STAGES = 3;
 constexpr int kThreads = 192;
 constexpr uint32_t kTmemCols = 128;
-constexpr long long kWaitCycles = 2000000000LL;          // ~1 s at 2 GHz: a healthy pipeline waits microseconds
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait on an mbarrier phase.  Returns false when the CTA is aborting (or the limit expired, which raises the abort).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitCycles) {
-            *abort_flag = 1;
-            if (status) atomicExch(status, code);
-            return false;
-        }
-    }
-}
-
-__device__ __forceinline__ int ld_acquire_sys_s32(const int* p) {
-    int v;
-    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
-        : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-        "}\n" ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// arrive on an mbarrier once all previously issued MMAs of this thread have completed
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// eight fp32 values -> eight bf16 in one 16-byte store; takes the values by value so that the caller's accumulator array never
-// has its address taken (an escaped array is spilled to local memory at every asm statement with a memory clobber)
-__device__ __forceinline__ void st_bf16x8(void* p, float a0, float a1, float a2, float a3, float a4, float a5, float a6, float a7) {
-    uint4 u;
-    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
-    h[0] = __floats2bfloat162_rn(a0, a1);
-    h[1] = __floats2bfloat162_rn(a2, a3);
-    h[2] = __floats2bfloat162_rn(a4, a5);
-    h[3] = __floats2bfloat162_rn(a6, a7);
-    *reinterpret_cast<uint4*>(p) = u;
-}
-
-// shared-memory matrix descriptor of a 128-byte-swizzled operand tile
-//   K-major : rows of 128 bytes (64 bf16 along K), 8-row groups 1024 bytes apart (SBO), LBO unused (=1)
-//   MN-major: rows of 128 bytes (64 bf16 along M/N), 8 K-rows per 1024-byte group (SBO), 64-element MN blocks LBO bytes apart
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
-    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
-    d |= 1ull << 46;                                       // descriptor version of sm_100
-    d |= 2ull << 61;                                       // SWIZZLE_128B
-    return d;
-}
-
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n, int a_mn_major, int b_mn_major) {
-    return (1u << 4)                                       // D format fp32
-           | (1u << 7) | (1u << 10)                        // A, B format bf16
-           | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
 
 struct __align__(1024) SharedStorage {
     __nv_bfloat16 a[STAGES][BM * BK];                      // 16 KB per stage
@@ -371,9 +253,6 @@ struct __align__(1024) PersistentStorage {
     int abort_flag;
 };
 
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 
 __global__ void __launch_bounds__(kThreads, 1) gemm_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                          const __grid_constant__ CUtensorMap map_b, GemmArgs g) {
@@ -1179,6 +1058,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tn256_kernel(const __grid_co
     if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
+}  // namespace
+
 // ---- host side: tensor maps ------------------------------------------------------------------------------------------
 PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
     static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
@@ -1218,6 +1099,8 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, in
     cache[key] = *map;
     return true;
 }
+
+namespace {
 
 constexpr size_t kSmemBytes = sizeof(SharedStorage) + 1024;
 

@@ -87,6 +87,26 @@ void attn_fwd(const AttnFwdArgs& a, cudaStream_t s);
 void attn_bwd_row(const AttnBwdRowArgs& a, cudaStream_t s);
 void attn_bwd_col(const AttnBwdColArgs& a, cudaStream_t s);
 bool attn_shape_supported(int H, int D, int T);
+
+// Dense tiles of a block-sparse mask on the tensor cores (attn_tile.cu): adds the tiles' contribution to partial results.
+struct AttnTileArgs {
+    int H, T;               // heads (even, head dim 32), edge types (<= 15)
+    int score, norm;        // SCORE_DOT or SCORE_BIASED; either normalisation
+    float scale, lo, hi;
+    const float* bias;      // [T, H] fp32, nullable
+    int n_rb;               // row blocks (of 128 destinations) that own at least one tile
+    const int* rb_ids;      // [n_rb] row-block index
+    const int* rb_ptr;      // [n_rb + 1] range of tiles of every listed row block
+    const int* tile_cb;     // [n_tiles] column-block index (of 128 sources)
+    const unsigned char* mask;   // [n_tiles, 128, 128] edge type of (row, column), 255 = no edge
+    int n_rows, n_cols;
+    float* acc; float* l; float* m;      // partial results of the residual edges, updated in place (m only for softmax)
+    long long acc_stride, l_stride;
+    int* status;            // device status word of the bounded waits
+    float* dbg_s;           // nullable: raw scores of the first tile of CTA (0, 0), [2, 128, 128]
+};
+bool attn_tile_supported(int H, int D, int T);
+int attn_tile_fwd(const AttnTileArgs& a, const void* q, const void* k, const void* v, long long ldq, long long ldk, cudaStream_t s);
 struct KernelInfo { const char* name; int regs; int local_bytes; int static_smem; int dyn_smem; int blocks_per_sm; };
 std::vector<KernelInfo> attn_kernel_info();            // compiled resources of the main attention kernel instances
 int attn_status();                                     // nonzero once after a bounded copy wait of an attention kernel expired (synchronises)

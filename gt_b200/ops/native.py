@@ -90,7 +90,7 @@ def check_status(device=None):
     if code != 0:
         status(device).zero_()
         raise RuntimeError(f"gt_b200 kernel reported an expired wait (code {code}): "
-                           "1-3 GEMM producer/MMA/epilogue, 4-6 TN GEMM, 7 attention row copy, >=100 peer flag of rank code-100")
+                           "1-3 GEMM producer/MMA/epilogue, 4-6 TN GEMM, 7 attention row copy, 8-10 tile attention producer/MMA/softmax, >=100 peer flag of rank code-100")
 
 
 def rng_state(device=None):

@@ -168,9 +168,11 @@ def check_status_all_ranks(dev, world):
 def _auto_grid(args, world, n, e_graph, f_in, rank):
     """--grid_auto / --head_auto: the white-box model's choice for this world size."""
     from ..perf import grid_select as gs
-    e_attn = gs.attention_edges(n, e_graph, args.exp_deg)
-    graph = gs.Graph(n, e_attn, e_graph + n, f_in, name=args.graph_name or args.synthetic or "graph")
-    model = gs.Model(args.hidden or 256, args.heads or 8, args.layers or 4, bf16=args.bf16, with_gcn=not args.no_gcn)
+    token = bool(getattr(args, "virtual_node", False))
+    e_attn = gs.attention_edges(n, e_graph, args.exp_deg) + (2 * n if token else 0)
+    graph = gs.Graph(n, e_attn, e_graph + n, f_in, name=args.graph_name or args.synthetic or "graph", token=token)
+    model = gs.Model(args.hidden or 256, args.heads or 8, args.layers or 4, bf16=args.bf16, with_gcn=not args.no_gcn,
+                     transport=getattr(args, "comm", "nccl"))
     if args.head_auto:
         best = gs.select_layout(world, graph, model)
     else:

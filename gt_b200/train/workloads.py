@@ -13,7 +13,7 @@ from ..models.exphormer_dist import DistExphormer, gcn_edges_with_self_loops
 from ..models.exphormer_ref import ExphormerRef
 from ..parallel.grid import make_grid
 
-DEFAULT_GRIDS = {1: (1, 1), 2: (2, 1), 4: (2, 2), 8: (2, 4)}
+DEFAULT_GRIDS = {1: (1, 1), 2: (2, 1), 4: (2, 2), 8: (4, 2)}
 
 
 def pad_to(n, mult):
