@@ -2,8 +2,8 @@
 
     python -m gt_b200.bench.bench_attention_tiles --nodes 131072 --heads 16 --density 0.03 0.1 0.3
 
-Builds a clustered mask (communities of 128 nodes whose internal mask holds the given fraction of its entries, plus
-``--background`` random edges per row), and times the forward on (a) the gather kernels alone and (b) the density dispatch
+Builds a clustered mask (communities of ``--community`` nodes whose internal mask holds the given fraction of its entries,
+plus ``--background`` random edges per row), and times the forward on (a) the gather kernels alone and (b) the density dispatch
 (dense tiles on ``attn_tile_fwd_kernel``, residual on the gather kernels).  CUDA events, L2 flushed between timed launches.
 One ``TILE`` line per density: edges, tiles, ms of both paths, and the dense-tile product rate of the tile kernel
 (4 * 128 * 128 * 32 FLOP per tile and head for ``Q K^T`` and ``P V``).  ``--only tile`` runs path (b) alone (profiler captures).
@@ -14,13 +14,13 @@ import json
 import torch
 
 
-def clustered_block(n, density, background, types, dev, seed=0):
+def clustered_block(n, density, background, types, dev, seed=0, community=128):
     from ..attention import BlockCSR
     g = torch.Generator(device=dev).manual_seed(seed)
-    n_cl = n // 128
-    on = torch.rand(n_cl, 128, 128, device=dev, generator=g) < density
+    n_cl = n // community
+    on = torch.rand(n_cl, community, community, device=dev, generator=g) < density
     c, r, s = on.nonzero(as_tuple=True)
-    dst, src = c * 128 + r, c * 128 + s
+    dst, src = c * community + r, c * community + s
     if background:
         bd = torch.arange(n, device=dev).repeat_interleave(background)
         bs = torch.randint(0, n, (bd.numel(),), device=dev, generator=g)
@@ -37,6 +37,7 @@ def main():
     ap.add_argument("--heads", type=int, default=16)
     ap.add_argument("--density", type=float, nargs="+", default=[0.03, 0.1, 0.3])
     ap.add_argument("--background", type=int, default=4)
+    ap.add_argument("--community", type=int, default=128, help="nodes per community: community / 128 dense tiles per row block")
     ap.add_argument("--types", type=int, default=3)
     ap.add_argument("--score", default="biased", choices=["dot", "biased"])
     ap.add_argument("--norm", default="softmax", choices=["softmax", "clampexp"])
@@ -71,9 +72,9 @@ def main():
         return ms / args.iters
 
     for dens in args.density:
-        blk = clustered_block(n, dens, args.background, args.types, dev)
+        blk = clustered_block(n, dens, args.background, args.types, dev, community=args.community)
         plan = tl.build_tile_plan(blk, min_share=0.0)
-        out = dict(nodes=n, heads=h, density=dens, edges=blk.num_edges, tiles=plan.num_tiles if plan else 0,
+        out = dict(nodes=n, heads=h, density=dens, community=args.community, edges=blk.num_edges, tiles=plan.num_tiles if plan else 0,
                    tiled_edges=plan.num_tiled_edges if plan else 0)
         if args.only == "both":
             blk._cache["tile_plan"] = None
