@@ -222,3 +222,37 @@ def test_profile_exports_a_chrome_trace_for_analyze_trace(tmp_path, monkeypatch)
     assert path.exists()
     r = analyze(str(path))
     assert r["kernels"] == 0 or r["busy_ms"] > 0            # CPU run: a valid trace without GPU events
+
+
+# ---- sparse-collective diagnosis tools ------------------------------------------------------------------------------------
+
+def test_bench_sparse_accumulate_candidates_agree():
+    from gt_b200.bench.bench_sparse_accumulate import main
+    res = main(["--cases", "300:1:16", "200:3:8", "--iters", "1"])
+    assert len(res) == 2 and "index_copy_ms" in res[0] and "index_copy_ms" not in res[1]
+    assert all(r["index_add_ms"] > 0 and r["sort_segment_ms"] > 0 for r in res)
+
+
+def _profile_sparse_worker(rank, world):
+    from gt_b200.bench.profile_sparse_comm import main
+    res = main(["--rows", "512", "--width", "16", "--share", "0.3", "--iters", "1"])
+    assert res["gather_ms"] > 0 and res["reduce_ms"] > 0 and 0.2 < res["share"] < 0.4
+
+
+def test_profile_sparse_comm_on_gloo():
+    run_dist(_profile_sparse_worker, 2)
+
+
+def test_analyze_coll_tables(tmp_path, capsys):
+    import json
+    from gt_b200.bench.analyze_coll_tables import main
+    a = {"_world": 4, "coll": {"rs": [20.0, 300.0]}, "_coll_curves_mb_ms": {"rs": [[1.0, 0.02], [64.0, 0.25]], "ag": [[1.0, 0.01]]}}
+    b = {"_world": 8, "coll": {"rs": [30.0, 150.0]}, "_coll_curves_mb_ms": {"rs": [[64.0, 0.5]]}}
+    pa, pb = tmp_path / "a.json", tmp_path / "b.json"
+    pa.write_text(json.dumps(a)); pb.write_text(json.dumps(b))
+    out = main([str(pa), str(pb)])
+    assert set(out) == {"rs", "ag"}
+    assert out["rs"]["columns"] == ["a@4", "b@8"]
+    assert out["rs"]["rates"][64.0] == [round(64 * 2 ** 20 / 0.25e-3 / 1e9, 1), round(64 * 2 ** 20 / 0.5e-3 / 1e9, 1)]
+    assert out["rs"]["rates"][1.0][1] is None
+    assert "RS: GB/s" in capsys.readouterr().out
