@@ -13,6 +13,7 @@ Extra entry points:
 ``attn_fwd_partial_pull``    forward that fetches K / V rows from the owners' symmetric buffers over NVLink
 """
 import math
+import os
 
 import torch
 
@@ -172,7 +173,22 @@ def _pack_stat(m, row_bias, p_scale):
     return torch.stack([m.float(), row_bias.float(), ps.float(), z.float()], dim=-1).contiguous()
 
 
-def _bwd(q, k, v, blk, gate, bias, row_vec, stat, score, norm, clamp, scale, seg_edges):
+# Score gradients handed from the column pass to the row pass (fp32 [E, H]): the row pass then gathers K only.  GT_ATTN_DS=0
+# restores the independent passes; blocks whose buffer would exceed GT_ATTN_DS_MAX_MB (default 4096) keep them as well.
+_DS_ON = os.environ.get("GT_ATTN_DS", "1") != "0"
+_DS_MAX_BYTES = int(os.environ.get("GT_ATTN_DS_MAX_MB", "4096")) << 20
+
+
+def ds_buffer(blk, h, dtype, device):
+    """The hand-off buffer of a block, or ``None`` when the passes run independently."""
+    if not _DS_ON or dtype != torch.bfloat16 or blk.num_edges == 0 or blk.num_edges * h * 4 > _DS_MAX_BYTES:
+        return None
+    return torch.empty(blk.num_edges, h, dtype=torch.float32, device=device)
+
+
+def _bwd(q, k, v, blk, gate, bias, row_vec, stat, score, norm, clamp, scale, seg_edges, row_map=None, dq_accum=None, plan=None):
+    """Both backward passes.  ``row_map`` / ``dq_accum`` / ``plan``: the compact-accumulate row pass (rows of the plan are
+    ``row_map``; dq is added into the fp32 ``dq_accum``)."""
     n, h, d = q.shape
     nc = k.shape[0]
     e = native.ext()
@@ -180,16 +196,24 @@ def _bwd(q, k, v, blk, gate, bias, row_vec, stat, score, norm, clamp, scale, seg
     g, b = _tables(gate, bias, score)
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     rv = row_vec.to(q.dtype).contiguous()
+    ds = ds_buffer(blk, h, q.dtype, q.device)
+    # column pass over the transposed structure (first: it leaves the score gradients for the row pass)
+    _, rowidx, et_t, pos, _ = blk.csc()
+    cplan = blk.col_plan(seg_edges)
+    dk, dv = torch.empty(nc, h, d, dtype=q.dtype, device=q.device), torch.empty(nc, h, d, dtype=q.dtype, device=q.device)
+    cscratch = torch.empty(cplan.num_slots, 2 * h * d, dtype=torch.float32, device=q.device) if cplan.num_slots else None
+    e.attn_bwd_col(q, k, v, rv, stat, rowidx, et_t, g, b, _plan_list(cplan), dk, dv, cscratch, h, d, sc, nm, scale, lo, hi, 0, 0, 0, 0,
+                   ds, pos if ds is not None else None)
     # row pass
-    plan = blk.row_plan(seg_edges)
+    plan = plan if plan is not None else blk.row_plan(seg_edges)
     nb = e.attn_bwd_row_blocks(plan.num_segments)
-    dq = torch.empty_like(q)
+    dq = torch.empty_like(q) if dq_accum is None else dq_accum
     t = g.shape[0] if g is not None else (b.shape[0] if b is not None else 0)
     dgp = torch.empty(nb, t * h * d, dtype=torch.float32, device=q.device) if g is not None else None
     dbp = torch.empty(nb, t * h, dtype=torch.float32, device=q.device) if b is not None else None
     scratch = torch.empty(plan.num_slots, h * d, dtype=torch.float32, device=q.device) if plan.num_slots else None
-    e.attn_bwd_row(q, k, v, rv, stat, blk.col, blk.etype, g, b, _plan_list(plan), None, dq, False, dgp, dbp, nb, scratch,
-                   h, d, sc, nm, scale, lo, hi, 0, 0, 0, 0)
+    e.attn_bwd_row(q, k, v, rv, stat, blk.col, blk.etype, g, b, _plan_list(plan), row_map, dq, dq_accum is not None, dgp, dbp, nb, scratch,
+                   h, d, sc, nm, scale, lo, hi, 0, 0, 0, 0, ds)
     dgate = dbias = None
     if g is not None:
         dgate = torch.empty(t * h * d, dtype=torch.float32, device=q.device)
@@ -199,12 +223,6 @@ def _bwd(q, k, v, blk, gate, bias, row_vec, stat, score, norm, clamp, scale, seg
         dbias = torch.empty(t * h, dtype=torch.float32, device=q.device)
         e.reduce_partials(dbp, dbias, False)
         dbias = dbias.view(t, h)
-    # column pass over the transposed structure
-    _, rowidx, et_t, _, _ = blk.csc()
-    cplan = blk.col_plan(seg_edges)
-    dk, dv = torch.empty(nc, h, d, dtype=q.dtype, device=q.device), torch.empty(nc, h, d, dtype=q.dtype, device=q.device)
-    cscratch = torch.empty(cplan.num_slots, 2 * h * d, dtype=torch.float32, device=q.device) if cplan.num_slots else None
-    e.attn_bwd_col(q, k, v, rv, stat, rowidx, et_t, g, b, _plan_list(cplan), dk, dv, cscratch, h, d, sc, nm, scale, lo, hi, 0, 0, 0, 0)
     return dq, dk, dv, dgate, dbias
 
 
@@ -225,35 +243,9 @@ def attn_bwd_partial_accum(q, k, v, blk: BlockCSR, gate, bias, m, dacc, dl, dq_a
                                                     seg_edges=seg_edges)
         dq_accum += dq.reshape(dq_accum.shape).to(dq_accum.dtype)
         return dk, dv, dgate, dbias
-    e = native.ext()
-    sc, nm, scale, lo, hi = _cfg(q, score, norm, clamp, scale)
-    g, b = _tables(gate, bias, score)
-    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-    rv = dacc.reshape(q.shape).to(q.dtype).contiguous()
-    stat = _pack_stat(m, dl, None)
     plan, rows = _dcsr_plan(blk, seg_edges)
-    nb = e.attn_bwd_row_blocks(plan.num_segments)
-    t = g.shape[0] if g is not None else (b.shape[0] if b is not None else 0)
-    dgp = torch.empty(nb, t * h * d, dtype=torch.float32, device=q.device) if g is not None else None
-    dbp = torch.empty(nb, t * h, dtype=torch.float32, device=q.device) if b is not None else None
-    scratch = torch.empty(plan.num_slots, h * d, dtype=torch.float32, device=q.device) if plan.num_slots else None
-    e.attn_bwd_row(q, k, v, rv, stat, blk.col, blk.etype, g, b, _plan_list(plan), rows, dq_accum, True, dgp, dbp, nb, scratch,
-                   h, d, sc, nm, scale, lo, hi, 0, 0, 0, 0)
-    dgate = dbias = None
-    if g is not None:
-        dgate = torch.empty(t * h * d, dtype=torch.float32, device=q.device)
-        e.reduce_partials(dgp, dgate, False)
-        dgate = dgate.view(t, h, d)
-    if b is not None:
-        dbias = torch.empty(t * h, dtype=torch.float32, device=q.device)
-        e.reduce_partials(dbp, dbias, False)
-        dbias = dbias.view(t, h)
-    nc = k.shape[0]
-    _, rowidx, et_t, _, _ = blk.csc()
-    cplan = blk.col_plan(seg_edges)
-    dk, dv = torch.empty(nc, h, d, dtype=q.dtype, device=q.device), torch.empty(nc, h, d, dtype=q.dtype, device=q.device)
-    cscratch = torch.empty(cplan.num_slots, 2 * h * d, dtype=torch.float32, device=q.device) if cplan.num_slots else None
-    e.attn_bwd_col(q, k, v, rv, stat, rowidx, et_t, g, b, _plan_list(cplan), dk, dv, cscratch, h, d, sc, nm, scale, lo, hi, 0, 0, 0, 0)
+    _, dk, dv, dgate, dbias = _bwd(q, k, v, blk, gate, bias, dacc.reshape(q.shape), _pack_stat(m, dl, None), score, norm, clamp, scale, seg_edges,
+                                   row_map=rows, dq_accum=dq_accum, plan=plan)
     return dk, dv, dgate, dbias
 
 

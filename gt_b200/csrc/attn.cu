@@ -921,6 +921,223 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 5 : 
     for (int i = threadIdx.x; i < acc_n; i += blockDim.x) part[i] = s_dg[i];
 }
 
+// End of a run of edges of one type in the K-only row pass: dq += g_t * A, and the gate gradient q * A goes into per-warp
+// REGISTER accumulators (one set per type, selected by a warp-uniform switch, so every index is static): the shared-memory
+// atomics of flush_type_run cost about as much as the whole K gather once the rest of the per-edge work is gone.
+template <int CPL>
+__device__ __forceinline__ void flush_type_run_regs(const float* s_gate, int t, int HD, const int (&foff)[CPL], const float (&qf)[CPL][8],
+                                                    float (&A)[CPL][8], float (&dqa)[CPL][8], float (&dg)[kMaxTypesReg][CPL][8], bool want_dg) {
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) {
+        const float* g = s_gate + t * HD + foff[i];
+#pragma unroll
+        for (int x = 0; x < 8; ++x) dqa[i][x] = fmaf(g[x], A[i][x], dqa[i][x]);
+    }
+    if (want_dg) {
+        switch (t) {
+#define GT_DG_CASE(TT)                                                                      \
+    case TT:                                                                                \
+        _Pragma("unroll") for (int i = 0; i < CPL; ++i)                                     \
+            _Pragma("unroll") for (int x = 0; x < 8; ++x) dg[TT][i][x] = fmaf(qf[i][x], A[i][x], dg[TT][i][x]); \
+        break;
+            GT_DG_CASE(0) GT_DG_CASE(1) GT_DG_CASE(2) GT_DG_CASE(3)
+#undef GT_DG_CASE
+            default: break;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < CPL; ++i)
+#pragma unroll
+        for (int x = 0; x < 8; ++x) A[i][x] = 0.f;
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// backward, row pass from stored score gradients.  When the column pass ran first and left ds of every entry in CSR order,
+// dq_i = scale * sum_t g_t * sum_{edges of type t} ds_ij k_j needs one gathered K row and H floats per edge: no V gather, no
+// dot products, no exponentials (the full row pass above recomputes all of them).  Same outputs as attn_bwd_row_kernel.
+// ------------------------------------------------------------------------------------------------------------------
+template <typename T, int CPL, bool GATED, int SPEC = 0>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (GATED ? 5 : 6) : 3)) attn_bwd_row_ds_kernel(AttnBwdRowArgs a) {
+    extern __shared__ float smem[];
+    const AttnCommon& c = a.c;
+    const int H = SPEC ? SPEC : c.H, D = SPEC ? 32 : c.D, HD = H * D;
+    float* s_gate = smem;
+    float* s_bias = smem + (c.score == SCORE_GATED ? c.T * HD : 0);
+    float* s_dg = s_bias + (c.score == SCORE_BIASED ? c.T * H : 0);      // [T, HD] or [T, H] block accumulators
+    load_tables(c, s_gate, s_bias);
+    const bool want_dg = GATED && a.dgate_part;
+    const bool want_db = c.score == SCORE_BIASED && a.dbias_part;
+    const int acc_n = want_dg ? c.T * HD : (want_db ? c.T * H : 0);
+    for (int i = threadIdx.x; i < acc_n; i += blockDim.x) s_dg[i] = 0.f;
+    __syncthreads();
+    const Lanes L = make_lanes(HD, D);
+    const size_t ldq = c.ldq ? (size_t)c.ldq : (size_t)HD, ldk = c.ldk ? (size_t)c.ldk : (size_t)HD;
+    const size_t ldo = c.ldo ? (size_t)c.ldo : (size_t)HD;
+    const T* q = static_cast<const T*>(a.q);
+    const T* kb = static_cast<const T*>(a.k);
+    const bool head_writer = (L.ll & (L.lph - 1)) == 0;
+    using Raw = typename Vec8<T>::Raw;
+    constexpr int U = kUnrollRow;
+    constexpr int NST = kAsyncStages;
+    constexpr int NT = kWarpsPerBlock * 32;
+    // per-thread rings: K chunks, then the score gradients, then the edge types of the groups in flight
+    uint4* ring = reinterpret_cast<uint4*>(smem + ((table_floats(c) + acc_n + 3) & ~3));
+    float* dring = reinterpret_cast<float*>(ring + (size_t)NST * U * CPL * NT);
+    int* tring = reinterpret_cast<int*>(dring + (size_t)NST * U * CPL * NT);
+
+    int foff[CPL], head[CPL];
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) { foff[i] = (L.ll + L.lpr * i) << 3; head[i] = foff[i] / D; }
+
+    float dg[kMaxTypesReg][CPL][8];                     // gate gradient of this warp's rows, per type (gated scores only)
+#pragma unroll
+    for (int tt = 0; tt < kMaxTypesReg; ++tt)
+#pragma unroll
+        for (int i = 0; i < CPL; ++i)
+#pragma unroll
+            for (int x = 0; x < 8; ++x) dg[tt][i][x] = 0.f;
+
+    const int n_warps = gridDim.x * kWarpsPerBlock;
+    for (int seg = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); seg < c.plan.n_seg; seg += n_warps) {
+        const int row = c.plan.seg_row[seg], beg = c.plan.seg_beg[seg], end = c.plan.seg_end[seg];
+        const int slot = c.plan.seg_slot[seg];
+        const long long srow = a.row_map ? a.row_map[row] : row;
+        float qf[CPL][8], A[CPL][8], dqa[CPL][8], db[kMaxTypesReg][CPL];
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) {
+            if (want_dg) {
+                Vec8<T>::load(q + srow * ldq + foff[i], qf[i]);
+#pragma unroll
+                for (int x = 0; x < 8; ++x) qf[i][x] *= c.scale;
+            } else {
+#pragma unroll
+                for (int x = 0; x < 8; ++x) qf[i][x] = 0.f;
+            }
+#pragma unroll
+            for (int x = 0; x < 8; ++x) { A[i][x] = 0.f; dqa[i][x] = 0.f; }
+#pragma unroll
+            for (int tt = 0; tt < kMaxTypesReg; ++tt) db[tt][i] = 0.f;
+        }
+        int gt_cached = -1;
+        const int n_it = (end - beg + U * L.epw - 1) / (U * L.epw);
+        int jn[U], tn[U], en[U];
+        auto fetch = [&](int g) {                       // column / type of edge group g, one iteration ahead of issue(g)
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                en[u] = min(beg + (g * U + u) * L.epw + L.sub, end - 1);        // padding slots reuse the last edge; their weight is zeroed
+                jn[u] = c.idx[en[u]];
+                tn[u] = c.etype ? c.etype[en[u]] : 0;
+            }
+        };
+        auto issue = [&](int g) {                       // start the copies of edge group g (one commit group per call)
+            if (g < n_it) {
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+#pragma unroll
+                    for (int i = 0; i < CPL; ++i) {
+                        const int slot_i = (((g % NST) * U + u) * CPL + i) * NT + threadIdx.x;
+                        cp_async16<true>(ring + slot_i, kb + (size_t)jn[u] * ldk + foff[i]);
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dring + slot_i)),
+                                     "l"(a.ds_in + (size_t)en[u] * H + head[i])
+                                     : "memory");
+                    }
+                    tring[((g % NST) * U + u) * NT + threadIdx.x] = tn[u];
+                }
+                if (g + 1 < n_it) fetch(g + 1);
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        if (n_it > 0) fetch(0);
+#pragma unroll
+        for (int it = 0; it < NST - 1; ++it) issue(it);
+        for (int it = 0; it < n_it; ++it) {
+            const int base = beg + it * U * L.epw;
+            issue(it + NST - 1);
+            asm volatile("cp.async.wait_group %0;" ::"n"(NST - 1) : "memory");
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const bool ok = base + u * L.epw + L.sub < end;
+                const int t = tring[((it % NST) * U + u) * NT + threadIdx.x];
+                if (GATED && ok && t != gt_cached) {                    // edges of a row are grouped by type: a run ends (rare)
+                    if (gt_cached >= 0) flush_type_run_regs<CPL>(s_gate, gt_cached, HD, foff, qf, A, dqa, dg, want_dg);
+                    gt_cached = t;
+                }
+#pragma unroll
+                for (int i = 0; i < CPL; ++i) {
+                    const int slot_i = (((it % NST) * U + u) * CPL + i) * NT + threadIdx.x;
+                    float kf[8];
+                    Vec8<T>::unpack(as_raw<T>(ring[slot_i]), kf);
+                    const float ds = ok ? dring[slot_i] : 0.f;
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) A[i][x] = fmaf(ds, kf[x], A[i][x]);
+                    if (!GATED && want_db) {
+#pragma unroll
+                        for (int tt = 0; tt < kMaxTypesReg; ++tt)
+                            if (t == tt) db[tt][i] += ds;
+                    }
+                }
+            }
+        }
+        if (GATED) {
+            if (gt_cached >= 0) flush_type_run_regs<CPL>(s_gate, gt_cached, HD, foff, qf, A, dqa, dg, want_dg);
+        } else {
+#pragma unroll
+            for (int i = 0; i < CPL; ++i)
+#pragma unroll
+                for (int x = 0; x < 8; ++x) dqa[i][x] = A[i][x];
+        }
+        for (int off = L.lpr; off < 32; off <<= 1) {    // merge the edge slots of the warp
+#pragma unroll
+            for (int i = 0; i < CPL; ++i)
+#pragma unroll
+                for (int x = 0; x < 8; ++x) dqa[i][x] += __shfl_xor_sync(GT_FULL_MASK, dqa[i][x], off);
+            if (want_db) {
+#pragma unroll
+                for (int tt = 0; tt < kMaxTypesReg; ++tt)
+#pragma unroll
+                    for (int i = 0; i < CPL; ++i) db[tt][i] += __shfl_xor_sync(GT_FULL_MASK, db[tt][i], off);
+            }
+        }
+        if (L.sub != 0) continue;
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) {
+            float dq[8];
+#pragma unroll
+            for (int x = 0; x < 8; ++x) dq[x] = dqa[i][x] * c.scale;
+            if (!GATED && want_db && head_writer) {
+#pragma unroll
+                for (int tt = 0; tt < kMaxTypesReg; ++tt)
+                    if (tt < c.T) atomicAdd(&s_dg[tt * H + head[i]], db[tt][i]);
+            }
+            if (slot >= 0) {
+                Vec8<float>::store(c.scratch + (size_t)slot * HD + foff[i], dq);
+            } else if (a.accumulate_dq) {
+                float* dst = static_cast<float*>(a.dq) + srow * ldo + foff[i];
+                float old[8];
+                Vec8<float>::load(dst, old);
+#pragma unroll
+                for (int x = 0; x < 8; ++x) old[x] += dq[x];
+                Vec8<float>::store(dst, old);
+            } else {
+                Vec8<T>::store(static_cast<T*>(a.dq) + srow * ldo + foff[i], dq);
+            }
+        }
+    }
+    if (want_dg) {                                      // one shared-memory reduction per warp and kernel instead of one per row and type
+#pragma unroll
+        for (int tt = 0; tt < kMaxTypesReg; ++tt)
+            if (tt < c.T) {
+#pragma unroll
+                for (int i = 0; i < CPL; ++i)
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) atomicAdd(&s_dg[tt * HD + foff[i] + x], dg[tt][i][x]);
+            }
+    }
+    __syncthreads();
+    float* part = want_dg ? a.dgate_part + (size_t)blockIdx.x * acc_n : (want_db ? a.dbias_part + (size_t)blockIdx.x * acc_n : nullptr);
+    for (int i = threadIdx.x; i < acc_n; i += blockDim.x) part[i] = s_dg[i];
+}
+
 // out[row] (+)= sum of the row's slots; grid (split rows, 32-column groups), block (32, 8)
 template <typename T>
 __global__ void sum_slots_kernel(const SegPlan plan, const float* scratch, int width, const int* row_map, T* out, float* out_f32,
@@ -1077,6 +1294,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 4 : 
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const bool ok = r[u] >= 0;
+                // CSR position of this entry, for the score gradients handed to the row pass (loaded ahead of the arithmetic)
+                const int pe = (a.ds_out != nullptr && ok) ? a.pos[base + u * L.epw + L.sub] : 0;
                 if (c.score == SCORE_GATED && t[u] != gt_cached) {      // a column's entries are grouped by type: rare reload
                     gt_cached = t[u];
 #pragma unroll
@@ -1115,7 +1334,9 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (ASYNC ? 4 : 
                         mask = (s >= c.lo && s <= c.hi) ? 1.f : 0.f;
                     }
                     const float P = ok ? p * st[u][i].z : 0.f;
-                    const float ds = P * (dp + st[u][i].y) * mask * c.scale;
+                    const float ds0 = P * (dp + st[u][i].y) * mask;
+                    const float ds = ds0 * c.scale;
+                    if (a.ds_out != nullptr && ok && (foff[i] % D) == 0) a.ds_out[(size_t)pe * H + head[i]] = ds0;
 #pragma unroll
                     for (int x = 0; x < 8; ++x) dv[i][x] = fmaf(P, rv[x], dv[i][x]);
                     if (c.score == SCORE_GATED) {
@@ -1350,6 +1571,32 @@ void attn_bwd_row(const AttnBwdRowArgs& a_in, cudaStream_t s) {
                 a.accumulate_dq, c.ldo ? c.ldo : HD);                                    \
     } while (0)
     const int spec = spec_heads(c.H, c.D);
+    if (a.ds_in != nullptr && c.dtype == DT_BF16) {
+        // the column pass ran first and left the score gradients: K-only row pass
+        const size_t ring_ds = (size_t)kAsyncStages * kUnrollRow * (cpl * (16 + 4) + 4) * kWarpsPerBlock * 32;
+        const size_t smd = ((sm + 15) & ~size_t(15)) + ring_ds;
+#define GT_LAUNCH_ROW_DS(CPL, SP)                                                                              \
+    do {                                                                                                       \
+        if (c.score == SCORE_GATED) {                                                                          \
+            set_smem(attn_bwd_row_ds_kernel<__nv_bfloat16, CPL, true, SP>, smd);                               \
+            attn_bwd_row_ds_kernel<__nv_bfloat16, CPL, true, SP><<<blocks, kWarpsPerBlock * 32, smd, s>>>(a);  \
+        } else {                                                                                               \
+            set_smem(attn_bwd_row_ds_kernel<__nv_bfloat16, CPL, false, SP>, smd);                              \
+            attn_bwd_row_ds_kernel<__nv_bfloat16, CPL, false, SP><<<blocks, kWarpsPerBlock * 32, smd, s>>>(a); \
+        }                                                                                                      \
+    } while (0)
+        if (cpl == 1 && spec == 8) GT_LAUNCH_ROW_DS(1, 8);
+        else if (cpl == 1 && spec == 4) GT_LAUNCH_ROW_DS(1, 4);
+        else if (cpl == 1) GT_LAUNCH_ROW_DS(1, 0);
+        else if (spec == 16) GT_LAUNCH_ROW_DS(2, 16);
+        else GT_LAUNCH_ROW_DS(2, 0);
+#undef GT_LAUNCH_ROW_DS
+        if (c.plan.n_split > 0)
+            sum_slots_kernel<__nv_bfloat16><<<dim3(c.plan.n_split, (HD + 31) / 32), dim3(32, 8), 0, s>>>(
+                c.plan, c.scratch, HD, a.row_map, a.accumulate_dq ? nullptr : static_cast<__nv_bfloat16*>(a.dq),
+                a.accumulate_dq ? static_cast<float*>(a.dq) : nullptr, a.accumulate_dq, c.ldo ? c.ldo : HD);
+        return;
+    }
     if (hl_cfg().ch[1] && hl::shape_ok(c)) {
         constexpr int NST = 3;
         const int ch = hl_cfg().ch[1];
@@ -1406,7 +1653,7 @@ void attn_bwd_col(const AttnBwdColArgs& a_in, cudaStream_t s) {
                                                                    static_cast<TT*>(a.dv), c.ldo ? c.ldo : HD);          \
     } while (0)
     const int spec = spec_heads(c.H, c.D);
-    if (hl_cfg().ch[2] && hl::shape_ok(c)) {
+    if (hl_cfg().ch[2] && hl::shape_ok(c) && a.ds_out == nullptr) {      // the head-lane column kernel does not store score gradients
         constexpr int NST = 3;
         const int ch = hl_cfg().ch[2];
         const size_t ring = (size_t)NST * ((2 * ch + 1) * 16 + 4) * hl::kThreads;

@@ -127,9 +127,12 @@ int64_t attn_bwd_row_blocks(int64_t n_seg) { return gt::attn_bwd_row_blocks((int
 void attn_bwd_row(Tensor q, Tensor k, Tensor v, Tensor row_vec, Tensor stat, Tensor idx, OptT etype, OptT gate, OptT bias,
                   std::vector<Tensor> plan, OptT row_map, Tensor dq, bool accumulate_dq, OptT dgate_part, OptT dbias_part,
                   int64_t n_blocks, OptT scratch, int64_t H, int64_t D, int64_t score, int64_t norm, double scale, double lo, double hi,
-                  int64_t ldq, int64_t ldk, int64_t ldr, int64_t ldo) {
+                  int64_t ldq, int64_t ldk, int64_t ldr, int64_t ldo, OptT ds_in) {
     c10::cuda::CUDAGuard guard(q.device());
     gt::AttnBwdRowArgs a{};
+    a.ds_in = cptr<float>(ds_in);
+    if (a.ds_in) TORCH_CHECK(ds_in->scalar_type() == torch::kFloat32 && ds_in->is_contiguous() && ds_in->numel() == idx.numel() * H,
+                             "ds_in must be a contiguous fp32 [E, H] tensor");
     a.c = make_common(q, H, D, idx, etype, gate, bias, plan, scratch, score, norm, scale, lo, hi);
     a.c.ldq = ldq; a.c.ldk = ldk; a.c.ldr = ldr; a.c.ldo = ldo;
     TORCH_CHECK(ldq % 8 == 0 && ldk % 8 == 0 && ldr % 8 == 0 && ldo % 8 == 0, "row strides must be multiples of 8 elements");
@@ -146,9 +149,13 @@ void attn_bwd_row(Tensor q, Tensor k, Tensor v, Tensor row_vec, Tensor stat, Ten
 
 void attn_bwd_col(Tensor q, Tensor k, Tensor v, Tensor row_vec, Tensor stat, Tensor rowidx, OptT etype_t, OptT gate, OptT bias,
                   std::vector<Tensor> plan, Tensor dk, Tensor dv, OptT scratch, int64_t H, int64_t D, int64_t score, int64_t norm,
-                  double scale, double lo, double hi, int64_t ldq, int64_t ldk, int64_t ldr, int64_t ldo) {
+                  double scale, double lo, double hi, int64_t ldq, int64_t ldk, int64_t ldr, int64_t ldo, OptT ds_out, OptT pos) {
     c10::cuda::CUDAGuard guard(q.device());
     gt::AttnBwdColArgs a{};
+    a.ds_out = ds_out.has_value() && ds_out->defined() ? ds_out->data_ptr<float>() : nullptr;
+    a.pos = cptr<int>(pos);
+    if (a.ds_out) TORCH_CHECK(a.pos != nullptr && ds_out->is_contiguous() && ds_out->numel() == rowidx.numel() * H && pos->numel() == rowidx.numel(),
+                              "ds_out must be a contiguous fp32 [E, H] tensor and pos the CSR position of every CSC entry");
     a.c = make_common(q, H, D, rowidx, etype_t, gate, bias, plan, scratch, score, norm, scale, lo, hi);
     a.c.ldq = ldq; a.c.ldk = ldk; a.c.ldr = ldr; a.c.ldo = ldo;
     TORCH_CHECK(ldq % 8 == 0 && ldk % 8 == 0 && ldr % 8 == 0 && ldo % 8 == 0, "row strides must be multiples of 8 elements");

@@ -72,6 +72,9 @@ struct AttnBwdRowArgs {
     float* dgate_part;      // [n_blocks, T, H*D] per-block partial sums (nullable)
     float* dbias_part;      // [n_blocks, T, H]   (nullable)
     int n_blocks;           // grid size the partial buffers were sized for
+    // nullable: [E, H] fp32 score gradients per CSR entry, written by a column pass that ran first.  The row pass then only
+    // gathers K rows and accumulates dq += ds * k (no V gather, no recomputation of the weights); v / row_vec / stat are unused.
+    const float* ds_in;
 };
 
 struct AttnBwdColArgs {
@@ -80,6 +83,10 @@ struct AttnBwdColArgs {
     const void* row_vec;
     const float4* stat;
     void* dk; void* dv;     // [n_cols, H*D] dtype
+    // nullable pair: the pass stores the score gradient of every entry (before the scale factor) at ds_out[pos[e] * H + head],
+    // pos = CSR position of CSC entry e, for a row pass that runs afterwards (AttnBwdRowArgs::ds_in)
+    float* ds_out;
+    const int* pos;
 };
 
 int attn_scratch_width_fwd(int H, int D);              // floats per forward slot

@@ -257,22 +257,24 @@ class _FusedBranch(torch.autograd.Function):
             ldo_kv, ldo_q = n_kvg, d
             q_v = qbuf
         k_v, v_v = kvg[:, :d], kvg[:, d:2 * d]
-        # row pass: dq and the gate gradient
+        # column pass first: dk | dv into the first two column groups of dkvg, and the score gradient of every edge for the row pass
+        from ..attention.backend_cuda import ds_buffer
+        ds = ds_buffer(blk, h, torch.bfloat16, dev)
+        _, rowidx, et_t, pos, _ = blk.csc()
+        cplan = blk.col_plan(SEG_EDGES)
+        cscratch = torch.empty(cplan.num_slots, 2 * hd, dtype=torch.float32, device=dev) if cplan.num_slots else None
+        e.attn_bwd_col(q_v, k_v, v_v, row_vec, stat, rowidx, et_t, gate_c, None, _plan_list(cplan), dkvg, dkvg[:, d:2 * d], cscratch,
+                       h, dh, sc, nm, scale, lo, hi, ldq, ldk, 0, ldo_kv, ds, pos if ds is not None else None)
+        # row pass: dq and the gate gradient (K-only when the score gradients were handed over)
         plan = blk.row_plan(SEG_EDGES)
         nb = e.attn_bwd_row_blocks(plan.num_segments)
         t = gate_c.shape[0]
         dgp = torch.empty(nb, t * hd, dtype=torch.float32, device=dev)
         scratch = torch.empty(plan.num_slots, hd, dtype=torch.float32, device=dev) if plan.num_slots else None
         e.attn_bwd_row(q_v, k_v, v_v, row_vec, stat, blk.col, blk.etype, gate_c, None, _plan_list(plan), None, dq, False, dgp, None, nb, scratch,
-                       h, dh, sc, nm, scale, lo, hi, ldq, ldk, 0, ldo_q)
+                       h, dh, sc, nm, scale, lo, hi, ldq, ldk, 0, ldo_q, ds)
         dgate = torch.empty(t * hd, dtype=torch.float32, device=dev)
         e.reduce_partials(dgp, dgate, False)
-        # column pass: dk | dv into the first two column groups of dkvg
-        _, rowidx, et_t, _, _ = blk.csc()
-        cplan = blk.col_plan(SEG_EDGES)
-        cscratch = torch.empty(cplan.num_slots, 2 * hd, dtype=torch.float32, device=dev) if cplan.num_slots else None
-        e.attn_bwd_col(q_v, k_v, v_v, row_vec, stat, rowidx, et_t, gate_c, None, _plan_list(cplan), dkvg, dkvg[:, d:2 * d], cscratch,
-                       h, dh, sc, nm, scale, lo, hi, ldq, ldk, 0, ldo_kv)
         if with_gcn:
             gm = layer.gcn_block.matrix(torch.bfloat16, dev)
             ptr, idx, _, _, w_t = gm.csc()

@@ -22,3 +22,18 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_sessionfinish(session, exitstatus):
+    """In-process tests may leave a default process group behind; tear it down (bounded) so the interpreter exits cleanly."""
+    try:
+        import threading
+
+        import torch.distributed as dist
+        if not (dist.is_available() and dist.is_initialized()):
+            return
+        th = threading.Thread(target=dist.destroy_process_group, daemon=True)
+        th.start()
+        th.join(timeout=10.0)
+    except Exception:
+        pass
