@@ -138,6 +138,21 @@ def run_ours(args):
         m_dev.copy_(m_host, non_blocking=True)
         return float(eng.train_step(loss_fn))             # device -> host read of the step's loss
 
+    if args.e2e_prefetch:
+        # opt-in: the same per-step transfers through the package's input pipeline (copy stream + staging buffers, loss read one
+        # step later); the static tensors of the captured step are refreshed device-to-device
+        from gt_b200.train.prefetch import AsyncScalar, InputPrefetcher
+        pre = InputPrefetcher({"x": x_host, "y": y_host, "m": m_host}, dev)
+        ring = AsyncScalar(dev)
+
+        def step_e2e():                                   # noqa: F811
+            st = pre.next()
+            x_dev.copy_(st["x"], non_blocking=True)
+            y_dev.copy_(st["y"], non_blocking=True)
+            m_dev.copy_(st["m"], non_blocking=True)
+            ring.push(eng.train_step(loss_fn))
+            return ring.pop_previous()
+
     # warm-up (includes CUDA-graph capture); the launch census is taken on one of these steps
     for i in range(max(args.warmup, 3)):
         before = native.launch_count()
@@ -245,13 +260,15 @@ def finish(dist, release=()):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--e2e_prefetch", action="store_true",
+                    help="end-to-end loop with the input pipeline of gt_b200.train.prefetch (default: copies and loss read on the step's stream)")
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--comm", default="p2p", choices=["nccl", "p2p"], help="grid collectives: NCCL or the package's peer-memory kernels")
     ap.add_argument("--heap_mb", type=int, default=2048)
     ap.add_argument("--grid", type=int, nargs="+", default=None, metavar="P",
-                    help="process grid P_d P_o (default: 1x1, 2x1, 2x2, 2x4 for 1, 2, 4, 8 GPUs); used by the grid-ranking measurements")
+                    help="process grid P_d P_o (default: 1x1, 2x1, 2x2, 4x2 for 1, 2, 4, 8 GPUs); used by the grid-ranking measurements")
     ap.add_argument("--no_graph", action="store_true", help="run the step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--profile", default=None, metavar="PREFIX",
                     help="after timing, write the per-kernel device time of one more step to PREFIX.rank<r>.txt (not part of the timed region)")

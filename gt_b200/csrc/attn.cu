@@ -956,8 +956,8 @@ __device__ __forceinline__ void flush_type_run_regs(const float* s_gate, int t, 
 // dq_i = scale * sum_t g_t * sum_{edges of type t} ds_ij k_j needs one gathered K row and H floats per edge: no V gather, no
 // dot products, no exponentials (the full row pass above recomputes all of them).  Same outputs as attn_bwd_row_kernel.
 // ------------------------------------------------------------------------------------------------------------------
-template <typename T, int CPL, bool GATED, int SPEC = 0>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (GATED ? 5 : 6) : 3)) attn_bwd_row_ds_kernel(AttnBwdRowArgs a) {
+template <typename T, int CPL, bool GATED, int SPEC = 0, int UU = kUnrollRow, int NSTG = kAsyncStages, int MINB = (CPL == 1 ? (GATED ? 5 : 6) : 3)>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, MINB) attn_bwd_row_ds_kernel(AttnBwdRowArgs a) {
     extern __shared__ float smem[];
     const AttnCommon& c = a.c;
     const int H = SPEC ? SPEC : c.H, D = SPEC ? 32 : c.D, HD = H * D;
@@ -977,8 +977,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, (CPL == 1 ? (GATED ? 5 : 
     const T* kb = static_cast<const T*>(a.k);
     const bool head_writer = (L.ll & (L.lph - 1)) == 0;
     using Raw = typename Vec8<T>::Raw;
-    constexpr int U = kUnrollRow;
-    constexpr int NST = kAsyncStages;
+    constexpr int U = UU;
+    constexpr int NST = NSTG;
     constexpr int NT = kWarpsPerBlock * 32;
     // per-thread rings: K chunks, then the score gradients, then the edge types of the groups in flight
     uint4* ring = reinterpret_cast<uint4*>(smem + ((table_floats(c) + acc_n + 3) & ~3));
@@ -1585,7 +1585,14 @@ void attn_bwd_row(const AttnBwdRowArgs& a_in, cudaStream_t s) {
             attn_bwd_row_ds_kernel<__nv_bfloat16, CPL, false, SP><<<blocks, kWarpsPerBlock * 32, smd, s>>>(a); \
         }                                                                                                      \
     } while (0)
-        if (cpl == 1 && spec == 8) GT_LAUNCH_ROW_DS(1, 8);
+        // 8 heads x 32 with gated scores (the benchmark layer): four edge groups per iteration and a four-deep ring at four blocks
+        // per SM measured fastest (0.484 ms on the 169K-node block against 0.525 ms for 2 x 4 at five blocks, 0.56 ms for 2 x 3 at six)
+        if (cpl == 1 && spec == 8 && c.score == SCORE_GATED) {
+            constexpr int UU = 4, NN = 4;
+            const size_t smx = ((sm + 15) & ~size_t(15)) + (size_t)NN * UU * (cpl * (16 + 4) + 4) * kWarpsPerBlock * 32;
+            set_smem(attn_bwd_row_ds_kernel<__nv_bfloat16, 1, true, 8, UU, NN, 4>, smx);
+            attn_bwd_row_ds_kernel<__nv_bfloat16, 1, true, 8, UU, NN, 4><<<blocks, kWarpsPerBlock * 32, smx, s>>>(a);
+        } else if (cpl == 1 && spec == 8) GT_LAUNCH_ROW_DS(1, 8);
         else if (cpl == 1 && spec == 4) GT_LAUNCH_ROW_DS(1, 4);
         else if (cpl == 1) GT_LAUNCH_ROW_DS(1, 0);
         else if (spec == 16) GT_LAUNCH_ROW_DS(2, 16);
