@@ -60,7 +60,7 @@ def run_reference(args):
         _unavailable(f"reference import failed: {type(e).__name__}: {e}")
 
     sys.path.insert(0, os.path.dirname(HERE))
-    from bench import GRIDS, WORKLOAD, ClockSampler
+    from bench import REFERENCE_GRIDS, WORKLOAD, ClockSampler
     from gt_b200.data.expander import keyed_expander_edges
     from gt_b200.data.synthetic import virtual_node_edges, workload_graph
     wl = workload_graph(WORKLOAD, seed=0, scale_down=args.scale_down)
@@ -73,7 +73,7 @@ def run_reference(args):
     attn_et = torch.cat([torch.zeros(ei.shape[1], dtype=torch.long), torch.ones(exp.shape[1], dtype=torch.long),
                          torch.full((tok.shape[1],), 2, dtype=torch.long)])
     n_pad = -(-n_tot // (8 * world)) * (8 * world)
-    pd, po = GRIDS[world]
+    pd, po = REFERENCE_GRIDS[world]
     grid = Grid2D(pd, po, n_tot, n_pad=n_pad, use_axonn=False).to(dev)
     gcn_blk, _ = grid.local_block(gcn_edges_with_self_loops(ei, n_tot))
     a_blk, a_et = grid.local_block(attn_ei, attn_et)

@@ -25,10 +25,12 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WORKLOAD = "exphormer_arxiv"
-# (P_d, P_o) = (row blocks, column blocks).  The 8-GPU grid of the workload has the factors 2 and 4; it is oriented as the
-# performance model selects (4 row blocks x 2 column blocks: measured 6.0 ms against 7.0 ms for 2 x 4, because the reduce-scattered
-# payload row is twice as wide as the gathered input row).  Both arms of the benchmark use this table.
+# (P_d, P_o) = (row blocks, column blocks).  The 8-GPU grid of the workload has the factors 2 and 4; this package orients it as
+# its performance model selects (4 row blocks x 2 column blocks: measured 6.0 ms against 7.0 ms for 2 x 4, because the
+# reduce-scattered payload row is twice as wide as the gathered input row).  The reference arm keeps the grids the benchmark
+# configuration names for it (2 x 4 at 8 GPUs), which is also what it was measured with on this machine.
 GRIDS = {1: (1, 1), 2: (2, 1), 4: (2, 2), 8: (4, 2)}
+REFERENCE_GRIDS = {1: (1, 1), 2: (2, 1), 4: (2, 2), 8: (2, 4)}
 
 
 class ClockSampler:
