@@ -1585,9 +1585,11 @@ void attn_bwd_row(const AttnBwdRowArgs& a_in, cudaStream_t s) {
             attn_bwd_row_ds_kernel<__nv_bfloat16, CPL, false, SP><<<blocks, kWarpsPerBlock * 32, smd, s>>>(a); \
         }                                                                                                      \
     } while (0)
-        // 8 heads x 32 with gated scores (the benchmark layer): four edge groups per iteration and a four-deep ring at four blocks
-        // per SM measured fastest (0.484 ms on the 169K-node block against 0.525 ms for 2 x 4 at five blocks, 0.56 ms for 2 x 3 at six)
-        if (cpl == 1 && spec == 8 && c.score == SCORE_GATED) {
+        // GT_ROWDS_WIDE=1: four edge groups per iteration and a four-deep ring at four blocks per SM for 8 heads x 32 with gated
+        // scores.  Timed at 0.484 ms on the 169K-node block against 0.525 ms for the default (2 groups, 4 stages, five blocks; 4 x 3:
+        // 0.508, 2 x 6: 0.534, 2 x 3 at six blocks: 0.561).  Opt-in: its results were timed but not compared with the oracle.
+        static const bool wide = [] { const char* e = getenv("GT_ROWDS_WIDE"); return e && e[0] == '1'; }();
+        if (wide && cpl == 1 && spec == 8 && c.score == SCORE_GATED) {
             constexpr int UU = 4, NN = 4;
             const size_t smx = ((sm + 15) & ~size_t(15)) + (size_t)NN * UU * (cpl * (16 + 4) + 4) * kWarpsPerBlock * 32;
             set_smem(attn_bwd_row_ds_kernel<__nv_bfloat16, 1, true, 8, UU, NN, 4>, smx);

@@ -256,3 +256,10 @@ def test_analyze_coll_tables(tmp_path, capsys):
     assert out["rs"]["rates"][64.0] == [round(64 * 2 ** 20 / 0.25e-3 / 1e9, 1), round(64 * 2 ** 20 / 0.5e-3 / 1e9, 1)]
     assert out["rs"]["rates"][1.0][1] is None
     assert "RS: GB/s" in capsys.readouterr().out
+
+
+def test_kernel_l2_factor_arithmetic():
+    from gt_b200.bench.kernel_l2 import L2_BYTES, gathered_bytes, l2_factor
+    assert gathered_bytes(32768, 8, 32) == 2 * 32768 * 256 * 2 < L2_BYTES // 2
+    lam = l2_factor(dict(edges=100, fwd_ms=1.0, bwd_ms=4.0), dict(edges=200, fwd_ms=4.0, bwd_ms=8.0))
+    assert lam == {"fwd": 0.5, "bwd": 1.0}
