@@ -5,7 +5,7 @@
 // Who needs it.  The regular aggregation (gt::spmm, reached from Python through gt_b200.ops.native.spmm) cuts very long
 // rows (hub nodes) into segments and merges the segments' partial sums through a scratch buffer that the Python wrapper
 // takes from the framework's caching allocator.  Some hosts of this library cannot do that: a serving process whose device
-// memory was handed out completely at start-up, code that runs between other components under a fixed memory budget, or a
+// memory was handed out completely at start-up, code that runs between other components with a fixed share of the device memory, or a
 // C / C++ embedder that links the shared object without any tensor framework behind it.  For them cudaMalloc is either
 // forbidden or may fail at an arbitrary moment, and a failed allocation in the middle of a request is worse than a size
 // limit that is known in advance.

@@ -1,7 +1,7 @@
 """The allocation-free aggregation entry point ``gt_spmm_csr_noalloc`` (declared in ``gt_b200/csrc/noalloc.h``).
 
-Some hosts of the library cannot allocate device memory while they run (all memory handed out at start-up, a fixed budget
-shared with other components, or a plain C embedder without a tensor framework).  For them the library keeps the split-row
+Some hosts of the library cannot allocate device memory while they run (all memory handed out at start-up, a fixed part of the
+device memory next to other components, or a plain C embedder without a tensor framework).  For them the library keeps the split-row
 scratch of the sparse aggregation in a built-in device array.  The test calls the exported C symbol through ``ctypes`` with
 raw device pointers, twice in a row (the second call finds the previous call's data in the shared scratch), and compares
 with the regular entry point ``gt_b200.ops.native.spmm``; it also checks that a request beyond the built-in capacity is
