@@ -263,3 +263,27 @@ def test_kernel_l2_factor_arithmetic():
     assert gathered_bytes(32768, 8, 32) == 2 * 32768 * 256 * 2 < L2_BYTES // 2
     lam = l2_factor(dict(edges=100, fwd_ms=1.0, bwd_ms=4.0), dict(edges=200, fwd_ms=4.0, bwd_ms=8.0))
     assert lam == {"fwd": 0.5, "bwd": 1.0}
+
+
+def test_plot_series_time_to_accuracy_model_and_versus(tmp_path):
+    import json
+    from gt_b200.bench import parse_logs, plot_figures
+    log = tmp_path / "a.log"
+    log.write_text(
+        "epoch    0 loss 3.8 train 0.02 val 0.10 test 0.02 | best val 0.10 test 0.02 @ 0 | 30.0 ms/epoch train\n"
+        "epoch   10 loss 3.1 train 0.20 val 0.45 test 0.18 | best val 0.45 test 0.18 @ 10 | 20.0 ms/epoch train\n"
+        "epoch   20 loss 2.9 train 0.30 val 0.55 test 0.28 | best val 0.55 test 0.28 @ 20 | 20.0 ms/epoch train\n")
+    rows = parse_logs.curves([str(log)])
+    tta = plot_figures.time_to_acc_series(rows, "val_acc", 0.5)
+    assert list(tta) == [str(log)] and abs(tta[str(log)] - 0.42) < 1e-9
+    assert plot_figures.time_to_acc_series(rows, "val_acc", 0.9) == {}
+    model = plot_figures.model_series()
+    assert {"world 1", "world 4", "world 8"} <= set(model)
+    assert all(0.8 < p / m < 1.25 for pts in model.values() for m, p, _ in pts)
+    res = tmp_path / "bench.jsonl"
+    res.write_text("\n".join(json.dumps(d) for d in [
+        dict(impl="reference", n_gpus=1, ms_per_step=100.0), dict(impl="gt_b200", n_gpus=1, ms_per_step=20.0),
+        dict(impl="reference", n_gpus=8, ms_per_step=40.0), dict(impl="gt_b200", n_gpus=8, ms_per_step=5.0),
+        dict(impl="gt_b200", n_gpus=4, ms_per_step=9.0)]) + "\nnot json\n")
+    assert plot_figures.main(["versus", str(res)]) == {"speed-up over reference": [(1, 5.0), (8, 8.0)]}
+    assert plot_figures.main(["time_to_acc", str(log), "--target", "0.5"]) == tta
