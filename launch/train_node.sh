@@ -1,6 +1,6 @@
 #!/usr/bin/env bash
 # One node, one process per GPU.  Usage: launch/train_node.sh <gpus> [train_dist flags...]
-#   launch/train_node.sh 8 --grid 2 4 --fused --synthetic exphormer_arxiv --bf16 --norm ln --cuda_graph --comm p2p
+#   launch/train_node.sh 8 --grid 4 2 --fused --synthetic exphormer_arxiv --bf16 --norm ln --cuda_graph --comm p2p
 set -euo pipefail
 GPUS=${1:?number of GPUs}; shift
 cd "$(dirname "$0")/.."
