@@ -1,6 +1,8 @@
 """Expander generation, synthetic graphs, partitioner + loaders (pure host, no process group)."""
 import os
 
+import pytest
+
 import torch
 
 from gt_b200.data.expander import KeyedPermutation, block_expander_edges, keyed_expander_edges
@@ -73,3 +75,54 @@ def test_partition_roundtrip_and_resume(tmp_path):
             tot_x += int(part["masks"]["train"].sum())
         assert tot_e == ei.shape[1] * (shape[2] if len(shape) == 3 else 1)
         assert tot_x == int(wl["masks"]["train"].sum())
+
+
+def test_plexus_layout_loader(tmp_path):
+    """A partition in the Plexus layout (destination-first edge files, features split in column pieces) loads onto grids whose
+    chunks differ from the partition's, with the same blocks and node arrays as a direct split of the global graph."""
+    from gt_b200.data.loader import grid_n_pad, load_plexus_partition, read_plexus_meta
+    wl = workload_graph("cpu_small", seed=2)
+    n, ei, x, y, masks = wl["n"], wl["edge_index"], wl["x"], wl["y"], wl["masks"]
+    w = torch.rand(ei.shape[1])
+    p = 3
+    chunk = -(-n // p)
+    f = x.shape[1]
+    out = tmp_path / "plexus"
+    for sub in ("edge_index/0", "input_features", "output_labels/0", "masks/train/0", "masks/val/0", "masks/test/0"):
+        os.makedirs(out / sub)
+    torch.save((n, f, int(y.max()) + 1), out / "metadata.pt")
+    pieces = [(j * f // p, (j + 1) * f // p) for j in range(p)]
+    for i in range(p):
+        a, b = i * chunk, min(n, (i + 1) * chunk)
+        torch.save(y[a:b].view(-1, 1), out / "output_labels" / "0" / f"{i}.pt")
+        for j, (c0, c1) in enumerate(pieces):
+            torch.save(x[a:b, c0:c1].clone(), out / "input_features" / f"{i}_{j}.pt")
+        for k, s in (("train", "train"), ("valid", "val"), ("test", "test")):
+            torch.save(masks[k][a:b].clone(), out / "masks" / s / "0" / f"{i}.pt")
+        for j in range(p):                                   # file "{dst chunk}_{src chunk}": rows (dst, src), global ids
+            sel = (ei[1] // chunk == i) & (ei[0] // chunk == j)
+            torch.save((ei[:, sel].flip(0).clone(), w[sel].clone()), out / "edge_index" / "0" / f"{i}_{j}.pt")
+    meta = read_plexus_meta(str(out))
+    assert meta["layout"] == "plexus" and meta["p_part"] == p and meta["chunk"] == chunk and meta["num_features"] == f
+    for shape in ((2, 2), (1, 2), (4, 1), (2, 1, 2)):
+        world = 1
+        for s in shape:
+            world *= s
+        n_pad = grid_n_pad(meta, world, 8)
+        assert n_pad % world == 0 and n_pad % 8 == 0 and n_pad >= n
+        tot_e = tot_train = 0
+        for rank in range(world):
+            g = BlockGrid.virtual(shape[0], shape[1], n, rank, p_heads=shape[2] if len(shape) == 3 else 1, n_pad=n_pad)
+            part = load_plexus_partition(str(out), g, "cpu")
+            ref_ei, _, ref_w = g.local_block(ei, None, w)
+            k = lambda e: e[1] * 100000 + e[0]                   # noqa: E731
+            o1, o2 = torch.argsort(k(part["edge_index"])), torch.argsort(k(ref_ei))
+            assert torch.equal(part["edge_index"][:, o1], ref_ei[:, o2]) and torch.allclose(part["weight"][o1], ref_w[o2])
+            assert torch.equal(part["x"], g.take_owned(x)) and torch.equal(part["y"], g.take_owned(y))
+            tot_e += part["num_local_edges"]
+            tot_train += int(part["masks"]["train"].sum())
+        assert tot_e == ei.shape[1] * (shape[2] if len(shape) == 3 else 1)
+        assert tot_train == int(masks["train"].sum()) * 1
+    os.makedirs(out / "edge_index" / "1")
+    with pytest.raises(ValueError):
+        read_plexus_meta(str(out))                            # two node orders: refused
