@@ -287,3 +287,21 @@ def test_plot_series_time_to_accuracy_model_and_versus(tmp_path):
         dict(impl="gt_b200", n_gpus=4, ms_per_step=9.0)]) + "\nnot json\n")
     assert plot_figures.main(["versus", str(res)]) == {"speed-up over reference": [(1, 5.0), (8, 8.0)]}
     assert plot_figures.main(["time_to_acc", str(log), "--target", "0.5"]) == tta
+
+
+def test_tile_density_orders():
+    import torch
+    from gt_b200.bench import tile_density as td
+    n = 1024
+    blocks = [torch.cartesian_prod(torch.arange(b * 128, (b + 1) * 128), torch.arange(b * 128, (b + 1) * 128)).t() for b in range(4)]
+    dense = torch.cat(blocks, 1)                                     # four fully dense diagonal tiles
+    dense = dense[:, torch.rand(dense.shape[1], generator=torch.Generator().manual_seed(0)) < 0.5]
+    st = td.tile_stats(dense, n, 1638)
+    assert st["dense_tiles"] == 4 and st["dense_edge_share"] == 1.0 and st["tiles_nonempty"] == 4 and st["tiles_total"] == 64
+    perm = torch.randperm(n, generator=torch.Generator().manual_seed(1))
+    assert td.tile_stats(perm[dense], n, 1638)["dense_edge_share"] == 0.0      # a random relabelling destroys the tiles
+    star = torch.stack([torch.full((600,), 900), torch.arange(600)])            # node 900 is the hub
+    ei = td.degree_order(torch.cat([star, star.flip(0)], 1), n)
+    assert int(ei[0][0]) == 0                                         # the hub becomes node 0
+    res = td.main(["--graph", "cpu_small", "--orders", "native", "degree", "--min_edges", "64"])
+    assert [r["order"] for r in res] == ["native", "degree"] and all(r["edges"] > 0 for r in res)
