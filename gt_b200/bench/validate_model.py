@@ -75,6 +75,10 @@ def main(argv=None):
             b = [g for g, _, _ in sorted(lst, key=lambda v: v[2])]
             print(f"world {world} ({tr}): measured order {a}, model order {b}: {'AGREE' if a[0] == b[0] else 'DIFFER'} on the best grid")
     print(f"worst ratio {worst:.2f}")
+    from .model_validation_data import OTHER_CONFIGS
+    print("other configurations (measured, not modelled):")
+    for r in OTHER_CONFIGS:
+        print(f"  {'x'.join(map(str, r['grid'])):>6s} {r['ms']:9.1f} ms {r['peak_gb']:6.1f} GB  {r['name']}")
     return worst
 
 
