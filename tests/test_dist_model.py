@@ -26,6 +26,10 @@ CASES = {
     "head_1x2x2_gcn": dict(grid=(1, 2, 2)),
     "head_1x1x4": dict(grid=(1, 1, 4), with_gcn=False),
     "head_sparse": dict(grid=(2, 1, 2), sparse_comm=True, sparse_threshold=1.0),
+    # the eight-rank grids of the benchmark configurations
+    "fused_4x2_ln": dict(grid=(4, 2), fused=True, norm="ln"),
+    "fused_2x4_ln": dict(grid=(2, 4), fused=True, norm="ln"),
+    "head_2x2x2": dict(grid=(2, 2, 2)),
 }
 
 
