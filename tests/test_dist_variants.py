@@ -12,6 +12,9 @@ VARIANTS = {
     "graphormer_2x2": dict(model="graphormer", grid=(2, 2)),
     "graphormer_ckpt_4x1": dict(model="graphormer", grid=(4, 1), checkpoint=True),
     "graphormer_khop_head_1x2x2": dict(model="graphormer", grid=(1, 2, 2), khop=True),
+    # the eight-rank layouts of the benchmark configurations
+    "unimp_label_head_2x2x2": dict(model="unimp", grid=(2, 2, 2), label=True),
+    "graphormer_khop_ckpt_4x2": dict(model="graphormer", grid=(4, 2), khop=True, checkpoint=True),
 }
 
 
