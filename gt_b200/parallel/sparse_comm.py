@@ -38,7 +38,8 @@ class SparseRowPlan:
 
     ``need_local``: sorted unique block-local row indices.  After construction: ``n_need``, ``remap`` (block-local ->
     compact, -1 = absent), ``recv_counts`` / ``send_counts`` per peer, ``send_idx`` (rows of my chunk the peers need,
-    grouped by peer), ``share`` (= max over the group of rows moved / rows of the block)."""
+    grouped by peer), ``share`` (= max over all ranks of rows moved / rows of the block), ``n_need_max`` (largest need set of any
+    rank).  Plans are built collectively: every rank constructs the plan of its own group at the same point of the program."""
 
     def __init__(self, group, rows_per_rank: int, need_local: torch.Tensor, name: str = "?", transport: str = "a2a",
                  heap=None):
@@ -80,10 +81,15 @@ class SparseRowPlan:
         self.need_local = need_local.to(_idt(n_blk)).contiguous()
         self.need_owner = owner.to(torch.int32).contiguous()              # pull transport: (peer, row) per compact row
         self.need_row = local_idx.to(torch.int32).contiguous()
-        sh = torch.tensor([self.n_need / max(n_blk, 1), self.n_send / max(n_blk, 1)], dtype=torch.float64, device=dev)
+        # Maxima over ALL ranks, not over this group: every rank builds the plan of its own group at the same point of the program,
+        # and decisions and buffer sizes derived from a plan must agree across groups too.  A rank belongs to a row group and a
+        # column group; if two row groups sized a symmetric-heap buffer differently (or one took the sparse and one the dense
+        # path), the heap offsets of their members would differ from then on, and the column groups, whose members come from
+        # different row groups, would no longer find their buffers at the same offset on every member.
+        sh = torch.tensor([self.n_need / max(n_blk, 1), self.n_send / max(n_blk, 1), float(self.n_need)], dtype=torch.float64, device=dev)
         if g > 1:
-            dist.all_reduce(sh, op=dist.ReduceOp.MAX, group=group)
-        self.share, self.share_send = float(sh[0]), float(sh[1])
+            dist.all_reduce(sh, op=dist.ReduceOp.MAX)
+        self.share, self.share_send, self.n_need_max = float(sh[0]), float(sh[1]), int(sh[2])
         self.ratio = A2A_OVER_AG
 
     def worthwhile(self, threshold=None):

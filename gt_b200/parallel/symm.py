@@ -276,9 +276,8 @@ class SymmetricHeap:
             dist.all_to_all(rows, [self._compact_index_for(plan, p, dev) for p in range(c.size)], group=plan.group)
             for p in range(c.size):
                 src[p] = rows[p]
-            n_max = torch.tensor([plan.n_need], device=dev)
-            dist.all_reduce(n_max, op=dist.ReduceOp.MAX, group=plan.group)
-            st = plan._pull = dict(ctx=c, src=src.contiguous(), n_max=int(n_max.item()))
+            # staging rows of the reduce: the largest need set of ANY rank, so that every rank's heap grows by the same amount
+            st = plan._pull = dict(ctx=c, src=src.contiguous(), n_max=int(plan.n_need_max))
         return st
 
     @staticmethod

@@ -102,3 +102,26 @@ def test_dist_exphormer_matches_reference(case):
     for s in shape:
         world *= s
     run_dist(_worker, world, case)
+
+
+def _uniform_plan_worker(rank, world):
+    """Row groups with very different need sets still agree on the shares and on the staging size of the reduce: what is derived
+    from a plan sizes buffers of the symmetric heap, whose offsets must stay equal on every rank."""
+    import torch.distributed as dist
+    from gt_b200.parallel.grid import make_grid
+    from gt_b200.parallel.sparse_comm import SparseRowPlan
+    grid = make_grid((2, 2), 64, n_pad=64)
+    per = grid.n_row_block // 2
+    n_need = 3 if grid.r == 0 else 29                      # ranks of row block 0 need few rows, those of row block 1 many
+    plan = SparseRowPlan(grid.row_group, per, torch.arange(n_need), "row")
+    vals = torch.tensor([plan.share, plan.share_send, float(plan.n_need_max)], dtype=torch.float64)
+    lo, hi = vals.clone(), vals.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    assert torch.equal(lo, hi), (lo, hi)
+    assert plan.n_need_max == 29 and plan.n_need in (3, 29)
+    assert plan.worthwhile(0.5) == (plan.share <= 0.5 and plan.share_send <= 0.5)
+
+
+def test_plan_shares_and_staging_sizes_agree_across_groups():
+    run_dist(_uniform_plan_worker, 4)
