@@ -17,13 +17,15 @@ the position and issues one extra barrier), so a buffer is rewritten only after 
 implies that every peer has finished reading the previous contents.  A wait that expires writes the peer index to the
 status word (``gt_b200.ops.native.check_status`` raises on the host); nothing spins forever.
 """
+import os
+import socket
+
 import torch
 import torch.distributed as dist
 
 from ..ops import native
 
 _DT = {torch.float32: 0, torch.bfloat16: 1, torch.int32: 2, torch.int64: 3, torch.uint8: 4}
-import os
 
 # polls before a wait on a peer gives up (~1 s at the default).  A rank-local stall longer than this (first-launch module
 # loading, a slow evaluation on one rank) makes the wait expire, so runs with long rank-local phases raise it.
@@ -85,9 +87,14 @@ class SymmetricHeap:
         self.base = e.heap_alloc(self.bytes)
         self.rank, self.world = dist.get_rank(), dist.get_world_size()
         handles = [None] * self.world
-        dist.all_gather_object(handles, (self.rank, e.heap_ipc_handle(self.base)))
+        dist.all_gather_object(handles, (self.rank, e.heap_ipc_handle(self.base), socket.gethostname()))
+        if len({host for _, _, host in handles}) > 1:
+            # CUDA IPC maps memory of GPUs of one machine; across nodes the grid collectives stay on NCCL
+            e.heap_free(self.base)
+            raise RuntimeError("the symmetric heap (peer-memory transport) spans the GPUs of ONE node, but the process group covers "
+                               f"{len({host for _, _, host in handles})} hosts: run with --comm nccl")
         self.peer_base = [0] * self.world
-        for r, h in handles:
+        for r, h, _ in handles:
             self.peer_base[r] = self.base if r == self.rank else e.heap_open(h)
         self.top = 0
         self.groups = {}
