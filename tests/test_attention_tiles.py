@@ -135,3 +135,23 @@ def test_tile_kernel_matches_oracle(n, nc, h, score, norm):
     assert _rel(o, o_r) < 2e-2
     for a, b in zip(gg, gr):
         assert _rel(a, b) < 4e-2
+
+
+def test_tile_split_without_edge_types_and_with_ragged_blocks():
+    """Blocks without edge types (plain dot-product models) and with row / column counts that are not multiples of the tile."""
+    torch.manual_seed(3)
+    n, nc, h, d = 333, 517, 2, 32
+    typed = clustered_block(n, nc, seed=5)
+    blk = BlockCSR.from_csr(typed.crow, typed.col, None, n_cols=nc)
+    plan = tl.build_tile_plan(blk, min_edges=300, min_share=0.0)
+    assert plan is not None and plan.residual.etype is None
+    assert int((plan.mask == 0).sum()) == plan.num_tiled_edges and int((plan.mask != tl.NO_EDGE).sum()) == plan.num_tiled_edges
+    assert int(plan.tile_cb.max()) * 128 < nc and int(plan.rb_ids.max()) * 128 < n
+    q, k, v = torch.randn(n, h, d), torch.randn(nc, h, d), torch.randn(nc, h, d)
+    for norm in ("softmax", "clampexp"):
+        full = bt.attn_fwd_partial(q, k, v, blk, None, None, score="dot", norm=norm)
+        part = merge(bt.attn_fwd_partial(q, k, v, plan.residual, None, None, score="dot", norm=norm),
+                     tl.tile_fwd_ref(q, k, v, plan, None, score="dot", norm=norm), norm)
+        assert (bt.normalize(full[0], full[1], norm) - bt.normalize(part[0], part[1], norm)).abs().max() < 1e-4
+    many = BlockCSR.from_csr(typed.crow, typed.col, typed.etype + 20, n_cols=nc)             # more edge types than a byte map encodes
+    assert tl.build_tile_plan(many, min_edges=300, min_share=0.0) is None
