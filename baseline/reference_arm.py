@@ -39,6 +39,8 @@ def run_reference(args):
         import triton  # noqa: F401
     except Exception as e:            # the reference's kernels are Triton
         _unavailable(f"triton not importable: {e}")
+    if not torch.cuda.is_available():
+        _unavailable("no CUDA device on this machine (the reference's kernels and NCCL need one)")
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)

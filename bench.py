@@ -85,6 +85,8 @@ def run_ours(args):
     from gt_b200.train.engine import TrainEngine, init_single_process_group
     from gt_b200.train.workloads import exphormer_workload
 
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py measures the sm_100a kernels and needs a CUDA device")
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
