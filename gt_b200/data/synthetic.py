@@ -62,12 +62,11 @@ def chung_lu(n: int, num_edges: int, gamma: float = 2.1, seed: int = 0, device="
     return ei[:, ei[0] != ei[1]]
 
 
-def rmat(scale: int, num_edges: int, a: float = 0.57, b: float = 0.19, c: float = 0.19, seed: int = 0, device="cpu",
-         chunk: int = 1 << 26) -> torch.Tensor:
-    """R-MAT graph on ``2**scale`` nodes: every bit of (src, dst) picks one of four quadrants with probabilities
-    (a, b, c, 1-a-b-c).  Generated in chunks to bound the temporary memory."""
+def rmat_chunks(scale: int, num_edges: int, a: float = 0.57, b: float = 0.19, c: float = 0.19, seed: int = 0, device="cpu",
+                chunk: int = 1 << 26):
+    """The edges of :func:`rmat` one chunk at a time (``[2, m]`` tensors, self loops removed): the same generator sequence, so
+    concatenating the chunks gives exactly ``rmat(...)``.  For consumers that keep only a block of the graph."""
     g = _gen(seed, device)
-    out = []
     for e0 in range(0, num_edges, chunk):
         m = min(chunk, num_edges - e0)
         src = torch.zeros(m, dtype=torch.long, device=device)
@@ -78,9 +77,40 @@ def rmat(scale: int, num_edges: int, a: float = 0.57, b: float = 0.19, c: float 
             down = u >= a + b                                                    # quadrants c and d: row bit set
             src = (src << 1) | right.long()
             dst = (dst << 1) | down.long()
-        out.append(torch.stack([src, dst]))
-    ei = torch.cat(out, dim=1)
-    return ei[:, ei[0] != ei[1]]
+        keep = src != dst
+        yield torch.stack([src[keep], dst[keep]])
+
+
+def rmat(scale: int, num_edges: int, a: float = 0.57, b: float = 0.19, c: float = 0.19, seed: int = 0, device="cpu",
+         chunk: int = 1 << 26) -> torch.Tensor:
+    """R-MAT graph on ``2**scale`` nodes: every bit of (src, dst) picks one of four quadrants with probabilities
+    (a, b, c, 1-a-b-c).  Generated in chunks to bound the temporary memory."""
+    parts = list(rmat_chunks(scale, num_edges, a, b, c, seed, device, chunk))
+    return torch.cat(parts, dim=1) if parts else torch.zeros(2, 0, dtype=torch.long, device=device)
+
+
+NODE_DATA_BLOCK = 1 << 16
+
+
+def node_data_range(lo: int, hi: int, num_features: int, num_classes: int, split: Sequence[float] = (0.5, 0.25, 0.25), seed: int = 0,
+                    device="cpu", dtype=torch.float32):
+    """Node data of the nodes ``[lo, hi)`` of an arbitrarily large graph: ``(x ~ N(0,1), y uniform, masks)``.  Node ``i`` draws from
+    the generator of its block ``i // 65536``, so any range, on any rank and any grid, yields the same values for the same node
+    without generating the rest of the graph."""
+    xs, ys, us = [], [], []
+    for blk in range(lo // NODE_DATA_BLOCK, -(-hi // NODE_DATA_BLOCK) if hi > lo else lo // NODE_DATA_BLOCK):
+        g = _gen(seed * 1_000_003 + blk + 1, device)
+        x = torch.randn(NODE_DATA_BLOCK, num_features, generator=g, device=device, dtype=torch.float32)
+        y = torch.randint(0, num_classes, (NODE_DATA_BLOCK,), generator=g, device=device)
+        u = torch.rand(NODE_DATA_BLOCK, generator=g, device=device)
+        a, b = max(lo, blk * NODE_DATA_BLOCK) - blk * NODE_DATA_BLOCK, min(hi, (blk + 1) * NODE_DATA_BLOCK) - blk * NODE_DATA_BLOCK
+        xs.append(x[a:b]); ys.append(y[a:b]); us.append(u[a:b])
+    if not xs:
+        z = torch.zeros(0, device=device)
+        return z.new_zeros(0, num_features).to(dtype), z.long(), {k: z.bool() for k in ("train", "valid", "test")}
+    x, y, u = torch.cat(xs).to(dtype), torch.cat(ys), torch.cat(us)
+    t0, t1 = split[0], split[0] + split[1]
+    return x, y, {"train": u < t0, "valid": (u >= t0) & (u < t1), "test": u >= t1}
 
 
 def virtual_node_edges(n: int, token: Optional[int] = None, device="cpu"):

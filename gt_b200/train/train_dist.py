@@ -44,6 +44,8 @@ def build_parser():
     a("--data", default=None, help="partition directory (gt_b200.data.partition or Plexus layout)")
     a("--synthetic", default=None, help="synthetic workload name (gt_b200.data.synthetic.WORKLOADS); default cpu_small")
     a("--scale_down", type=int, default=1)
+    a("--stream_gen", action="store_true",
+      help="(--synthetic exphormer_rmat26) build every rank's blocks from streamed edge chunks: no rank holds the global graph")
     a("--virtual_node", action="store_true", help="(exphormer) add one global token connected to every node (edge type 2)")
     a("--graph_name", default=None)
     # layer kind
@@ -243,7 +245,8 @@ def main(argv=None):
         if args.model == "exphormer":
             layer = "ring" if args.ring else ("streamed" if args.stream_sub > 1 else ("pipelined" if args.pipeline_sub > 1 else
                                                                                       ("fused" if args.fused else "plain")))
-            wl = W.exphormer_workload(name, args.grid, dev, dtype, seed=args.seed, scale_down=args.scale_down, exp_deg=args.exp_deg,
+            build = W.exphormer_workload_streamed if args.stream_gen else W.exphormer_workload
+            wl = build(name, args.grid, dev, dtype, seed=args.seed, scale_down=args.scale_down, exp_deg=args.exp_deg,
                                       virtual_node=args.virtual_node, dropout=args.dropout, backend=backend, layer=layer, norm=args.norm,
                                       stream_sub=max(args.stream_sub, args.pipeline_sub), comm_bf16=args.comm_bf16 or args.bf16, heap=heap,
                                       layers=args.layers, hidden=args.hidden, heads=args.heads, with_gcn=not args.no_gcn,

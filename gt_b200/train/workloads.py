@@ -36,7 +36,7 @@ def _generate(name, seed, scale_down, device):
 
 def exphormer_workload(name="exphormer_arxiv", grid_shape=None, device="cpu", dtype=torch.float32, seed=0, scale_down=1,
                        exp_deg=4, virtual_node=True, dropout=0.1, backend=None, layer="fused", norm="ln", stream_sub=1,
-                       comm_bf16=True, heap=None, layers=None, hidden=None, heads=None, **model_kw):
+                       comm_bf16=True, heap=None, layers=None, hidden=None, heads=None, return_blocks=False, **model_kw):
     """Exphormer on a named graph: symmetrised base graph + degree-``exp_deg`` expander (both directions) + optional global
     token (edge type 2) + one self loop per node for the GCN branch.  Returns a dict with ``grid, model, x, y, masks,
     n_train, num_attn_edges, num_nodes, cfg``."""
@@ -75,6 +75,104 @@ def exphormer_workload(name="exphormer_arxiv", grid_shape=None, device="cpu", dt
                x=grid.take_owned(x).to(dtype), y=grid.take_owned(y),
                masks={k: grid.take_owned(m.to(torch.uint8)).bool() & grid.valid_mask.cpu() for k, m in masks.items()},
                n_train=int(masks["train"].sum()), in_degree=degrees(ei, n)[0].cpu())
+    if return_blocks:                                          # local edge lists of this rank (tests)
+        out["blocks"] = dict(attn=a_blk, attn_type=a_et, gcn=g_blk)
+    return out
+
+
+def exphormer_workload_streamed(name="exphormer_rmat26", grid_shape=None, device="cpu", dtype=torch.float32, seed=0, scale_down=1, exp_deg=4,
+                                virtual_node=False, chunk_edges=1 << 24, dropout=0.1, backend=None, layer="streamed", norm="ln", stream_sub=1,
+                                comm_bf16=True, heap=None, layers=None, hidden=None, heads=None, return_blocks=False, **model_kw):
+    """:func:`exphormer_workload` for the R-MAT scale-out workload without any rank ever holding the global graph.
+
+    Every rank walks the same seeded sequence of R-MAT edge chunks (``chunk_edges`` edges at a time), symmetrises each chunk and
+    keeps the edges of ITS block only; duplicates are removed inside the block (which equals removing them globally and then
+    taking the block).  Expander edges come from the per-block generator, the token's edges are written down directly, and the
+    node data of the owned chunk come from per-node-block generators (:func:`gt_b200.data.synthetic.node_data_range`).  Peak
+    host / device memory is one chunk plus the block, instead of the whole edge list plus its sort buffers."""
+    import math
+
+    from ..attention.csr import BlockCSR  # noqa: F401  (the model builds its CSR from the local edge lists)
+    from ..data.expander import block_expander_edges
+    from ..data.synthetic import WORKLOADS, node_data_range, rmat_chunks
+    if name != "exphormer_rmat26":
+        raise ValueError("the streamed builder generates the R-MAT workload 'exphormer_rmat26'")
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    grid_shape = tuple(grid_shape or DEFAULT_GRIDS[world])
+    cfg = dict(WORKLOADS[name])
+    sc = 26 - int(math.log2(scale_down)) if scale_down > 1 else 26
+    n = 1 << sc
+    cfg["n"] = n
+    n_tot = n + (1 if virtual_node else 0)
+    n_pad = pad_to(n_tot, 8 * world * max(stream_sub, 1))
+    grid = make_grid(grid_shape, n_tot, n_pad=n_pad).to(device)
+    dev = torch.device(device)
+    gen_dev = dev if dev.type == "cuda" else torch.device("cpu")
+    n_cols = grid.n_col_block
+    keys = []
+    for chunk in rmat_chunks(sc, (16 << sc) // 2, seed=seed, device=gen_dev, chunk=chunk_edges):
+        both = torch.cat([chunk, chunk.flip(0)], dim=1)
+        loc, _ = grid.local_block(both)
+        keys.append(torch.unique(loc[1] * n_cols + loc[0]))                  # (row-local dst, col-local src) as one key
+    key = torch.unique(torch.cat(keys)) if keys else torch.zeros(0, dtype=torch.long, device=gen_dev)
+    base = torch.stack([key % n_cols, key // n_cols])                          # local (src, dst), sorted by (dst, src)
+    exp = block_expander_edges(grid, n, exp_deg, seed=seed, device=gen_dev) if exp_deg > 0 else base.new_zeros(2, 0)
+    parts, types = [base, exp], [0, 1]
+    if virtual_node:                                                           # token id n: edges (i -> n) and (n -> i) for i < n
+        r_lo_hi, (c_lo, c_hi) = grid.row_block_ranges(), grid.col_block_range()
+        tok_in_rows = any(lo <= n < hi for lo, hi in r_lo_hi)
+        tok_in_cols = c_lo <= n < c_hi
+        t_src, t_dst = [], []
+        if tok_in_rows:                                                        # the token attends to the nodes of my column block
+            src = torch.arange(c_lo, min(c_hi, n), device=gen_dev)
+            t_src.append(src); t_dst.append(torch.full_like(src, n))
+        if tok_in_cols:                                                        # the nodes of my row block attend to the token
+            dst = torch.cat([torch.arange(lo, min(hi, n), device=gen_dev) for lo, hi in r_lo_hi]) if any(lo < n for lo, _ in r_lo_hi) \
+                else torch.zeros(0, dtype=torch.long, device=gen_dev)
+            t_src.append(torch.full_like(dst, n)); t_dst.append(dst)
+        if t_src:
+            gs_, gd_ = torch.cat(t_src), torch.cat(t_dst)
+            parts.append(torch.stack([grid.global_to_col_local(gs_), grid.global_to_row_local(gd_)]))
+            types.append(2)
+    a_blk = torch.cat(parts, dim=1)
+    a_et = torch.cat([torch.full((p.shape[1],), t, dtype=torch.long, device=gen_dev) for p, t in zip(parts, types)])
+    # GCN block: base edges + one self loop for every node that is both one of my rows and one of my columns
+    cb_lo, cb_hi = grid.col_block_range()
+    loops_g = torch.cat([torch.arange(max(lo, cb_lo), max(min(hi, cb_hi, n_tot), max(lo, cb_lo)), device=gen_dev)
+                         for lo, hi in grid.row_block_ranges()] + [torch.zeros(0, dtype=torch.long, device=gen_dev)])
+    loops = torch.stack([grid.global_to_col_local(loops_g), grid.global_to_row_local(loops_g)])
+    g_blk = torch.cat([base, loops], dim=1)
+    backend = backend or ("cuda" if dev.type == "cuda" else "torch")
+    bf16 = dtype == torch.bfloat16
+    kw = dict(dropout=dropout, gnn_dropout=dropout, num_edge_types=3 if virtual_node else 2, backend=backend, norm=norm,
+              fused=layer in ("fused", "streamed", "pipelined"), stream_sub=stream_sub if layer == "streamed" else 1,
+              pipeline_sub=stream_sub if layer == "pipelined" else 1,
+              comm_dtype=torch.bfloat16 if (comm_bf16 and dev.type == "cuda") else None,
+              rs_dtype=torch.bfloat16 if (comm_bf16 and dev.type == "cuda" and world > 1) else None,
+              kernel_dtype=torch.bfloat16 if bf16 else None, heap=heap)
+    kw.update(model_kw)
+    torch.manual_seed(seed)
+    model = DistExphormer(grid, g_blk.to(dev), a_blk.to(dev), a_et.to(dev), cfg["features"], hidden or cfg["hidden"], cfg["classes"],
+                          layers or cfg["layers"], heads or cfg["heads"], **kw).to(dev)
+    lo, hi = grid.owned_range()
+    x_o, y_o, m_o = node_data_range(lo, min(hi, n), cfg["features"], cfg["classes"], (0.01, 0.01, 0.98), seed=seed + 17, device="cpu")
+
+    def pad_rows(t):
+        out = t.new_zeros((grid.chunk,) + tuple(t.shape[1:]))
+        out[:t.shape[0]] = t
+        return out
+
+    valid = grid.valid_mask.cpu()
+    masks = {k: pad_rows(v) & valid for k, v in m_o.items()}
+    counts = torch.tensor([a_blk.shape[1], g_blk.shape[1], int(masks["train"].sum())], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(counts)
+    p_heads = grid_shape[2] if len(grid_shape) == 3 else 1
+    out = dict(grid=grid, model=model, cfg=cfg, num_nodes=n_tot, num_attn_edges=int(counts[0].item()) // p_heads,
+               num_gcn_edges=int(counts[1].item()) // p_heads, x=pad_rows(x_o).to(dtype), y=pad_rows(y_o), masks=masks,
+               n_train=int(counts[2].item()), in_degree=None)
+    if return_blocks:
+        out["blocks"] = dict(attn=a_blk, attn_type=a_et, gcn=g_blk)
     return out
 
 

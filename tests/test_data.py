@@ -126,3 +126,44 @@ def test_plexus_layout_loader(tmp_path):
     os.makedirs(out / "edge_index" / "1")
     with pytest.raises(ValueError):
         read_plexus_meta(str(out))                            # two node orders: refused
+
+
+def _streamed_workload_worker(rank, world, shape):
+    """The streamed builder yields, block by block, the edge sets of the builder that materialises the global graph (same R-MAT
+    chunk sequence), and node data that depend only on the node id."""
+    import torch.distributed as dist
+    from gt_b200.data.synthetic import node_data_range
+    from gt_b200.train.workloads import exphormer_workload, exphormer_workload_streamed
+    kw = dict(name="exphormer_rmat26", grid_shape=shape, scale_down=1 << 15, virtual_node=True, layers=1, hidden=16, heads=2,
+              return_blocks=True)
+    layer = "fused" if len(shape) == 2 else "head"
+    a = exphormer_workload(layer=layer, **kw)
+    b = exphormer_workload_streamed(layer=layer, chunk_edges=1 << 26, **kw)
+
+    def keyset(ei, et=None):
+        k = ei[1] * 10_000_000 + ei[0] * 10 + (et if et is not None else 0)
+        return torch.unique(k)
+
+    assert a["num_nodes"] == b["num_nodes"] == 2049 and a["grid"].n_pad == b["grid"].n_pad
+    assert torch.equal(keyset(a["blocks"]["attn"], a["blocks"]["attn_type"]), keyset(b["blocks"]["attn"].cpu(), b["blocks"]["attn_type"].cpu()))
+    assert a["blocks"]["attn"].shape[1] == b["blocks"]["attn"].shape[1]
+    assert torch.equal(keyset(a["blocks"]["gcn"]), keyset(b["blocks"]["gcn"].cpu())) and a["blocks"]["gcn"].shape[1] == b["blocks"]["gcn"].shape[1]
+    assert a["num_attn_edges"] == b["num_attn_edges"] and a["num_gcn_edges"] == b["num_gcn_edges"]
+    # a smaller chunk size walks a different random sequence: another graph of the same family, same bookkeeping
+    c = exphormer_workload_streamed(layer=layer, chunk_edges=1 << 12, **kw)
+    assert 0.8 < c["num_attn_edges"] / b["num_attn_edges"] < 1.25
+    lo, hi = b["grid"].owned_range()
+    x_ref, y_ref, _ = node_data_range(0, 2048, b["cfg"]["features"], b["cfg"]["classes"], (0.01, 0.01, 0.98), seed=17)
+    nv = max(min(hi, 2048) - lo, 0)
+    assert torch.equal(b["x"][:nv], x_ref[lo:lo + nv]) and torch.equal(b["y"][:nv], y_ref[lo:lo + nv])
+    tot = torch.tensor([float(b["masks"]["train"].sum())], dtype=torch.float64)
+    dist.all_reduce(tot)
+    assert int(tot.item()) == b["n_train"]
+    out = b["model"](b["x"])                                  # the model runs on the streamed blocks
+    assert out.shape[0] == b["grid"].chunk and torch.isfinite(out).all()
+
+
+@pytest.mark.parametrize("shape", [(2, 2), (1, 2, 2)], ids=["2x2", "1x2x2"])
+def test_streamed_workload_matches_global_builder(shape):
+    from dist_utils import run_dist
+    run_dist(_streamed_workload_worker, 4, shape)

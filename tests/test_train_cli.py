@@ -70,7 +70,9 @@ def _cli_worker(rank, world, argv):
     ["--grid", "2", "1", "--synthetic", "cpu_small", "--scale_down", "4", "--model", "unimp", "--label_input", "--epochs", "3"],
     ["--grid", "1", "1", "2", "--synthetic", "cpu_small", "--scale_down", "4", "--model", "graphormer", "--epochs", "3", "--heads", "4"],
     ["--grid_auto", "--synthetic", "cpu_small", "--scale_down", "4", "--epochs", "3", "--auto_ckpt"],
-], ids=["fused_2x1_stats", "streamed_1x2_census", "unimp_label", "graphormer_head", "grid_auto"])
+    ["--grid", "2", "1", "--synthetic", "exphormer_rmat26", "--scale_down", "32768", "--stream_gen", "--stream_sub", "2", "--fused", "--epochs", "3",
+     "--hidden", "32", "--heads", "4", "--norm", "ln"],
+], ids=["fused_2x1_stats", "streamed_1x2_census", "unimp_label", "graphormer_head", "grid_auto", "rmat_stream_gen"])
 def test_cli_on_gloo_ranks(argv):
     run_dist(_cli_worker, 2, argv)
 
