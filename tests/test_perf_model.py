@@ -123,3 +123,23 @@ def test_analytic_gather_model_against_the_measured_degree_sweep():
     # bytes scale with the width, the per-row latency does not
     wide = gs.attn_theory_ms(n * 64, n, 16, 32, "fwd")
     assert 1.9 < wide / gs.attn_theory_ms(n * 64, n, 8, 32, "fwd") < 2.0
+
+
+def test_streamed_memory_model_against_the_measured_scale_out_runs():
+    """Peak memory of the streamed layer on the R-MAT workload at 2^22 nodes: 72.0 GB on one GPU (8 sub-blocks) and 12.4 GB per
+    rank on a 4 x 2 grid were measured; the full 2^26-node graph is predicted to fit 8 x 180 GB only as an 8 x 1 grid."""
+    from gt_b200.perf import grid_select as gs
+    m = gs.Model(256, 8, 2)
+
+    def graph(sc):
+        n = 1 << sc
+        e_base = int((16 << sc) * 0.93)                  # symmetrised R-MAT edges after duplicate removal
+        return gs.Graph(n, gs.attention_edges(n, e_base, 4), e_base + n, 128, "rmat", classes=172, exp_deg=4)
+
+    g22 = graph(22)
+    for grid, measured in (((1, 1), 72.0), ((4, 2), 12.4)):
+        gb = gs.peak_memory_bytes(grid[0], grid[1], g22, m, n_sub=8, streamed=True) / 2 ** 30
+        assert 0.85 < gb / measured < 1.15, (grid, gb, measured)
+    g26 = graph(26)
+    assert gs.peak_memory_bytes(8, 1, g26, m, n_sub=16, streamed=True) / 2 ** 30 < 180 * 0.9
+    assert gs.peak_memory_bytes(2, 4, g26, m, n_sub=32, streamed=True) / 2 ** 30 > 180
