@@ -19,6 +19,7 @@ status word (``gt_b200.ops.native.check_status`` raises on the host); nothing sp
 """
 import os
 import socket
+import zlib
 
 import torch
 import torch.distributed as dist
@@ -39,6 +40,24 @@ MAX_SPINS_EAGER = int(os.environ.get("GT_PEER_WAIT_SPINS_EAGER", str(20 * MAX_SP
 def wait_spins():
     """Poll limit for a peer wait that is being enqueued now."""
     return MAX_SPINS if torch.cuda.is_current_stream_capturing() else MAX_SPINS_EAGER
+
+
+def alloc_log_update(log, off, nbytes):
+    """``(number of allocations, running CRC of their offsets and sizes)`` after one more allocation."""
+    n, crc = log
+    return n + 1, zlib.crc32(f"{off}:{nbytes};".encode(), crc)
+
+
+def check_alloc_logs(log, group=None):
+    """Compare the allocation logs of the ranks of ``group``; raises ``RuntimeError`` naming the ranks that differ."""
+    world = dist.get_world_size(group)
+    logs = [None] * world
+    dist.all_gather_object(logs, tuple(log), group=group)
+    if len(set(logs)) > 1:
+        common = max(set(logs), key=logs.count)
+        odd = [i for i, v in enumerate(logs) if v != common]
+        raise RuntimeError(f"symmetric heap out of step: ranks {odd} of the group made a different sequence of allocations "
+                           f"(allocations, checksum) = {logs}; every rank must allocate the same sizes in the same order")
 
 
 class GroupContext:
@@ -97,6 +116,7 @@ class SymmetricHeap:
         for r, h, _ in handles:
             self.peer_base[r] = self.base if r == self.rank else e.heap_open(h)
         self.top = 0
+        self.alloc_log = (0, 0)
         self.groups = {}
         self.named = {}
         dist.barrier()
@@ -107,7 +127,14 @@ class SymmetricHeap:
         if off + nbytes > self.bytes:
             raise MemoryError(f"symmetric heap exhausted: need {off + nbytes} bytes, have {self.bytes} (raise --heap_mb)")
         self.top = off + nbytes
+        self.alloc_log = alloc_log_update(self.alloc_log, off, nbytes)
         return off
+
+    def check_symmetric(self, group=None):
+        """Raise unless every rank has made the same sequence of allocations (same offsets and sizes in the same order): peers
+        address each other's buffers by offset, so one rank that allocates differently leaves everyone reading the wrong bytes
+        and waiting on the wrong flags.  Collective over ``group`` (default: all ranks); host side only."""
+        check_alloc_logs(self.alloc_log, group)
 
     def view(self, off, shape, dtype):
         return native.ext().tensor_from_ptr(self.base + off, list(shape), _DT[dtype], self.device.index or 0)

@@ -384,6 +384,8 @@ def main(argv=None):
         epoch_ms.append(ms)
         if cuda:
             check_status_all_ranks(dev, world)            # device_epoch_ms has synchronised: the status word is final for this epoch
+            if heap is not None and epoch == start_epoch:
+                heap.check_symmetric()                        # once: every rank has made the same symmetric-heap allocations
         if epoch in (start_epoch, start_epoch + 2):
             mem(f"after step (epoch {epoch})", model)
         if epoch % args.eval_every == 0 or epoch == args.epochs - 1:

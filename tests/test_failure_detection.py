@@ -139,3 +139,24 @@ def test_bounded_device_wait_expires_and_the_context_survives():
     x = torch.arange(8, device=dev).float()
     assert float((x * 2).sum()) == 56.0                                 # the context is alive
     assert int(other[0].item()) != 0                                    # my arrival was published before the wait
+
+
+def _alloc_log_worker(rank, world):
+    """Allocation logs that agree pass; a rank that allocated a different size is named."""
+    from gt_b200.parallel.symm import alloc_log_update, check_alloc_logs
+    log = (0, 0)
+    for off, nbytes in ((0, 256), (256, 4096), (4352, 32)):
+        log = alloc_log_update(log, off, nbytes)
+    check_alloc_logs(log)                                   # identical on every rank
+    bad = alloc_log_update(log, 4608, 1024 if rank != 2 else 2048)
+    try:
+        check_alloc_logs(bad)
+    except RuntimeError as exc:
+        assert "ranks [2]" in str(exc)
+    else:
+        raise AssertionError("a rank with a different allocation went unnoticed")
+
+
+def test_symmetric_heap_allocation_logs_are_compared_across_ranks():
+    from dist_utils import run_dist
+    run_dist(_alloc_log_worker, 4)

@@ -346,6 +346,8 @@ def _multi_worker(rank, world, store, comm, dtype_name):
     for shape, name in MULTI[world]:
         try:
             _exphormer_case(dev, shape, name, dtype, heap)
+            if heap is not None:
+                heap.check_symmetric()                        # names the first case after which the ranks' heaps differ
         except Exception as exc:                              # noqa: BLE001  (collected, reported together below)
             failures.append(f"{name} on {shape}: {type(exc).__name__}: {exc}")
     for shape, cfg in MULTI_VARIANTS[world]:
