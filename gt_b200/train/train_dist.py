@@ -44,6 +44,9 @@ def build_parser():
     a("--data", default=None, help="partition directory (gt_b200.data.partition or Plexus layout)")
     a("--synthetic", default=None, help="synthetic workload name (gt_b200.data.synthetic.WORKLOADS); default cpu_small")
     a("--scale_down", type=int, default=1)
+    a("--heartbeat", type=float, default=0.0, metavar="SECONDS",
+      help="host-side failure detection: every rank bumps a counter in the job's store once per epoch and checks its peers' before "
+           "launching the step; a peer that announced a failure or was silent for SECONDS ends the run with PeerFailure (0 = off)")
     a("--stream_gen", action="store_true",
       help="(--synthetic exphormer_rmat26) build every rank's blocks from streamed edge chunks: no rank holds the global graph")
     a("--virtual_node", action="store_true", help="(exphormer) add one global token connected to every node (edge type 2)")
@@ -358,6 +361,10 @@ def main(argv=None):
 
     best = dict(val=-1.0, test=0.0, epoch=-1)
     epoch_ms = []
+    hb = None
+    if args.heartbeat > 0 and world > 1:
+        from ..utils.health import Heartbeat
+        hb = Heartbeat(timeout=args.heartbeat)
     if cuda:
         torch.cuda.reset_peak_memory_stats()
     for epoch in range(start_epoch, args.epochs):
@@ -377,8 +384,14 @@ def main(argv=None):
             census_ctx = saved_tensor_census(grid, rank, hidden=args.hidden)
         if cstats is not None:
             cstats.begin_epoch()
+        if hb is not None:                                    # before this epoch's launches: is every peer still there?
+            hb.beat()
+            hb.check(wait_for_first=60.0 if epoch == start_epoch else 0.0)
         with prof_ctx, census_ctx:
-            loss, ms = device_epoch_ms(lambda: eng.train_step(loss_fn), dev)
+            if hb is not None:
+                loss, ms = hb.guarded(device_epoch_ms, lambda: eng.train_step(loss_fn), dev)      # an exception here is announced to the peers
+            else:
+                loss, ms = device_epoch_ms(lambda: eng.train_step(loss_fn), dev)
         if cstats is not None:
             cstats.end_epoch(keep=epoch >= start_epoch + 2)
         epoch_ms.append(ms)

@@ -65,7 +65,8 @@ def _cli_worker(rank, world, argv):
 
 
 @pytest.mark.parametrize("argv", [
-    ["--grid", "2", "1", "--synthetic", "cpu_small", "--scale_down", "4", "--fused", "--epochs", "3", "--norm", "ln", "--coll_stats", "--timers"],
+    ["--grid", "2", "1", "--synthetic", "cpu_small", "--scale_down", "4", "--fused", "--epochs", "3", "--norm", "ln", "--coll_stats", "--timers",
+     "--heartbeat", "30"],
     ["--grid", "1", "2", "--synthetic", "cpu_small", "--scale_down", "4", "--stream_sub", "2", "--fused", "--epochs", "3", "--saved_census"],
     ["--grid", "2", "1", "--synthetic", "cpu_small", "--scale_down", "4", "--model", "unimp", "--label_input", "--epochs", "3"],
     ["--grid", "1", "1", "2", "--synthetic", "cpu_small", "--scale_down", "4", "--model", "graphormer", "--epochs", "3", "--heads", "4"],
