@@ -122,3 +122,20 @@ def test_collective_census_counts_the_peer_memory_transport(monkeypatch):
     t = st.table()
     assert t[("p2p_all_gather", 4)] == dict(calls=1.0, mbytes=64 / 2 ** 20, ms=0.0)
     assert t[("p2p_all_reduce", 2)]["calls"] == 1.0 and t[("p2p_sparse_gather", 2)]["mbytes"] == 40 / 2 ** 20
+
+
+def test_resilient_launcher_restarts_and_gives_up(tmp_path):
+    """The supervisor resumes from the checkpoint of an earlier run and stops after MAX_RESTARTS failed attempts."""
+    import os
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = os.path.join(root, "launch", "train_resilient.sh")
+    ck = str(tmp_path / "run.pt")
+    base = ["--grid", "1", "1", "--synthetic", "cpu_small", "--scale_down", "8", "--fused", "--hidden", "16", "--heads", "2", "--layers", "1"]
+    env = dict(os.environ, SAVE_EVERY="2", RESTART_DELAY="0", MAX_RESTARTS="1")
+    r = subprocess.run([script, "0", ck] + base + ["--epochs", "2"], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and os.path.exists(ck) and "finished after 0 restart" in r.stdout
+    r = subprocess.run([script, "0", ck] + base + ["--epochs", "4"], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "continuing at epoch 2" in r.stdout
+    r = subprocess.run([script, "0", str(tmp_path / "none.pt"), "--no_such_flag"], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode != 0 and "restart 1 of 1" in r.stderr and "giving up after 1 restarts" in r.stderr
