@@ -44,6 +44,8 @@ def build_parser():
     a("--data", default=None, help="partition directory (gt_b200.data.partition or Plexus layout)")
     a("--synthetic", default=None, help="synthetic workload name (gt_b200.data.synthetic.WORKLOADS); default cpu_small")
     a("--scale_down", type=int, default=1)
+    a("--eval_only", action="store_true",
+      help="with --resume: load the checkpoint, evaluate train / validation / test accuracy once (eval mode, no gradient) and exit")
     a("--heartbeat", type=float, default=0.0, metavar="SECONDS",
       help="host-side failure detection: every rank bumps a counter in the job's store once per epoch and checks its peers' before "
            "launching the step; a peer that announced a failure or was silent for SECONDS ends the run with PeerFailure (0 = off)")
@@ -359,6 +361,21 @@ def main(argv=None):
         logits, loss_mask, n_loss = forward(True)
         return dist_cross_entropy(logits, y_loc, loss_mask, n_loss)
 
+    if args.eval_only:
+        if not args.resume:
+            raise SystemExit("--eval_only evaluates a checkpoint: give --resume FILE")
+        model.eval()
+        if heap is not None:
+            heap.begin_step()
+        with torch.no_grad():
+            (logits, _, _), ms = device_epoch_ms(lambda: forward(False), dev)
+            acc = dist_accuracy(logits, y_loc, masks)
+        if cuda:
+            check_status_all_ranks(dev, world)
+        if rank == 0:
+            print(f"EVAL checkpoint={args.resume} epoch={start_epoch} train={acc['train']:.4f} val={acc['valid']:.4f} test={acc['test']:.4f} "
+                  f"forward_ms={ms:.2f} grid={'x'.join(map(str, args.grid))} world={world}", flush=True)
+        return dict(eval=acc, epoch=start_epoch, forward_ms=ms)
     best = dict(val=-1.0, test=0.0, epoch=-1)
     epoch_ms = []
     hb = None

@@ -139,3 +139,17 @@ def test_resilient_launcher_restarts_and_gives_up(tmp_path):
     assert r.returncode == 0 and "continuing at epoch 2" in r.stdout
     r = subprocess.run([script, "0", str(tmp_path / "none.pt"), "--no_such_flag"], env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode != 0 and "restart 1 of 1" in r.stderr and "giving up after 1 restarts" in r.stderr
+
+
+def test_eval_only_reports_the_checkpoint(tmp_path, capsys):
+    from gt_b200.train import train_dist
+    ck = str(tmp_path / "m.pt")
+    base = ["--grid", "1", "1", "--synthetic", "cpu_small", "--scale_down", "8", "--fused", "--hidden", "16", "--heads", "2", "--layers", "1"]
+    trained = train_dist.main(base + ["--epochs", "3", "--save", ck, "--eval_every", "1"])
+    capsys.readouterr()
+    res = train_dist.main(base + ["--resume", ck, "--eval_only"])
+    out = capsys.readouterr().out
+    assert "EVAL checkpoint=" in out and res["epoch"] == 3
+    assert abs(res["eval"]["valid"] - trained["best"]["val"]) < 0.2 and 0.0 <= res["eval"]["test"] <= 1.0
+    with pytest.raises(SystemExit):
+        train_dist.main(base + ["--eval_only"])
