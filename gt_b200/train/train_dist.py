@@ -46,6 +46,8 @@ def build_parser():
     a("--scale_down", type=int, default=1)
     a("--eval_only", action="store_true",
       help="with --resume: load the checkpoint, evaluate train / validation / test accuracy once (eval mode, no gradient) and exit")
+    a("--predict_out", default=None, metavar="FILE",
+      help="with --eval_only: rank 0 writes {'pred': int64 [N] predicted classes in node order, 'num_nodes': N} to FILE")
     a("--heartbeat", type=float, default=0.0, metavar="SECONDS",
       help="host-side failure detection: every rank bumps a counter in the job's store once per epoch and checks its peers' before "
            "launching the step; a peer that announced a failure or was silent for SECONDS ends the run with PeerFailure (0 = off)")
@@ -372,6 +374,20 @@ def main(argv=None):
             acc = dist_accuracy(logits, y_loc, masks)
         if cuda:
             check_status_all_ranks(dev, world)
+        if args.predict_out:
+            lo, hi = grid.owned_range()
+            mine = (int(lo), logits.argmax(dim=1).cpu())
+            parts = [None] * world
+            if world > 1:
+                dist.all_gather_object(parts, mine)
+            else:
+                parts = [mine]
+            if rank == 0:
+                n_all = grid.num_nodes
+                pred = torch.full((grid.n_pad,), -1, dtype=torch.long)
+                for lo_r, p_r in parts:                              # head-axis replicas write the same values
+                    pred[lo_r:lo_r + p_r.numel()] = p_r
+                torch.save(dict(pred=pred[:n_all].clone(), num_nodes=n_all), args.predict_out)
         if rank == 0:
             print(f"EVAL checkpoint={args.resume} epoch={start_epoch} train={acc['train']:.4f} val={acc['valid']:.4f} test={acc['test']:.4f} "
                   f"forward_ms={ms:.2f} grid={'x'.join(map(str, args.grid))} world={world}", flush=True)

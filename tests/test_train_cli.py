@@ -153,3 +153,19 @@ def test_eval_only_reports_the_checkpoint(tmp_path, capsys):
     assert abs(res["eval"]["valid"] - trained["best"]["val"]) < 0.2 and 0.0 <= res["eval"]["test"] <= 1.0
     with pytest.raises(SystemExit):
         train_dist.main(base + ["--eval_only"])
+
+
+def _predict_worker(rank, world, ck, out):
+    from gt_b200.train.train_dist import main
+    base = ["--grid", "2", "1", "--synthetic", "cpu_small", "--scale_down", "8", "--fused", "--hidden", "16", "--heads", "2", "--layers", "1"]
+    main(base + ["--epochs", "2", "--save", ck])
+    res = main(base + ["--resume", ck, "--eval_only", "--predict_out", out])
+    assert 0.0 <= res["eval"]["train"] <= 1.0
+
+
+def test_eval_only_writes_predictions_in_node_order(tmp_path):
+    ck, out = str(tmp_path / "m.pt"), str(tmp_path / "pred.pt")
+    run_dist(_predict_worker, 2, ck, out)
+    blob = torch.load(out, weights_only=True)
+    n = blob["num_nodes"]
+    assert blob["pred"].shape == (n,) and int(blob["pred"].min()) >= 0 and n == 250
