@@ -101,6 +101,33 @@ def build_parser():
     return ap
 
 
+def parse_with_config(ap, argv=None):
+    """``--config FILE`` (YAML or JSON mapping of flag names to values) supplies defaults; flags on the command line win.
+    Unknown keys are an error, so a misspelt option does not pass silently."""
+    pre = argparse.ArgumentParser(add_help=False)
+    pre.add_argument("--config", default=None)
+    known, _ = pre.parse_known_args(argv)
+    ap.add_argument("--config", default=None, metavar="FILE", help="YAML / JSON file with default values for the flags above")
+    if known.config:
+        with open(known.config) as f:
+            text = f.read()
+        if known.config.endswith(".json"):
+            import json
+            cfg = json.loads(text)
+        else:
+            import yaml
+            cfg = yaml.safe_load(text) or {}
+        if not isinstance(cfg, dict):
+            raise SystemExit(f"--config {known.config}: expected a mapping of flag names to values")
+        dests = {a.dest for a in ap._actions}
+        cfg = {str(k).lstrip("-").replace("-", "_"): v for k, v in cfg.items()}
+        unknown = sorted(set(cfg) - dests)
+        if unknown:
+            raise SystemExit(f"--config {known.config}: unknown options {unknown}")
+        ap.set_defaults(**cfg)
+    return ap.parse_args(argv)
+
+
 def validate(args):
     args.stream_overlap = not args.no_stream_overlap
     if args.backend == "triton":
@@ -195,7 +222,7 @@ def _auto_grid(args, world, n, e_graph, f_in, rank):
 
 
 def main(argv=None):
-    args = build_parser().parse_args(argv)
+    args = parse_with_config(build_parser(), argv)
     head_grid = validate(args)
     init_dist()
     rank, world = dist.get_rank(), dist.get_world_size()

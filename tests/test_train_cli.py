@@ -169,3 +169,19 @@ def test_eval_only_writes_predictions_in_node_order(tmp_path):
     blob = torch.load(out, weights_only=True)
     n = blob["num_nodes"]
     assert blob["pred"].shape == (n,) and int(blob["pred"].min()) >= 0 and n == 250
+
+
+def test_config_file_supplies_defaults_and_flags_win(tmp_path):
+    from gt_b200.train.train_dist import build_parser, parse_with_config
+    cfg = tmp_path / "run.yaml"
+    cfg.write_text("grid: [2, 1]\nfused: true\nhidden: 64\n--epochs: 7\nsynthetic: cpu_small\n")
+    args = parse_with_config(build_parser(), ["--config", str(cfg), "--hidden", "32"])
+    assert args.grid == [2, 1] and args.fused and args.hidden == 32 and args.epochs == 7 and args.synthetic == "cpu_small"
+    js = tmp_path / "run.json"
+    js.write_text('{"layers": 3, "norm": "ln"}')
+    args = parse_with_config(build_parser(), ["--config", str(js)])
+    assert args.layers == 3 and args.norm == "ln" and args.grid == [1, 1]
+    bad = tmp_path / "bad.yaml"
+    bad.write_text("hiden: 64\n")
+    with pytest.raises(SystemExit):
+        parse_with_config(build_parser(), ["--config", str(bad)])
