@@ -46,6 +46,8 @@ def build_parser():
     a("--scale_down", type=int, default=1)
     a("--eval_only", action="store_true",
       help="with --resume: load the checkpoint, evaluate train / validation / test accuracy once (eval mode, no gradient) and exit")
+    a("--metrics_jsonl", default=None, metavar="FILE",
+      help="rank 0 appends one JSON object per evaluated epoch (epoch, loss, accuracies, device ms of the epoch, best so far)")
     a("--predict_out", default=None, metavar="FILE",
       help="with --eval_only: rank 0 writes {'pred': int64 [N] predicted classes in node order, 'num_nodes': N} to FILE")
     a("--heartbeat", type=float, default=0.0, metavar="SECONDS",
@@ -470,6 +472,12 @@ def main(argv=None):
             loss_tot = loss.detach().clone().float()
             if world > 1:
                 dist.all_reduce(loss_tot)
+            if rank == 0 and args.metrics_jsonl:
+                import json
+                with open(args.metrics_jsonl, "a") as mf:
+                    mf.write(json.dumps(dict(epoch=epoch, loss=float(loss_tot.item()), train=float(acc["train"]), val=float(acc["valid"]),
+                                             test=float(acc["test"]), epoch_ms=float(ms), best_val=float(best["val"]),
+                                             best_epoch=int(best["epoch"]), world=world, grid=list(args.grid))) + "\n")
             if rank == 0 and (epoch % 10 == 0 or epoch == args.epochs - 1):
                 print(f"epoch {epoch:4d} loss {loss_tot.item():.4f} train {acc['train']:.4f} val {acc['valid']:.4f} test {acc['test']:.4f} "
                       f"| best val {best['val']:.4f} test {best['test']:.4f} @ {best['epoch']} | {sum(epoch_ms) / len(epoch_ms):.1f} ms/epoch train",

@@ -185,3 +185,14 @@ def test_config_file_supplies_defaults_and_flags_win(tmp_path):
     bad.write_text("hiden: 64\n")
     with pytest.raises(SystemExit):
         parse_with_config(build_parser(), ["--config", str(bad)])
+
+
+def test_metrics_jsonl(tmp_path):
+    import json
+    from gt_b200.train import train_dist
+    mf = tmp_path / "m.jsonl"
+    train_dist.main(["--grid", "1", "1", "--synthetic", "cpu_small", "--scale_down", "8", "--fused", "--hidden", "16", "--heads", "2", "--layers", "1",
+                     "--epochs", "4", "--eval_every", "2", "--metrics_jsonl", str(mf)])
+    rows = [json.loads(l) for l in mf.read_text().splitlines()]
+    assert [r["epoch"] for r in rows] == [0, 2, 3] and all(r["epoch_ms"] > 0 and 0 <= r["val"] <= 1 for r in rows)
+    assert rows[-1]["best_val"] >= rows[0]["val"] and rows[0]["grid"] == [1, 1]
