@@ -36,6 +36,27 @@ def curves(paths):
     return rows
 
 
+def curves_jsonl(paths):
+    """The rows of :func:`curves` from ``train_dist --metrics_jsonl`` files (one JSON object per evaluated epoch).  The training
+    time of an epoch row is the sum of the device times of the evaluated epochs so far, scaled to the epochs in between."""
+    import json
+    rows = []
+    for p in paths:
+        seconds, last_epoch = 0.0, -1
+        with open(p) as f:
+            for line in f:
+                line = line.strip()
+                if not line.startswith("{"):
+                    continue
+                d = json.loads(line)
+                seconds += (d["epoch"] - last_epoch) * d["epoch_ms"] / 1e3
+                last_epoch = d["epoch"]
+                rows.append(dict(log=p, epoch=int(d["epoch"]), train_seconds=seconds, loss=float(d["loss"]), train_acc=float(d["train"]),
+                                 val_acc=float(d["val"]), test_acc=float(d["test"]), best_val=float(d["best_val"]),
+                                 test_at_best_val=None, best_epoch=int(d["best_epoch"])))
+    return rows
+
+
 def steady(paths):
     rows = []
     for p in paths:

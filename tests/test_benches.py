@@ -305,3 +305,14 @@ def test_tile_density_orders():
     assert int(ei[0][0]) == 0                                         # the hub becomes node 0
     res = td.main(["--graph", "cpu_small", "--orders", "native", "degree", "--min_edges", "64"])
     assert [r["order"] for r in res] == ["native", "degree"] and all(r["edges"] > 0 for r in res)
+
+
+def test_curves_from_metrics_jsonl(tmp_path):
+    import json
+    from gt_b200.bench import parse_logs, plot_figures
+    f = tmp_path / "m.jsonl"
+    f.write_text("\n".join(json.dumps(dict(epoch=e, loss=3.0 - e * 0.1, train=0.1 * e, val=0.2 * e, test=0.15 * e, epoch_ms=20.0, best_val=0.2 * e,
+                                           best_epoch=e, world=1, grid=[1, 1])) for e in (0, 2, 4)) + "\n")
+    rows = parse_logs.curves_jsonl([str(f)])
+    assert [r["epoch"] for r in rows] == [0, 2, 4] and abs(rows[-1]["train_seconds"] - 0.1) < 1e-9
+    assert plot_figures.time_to_acc_series(rows, "val_acc", 0.4) == {str(f): rows[1]["train_seconds"]}
