@@ -1,0 +1,108 @@
+"""Happens-before check of the peer-memory protocols (``gt_b200.utils.hb_check`` on the programs of ``gt_b200.parallel.protocol_model``)."""
+import os
+import re
+
+import pytest
+
+from gt_b200.parallel import protocol_model as pm
+from gt_b200.utils.hb_check import ProtocolTrace, check
+
+GRIDS = [(1, 2), (2, 1), (2, 2), (4, 2), (2, 4), (8, 1), (1, 8)]
+
+
+def test_checker_on_hand_written_programs():
+    # publish / consume through a channel: ordered
+    tr = ProtocolTrace(2)
+    tr.write(0, 0, "b", 1); tr.signal(0, "c", (0, 1)); tr.signal(1, "c", (0, 1)); tr.wait(1, "c", (0, 1), 0); tr.read(1, 0, "b", 1)
+    assert not check(tr).violations
+    # the consumer does not wait: the read may come first
+    tr = ProtocolTrace(2)
+    tr.write(0, 0, "b", 1); tr.read(1, 0, "b", 1)
+    assert [v.kind for v in check(tr).violations] == ["read-before-write"]
+    # ordering through a third rank: 0 -> 2 -> 1
+    tr = ProtocolTrace(3)
+    tr.write(0, 0, "b", 1); tr.signal(0, "a", (0, 2))
+    tr.signal(2, "a", (0, 2)); tr.wait(2, "a", (0, 2), 0); tr.signal(2, "z", (1, 2))
+    tr.signal(1, "z", (1, 2)); tr.wait(1, "z", (1, 2), 2); tr.read(1, 0, "b", 1)
+    assert not check(tr).violations
+    # the owner overwrites while the reader has not said that it is done
+    tr = ProtocolTrace(2)
+    tr.write(0, 0, "b", 1); tr.signal(0, "c", (0, 1)); tr.write(0, 0, "b", 2)
+    tr.signal(1, "c", (0, 1)); tr.wait(1, "c", (0, 1), 0); tr.read(1, 0, "b", 1)
+    kinds = {v.kind for v in check(tr).violations}
+    assert kinds and kinds <= {"write-while-read", "read-before-write", "wrong-version"}
+    # two writers of one location without an order between them
+    tr = ProtocolTrace(2)
+    tr.write(0, 0, "b", 1); tr.write(1, 0, "b", 2)
+    assert [v.kind for v in check(tr).violations] == ["write-write"]
+    # a wait before the first signal of the waiting rank needs nothing (epoch 0)
+    tr = ProtocolTrace(2)
+    tr.wait(0, "c", (0, 1), 1)
+    rep = check(tr)
+    assert rep.completed and not rep.expired
+
+
+@pytest.mark.parametrize("grid", GRIDS)
+def test_fused_step_is_race_free(grid):
+    for layers in (1, 2, 3, 4):
+        for kw in (dict(), dict(eval_after=True), dict(recompute=True), dict(recompute=True, eval_after=True)):
+            rep = check(pm.fused_step_trace(grid[0], grid[1], layers, steps=3, **kw))
+            assert rep.completed and not rep.violations and not rep.expired and not any(rep.status), (grid, layers, kw, pm.describe(rep))
+
+
+def test_single_buffering_is_caught():
+    rep = check(pm.fused_step_trace(2, 2, 3, steps=2, copies=1))
+    assert any(v.kind == "write-while-read" and v.buf[1] == "fb_x" for v in rep.violations)
+    rep = check(pm.fused_step_trace(2, 1, 2, steps=1, copies=1))
+    assert {v.buf[1] for v in rep.violations} == {"fb_x", "fb_dxc"}
+    # a row group alone is ordered layer by layer by its payload exchange (every member waits for every member): one copy would do
+    assert not check(pm.fused_step_trace(1, 2, 3, steps=2, copies=1)).violations
+    assert not check(pm.barrier_collective_trace(4, 6)).violations
+    assert check(pm.barrier_collective_trace(4, 6, copies=1)).violations
+
+
+def test_begin_step_barriers_are_what_protects_the_restart_of_the_alternation():
+    # odd depth + recomputation + an evaluation pass: the last use before a step and the first use of the step take the same copy,
+    # and nothing but the barriers of begin_step orders them
+    kw = dict(recompute=True, eval_after=True)
+    assert check(pm.fused_step_trace(2, 2, 3, steps=2, begin_barriers=False, **kw)).violations
+    assert not check(pm.fused_step_trace(2, 2, 3, steps=2, begin_barriers=True, **kw)).violations
+
+
+def test_lost_signal_expires_the_waits_on_that_peer_and_nobody_blocks():
+    rep = check(pm.fused_step_trace(2, 2, 3, steps=2), drop={(1, "pay0", 2)})
+    assert rep.completed
+    assert {(r, chan, peer) for r, _, chan, peer in rep.expired} == {(0, "pay0", 1), (1, "pay0", 1)}
+    assert rep.status[:2] == [101, 101] and rep.status[2:] == [0, 0]          # index of the silent peer within its row group
+    assert any(v.kind == "read-before-write" and v.buf[1] == "fb_pay" for v in rep.violations)       # what the expired wait no longer guarantees
+    worst = check(pm.fused_step_trace(2, 2, 3, steps=2), drop={(1, "pay0", 2)}, cascade=True)
+    assert worst.completed and set(rep.expired) <= set(worst.expired) and len(worst.expired) > len(rep.expired)
+    rep = check(pm.fused_step_trace(4, 2, 4, steps=2), drop={(5, "barrier_world", 2)})
+    assert rep.completed and rep.status == [105] * 8 and not rep.violations
+
+
+def test_stopped_rank_leaves_no_rank_blocked():
+    rep = check(pm.fused_step_trace(2, 2, 2, steps=2), die={3: 60})
+    assert rep.completed and rep.expired
+    assert all(peer == 3 for _, _, _, peer in rep.expired)
+    assert all(s >= 100 for s in rep.status[:3]) and rep.status[3] == 0
+
+
+def test_model_names_the_staging_kinds_and_channels_of_the_source():
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = open(os.path.join(root, "gt_b200", "parallel", "fused_layer.py")).read()
+    model = open(os.path.join(root, "gt_b200", "parallel", "protocol_model.py")).read()
+    kinds_src = set(re.findall(r'staging\([^"]*"(fb_\w+)"\)', src))
+    kinds_model = set(re.findall(r'staging\("(fb_\w+)"', model))
+    assert kinds_src == kinds_model == {"fb_x", "fb_pay", "fb_dpay", "fb_dxc", "fb_dxr"}
+    chans_src = set(re.findall(r"comm\.(\w+)\.signal\(\)", src))
+    chans_model = set(re.findall(r'tr\.signal\(r, "(\w+?)%d"', model))
+    assert chans_src == chans_model == {"x_col", "x_row", "pay", "dpay", "dx_col", "dx_row"}
+
+
+def test_cli(capsys):
+    assert pm.main(["--grid", "2", "2", "--layers", "2", "--steps", "2"]) == 0
+    assert "violations 0" in capsys.readouterr().out
+    assert pm.main(["--grid", "2", "2", "--layers", "2", "--copies", "1"]) == 1
+    assert pm.main(["--grid", "2", "1", "--layers", "2", "--drop", "1", "x_col0", "1"]) == 1
+    assert "expired: rank 0" in capsys.readouterr().out
