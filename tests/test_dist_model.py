@@ -30,6 +30,9 @@ CASES = {
     "fused_4x2_ln": dict(grid=(4, 2), fused=True, norm="ln"),
     "fused_2x4_ln": dict(grid=(2, 4), fused=True, norm="ln"),
     "head_2x2x2": dict(grid=(2, 2, 2)),
+    # grids whose factors are not powers of two
+    "fused_3x2": dict(grid=(3, 2), fused=True),
+    "streamed_2x3": dict(grid=(2, 3), fused=True, stream_sub=2),
 }
 
 
