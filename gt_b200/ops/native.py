@@ -68,10 +68,13 @@ _STATE = {}
 
 
 def _state(device):
-    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    if torch.device(device).type == "cpu":                  # host emulation of the peer-memory transport (parallel/symm_host.py)
+        key, dev = "cpu", torch.device("cpu")
+    else:
+        key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+        dev = torch.device("cuda", key)
     st = _STATE.get(key)
     if st is None:
-        dev = torch.device("cuda", key)
         st = dict(status=torch.zeros(1, dtype=torch.int32, device=dev),
                   rng=torch.tensor([0x5EED, 0], dtype=torch.int64, device=dev))
         _STATE[key] = st

@@ -33,14 +33,15 @@ def set_transport(heap):
 
 def _p2p_ok(x, group, rows_out):
     h = _HEAP[0]
-    if h is None or not x.is_cuda or x.dtype not in (torch.float32, torch.bfloat16):
+    if h is None or not h.reaches(x) or x.dtype not in h._float_types():
         return False
     per_rank = x.numel() // (group_size(group) if rows_out else 1)
     return (per_rank * x.element_size()) % 16 == 0 and per_rank % 8 == 0
 
 
 def _a2a_p2p_ok(x, slab_elems):
-    return _HEAP[0] is not None and x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and (slab_elems * x.element_size()) % 16 == 0
+    h = _HEAP[0]
+    return h is not None and h.reaches(x) and x.dtype in h._float_types() and (slab_elems * x.element_size()) % 16 == 0
 
 
 def _instrument(kind, group, nbytes, fn):
@@ -269,7 +270,7 @@ def _sum_over_ranks(x, group):
     if group_size(group) == 1:
         return x.clone()
     h = _HEAP[0]
-    if h is not None and x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and x.numel() % 8 == 0 and x.numel() > 0:
+    if h is not None and h.reaches(x) and x.dtype in h._float_types() and x.numel() % 8 == 0 and x.numel() > 0:
         x = x.contiguous()
         return _instrument("all_reduce", group, x.numel() * x.element_size(), lambda: h.all_reduce(x, torch.empty_like(x), group=group))
     y = x.clone()

@@ -26,7 +26,8 @@ import torch.distributed as dist
 
 from ..ops import native
 
-_DT = {torch.float32: 0, torch.bfloat16: 1, torch.int32: 2, torch.int64: 3, torch.uint8: 4}
+_DT = {torch.float32: 0, torch.bfloat16: 1, torch.int32: 2, torch.int64: 3, torch.uint8: 4,
+       torch.float64: 5}        # 5: host emulation only (parity tests in double precision); the device kernels move fp32 / bf16
 
 # polls before a wait on a peer gives up (~1 s at the default).  A rank-local stall longer than this (first-launch module
 # loading, a slow evaluation on one rank) makes the wait expire, so runs with long rank-local phases raise it.
@@ -37,9 +38,19 @@ MAX_SPINS = int(os.environ.get("GT_PEER_WAIT_SPINS", "5000000"))
 MAX_SPINS_EAGER = int(os.environ.get("GT_PEER_WAIT_SPINS_EAGER", str(20 * MAX_SPINS)))
 
 
+_NO_CUDA = [False]
+
+
 def wait_spins():
     """Poll limit for a peer wait that is being enqueued now."""
-    return MAX_SPINS if torch.cuda.is_current_stream_capturing() else MAX_SPINS_EAGER
+    if _NO_CUDA[0]:
+        return MAX_SPINS_EAGER
+    try:
+        capturing = torch.cuda.is_current_stream_capturing()
+    except Exception:                                       # no CUDA runtime in this process: the host emulation of the heap
+        _NO_CUDA[0] = True
+        capturing = False
+    return MAX_SPINS if capturing else MAX_SPINS_EAGER
 
 
 def alloc_log_update(log, off, nbytes):
@@ -96,12 +107,17 @@ class GroupContext:
 
 
 class SymmetricHeap:
+    host = False                 # True in the host emulation (symm_host.HostSymmetricHeap): CPU tensors, float64 allowed
+
     def __init__(self, device, bytes_=1 << 30):
         if not dist.is_initialized():
             raise RuntimeError("the symmetric heap needs an initialised process group (IPC handle exchange)")
         self.device = torch.device(device)
         torch.cuda.set_device(self.device)
-        e = native.ext()
+        self._map_heaps(native.ext(), bytes_)
+
+    def _map_heaps(self, e, bytes_):
+        """Allocate this rank's heap, exchange the handles and map every peer's heap."""
         self.bytes = int(bytes_)
         self.base = e.heap_alloc(self.bytes)
         self.rank, self.world = dist.get_rank(), dist.get_world_size()
@@ -135,6 +151,13 @@ class SymmetricHeap:
         address each other's buffers by offset, so one rank that allocates differently leaves everyone reading the wrong bytes
         and waiting on the wrong flags.  Collective over ``group`` (default: all ranks); host side only."""
         check_alloc_logs(self.alloc_log, group)
+
+    def _float_types(self):
+        return (torch.float32, torch.bfloat16, torch.float64) if self.host else (torch.float32, torch.bfloat16)
+
+    def reaches(self, x):
+        """``x`` lives where this heap's kernels run."""
+        return x.is_cuda or self.host
 
     def view(self, off, shape, dtype):
         return native.ext().tensor_from_ptr(self.base + off, list(shape), _DT[dtype], self.device.index or 0)
@@ -183,7 +206,7 @@ class SymmetricHeap:
     def reduce_scatter(self, x, group):
         c = self.ctx(group)
         x = x.contiguous()
-        if x.dtype not in (torch.float32, torch.bfloat16) or (x.numel() // c.size) % 8:
+        if x.dtype not in self._float_types() or (x.numel() // c.size) % 8:
             raise ValueError("reduce_scatter needs fp32 / bf16 chunks that are multiples of 8 elements")
         nbytes = x.numel() * x.element_size()
         off = c.staging(nbytes, "rs")
@@ -303,13 +326,8 @@ class SymmetricHeap:
             # owner-side table of the reduce: for every peer p and owned row r, the compact row of p that holds a partial of r
             dev = self.device
             src = torch.full((c.size, plan.rows_per_rank), -1, dtype=torch.int32, device=dev)
-            mine = torch.full((plan.rows_per_rank,), -1, dtype=torch.int32, device=dev)
-            sel = plan.need_owner == c.me
-            mine[plan.need_row[sel].long()] = torch.nonzero(sel).squeeze(1).to(torch.int32)
-            rows = [torch.empty_like(mine) for _ in range(c.size)]
-            dist.all_to_all(rows, [self._compact_index_for(plan, p, dev) for p in range(c.size)], group=plan.group)
-            for p in range(c.size):
-                src[p] = rows[p]
+            send = torch.stack([self._compact_index_for(plan, p, dev) for p in range(c.size)]).contiguous()
+            dist.all_to_all_single(src, send, group=plan.group)          # row p of src: peer p's compact rows for my rows
             # staging rows of the reduce: the largest need set of ANY rank, so that every rank's heap grows by the same amount
             st = plan._pull = dict(ctx=c, src=src.contiguous(), n_max=int(plan.n_need_max))
         return st
@@ -340,7 +358,7 @@ class SymmetricHeap:
         """``y2 [n_need, F]`` partial rows -> ``[rows_per_rank, F]``: sum of the partials the peers hold for my rows."""
         st = self._plan_state(plan)
         c = st["ctx"]
-        if y2.shape[1] % 8 or y2.dtype not in (torch.float32, torch.bfloat16):
+        if y2.shape[1] % 8 or y2.dtype not in self._float_types():
             raise ValueError("pull_reduce needs fp32 / bf16 rows with a width that is a multiple of 8")
         nbytes = max(st["n_max"], 1) * y2.shape[1] * y2.element_size()
         off = c.staging(nbytes, "pr")

@@ -36,7 +36,7 @@ CASES = {
 }
 
 
-def _worker(rank, world, case):
+def _worker(rank, world, case, host_heap=False):
     import sys, os
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
     from helpers import random_graph
@@ -64,6 +64,13 @@ def _worker(rank, world, case):
     gcn_blk, _ = grid.local_block(gcn_edges_with_self_loops(ei, n))
     attn_ei, attn_et = ExphormerRef.build_attention_edges(ei, exp)
     a_blk, a_et = grid.local_block(attn_ei, attn_et)
+    heap = None
+    if host_heap:                                           # peer-memory transport between the CPU ranks (shared host memory)
+        from gt_b200.parallel.collectives import set_transport
+        from gt_b200.parallel.symm_host import HostSymmetricHeap
+        heap = HostSymmetricHeap(16 << 20, wait_seconds=60.0)
+        set_transport(heap)
+        cfg.update(sparse_transport="pull", heap=heap)
     model = DistExphormer(grid, gcn_blk, a_blk, a_et, f, hid, classes, 2, heads, dropout=0.0, gnn_dropout=0.0, backend="torch", **cfg).double()
     model.load_ref_state_dict(ref.state_dict())
     set_step(0)
@@ -96,15 +103,40 @@ def _worker(rank, world, case):
     ref.eval(); model.eval()
     with torch.no_grad():
         assert (model(grid.take_owned(x))[:nv] - ref(x, ei, exp)[lo:lo + nv]).abs().max() < 1e-9
+    if heap is not None:
+        import torch.distributed as dist
+        from gt_b200.ops import native
+        heap.check_symmetric()                              # every rank made the same allocations in the same order
+        native.check_status(torch.device("cpu"))            # no wait expired
+        assert heap.alloc_log[0] > 2, "the case never used the heap"
+        dist.barrier()
+        set_transport(None)
+        heap.close()
+
+
+def _world_of(case):
+    world = 1
+    for s in CASES[case]["grid"]:
+        world *= s
+    return world
 
 
 @pytest.mark.parametrize("case", list(CASES))
 def test_dist_exphormer_matches_reference(case):
-    shape = CASES[case]["grid"]
-    world = 1
-    for s in shape:
-        world *= s
-    run_dist(_worker, world, case)
+    run_dist(_worker, _world_of(case), case)
+
+
+HEAP_CASES = ["plain_2x2", "fused_2x2", "fused_colmajor", "fused_gather_proj", "fused_sparse", "fused_ckpt", "pipelined", "streamed",
+              "streamed_sync_ckpt", "streamed_sparse", "head_2x1x2", "head_1x2x2_gcn", "head_sparse", "fused_4x2_ln", "fused_2x4_ln",
+              "head_2x2x2", "fused_3x2", "streamed_2x3"]
+
+
+@pytest.mark.parametrize("case", HEAP_CASES)
+def test_dist_exphormer_matches_reference_on_the_host_heap(case):
+    """The same parity (logits, loss, every parameter gradient, BN statistics, evaluation pass) with the dense and sparse row
+    collectives and the head all-to-all on the peer-memory transport, emulated between the CPU ranks: the heap's allocation
+    sequence, staging alternation and barriers run as they do on GPUs, in double precision."""
+    run_dist(_worker, _world_of(case), case, True)
 
 
 def _uniform_plan_worker(rank, world):

@@ -18,7 +18,7 @@ VARIANTS = {
 }
 
 
-def _variant_worker(rank, world, case):
+def _variant_worker(rank, world, case, host_heap=False):
     import os, sys
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
     from helpers import random_graph
@@ -66,6 +66,12 @@ def _variant_worker(rank, world, case):
         assert (d_in[:nvd] == ind[lo:hi]).all() and (d_out[:nvd] == outd[lo:hi]).all()
         fw = dict(degree_loc=d_in, out_degree_loc=d_out if outdeg else None)
     blk_ei, blk_et = grid.local_block(a_ei, a_et)
+    heap = None
+    if host_heap:                                           # peer-memory transport between the CPU ranks (shared host memory)
+        from gt_b200.parallel.collectives import set_transport
+        from gt_b200.parallel.symm_host import HostSymmetricHeap
+        heap = HostSymmetricHeap(16 << 20, wait_seconds=60.0)
+        set_transport(heap)
     model = gv.DistGTVariant(grid, blk_ei, blk_et, f, hid, classes, 2, heads, model=cfg["model"], dropout=0.0, backend="torch",
                              checkpoint=cfg.get("checkpoint", False), **kw).double()
     model.load_ref_state_dict(ref.state_dict())
@@ -86,14 +92,35 @@ def _variant_worker(rank, world, case):
         if gr is None:
             continue
         assert (p.grad - gr).abs().max() < 1e-8 * max(1.0, gr.abs().max().item()), name
+    if heap is not None:
+        import torch.distributed as dist
+        from gt_b200.ops import native
+        heap.check_symmetric()
+        native.check_status(torch.device("cpu"))
+        assert heap.alloc_log[0] > 2, "the case never used the heap"
+        dist.barrier()
+        set_transport(None)
+        heap.close()
+
+
+def _world_of(case):
+    world = 1
+    for s in VARIANTS[case]["grid"]:
+        world *= s
+    return world
 
 
 @pytest.mark.parametrize("case", list(VARIANTS))
 def test_variants_match_reference(case):
-    world = 1
-    for s in VARIANTS[case]["grid"]:
-        world *= s
-    run_dist(_variant_worker, world, case)
+    run_dist(_variant_worker, _world_of(case), case)
+
+
+@pytest.mark.parametrize("case", ["unimp_2x2", "unimp_head_2x1x2", "graphormer_2x2", "graphormer_khop_head_1x2x2", "unimp_label_head_2x2x2",
+                                  "graphormer_khop_ckpt_4x2"])
+def test_variants_match_reference_on_the_host_heap(case):
+    """Softmax attention (cross-rank maximum), label inputs, degree embeddings and the head axis with the row collectives on the
+    peer-memory transport emulated between the CPU ranks."""
+    run_dist(_variant_worker, _world_of(case), case, True)
 
 
 OPS = {
