@@ -232,6 +232,8 @@ class DistExphormerLayerHead(_LayerBase):
         kdt = self.kernel_dtype or x.dtype
         t = timers()
         gate = self.gate(edge_type_emb)
+        if not self.with_gcn and os.environ.get("GT_HEAD_MERGED", "1") == "0":
+            return self.tail(x, self._attention_separate(x, gate), None)
         t.start("qkv proj")
         q = K.linear(x, self.q.weight).view(n, p_i, ds)
         # weight rows interleaved per head group so that the all-to-all input [n, P_i, (2|3) ds] is a view
@@ -265,6 +267,32 @@ class DistExphormerLayerHead(_LayerBase):
         o = back[:, :, :ds].reshape(n, h * d)
         agg_rows = back[:, :, ds:].reshape(n, self.dim_h) if self.with_gcn else None
         return self.tail(x, o, agg_rows)
+
+
+    def _attention_separate(self, x, gate):
+        """``GT_HEAD_MERGED=0``, attention-only layers: Q, K and V travel separately (three all-to-alls and three gathers instead of
+        one for Q and one for the merged ``[K | V]`` tensor): the A/B switch of the layer's communication pattern
+        (``gt3d/gt3d/models/exphormer_dist.py:484-505``)."""
+        if self.sp_row is not None or self.sp_col is not None:
+            raise ValueError("GT_HEAD_MERGED=0 has no sparse-communication path")
+        g = self.grid
+        n, d, p_i, hg, ds = x.shape[0], self.d_head, g.p_heads, self.hg, self.ds
+        kdt = self.kernel_dtype or x.dtype
+        wire = self.comm_dtype
+        t = timers()
+
+        def to_block(w, group):
+            y = K.linear(x, w).view(n, p_i, ds)
+            y = rows_to_heads(y if wire is None else y.to(wire), g.head_group, p_i)
+            return _gather_rows(y, group, None).to(kdt).reshape(-1, hg, d)
+        t.start("head: a2a + gather q/k/v")
+        q_blk, k_blk, v_blk = to_block(self.q.weight, g.row_group), to_block(self.k.weight, g.col_group), to_block(self.v.weight, g.col_group)
+        t.stop("head: a2a + gather q/k/v")
+        acc, l, m = self.attn(q_blk, k_blk, v_blk, gate[:, g.h * hg:(g.h + 1) * hg].contiguous())
+        o_h, _ = combine_partials(acc, l, m, g, "clampexp", 1e-6, rs_dtype=self.rs_dtype)
+        back = o_h.reshape(-1, 1, ds)
+        back = heads_to_rows((back if wire is None else back.to(wire)).contiguous(), g.head_group, p_i).to(x.dtype)
+        return back.reshape(n, self.num_heads * d)
 
 
 class DistExphormerLayerPipelined(DistExphormerLayerFused):

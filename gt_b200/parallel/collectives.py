@@ -12,9 +12,11 @@ Every dense tensor is node-sharded ``[chunk, ...]``; the layers move rows with
 (e.g. bf16) may be given: the payload is cast for the transfer and cast back.  The raw functions run on NCCL (GPU) or
 gloo (CPU tests; gloo has no reduce-scatter, so it is emulated with an all-reduce).  The B200 fast path replaces these
 NCCL calls by kernels that read / write peer memory directly (:mod:`gt_b200.parallel.symm`); the layers select it with
-``comm="p2p"``.  Unlike the reference there is no host synchronisation before a collective: inside one NVSwitch domain
-concurrent row- and column-group traffic does not share a NIC.
+``comm="p2p"``.  Unlike the reference there is no host synchronisation before a collective by default: inside one NVSwitch
+domain concurrent row- and column-group traffic does not share a NIC (``GT_SYNC_COLLECTIVES`` switches it on).
 """
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -44,7 +46,24 @@ def _a2a_p2p_ok(x, slab_elems):
     return h is not None and h.reaches(x) and x.dtype in h._float_types() and (slab_elems * x.element_size()) % 16 == 0
 
 
+# GT_SYNC_COLLECTIVES (default 0): 1 = host-synchronise the current stream before every synchronous collective, so that the previous
+# collective, possibly on another communicator, has completed before this one is posted; 2 = also a barrier over the group.  On
+# one NVSwitch node communicators do not share a NIC and the default is off; the reference needs the synchronisation when two
+# cross-node groups share a network interface (``gt3d/gt3d/dist/grid2d.py:55-69``, default on there), and multi-node runs of this
+# package on NCCL can switch it on for the same reason.  Asynchronous gathers are never synchronised.
+SYNC_COLLECTIVES = int(os.environ.get("GT_SYNC_COLLECTIVES", "0"))
+
+
+def _pre_collective(group):
+    if SYNC_COLLECTIVES and torch.cuda.is_available() and not torch.cuda.is_current_stream_capturing():
+        torch.cuda.current_stream().synchronize()
+        if SYNC_COLLECTIVES >= 2 and group_size(group) > 1:
+            dist.barrier(group=group)
+
+
 def _instrument(kind, group, nbytes, fn):
+    if SYNC_COLLECTIVES:
+        _pre_collective(group)
     hook = _STATS_HOOK[0]
     if hook is None:
         return fn()

@@ -2,6 +2,8 @@
 gradient all-reduce.  Dense inputs and outputs are the owned chunk ``[chunk, ...]``; padded rows are kept out of
 statistics and losses through ``grid.valid_mask``.  Semantics follow ``gt3d/gt3d/dist/layers.py:67-324``.
 """
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -148,9 +150,17 @@ class DistBatchNorm1d(torch.nn.Module):
 
     def forward(self, x):
         if self.training:
-            return self.apply_stats(x, all_reduce_sum(self.local_stats(x)))
+            return self.apply_stats(x, _stats_sum(self.local_stats(x)))
         mean, var = self.running_mean.to(x.dtype), self.running_var.to(x.dtype)
         return (x - mean) * torch.rsqrt(var + self.eps) * self.weight.to(x.dtype) + self.bias.to(x.dtype)
+
+
+def _stats_sum(stats):
+    """Sum of the BatchNorm statistics over all ranks.  ``GT_BN_NO_SYNC=1`` skips the all-reduces (forward and backward): a timing
+    ablation with rank-local, i.e. wrong, statistics (the reference's ``GT3D_BN_NO_SYNC``, ``gt3d/gt3d/dist/layers.py:44-45``)."""
+    if os.environ.get("GT_BN_NO_SYNC", "0") == "1":
+        return stats
+    return all_reduce_sum(stats)
 
 
 def dist_batchnorm_pair(bn_a, x_a, bn_b, x_b):
@@ -158,7 +168,7 @@ def dist_batchnorm_pair(bn_a, x_a, bn_b, x_b):
     if not bn_a.training:
         return bn_a(x_a), bn_b(x_b)
     d = x_a.shape[1]
-    stats = all_reduce_sum(torch.cat([bn_a.local_stats(x_a), bn_b.local_stats(x_b)]))
+    stats = _stats_sum(torch.cat([bn_a.local_stats(x_a), bn_b.local_stats(x_b)]))
     return bn_a.apply_stats(x_a, stats[:2 * d]), bn_b.apply_stats(x_b, stats[2 * d:])
 
 

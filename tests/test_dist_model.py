@@ -30,6 +30,7 @@ CASES = {
     "fused_4x2_ln": dict(grid=(4, 2), fused=True, norm="ln"),
     "fused_2x4_ln": dict(grid=(2, 4), fused=True, norm="ln"),
     "head_2x2x2": dict(grid=(2, 2, 2)),
+    "head_separate_qkv_2x1x2": dict(grid=(2, 1, 2), with_gcn=False, env={"GT_HEAD_MERGED": "0"}),
     # grids whose factors are not powers of two
     "fused_3x2": dict(grid=(3, 2), fused=True),
     "streamed_2x3": dict(grid=(2, 3), fused=True, stream_sub=2),
@@ -46,6 +47,7 @@ def _worker(rank, world, case, host_heap=False):
     from gt_b200.parallel.grid import make_grid
     from gt_b200.parallel.layers import allreduce_grads, dist_cross_entropy, set_step
     cfg = dict(CASES[case])
+    os.environ.update(cfg.pop("env", {}))
     grid_shape = cfg.pop("grid")
     layout = cfg.pop("layout", "row_major")
     n, f, hid, classes, heads = 94, 12, 16, 5, 4
@@ -160,3 +162,36 @@ def _uniform_plan_worker(rank, world):
 
 def test_plan_shares_and_staging_sizes_agree_across_groups():
     run_dist(_uniform_plan_worker, 4)
+
+
+def _bn_no_sync_worker(rank, world):
+    """``GT_BN_NO_SYNC=1``: the statistics stay rank-local (a timing ablation), forward and backward run without a collective."""
+    import os
+    os.environ["GT_BN_NO_SYNC"] = "1"
+    from gt_b200.parallel.grid import make_grid
+    from gt_b200.parallel.layers import DistBatchNorm1d, set_step
+    grid = make_grid((2, 1), 32, n_pad=32)
+    torch.manual_seed(rank)
+    x = torch.randn(16, 8, dtype=torch.float64, requires_grad=True)
+    bn = DistBatchNorm1d(grid, 8).double()
+    set_step(0)
+    bn.train()
+    import torch.distributed as dist
+    real = dist.all_reduce
+
+    def forbidden(*a, **k):
+        raise AssertionError("a collective ran although GT_BN_NO_SYNC=1")
+    dist.all_reduce = forbidden
+    try:
+        out = bn(x)
+        out.square().sum().backward()
+    finally:
+        dist.all_reduce = real
+    mean = x.detach().sum(0) / 32                            # local sums over the global node count: wrong on purpose
+    var = (x.detach() ** 2).sum(0) / 32 - mean * mean
+    assert (out.detach() - (x.detach() - mean) * torch.rsqrt(var + bn.eps)).abs().max() < 1e-10
+    assert x.grad is not None and torch.isfinite(x.grad).all()
+
+
+def test_bn_no_sync_switch_keeps_the_statistics_local():
+    run_dist(_bn_no_sync_worker, 2)
