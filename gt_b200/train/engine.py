@@ -72,8 +72,8 @@ class TrainEngine:
         n = -(-n // 8) * 8
         self.numel = n
         self.flat_p = torch.zeros(n, dtype=torch.float32, device=dev)
-        self.flat_g = heap.empty(n, torch.float32, "grads") if (heap is not None and self.cuda) else \
-            torch.zeros(n, dtype=torch.float32, device=dev)
+        self.on_heap = heap is not None and (self.cuda or heap.host)     # gradients live in the symmetric heap, reduced by its kernels
+        self.flat_g = heap.empty(n, torch.float32, "grads") if self.on_heap else torch.zeros(n, dtype=torch.float32, device=dev)
         self.flat_m = torch.zeros_like(self.flat_p)
         self.flat_v = torch.zeros_like(self.flat_p)
         # bf16 shadow of the parameters, refreshed by the optimizer kernel: the GEMMs read it instead of casting every step
@@ -99,6 +99,8 @@ class TrainEngine:
             self._hyper_slots = torch.zeros(self.HYPER_SLOTS, 8, dtype=torch.float32).pin_memory()
             self._hyper_events = [None] * self.HYPER_SLOTS
             self.g_sum = heap.empty(self.numel, torch.float32, "grads_sum") if heap is not None else None
+        elif self.on_heap:
+            self.g_sum = heap.empty(self.numel, torch.float32, "grads_sum")
         self.use_graph = use_graph and self.cuda
         self.graph_warmup = graph_warmup
         self._graph = None
@@ -126,7 +128,7 @@ class TrainEngine:
     def _reduce_grads(self):
         if self.world == 1:
             return self.flat_g
-        if self.heap is not None and self.cuda:
+        if self.on_heap:
             if self.world <= 8 and os.environ.get("GT_GRAD_ALLREDUCE", "two_shot") == "two_shot":
                 # one kernel per rank: reduce my slice from every member, store it to every member (2 n bytes per rank, no barrier)
                 self.heap.all_reduce_two_shot("grads", "grads_sum", self.numel, group=self.group)

@@ -85,7 +85,8 @@ def build_parser():
     a("--ffn_mult", type=int, default=2)
     a("--khop", action="store_true", help="(graphormer) 2-hop mask with shortest-path-bucket bias and in/out-degree embeddings")
     # communication
-    a("--comm", default="nccl", choices=["nccl", "p2p"], help="grid collectives: NCCL or the peer-memory kernels (symmetric heap)")
+    a("--comm", default="nccl", choices=["nccl", "p2p"],
+      help="grid collectives: NCCL (gloo on CPU ranks) or the peer-memory transport (symmetric heap; between CPU ranks an emulation over shared host memory)")
     a("--heap_mb", type=int, default=2048)
     a("--nccl_tune", default="auto", choices=["auto", "on", "off"])
     a("--sparse_comm", action="store_true")
@@ -246,9 +247,13 @@ def main(argv=None):
     if args.timers:
         enable_timers(True)
     heap = None
-    if args.comm == "p2p" and cuda and world > 1:
-        from ..parallel.symm import SymmetricHeap
-        heap = SymmetricHeap(dev, args.heap_mb << 20)
+    if args.comm == "p2p" and world > 1:
+        if cuda:
+            from ..parallel.symm import SymmetricHeap
+            heap = SymmetricHeap(dev, args.heap_mb << 20)
+        else:                                               # CPU ranks of one machine: the same heap logic over shared host memory
+            from ..parallel.symm_host import HostSymmetricHeap
+            heap = HostSymmetricHeap(args.heap_mb << 20)
         set_transport(heap)
 
     def mem(tag, model=None):
@@ -505,6 +510,11 @@ def main(argv=None):
               f"grid={'x'.join(map(str, args.grid))} world={world}", flush=True)
         print(f"STEADY model={args.model} grid={'x'.join(map(str, args.grid))} world={world} hidden={args.hidden} layers={args.layers} "
               f"ms_per_epoch={sum(steady) / max(len(steady), 1):.2f} peak_gb={peak.item():.2f} timing=device_max_over_ranks", flush=True)
+    if heap is not None and heap.host:                       # unmap and delete the shared files once every rank is done with them
+        native.check_status(dev)
+        dist.barrier()
+        set_transport(None)
+        heap.close()
     return dict(best=best, epoch_ms=epoch_ms)
 
 

@@ -196,3 +196,28 @@ def test_metrics_jsonl(tmp_path):
     rows = [json.loads(l) for l in mf.read_text().splitlines()]
     assert [r["epoch"] for r in rows] == [0, 2, 3] and all(r["epoch_ms"] > 0 and 0 <= r["val"] <= 1 for r in rows)
     assert rows[-1]["best_val"] >= rows[0]["val"] and rows[0]["grid"] == [1, 1]
+
+
+def _p2p_worker(rank, world, argv, out_path):
+    """The same run on gloo collectives and on the peer-memory transport (emulated between the CPU ranks): the losses agree."""
+    from gt_b200.train.train_dist import main
+    a = main(argv + ["--metrics_jsonl", out_path + ".gloo"])
+    b = main(argv + ["--comm", "p2p", "--heap_mb", "64", "--metrics_jsonl", out_path + ".p2p"])
+    assert len(a["epoch_ms"]) == len(b["epoch_ms"])
+    assert abs(a["best"]["val"] - b["best"]["val"]) < 1e-6
+
+
+@pytest.mark.parametrize("argv", [
+    ["--grid", "2", "2", "--synthetic", "cpu_small", "--scale_down", "4", "--fused", "--epochs", "4", "--norm", "ln", "--dropout", "0.0"],
+    ["--grid", "2", "2", "--synthetic", "cpu_small", "--scale_down", "4", "--fused", "--epochs", "4", "--sparse_comm", "--sparse_threshold", "1.0",
+     "--dropout", "0.0"],
+    ["--grid", "2", "1", "2", "--synthetic", "cpu_small", "--scale_down", "4", "--no_gcn", "--epochs", "4", "--heads", "4", "--dropout", "0.0"],
+], ids=["fused_2x2", "sparse_2x2", "head_2x1x2"])
+def test_cli_comm_p2p_between_cpu_ranks_matches_gloo(argv, tmp_path):
+    import json
+    out = str(tmp_path / "m")
+    run_dist(_p2p_worker, 4, argv, out)
+    rows = {k: [json.loads(line) for line in open(out + "." + k)] for k in ("gloo", "p2p")}
+    assert len(rows["gloo"]) == len(rows["p2p"]) > 0
+    for ra, rb in zip(rows["gloo"], rows["p2p"]):
+        assert abs(ra["loss"] - rb["loss"]) < 1e-4 * max(1.0, abs(ra["loss"])), (ra, rb)
