@@ -59,7 +59,8 @@ def _round8(n):
 def branch_supported(layer, x):
     g = layer.grid
     h, dh, d = layer.num_heads, layer.d_head, layer.dim_h
-    if not (x.is_cuda and x.dtype == torch.bfloat16 and layer.kernel_dtype in (None, torch.bfloat16)):
+    on_device = x.is_cuda or (_HEAP[0] is not None and _HEAP[0].host)      # host: the emulated transport between CPU ranks (tests)
+    if not (on_device and x.dtype == torch.bfloat16 and layer.kernel_dtype in (None, torch.bfloat16)):
         return False
     if getattr(layer, "sp_row", None) is not None or getattr(layer, "sp_col", None) is not None or layer.gather_proj:
         return False

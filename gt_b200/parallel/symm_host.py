@@ -11,8 +11,9 @@ flags are real words in shared memory, and every wait is bounded and records ``1
 
 What it is for: the multi-rank logic of the transport can be tested where there are fewer GPUs than ranks, or none
 (``tests/test_host_heap.py``: every collective against gloo on 2 x 2 grids with unequal row groups, the allocation logs of all
-ranks compared, and the distributed model parity cases in double precision with the heap transport switched on).  What it does not
-cover: the device kernels themselves (their index arithmetic, the in-kernel waits of the fused layer), which the GPU tests cover.
+ranks compared, the distributed model parity cases in double precision with the heap transport switched on, and the fused 2D
+layer as one operator, whose kernels :mod:`gt_b200.parallel.fused_host` restates in torch, on grids up to 4 x 2).  What it does
+not cover: the device kernels themselves (their index arithmetic, their memory ordering on a GPU), which the GPU tests cover.
 
 The reference's pull collectives have no host mode (``gt3d/gt3d/dist/pullcomm/__init__.py:40-80`` needs NVSHMEM and GPUs).
 """
@@ -24,6 +25,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops import native
+from .fused_host import FusedKernelsHost
 from .symm import SymmetricHeap
 
 _SHIFT = 44
@@ -31,8 +33,9 @@ _MASK = (1 << _SHIFT) - 1
 _TYPES = {0: torch.float32, 1: torch.bfloat16, 2: torch.int32, 3: torch.int64, 4: torch.uint8, 5: torch.float64}
 
 
-class HostExt:
-    """The entry points of the native module that the symmetric heap uses, on shared host memory."""
+class HostExt(FusedKernelsHost):
+    """The entry points of the native module that the symmetric heap uses, on shared host memory (plus, from the mixin, the
+    kernels of the fused layer restated in torch)."""
 
     def __init__(self, rank, wait_seconds=20.0):
         self.rank, self.wait_seconds = int(rank), float(wait_seconds)

@@ -102,3 +102,101 @@ def _expiry_worker(rank, world):
 
 def test_a_silent_rank_expires_the_barrier_with_its_index():
     run_dist(_expiry_worker, 3)
+
+
+def _fused_worker(rank, world, grid_shape, cfg):
+    """The fused 2D layer as ONE operator with its collectives inside the (emulated) kernels, bf16, against the fp64 reference model:
+    logits, loss and every parameter gradient, two steps in a row (every staging copy and channel is reused)."""
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    import torch.distributed as dist
+    from helpers import random_graph
+    from test_gpu_parity import TOL, _grad_err, _grad_floor
+    from gt_b200.data.expander import random_regular_expander_edges
+    from gt_b200.models.exphormer_dist import DistExphormer
+    from gt_b200.models.exphormer_ref import ExphormerRef, gcn_edges_with_self_loops
+    from gt_b200.ops import native
+    from gt_b200.parallel import fused_layer
+    from gt_b200.parallel.collectives import set_transport
+    from gt_b200.parallel.grid import make_grid
+    from gt_b200.parallel.layers import dist_cross_entropy, set_step
+    from gt_b200.parallel.symm_host import HostSymmetricHeap
+    from gt_b200.train.engine import TrainEngine
+    cfg = dict(cfg)
+    n, f, hid, classes, heads = 500, 16, 64, 8, 4
+    torch.manual_seed(0)
+    ei, _ = random_graph(n, 4, seed=3, hub=True, empty=())
+    ei = ei[:, ei[0] != ei[1]]
+    exp = random_regular_expander_edges(n, 3, seed=1)
+    x = torch.randn(n, f, dtype=torch.float64)
+    y = torch.randint(0, classes, (n,))
+    mask = torch.rand(n) < 0.6
+    with_gcn = cfg.get("with_gcn", True)
+    ref = ExphormerRef(f, hid, classes, 2, heads, dropout=0.0, gnn_dropout=0.0, with_gcn=with_gcn, norm="ln").double()
+    n_pad = -(-n // (16 * world)) * (16 * world)
+    grid = make_grid(grid_shape, n, n_pad=n_pad)
+    gcn_blk, _ = grid.local_block(gcn_edges_with_self_loops(ei, n))
+    attn_ei, attn_et = ExphormerRef.build_attention_edges(ei, exp)
+    a_blk, a_et = grid.local_block(attn_ei, attn_et)
+    heap = HostSymmetricHeap(32 << 20, wait_seconds=60.0)
+    set_transport(heap)
+    bf = torch.bfloat16
+    model = DistExphormer(grid, gcn_blk, a_blk, a_et, f, hid, classes, 2, heads, dropout=0.0, gnn_dropout=0.0, backend="torch", fused=True,
+                          norm="ln", comm_dtype=bf, rs_dtype=bf, kernel_dtype=bf, heap=heap, **cfg)
+    model.load_ref_state_dict(ref.state_dict())
+    eng = TrainEngine(model, heap=heap)
+    calls = {"n": 0}
+    real = fused_layer._FusedBranch.apply
+
+    def counted(*a):
+        calls["n"] += 1
+        return real(*a)
+    fused_layer._FusedBranch.apply = counted
+    set_step(0)
+    ref.train(); model.train()
+    out_ref = ref(x, ei, exp)
+    loss_ref = torch.nn.functional.cross_entropy(out_ref[mask], y[mask], reduction="sum") / int(mask.sum())
+    loss_ref.backward()
+    ref_grads = dict(ref.named_parameters())
+    floor = _grad_floor(ref_grads)
+    tol_f, tol_g = TOL[bf]
+    lo, hi = grid.owned_range()
+    nv = max(min(hi, n) - lo, 0)
+    failures = []
+    for step in range(2):
+        dist.barrier()
+        heap.begin_step()
+        eng.flat_g.zero_()
+        out = model(grid.take_owned(x).to(bf))
+        err = (out[:nv].double() - out_ref[lo:lo + nv]).abs().max().item() / out_ref.abs().max().item() if nv else 0.0
+        m_loc = grid.take_owned(mask.to(torch.uint8)).bool() & grid.valid_mask
+        loss = dist_cross_entropy(out, grid.take_owned(y), m_loc, int(mask.sum()))
+        loss.backward()
+        tot = loss.detach().float().clone()
+        dist.all_reduce(tot)
+        g = eng._reduce_grads()                               # the two-shot all-reduce of the heap
+        if err >= tol_f:
+            failures.append(("logits", step, err))
+        if abs(tot.item() - loss_ref.item()) >= tol_f * max(1.0, abs(loss_ref.item())) * 4:
+            failures.append(("loss", step, tot.item(), loss_ref.item()))
+        for pname, p in model.named_parameters():
+            gr = ref_grads[pname].grad
+            if gr is None:
+                continue
+            off = eng.offsets[id(p)]
+            e_ = _grad_err(g[off:off + p.numel()].view_as(p), gr, floor)
+            if e_ >= tol_g:
+                failures.append((pname, step, e_))
+    native.check_status(torch.device("cpu"))
+    heap.check_symmetric()
+    assert calls["n"] == 2 * 2, calls                         # two layers, two steps: the operator ran, not the op-by-op fallback
+    assert not failures, failures
+    dist.barrier()
+    set_transport(None)
+    heap.close()
+
+
+@pytest.mark.parametrize("grid_shape,cfg", [((2, 2), {}), ((2, 1), {}), ((1, 2), {}), ((4, 2), {}), ((2, 4), {}), ((2, 2), dict(with_gcn=False)),
+                                            ((3, 2), {})],
+                         ids=["2x2", "2x1", "1x2", "4x2", "2x4", "2x2_nogcn", "3x2"])
+def test_fused_operator_with_in_kernel_collectives_between_cpu_ranks(grid_shape, cfg):
+    run_dist(_fused_worker, grid_shape[0] * grid_shape[1], grid_shape, cfg)
