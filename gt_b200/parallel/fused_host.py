@@ -66,6 +66,7 @@ class FusedKernelsHost:
         for i, ptr in enumerate(peer_ptrs):
             if flags is not None and i != me:
                 self._wait_one(flags, i, want, status)
+            self._access("read", ptr)
             a = self._typed(ptr, chunk * k, torch.bfloat16).view(chunk, k)
             if gathered is not None:
                 gathered[i * chunk:(i + 1) * chunk] = a
@@ -77,6 +78,7 @@ class FusedKernelsHost:
             raise NotImplementedError("strided slots")
         for i, ptr in enumerate(slot_ptrs):
             y = a[i * chunk:(i + 1) * chunk].float() @ b.float().t()
+            self._access("write", ptr)
             self._typed(ptr, chunk * n, torch.bfloat16).view(chunk, n).copy_(y)
 
     # ---- attention, gated scores and clamp-exp weights, partial form --------------------------------------------------------------
@@ -105,6 +107,7 @@ class FusedKernelsHost:
             l.copy_(l + s if accumulate else s)
             return
         for i, ptr in enumerate(push_ptrs):                  # rows of owner i go into MY slot of owner i's payload buffer
+            self._access("write", ptr)
             slot = self._typed(ptr, push_rows * push_ld, torch.bfloat16).view(push_rows, push_ld)
             lo_r = i * push_rows
             slot[:, :h * d] = a[lo_r:lo_r + push_rows]
@@ -164,13 +167,14 @@ class FusedKernelsHost:
             return
         for i, p in enumerate(push_ptrs):                    # the pointer already addresses the aggregation columns of my slot
             width = x.shape[1]
+            self._access("write", p)
             flat = self._typed(p, (push_rows - 1) * push_ld + width, torch.bfloat16)
             torch.as_strided(flat, (push_rows, width), (push_ld, 1)).copy_(y[i * push_rows:(i + 1) * push_rows])
 
     # ---- payload packing and the owner-side sums -----------------------------------------------------------------------------------
-    @staticmethod
-    def pack_cols(parts, packed, to_packed):
+    def pack_cols(self, parts, packed, to_packed):
         c = 0
+        self._access("write" if to_packed else "read", packed)
         for t in parts:
             w = t.shape[1]
             if to_packed:
@@ -180,6 +184,8 @@ class FusedKernelsHost:
             c += w
 
     def _wait_one(self, flags, p, want, status):
+        if self.log is not None:
+            self._note("wait", self._place(flags)[1], p)
         deadline = time.monotonic() + self.wait_seconds
         while int(flags[p]) < want:
             if time.monotonic() > deadline:
@@ -190,6 +196,7 @@ class FusedKernelsHost:
     def sum_payload(self, slots, acc, l, agg, l_off, agg_off, flags, counter, max_spins, status):
         if flags is not None:
             self._wait(flags, slots.shape[0], int(counter), status)
+        self._access("read", slots)
         s = slots.float().sum(0)
         acc.copy_(s[:, :acc.shape[1]])
         l.copy_(s[:, l_off:l_off + l.shape[1]])
@@ -202,6 +209,7 @@ class FusedKernelsHost:
         hd, h = row_vec.shape[1], stat.shape[1]
         stat.zero_()
         for i, ptr in enumerate(src_ptrs):
+            self._access("read", ptr)
             pay = self._typed(ptr, rows_per_peer * width, torch.bfloat16).view(rows_per_peer, width)
             r = slice(i * rows_per_peer, (i + 1) * rows_per_peer)
             row_vec[r] = pay[:, :hd]
@@ -212,6 +220,7 @@ class FusedKernelsHost:
     def sum_slots_wait(self, slots, out, accumulate, flags, counter, max_spins, status):
         if flags is not None:
             self._wait(flags, slots.shape[0], int(counter), status)
+        self._access("read", slots)
         s = slots.float().sum(0).view(out.shape)
         out.copy_(out.float() + s if accumulate else s)
 

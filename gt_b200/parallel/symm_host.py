@@ -42,6 +42,29 @@ class HostExt(FusedKernelsHost):
         self.segments = {}                                   # base address -> uint8 tensor over the mapped file
         self.paths = {}
         self._mod = self                                     # native.check_status looks for optional entry points here
+        self.log = None                                      # a list: record every access to heap memory and every signal / wait
+
+    # ---- recording (tests compare the recorded sequence with the protocol model) -----------------------------------------------------
+    def _note(self, *event):
+        if self.log is not None:
+            self.log.append(event)
+
+    def _place(self, where):
+        """``(owner rank, offset)`` of an address or of a tensor that lives in a mapped heap; ``None`` for other tensors."""
+        if isinstance(where, torch.Tensor) and where.numel() != 1:
+            a = where.data_ptr()
+            for base, seg in self.segments.items():
+                if seg.data_ptr() <= a < seg.data_ptr() + seg.numel():
+                    return (base >> _SHIFT) - 1, a - seg.data_ptr()
+            return None
+        ptr = int(where)
+        return (ptr >> _SHIFT) - 1, ptr & _MASK
+
+    def _access(self, kind, where):
+        if self.log is not None:
+            at = self._place(where)
+            if at is not None:
+                self.log.append((kind,) + at)
 
     # ---- heap management ---------------------------------------------------------------------------------------------------
     def heap_alloc(self, nbytes):
@@ -82,15 +105,18 @@ class HostExt(FusedKernelsHost):
         return seg[off:off + nbytes].view(dtype)
 
     def tensor_from_ptr(self, ptr, shape, dtype_code, device_index):
+        self._access("view", ptr)
         n = 1
         for s in shape:
             n *= int(s)
         return self._typed(ptr, n, _TYPES[int(dtype_code)]).view(*shape)
 
     # ---- ordering ----------------------------------------------------------------------------------------------------------
-    def _wait(self, flags, n_peers, epoch, status):
+    def _wait(self, flags, n_peers, epoch, status, note=True):
         deadline = time.monotonic() + self.wait_seconds
         for p in range(n_peers):
+            if note and self.log is not None:
+                self._note("wait", self._place(flags)[1], p)
             while int(flags[p]) < epoch:
                 if time.monotonic() > deadline:
                     status.fill_(100 + p)
@@ -103,11 +129,14 @@ class HostExt(FusedKernelsHost):
         n = peer_flag_ptrs.numel()
         for p in range(n):
             self._typed(peer_flag_ptrs[p], 64, torch.int32)[me] = epoch
-        self._wait(my_flags, n, epoch, status)
+        if self.log is not None:
+            self._note("barrier", self._place(my_flags)[1])
+        self._wait(my_flags, n, epoch, status, note=False)
 
     def channel_signal(self, ptrs, me, counter):
         epoch = int(counter) + 1
         counter.fill_(epoch)
+        self._note("signal", int(ptrs[0]) & _MASK)
         for p in ptrs:
             self._typed(p, 8, torch.int32)[me] = epoch
 
@@ -179,8 +208,10 @@ class HostExt(FusedKernelsHost):
             return
         acc = torch.zeros(hi - lo, dtype=torch.float32)
         for p in src:
+            self._access("read", p)
             acc += self._typed(p, n, torch.float32)[lo:hi]
         for p in dst:
+            self._access("write", p)
             self._typed(p, n, torch.float32)[lo:hi] = acc
 
 

@@ -104,6 +104,76 @@ def test_a_silent_rank_expires_the_barrier_with_its_index():
     run_dist(_expiry_worker, 3)
 
 
+FAMILIES = ("x_col", "x_row", "pay", "dpay", "dx_col", "dx_row")
+
+
+def _compare_with_protocol_model(log, model, grid, rank):
+    """The sequence of writes, reads, signals and waits that the operator made on shared memory equals the program of this rank in
+    ``gt_b200.parallel.protocol_model`` (the input of the happens-before check): the model describes the code."""
+    from gt_b200.parallel import protocol_model as pm
+    comms = [layer._fb_comm for layer in model.layers]
+    chan = {}
+    for li, c in enumerate(comms):
+        for fam in FAMILIES:
+            ch = getattr(c, fam)
+            chan[ch.off] = (fam + str(li), ch.ctx.ranks)
+    bufs = []
+    for ctx in (comms[0].col, comms[0].row):
+        for key, (off, nbytes) in ctx.buffers.items():
+            if isinstance(key, tuple) and isinstance(key[0], str) and key[0].startswith("fb_"):
+                slots = ctx.size if key[0] in ("fb_pay", "fb_dxc", "fb_dxr") else 1
+                bufs.append((off, nbytes, key[0], key[1], slots))
+
+    def locate(off):
+        for base, nbytes, kind, copy, slots in bufs:
+            if base <= off < base + nbytes:
+                return kind, copy, slots, (off - base) // (nbytes // slots)
+        return None
+
+    got, since_signal = [], set()
+    for ev in log:
+        if ev[0] == "signal":
+            if ev[1] in chan:
+                got.append(("signal", chan[ev[1]][0]))
+                since_signal = set()
+        elif ev[0] == "wait":
+            if ev[1] in chan:
+                name, ranks = chan[ev[1]]
+                got.append(("wait", name, ranks[ev[2]]))
+        elif ev[0] in ("view", "write", "read"):
+            at = locate(ev[2])
+            if at is None:
+                continue
+            kind, copy, slots, slot = at
+            if ev[0] == "view":
+                if kind == "fb_x" and ev[1] == rank:         # x is copied into its staging buffer through a tensor view
+                    got.append(("write", rank, kind, copy, None))
+                continue
+            if ev[0] == "read" and slots > 1:                # the owner reads all slots of the buffer in one kernel
+                got.extend(("read", ev[1], kind, copy, s_) for s_ in range(slots))
+                continue
+            item = (ev[0], ev[1], kind, copy, slot if slots > 1 else None)
+            if ev[0] == "write":
+                if item in since_signal:                     # attention rows and aggregation rows go into the same slot
+                    continue
+                since_signal.add(item)
+            got.append(item)
+    want = []
+    prog = pm.fused_step_trace(grid.p_rows, grid.p_cols, len(comms), steps=2).prog[rank]
+    for op, a, b, _, _ in prog:
+        if op in ("write", "read"):
+            if len(b) > 1 and isinstance(b[1], str) and b[1].startswith("fb_"):
+                want.append((op, a, b[1], b[2], b[3] if len(b) > 3 else None))
+        elif op == "signal":
+            if a[0].rstrip("0123456789") in FAMILIES:
+                want.append(("signal", a[0]))
+        elif a[0].rstrip("0123456789") in FAMILIES:
+            want.append(("wait", a[0], b))
+    assert len(got) == len(want), (len(got), len(want))
+    for i, (g_, w_) in enumerate(zip(got, want)):
+        assert g_ == w_, (i, g_, w_)
+
+
 def _fused_worker(rank, world, grid_shape, cfg):
     """The fused 2D layer as ONE operator with its collectives inside the (emulated) kernels, bf16, against the fp64 reference model:
     logits, loss and every parameter gradient, two steps in a row (every staging copy and channel is reused)."""
@@ -162,6 +232,7 @@ def _fused_worker(rank, world, grid_shape, cfg):
     lo, hi = grid.owned_range()
     nv = max(min(hi, n) - lo, 0)
     failures = []
+    native.ext().log = []                                     # record what the operator does to shared memory, in order
     for step in range(2):
         dist.barrier()
         heap.begin_step()
@@ -190,6 +261,7 @@ def _fused_worker(rank, world, grid_shape, cfg):
     heap.check_symmetric()
     assert calls["n"] == 2 * 2, calls                         # two layers, two steps: the operator ran, not the op-by-op fallback
     assert not failures, failures
+    _compare_with_protocol_model(native.ext().log, model, grid, rank)
     dist.barrier()
     set_transport(None)
     heap.close()
