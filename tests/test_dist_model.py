@@ -133,12 +133,22 @@ HEAP_CASES = ["plain_2x2", "fused_2x2", "fused_colmajor", "fused_gather_proj", "
               "head_2x2x2", "fused_3x2", "streamed_2x3"]
 
 
-@pytest.mark.parametrize("case", HEAP_CASES)
-def test_dist_exphormer_matches_reference_on_the_host_heap(case):
+def _heap_cases_worker(rank, world, cases):
+    import torch.distributed as dist
+    for case in cases:                                       # one set of processes per world size: a fresh heap and grid per case
+        try:
+            _worker(rank, world, case, True)
+        except Exception as exc:
+            raise AssertionError(f"case {case}: {type(exc).__name__}: {exc}") from exc
+        dist.barrier()
+
+
+@pytest.mark.parametrize("world", sorted({_world_of(c) for c in HEAP_CASES}))
+def test_dist_exphormer_matches_reference_on_the_host_heap(world):
     """The same parity (logits, loss, every parameter gradient, BN statistics, evaluation pass) with the dense and sparse row
     collectives and the head all-to-all on the peer-memory transport, emulated between the CPU ranks: the heap's allocation
     sequence, staging alternation and barriers run as they do on GPUs, in double precision."""
-    run_dist(_worker, _world_of(case), case, True)
+    run_dist(_heap_cases_worker, world, [c for c in HEAP_CASES if _world_of(c) == world], timeout=900)
 
 
 def _uniform_plan_worker(rank, world):

@@ -115,12 +115,25 @@ def test_variants_match_reference(case):
     run_dist(_variant_worker, _world_of(case), case)
 
 
-@pytest.mark.parametrize("case", ["unimp_2x2", "unimp_head_2x1x2", "graphormer_2x2", "graphormer_khop_head_1x2x2", "unimp_label_head_2x2x2",
-                                  "graphormer_khop_ckpt_4x2"])
-def test_variants_match_reference_on_the_host_heap(case):
+HEAP_VARIANTS = ["unimp_2x2", "unimp_head_2x1x2", "graphormer_2x2", "graphormer_khop_head_1x2x2", "unimp_label_head_2x2x2",
+                 "graphormer_khop_ckpt_4x2"]
+
+
+def _heap_variants_worker(rank, world, cases):
+    import torch.distributed as dist
+    for case in cases:                                       # one set of processes per world size: a fresh heap and grid per case
+        try:
+            _variant_worker(rank, world, case, True)
+        except Exception as exc:
+            raise AssertionError(f"case {case}: {type(exc).__name__}: {exc}") from exc
+        dist.barrier()
+
+
+@pytest.mark.parametrize("world", sorted({_world_of(c) for c in HEAP_VARIANTS}))
+def test_variants_match_reference_on_the_host_heap(world):
     """Softmax attention (cross-rank maximum), label inputs, degree embeddings and the head axis with the row collectives on the
     peer-memory transport emulated between the CPU ranks."""
-    run_dist(_variant_worker, _world_of(case), case, True)
+    run_dist(_heap_variants_worker, world, [c for c in HEAP_VARIANTS if _world_of(c) == world], timeout=900)
 
 
 OPS = {

@@ -259,6 +259,7 @@ def _fused_worker(rank, world, grid_shape, cfg):
                 failures.append((pname, step, e_))
     native.check_status(torch.device("cpu"))
     heap.check_symmetric()
+    fused_layer._FusedBranch.apply = real
     assert calls["n"] == 2 * 2, calls                         # two layers, two steps: the operator ran, not the op-by-op fallback
     assert not failures, failures
     _compare_with_protocol_model(native.ext().log, model, grid, rank)
@@ -267,8 +268,19 @@ def _fused_worker(rank, world, grid_shape, cfg):
     heap.close()
 
 
-@pytest.mark.parametrize("grid_shape,cfg", [((2, 2), {}), ((2, 1), {}), ((1, 2), {}), ((4, 2), {}), ((2, 4), {}), ((2, 2), dict(with_gcn=False)),
-                                            ((3, 2), {})],
-                         ids=["2x2", "2x1", "1x2", "4x2", "2x4", "2x2_nogcn", "3x2"])
-def test_fused_operator_with_in_kernel_collectives_between_cpu_ranks(grid_shape, cfg):
-    run_dist(_fused_worker, grid_shape[0] * grid_shape[1], grid_shape, cfg)
+FUSED_GRIDS = [((2, 2), {}), ((2, 1), {}), ((1, 2), {}), ((4, 2), {}), ((2, 4), {}), ((2, 2), dict(with_gcn=False)), ((3, 2), {})]
+
+
+def _fused_cases_worker(rank, world, cases):
+    import torch.distributed as dist
+    for grid_shape, cfg in cases:                            # one set of processes per world size: a fresh heap, grid and model per case
+        try:
+            _fused_worker(rank, world, grid_shape, cfg)
+        except Exception as exc:
+            raise AssertionError(f"grid {grid_shape} {cfg}: {type(exc).__name__}: {exc}") from exc
+        dist.barrier()
+
+
+@pytest.mark.parametrize("world", sorted({g[0] * g[1] for g, _ in FUSED_GRIDS}))
+def test_fused_operator_with_in_kernel_collectives_between_cpu_ranks(world):
+    run_dist(_fused_cases_worker, world, [(g, c) for g, c in FUSED_GRIDS if g[0] * g[1] == world], timeout=900)
