@@ -17,6 +17,7 @@ not cover: the device kernels themselves (their index arithmetic, their memory o
 
 The reference's pull collectives have no host mode (``gt3d/gt3d/dist/pullcomm/__init__.py:40-80`` needs NVSHMEM and GPUs).
 """
+import atexit
 import os
 import tempfile
 import time
@@ -31,6 +32,13 @@ from .symm import SymmetricHeap
 _SHIFT = 44
 _MASK = (1 << _SHIFT) - 1
 _TYPES = {0: torch.float32, 1: torch.bfloat16, 2: torch.int32, 3: torch.int64, 4: torch.uint8, 5: torch.float64}
+
+
+def _unlink(path):
+    try:
+        os.unlink(path)
+    except OSError:
+        pass
 
 
 class HostExt(FusedKernelsHost):
@@ -75,6 +83,7 @@ class HostExt(FusedKernelsHost):
         base = (self.rank + 1) << _SHIFT
         self.segments[base] = torch.from_file(path, shared=True, size=int(nbytes), dtype=torch.uint8)
         self.paths[base] = path
+        atexit.register(_unlink, path)                       # a rank that ends with an exception never reaches heap_free
         return base
 
     def heap_ipc_handle(self, base):
@@ -92,8 +101,8 @@ class HostExt(FusedKernelsHost):
     def heap_free(self, base):
         self.segments.pop(base, None)
         path = self.paths.pop(base, None)
-        if path and os.path.exists(path):
-            os.unlink(path)
+        if path:
+            _unlink(path)
 
     def _typed(self, ptr, numel, dtype):
         ptr = int(ptr)
