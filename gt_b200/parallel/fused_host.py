@@ -66,8 +66,7 @@ class FusedKernelsHost:
         for i, ptr in enumerate(peer_ptrs):
             if flags is not None and i != me:
                 self._wait_one(flags, i, want, status)
-            self._access("read", ptr)
-            a = self._typed(ptr, chunk * k, torch.bfloat16).view(chunk, k)
+            a = self._typed(ptr, chunk * k, torch.bfloat16, "read").view(chunk, k)
             if gathered is not None:
                 gathered[i * chunk:(i + 1) * chunk] = a
             c[i * chunk:(i + 1) * chunk] = self._epilogue(a.float() @ b.float().t(), bias, act, p)
@@ -78,8 +77,7 @@ class FusedKernelsHost:
             raise NotImplementedError("strided slots")
         for i, ptr in enumerate(slot_ptrs):
             y = a[i * chunk:(i + 1) * chunk].float() @ b.float().t()
-            self._access("write", ptr)
-            self._typed(ptr, chunk * n, torch.bfloat16).view(chunk, n).copy_(y)
+            self._typed(ptr, chunk * n, torch.bfloat16, "write").view(chunk, n).copy_(y)
 
     # ---- attention, gated scores and clamp-exp weights, partial form --------------------------------------------------------------
     @staticmethod
@@ -107,8 +105,7 @@ class FusedKernelsHost:
             l.copy_(l + s if accumulate else s)
             return
         for i, ptr in enumerate(push_ptrs):                  # rows of owner i go into MY slot of owner i's payload buffer
-            self._access("write", ptr)
-            slot = self._typed(ptr, push_rows * push_ld, torch.bfloat16).view(push_rows, push_ld)
+            slot = self._typed(ptr, push_rows * push_ld, torch.bfloat16, "write").view(push_rows, push_ld)
             lo_r = i * push_rows
             slot[:, :h * d] = a[lo_r:lo_r + push_rows]
             slot[:, push_l_off:push_l_off + h] = s[lo_r:lo_r + push_rows]
@@ -167,8 +164,7 @@ class FusedKernelsHost:
             return
         for i, p in enumerate(push_ptrs):                    # the pointer already addresses the aggregation columns of my slot
             width = x.shape[1]
-            self._access("write", p)
-            flat = self._typed(p, (push_rows - 1) * push_ld + width, torch.bfloat16)
+            flat = self._typed(p, (push_rows - 1) * push_ld + width, torch.bfloat16, "write")
             torch.as_strided(flat, (push_rows, width), (push_ld, 1)).copy_(y[i * push_rows:(i + 1) * push_rows])
 
     # ---- payload packing and the owner-side sums -----------------------------------------------------------------------------------
@@ -209,8 +205,7 @@ class FusedKernelsHost:
         hd, h = row_vec.shape[1], stat.shape[1]
         stat.zero_()
         for i, ptr in enumerate(src_ptrs):
-            self._access("read", ptr)
-            pay = self._typed(ptr, rows_per_peer * width, torch.bfloat16).view(rows_per_peer, width)
+            pay = self._typed(ptr, rows_per_peer * width, torch.bfloat16, "read").view(rows_per_peer, width)
             r = slice(i * rows_per_peer, (i + 1) * rows_per_peer)
             row_vec[r] = pay[:, :hd]
             stat[r, :, 0] = pay[:, l_off:l_off + h].float()

@@ -68,11 +68,14 @@ class HostExt(FusedKernelsHost):
         ptr = int(where)
         return (ptr >> _SHIFT) - 1, ptr & _MASK
 
-    def _access(self, kind, where):
+    def _access(self, kind, where, nbytes=None):
+        """Record ``(kind, owner rank, offset, bytes)`` for an address or a tensor inside a heap."""
         if self.log is not None:
             at = self._place(where)
             if at is not None:
-                self.log.append((kind,) + at)
+                if nbytes is None:
+                    nbytes = where.numel() * where.element_size()
+                self.log.append((kind,) + at + (int(nbytes),))
 
     # ---- heap management ---------------------------------------------------------------------------------------------------
     def heap_alloc(self, nbytes):
@@ -104,21 +107,23 @@ class HostExt(FusedKernelsHost):
         if path:
             _unlink(path)
 
-    def _typed(self, ptr, numel, dtype):
+    def _typed(self, ptr, numel, dtype, kind=None):
+        """Typed view of ``numel`` elements at an address; ``kind`` ('read' / 'write') records the access."""
         ptr = int(ptr)
         seg = self.segments[ptr >> _SHIFT << _SHIFT]
         off = ptr & _MASK
         nbytes = numel * torch.empty(0, dtype=dtype).element_size()
+        if kind is not None:
+            self._access(kind, ptr, nbytes)
         if off + nbytes > seg.numel():
             raise IndexError(f"access of {nbytes} bytes at offset {off} leaves the heap of rank {(ptr >> _SHIFT) - 1}")
         return seg[off:off + nbytes].view(dtype)
 
     def tensor_from_ptr(self, ptr, shape, dtype_code, device_index):
-        self._access("view", ptr)
         n = 1
         for s in shape:
             n *= int(s)
-        return self._typed(ptr, n, _TYPES[int(dtype_code)]).view(*shape)
+        return self._typed(ptr, n, _TYPES[int(dtype_code)], "view").view(*shape)
 
     # ---- ordering ----------------------------------------------------------------------------------------------------------
     def _wait(self, flags, n_peers, epoch, status, note=True):
@@ -139,13 +144,13 @@ class HostExt(FusedKernelsHost):
         for p in range(n):
             self._typed(peer_flag_ptrs[p], 64, torch.int32)[me] = epoch
         if self.log is not None:
-            self._note("barrier", self._place(my_flags)[1])
+            self._note("barrier", self._place(my_flags)[1], tuple((int(q) >> _SHIFT) - 1 for q in peer_flag_ptrs))
         self._wait(my_flags, n, epoch, status, note=False)
 
     def channel_signal(self, ptrs, me, counter):
         epoch = int(counter) + 1
         counter.fill_(epoch)
-        self._note("signal", int(ptrs[0]) & _MASK)
+        self._note("signal", int(ptrs[0]) & _MASK, tuple((int(q) >> _SHIFT) - 1 for q in ptrs))
         for p in ptrs:
             self._typed(p, 8, torch.int32)[me] = epoch
 
@@ -162,26 +167,26 @@ class HostExt(FusedKernelsHost):
         chunk = out.numel() // n
         flat = out.view(n, chunk)
         for p in range(n):
-            flat[p] = self._typed(table[p], chunk, out.dtype)
+            flat[p] = self._typed(table[p], chunk, out.dtype, "read")
 
     def pull_reduce_scatter(self, table, me, out):
         n, chunk = table.numel(), out.numel()
         acc = torch.zeros(chunk, dtype=self._acc_type(out.dtype))
         for p in range(n):
-            acc += self._typed(table[p], n * chunk, out.dtype)[me * chunk:(me + 1) * chunk].to(acc.dtype)
+            acc += self._typed(table[p], n * chunk, out.dtype, "read")[me * chunk:(me + 1) * chunk].to(acc.dtype)
         out.view(-1).copy_(acc)
 
     def pull_all_reduce(self, table, out):
         acc = torch.zeros(out.numel(), dtype=self._acc_type(out.dtype))
         for p in range(table.numel()):
-            acc += self._typed(table[p], out.numel(), out.dtype).to(acc.dtype)
+            acc += self._typed(table[p], out.numel(), out.dtype, "read").to(acc.dtype)
         out.view(-1).copy_(acc)
 
     def pull_all_to_all(self, table, me, rows, slab_bytes, to_heads, out):
         n = table.numel()
         slab = int(slab_bytes) // out.element_size()
         for p in range(n):
-            src = self._typed(table[p], rows * n * slab, out.dtype)
+            src = self._typed(table[p], rows * n * slab, out.dtype, "read")
             if to_heads:                                     # rows of peer p, my head slab
                 out.view(n, rows, slab)[p] = src.view(rows, n, slab)[:, me]
             else:                                            # my rows, peer p's head slab
@@ -193,7 +198,7 @@ class HostExt(FusedKernelsHost):
             sel = torch.nonzero(owner == p).squeeze(1)
             if sel.numel():
                 rows = row[sel].long()
-                src = self._typed(table[p], (int(rows.max()) + 1) * width, out.dtype).view(-1, width)
+                src = self._typed(table[p], (int(rows.max()) + 1) * width, out.dtype, "read").view(-1, width)
                 out[sel] = src[rows]
 
     def pull_reduce_rows(self, table, src, out):
@@ -204,7 +209,7 @@ class HostExt(FusedKernelsHost):
             sel = torch.nonzero(idx >= 0).squeeze(1)
             if sel.numel():
                 rows = idx[sel]
-                buf = self._typed(table[p], (int(rows.max()) + 1) * width, out.dtype).view(-1, width)
+                buf = self._typed(table[p], (int(rows.max()) + 1) * width, out.dtype, "read").view(-1, width)
                 acc[sel] += buf[rows].to(acc.dtype)
         out.copy_(acc)
 
@@ -217,11 +222,9 @@ class HostExt(FusedKernelsHost):
             return
         acc = torch.zeros(hi - lo, dtype=torch.float32)
         for p in src:
-            self._access("read", p)
-            acc += self._typed(p, n, torch.float32)[lo:hi]
+            acc += self._typed(int(p) + 4 * lo, hi - lo, torch.float32, "read")
         for p in dst:
-            self._access("write", p)
-            self._typed(p, n, torch.float32)[lo:hi] = acc
+            self._typed(int(p) + 4 * lo, hi - lo, torch.float32, "write").copy_(acc)
 
 
 class HostSymmetricHeap(SymmetricHeap):
@@ -231,10 +234,28 @@ class HostSymmetricHeap(SymmetricHeap):
 
     host = True
 
-    def __init__(self, bytes_=64 << 20, wait_seconds=20.0):
+    def __init__(self, bytes_=64 << 20, wait_seconds=20.0, record=False):
         if not dist.is_initialized():
             raise RuntimeError("the symmetric heap needs an initialised process group (handle exchange)")
         self.device = torch.device("cpu")
         e = HostExt(dist.get_rank(), wait_seconds)
+        if record:
+            e.log = []
         native._EXT[0] = e
         self._map_heaps(e, bytes_)
+
+    def check_recorded(self):
+        """Collective over all ranks (heap built with ``record=True``): gather what every rank did to shared memory (accesses with
+        their byte ranges, signals, barriers, waits) and run the happens-before check of :mod:`gt_b200.utils.hb_check` on the
+        recorded programs.  Raises ``RuntimeError`` listing accesses that no chain of signals and waits orders (a read that could
+        run before the write it follows in this run, a write that could land while a peer still reads).  Returns the report."""
+        from ..utils.hb_check import check, trace_from_logs
+        e = native.ext()
+        logs = [None] * self.world
+        dist.all_gather_object(logs, list(e.log))
+        rep = check(trace_from_logs(logs), require_writes=False)
+        if rep.violations or rep.expired or not rep.completed:
+            lines = [f"{v.kind}: rank {v.rank}, memory of rank {v.owner} at offset {v.buf}: {v.detail}" for v in rep.violations[:8]]
+            lines += [f"wait of rank {r} on flag {chan} for rank {peer} can never pass" for r, _, chan, peer in rep.expired[:8]]
+            raise RuntimeError("recorded run of the peer-memory transport is not ordered by its signals and waits:\n  " + "\n  ".join(lines))
+        return rep

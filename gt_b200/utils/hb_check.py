@@ -18,6 +18,9 @@ program of every rank:
   satisfy then *expires*, as the bounded device waits do: the rank records ``100 + index of the silent peer`` in its status word
   and carries on, so the checker also shows that no rank can block for ever and which peer every status word names.
 
+Two sources of programs: hand-written models (:mod:`gt_b200.parallel.protocol_model`) and recorded runs of the real code on the
+host transport (:func:`trace_from_logs`, used by ``HostSymmetricHeap.check_recorded``).
+
 The reference has no counterpart (its collectives are NCCL calls; ``gt3d/gt3d/dist/grid2d.py:55-69`` orders them with host
 synchronisation); compute-sanitizer's race detection is the tool one would use on a device, this is the protocol-level
 equivalent that needs none.
@@ -58,7 +61,7 @@ class ProtocolTrace:
         return sum(len(p) for p in self.prog)
 
 
-def check(trace, drop=(), die=None, max_violations=64, cascade=False):
+def check(trace, drop=(), die=None, max_violations=64, cascade=False, require_writes=True):
     """Run the programs of ``trace`` and return a :class:`Report`.
 
     ``drop``: set of ``(rank, chan, k)``: the k-th signal (1-based) of ``rank`` on channel name ``chan`` is not published.
@@ -66,7 +69,9 @@ def check(trace, drop=(), die=None, max_violations=64, cascade=False):
     ``cascade``: what happens when no rank can move.  ``False``: only the waits whose peer will never publish (its signal was
     dropped, or it has stopped) expire, and the ranks behind them carry on: the smallest set of expired waits, which names the
     root cause.  ``True``: every pending wait expires at once, as when all ranks started to wait at about the same time and
-    run into the same limit together: the largest set."""
+    run into the same limit together: the largest set.
+    ``require_writes``: report a read of a location nobody has written.  Recorded runs (:func:`trace_from_logs`) switch it off:
+    writes made by code outside the recorded entry points are not in the log."""
     world = trace.world
     die = dict(die or {})
     drop = set(drop)
@@ -142,13 +147,13 @@ def check(trace, drop=(), die=None, max_violations=64, cascade=False):
             key = (a, b)
             lw = last_write.get(key)
             if lw is None:
-                report("read-before-write", r, a, b, f"{note}: nothing has been written where {tag} is expected")
-            else:
-                if lw[1] != r and not ordered(lw[1], lw[2], r):
-                    report("read-before-write", r, a, b, f"{note}: read of {tag} is not ordered after rank {lw[1]}'s write of {lw[0]}")
-                elif lw[0] != tag:
-                    report("wrong-version", r, a, b, f"{note}: expected {tag}, the buffer holds {lw[0]}")
-                reads.setdefault(key, {})[r] = vc[r][r]
+                if require_writes:
+                    report("read-before-write", r, a, b, f"{note}: nothing has been written where {tag} is expected")
+            elif lw[1] != r and not ordered(lw[1], lw[2], r):
+                report("read-before-write", r, a, b, f"{note}: read of {tag} is not ordered after rank {lw[1]}'s write of {lw[0]}")
+            elif tag is not None and lw[0] != tag:
+                report("wrong-version", r, a, b, f"{note}: expected {tag}, the buffer holds {lw[0]}")
+            reads.setdefault(key, {})[r] = vc[r][r]
         pc[r] += 1
         return True
 
@@ -167,3 +172,55 @@ def check(trace, drop=(), die=None, max_violations=64, cascade=False):
             step(r, expire=True)
     completed = all(pc[r] >= len(trace.prog[r]) for r in range(world) if r not in die)
     return Report(violations, status, expired, completed, trace.n_ops())
+
+
+def trace_from_logs(logs):
+    """A :class:`ProtocolTrace` from what the ranks of a run on the host transport recorded (``HostExt.log`` of every rank, in rank
+    order): events ``(kind, owner, offset, bytes)`` for ``kind`` in view / write / read, ``("signal", flag offset, members)``,
+    ``("barrier", flag offset, members)`` and ``("wait", flag offset, member index)``.
+
+    Byte ranges are cut at every boundary that occurs in the logs of the same owner, so overlapping accesses meet on common
+    pieces.  A ``view`` (a tensor over heap memory handed to code outside the recorded entry points) counts as a write of its
+    range unless the next recorded event of that rank (waits aside) is an access that starts at the same address: then the view
+    was only the operand of that access.  Reads name no version (``tag=None``)."""
+    world = len(logs)
+    events = []
+    for r, log in enumerate(logs):
+        out = []
+        for i, ev in enumerate(log):
+            if ev[0] == "view":
+                j = i + 1
+                while j < len(log) and log[j][0] == "wait":          # a kernel waits before it touches its operand
+                    j += 1
+                nxt = log[j] if j < len(log) else None
+                if nxt is not None and nxt[0] in ("read", "write") and nxt[1] == ev[1] and nxt[2] == ev[2]:
+                    continue
+                ev = ("write",) + tuple(ev[1:])
+            out.append(ev)
+        events.append(out)
+    cuts = {}
+    for log in events:
+        for ev in log:
+            if ev[0] in ("read", "write"):
+                cuts.setdefault(ev[1], set()).update((ev[2], ev[2] + ev[3]))
+    cuts = {o: sorted(c) for o, c in cuts.items()}
+    import bisect
+    tr = ProtocolTrace(world)
+    for r, log in enumerate(events):
+        members_of = {}
+        for ev in log:
+            if ev[0] in ("read", "write"):
+                c = cuts[ev[1]]
+                i, j = bisect.bisect_left(c, ev[2]), bisect.bisect_left(c, ev[2] + ev[3])
+                for lo in c[i:j]:
+                    (tr.write if ev[0] == "write" else tr.read)(r, ev[1], lo, None, f"{ev[0]} of {ev[3]} bytes at offset {ev[2]}")
+            elif ev[0] == "signal":
+                members_of[ev[1]] = ev[2]
+                tr.signal(r, ev[1], ev[2])
+            elif ev[0] == "barrier":
+                members_of[ev[1]] = ev[2]
+                tr.barrier(r, ev[1], ev[2])
+            elif ev[0] == "wait":
+                members = members_of[ev[1]]
+                tr.wait(r, ev[1], members, members[ev[2]])
+    return tr

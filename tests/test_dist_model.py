@@ -70,7 +70,7 @@ def _worker(rank, world, case, host_heap=False):
     if host_heap:                                           # peer-memory transport between the CPU ranks (shared host memory)
         from gt_b200.parallel.collectives import set_transport
         from gt_b200.parallel.symm_host import HostSymmetricHeap
-        heap = HostSymmetricHeap(16 << 20, wait_seconds=60.0)
+        heap = HostSymmetricHeap(16 << 20, wait_seconds=60.0, record=True)
         set_transport(heap)
         cfg.update(sparse_transport="pull", heap=heap)
     model = DistExphormer(grid, gcn_blk, a_blk, a_et, f, hid, classes, 2, heads, dropout=0.0, gnn_dropout=0.0, backend="torch", **cfg).double()
@@ -108,7 +108,8 @@ def _worker(rank, world, case, host_heap=False):
     if heap is not None:
         import torch.distributed as dist
         from gt_b200.ops import native
-        heap.check_symmetric()                              # every rank made the same allocations in the same order
+        heap.check_symmetric()
+        heap.check_recorded()                               # the recorded accesses are ordered by the recorded barriers                              # every rank made the same allocations in the same order
         native.check_status(torch.device("cpu"))            # no wait expired
         assert heap.alloc_log[0] > 2, "the case never used the heap"
         dist.barrier()

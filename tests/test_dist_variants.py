@@ -70,7 +70,7 @@ def _variant_worker(rank, world, case, host_heap=False):
     if host_heap:                                           # peer-memory transport between the CPU ranks (shared host memory)
         from gt_b200.parallel.collectives import set_transport
         from gt_b200.parallel.symm_host import HostSymmetricHeap
-        heap = HostSymmetricHeap(16 << 20, wait_seconds=60.0)
+        heap = HostSymmetricHeap(16 << 20, wait_seconds=60.0, record=True)
         set_transport(heap)
     model = gv.DistGTVariant(grid, blk_ei, blk_et, f, hid, classes, 2, heads, model=cfg["model"], dropout=0.0, backend="torch",
                              checkpoint=cfg.get("checkpoint", False), **kw).double()
@@ -96,6 +96,7 @@ def _variant_worker(rank, world, case, host_heap=False):
         import torch.distributed as dist
         from gt_b200.ops import native
         heap.check_symmetric()
+        heap.check_recorded()                               # the recorded accesses are ordered by the recorded barriers
         native.check_status(torch.device("cpu"))
         assert heap.alloc_log[0] > 2, "the case never used the heap"
         dist.barrier()

@@ -19,7 +19,7 @@ def _collectives_worker(rank, world, dtype_name):
     dtype = getattr(torch, dtype_name)
     tol = dict(float64=1e-12, float32=1e-5, bfloat16=5e-2)[dtype_name]
     grid = make_grid((2, 2), 64, n_pad=64)
-    heap = HostSymmetricHeap(8 << 20, wait_seconds=30.0)
+    heap = HostSymmetricHeap(8 << 20, wait_seconds=30.0, record=True)
     g = torch.Generator().manual_seed(100 + rank)
     try:
         for rep in range(3):                                 # three rounds: every staging copy is reused
@@ -74,6 +74,8 @@ def _collectives_worker(rank, world, dtype_name):
                 assert torch.equal(heap.view(heap.named["grads_sum"][0], (n,), torch.float32), want), "two-shot all-reduce"
             heap.check_symmetric()
         native.check_status(torch.device("cpu"))
+        rep = heap.check_recorded()                          # every recorded access is ordered by the recorded signals and waits
+        assert rep.n_ops > 500
     finally:
         dist.barrier()
         heap.close()
@@ -207,7 +209,7 @@ def _fused_worker(rank, world, grid_shape, cfg):
     gcn_blk, _ = grid.local_block(gcn_edges_with_self_loops(ei, n))
     attn_ei, attn_et = ExphormerRef.build_attention_edges(ei, exp)
     a_blk, a_et = grid.local_block(attn_ei, attn_et)
-    heap = HostSymmetricHeap(32 << 20, wait_seconds=60.0)
+    heap = HostSymmetricHeap(32 << 20, wait_seconds=60.0, record=True)
     set_transport(heap)
     bf = torch.bfloat16
     model = DistExphormer(grid, gcn_blk, a_blk, a_et, f, hid, classes, 2, heads, dropout=0.0, gnn_dropout=0.0, backend="torch", fused=True,
@@ -232,7 +234,7 @@ def _fused_worker(rank, world, grid_shape, cfg):
     lo, hi = grid.owned_range()
     nv = max(min(hi, n) - lo, 0)
     failures = []
-    native.ext().log = []                                     # record what the operator does to shared memory, in order
+    del native.ext().log[:]                                   # from here: what the operator does to shared memory, in order
     for step in range(2):
         dist.barrier()
         heap.begin_step()
@@ -263,6 +265,7 @@ def _fused_worker(rank, world, grid_shape, cfg):
     assert calls["n"] == 2 * 2, calls                         # two layers, two steps: the operator ran, not the op-by-op fallback
     assert not failures, failures
     _compare_with_protocol_model(native.ext().log, model, grid, rank)
+    heap.check_recorded()                                     # and the recorded run itself passes the happens-before check
     dist.barrier()
     set_transport(None)
     heap.close()
@@ -284,3 +287,35 @@ def _fused_cases_worker(rank, world, cases):
 @pytest.mark.parametrize("world", sorted({g[0] * g[1] for g, _ in FUSED_GRIDS}))
 def test_fused_operator_with_in_kernel_collectives_between_cpu_ranks(world):
     run_dist(_fused_cases_worker, world, [(g, c) for g, c in FUSED_GRIDS if g[0] * g[1] == world], timeout=900)
+
+
+def _single_copy_worker(rank, world):
+    """Negative control of the recorded check: with ONE staging copy per kind a rank may rewrite its buffer while a peer still reads the
+    previous contents.  Whether that corrupts data depends on timing; the happens-before check of the recorded run reports it always."""
+    import torch.distributed as dist
+    from gt_b200.parallel import symm
+    from gt_b200.parallel.symm_host import HostSymmetricHeap
+    orig = symm.GroupContext.staging
+
+    def one_copy(self, nbytes, kind):
+        self.kind_count[kind] = 0
+        return orig(self, nbytes, kind)
+    heap = HostSymmetricHeap(4 << 20, wait_seconds=30.0, record=True)
+    try:
+        x = torch.randn(16, 8)
+        for _ in range(4):
+            heap.all_gather(x, None)
+        heap.check_recorded()                                # two copies: ordered
+        symm.GroupContext.staging = one_copy
+        for _ in range(4):
+            heap.all_gather(x, None)
+        with pytest.raises(RuntimeError, match="write-while-read|read-before-write"):
+            heap.check_recorded()
+    finally:
+        symm.GroupContext.staging = orig
+        dist.barrier()
+        heap.close()
+
+
+def test_recorded_check_reports_single_buffering():
+    run_dist(_single_copy_worker, 3)
