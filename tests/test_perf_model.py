@@ -143,3 +143,28 @@ def test_streamed_memory_model_against_the_measured_scale_out_runs():
     g26 = graph(26)
     assert gs.peak_memory_bytes(8, 1, g26, m, n_sub=16, streamed=True) / 2 ** 30 < 180 * 0.9
     assert gs.peak_memory_bytes(2, 4, g26, m, n_sub=32, streamed=True) / 2 ** 30 > 180
+
+
+def test_planner_lists_every_layout_and_agrees_with_the_selectors(capsys):
+    import json
+    from gt_b200.perf import grid_select as gs
+    from gt_b200.perf import plan
+    rows = plan.main(["--workload", "exphormer_arxiv", "--gpus", "8"])
+    out = capsys.readouterr().out
+    assert "fastest that fits: fused 4x2" in out and "--grid 4 2 --fused" in out
+    fams = {r["family"] for r in rows}
+    assert fams == {"fused", "head", "streamed", "ring"}
+    assert {tuple(r["grid"]) for r in rows if r["family"] == "fused"} == {(1, 8), (2, 4), (4, 2), (8, 1)}
+    w = plan.WORKLOADS["exphormer_arxiv"]
+    g = gs.Graph(w["nodes"], gs.attention_edges(w["nodes"], w["edges"], w["exp_deg"]) + 2 * w["nodes"], w["edges"] + w["nodes"], w["features"],
+                 exp_deg=w["exp_deg"], token=True)
+    best = gs.select_grid(8, g, gs.Model(256, 8, 4, transport="p2p"))
+    assert tuple(best.grid) == tuple(rows[0]["grid"]) and abs(best.ms - rows[0]["ms"]) < 1e-9
+    # the scale-out graph: nothing but the streamed layer on 8 x 1 fits; the planner says so and gives the flags
+    rows = plan.main(["--workload", "exphormer_rmat26", "--layers", "2", "--gpus", "8", "--json"])
+    blob = json.loads(capsys.readouterr().out)
+    fitting = [r for r in blob["layouts"] if r["fits"]]
+    assert [(r["family"], tuple(r["grid"])) for r in fitting] == [("streamed", (8, 1))] and fitting[0]["n_sub"] == 16
+    assert "--stream_sub 16" in fitting[0]["flags"]
+    with pytest.raises(SystemExit):
+        plan.main(["--gpus", "8"])
