@@ -97,6 +97,8 @@ class FusedKernelsHost:
     def attn_fwd(self, q, k, v, idx, etype, gate, bias, plan, row_map, acc, l, m, scratch, h, d, score, norm, scale, lo, hi, acc_stride, l_stride,
                  accumulate, k_peers, v_peers, rows_per_peer, ldq, ldk, push_ptrs, push_rows, push_ld, push_l_off):
         self._check_mode(score, norm, gate, etype)
+        if k_peers is not None or v_peers is not None or row_map is not None:
+            raise NotImplementedError("the emulation covers the forward of the fused layer (local K / V, every row of the block)")
         rows = _edge_rows(plan, idx.numel())
         a, s = self._partial(q.float(), k.float(), v.float(), rows, idx.long(), etype.long(), gate.float(), h, d, scale, lo, hi)
         a = a.reshape(q.shape[0], h * d)
