@@ -90,7 +90,7 @@ def _expiry_worker(rank, world):
     import torch.distributed as dist
     from gt_b200.ops import native
     from gt_b200.parallel.symm_host import HostSymmetricHeap
-    heap = HostSymmetricHeap(1 << 20, wait_seconds=0.5)
+    heap = HostSymmetricHeap(1 << 20, wait_seconds=2.0)
     ctx = heap.ctx(None)
     dist.barrier()
     if rank != 1:                                            # rank 1 never arrives: the others give up after the limit and say who
