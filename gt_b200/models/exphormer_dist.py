@@ -139,6 +139,7 @@ class DistExphormerLayerFused(_LayerBase):
         self.sp_row = sparse["row"] if sparse is not None else None
         self.sp_col = sparse["col"] if sparse is not None else None
         self.gcn_block = gcn_block
+        self.token = None                                    # a parallel.token_dense.DenseToken: the global token outside the sparse structure
         self.attn = DistAttentionPartial(grid, attn_block, num_heads, self.d_head, backend=backend, score="gated",
                                          norm="clampexp")
 
@@ -198,11 +199,16 @@ class DistExphormerLayerFused(_LayerBase):
         if type(self) is DistExphormerLayerFused:
             # the whole branch as one explicit-backward operator on the native kernels (collectives inside the kernels)
             from ..parallel.fused_layer import fused_branch
-            out = fused_branch(self, x, self.gate(edge_type_emb))
+            gate = self.gate(edge_type_emb)
+            out = fused_branch(self, x, gate)
             if out is not None:
                 acc_o, l_o, agg_o = out
+                if self.token is not None:
+                    acc_o, l_o = self.token.add(self, x, gate, acc_o, l_o)
                 return self.tail(x, acc_o, agg_o, l=l_o)
         (acc_o, l_o), agg_o = self.branches(x, edge_type_emb)
+        if self.token is not None:
+            acc_o, l_o = self.token.add(self, x, self.gate(edge_type_emb), acc_o, l_o)
         return self.tail(x, acc_o, agg_o, l=l_o)
 
     def stacked_params(self):
@@ -577,7 +583,7 @@ class DistExphormer(nn.Module):
                  backend="cuda", gcn_weight=None, checkpoint=False, comm_dtype=None, fused=False, rs_dtype=None,
                  pipeline_sub=1, stream_sub=1, norm="bn", ring=False, with_gcn=True, with_attn=True, gather_proj=False,
                  stream_overlap=True, stream_compact=True, kernel_dtype=None, sparse_comm=False, sparse_threshold=None,
-                 sparse_transport="a2a", heap=None):
+                 sparse_transport="a2a", heap=None, token_node=None):
         super().__init__()
         self.grid = grid
         head_grid = grid.p_heads > 1 or getattr(grid, "head_group", None) is not None
@@ -667,6 +673,13 @@ class DistExphormer(nn.Module):
             mk = lambda: DistExphormerLayer(grid, gcn_block, attn_block, *common, comm_dtype=comm_dtype, with_gcn=with_gcn,   # noqa: E731
                                             with_attn=with_attn, norm=norm)
         self.layers = nn.ModuleList([mk() for _ in range(num_layers)])
+        if token_node is not None:
+            # the global token's row and column as dense terms on the owned rows; the blocks must then not contain its edges
+            if not (fused and stream_sub <= 1 and not ring and not head_grid):
+                raise ValueError("a dense global token is implemented for the fused and pipelined layers")
+            from ..parallel.token_dense import DenseToken
+            for layer in self.layers:
+                layer.token = DenseToken(grid, token_node)
         self.head = nn.Linear(dim_hidden, dim_out)
 
     def pre_mp(self, x):

@@ -56,6 +56,9 @@ def build_parser():
     a("--stream_gen", action="store_true",
       help="(--synthetic exphormer_rmat26) build every rank's blocks from streamed edge chunks: no rank holds the global graph")
     a("--virtual_node", action="store_true", help="(exphormer) add one global token connected to every node (edge type 2)")
+    a("--token_dense", action="store_true",
+      help="(--virtual_node, fused / pipelined layers) keep the token's 2 n edges out of the sparse blocks and compute its row and column as "
+           "dense terms on the owned rows plus one small all-reduce: no rank carries the token's row or column")
     a("--graph_name", default=None)
     # layer kind
     a("--fused", action="store_true", help="fused-communication layer: gather x once, one reduce-scatter")
@@ -147,6 +150,9 @@ def validate(args):
         raise SystemExit("the head grid has its own layer: no --fused / --ring / --gather_proj / --pipeline_sub / --stream_sub / --grid_auto")
     if args.sparse_comm and args.model != "exphormer":
         raise SystemExit("--sparse_comm is implemented for the Exphormer layers")
+    if args.token_dense and not (args.virtual_node and args.model == "exphormer" and args.fused and not head and not args.ring
+                                 and args.stream_sub <= 1 and args.data is None and not args.stream_gen):
+        raise SystemExit("--token_dense needs --virtual_node with the fused or pipelined Exphormer layer on a synthetic graph")
     return head
 
 
@@ -289,6 +295,7 @@ def main(argv=None):
             build = W.exphormer_workload_streamed if args.stream_gen else W.exphormer_workload
             wl = build(name, args.grid, dev, dtype, seed=args.seed, scale_down=args.scale_down, exp_deg=args.exp_deg,
                                       virtual_node=args.virtual_node, dropout=args.dropout, backend=backend, layer=layer, norm=args.norm,
+                                      **(dict(token_dense=True) if args.token_dense else {}),
                                       stream_sub=max(args.stream_sub, args.pipeline_sub), comm_bf16=args.comm_bf16 or args.bf16, heap=heap,
                                       layers=args.layers, hidden=args.hidden, heads=args.heads, with_gcn=not args.no_gcn,
                                       with_attn=not args.no_attn, gather_proj=args.gather_proj, checkpoint=args.checkpoint,

@@ -36,10 +36,12 @@ def _generate(name, seed, scale_down, device):
 
 def exphormer_workload(name="exphormer_arxiv", grid_shape=None, device="cpu", dtype=torch.float32, seed=0, scale_down=1,
                        exp_deg=4, virtual_node=True, dropout=0.1, backend=None, layer="fused", norm="ln", stream_sub=1,
-                       comm_bf16=True, heap=None, layers=None, hidden=None, heads=None, return_blocks=False, **model_kw):
+                       comm_bf16=True, heap=None, layers=None, hidden=None, heads=None, return_blocks=False, token_dense=False,
+                       **model_kw):
     """Exphormer on a named graph: symmetrised base graph + degree-``exp_deg`` expander (both directions) + optional global
-    token (edge type 2) + one self loop per node for the GCN branch.  Returns a dict with ``grid, model, x, y, masks,
-    n_train, num_attn_edges, num_nodes, cfg``."""
+    token (edge type 2) + one self loop per node for the GCN branch.  ``token_dense``: the token's edges stay out of the sparse
+    blocks and its row and column are computed as dense terms (``parallel/token_dense.py``; same model, same result).  Returns a
+    dict with ``grid, model, x, y, masks, n_train, num_attn_edges, num_nodes, cfg``."""
     world = dist.get_world_size() if dist.is_initialized() else 1
     grid_shape = tuple(grid_shape or DEFAULT_GRIDS[world])
     wl = _generate(name, seed, scale_down, device)
@@ -49,7 +51,8 @@ def exphormer_workload(name="exphormer_arxiv", grid_shape=None, device="cpu", dt
     ei = wl["edge_index"]
     exp = keyed_expander_edges(n, exp_deg, seed=seed, device=ei.device)
     tok = virtual_node_edges(n)[0].to(ei.device) if virtual_node else None
-    attn_ei, attn_et = ExphormerRef.build_attention_edges(ei, exp, tok)
+    token_dense = bool(token_dense and virtual_node)
+    attn_ei, attn_et = ExphormerRef.build_attention_edges(ei, exp, None if token_dense else tok)
     gcn_ei = gcn_edges_with_self_loops(ei, n_tot)
     n_pad = pad_to(n_tot, 8 * world * max(stream_sub, 1))
     grid = make_grid(grid_shape, n_tot, n_pad=n_pad).to(device)
@@ -63,7 +66,7 @@ def exphormer_workload(name="exphormer_arxiv", grid_shape=None, device="cpu", dt
               pipeline_sub=stream_sub if layer == "pipelined" else 1, ring=layer == "ring",
               comm_dtype=torch.bfloat16 if (comm_bf16 and dev.type == "cuda") else None,
               rs_dtype=torch.bfloat16 if (comm_bf16 and dev.type == "cuda" and world > 1) else None,
-              kernel_dtype=torch.bfloat16 if bf16 else None, heap=heap)
+              kernel_dtype=torch.bfloat16 if bf16 else None, heap=heap, token_node=n if token_dense else None)
     kw.update(model_kw)
     torch.manual_seed(seed)
     model = DistExphormer(grid, g_blk.to(dev), a_blk.to(dev), a_et.to(dev), cfg["features"], hidden or cfg["hidden"], cfg["classes"],
@@ -71,8 +74,8 @@ def exphormer_workload(name="exphormer_arxiv", grid_shape=None, device="cpu", dt
     x = torch.cat([wl["x"], wl["x"].new_zeros(n_tot - n, wl["x"].shape[1])])
     y = torch.cat([wl["y"], wl["y"].new_zeros(n_tot - n)])
     masks = {k: torch.cat([m, m.new_zeros(n_tot - n)]) for k, m in wl["masks"].items()}
-    out = dict(grid=grid, model=model, cfg=cfg, num_nodes=n_tot, num_attn_edges=int(attn_ei.shape[1]), num_gcn_edges=int(gcn_ei.shape[1]),
-               x=grid.take_owned(x).to(dtype), y=grid.take_owned(y),
+    out = dict(grid=grid, model=model, cfg=cfg, num_nodes=n_tot, num_attn_edges=int(attn_ei.shape[1]) + (2 * n if token_dense else 0),
+               num_gcn_edges=int(gcn_ei.shape[1]), x=grid.take_owned(x).to(dtype), y=grid.take_owned(y),
                masks={k: grid.take_owned(m.to(torch.uint8)).bool() & grid.valid_mask.cpu() for k, m in masks.items()},
                n_train=int(masks["train"].sum()), in_degree=degrees(ei, n)[0].cpu())
     if return_blocks:                                          # local edge lists of this rank (tests)

@@ -206,3 +206,63 @@ def _bn_no_sync_worker(rank, world):
 
 def test_bn_no_sync_switch_keeps_the_statistics_local():
     run_dist(_bn_no_sync_worker, 2)
+
+
+def _token_dense_worker(rank, world, grid_shape, cfg):
+    """A global token kept out of the sparse blocks (``parallel/token_dense.py``: its row and column as dense terms) gives the
+    reference model's logits, loss and parameter gradients, where the reference has the token's 2 n edges in its edge list."""
+    import os, sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from helpers import random_graph
+    from gt_b200.data.expander import random_regular_expander_edges
+    from gt_b200.data.synthetic import virtual_node_edges
+    from gt_b200.models.exphormer_dist import DistExphormer
+    from gt_b200.models.exphormer_ref import ExphormerRef, gcn_edges_with_self_loops
+    from gt_b200.parallel.grid import make_grid
+    from gt_b200.parallel.layers import allreduce_grads, dist_cross_entropy, set_step
+    n, f, hid, classes, heads = 93, 12, 16, 5, 4
+    torch.manual_seed(0)
+    ei, _ = random_graph(n, 3, seed=3, hub=True, empty=())
+    ei = ei[:, ei[0] != ei[1]]
+    exp = random_regular_expander_edges(n, 2, seed=1)
+    tok, _ = virtual_node_edges(n)                           # the token is node n
+    n_tot = n + 1
+    x = torch.randn(n_tot, f, dtype=torch.float64)
+    y = torch.randint(0, classes, (n_tot,))
+    mask = torch.rand(n_tot) < 0.6
+    norm = cfg.get("norm", "bn")
+    ref = ExphormerRef(f, hid, classes, 2, heads, dropout=0.0, gnn_dropout=0.0, num_edge_types=3, norm=norm).double()
+    grid = make_grid(grid_shape, n_tot, n_pad=96)
+    gcn_full = gcn_edges_with_self_loops(ei, n_tot)
+    gcn_blk, _ = grid.local_block(gcn_full)
+    attn_ei, attn_et = ExphormerRef.build_attention_edges(ei, exp)                  # WITHOUT the token's edges
+    a_blk, a_et = grid.local_block(attn_ei, attn_et)
+    model = DistExphormer(grid, gcn_blk, a_blk, a_et, f, hid, classes, 2, heads, dropout=0.0, gnn_dropout=0.0, num_edge_types=3,
+                          backend="torch", fused=True, token_node=n, **cfg).double()
+    model.load_ref_state_dict(ref.state_dict())
+    set_step(0)
+    ref.train(); model.train()
+    out_ref = ref(x, ei, exp, tok)                           # the reference: token edges (type 2) in the edge list
+    loss_ref = torch.nn.functional.cross_entropy(out_ref[mask], y[mask], reduction="sum") / int(mask.sum())
+    loss_ref.backward()
+    out = model(grid.take_owned(x))
+    lo, hi = grid.owned_range()
+    nv = max(min(hi, n_tot) - lo, 0)
+    assert (out[:nv] - out_ref[lo:lo + nv]).abs().max() < 1e-9, (out[:nv] - out_ref[lo:lo + nv]).abs().max()
+    m_loc = grid.take_owned(mask.to(torch.uint8)).bool() & grid.valid_mask
+    dist_cross_entropy(out, grid.take_owned(y), m_loc, int(mask.sum())).backward()
+    allreduce_grads(list(model.parameters()))
+    ref_grads = dict(ref.named_parameters())
+    for name, p in model.named_parameters():
+        gr = ref_grads[name].grad
+        if gr is None:
+            continue
+        err = (p.grad - gr).abs().max().item()
+        assert err < 1e-8 * max(1.0, gr.abs().max().item()), (name, err)
+    # the reference GCN sees the token as an isolated node with a self loop, like gcn_full here; nothing else to compare
+
+
+@pytest.mark.parametrize("grid_shape,cfg", [((2, 2), {}), ((4, 2), dict(norm="ln")), ((1, 2), {}), ((2, 2), dict(pipeline_sub=2)), ((1, 1), {})],
+                         ids=["2x2", "4x2_ln", "1x2", "2x2_pipelined", "1x1"])
+def test_dense_global_token_matches_token_edges(grid_shape, cfg):
+    run_dist(_token_dense_worker, grid_shape[0] * grid_shape[1], grid_shape, cfg)

@@ -194,16 +194,23 @@ def _fused_worker(rank, world, grid_shape, cfg):
     from gt_b200.parallel.symm_host import HostSymmetricHeap
     from gt_b200.train.engine import TrainEngine
     cfg = dict(cfg)
-    n, f, hid, classes, heads = 500, 16, 64, 8, 4
+    token = cfg.pop("token", False)                           # a global token, computed as dense terms outside the operator
+    n, f, hid, classes, heads = 500 - (1 if token else 0), 16, 64, 8, 4
     torch.manual_seed(0)
     ei, _ = random_graph(n, 4, seed=3, hub=True, empty=())
     ei = ei[:, ei[0] != ei[1]]
     exp = random_regular_expander_edges(n, 3, seed=1)
+    tok = None
+    if token:
+        from gt_b200.data.synthetic import virtual_node_edges
+        tok = virtual_node_edges(n)[0]
+        cfg.update(token_node=n, num_edge_types=3)
+        n += 1
     x = torch.randn(n, f, dtype=torch.float64)
     y = torch.randint(0, classes, (n,))
     mask = torch.rand(n) < 0.6
     with_gcn = cfg.get("with_gcn", True)
-    ref = ExphormerRef(f, hid, classes, 2, heads, dropout=0.0, gnn_dropout=0.0, with_gcn=with_gcn, norm="ln").double()
+    ref = ExphormerRef(f, hid, classes, 2, heads, dropout=0.0, gnn_dropout=0.0, with_gcn=with_gcn, norm="ln", num_edge_types=3 if token else 2).double()
     n_pad = -(-n // (16 * world)) * (16 * world)
     grid = make_grid(grid_shape, n, n_pad=n_pad)
     gcn_blk, _ = grid.local_block(gcn_edges_with_self_loops(ei, n))
@@ -225,7 +232,7 @@ def _fused_worker(rank, world, grid_shape, cfg):
     fused_layer._FusedBranch.apply = counted
     set_step(0)
     ref.train(); model.train()
-    out_ref = ref(x, ei, exp)
+    out_ref = ref(x, ei, exp, tok)
     loss_ref = torch.nn.functional.cross_entropy(out_ref[mask], y[mask], reduction="sum") / int(mask.sum())
     loss_ref.backward()
     ref_grads = dict(ref.named_parameters())
@@ -271,7 +278,8 @@ def _fused_worker(rank, world, grid_shape, cfg):
     heap.close()
 
 
-FUSED_GRIDS = [((2, 2), {}), ((2, 1), {}), ((1, 2), {}), ((4, 2), {}), ((2, 4), {}), ((2, 2), dict(with_gcn=False)), ((3, 2), {})]
+FUSED_GRIDS = [((2, 2), {}), ((2, 1), {}), ((1, 2), {}), ((4, 2), {}), ((2, 4), {}), ((2, 2), dict(with_gcn=False)), ((3, 2), {}),
+               ((2, 2), dict(token=True)), ((4, 2), dict(token=True))]
 
 
 def _fused_cases_worker(rank, world, cases):

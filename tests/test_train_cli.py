@@ -221,3 +221,23 @@ def test_cli_comm_p2p_between_cpu_ranks_matches_gloo(argv, tmp_path):
     assert len(rows["gloo"]) == len(rows["p2p"]) > 0
     for ra, rb in zip(rows["gloo"], rows["p2p"]):
         assert abs(ra["loss"] - rb["loss"]) < 1e-4 * max(1.0, abs(ra["loss"])), (ra, rb)
+
+
+def _token_dense_cli_worker(rank, world, out_path):
+    from gt_b200.train.train_dist import main
+    base = ["--grid", "2", "2", "--synthetic", "cpu_small", "--scale_down", "4", "--fused", "--virtual_node", "--epochs", "4", "--norm", "ln",
+            "--dropout", "0.0"]
+    main(base + ["--metrics_jsonl", out_path + ".edges"])
+    main(base + ["--token_dense", "--metrics_jsonl", out_path + ".dense"])
+    with pytest.raises(SystemExit):
+        main(["--grid", "2", "2", "--synthetic", "cpu_small", "--token_dense", "--epochs", "1"])
+
+
+def test_cli_token_dense_trains_like_token_edges(tmp_path):
+    import json
+    out = str(tmp_path / "m")
+    run_dist(_token_dense_cli_worker, 4, out)
+    rows = {k: [json.loads(line) for line in open(out + "." + k)] for k in ("edges", "dense")}
+    assert len(rows["edges"]) == len(rows["dense"]) > 0
+    for ra, rb in zip(rows["edges"], rows["dense"]):
+        assert abs(ra["loss"] - rb["loss"]) < 1e-4 * max(1.0, abs(ra["loss"])), (ra, rb)
