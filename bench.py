@@ -113,7 +113,8 @@ def run_ours(args):
         if not bool(ok.item()):
             heap, args.comm = None, "nccl"
     grid_shape = tuple(args.grid) if args.grid else GRIDS[world]
-    wl = exphormer_workload(WORKLOAD, grid_shape, dev, torch.bfloat16, seed=0, heap=heap, scale_down=args.scale_down)
+    wl = exphormer_workload(WORKLOAD, grid_shape, dev, torch.bfloat16, seed=0, heap=heap, scale_down=args.scale_down,
+                            token_dense=args.token_dense)
     model, grid = wl["model"], wl["grid"]
     for p in model.parameters():
         dist.broadcast(p.data, src=0)
@@ -211,6 +212,7 @@ def run_ours(args):
                        "parallelism": "grid " + "x".join(map(str, grid_shape)), "grid": list(grid_shape),
                        "comm": args.comm if world > 1 else "none",
                        "cuda_graph": not args.no_graph, "scale_down": args.scale_down,
+                       "global_token": "dense terms" if args.token_dense else "edges of the sparse blocks",
                        "l2": "step working set (>2 GB of activations) exceeds the 126 MB L2; no explicit flush"},
             "clocks": clocks,
             "e2e": {"value": edges_layers / (ms_e2e * 1e-3), "unit": "edges/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
@@ -266,6 +268,8 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--e2e_prefetch", action="store_true",
                     help="end-to-end loop with the input pipeline of gt_b200.train.prefetch (default: copies and loss read on the step's stream)")
+    ap.add_argument("--token_dense", action="store_true",
+                    help="the global token as dense terms instead of 2 n edges (gt_b200/parallel/token_dense.py; same model and result; off by default)")
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
