@@ -91,6 +91,9 @@ def build_parser():
     a("--comm", default="nccl", choices=["nccl", "p2p"],
       help="grid collectives: NCCL (gloo on CPU ranks) or the peer-memory transport (symmetric heap; between CPU ranks an emulation over shared host memory)")
     a("--heap_mb", type=int, default=2048)
+    a("--check_protocol", action="store_true",
+      help="(--comm p2p between CPU ranks) record every access to shared memory with the signals, barriers and waits around it, and run the "
+           "happens-before check on the recorded run at the end: a race check of this configuration's peer-memory protocol without GPUs")
     a("--nccl_tune", default="auto", choices=["auto", "on", "off"])
     a("--sparse_comm", action="store_true")
     a("--sparse_threshold", type=float, default=None)
@@ -150,6 +153,8 @@ def validate(args):
         raise SystemExit("the head grid has its own layer: no --fused / --ring / --gather_proj / --pipeline_sub / --stream_sub / --grid_auto")
     if args.sparse_comm and args.model != "exphormer":
         raise SystemExit("--sparse_comm is implemented for the Exphormer layers")
+    if args.check_protocol and (args.comm != "p2p" or torch.cuda.is_available()):
+        raise SystemExit("--check_protocol records the host emulation of the peer-memory transport: CPU ranks with --comm p2p")
     if args.token_dense and not (args.virtual_node and args.model == "exphormer" and args.fused and not head and not args.ring
                                  and args.stream_sub <= 1 and args.data is None and not args.stream_gen):
         raise SystemExit("--token_dense needs --virtual_node with the fused or pipelined Exphormer layer on a synthetic graph")
@@ -259,7 +264,7 @@ def main(argv=None):
             heap = SymmetricHeap(dev, args.heap_mb << 20)
         else:                                               # CPU ranks of one machine: the same heap logic over shared host memory
             from ..parallel.symm_host import HostSymmetricHeap
-            heap = HostSymmetricHeap(args.heap_mb << 20)
+            heap = HostSymmetricHeap(args.heap_mb << 20, record=args.check_protocol)
         set_transport(heap)
 
     def mem(tag, model=None):
@@ -519,6 +524,10 @@ def main(argv=None):
               f"ms_per_epoch={sum(steady) / max(len(steady), 1):.2f} peak_gb={peak.item():.2f} timing=device_max_over_ranks", flush=True)
     if heap is not None and heap.host:                       # unmap and delete the shared files once every rank is done with them
         native.check_status(dev)
+        if args.check_protocol:
+            rep = heap.check_recorded()                      # raises on an access that the recorded signals and waits do not order
+            if rank == 0:
+                print(f"[protocol] {rep.n_ops} recorded operations on {world} ranks: every access to shared memory is ordered", flush=True)
         dist.barrier()
         set_transport(None)
         heap.close()

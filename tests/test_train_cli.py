@@ -202,7 +202,7 @@ def _p2p_worker(rank, world, argv, out_path):
     """The same run on gloo collectives and on the peer-memory transport (emulated between the CPU ranks): the losses agree."""
     from gt_b200.train.train_dist import main
     a = main(argv + ["--metrics_jsonl", out_path + ".gloo"])
-    b = main(argv + ["--comm", "p2p", "--heap_mb", "64", "--metrics_jsonl", out_path + ".p2p"])
+    b = main(argv + ["--comm", "p2p", "--heap_mb", "64", "--check_protocol", "--metrics_jsonl", out_path + ".p2p"])
     assert len(a["epoch_ms"]) == len(b["epoch_ms"])
     assert abs(a["best"]["val"] - b["best"]["val"]) < 1e-6
 
