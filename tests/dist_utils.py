@@ -39,3 +39,38 @@ def run_dist(fn, world, *args, timeout=300):
             while not err_q.empty():
                 msgs.append("rank %d:\n%s" % err_q.get())
             raise AssertionError("distributed test failed\n" + "\n".join(msgs))
+
+
+def _group_entry(rank, world, fn, cases, done_path):
+    """All cases of one world size in ONE set of processes (a process start costs more than a case); rank 0 notes every case that
+    all ranks finished, so that the test of a case can tell whether it ran, failed or was never reached."""
+    for case in cases:
+        try:
+            fn(rank, world, case)
+        except Exception as exc:
+            raise AssertionError(f"case {case}: {type(exc).__name__}: {exc}") from exc
+        dist.barrier()
+        if rank == 0:
+            with open(done_path, "a") as f:
+                f.write(case + "\n")
+
+
+_GROUPS = {}
+
+
+def grouped_case(fn, cases, world, case, timeout=1200):
+    """Assert that ``case`` passed in the grouped run of ``cases`` (all of world size ``world``) through ``fn(rank, world, case)``; the
+    group runs once per test session."""
+    key = (fn.__module__, fn.__name__, world)
+    if key not in _GROUPS:
+        with tempfile.TemporaryDirectory() as tmp:
+            done = os.path.join(tmp, "done")
+            open(done, "w").close()
+            err = None
+            try:
+                run_dist(_group_entry, world, fn, list(cases), done, timeout=timeout)
+            except AssertionError as exc:
+                err = str(exc)
+            _GROUPS[key] = (set(open(done).read().split()), err)
+    ok, err = _GROUPS[key]
+    assert case in ok, err or f"case {case} did not run"

@@ -1,9 +1,11 @@
 """Distributed Exphormer (every layer kind) vs the single-process reference on gloo CPU ranks, fp64: owned-chunk logits,
 loss, every parameter gradient after the all-reduce, BatchNorm running statistics (dropout 0 makes parity exact)."""
+import os
+
 import pytest
 import torch
 
-from dist_utils import run_dist
+from dist_utils import grouped_case, run_dist
 
 CASES = {
     "plain_2x2": dict(grid=(2, 2)),
@@ -124,9 +126,17 @@ def _world_of(case):
     return world
 
 
+def _case_worker(rank, world, case):
+    try:
+        _worker(rank, world, case)
+    finally:
+        os.environ.pop("GT_HEAD_MERGED", None)               # a case may have set a switch for itself
+
+
 @pytest.mark.parametrize("case", list(CASES))
 def test_dist_exphormer_matches_reference(case):
-    run_dist(_worker, _world_of(case), case)
+    world = _world_of(case)
+    grouped_case(_case_worker, [c for c in CASES if _world_of(c) == world], world, case)
 
 
 HEAP_CASES = ["plain_2x2", "fused_2x2", "fused_colmajor", "fused_gather_proj", "fused_sparse", "fused_ckpt", "pipelined", "streamed",

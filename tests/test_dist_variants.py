@@ -3,7 +3,7 @@ references on gloo CPU ranks (fp64), plus the plain distributed operator and the
 import pytest
 import torch
 
-from dist_utils import run_dist
+from dist_utils import grouped_case, run_dist
 
 VARIANTS = {
     "unimp_2x2": dict(model="unimp", grid=(2, 2)),
@@ -113,7 +113,8 @@ def _world_of(case):
 
 @pytest.mark.parametrize("case", list(VARIANTS))
 def test_variants_match_reference(case):
-    run_dist(_variant_worker, _world_of(case), case)
+    world = _world_of(case)
+    grouped_case(_variant_worker, [c for c in VARIANTS if _world_of(c) == world], world, case)
 
 
 HEAP_VARIANTS = ["unimp_2x2", "unimp_head_2x1x2", "graphormer_2x2", "graphormer_khop_head_1x2x2", "unimp_label_head_2x2x2",
@@ -192,12 +193,17 @@ def _op_worker(rank, world, case):
             assert (gsum - b.grad).abs().max() < 1e-10
 
 
-@pytest.mark.parametrize("case", list(OPS))
-def test_dist_operator_matches_reference(case):
+def _op_world(case):
     world = 1
     for s in OPS[case]["grid"]:
         world *= s
-    run_dist(_op_worker, world, case)
+    return world
+
+
+@pytest.mark.parametrize("case", list(OPS))
+def test_dist_operator_matches_reference(case):
+    world = _op_world(case)
+    grouped_case(_op_worker, [c for c in OPS if _op_world(c) == world], world, case)
 
 
 def _torchgt_style_worker(rank, world, fused):
