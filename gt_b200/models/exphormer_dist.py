@@ -709,7 +709,7 @@ class DistExphormer(nn.Module):
 
     def on_flat_layout(self, engine):
         """Called by the training engine once its flat buffers exist: hand every fused layer the stacked views."""
-        if not engine.cuda:
+        if engine.flat_p_bf16 is None:
             return
         for layer in self.layers:
             if hasattr(layer, "stacked_params"):

@@ -77,14 +77,16 @@ class TrainEngine:
         self.flat_m = torch.zeros_like(self.flat_p)
         self.flat_v = torch.zeros_like(self.flat_p)
         # bf16 shadow of the parameters, refreshed by the optimizer kernel: the GEMMs read it instead of casting every step
-        self.flat_p_bf16 = torch.zeros(n, dtype=torch.bfloat16, device=dev) if self.cuda else None
+        shadow = self.cuda or (heap is not None and heap.host)   # host: the emulated transport, so that tests run the same operator path
+        self.flat_p_bf16 = torch.zeros(n, dtype=torch.bfloat16, device=dev) if shadow else None
         for p in order:
             off, k = self.offsets[id(p)], p.numel()
             self.flat_p[off:off + k].copy_(p.data.reshape(-1).float())
             p.data = self.flat_p[off:off + k].view_as(p)
             p.grad = self.flat_g[off:off + k].view_as(p)
-            if self.cuda:
+            if shadow:
                 p._bf16 = self.flat_p_bf16[off:off + k].view_as(p)
+            if self.cuda:
                 p._direct_grad = True         # backward kernels may add into p.grad themselves and return no gradient to autograd
                 p._site = 0x51700000 + off    # dropout site id: position in the flat space, not an address
         self.sync_shadow()
@@ -158,6 +160,7 @@ class TrainEngine:
         self.flat_p.mul_(1 - self.cur_lr * self.wd)
         denom = (self.flat_v / (1 - b2 ** t)).sqrt_().add_(self.eps)
         self.flat_p.addcdiv_(self.flat_m / (1 - b1 ** t), denom, value=-self.cur_lr)
+        self.sync_shadow()
 
     def _body(self, loss_fn):
         if self.heap is not None:
@@ -196,7 +199,7 @@ class TrainEngine:
     def sync_shadow(self):
         """Refresh the bf16 shadow after the fp32 parameters were written by anything but the optimizer kernel (a loaded
         checkpoint, a broadcast)."""
-        if self.cuda:
+        if self.flat_p_bf16 is not None:
             self.flat_p_bf16.copy_(self.flat_p)
 
     def span(self, params, what="bf16"):

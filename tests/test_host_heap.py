@@ -223,6 +223,8 @@ def _fused_worker(rank, world, grid_shape, cfg):
                           norm="ln", comm_dtype=bf, rs_dtype=bf, kernel_dtype=bf, heap=heap, **cfg)
     model.load_ref_state_dict(ref.state_dict())
     eng = TrainEngine(model, heap=heap)
+    # as on GPUs: the operator reads K | V | message | Q from the engine's stacked bf16 shadow and adds their gradients into its flat buffer
+    assert all(layer._w_stack is not None and layer._w_stack[1] is not None for layer in model.layers)
     calls = {"n": 0}
     real = fused_layer._FusedBranch.apply
 
