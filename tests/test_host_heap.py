@@ -330,3 +330,55 @@ def _single_copy_worker(rank, world):
 
 def test_recorded_check_reports_single_buffering():
     run_dist(_single_copy_worker, 3)
+
+
+def _train_steps_worker(rank, world, grid_shape):
+    """Whole training steps through ``TrainEngine.train_step`` with the fused operator on the host transport: the loss falls, no wait
+    expires, and the replicated parameters stay bit-identical on all ranks (every rank gets the same reduced gradient)."""
+    import torch.distributed as dist
+    from gt_b200.ops import native
+    from gt_b200.parallel.collectives import set_transport
+    from gt_b200.parallel.layers import dist_cross_entropy
+    from gt_b200.parallel.symm_host import HostSymmetricHeap
+    from gt_b200.train.engine import TrainEngine
+    from gt_b200.train.workloads import exphormer_workload
+    heap = HostSymmetricHeap(64 << 20, wait_seconds=60.0, record=True)
+    set_transport(heap)
+    wl = exphormer_workload("cpu_small", grid_shape, "cpu", torch.bfloat16, seed=0, heap=heap, scale_down=4, dropout=0.0, layers=2, hidden=32, heads=4,
+                            kernel_dtype=torch.bfloat16, comm_dtype=torch.bfloat16, rs_dtype=torch.bfloat16)
+    model = wl["model"]
+    for p in model.parameters():
+        dist.broadcast(p.data, src=0)
+    eng = TrainEngine(model, lr=2e-2, weight_decay=0.0, total_steps=12, warmup=1, heap=heap)
+    assert all(layer._w_stack is not None for layer in model.layers)
+    x, y, m = wl["x"], wl["y"], wl["masks"]["train"]
+    from gt_b200.parallel import fused_layer
+    calls, real = {"n": 0}, fused_layer._FusedBranch.apply
+
+    def counted(*a):
+        calls["n"] += 1
+        return real(*a)
+    fused_layer._FusedBranch.apply = counted
+    losses = []
+    for _ in range(6):
+        loss = eng.train_step(lambda: dist_cross_entropy(model(x), y, m, wl["n_train"]))
+        tot = loss.detach().float().clone()
+        dist.all_reduce(tot)
+        losses.append(tot.item())
+    fused_layer._FusedBranch.apply = real
+    native.check_status(torch.device("cpu"))
+    assert calls["n"] == 6 * 2, calls                         # the operator ran in every layer of every step
+    assert all(torch.isfinite(torch.tensor(losses))) and losses[-1] < losses[0] - 0.05, losses
+    flat = [torch.empty_like(eng.flat_p) for _ in range(world)]
+    dist.all_gather(flat, eng.flat_p)
+    assert all(torch.equal(flat[0], f) for f in flat[1:]), "replicated parameters differ between ranks"
+    assert torch.equal(eng.flat_p_bf16.float(), eng.flat_p.to(torch.bfloat16).float())          # the shadow follows the optimizer
+    heap.check_symmetric()
+    heap.check_recorded()
+    dist.barrier()
+    set_transport(None)
+    heap.close()
+
+
+def test_training_steps_with_the_fused_operator_between_cpu_ranks():
+    run_dist(_train_steps_worker, 4, (2, 2))
