@@ -14,8 +14,10 @@ warm-up, and whole-step CUDA-graph capture.
 
 On CPU tensors (gloo tests, the CPU baseline) the same engine drives ``torch.optim.AdamW`` semantics in plain torch ops.
 """
+import atexit
 import math
 import os
+import shutil
 import tempfile
 
 import torch
@@ -35,8 +37,9 @@ def init_single_process_group(backend=None):
     if dist.is_initialized():
         return
     backend = backend or ("nccl" if torch.cuda.is_available() else "gloo")
-    path = os.path.join(tempfile.mkdtemp(prefix="gt_b200_pg_"), "store")
-    dist.init_process_group(backend, init_method=f"file://{path}", rank=0, world_size=1)
+    folder = tempfile.mkdtemp(prefix="gt_b200_pg_")
+    atexit.register(shutil.rmtree, folder, True)             # the rendezvous file is of no use after the process
+    dist.init_process_group(backend, init_method=f"file://{os.path.join(folder, 'store')}", rank=0, world_size=1)
 
 
 class TrainEngine:
