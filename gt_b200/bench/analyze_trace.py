@@ -53,9 +53,9 @@ def analyze(path, top_gaps=5):
 
 def main(argv=None):
     argv = sys.argv[1:] if argv is None else argv
-    if not argv:
+    if not argv or argv[0] in ("-h", "--help"):
         print(__doc__)
-        return 2
+        return 2 if not argv else 0
     out = []
     for path in argv:
         r = analyze(path)

@@ -316,3 +316,25 @@ def test_curves_from_metrics_jsonl(tmp_path):
     rows = parse_logs.curves_jsonl([str(f)])
     assert [r["epoch"] for r in rows] == [0, 2, 4] and abs(rows[-1]["train_seconds"] - 0.1) < 1e-9
     assert plot_figures.time_to_acc_series(rows, "val_acc", 0.4) == {str(f): rows[1]["train_seconds"]}
+
+
+def _bench_modules():
+    import glob
+    import os
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gt_b200", "bench")
+    names = sorted(os.path.basename(f)[:-3] for f in glob.glob(os.path.join(root, "*.py")))
+    return [n for n in names if not n.startswith("_") and n != "model_validation_data"]
+
+
+def test_every_bench_tool_imports_and_answers_help_without_a_gpu():
+    """The measurement tools need GPUs to measure, but none may need one to import or to print its usage."""
+    import subprocess
+    import sys
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    procs = {n: subprocess.Popen([sys.executable, "-m", f"gt_b200.bench.{n}", "--help"], cwd=root, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+             for n in _bench_modules()}
+    assert len(procs) >= 25
+    for n, p in procs.items():
+        out, _ = p.communicate(timeout=300)
+        assert p.returncode == 0 and len(out) > 40, (n, p.returncode, out[-300:])
