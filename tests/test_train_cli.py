@@ -241,3 +241,21 @@ def test_cli_token_dense_trains_like_token_edges(tmp_path):
     assert len(rows["edges"]) == len(rows["dense"]) > 0
     for ra, rb in zip(rows["edges"], rows["dense"]):
         assert abs(ra["loss"] - rb["loss"]) < 1e-4 * max(1.0, abs(ra["loss"])), (ra, rb)
+
+
+def test_launch_scripts_parse_and_never_touch_gpu_settings():
+    """Shell syntax of every launcher; none of them sets clocks, power limits, persistence or compute modes, and every Nsight Compute
+    command line leaves the clocks alone."""
+    import glob
+    import re
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    scripts = sorted(glob.glob(os.path.join(root, "launch", "*")) + [os.path.join(root, "baseline", "dac26", "launch.sh")])
+    assert len(scripts) >= 8
+    for path in scripts:
+        assert subprocess.run(["bash", "-n", path]).returncode == 0, path
+        text = open(path).read()
+        assert not re.search(r"nvidia-smi\s+(-lgc|-ac|-pm|-pl|-c|--lock|--reset|-rgc|-r\b)", text), path
+        for line in text.splitlines():
+            if re.match(r"\s*ncu\s", line) or " ncu " in line and not line.lstrip().startswith("#"):
+                assert "--clock-control none" in text, path
