@@ -117,6 +117,7 @@ class Model:
     ffn_mult: int = 2
     sparse_comm: bool = False
     transport: str = "nccl"        # "nccl" or "p2p" (peer-memory kernels: lower latency, pull instead of a2a-v)
+    token_dense: bool = False      # the global token as dense terms on the owned rows (parallel/token_dense.py), not as 2 n edges
 
     @property
     def wire_bytes(self):
@@ -283,7 +284,9 @@ def fused_layer_ms(pd, po, g: Graph, m: Model, gpn=GPUS_PER_NODE):
     d, H, b, a = m.hidden, m.heads, m.wire_bytes, m.act_bytes
     R, C, O = g.n / pd, g.n / po, g.n / P
     ea, eg = g.e_attn / P, g.e_gcn / P
-    if g.token and P > 1:
+    if g.token and m.token_dense:
+        ea = (g.e_attn - 2 * g.n) / P                        # the token's row and column are not edges (dense terms below)
+    elif g.token and P > 1:
         # The token's row lies in ONE row block (n / po entries for each rank of that row group) and its column in ONE column
         # block (n / pd entries per rank of that column group): the rank that has both is the straggler every other rank waits
         # for at the next collective, so the step runs at its speed.
@@ -301,6 +304,12 @@ def fused_layer_ms(pd, po, g: Graph, m: Model, gpn=GPUS_PER_NODE):
     bw["attn"] = attn_ms(ea, R, C, H, d // H, "bwd", g.skew)
     bw["spmm"] = spmm_ms(eg, C, R, d, g.skew) if m.with_gcn else 0.0
     bw["gemm"] = gemm_ms(proj, d, 1) + gemm_ms(proj, d, 2)
+    if g.token and m.token_dense:
+        # Q, K and V of the owned rows, about a dozen element-wise passes over [O, d] fp32 in some twenty small kernels, and two
+        # all-reduces of a few hundred numbers per direction (an estimate from the model's primitives: not measured)
+        small = coll_ms("ar", (min(P, gpn), max(1, P // gpn)), 4 * (d + H + 8), m.transport)
+        f["token"] = 3 * gemm_ms(2 * O * d * d, d, 0) + ew_ms(O * d * 4 * 12, 20) + 2 * small
+        bw["token"] = 3 * (gemm_ms(2 * O * d * d, d, 1) + gemm_ms(2 * O * d * d, d, 2)) + ew_ms(O * d * 4 * 24, 40) + 2 * small
     if m.transport == "p2p" and not m.sparse_comm:
         # collectives inside the compute kernels (peer memory, epoch channels): the transfer hides behind the kernel that
         # issues it; what remains is the flag latency, the part of the transfer that outlasts the kernel, and the owner-side

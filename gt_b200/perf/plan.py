@@ -62,6 +62,7 @@ def main(argv=None):
     ap.add_argument("--classes", type=int, default=40)
     ap.add_argument("--exp_deg", type=int, default=4, help="expander degree of the Exphormer attention graph (0: attention over the graph edges only)")
     ap.add_argument("--token", action="store_true", help="a global token connected to every node")
+    ap.add_argument("--token_dense", action="store_true", help="model the token as dense terms (train_dist --token_dense) instead of 2 n edges")
     ap.add_argument("--hidden", type=int, default=256)
     ap.add_argument("--heads", type=int, default=8)
     ap.add_argument("--layers", type=int, default=4)
@@ -78,7 +79,7 @@ def main(argv=None):
         ap.error("give --workload or both --nodes and --edges")
     e_attn = gs.attention_edges(args.nodes, args.edges, args.exp_deg) + (2 * args.nodes if args.token else 0)
     g = gs.Graph(args.nodes, e_attn, args.edges + args.nodes, args.features, classes=args.classes, exp_deg=args.exp_deg, token=args.token)
-    m = gs.Model(args.hidden, args.heads, args.layers, with_gcn=not args.no_gcn, transport=args.comm)
+    m = gs.Model(args.hidden, args.heads, args.layers, with_gcn=not args.no_gcn, transport=args.comm, token_dense=args.token_dense)
     rows = layouts(args.gpus, g, m, args.capacity_gb)
     if args.json:
         print(json.dumps(dict(nodes=args.nodes, attn_edges=e_attn, gpus=args.gpus, capacity_gb=args.capacity_gb, layouts=rows)))

@@ -168,3 +168,17 @@ def test_planner_lists_every_layout_and_agrees_with_the_selectors(capsys):
     assert "--stream_sub 16" in fitting[0]["flags"]
     with pytest.raises(SystemExit):
         plan.main(["--gpus", "8"])
+
+
+def test_model_prices_the_dense_token_option():
+    from gt_b200.perf import grid_select as gs
+    n, e = 169_344, 2_332_486
+    g = gs.Graph(n, gs.attention_edges(n, e, 4) + 2 * n, e + n, 128, exp_deg=4, token=True)
+    edges = gs.Model(256, 8, 4, transport="p2p")
+    dense = gs.Model(256, 8, 4, transport="p2p", token_dense=True)
+    t_e, parts_e = gs.predict_fused_ms(4, 2, g, edges, breakdown=True)
+    t_d, parts_d = gs.predict_fused_ms(4, 2, g, dense, breakdown=True)
+    assert "token" in parts_d and "token" not in parts_e
+    assert parts_d["attn"] < parts_e["attn"] and parts_d["bwd attn"] < parts_e["bwd attn"]       # no straggler row / column any more
+    assert t_d - parts_d["token"] - parts_d["bwd token"] < t_e                                    # the sparse part got faster ...
+    assert t_d > t_e                                                                             # ... but the dense terms as written cost more
