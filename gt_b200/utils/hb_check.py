@@ -25,6 +25,7 @@ The reference has no counterpart (its collectives are NCCL calls; ``gt3d/gt3d/di
 synchronisation); compute-sanitizer's race detection is the tool one would use on a device, this is the protocol-level
 equivalent that needs none.
 """
+import bisect
 from collections import namedtuple
 
 Violation = namedtuple("Violation", "kind rank op owner buf detail")
@@ -204,7 +205,6 @@ def trace_from_logs(logs):
             if ev[0] in ("read", "write"):
                 cuts.setdefault(ev[1], set()).update((ev[2], ev[2] + ev[3]))
     cuts = {o: sorted(c) for o, c in cuts.items()}
-    import bisect
     tr = ProtocolTrace(world)
     for r, log in enumerate(events):
         members_of = {}
