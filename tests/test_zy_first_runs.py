@@ -36,3 +36,31 @@ def test_dense_global_token_matches_token_edges_on_the_kernels():
     scale = outs[False].abs().max().item()
     assert (outs[True] - outs[False]).abs().max().item() < 3e-2 * scale
     assert (losses[True] - losses[False]).abs().max().item() < 3e-2
+
+
+BASE = ["--grid", "1", "1", "--synthetic", "exphormer_arxiv", "--scale_down", "32", "--fused", "--norm", "ln", "--bf16", "--virtual_node", "--layers", "2",
+        "--hidden", "64", "--heads", "4", "--dropout", "0.0", "--warmup", "1"]
+
+
+def test_trainer_command_line_on_a_gpu(tmp_path):
+    """``train_dist`` end to end on one GPU with a captured step: save, evaluate the checkpoint only, write predictions and metrics."""
+    import json
+    from gt_b200.train.train_dist import main
+    ck, pred, met = str(tmp_path / "ck.pt"), str(tmp_path / "pred.pt"), str(tmp_path / "m.jsonl")
+    res = main(BASE + ["--epochs", "6", "--cuda_graph", "--save", ck, "--metrics_jsonl", met])
+    assert len(res["epoch_ms"]) == 6 and all(t > 0 for t in res["epoch_ms"])
+    rows = [json.loads(line) for line in open(met)]
+    assert rows and rows[-1]["loss"] < rows[0]["loss"]
+    ev = main(BASE + ["--epochs", "6", "--resume", ck, "--eval_only", "--predict_out", pred])
+    blob = torch.load(pred)
+    assert blob["pred"].numel() == blob["num_nodes"] and 0.0 <= ev["eval"]["valid"] <= 1.0 and ev["epoch"] == 6
+
+
+def test_dense_token_and_streamed_generation_from_the_command_line():
+    from gt_b200.train.train_dist import main
+    a = main(BASE + ["--epochs", "4"])
+    b = main(BASE + ["--epochs", "4", "--token_dense"])
+    assert abs(a["best"]["val"] - b["best"]["val"]) < 0.05
+    c = main(["--grid", "1", "1", "--synthetic", "exphormer_rmat26", "--scale_down", "16384", "--stream_gen", "--stream_sub", "2", "--fused", "--bf16",
+              "--epochs", "3", "--hidden", "64", "--heads", "4", "--norm", "ln"])
+    assert len(c["epoch_ms"]) == 3
