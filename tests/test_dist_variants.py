@@ -246,3 +246,14 @@ def _torchgt_style_worker(rank, world, fused):
 @pytest.mark.parametrize("fused", [False, True], ids=["plain", "fused"])
 def test_torchgt_style_graphormer_matches_single_device(fused):
     run_dist(_torchgt_style_worker, 2, fused)
+
+
+def _stage_diff_worker(rank, world):
+    from gt_b200.utils.stage_diff import main
+    rows = main(["--grid", "2", "1", "--fused", "--token", "--token_dense", "--layers", "2"])
+    assert [r[0] for r in rows] == ["input stage", "layer 0", "layer 1", "logits"]
+    assert all(err < 1e-10 and mag > 0 for _, err, mag in rows), rows
+
+
+def test_stage_by_stage_diff_tool():
+    run_dist(_stage_diff_worker, 2)
