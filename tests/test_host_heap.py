@@ -382,3 +382,31 @@ def _train_steps_worker(rank, world, grid_shape):
 
 def test_training_steps_with_the_fused_operator_between_cpu_ranks():
     run_dist(_train_steps_worker, 4, (2, 2))
+
+
+def test_emulated_entry_points_keep_the_signatures_of_the_native_binding():
+    """Drift guard: every entry point that the host emulation restates takes as many arguments as the function of the same name in the
+    native module (whose Python-visible signatures pybind11 writes into the docstrings).  A change of a binding that is not mirrored
+    here would otherwise only show up as a TypeError in some emulated run."""
+    import inspect
+    from gt_b200 import build_ext
+    from gt_b200.parallel.symm_host import HostExt
+    mod = build_ext.load_prebuilt()
+    if mod is None:
+        pytest.skip("the native module is not built here")
+    checked = 0
+    for name, fn in inspect.getmembers(HostExt, predicate=inspect.isfunction):
+        if name.startswith("_"):
+            continue
+        assert hasattr(mod, name), f"{name} is emulated but the native module has no such entry point"
+        doc = getattr(mod, name).__doc__.splitlines()[0]
+        inner = doc[doc.index("(") + 1:doc.rindex(")")]
+        depth, n = 0, 1 if inner.strip() else 0
+        for ch in inner:
+            depth += ch in "[("
+            depth -= ch in "])"
+            n += ch == "," and depth == 0
+        params = [p for p in inspect.signature(fn).parameters if p != "self"]
+        assert n == len(params), (name, doc, params)
+        checked += 1
+    assert checked >= 30
