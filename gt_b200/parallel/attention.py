@@ -239,6 +239,8 @@ class DistAttentionPullKV(_OpBase):
 
     def __init__(self, grid, block, num_heads, head_dim, heap, score="gated", norm="clampexp", clamp=(-5.0, 5.0)):
         super().__init__(grid, block, num_heads, head_dim, "cuda", score, norm, clamp, 1e-6)
+        if not heap.group_is_local(grid.col_group):
+            raise ValueError("K / V rows are pulled from peer memory: the column group must lie within one machine")
         self.heap = heap
 
     def forward(self, q_blk, k_loc, v_loc, gate=None):

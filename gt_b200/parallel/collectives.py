@@ -35,15 +35,15 @@ def set_transport(heap):
 
 def _p2p_ok(x, group, rows_out):
     h = _HEAP[0]
-    if h is None or not h.reaches(x) or x.dtype not in h._float_types():
+    if h is None or not h.reaches(x, group) or x.dtype not in h._float_types():
         return False
     per_rank = x.numel() // (group_size(group) if rows_out else 1)
     return (per_rank * x.element_size()) % 16 == 0 and per_rank % 8 == 0
 
 
-def _a2a_p2p_ok(x, slab_elems):
+def _a2a_p2p_ok(x, slab_elems, group):
     h = _HEAP[0]
-    return h is not None and h.reaches(x) and x.dtype in h._float_types() and (slab_elems * x.element_size()) % 16 == 0
+    return h is not None and h.reaches(x, group) and x.dtype in h._float_types() and (slab_elems * x.element_size()) % 16 == 0
 
 
 # GT_SYNC_COLLECTIVES (default 0): 1 = host-synchronise the current stream before every synchronous collective, so that the previous
@@ -132,7 +132,7 @@ def raw_rows_to_heads(x, group, p):
     if p == 1:
         return x
     chunk, h, d = x.shape
-    if _a2a_p2p_ok(x, (h // p) * d):
+    if _a2a_p2p_ok(x, (h // p) * d, group):
         return _HEAP[0].rows_to_heads(x.contiguous(), group)
     send = x.view(chunk, p, h // p, d).transpose(0, 1).contiguous()
     return raw_all_to_all(send, group).view(p * chunk, h // p, d)
@@ -144,7 +144,7 @@ def raw_heads_to_rows(y, group, p):
         return y
     n, hg, d = y.shape
     chunk = n // p
-    if _a2a_p2p_ok(y, hg * d):
+    if _a2a_p2p_ok(y, hg * d, group):
         return _HEAP[0].heads_to_rows(y.contiguous(), group)
     recv = raw_all_to_all(y.contiguous().view(p, chunk, hg, d), group)
     return recv.transpose(0, 1).contiguous().view(chunk, p * hg, d)
@@ -289,7 +289,7 @@ def _sum_over_ranks(x, group):
     if group_size(group) == 1:
         return x.clone()
     h = _HEAP[0]
-    if h is not None and h.reaches(x) and x.dtype in h._float_types() and x.numel() % 8 == 0 and x.numel() > 0:
+    if h is not None and h.reaches(x, group) and x.dtype in h._float_types() and x.numel() % 8 == 0 and x.numel() > 0:
         x = x.contiguous()
         return _instrument("all_reduce", group, x.numel() * x.element_size(), lambda: h.all_reduce(x, torch.empty_like(x), group=group))
     y = x.clone()

@@ -22,7 +22,7 @@ from .grid import group_size
 
 def fused_ok(x, weight, group):
     heap = _HEAP[0]
-    return (heap is not None and x.is_cuda and x.dtype == torch.bfloat16 and group_size(group) > 1 and x.dim() == 2
+    return (heap is not None and x.is_cuda and heap.group_is_local(group) and x.dtype == torch.bfloat16 and group_size(group) > 1 and x.dim() == 2
             and x.shape[1] % 8 == 0 and x.shape[1] <= 512 and weight.shape[0] % 8 == 0 and group_size(group) <= 8)
 
 

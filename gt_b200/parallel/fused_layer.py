@@ -69,7 +69,8 @@ def branch_supported(layer, x):
     if not native.ext().attn_shape_supported(h, dh, 3):
         return False
     multi = group_size(g.row_group) > 1 or group_size(g.col_group) > 1
-    if multi and (_HEAP[0] is None or group_size(g.row_group) > 8 or group_size(g.col_group) > 8):
+    if multi and (_HEAP[0] is None or group_size(g.row_group) > 8 or group_size(g.col_group) > 8
+                  or not (_HEAP[0].group_is_local(g.row_group) and _HEAP[0].group_is_local(g.col_group))):
         return False
     if x.shape[0] % 8:
         return False

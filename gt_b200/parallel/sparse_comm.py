@@ -130,7 +130,7 @@ class SparseRowPlan:
         if self.g == 1:
             out = x2.index_select(0, self.send_idx.long()).view(-1, *shp)
             return (None, (lambda: out)) if async_op else out
-        if self.transport == "pull" and self.heap.reaches(x):
+        if self.transport == "pull" and self.heap.reaches(x, self.group):
             xp, width = self._pad8(x2)
             out = self.heap.pull_gather(xp, self)[:, :width].reshape(-1, *shp)
             return (None, (lambda: out)) if async_op else out
@@ -149,7 +149,7 @@ class SparseRowPlan:
         if self.g == 1:
             out = self._accumulate(y2).view(-1, *shp)
             return (None, (lambda: out)) if async_op else out
-        if self.transport == "pull" and self.heap.reaches(y):
+        if self.transport == "pull" and self.heap.reaches(y, self.group):
             yp, width = self._pad8(y2)
             out = self.heap.pull_reduce(yp, self)[:, :width].reshape(-1, *shp)
             return (None, (lambda: out)) if async_op else out

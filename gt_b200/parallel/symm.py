@@ -122,15 +122,19 @@ class SymmetricHeap:
         self.base = e.heap_alloc(self.bytes)
         self.rank, self.world = dist.get_rank(), dist.get_world_size()
         handles = [None] * self.world
-        dist.all_gather_object(handles, (self.rank, e.heap_ipc_handle(self.base), socket.gethostname()))
-        if len({host for _, _, host in handles}) > 1:
-            # CUDA IPC maps memory of GPUs of one machine; across nodes the grid collectives stay on NCCL
-            e.heap_free(self.base)
-            raise RuntimeError("the symmetric heap (peer-memory transport) spans the GPUs of ONE node, but the process group covers "
-                               f"{len({host for _, _, host in handles})} hosts: run with --comm nccl")
+        # GT_HOSTNAME overrides the machine name (tests split the ranks of one machine into pretended nodes)
+        dist.all_gather_object(handles, (self.rank, e.heap_ipc_handle(self.base), os.environ.get("GT_HOSTNAME") or socket.gethostname()))
+        # Peer memory is mapped between the ranks of ONE machine.  When the process group covers several, every rank maps the heaps
+        # of its own machine only: a group whose members all share a machine runs on the peer-memory transport, any other group
+        # stays on NCCL (``group_is_local``), and every rank still makes the same allocations, so offsets agree wherever they are used.
+        self.hosts = [None] * self.world
+        for r, _, host in handles:
+            self.hosts[r] = host
         self.peer_base = [0] * self.world
-        for r, h, _ in handles:
-            self.peer_base[r] = self.base if r == self.rank else e.heap_open(h)
+        for r, h, host in handles:
+            if host == self.hosts[self.rank]:
+                self.peer_base[r] = self.base if r == self.rank else e.heap_open(h)
+        self._local_groups = {}
         self.top = 0
         self.alloc_log = (0, 0)
         self.groups = {}
@@ -155,9 +159,18 @@ class SymmetricHeap:
     def _float_types(self):
         return (torch.float32, torch.bfloat16, torch.float64) if self.host else (torch.float32, torch.bfloat16)
 
-    def reaches(self, x):
-        """``x`` lives where this heap's kernels run."""
-        return x.is_cuda or self.host
+    def group_is_local(self, group=None):
+        """Every rank of ``group`` (default: all ranks) runs on this rank's machine, so their heaps are mapped here."""
+        key = id(group) if group is not None else None
+        ok = self._local_groups.get(key)
+        if ok is None:
+            ranks = range(self.world) if group is None else dist.get_process_group_ranks(group)
+            ok = self._local_groups[key] = all(self.hosts[r] == self.hosts[self.rank] for r in ranks)
+        return ok
+
+    def reaches(self, x, group=None):
+        """``x`` lives where this heap's kernels run, and the heaps of all ranks of ``group`` are mapped on this rank."""
+        return (x.is_cuda or self.host) and self.group_is_local(group)
 
     def view(self, off, shape, dtype):
         return native.ext().tensor_from_ptr(self.base + off, list(shape), _DT[dtype], self.device.index or 0)

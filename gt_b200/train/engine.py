@@ -75,7 +75,8 @@ class TrainEngine:
         n = -(-n // 8) * 8
         self.numel = n
         self.flat_p = torch.zeros(n, dtype=torch.float32, device=dev)
-        self.on_heap = heap is not None and (self.cuda or heap.host)     # gradients live in the symmetric heap, reduced by its kernels
+        # gradients live in the symmetric heap and are reduced by its kernels when every rank of the group is on this machine
+        self.on_heap = heap is not None and (self.cuda or heap.host) and heap.group_is_local(group)
         self.flat_g = heap.empty(n, torch.float32, "grads") if self.on_heap else torch.zeros(n, dtype=torch.float32, device=dev)
         self.flat_m = torch.zeros_like(self.flat_p)
         self.flat_v = torch.zeros_like(self.flat_p)

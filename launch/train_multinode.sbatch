@@ -7,6 +7,8 @@
 # Multi-node launch under Slurm: one torchrun agent per node, 8 ranks each (one per B200).  Ranks are laid out so that a
 # row group (P_o <= 8 consecutive ranks) stays inside an NVSwitch domain; see gt_b200/perf/grid_select.py placement().
 #   sbatch --nodes 4 launch/train_multinode.sbatch --grid 4 8 --fused --data /data/papers100M_p32 --bf16 --norm ln
+# With --comm p2p the groups whose ranks all sit on one node (here: the row groups) move their rows through peer memory, the
+# groups that cross nodes (the column groups, the gradient all-reduce) stay on NCCL.
 set -euo pipefail
 cd "${SLURM_SUBMIT_DIR:-$(dirname "$0")/..}"
 HEAD=$(scontrol show hostnames "$SLURM_JOB_NODELIST" | head -n 1)

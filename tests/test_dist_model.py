@@ -276,3 +276,34 @@ def _token_dense_worker(rank, world, grid_shape, cfg):
                          ids=["2x2", "4x2_ln", "1x2", "2x2_pipelined", "1x1"])
 def test_dense_global_token_matches_token_edges(grid_shape, cfg):
     run_dist(_token_dense_worker, grid_shape[0] * grid_shape[1], grid_shape, cfg)
+
+
+def _two_node_worker(rank, world, cases):
+    """Four ranks that pretend to sit on two machines (ranks 0-1 and 2-3): on the 2 x 2 grid the row groups lie within a machine and
+    run on the peer-memory transport, the column groups and the world group cross machines and stay on gloo; same parity."""
+    import torch.distributed as dist
+    os.environ["GT_HOSTNAME"] = "node%d" % (rank // 2)
+    from gt_b200.parallel import collectives
+    used = {"heap": 0, "gloo": 0}
+    real_ag = dist.all_gather_into_tensor
+
+    def counting_ag(*a, **k):
+        used["gloo"] += 1
+        return real_ag(*a, **k)
+    dist.all_gather_into_tensor = counting_ag
+    try:
+        for case in cases:
+            try:
+                _worker(rank, world, case, True)
+            except Exception as exc:
+                raise AssertionError(f"case {case}: {type(exc).__name__}: {exc}") from exc
+            dist.barrier()
+    finally:
+        dist.all_gather_into_tensor = real_ag
+        os.environ.pop("GT_HOSTNAME", None)
+    assert used["gloo"] > 0, "no collective of a cross-machine group ran on gloo"
+    assert collectives._HEAP[0] is None
+
+
+def test_groups_within_a_machine_use_peer_memory_and_the_others_do_not():
+    run_dist(_two_node_worker, 4, ["plain_2x2", "fused_2x2", "fused_sparse", "streamed", "head_2x1x2"], timeout=900)
