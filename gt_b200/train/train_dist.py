@@ -373,6 +373,11 @@ def main(argv=None):
     if rank == 0:
         print(f"data: N={n} (padded {grid.n_pad}, chunk {grid.chunk}) grid={tuple(args.grid)} backend={backend} E={e_total} "
               f"n_train={n_train} dtype={str(dtype).split('.')[-1]} comm={args.comm}", flush=True)
+        if heap is not None and len(set(heap.hosts)) > 1:
+            kinds = [("row", grid.row_group), ("column", grid.col_group)] + ([("head", grid.head_group)] if getattr(grid, "p_heads", 1) > 1 else [])
+            print("[comm] " + str(len(set(heap.hosts))) + " machines: " + ", ".join(
+                f"{k} group on {'peer memory' if heap.group_is_local(g) else 'NCCL'}" for k, g in kinds)
+                + f", gradient all-reduce on {'peer memory' if heap.group_is_local(None) else 'NCCL'}", flush=True)
         if args.sparse_comm and getattr(model, "sparse_info", None):
             inf = model.sparse_info
             print(f"[sparse_comm] row share {inf['row_share']:.3f} -> {'SPARSE' if inf['use_row'] else 'dense'}; "

@@ -259,3 +259,21 @@ def test_launch_scripts_parse_and_never_touch_gpu_settings():
         for line in text.splitlines():
             if re.match(r"\s*ncu\s", line) or " ncu " in line and not line.lstrip().startswith("#"):
                 assert "--clock-control none" in text, path
+
+
+def _two_machines_cli_worker(rank, world):
+    os.environ["GT_HOSTNAME"] = "node%d" % (rank // 2)
+    try:
+        from gt_b200.train.train_dist import main
+        res = main(["--grid", "2", "2", "--synthetic", "cpu_small", "--scale_down", "4", "--fused", "--epochs", "3", "--norm", "ln", "--comm", "p2p",
+                    "--heap_mb", "64", "--check_protocol"])
+        assert len(res["epoch_ms"]) == 3
+    finally:
+        os.environ.pop("GT_HOSTNAME", None)
+
+
+def test_cli_on_two_pretended_machines_mixes_the_transports(capfd):
+    run_dist(_two_machines_cli_worker, 4)
+    out = capfd.readouterr().out
+    assert "[comm] 2 machines: row group on peer memory, column group on NCCL, gradient all-reduce on NCCL" in out
+    assert "[protocol]" in out
