@@ -310,7 +310,9 @@ def fused_layer_ms(pd, po, g: Graph, m: Model, gpn=GPUS_PER_NODE):
         small = coll_ms("ar", (min(P, gpn), max(1, P // gpn)), 4 * (d + H + 8), m.transport)
         f["token"] = 3 * gemm_ms(2 * O * d * d, d, 0) + ew_ms(O * d * 4 * 12, 20) + 2 * small
         bw["token"] = 3 * (gemm_ms(2 * O * d * d, d, 1) + gemm_ms(2 * O * d * d, d, 2)) + ew_ms(O * d * 4 * 24, 40) + 2 * small
-    if m.transport == "p2p" and not m.sparse_comm:
+    if m.transport == "p2p" and not m.sparse_comm and pl["row"][1] == 1 and pl["col"][1] == 1:
+        # (both groups within one machine; a group that crosses machines takes the operator off the peer-memory path and the layer
+        # runs with NCCL collectives for that group: the branch below is then the estimate)
         # collectives inside the compute kernels (peer memory, epoch channels): the transfer hides behind the kernel that
         # issues it; what remains is the flag latency, the part of the transfer that outlasts the kernel, and the owner-side
         # slot sums / unpacking passes
