@@ -192,6 +192,10 @@ class SymmetricHeap:
         key = id(group) if group is not None else None
         c = self.groups.get(key)
         if c is None:
+            if not self.group_is_local(group):
+                # never hand a kernel the address of a heap that is not mapped here: refuse on the host
+                raise RuntimeError("this group crosses machines: its collectives run on NCCL, not on the peer-memory transport "
+                                   "(callers test SymmetricHeap.group_is_local / reaches first)")
             c = self.groups[key] = GroupContext(self, group, str(key))
         return c
 

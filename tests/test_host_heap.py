@@ -410,3 +410,27 @@ def test_emulated_entry_points_keep_the_signatures_of_the_native_binding():
         assert n == len(params), (name, doc, params)
         checked += 1
     assert checked >= 30
+
+
+def _refuse_worker(rank, world):
+    """A collective of the heap over a group that crosses (pretended) machines is refused on the host; it never reaches a kernel."""
+    import torch.distributed as dist
+    os.environ["GT_HOSTNAME"] = "node%d" % (rank // 2)
+    from gt_b200.parallel.symm_host import HostSymmetricHeap
+    try:
+        heap = HostSymmetricHeap(1 << 20)
+        assert not heap.group_is_local(None) and heap.peer_base[(rank + 2) % 4] == 0 and heap.peer_base[rank ^ 1] != 0
+        pair = [dist.new_group([0, 1]), dist.new_group([2, 3])][rank // 2]
+        assert heap.group_is_local(pair)
+        x = torch.full((8, 8), float(rank))
+        assert torch.equal(heap.all_gather(x, pair)[8:], torch.full((8, 8), float(rank | 1)))
+        with pytest.raises(RuntimeError, match="crosses machines"):
+            heap.all_gather(x, None)
+        dist.barrier()
+        heap.close()
+    finally:
+        os.environ.pop("GT_HOSTNAME", None)
+
+
+def test_heap_refuses_groups_that_cross_machines():
+    run_dist(_refuse_worker, 4)
