@@ -338,3 +338,23 @@ def test_every_bench_tool_imports_and_answers_help_without_a_gpu():
     for n, p in procs.items():
         out, _ = p.communicate(timeout=300)
         assert p.returncode == 0 and len(out) > 40, (n, p.returncode, out[-300:])
+
+
+def test_timing_regression_check(tmp_path, capsys):
+    import json
+    from gt_b200.bench import check_regression as cr
+    assert cr.recorded_ms((4, 2)) == 6.00 and cr.recorded_ms((3, 3)) is None
+    line = dict(ms_per_step=6.2, config=dict(grid=[4, 2]), clocks=dict(reasons=[]))
+    assert cr.judge(line)[0] == "ok"
+    assert cr.judge(dict(line, ms_per_step=7.5))[0] == "slower"
+    assert cr.judge(dict(line, ms_per_step=9.0, clocks=dict(reasons=["sw_thermal_slowdown"])))[0] == "inconclusive"
+    assert cr.judge(dict(line, clocks=dict(reasons=["sw_power_cap"])))[0] == "ok"          # a power cap during dense kernels is normal
+    assert cr.judge(dict(line, config=dict(grid=[3, 3])))[0] == "unknown"
+    f = tmp_path / "lines.txt"
+    f.write_text("NCCL version 2.28\n" + json.dumps(line) + "\n" + json.dumps(dict(line, ms_per_step=20.0, config=dict(grid=[1, 1]))) + "\n")
+    assert cr.main(["--from_json", str(f)]) == 0
+    out = capsys.readouterr().out
+    assert "[ok] grid 4x2" in out and "[ok] grid 1x1" in out
+    g = tmp_path / "slow.json"
+    g.write_text(json.dumps(dict(line, ms_per_step=8.0)))
+    assert cr.main(["--from_json", str(g), "--tolerance", "0.2"]) == 1
