@@ -31,7 +31,10 @@ def recorded_ms(grid, transport=None):
 
 def judge(result, tolerance=0.10):
     """``(verdict, text)`` for one result line of ``bench.py``: verdict in ok / slower / inconclusive / unknown."""
-    grid = tuple(result.get("config", {}).get("grid") or ())
+    cfg = result.get("config", {})
+    grid = tuple(cfg.get("grid") or ())
+    if not grid and str(cfg.get("parallelism", "")).startswith("grid "):
+        grid = tuple(int(v) for v in cfg["parallelism"][5:].split("x"))
     ms = result.get("ms_per_step")
     if not grid or ms is None:
         return "unknown", "not a bench.py result line"
