@@ -277,3 +277,25 @@ def test_cli_on_two_pretended_machines_mixes_the_transports(capfd):
     out = capfd.readouterr().out
     assert "[comm] 2 machines: row group on peer memory, column group on NCCL, gradient all-reduce on NCCL" in out
     assert "[protocol]" in out
+
+
+def test_resilient_launcher_retries_an_out_of_memory_run_with_checkpointing(tmp_path):
+    """A stand-in interpreter fails the first attempt with an out-of-memory message; the supervisor's second attempt carries --checkpoint."""
+    import stat
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    fake = tmp_path / "fakepython"
+    calls = tmp_path / "calls.txt"
+    fake.write_text(f"""#!/usr/bin/env bash
+echo "$@" >> {calls}
+if [ "$(wc -l < {calls})" -eq 1 ]; then echo "torch.OutOfMemoryError: CUDA out of memory. Tried to allocate 20.00 GiB" >&2; exit 1; fi
+exit 0
+""")
+    fake.chmod(fake.stat().st_mode | stat.S_IXUSR)
+    env = dict(os.environ, PYTHON=str(fake), RESTART_DELAY="0", MAX_RESTARTS="2")
+    r = subprocess.run([os.path.join(root, "launch", "train_resilient.sh"), "0", str(tmp_path / "x.pt"), "--grid", "1", "1"], env=env, capture_output=True,
+                       text=True, timeout=120)
+    lines = calls.read_text().splitlines()
+    assert r.returncode == 0 and len(lines) == 2, (r.stdout, r.stderr)
+    assert "--checkpoint" not in lines[0] and "--checkpoint" in lines[1]
+    assert "ran out of memory" in r.stderr and "finished after 1 restart" in r.stdout
