@@ -31,6 +31,8 @@ def recorded_ms(grid, transport=None):
 
 def judge(result, tolerance=0.10):
     """``(verdict, text)`` for one result line of ``bench.py``: verdict in ok / slower / inconclusive / unknown."""
+    if result.get("impl") == "reference":
+        return "unknown", "line of the reference arm: not compared"
     cfg = result.get("config", {})
     grid = tuple(cfg.get("grid") or ())
     if not grid and str(cfg.get("parallelism", "")).startswith("grid "):

@@ -350,6 +350,8 @@ def test_timing_regression_check(tmp_path, capsys):
     assert cr.judge(dict(line, ms_per_step=9.0, clocks=dict(reasons=["sw_thermal_slowdown"])))[0] == "inconclusive"
     assert cr.judge(dict(line, clocks=dict(reasons=["sw_power_cap"])))[0] == "ok"          # a power cap during dense kernels is normal
     assert cr.judge(dict(line, config=dict(grid=[3, 3])))[0] == "unknown"
+    assert cr.judge(dict(line, ms_per_step=40.6, impl="reference"))[0] == "unknown"       # the reference arm's lines are not judged
+    assert cr.judge(dict(ms_per_step=27.0, config=dict(parallelism="grid 1x1")))[0] == "slower"
     f = tmp_path / "lines.txt"
     f.write_text("NCCL version 2.28\n" + json.dumps(line) + "\n" + json.dumps(dict(line, ms_per_step=20.0, config=dict(grid=[1, 1]))) + "\n")
     assert cr.main(["--from_json", str(f)]) == 0
