@@ -29,7 +29,7 @@ def recorded_ms(grid, transport=None):
     return None
 
 
-def judge(result, tolerance=0.10):
+def assess(result, tolerance=0.10):
     """``(verdict, text)`` for one result line of ``bench.py``: verdict in ok / slower / inconclusive / unknown."""
     if result.get("impl") == "reference":
         return "unknown", "line of the reference arm: not compared"
@@ -92,7 +92,7 @@ def main(argv=None):
     results = [r for f in args.from_json for r in read_results(f)] if args.from_json else [run_bench(n, args.steps, args.warmup, extra) for n in args.gpus]
     verdicts = []
     for r in results:
-        v, text = judge(r, args.tolerance)
+        v, text = assess(r, args.tolerance)
         verdicts.append(v)
         print(f"[{v}] {text}")
     return 1 if "slower" in verdicts else (2 if "inconclusive" in verdicts else 0)

@@ -345,13 +345,13 @@ def test_timing_regression_check(tmp_path, capsys):
     from gt_b200.bench import check_regression as cr
     assert cr.recorded_ms((4, 2)) == 6.00 and cr.recorded_ms((3, 3)) is None
     line = dict(ms_per_step=6.2, config=dict(grid=[4, 2]), clocks=dict(reasons=[]))
-    assert cr.judge(line)[0] == "ok"
-    assert cr.judge(dict(line, ms_per_step=7.5))[0] == "slower"
-    assert cr.judge(dict(line, ms_per_step=9.0, clocks=dict(reasons=["sw_thermal_slowdown"])))[0] == "inconclusive"
-    assert cr.judge(dict(line, clocks=dict(reasons=["sw_power_cap"])))[0] == "ok"          # a power cap during dense kernels is normal
-    assert cr.judge(dict(line, config=dict(grid=[3, 3])))[0] == "unknown"
-    assert cr.judge(dict(line, ms_per_step=40.6, impl="reference"))[0] == "unknown"       # the reference arm's lines are not judged
-    assert cr.judge(dict(ms_per_step=27.0, config=dict(parallelism="grid 1x1")))[0] == "slower"
+    assert cr.assess(line)[0] == "ok"
+    assert cr.assess(dict(line, ms_per_step=7.5))[0] == "slower"
+    assert cr.assess(dict(line, ms_per_step=9.0, clocks=dict(reasons=["sw_thermal_slowdown"])))[0] == "inconclusive"
+    assert cr.assess(dict(line, clocks=dict(reasons=["sw_power_cap"])))[0] == "ok"          # a power cap during dense kernels is normal
+    assert cr.assess(dict(line, config=dict(grid=[3, 3])))[0] == "unknown"
+    assert cr.assess(dict(line, ms_per_step=40.6, impl="reference"))[0] == "unknown"       # the reference arm's lines are not compared
+    assert cr.assess(dict(ms_per_step=27.0, config=dict(parallelism="grid 1x1")))[0] == "slower"
     f = tmp_path / "lines.txt"
     f.write_text("NCCL version 2.28\n" + json.dumps(line) + "\n" + json.dumps(dict(line, ms_per_step=20.0, config=dict(grid=[1, 1]))) + "\n")
     assert cr.main(["--from_json", str(f)]) == 0
