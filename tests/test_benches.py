@@ -353,7 +353,7 @@ def test_timing_regression_check(tmp_path, capsys):
     assert cr.assess(dict(line, ms_per_step=40.6, impl="reference"))[0] == "unknown"       # the reference arm's lines are not compared
     assert cr.assess(dict(ms_per_step=27.0, config=dict(parallelism="grid 1x1")))[0] == "slower"
     f = tmp_path / "lines.txt"
-    f.write_text("NCCL version 2.28\n" + json.dumps(line) + "\n" + json.dumps(dict(line, ms_per_step=20.0, config=dict(grid=[1, 1]))) + "\n")
+    f.write_text("NCCL version 2.28\n" + json.dumps(line) + "\n" + json.dumps(dict(line, ms_per_step=19.0, config=dict(grid=[1, 1]))) + "\n")
     assert cr.main(["--from_json", str(f)]) == 0
     out = capsys.readouterr().out
     assert "[ok] grid 4x2" in out and "[ok] grid 1x1" in out
