@@ -135,6 +135,14 @@ class SymmetricHeap:
             if host == self.hosts[self.rank]:
                 self.peer_base[r] = self.base if r == self.rank else e.heap_open(h)
         self._local_groups = {}
+        per_host = {}
+        for r, host in enumerate(self.hosts):
+            per_host.setdefault(host, []).append(r)
+        # groups of one kind are all local or all remote only if every machine holds the same number of consecutive ranks
+        self.uniform_placement = len({len(v) for v in per_host.values()}) == 1 and all(v == list(range(v[0], v[0] + len(v))) for v in per_host.values())
+        if not self.uniform_placement and self.rank == 0:
+            print(f"[symm] ranks per machine {sorted(len(v) for v in per_host.values())}: groups of one kind may differ in transport between "
+                  "ranks; check_symmetric() will tell whether the heaps stay in step", flush=True)
         self.top = 0
         self.alloc_log = (0, 0)
         self.groups = {}
