@@ -213,6 +213,9 @@ def run_ours(args):
                        "comm": args.comm if world > 1 else "none",
                        "cuda_graph": not args.no_graph, "scale_down": args.scale_down,
                        "global_token": "dense terms" if args.token_dense else "edges of the sparse blocks",
+                       "grid_choice": ("default of this arm for %d GPUs: the benchmark's factorisation, row x column blocks oriented by the "
+                                       "performance model (--grid runs any other; the reference arm keeps its own)" % world) if not args.grid
+                       else "given with --grid",
                        "l2": "step working set (>2 GB of activations) exceeds the 126 MB L2; no explicit flush"},
             "clocks": clocks,
             "e2e": {"value": edges_layers / (ms_e2e * 1e-3), "unit": "edges/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
