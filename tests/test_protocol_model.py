@@ -106,3 +106,82 @@ def test_cli(capsys):
     assert pm.main(["--grid", "2", "2", "--layers", "2", "--copies", "1"]) == 1
     assert pm.main(["--grid", "2", "1", "--layers", "2", "--drop", "1", "x_col0", "1"]) == 1
     assert "expired: rank 0" in capsys.readouterr().out
+
+
+def _all_orders(trace):
+    """Brute force over every interleaving of a small trace that respects the waits: for each pair of conflicting accesses (same
+    location, different ranks, at least one write) the set of relative orders that occur; ``None`` if some interleaving gets stuck."""
+    world = trace.world
+    progs = trace.prog
+    orders = {}
+    stuck = [False]
+
+    def rec(pcs, counts, published, seen):
+        if all(pcs[r] == len(progs[r]) for r in range(world)):
+            return
+        moved = False
+        for r in range(world):
+            if pcs[r] == len(progs[r]):
+                continue
+            op, a, b, _, _ = progs[r][pcs[r]]
+            c2, p2, s2 = counts, published, seen
+            if op == "wait":
+                if published[b].get(a, 0) < counts[r].get(a, 0):
+                    continue
+            elif op == "signal":
+                k = counts[r].get(a, 0) + 1
+                c2 = [dict(c) for c in counts]; c2[r][a] = k
+                p2 = [dict(p) for p in published]; p2[r][a] = k
+            else:
+                me = (r, pcs[r], op, (a, b))
+                for other in seen:
+                    if other[3] == me[3] and other[0] != r and "write" in (op, other[2]):
+                        orders.setdefault(frozenset((other[:2], me[:2])), set()).add((other[:2], me[:2]))
+                s2 = seen + (me,)
+            moved = True
+            n = list(pcs); n[r] += 1
+            rec(tuple(n), c2, p2, s2)
+        if not moved:
+            stuck[0] = True
+
+    rec(tuple([0] * world), [dict() for _ in range(world)], [dict() for _ in range(world)], ())
+    return None if stuck[0] else orders
+
+
+def test_checker_agrees_with_brute_force_on_random_small_programs():
+    """The vector-clock verdict of one execution against the definition of a race (two conflicting accesses that occur in both orders
+    over all interleavings), on random programs of two or three ranks: it reports something if and only if a race exists."""
+    from hypothesis import assume, given, settings, strategies as st
+    bufs, chans = ["p", "q"], ["c", "d"]
+
+    def op_strategy(world):
+        return st.one_of(
+            st.tuples(st.just("write"), st.integers(0, world - 1), st.sampled_from(bufs)),
+            st.tuples(st.just("read"), st.integers(0, world - 1), st.sampled_from(bufs)),
+            st.tuples(st.just("signal"), st.sampled_from(chans)),
+            st.tuples(st.just("wait"), st.sampled_from(chans), st.integers(0, world - 1)))
+
+    @settings(max_examples=400, deadline=None, derandomize=True)
+    @given(st.integers(2, 3).flatmap(lambda w: st.tuples(st.just(w), st.lists(st.lists(op_strategy(w), min_size=1, max_size=4), min_size=w, max_size=w))))
+    def run(case):
+        world, programs = case
+        members = tuple(range(world))
+        tr = ProtocolTrace(world)
+        for r, ops in enumerate(programs):
+            for op in ops:
+                if op[0] == "write":
+                    tr.write(r, op[1], op[2], None)
+                elif op[0] == "read":
+                    tr.read(r, op[1], op[2], None)
+                elif op[0] == "signal":
+                    tr.signal(r, op[1], members)
+                else:
+                    tr.wait(r, op[1], members, op[2])
+        orders = _all_orders(tr)
+        assume(orders is not None)                           # programs that can get stuck are another matter (expiring waits)
+        racy = any(len(v) == 2 for v in orders.values())
+        rep = check(tr, require_writes=False)
+        assert rep.completed and not rep.expired
+        assert bool(rep.violations) == racy, (programs, rep.violations, orders)
+
+    run()
