@@ -185,3 +185,22 @@ def test_checker_agrees_with_brute_force_on_random_small_programs():
         assert bool(rep.violations) == racy, (programs, rep.violations, orders)
 
     run()
+
+
+def test_recorded_byte_ranges_conflict_exactly_when_they_overlap():
+    from hypothesis import given, settings, strategies as st
+    from gt_b200.utils.hb_check import trace_from_logs
+    rng = st.tuples(st.integers(0, 40), st.integers(1, 24))
+
+    @settings(max_examples=300, deadline=None, derandomize=True)
+    @given(rng, rng, st.booleans())
+    def run(a, b, synchronised):
+        logs = [[("write", 0, a[0], a[1])], [("read", 0, b[0], b[1])]]
+        if synchronised:                                     # rank 1 waits for rank 0's signal before it reads
+            logs[0].append(("signal", 1000, (0, 1)))
+            logs[1] = [("signal", 1000, (0, 1)), ("wait", 1000, 0)] + logs[1]
+        overlap = a[0] < b[0] + b[1] and b[0] < a[0] + a[1]
+        rep = check(trace_from_logs(logs), require_writes=False)
+        assert bool(rep.violations) == (overlap and not synchronised), (a, b, synchronised, rep.violations)
+
+    run()
