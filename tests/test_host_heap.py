@@ -434,3 +434,25 @@ def _refuse_worker(rank, world):
 
 def test_heap_refuses_groups_that_cross_machines():
     run_dist(_refuse_worker, 4)
+
+
+def test_edge_rows_from_a_segment_plan_match_the_csr_rows():
+    """The host kernels recover the row (or column) of every entry from a pass's segment list: hub rows cut into several segments,
+    empty rows, the longest-first order of the segments and the transposed (column) plan included."""
+    from gt_b200.attention.backend_cuda import _plan_list
+    from gt_b200.attention.csr import BlockCSR
+    from gt_b200.parallel.fused_host import _edge_rows
+    g = torch.Generator().manual_seed(5)
+    n_rows, n_cols = 300, 257
+    dst = torch.cat([torch.randint(0, n_rows, (2000,), generator=g), torch.full((900,), 7), torch.full((40,), 11)])      # rows 7 and 11 are hubs
+    src = torch.randint(0, n_cols, (dst.numel(),), generator=g)
+    ei = torch.unique(torch.stack([src, dst]), dim=1)
+    blk = BlockCSR.from_edges(ei, n_rows, n_cols, torch.zeros(ei.shape[1], dtype=torch.long))
+    for seg in (16, 64, 512):
+        plan = blk.row_plan(seg)
+        assert plan.num_segments > n_rows // 2 and int((plan.seg_end - plan.seg_beg).max()) <= seg
+        assert torch.equal(_edge_rows(_plan_list(plan), blk.num_edges), blk.rows().long())
+        _, rowidx, _, pos, _ = blk.csc()
+        cols = _edge_rows(_plan_list(blk.col_plan(seg)), blk.num_edges)
+        assert torch.equal(cols, blk.col.long()[pos.long()])                # the column of every CSC entry
+        assert torch.equal(rowidx.long(), blk.rows().long()[pos.long()])
