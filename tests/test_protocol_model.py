@@ -151,6 +151,7 @@ def _all_orders(trace):
 def test_checker_agrees_with_brute_force_on_random_small_programs():
     """The vector-clock verdict of one execution against the definition of a race (two conflicting accesses that occur in both orders
     over all interleavings), on random programs of two or three ranks: it reports something if and only if a race exists."""
+    pytest.importorskip("hypothesis")
     from hypothesis import assume, given, settings, strategies as st
     bufs, chans = ["p", "q"], ["c", "d"]
 
@@ -188,6 +189,7 @@ def test_checker_agrees_with_brute_force_on_random_small_programs():
 
 
 def test_recorded_byte_ranges_conflict_exactly_when_they_overlap():
+    pytest.importorskip("hypothesis")
     from hypothesis import given, settings, strategies as st
     from gt_b200.utils.hb_check import trace_from_logs
     rng = st.tuples(st.integers(0, 40), st.integers(1, 24))
