@@ -1,7 +1,8 @@
-"""Symmetric heap and peer-memory collectives (NVLink 5 / NVSwitch, one process per GPU on one node).
+"""Symmetric heap and peer-memory collectives (NVLink 5 / NVSwitch, one process per GPU).
 
-Every rank ``cudaMalloc``s one heap of the same size, exports it with CUDA IPC and opens the heaps of all peers, so
-every kernel can be given a table of peer base addresses.  Allocation inside the heap is a bump allocator that all
+Every rank ``cudaMalloc``s one heap of the same size, exports it with CUDA IPC and opens the heaps of the peers on its machine, so
+every kernel can be given a table of peer base addresses.  A job on several machines keeps one heap per rank all the same; a
+process group then runs on this transport if all of its ranks share a machine (``group_is_local``) and on NCCL otherwise.  Allocation inside the heap is a bump allocator that all
 ranks drive with the same sequence of requests: an object therefore lives at the same offset on every rank
 ("symmetric").  NCCL / gloo is only used once, to exchange the 64-byte IPC handles.
 
