@@ -299,3 +299,41 @@ exit 0
     assert r.returncode == 0 and len(lines) == 2, (r.stdout, r.stderr)
     assert "--checkpoint" not in lines[0] and "--checkpoint" in lines[1]
     assert "ran out of memory" in r.stderr and "finished after 1 restart" in r.stdout
+
+
+def _regrid_worker(rank, world, tmp):
+    """A checkpoint does not depend on the grid: saved on 2 x 1, resumed on 1 x 2, the run continues like the uninterrupted one."""
+    from gt_b200.train.train_dist import main
+    base = ["--synthetic", "cpu_small", "--scale_down", "4", "--fused", "--norm", "ln", "--dropout", "0.0", "--warmup", "1", "--lr", "5e-3", "--epochs", "6"]
+    main(["--grid", "2", "1"] + base + ["--metrics_jsonl", tmp + "/full.jsonl"])
+    ck = tmp + "/half.pt"
+
+    class Stop(Exception):
+        pass
+    from gt_b200.train import checkpoint as cp
+    real = cp.save_checkpoint
+
+    def save_then_stop(path, model, eng, epoch, extra=None):
+        real(path, model, eng, epoch, extra)
+        if epoch == 3:
+            raise Stop()
+    cp.save_checkpoint = save_then_stop
+    try:
+        with pytest.raises(Stop):
+            main(["--grid", "2", "1"] + base + ["--save", ck, "--save_every", "3"])
+    finally:
+        cp.save_checkpoint = real
+    import torch.distributed as dist
+    dist.barrier()
+    main(["--grid", "1", "2"] + base + ["--resume", ck, "--metrics_jsonl", tmp + "/resumed.jsonl"])
+
+
+def test_checkpoint_resumes_on_another_grid(tmp_path):
+    import json
+    run_dist(_regrid_worker, 2, str(tmp_path))
+    full = [json.loads(line) for line in open(tmp_path / "full.jsonl")]
+    res = [json.loads(line) for line in open(tmp_path / "resumed.jsonl")]
+    assert [r["epoch"] for r in res] == [3, 4, 5] or res[-1]["epoch"] == 5
+    last_full = [r for r in full if r["epoch"] == 5][0]
+    last_res = [r for r in res if r["epoch"] == 5][0]
+    assert abs(last_full["loss"] - last_res["loss"]) < 1e-4 * max(1.0, abs(last_full["loss"])), (last_full, last_res)
