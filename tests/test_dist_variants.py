@@ -257,3 +257,31 @@ def _stage_diff_worker(rank, world):
 
 def test_stage_by_stage_diff_tool():
     run_dist(_stage_diff_worker, 2)
+
+
+def test_state_dict_names_are_the_reference_names_for_every_layer_kind():
+    """The checkpoint contract: every distributed model exposes exactly the parameter and buffer names (and shapes) of its reference
+    model, whatever layer kind implements it, so a rank-0 ``state_dict()`` is a reference checkpoint and the other way round."""
+    from gt_b200.data.expander import random_regular_expander_edges
+    from gt_b200.data.synthetic import erdos_renyi, symmetrize
+    from gt_b200.models.exphormer_dist import DistExphormer
+    from gt_b200.models.exphormer_ref import ExphormerRef, gcn_edges_with_self_loops
+    from gt_b200.parallel.grid import make_grid
+    from gt_b200.train.engine import init_single_process_group
+    init_single_process_group("gloo")
+    n, f, hid, classes, heads = 64, 8, 16, 4, 4
+    ei = symmetrize(erdos_renyi(n, 4, seed=1), n)
+    exp = random_regular_expander_edges(n, 2, seed=1)
+    grid = make_grid((1, 1), n, n_pad=64)
+    g_blk, _ = grid.local_block(gcn_edges_with_self_loops(ei, n))
+    a_ei, a_et = ExphormerRef.build_attention_edges(ei, exp)
+    a_blk, a_bt = grid.local_block(a_ei, a_et)
+    for norm in ("bn", "ln", "rms"):
+        ref = ExphormerRef(f, hid, classes, 2, heads, norm=norm)
+        want = {k: tuple(v.shape) for k, v in ref.state_dict().items()}
+        for kw in (dict(), dict(fused=True), dict(fused=True, pipeline_sub=2), dict(fused=True, stream_sub=2), dict(fused=True, gather_proj=True),
+                   dict(ring=True)):
+            model = DistExphormer(grid, g_blk, a_blk, a_bt, f, hid, classes, 2, heads, backend="torch", norm=norm, **kw)
+            got = {k: tuple(v.shape) for k, v in model.state_dict().items()}
+            assert got == want, (norm, kw, sorted(set(got) ^ set(want)))
+            model.load_state_dict(ref.state_dict())            # and the reference checkpoint loads as it is
