@@ -285,3 +285,55 @@ def test_state_dict_names_are_the_reference_names_for_every_layer_kind():
             got = {k: tuple(v.shape) for k, v in model.state_dict().items()}
             assert got == want, (norm, kw, sorted(set(got) ^ set(want)))
             model.load_state_dict(ref.state_dict())            # and the reference checkpoint loads as it is
+
+
+def test_official_checkpoint_keys_load_into_the_reference_and_distributed_models():
+    """A state dict in the key layout of the official implementation (``MultiModel``: ``layers.i.models.1.self_attn.Q.weight`` ...) fills
+    the reference model and a distributed model; every tensor arrives where the key map says."""
+    import re
+    from gt_b200.models import exphormer_ref as er
+    from gt_b200.models.exphormer_dist import DistExphormer
+    from gt_b200.parallel.grid import make_grid
+    from gt_b200.train.engine import init_single_process_group
+    init_single_process_group("gloo")
+    torch.manual_seed(3)
+    src = er.ExphormerRef(8, 16, 4, 2, 4, norm="bn")
+    inv_layer = {v: k for k, v in er._LAYER_KEYS.items()}
+    inv_norm = {v: k for k, v in er._NORM_PREFIX.items()}
+    official = {}
+    for key, val in src.state_dict().items():
+        if key == "edge_type_emb.weight":
+            official["encoder.edge_encoder.encoder.weight"] = val[0:1].clone()
+            official["encoder.exp_edge_fixer.exp_edge_attr.weight"] = val[1:2].clone()
+        elif key == "pre_lin.weight":
+            official["pre_mp.Layer_0.layer.model.weight"] = val.clone()
+        elif key.startswith("pre_bn."):
+            official["pre_mp.Layer_0.post_layer.0." + key[7:]] = val.clone()
+        elif key.startswith("head."):
+            official["post_mp.layer_post_mp.model.0.model." + key[5:]] = val.clone()
+        else:
+            m = re.fullmatch(r"layers\.(\d+)\.(.+)", key)
+            rest = m.group(2)
+            if rest in inv_layer:
+                official[f"layers.{m.group(1)}.{inv_layer[rest]}"] = val.clone()
+            else:
+                pre = next(p for p in inv_norm if rest.startswith(p))
+                official[f"layers.{m.group(1)}.{inv_norm[pre]}{rest[len(pre):]}"] = val.clone()
+    assert all(er.official_to_ref_key(k) is not None for k in official) and er.official_to_ref_key("optimizer.state") is None
+    dst = er.ExphormerRef(8, 16, 4, 2, 4, norm="bn")
+    er.load_official_state_dict(dst, official)
+    for k, v in src.state_dict().items():
+        assert torch.equal(dst.state_dict()[k], v), k
+    n = 32
+    from gt_b200.data.synthetic import erdos_renyi, symmetrize
+    from gt_b200.data.expander import random_regular_expander_edges
+    ei = symmetrize(erdos_renyi(n, 3, seed=1), n)
+    grid = make_grid((1, 1), n, n_pad=32)
+    a_ei, a_et = er.ExphormerRef.build_attention_edges(ei, random_regular_expander_edges(n, 2, seed=1))
+    model = DistExphormer(grid, grid.local_block(er.gcn_edges_with_self_loops(ei, n))[0], *grid.local_block(a_ei, a_et), 8, 16, 4, 2, 4, backend="torch",
+                          fused=True)
+    er.load_official_state_dict(model, official)
+    for k, v in src.state_dict().items():
+        assert torch.equal(model.state_dict()[k], v), k
+    with pytest.raises(KeyError):
+        er.load_official_state_dict(dst, dict(official, **{"encoder.node_encoder.weight": torch.zeros(1)}))
