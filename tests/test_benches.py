@@ -360,3 +360,16 @@ def test_timing_regression_check(tmp_path, capsys):
     g = tmp_path / "slow.json"
     g.write_text(json.dumps(dict(line, ms_per_step=8.0)))
     assert cr.main(["--from_json", str(g), "--tolerance", "0.2"]) == 1
+
+
+def test_every_module_of_the_package_imports_without_a_gpu():
+    import importlib
+    import pkgutil
+    import gt_b200
+    bad = []
+    for m in pkgutil.walk_packages(gt_b200.__path__, "gt_b200."):
+        try:
+            importlib.import_module(m.name)
+        except Exception as exc:                             # noqa: BLE001
+            bad.append((m.name, repr(exc)[:200]))
+    assert not bad, bad
