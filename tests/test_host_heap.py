@@ -456,3 +456,46 @@ def test_edge_rows_from_a_segment_plan_match_the_csr_rows():
         cols = _edge_rows(_plan_list(blk.col_plan(seg)), blk.num_edges)
         assert torch.equal(cols, blk.col.long()[pos.long()])                # the column of every CSC entry
         assert torch.equal(rowidx.long(), blk.rows().long()[pos.long()])
+
+
+def test_every_python_call_into_the_native_module_passes_the_bound_number_of_arguments():
+    """Static drift guard: the bindings declare no default arguments, so every ``ext().f(...)`` / ``e.f(...)`` call in the package must
+    pass exactly as many positional arguments as the bound function takes (a wrong count would only fail when that line runs on a GPU)."""
+    import ast
+    import glob
+    from gt_b200 import build_ext
+    mod = build_ext.load_prebuilt()
+    if mod is None:
+        pytest.skip("the native module is not built here")
+
+    def arity(fn):
+        doc = fn.__doc__.splitlines()[0]
+        inner = doc[doc.index("(") + 1:doc.rindex(")")]
+        depth, n = 0, 1 if inner.strip() else 0
+        for ch in inner:
+            depth += ch in "[("
+            depth -= ch in "])"
+            n += ch == "," and depth == 0
+        return n
+    bound = {name: arity(getattr(mod, name)) for name in dir(mod) if not name.startswith("_") and callable(getattr(mod, name))}
+
+    def is_ext(node):                                        # e, ext(), native.ext(), self.ext() ...
+        if isinstance(node, ast.Name):
+            return node.id == "e"
+        if isinstance(node, ast.Call):
+            f = node.func
+            return (isinstance(f, ast.Name) and f.id == "ext") or (isinstance(f, ast.Attribute) and f.attr == "ext")
+        return False
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gt_b200")
+    checked, wrong = 0, []
+    for path in glob.glob(os.path.join(root, "**", "*.py"), recursive=True):
+        tree = ast.parse(open(path).read())
+        for node in ast.walk(tree):
+            if isinstance(node, ast.Call) and isinstance(node.func, ast.Attribute) and node.func.attr in bound and is_ext(node.func.value):
+                if any(isinstance(a, ast.Starred) for a in node.args):
+                    continue
+                checked += 1
+                if node.keywords or len(node.args) != bound[node.func.attr]:
+                    wrong.append((os.path.relpath(path, root), node.lineno, node.func.attr, len(node.args), bound[node.func.attr]))
+    assert not wrong, wrong
+    assert checked >= 80, checked
