@@ -486,9 +486,11 @@ def test_every_python_call_into_the_native_module_passes_the_bound_number_of_arg
             f = node.func
             return (isinstance(f, ast.Name) and f.id == "ext") or (isinstance(f, ast.Attribute) and f.attr == "ext")
         return False
-    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gt_b200")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     checked, wrong = 0, []
-    for path in glob.glob(os.path.join(root, "**", "*.py"), recursive=True):
+    files = glob.glob(os.path.join(root, "gt_b200", "**", "*.py"), recursive=True) + glob.glob(os.path.join(root, "tests", "*.py")) \
+        + [os.path.join(root, "bench.py")]
+    for path in files:
         tree = ast.parse(open(path).read())
         for node in ast.walk(tree):
             if isinstance(node, ast.Call) and isinstance(node.func, ast.Attribute) and node.func.attr in bound and is_ext(node.func.value):
