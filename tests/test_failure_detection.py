@@ -160,3 +160,24 @@ def _alloc_log_worker(rank, world):
 def test_symmetric_heap_allocation_logs_are_compared_across_ranks():
     from dist_utils import run_dist
     run_dist(_alloc_log_worker, 4)
+
+
+def test_every_polling_loop_in_the_kernel_sources_is_bounded():
+    """Source check of the rule that no device wait may spin for ever: every ``while`` loop that polls a peer flag, an mbarrier or an
+    asynchronous-copy group names a limit (a spin count or a clock budget) in its condition or in the lines right below it."""
+    import glob
+    import os
+    import re
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gt_b200", "csrc")
+    poll = re.compile(r"while\s*\(.*(ld_acquire|try_wait|test_wait|volatile|ld_relaxed|\*flag|->flag)")
+    bound = re.compile(r"spins|kWaitCycles|clock64|tries|max_iter|limit", re.I)
+    found, unbounded = 0, []
+    for path in sorted(glob.glob(os.path.join(root, "*.cu")) + glob.glob(os.path.join(root, "*.cuh")) + glob.glob(os.path.join(root, "*.h"))):
+        lines = open(path).read().splitlines()
+        for i, line in enumerate(lines):
+            if poll.search(line) and not line.lstrip().startswith("//"):
+                found += 1
+                if not bound.search(" ".join(lines[i:i + 4])):
+                    unbounded.append((os.path.basename(path), i + 1, line.strip()))
+    assert found >= 12, found
+    assert not unbounded, unbounded
