@@ -13,8 +13,9 @@ collective.  Both pieces are dense and tiny, so they need not be edges at all:
 
 ``DenseToken.add`` does this to the unnormalised ``(acc, l)`` of the owned rows (the partial-softmax state adds, which is why the
 clamp-exp weights of the Exphormer layer allow it), with torch operations that autograd differentiates; the token's features travel
-to all ranks as a sum in which only the owner's term is non-zero.  It needs the owned rows' Q, K and V, i.e. three ``[O, d] x [d, d]``
-products per layer beside the block projections of the sparse path.  The sparse structure is then built without the token's
+to all ranks as a sum in which only the owner's term is non-zero.  Scores against one key (or from one query) are linear in ``x``, so
+the owned rows' Q, K and V are never formed: per layer two ``[O, d] x [d, H]`` products, one ``[H, O] x [O, d]`` product and one update
+of ``acc`` beside the block projections of the sparse path.  The sparse structure is then built without the token's
 edges (``exphormer_workload(token_dense=True)``, ``train_dist --token_dense``).
 
 Every rank must run the same collectives in forward and backward, so every term is tied to ``x`` on every rank (with a zero factor
@@ -25,7 +26,6 @@ its kernel benchmarks do (``gt3d/bench/bench_attention_single_gpu.py:89-97``), a
 """
 import torch
 
-from ..ops import functional as K
 from .collectives import all_reduce_sum
 
 
@@ -60,18 +60,21 @@ class DenseToken:
         onehot, mask = self.onehot.to(ct), self.others.to(ct).unsqueeze(1)
         # the token's features on every rank: a sum over ranks in which only the owner's term is non-zero
         x_t = all_reduce_sum(self._pad8((x.to(ct) * onehot.unsqueeze(1)).sum(0)))[:x.shape[1]]
-        wq, wk, wv = layer.q.weight.to(ct), layer.k.weight.to(ct), layer.v.weight.to(ct)
-        q_t, k_t, v_t = (x_t @ wq.t()).view(h, d), (x_t @ wk.t()).view(h, d), (x_t @ wv.t()).view(h, d)
-        q = K.linear(x, layer.q.weight).to(ct).view(o, h, d)
-        k = K.linear(x, layer.k.weight).to(ct).view(o, h, d)
-        v = K.linear(x, layer.v.weight).to(ct).view(o, h, d)
-        # column of the token: one more source for every owned row
-        p_col = torch.exp((((q * g2) * k_t).sum(-1) * scale).clamp(c_lo, c_hi)) * mask
+        din = x.shape[1]
+        wq, wk, wv = (w.weight.to(ct).view(h, d, din) for w in (layer.q, layer.k, layer.v))
+        q_t, k_t, v_t = (torch.einsum("hdi,i->hd", w, x_t) for w in (wq, wk, wv))
+        xc = x.to(ct)
+        # Scores against ONE key (or from ONE query) are linear in x: s_i[h] = x_i . u[h] with u[h] = scale * W_q[h]^T (g_2[h] * k_t[h]), so
+        # the owned rows' Q, K and V are never formed: two [O, d_in] x [d_in, H] products and one [H, O] x [O, d_in] product replace
+        # three [O, d_in] x [d_in, H d] projections, and every element-wise pass below runs on [O, H].
+        u_col = torch.einsum("hd,hdi->hi", g2 * k_t, wq) * scale
+        p_col = torch.exp((xc @ u_col.t()).clamp(c_lo, c_hi)) * mask                 # column of the token: one more source per owned row
         acc = acc + p_col.unsqueeze(-1) * v_t
         l = l + p_col
-        # row of the token: partial sums over the owned nodes, completed by one small all-reduce
-        p_row = torch.exp(((k * (q_t * g2)).sum(-1) * scale).clamp(c_lo, c_hi)) * mask
-        part = torch.cat([(p_row.unsqueeze(-1) * v).sum(0).reshape(-1), p_row.sum(0)])
+        u_row = torch.einsum("hd,hdi->hi", g2 * q_t, wk) * scale
+        p_row = torch.exp((xc @ u_row.t()).clamp(c_lo, c_hi)) * mask                 # row of the token: weights of the owned nodes
+        z = p_row.t() @ xc                                                           # [H, d_in]: sum_j p_j x_j per head
+        part = torch.cat([torch.einsum("hi,hdi->hd", z, wv).reshape(-1), p_row.sum(0)])
         tot = all_reduce_sum(self._pad8(part))
         acc = acc + onehot.view(o, 1, 1) * tot[:hd].view(1, h, d)
         l = l + onehot.view(o, 1) * tot[hd:hd + h].view(1, h)

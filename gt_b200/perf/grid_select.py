@@ -305,11 +305,12 @@ def fused_layer_ms(pd, po, g: Graph, m: Model, gpn=GPUS_PER_NODE):
     bw["spmm"] = spmm_ms(eg, C, R, d, g.skew) if m.with_gcn else 0.0
     bw["gemm"] = gemm_ms(proj, d, 1) + gemm_ms(proj, d, 2)
     if g.token and m.token_dense:
-        # Q, K and V of the owned rows, about a dozen element-wise passes over [O, d] fp32 in some twenty small kernels, and two
-        # all-reduces of a few hundred numbers per direction (an estimate from the model's primitives: not measured)
+        # two [O, d] x [d, H] products and one [H, O] x [O, d] product (at the GEMM floor), one cast of x and one update of acc
+        # ([O, d] fp32 read + write), a dozen small kernels on [O, H], and two all-reduces of a few hundred numbers per direction
+        # (an estimate from the model's primitives: not measured)
         small = coll_ms("ar", (min(P, gpn), max(1, P // gpn)), 4 * (d + H + 8), m.transport)
-        f["token"] = 3 * gemm_ms(2 * O * d * d, d, 0) + ew_ms(O * d * 4 * 12, 20) + 2 * small
-        bw["token"] = 3 * (gemm_ms(2 * O * d * d, d, 1) + gemm_ms(2 * O * d * d, d, 2)) + ew_ms(O * d * 4 * 24, 40) + 2 * small
+        f["token"] = 3 * gemm_ms(2 * O * d * H, d, 0) + ew_ms(O * d * (2 + 4 + 8), 16) + 2 * small
+        bw["token"] = 6 * gemm_ms(2 * O * d * H, d, 1) + ew_ms(O * d * (4 + 8 + 8), 32) + 2 * small
     if m.transport == "p2p" and not m.sparse_comm and pl["row"][1] == 1 and pl["col"][1] == 1:
         # (both groups within one machine; a group that crosses machines takes the operator off the peer-memory path and the layer
         # runs with NCCL collectives for that group: the branch below is then the estimate)
