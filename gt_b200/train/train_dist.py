@@ -444,6 +444,13 @@ def main(argv=None):
                   f"forward_ms={ms:.2f} grid={'x'.join(map(str, args.grid))} world={world}", flush=True)
         return dict(eval=acc, epoch=start_epoch, forward_ms=ms)
     best = dict(val=-1.0, test=0.0, epoch=-1)
+    host_ms = []                                             # host time to ENQUEUE a step (no synchronisation inside)
+
+    def enqueue_step():
+        t0 = time.perf_counter()
+        out = eng.train_step(loss_fn)
+        host_ms.append((time.perf_counter() - t0) * 1e3)
+        return out
     epoch_ms = []
     hb = None
     if args.heartbeat > 0 and world > 1:
@@ -473,9 +480,9 @@ def main(argv=None):
             hb.check(wait_for_first=60.0 if epoch == start_epoch else 0.0)
         with prof_ctx, census_ctx:
             if hb is not None:
-                loss, ms = hb.guarded(device_epoch_ms, lambda: eng.train_step(loss_fn), dev)      # an exception here is announced to the peers
+                loss, ms = hb.guarded(device_epoch_ms, enqueue_step, dev)      # an exception here is announced to the peers
             else:
-                loss, ms = device_epoch_ms(lambda: eng.train_step(loss_fn), dev)
+                loss, ms = device_epoch_ms(enqueue_step, dev)
         if cstats is not None:
             cstats.end_epoch(keep=epoch >= start_epoch + 2)
         epoch_ms.append(ms)
@@ -518,6 +525,20 @@ def main(argv=None):
         cstats.report()
     if args.timers:
         timers().report(divide_by=max(len(epoch_ms) - 2, 1))
+        # Host-side enqueue time of a step per rank (epochs 2+): close to the device time means the step is paced by the host (launch /
+        # autograd bound; a captured step enqueues in a fraction of it); the spread over ranks is skew the collectives absorb
+        # (the reference prints the same for its backward pass, gt3d/gt3d/train/train_dist.py:609-615,655-664).
+        keep = host_ms[2:] if len(host_ms) > 2 else host_ms
+        mine = torch.tensor([sum(keep) / max(len(keep), 1)], dtype=torch.float64, device=dev)
+        every = [torch.zeros_like(mine) for _ in range(world)]
+        if world > 1:
+            dist.all_gather(every, mine)
+        else:
+            every = [mine]
+        if rank == 0:
+            vals = [float(v.item()) for v in every]
+            print(f"[cpu] step enqueue ms per epoch: min {min(vals):.2f} max {max(vals):.2f} mean {sum(vals) / len(vals):.2f} | per rank: "
+                  + " ".join(f"{v:.1f}" for v in vals), flush=True)
     steady = epoch_ms[2:] if len(epoch_ms) > 2 else epoch_ms
     peak = torch.tensor([torch.cuda.max_memory_allocated() / 2 ** 30 if cuda else 0.0], device=dev)
     if world > 1:
