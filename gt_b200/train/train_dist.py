@@ -378,6 +378,11 @@ def main(argv=None):
             print("[comm] " + str(len(set(heap.hosts))) + " machines: " + ", ".join(
                 f"{k} group on {'peer memory' if heap.group_is_local(g) else 'NCCL'}" for k, g in kinds)
                 + f", gradient all-reduce on {'peer memory' if heap.group_is_local(None) else 'NCCL'}", flush=True)
+        if hasattr(model, "compaction_stats"):
+            tot, ne = model.compaction_stats()
+            if tot > 0:                                      # streamed / pipelined layers: how hypersparse the sub-blocks are
+                print(f"[compact] attention (row, sub-block) pairs with edges: {ne}/{tot} = {100 * ne / tot:.1f}% "
+                      "(the rows the compact-accumulate kernels visit)", flush=True)
         if args.sparse_comm and getattr(model, "sparse_info", None):
             inf = model.sparse_info
             print(f"[sparse_comm] row share {inf['row_share']:.3f} -> {'SPARSE' if inf['use_row'] else 'dense'}; "
