@@ -235,10 +235,34 @@ def _auto_grid(args, world, n, e_graph, f_in, rank):
     return list(best.grid)
 
 
+def nccl_tune(args):
+    """``--nccl_tune``: raise NCCL's channel count for ring collectives (``NCCL_MIN_NCHANNELS=16``, ``NCCL_ALGO=Ring``, only where the
+    environment does not set them) BEFORE the communicators are created.  ``auto`` does so only when the job spans several machines
+    and the column group of the grid crosses them (its reduce-scatter then runs over the network, the case the reference tunes:
+    ``gt3d/gt3d/train/train_dist.py:230-280``), and never with ``--sparse_comm`` (the setting slows the all-to-all-v); inside one
+    NVSwitch domain NCCL's defaults are kept.  ``on`` forces it, ``off`` skips it.  Returns the line that rank 0 prints."""
+    from ..perf.grid_select import placement
+    if args.nccl_tune == "off":
+        return None
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    gpn = max(1, int(os.environ.get("LOCAL_WORLD_SIZE", str(world))))
+    dims = list(args.grid) + [1] * (3 - len(args.grid))
+    k, m = placement(dims[0], dims[1], dims[2], gpn)["col"]
+    want = args.nccl_tune == "on" or (world > gpn and m > 1 and not args.sparse_comm)
+    if want:
+        os.environ.setdefault("NCCL_MIN_NCHANNELS", "16")
+        os.environ.setdefault("NCCL_ALGO", "Ring")
+    setting = f"NCCL_MIN_NCHANNELS={os.environ.get('NCCL_MIN_NCHANNELS')} NCCL_ALGO={os.environ.get('NCCL_ALGO')}" if want else "NCCL defaults"
+    return f"[nccl_tune] {max(1, world // gpn)} machine(s), column group layout {k}x{m} -> {setting}"
+
+
 def main(argv=None):
     args = parse_with_config(build_parser(), argv)
     head_grid = validate(args)
+    tune_line = nccl_tune(args) if not dist.is_initialized() else None
     init_dist()
+    if tune_line and dist.get_rank() == 0:
+        print(tune_line, flush=True)
     rank, world = dist.get_rank(), dist.get_world_size()
     cuda = torch.cuda.is_available()
     dev = torch.device("cuda", torch.cuda.current_device()) if cuda else torch.device("cpu")

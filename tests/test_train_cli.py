@@ -337,3 +337,21 @@ def test_checkpoint_resumes_on_another_grid(tmp_path):
     last_full = [r for r in full if r["epoch"] == 5][0]
     last_res = [r for r in res if r["epoch"] == 5][0]
     assert abs(last_full["loss"] - last_res["loss"]) < 1e-4 * max(1.0, abs(last_full["loss"])), (last_full, last_res)
+
+
+def test_nccl_tune_only_touches_the_environment_when_the_column_group_crosses_machines(monkeypatch):
+    from gt_b200.train import train_dist as td
+    for var in ("NCCL_ALGO", "NCCL_MIN_NCHANNELS"):
+        monkeypatch.delenv(var, raising=False)
+    parse = td.build_parser().parse_args
+    monkeypatch.setenv("WORLD_SIZE", "8"); monkeypatch.setenv("LOCAL_WORLD_SIZE", "8")
+    assert "NCCL defaults" in td.nccl_tune(parse(["--grid", "4", "2"])) and "NCCL_ALGO" not in os.environ
+    monkeypatch.setenv("WORLD_SIZE", "32")
+    assert "NCCL defaults" in td.nccl_tune(parse(["--grid", "4", "8", "--sparse_comm"])) and "NCCL_ALGO" not in os.environ
+    assert td.nccl_tune(parse(["--grid", "4", "8", "--nccl_tune", "off"])) is None
+    line = td.nccl_tune(parse(["--grid", "4", "8"]))
+    assert "4 machine(s)" in line and os.environ["NCCL_ALGO"] == "Ring" and os.environ["NCCL_MIN_NCHANNELS"] == "16"
+    monkeypatch.delenv("NCCL_ALGO"); monkeypatch.delenv("NCCL_MIN_NCHANNELS")
+    monkeypatch.setenv("WORLD_SIZE", "8")
+    assert "NCCL_ALGO=Ring" in td.nccl_tune(parse(["--grid", "4", "2", "--nccl_tune", "on"]))
+    monkeypatch.delenv("NCCL_ALGO"); monkeypatch.delenv("NCCL_MIN_NCHANNELS")
